@@ -1,0 +1,182 @@
+/*
+ * C-ABI of libnumba_mlir_gpu_runtime_cuda.so -- the CUDA (sm_100a) replacement
+ * for numba-mlir's SYCL GPU runtime.
+ *
+ * Every symbol has C linkage, takes plain pointers and sizes, and is what the
+ * JIT-generated host code of numba-mlir binds by name (the reference registers
+ * these names in numba_mlir/numba_mlir/mlir/gpu_runtime.py:34-81 and emits the
+ * calls in mlir/lib/Conversion/GpuRuntimeToLlvm.cpp:95-194).  Each declaration
+ * cites the reference definition it replaces.
+ *
+ * Error model.  The reference prints to stdout and abort()s on any failure
+ * (numba_mlir_gpu_runtime_sycl/lib/Utils.hpp:8-21).  This library records the
+ * message in a sticky per-process slot (gpuxGetLastError), prints it to stderr
+ * and returns NULL / does nothing; set NUMBA_MLIR_GPU_RUNTIME_ABORT=1 to get
+ * the reference's abort() behaviour.
+ */
+#ifndef NUMBA_MLIR_GPU_RUNTIME_CUDA_H
+#define NUMBA_MLIR_GPU_RUNTIME_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- shared types: numba_mlir_gpu_common/GpuCommon.hpp:30-64 ------------- */
+
+/* GpuAllocType, GpuCommon.hpp:30 */
+enum {
+  GPUX_ALLOC_DEVICE = 0,
+  GPUX_ALLOC_SHARED = 1,
+  GPUX_ALLOC_LOCAL = 2,
+  GPUX_ALLOC_HOST = 3
+};
+
+/* GpuParamType, GpuCommon.hpp:32-42 */
+enum {
+  GPUX_PARAM_NULL = 0,
+  GPUX_PARAM_BOOL = 1,
+  GPUX_PARAM_INT8 = 2,
+  GPUX_PARAM_INT16 = 3,
+  GPUX_PARAM_INT32 = 4,
+  GPUX_PARAM_INT64 = 5,
+  GPUX_PARAM_FLOAT32 = 6,
+  GPUX_PARAM_FLOAT64 = 7,
+  GPUX_PARAM_PTR = 8
+};
+
+/* GPUParamDesc, GpuCommon.hpp:45-55: `data` points AT the argument value.
+ * A GPUX_PARAM_PTR entry with data == NULL asks for `size` bytes of
+ * work-group-local memory; the kernel receives, in that pointer-sized slot,
+ * the byte offset of the region inside its dynamic shared memory.
+ * The array is terminated by {NULL, 0, GPUX_PARAM_NULL}. */
+typedef struct GPUXParamDesc {
+  const void *data;
+  int32_t size;
+  int32_t type;
+} GPUXParamDesc;
+
+/* GPUAllocResult, GpuCommon.hpp:61-64 */
+typedef struct GPUXAllocResult {
+  void *ptr;
+  void *event;
+} GPUXAllocResult;
+
+/* Memref<2,T>, numba_mlir/numba_mlir/math_runtime/include/Common.hpp:17-23.
+ * dims and strides are in ELEMENTS. */
+typedef struct GPUXMemref2f {
+  void *userData;
+  float *data;
+  size_t offset;
+  size_t dims[2];
+  size_t strides[2];
+} GPUXMemref2f;
+
+/* ---- the 13 reference exports -------------------------------------------- */
+
+/* numba_mlir_gpu_runtime_sycl/lib/GpuRuntime.cpp:361.  deviceName: NULL or ""
+ * (-> $NUMBA_MLIR_DEFAULT_DEVICE, else device 0), "cuda", "cuda:N",
+ * "cuda:gpu:N", "gpu:N" or "N".  The queue is refcounted; buffers and events
+ * created from it keep it alive (GpuRuntime.cpp:248-260,287-300). */
+void *gpuxQueueCreate(const char *deviceName);
+/* GpuRuntime.cpp:367 */
+void gpuxQueueDestroy(void *queue);
+/* GpuRuntime.cpp:373.  The blob is one of: an sm_100a cubin / fatbin, PTX
+ * text, CUDA C source prefixed by the line "//NMB200:CUDA-SOURCE" (compiled
+ * with NVRTC for sm_100a, the analogue of the driver JIT the reference gets
+ * from zeModuleCreate on SPIR-V), or the text "NMB200:BUILTIN" which names the
+ * hand-written kernels linked into this library. */
+void *gpuxModuleLoad(void *queue, const void *data, size_t dataSize);
+/* GpuRuntime.cpp:379 */
+void gpuxModuleDestroy(void *module);
+/* GpuRuntime.cpp:385 */
+void *gpuxKernelGet(void *module, const char *name);
+/* GpuRuntime.cpp:393 */
+void gpuxKernelDestroy(void *kernel);
+/* GpuRuntime.cpp:399.  grid* are group counts, block* group sizes; events is
+ * a NULL-terminated array of event handles; params a GPUXParamDesc array.
+ * Returns an event to pass to gpuxWait / gpuxDestroyEvent. */
+void *gpuxLaunchKernel(void *queue, void *kernel, size_t gridX, size_t gridY,
+                       size_t gridZ, size_t blockX, size_t blockY,
+                       size_t blockZ, void *events, void *params);
+/* GpuRuntime.cpp:412 */
+void gpuxWait(void *queue, void *event);
+/* GpuRuntime.cpp:419 */
+void gpuxDestroyEvent(void *queue, void *event);
+/* GpuRuntime.cpp:427.  type is a GPUX_ALLOC_* value; LOCAL yields ptr NULL. */
+void gpuxAlloc(void *queue, size_t size, size_t alignment, int type,
+               void *events, GPUXAllocResult *ret);
+/* GpuRuntime.cpp:439 */
+void gpuxDeAlloc(void *queue, void *ptr);
+/* GpuRuntime.cpp:445, heuristic of GpuModule.cpp:453-509: gridSize holds the
+ * GLOBAL sizes; dimensions of size <= 1 get block size 1. */
+void gpuxSuggestBlockSize(void *queue, void *kernel, const uint32_t *gridSize,
+                          uint32_t *blockSize, size_t numDims);
+/* GpuRuntime.cpp:455.  The reference copies a native sycl::queue; here the
+ * native handle is a cudaStream_t (NULL = the legacy default stream) of the
+ * current device and the result is a queue handle that launches on it. */
+void *gpuxDuplicateQueue(void *nativeStream);
+
+/* Device BLAS entry: math_runtime/sycl/lib/NumpyLinalg.cpp:166-175, bound as
+ * "_mlir_ciface_mkl_gemm_float32_device" (mlir/math_runtime.py:20-40).
+ * C = alpha * A @ B + beta * C; every operand needs one unit stride
+ * (NumpyLinalg.cpp:73-86).  Blocking, like the reference's .wait(). */
+void _mlir_ciface_mkl_gemm_float32_device(void *queue, const GPUXMemref2f *a,
+                                          const GPUXMemref2f *b, float alpha,
+                                          float beta, GPUXMemref2f *c);
+void mkl_gemm_float32_device(void *queue, const GPUXMemref2f *a,
+                             const GPUXMemref2f *b, float alpha, float beta,
+                             GPUXMemref2f *c);
+
+/* ---- extensions (no counterpart in the reference, where dpctl moved the
+ * data: mlir/tests/test_gpu.py:52-87) ------------------------------------- */
+
+enum { GPUX_COPY_H2D = 0, GPUX_COPY_D2H = 1, GPUX_COPY_D2D = 2, GPUX_COPY_DEFAULT = 3 };
+/* Asynchronous copy on the queue's stream; returns an event. */
+void *gpuxMemcpy(void *queue, void *dst, const void *src, size_t bytes,
+                 int kind, void *events);
+/* Asynchronous byte fill on the queue's stream; returns an event. */
+void *gpuxMemset(void *queue, void *dst, int value, size_t bytes, void *events);
+/* Records an event at the current tail of the queue's stream. */
+void *gpuxRecordEvent(void *queue);
+/* Milliseconds between two completed events of the same device. */
+float gpuxEventElapsedMs(void *startEvent, void *endEvent);
+/* Blocks until everything submitted to the queue has finished. */
+void gpuxQueueSynchronize(void *queue);
+/* cudaStream_t of the queue (role of GPUQueueInterface::getQueue,
+ * GpuCommon.hpp:25-27) and its CUDA device ordinal. */
+void *gpuxQueueGetStream(void *queue);
+int gpuxQueueGetDevice(void *queue);
+/* Sticky error message of the last failed call (NULL when none). */
+const char *gpuxGetLastError(void);
+void gpuxClearLastError(void);
+/* Number of kernels launched by this library since load (all queues). */
+uint64_t gpuxLaunchCount(void);
+
+/* Host-only: NVRTC-compiles a "//NMB200:CUDA-SOURCE" blob to an sm_100a cubin
+ * without touching a device; the result is malloc()ed, release it with
+ * gpuxFreeHostBlob. */
+void *gpuxCompileToCubin(const void *data, size_t dataSize, size_t *outSize);
+void gpuxFreeHostBlob(void *blob);
+/* '\n'-separated names of the kernels behind the "NMB200:BUILTIN" module. */
+const char *gpuxBuiltinKernelNames(void);
+
+/* Library routine surfaced the way the reference surfaces device library
+ * calls (external_call + "gpu_runtime.device_func",
+ * mlir/numpy/funcs.py:780-785): D[i,j] = sqrt(max(|x_i|^2 + |y_j|^2 -
+ * 2 x_i.y_j, 0)) with the dot products on tcgen05 tensor cores (3xTF32).
+ * Semantics follow the reference's pairwise kernels
+ * (mlir/tests/test_gpu.py:1396-1430,2226-2266).  x: (M,K), y: (N,K),
+ * d: (M,N), row-major float32 with unit inner stride.  Asynchronous on the
+ * queue's stream; returns an event. */
+void *_mlir_ciface_nmb_pairwise_distance_float32_device(void *queue,
+                                                        const GPUXMemref2f *x,
+                                                        const GPUXMemref2f *y,
+                                                        GPUXMemref2f *d);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NUMBA_MLIR_GPU_RUNTIME_CUDA_H */

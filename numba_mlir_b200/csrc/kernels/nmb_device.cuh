@@ -1,0 +1,215 @@
+// Device-side support library for sm_100a.
+//
+// Included by the hand-written kernels linked into the runtime and handed,
+// under the name "nmb_device.cuh", to every NVRTC compilation of generated
+// code (fused ufunc chains and @kernel bodies).  It must therefore compile
+// without any system header.
+#pragma once
+
+#ifdef __CUDACC_RTC__
+typedef signed char int8_t;
+typedef unsigned char uint8_t;
+typedef short int16_t;
+typedef unsigned short uint16_t;
+typedef int int32_t;
+typedef unsigned int uint32_t;
+typedef long long int64_t;
+typedef unsigned long long uint64_t;
+#else
+#include <cstdint>
+#endif
+
+namespace nmb {
+
+// ---------------------------------------------------------------- vectors ---
+// N consecutive elements moved with one (or two, for 8-byte types) 128-bit
+// access.  The alignment makes the compiler emit ld/st.global.v4.
+template <typename T, int N> struct alignas(sizeof(T) * N <= 16 ? sizeof(T) * N : 16) Vec {
+  T v[N];
+};
+
+// Streaming (read-once) load: bypass L1 allocation, mark evict-first in L2.
+template <typename T, int N>
+__device__ __forceinline__ Vec<T, N> load_stream(const T *p) {
+  Vec<T, N> r;
+  if constexpr (sizeof(T) * N == 16) {
+    int4 raw = __ldcs(reinterpret_cast<const int4 *>(p));
+    r = *reinterpret_cast<Vec<T, N> *>(&raw);
+  } else if constexpr (sizeof(T) * N == 32) {
+    int4 raw0 = __ldcs(reinterpret_cast<const int4 *>(p));
+    int4 raw1 = __ldcs(reinterpret_cast<const int4 *>(p) + 1);
+    *reinterpret_cast<int4 *>(&r.v[0]) = raw0;
+    *reinterpret_cast<int4 *>(&r.v[N / 2]) = raw1;
+  } else if constexpr (sizeof(T) * N == 8) {
+    int2 raw = __ldcs(reinterpret_cast<const int2 *>(p));
+    r = *reinterpret_cast<Vec<T, N> *>(&raw);
+  } else if constexpr (sizeof(T) * N == 4) {
+    int raw = __ldcs(reinterpret_cast<const int *>(p));
+    r = *reinterpret_cast<Vec<T, N> *>(&raw);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      r.v[i] = __ldcs(p + i);
+  }
+  return r;
+}
+
+// Reused (broadcast) load through the read-only path.
+template <typename T, int N>
+__device__ __forceinline__ Vec<T, N> load_reuse(const T *p) {
+  Vec<T, N> r;
+  if constexpr (sizeof(T) * N == 16) {
+    int4 raw = __ldg(reinterpret_cast<const int4 *>(p));
+    r = *reinterpret_cast<Vec<T, N> *>(&raw);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      r.v[i] = __ldg(p + i);
+  }
+  return r;
+}
+
+template <typename T, int N>
+__device__ __forceinline__ void store_stream(T *p, const Vec<T, N> &r) {
+  if constexpr (sizeof(T) * N == 16) {
+    __stcs(reinterpret_cast<int4 *>(p), *reinterpret_cast<const int4 *>(&r));
+  } else if constexpr (sizeof(T) * N == 32) {
+    __stcs(reinterpret_cast<int4 *>(p), *reinterpret_cast<const int4 *>(&r.v[0]));
+    __stcs(reinterpret_cast<int4 *>(p) + 1,
+           *reinterpret_cast<const int4 *>(&r.v[N / 2]));
+  } else if constexpr (sizeof(T) * N == 8) {
+    __stcs(reinterpret_cast<int2 *>(p), *reinterpret_cast<const int2 *>(&r));
+  } else if constexpr (sizeof(T) * N == 4) {
+    __stcs(reinterpret_cast<int *>(p), *reinterpret_cast<const int *>(&r));
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      __stcs(p + i, r.v[i]);
+  }
+}
+
+// ------------------------------------------------- fused elementwise loop ---
+// A Chain describes one fused ufunc chain over a flat, C-contiguous output
+// index space of n elements:
+//
+//   struct Chain {
+//     struct In  { ... };                     // registers for one vector step
+//     struct Out { ... };
+//     template <int V> __device__ void load(int64_t i, In &) const;
+//     template <int V> __device__ void compute(const In &, Out &) const;
+//     template <int V> __device__ void store(int64_t i, const Out &) const;
+//   };
+//
+// V is the number of consecutive elements handled per step (4 when every
+// pointer is 16-byte aligned and broadcast extents divide by 4, else 1).
+// Every thread issues all loads of its UNROLL steps before the first use so
+// that UNROLL x (#inputs) 128-bit requests are in flight per thread; a block
+// covers BLOCK*V*UNROLL consecutive elements, each step fully coalesced.
+template <int BLOCK, int V, int UNROLL, typename Chain>
+__device__ __forceinline__ void eltwise_tile(const Chain &chain, int64_t n) {
+  const int64_t tile = (int64_t)BLOCK * V * UNROLL;
+  const int64_t base = (int64_t)blockIdx.x * tile + (int64_t)threadIdx.x * V;
+  if (base + tile - (int64_t)threadIdx.x * V <= n) {
+    // Full tile: no bounds checks.
+    typename Chain::template In<V> in[UNROLL];
+    typename Chain::template Out<V> out[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      chain.template load<V>(base + (int64_t)u * BLOCK * V, in[u]);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      chain.template compute<V>(in[u], out[u]);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+      chain.template store<V>(base + (int64_t)u * BLOCK * V, out[u]);
+  } else {
+#pragma unroll 1
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t i = base + (int64_t)u * BLOCK * V;
+      if (i + V <= n) {
+        typename Chain::template In<V> in;
+        typename Chain::template Out<V> out;
+        chain.template load<V>(i, in);
+        chain.template compute<V>(in, out);
+        chain.template store<V>(i, out);
+      } else {
+        // Ragged end: element by element.
+        for (int64_t j = i; j < n && j < i + V; ++j) {
+          typename Chain::template In<1> in;
+          typename Chain::template Out<1> out;
+          chain.template load<1>(j, in);
+          chain.template compute<1>(in, out);
+          chain.template store<1>(j, out);
+        }
+      }
+    }
+  }
+}
+
+// Number of blocks eltwise_tile needs for n elements.
+__host__ __device__ inline int64_t eltwise_grid(int64_t n, int block, int v, int unroll) {
+  const int64_t tile = (int64_t)block * v * unroll;
+  return (n + tile - 1) / tile;
+}
+
+// --------------------------------------------------------- warp / block ops ---
+template <typename T, typename Op>
+__device__ __forceinline__ T warp_reduce(T v, Op op) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1)
+    v = op(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
+struct OpAdd {
+  template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a + b; }
+};
+struct OpMul {
+  template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a * b; }
+};
+// min/max as the reference defines them: select(a < b, a, b)
+// (numba_mlir/mlir/builtin/funcs.py:140-160).
+struct OpMin {
+  template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return b < a ? b : a; }
+};
+struct OpMax {
+  template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a < b ? b : a; }
+};
+
+// Block-wide reduction through warp shuffles and one shared-memory exchange.
+// Every thread of the block must call it; all threads receive the result.
+// `scratch` holds 32 elements of T.
+template <typename T, typename Op>
+__device__ __forceinline__ T block_reduce(T v, Op op, T neutral, T *scratch) {
+  const int lane = threadIdx.x & 31;
+  const int nthreads = blockDim.x * blockDim.y * blockDim.z;
+  const int tid = threadIdx.x + blockDim.x * (threadIdx.y + blockDim.y * threadIdx.z);
+  const int warp = tid >> 5;
+  const int nwarps = (nthreads + 31) >> 5;
+  v = warp_reduce(v, op);
+  __syncthreads();
+  if ((tid & 31) == 0)
+    scratch[warp] = v;
+  __syncthreads();
+  T r = (tid & 31) < nwarps ? scratch[tid & 31] : neutral;
+  (void)lane;
+  r = warp_reduce(r, op);
+  return r;
+}
+
+// ------------------------------------------------------------------- math ---
+// float32 stays float32 (numba_mlir/mlir/builtin/funcs.py:180-227); the CUDA
+// functions below are the IEEE-rounded (sqrt, div) or <= 2 ulp (log, exp, erf)
+// library versions, never the -use_fast_math intrinsics.
+__device__ __forceinline__ float f_log(float x) { return logf(x); }
+__device__ __forceinline__ float f_exp(float x) { return expf(x); }
+__device__ __forceinline__ float f_sqrt(float x) { return __fsqrt_rn(x); }
+__device__ __forceinline__ float f_erf(float x) { return erff(x); }
+__device__ __forceinline__ float f_div(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ double f_log(double x) { return log(x); }
+__device__ __forceinline__ double f_exp(double x) { return exp(x); }
+__device__ __forceinline__ double f_sqrt(double x) { return __dsqrt_rn(x); }
+__device__ __forceinline__ double f_erf(double x) { return erf(x); }
+__device__ __forceinline__ double f_div(double a, double b) { return __ddiv_rn(a, b); }
+
+} // namespace nmb
