@@ -1,0 +1,534 @@
+// Reducers and kernel bodies for axis and full reductions.
+//
+// Semantics follow the reference's _array_reduce
+// (numba_mlir/numba_mlir/mlir/numpy/funcs.py:163-214): sum/prod accumulate in
+// int64 for every integer dtype and in the array dtype for floats; min/max are
+// select(a < b, a, b) with +-inf / integer limits as identity (:278-295);
+// argmin/argmax use the (value, index) pair combiner that keeps the lower index
+// on ties (numba_mlir/mlir/builtin/funcs.py:118-138).  NaNs are not ordered by
+// `<` and are therefore ignored, as in the reference's select.
+//
+// Data movement: the reduced matrix is streamed through shared memory in 16 KB
+// tiles by the TMA bulk-copy engine (4-stage mbarrier ring per CTA), reduced
+// from shared memory with 128-bit reads, then combined with warp shuffles and
+// one shared-memory exchange per row.  Cross-CTA combination (column and full
+// reductions) goes through partials in scratch memory and a ticket counter:
+// the CTA that draws the last ticket merges the partials in index order, so
+// results do not depend on scheduling.
+#pragma once
+
+#include "bulk_pipe.cuh"
+
+namespace nmb {
+namespace red {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kTileBytes = 16384;
+constexpr int kStages = 4;
+constexpr int kSmemBytes = kStages * kTileBytes + 64 + 32 * 16;
+
+template <typename T> struct Limits;
+template <> struct Limits<float> {
+  static __device__ __forceinline__ float lowest() { return -__int_as_float(0x7f800000); }
+  static __device__ __forceinline__ float highest() { return __int_as_float(0x7f800000); }
+};
+template <> struct Limits<double> {
+  static __device__ __forceinline__ double lowest() { return -__longlong_as_double(0x7ff0000000000000ll); }
+  static __device__ __forceinline__ double highest() { return __longlong_as_double(0x7ff0000000000000ll); }
+};
+template <> struct Limits<int32_t> {
+  static __device__ __forceinline__ int32_t lowest() { return (int32_t)0x80000000; }
+  static __device__ __forceinline__ int32_t highest() { return 0x7fffffff; }
+};
+template <> struct Limits<int64_t> {
+  static __device__ __forceinline__ int64_t lowest() { return (int64_t)0x8000000000000000ll; }
+  static __device__ __forceinline__ int64_t highest() { return 0x7fffffffffffffffll; }
+};
+
+template <typename T> struct WideAcc { using type = T; };
+template <> struct WideAcc<int32_t> { using type = int64_t; };
+
+template <typename T> struct SumR {
+  using In = T;
+  using Acc = typename WideAcc<T>::type;
+  using Out = Acc;
+  static __device__ __forceinline__ Acc identity() { return Acc(0); }
+  static __device__ __forceinline__ void acc(Acc &a, T x, int64_t) { a += (Acc)x; }
+  static __device__ __forceinline__ Acc merge(Acc a, Acc b) { return a + b; }
+  static __device__ __forceinline__ Acc shfl(Acc a, int off) { return __shfl_xor_sync(0xffffffffu, a, off); }
+  static __device__ __forceinline__ Out fin(Acc a) { return a; }
+};
+template <typename T> struct ProdR {
+  using In = T;
+  using Acc = typename WideAcc<T>::type;
+  using Out = Acc;
+  static __device__ __forceinline__ Acc identity() { return Acc(1); }
+  static __device__ __forceinline__ void acc(Acc &a, T x, int64_t) { a *= (Acc)x; }
+  static __device__ __forceinline__ Acc merge(Acc a, Acc b) { return a * b; }
+  static __device__ __forceinline__ Acc shfl(Acc a, int off) { return __shfl_xor_sync(0xffffffffu, a, off); }
+  static __device__ __forceinline__ Out fin(Acc a) { return a; }
+};
+template <typename T> struct MinR {
+  using In = T;
+  using Acc = T;
+  using Out = T;
+  static __device__ __forceinline__ Acc identity() { return Limits<T>::highest(); }
+  static __device__ __forceinline__ void acc(Acc &a, T x, int64_t) { a = x < a ? x : a; }
+  static __device__ __forceinline__ Acc merge(Acc a, Acc b) { return b < a ? b : a; }
+  static __device__ __forceinline__ Acc shfl(Acc a, int off) { return __shfl_xor_sync(0xffffffffu, a, off); }
+  static __device__ __forceinline__ Out fin(Acc a) { return a; }
+};
+template <typename T> struct MaxR {
+  using In = T;
+  using Acc = T;
+  using Out = T;
+  static __device__ __forceinline__ Acc identity() { return Limits<T>::lowest(); }
+  static __device__ __forceinline__ void acc(Acc &a, T x, int64_t) { a = a < x ? x : a; }
+  static __device__ __forceinline__ Acc merge(Acc a, Acc b) { return a < b ? b : a; }
+  static __device__ __forceinline__ Acc shfl(Acc a, int off) { return __shfl_xor_sync(0xffffffffu, a, off); }
+  static __device__ __forceinline__ Out fin(Acc a) { return a; }
+};
+
+template <typename T> struct alignas(16) ValIdx {
+  T v;
+  int64_t i;
+};
+// MIN = true: argmin, false: argmax.  The lower index wins ties whatever the
+// merge order, so the result is NumPy's first occurrence.
+template <typename T, bool MIN> struct ArgR {
+  using In = T;
+  using Acc = ValIdx<T>;
+  using Out = int64_t;
+  static __device__ __forceinline__ Acc identity() {
+    return Acc{MIN ? Limits<T>::highest() : Limits<T>::lowest(), 0x7fffffffffffffffll};
+  }
+  static __device__ __forceinline__ bool better(T xv, int64_t xi, T av, int64_t ai) {
+    return MIN ? (xv < av || (xv == av && xi < ai)) : (av < xv || (xv == av && xi < ai));
+  }
+  static __device__ __forceinline__ void acc(Acc &a, T x, int64_t idx) {
+    if (better(x, idx, a.v, a.i)) {
+      a.v = x;
+      a.i = idx;
+    }
+  }
+  static __device__ __forceinline__ Acc merge(Acc a, Acc b) { return better(b.v, b.i, a.v, a.i) ? b : a; }
+  static __device__ __forceinline__ Acc shfl(Acc a, int off) {
+    Acc r;
+    r.v = __shfl_xor_sync(0xffffffffu, a.v, off);
+    r.i = __shfl_xor_sync(0xffffffffu, a.i, off);
+    return r;
+  }
+  static __device__ __forceinline__ Out fin(Acc a) { return a.i; }
+};
+
+// L2 (cache-global) load of an accumulator another CTA wrote.
+template <typename A> __device__ __forceinline__ A load_cg(const A *p) {
+  A r;
+  if constexpr (sizeof(A) == 4) {
+    int raw = __ldcg(reinterpret_cast<const int *>(p));
+    r = *reinterpret_cast<A *>(&raw);
+  } else if constexpr (sizeof(A) == 8) {
+    long long raw = __ldcg(reinterpret_cast<const long long *>(p));
+    r = *reinterpret_cast<A *>(&raw);
+  } else {
+    static_assert(sizeof(A) == 16, "accumulator size");
+    int4 raw = __ldcg(reinterpret_cast<const int4 *>(p));
+    r = *reinterpret_cast<A *>(&raw);
+  }
+  return r;
+}
+
+template <typename R> __device__ __forceinline__ typename R::Acc warp_merge(typename R::Acc a) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1)
+    a = R::merge(a, R::shfl(a, off));
+  return a;
+}
+
+// Block-wide merge; every thread calls it, every thread gets the result.
+template <typename R>
+__device__ __forceinline__ typename R::Acc block_merge(typename R::Acc a, typename R::Acc *scratch) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  a = warp_merge<R>(a);
+  __syncthreads();
+  if (lane == 0)
+    scratch[warp] = a;
+  __syncthreads();
+  typename R::Acc r = lane < kWarps ? scratch[lane] : R::identity();
+  return warp_merge<R>(r);
+}
+
+struct Smem {
+  unsigned char *tiles;
+  uint64_t *full;
+  void *scratch;
+  __device__ __forceinline__ explicit Smem(unsigned char *raw)
+      : tiles(raw), full(reinterpret_cast<uint64_t *>(raw + kStages * kTileBytes)),
+        scratch(raw + kStages * kTileBytes + 64) {}
+  __device__ __forceinline__ void init() {
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kStages; ++s)
+        mbar_init(&full[s], 1);
+      mbar_init_fence();
+    }
+    __syncthreads();
+  }
+};
+
+// Waits for use number `use` of a stage.  A thread whose wait ran out marks
+// itself dead (no more waiting, results are garbage) and flags the status word;
+// control flow stays uniform so block barriers still match.
+__device__ __forceinline__ void stage_wait(uint64_t *bar, int64_t use, bool &dead, uint32_t *status) {
+  if (!dead && !mbar_wait(bar, (uint32_t)(use & 1))) {
+    dead = true;
+    atomicExch(status, (uint32_t)kStatusWaitTimeout);
+  }
+}
+
+// After a timeout: give copies still in flight a bounded chance to land before
+// the CTA's shared memory is released.
+__device__ __forceinline__ void drain_after_timeout(Smem &sm, int64_t issued) {
+  if (threadIdx.x == 0)
+    for (int64_t i = issued > kStages ? issued - kStages : 0; i < issued; ++i)
+      (void)mbar_wait(&sm.full[i % kStages], (uint32_t)((i / kStages) & 1));
+}
+
+// ----------------------------------------------------------- row reduction ---
+// out[r] = reduce(a[r, :]) for a C-contiguous (rows, cols) matrix whose base is
+// 16-byte aligned and whose row size is a multiple of 16 bytes.
+// Grid: any number of CTAs <= rows; CTA b owns rows [rows*b/G, rows*(b+1)/G).
+template <typename R>
+__device__ __forceinline__ void reduce_rows_body(const typename R::In *__restrict__ a,
+                                                 typename R::Out *__restrict__ out, int64_t rows,
+                                                 int64_t cols, uint32_t *status,
+                                                 unsigned char *smem_raw) {
+  using T = typename R::In;
+  using Acc = typename R::Acc;
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int64_t TILE = kTileBytes / sizeof(T);
+  Smem sm(smem_raw);
+  T *tiles = reinterpret_cast<T *>(sm.tiles);
+  Acc *scratch = reinterpret_cast<Acc *>(sm.scratch);
+  sm.init();
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t G = gridDim.x, b = blockIdx.x;
+  const int64_t r_begin = rows * b / G, r_end = rows * (b + 1) / G;
+  const int64_t nrows = r_end - r_begin;
+  const int64_t cpr = (cols + TILE - 1) / TILE;            // tiles per row
+  const int64_t rt = cpr == 1 ? (TILE / cols > 0 ? TILE / cols : 1) : 1; // rows per tile
+  const int64_t ntiles = cpr == 1 ? (nrows + rt - 1) / rt : nrows * cpr;
+  const bool warp_rows = cpr == 1 && cols * (int64_t)sizeof(T) <= 2048;
+
+  auto issue = [&](int64_t i) {
+    const int s = (int)(i % kStages);
+    const T *src;
+    uint32_t bytes;
+    if (cpr == 1) {
+      const int64_t r0 = r_begin + i * rt;
+      const int64_t nr = r_end - r0 < rt ? r_end - r0 : rt;
+      src = a + r0 * cols;
+      bytes = (uint32_t)(nr * cols * sizeof(T));
+    } else {
+      const int64_t r = r_begin + i / cpr, c0 = (i % cpr) * TILE;
+      const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
+      src = a + r * cols + c0;
+      bytes = (uint32_t)(ne * sizeof(T));
+    }
+    mbar_expect_tx(&sm.full[s], bytes);
+    bulk_load(tiles + (int64_t)s * TILE, src, bytes, &sm.full[s]);
+  };
+
+  int64_t issued = 0;
+  if (tid == 0)
+    for (; issued < kStages && issued < ntiles; ++issued)
+      issue(issued);
+
+  bool dead = false;
+  Acc racc = R::identity();
+  for (int64_t i = 0; i < ntiles; ++i) {
+    const int s = (int)(i % kStages);
+    stage_wait(&sm.full[s], i / kStages, dead, status);
+    const T *tile = tiles + (int64_t)s * TILE;
+    if (cpr == 1) {
+      const int64_t r0 = r_begin + i * rt;
+      const int nr = (int)(r_end - r0 < rt ? r_end - r0 : rt);
+      if (warp_rows) {
+        for (int j = warp; j < nr; j += kWarps) {
+          Acc acc = R::identity();
+          const T *row = tile + (int64_t)j * cols;
+          for (int64_t v = (int64_t)lane * VEC; v < cols; v += 32 * VEC) {
+            const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(row + v);
+#pragma unroll
+            for (int l = 0; l < VEC; ++l)
+              R::acc(acc, x.v[l], v + l);
+          }
+          acc = warp_merge<R>(acc);
+          if (lane == 0)
+            out[r0 + j] = R::fin(acc);
+        }
+      } else {
+        for (int j = 0; j < nr; ++j) {
+          const T *row = tile + (int64_t)j * cols;
+          Acc acc = R::identity();
+          for (int64_t v = (int64_t)tid * VEC; v < cols; v += kThreads * VEC) {
+            const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(row + v);
+#pragma unroll
+            for (int l = 0; l < VEC; ++l)
+              R::acc(acc, x.v[l], v + l);
+          }
+          acc = block_merge<R>(acc, scratch);
+          if (tid == 0)
+            out[r0 + j] = R::fin(acc);
+        }
+      }
+    } else {
+      const int64_t r = r_begin + i / cpr, ch = i % cpr, c0 = ch * TILE;
+      const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
+      for (int64_t v = (int64_t)tid * VEC; v < ne; v += kThreads * VEC) {
+        const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(tile + v);
+#pragma unroll
+        for (int l = 0; l < VEC; ++l)
+          R::acc(racc, x.v[l], c0 + v + l);
+      }
+      if (ch == cpr - 1) {
+        const Acc total = block_merge<R>(racc, scratch);
+        if (tid == 0)
+          out[r] = R::fin(total);
+        racc = R::identity();
+      }
+    }
+    __syncthreads(); // the whole CTA is done with stage s
+    if (tid == 0 && issued < ntiles)
+      issue(issued++);
+  }
+  if (__syncthreads_or(dead))
+    drain_after_timeout(sm, issued);
+}
+
+// -------------------------------------------------------- column reduction ---
+// out[c] = reduce(a[:, c]).  Grid (col_tiles, row_blocks): CTA (x, y) reduces
+// rows [rows*y/Gy, rows*(y+1)/Gy) of the 256*VEC columns starting at
+// x*256*VEC; partials[y][c] and counters[x] live in scratch memory (counters
+// start at zero and are left at zero).
+template <typename R>
+__device__ __forceinline__ void reduce_cols_body(const typename R::In *__restrict__ a,
+                                                 typename R::Out *__restrict__ out,
+                                                 typename R::Acc *partials, uint32_t *counters,
+                                                 int64_t rows, int64_t cols, uint32_t *status,
+                                                 unsigned char *smem_raw) {
+  using T = typename R::In;
+  using Acc = typename R::Acc;
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int COLS = kThreads * VEC;
+  constexpr int RS = kTileBytes / (COLS * (int)sizeof(T)); // rows per stage
+  constexpr int64_t TILE = kTileBytes / sizeof(T);
+  Smem sm(smem_raw);
+  T *tiles = reinterpret_cast<T *>(sm.tiles);
+  sm.init();
+
+  const int tid = threadIdx.x;
+  const int64_t c0 = (int64_t)blockIdx.x * COLS;
+  const int ncols = (int)(cols - c0 < COLS ? cols - c0 : COLS);
+  const int64_t Gy = gridDim.y, by = blockIdx.y;
+  const int64_t r_begin = rows * by / Gy, r_end = rows * (by + 1) / Gy;
+  const int64_t nsteps = (r_end - r_begin + RS - 1) / RS;
+
+  auto issue = [&](int64_t i) {
+    const int s = (int)(i % kStages);
+    const int64_t r0 = r_begin + i * RS;
+    const int nr = (int)(r_end - r0 < RS ? r_end - r0 : RS);
+    const uint32_t row_bytes = (uint32_t)(ncols * sizeof(T));
+    mbar_expect_tx(&sm.full[s], row_bytes * nr);
+    for (int j = 0; j < nr; ++j)
+      bulk_load(tiles + (int64_t)s * TILE + (int64_t)j * COLS, a + (r0 + j) * cols + c0, row_bytes,
+                &sm.full[s]);
+  };
+
+  int64_t issued = 0;
+  if (tid == 0)
+    for (; issued < kStages && issued < nsteps; ++issued)
+      issue(issued);
+
+  Acc acc[VEC];
+#pragma unroll
+  for (int l = 0; l < VEC; ++l)
+    acc[l] = R::identity();
+  const bool active = tid * VEC < ncols;
+  bool dead = false;
+  for (int64_t i = 0; i < nsteps; ++i) {
+    const int s = (int)(i % kStages);
+    stage_wait(&sm.full[s], i / kStages, dead, status);
+    const int64_t r0 = r_begin + i * RS;
+    const int nr = (int)(r_end - r0 < RS ? r_end - r0 : RS);
+    if (active) {
+      const T *tile = tiles + (int64_t)s * TILE + tid * VEC;
+      for (int j = 0; j < nr; ++j) {
+        const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(tile + (int64_t)j * COLS);
+#pragma unroll
+        for (int l = 0; l < VEC; ++l)
+          R::acc(acc[l], x.v[l], r0 + j);
+      }
+    }
+    __syncthreads();
+    if (tid == 0 && issued < nsteps)
+      issue(issued++);
+  }
+  if (__syncthreads_or(dead))
+    drain_after_timeout(sm, issued);
+
+  if (Gy == 1) {
+    if (active)
+#pragma unroll
+      for (int l = 0; l < VEC; ++l)
+        out[c0 + tid * VEC + l] = R::fin(acc[l]);
+    return;
+  }
+  if (active)
+#pragma unroll
+    for (int l = 0; l < VEC; ++l)
+      partials[by * cols + c0 + tid * VEC + l] = acc[l];
+  __threadfence();
+  __shared__ bool last;
+  __syncthreads();
+  if (tid == 0)
+    last = atomicAdd(&counters[blockIdx.x], 1u) == (uint32_t)(Gy - 1);
+  __syncthreads();
+  if (!last)
+    return;
+  __threadfence();
+  if (active) {
+#pragma unroll
+    for (int l = 0; l < VEC; ++l) {
+      Acc m = R::identity();
+      for (int64_t y = 0; y < Gy; ++y)
+        m = R::merge(m, load_cg(partials + y * cols + c0 + tid * VEC + l));
+      out[c0 + tid * VEC + l] = R::fin(m);
+    }
+  }
+  if (tid == 0)
+    counters[blockIdx.x] = 0;
+}
+
+// ---------------------------------------------------------- full reduction ---
+// out[0] = reduce(a[0:n]).  CTA b streams the span [b*span, (b+1)*span) with
+// span a multiple of the tile size; partials[G] and one counter live in
+// scratch memory.  a is 16-byte aligned; the last n % VEC elements are read
+// directly by the merging CTA.
+template <typename R>
+__device__ __forceinline__ void reduce_all_body(const typename R::In *__restrict__ a,
+                                                typename R::Out *__restrict__ out,
+                                                typename R::Acc *partials, uint32_t *counter,
+                                                int64_t n, int64_t span, uint32_t *status,
+                                                unsigned char *smem_raw) {
+  using T = typename R::In;
+  using Acc = typename R::Acc;
+  constexpr int VEC = 16 / sizeof(T);
+  constexpr int64_t TILE = kTileBytes / sizeof(T);
+  Smem sm(smem_raw);
+  T *tiles = reinterpret_cast<T *>(sm.tiles);
+  Acc *scratch = reinterpret_cast<Acc *>(sm.scratch);
+  sm.init();
+
+  const int tid = threadIdx.x;
+  const int64_t G = gridDim.x, b = blockIdx.x;
+  const int64_t nvec = n - n % VEC;
+  const int64_t begin = b * span < nvec ? b * span : nvec;
+  const int64_t end = (b + 1) * span < nvec ? (b + 1) * span : nvec;
+  const int64_t ntiles = (end - begin + TILE - 1) / TILE;
+
+  auto issue = [&](int64_t i) {
+    const int s = (int)(i % kStages);
+    const int64_t e0 = begin + i * TILE;
+    const int64_t ne = end - e0 < TILE ? end - e0 : TILE;
+    mbar_expect_tx(&sm.full[s], (uint32_t)(ne * sizeof(T)));
+    bulk_load(tiles + (int64_t)s * TILE, a + e0, (uint32_t)(ne * sizeof(T)), &sm.full[s]);
+  };
+  int64_t issued = 0;
+  if (tid == 0)
+    for (; issued < kStages && issued < ntiles; ++issued)
+      issue(issued);
+
+  Acc acc = R::identity();
+  bool dead = false;
+  for (int64_t i = 0; i < ntiles; ++i) {
+    const int s = (int)(i % kStages);
+    stage_wait(&sm.full[s], i / kStages, dead, status);
+    const int64_t e0 = begin + i * TILE;
+    const int64_t ne = end - e0 < TILE ? end - e0 : TILE;
+    const T *tile = tiles + (int64_t)s * TILE;
+    for (int64_t v = (int64_t)tid * VEC; v < ne; v += kThreads * VEC) {
+      const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(tile + v);
+#pragma unroll
+      for (int l = 0; l < VEC; ++l)
+        R::acc(acc, x.v[l], e0 + v + l);
+    }
+    __syncthreads();
+    if (tid == 0 && issued < ntiles)
+      issue(issued++);
+  }
+  if (__syncthreads_or(dead))
+    drain_after_timeout(sm, issued);
+
+  acc = block_merge<R>(acc, scratch);
+  __shared__ bool last;
+  if (tid == 0) {
+    partials[b] = acc;
+    __threadfence();
+    last = atomicAdd(counter, 1u) == (uint32_t)(G - 1);
+  }
+  __syncthreads();
+  if (!last)
+    return;
+  __threadfence();
+  Acc m = R::identity();
+  for (int64_t g = tid; g < G; g += kThreads)
+    m = R::merge(m, load_cg(partials + g));
+  if (tid == 0)
+    for (int64_t e = nvec; e < n; ++e)
+      R::acc(m, a[e], e);
+  m = block_merge<R>(m, scratch);
+  if (tid == 0) {
+    out[0] = R::fin(m);
+    *counter = 0;
+  }
+}
+
+// ------------------------------------------------ any layout, any alignment ---
+// out[o*inner + i] = reduce_k a[o*so + k*sk + i*si] (element strides).
+// mode 0: one warp per output, lanes stride over k (reduced axis contiguous);
+// mode 1: one thread per output, consecutive threads on consecutive i.
+template <typename R>
+__device__ __forceinline__ void reduce_generic_body(const typename R::In *__restrict__ a,
+                                                    typename R::Out *__restrict__ out, int64_t outer,
+                                                    int64_t K, int64_t inner, int64_t so, int64_t sk,
+                                                    int64_t si, int mode) {
+  using Acc = typename R::Acc;
+  const int64_t nout = outer * inner;
+  if (mode == 0) {
+    const int lane = threadIdx.x & 31;
+    const int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (w >= nout)
+      return;
+    const int64_t o = w / inner, i = w % inner;
+    Acc acc = R::identity();
+    for (int64_t k = lane; k < K; k += 32)
+      R::acc(acc, a[o * so + k * sk + i * si], k);
+    acc = warp_merge<R>(acc);
+    if (lane == 0)
+      out[w] = R::fin(acc);
+  } else {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= nout)
+      return;
+    const int64_t o = t / inner, i = t % inner;
+    Acc acc = R::identity();
+    for (int64_t k = 0; k < K; ++k)
+      R::acc(acc, a[o * so + k * sk + i * si], k);
+    out[t] = R::fin(acc);
+  }
+}
+
+} // namespace red
+} // namespace nmb

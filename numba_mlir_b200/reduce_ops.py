@@ -1,0 +1,155 @@
+"""Host dispatch of the reduction kernels (sum/prod/min/max/argmin/argmax).
+
+Result dtypes follow the reference's _array_reduce
+(numba_mlir/numba_mlir/mlir/numpy/funcs.py:163-214): sum and prod of an integer
+array are int64, of a float array the array's dtype; min/max keep the dtype;
+argmin/argmax are int64 (NumPy's intp).  Everything runs on the device through
+gpuxLaunchKernel; there is no host-side combination step (the reference reduces
+work-group partials in a host loop, mlir/lib/Conversion/GpuToGpuRuntime.cpp:2232-2273).
+"""
+
+import numpy as np
+
+from . import runtime as _rt
+from .device_array import DeviceArray, empty
+
+_TY = {np.dtype(np.float32): "f32", np.dtype(np.float64): "f64",
+       np.dtype(np.int32): "i32", np.dtype(np.int64): "i64"}
+OPS = ("sum", "prod", "min", "max", "argmin", "argmax")
+SMS = 148  # B200
+_CTAS = SMS * 3  # three 65 KB CTAs fit one SM
+_TILE_BYTES = 16384
+_I64 = np.int64
+
+
+def out_dtype(op, dtype):
+    dtype = np.dtype(dtype)
+    if op in ("argmin", "argmax"):
+        return np.dtype(np.int64)
+    if op in ("sum", "prod") and dtype.kind in "iu":
+        return np.dtype(np.int64)
+    return dtype
+
+
+def _acc_bytes(op, dtype):
+    if op in ("argmin", "argmax"):
+        return 16
+    return out_dtype(op, dtype).itemsize
+
+
+def _kernel_type(dtype):
+    try:
+        return _TY[np.dtype(dtype)]
+    except KeyError:
+        raise TypeError(f"reductions support float32/float64/int32/int64, not {dtype}") from None
+
+
+def reduce(a, op, axis=None, out=None):
+    """Reduces DeviceArray `a` with `op` over `axis` (None = all elements).
+
+    Returns a DeviceArray; a 0-d one for axis=None."""
+    if op not in OPS:
+        raise ValueError(f"unknown reduction {op}")
+    ty = _kernel_type(a.dtype)
+    odt = out_dtype(op, a.dtype)
+    q = a.queue
+    if axis is None:
+        if a.size == 0:
+            raise ValueError("zero-size array to reduction operation")
+        flat = a if a.is_c_contiguous else a.copy()
+        if out is None:
+            out = empty((), odt, queue=q)
+        _launch_all(q, flat, out, op, ty)
+        return out
+    axis = int(axis)
+    if axis < 0:
+        axis += a.ndim
+    if not 0 <= axis < a.ndim:
+        raise ValueError("axis out of range")
+    oshape = a.shape[:axis] + a.shape[axis + 1:]
+    if a.shape[axis] == 0:
+        raise ValueError("zero-size reduction axis")
+    if out is None:
+        out = empty(oshape, odt, queue=q)
+    if out.size == 0:
+        return out
+    outer = int(np.prod(a.shape[:axis], dtype=np.int64))
+    K = a.shape[axis]
+    inner = int(np.prod(a.shape[axis + 1:], dtype=np.int64))
+    it = a.dtype.itemsize
+    vec = 16 // it
+    aligned = a.is_c_contiguous and a.ptr % 16 == 0
+    if aligned and inner == 1 and K % vec == 0:
+        _launch_rows(q, a, out, op, ty, outer, K)
+    elif aligned and outer == 1 and inner % vec == 0:
+        _launch_cols(q, a, out, op, ty, K, inner)
+    else:
+        _launch_generic(q, a, out, op, ty, axis, outer, K, inner)
+    return out
+
+
+def _launch_rows(q, a, out, op, ty, rows, cols):
+    k = q.builtin(f"nmb_reduce_rows_{op}_{ty}")
+    grid = max(1, min(rows, _CTAS))
+    q.launch(k, (grid,), (256,),
+             [("ptr", a.ptr), ("ptr", out.ptr), _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
+
+
+def _launch_cols(q, a, out, op, ty, rows, cols):
+    k = q.builtin(f"nmb_reduce_cols_{op}_{ty}")
+    vec = 16 // a.dtype.itemsize
+    tile_cols = 256 * vec
+    col_tiles = (cols + tile_cols - 1) // tile_cols
+    rows_per_stage = _TILE_BYTES // (tile_cols * a.dtype.itemsize)
+    row_blocks = max(1, min((_CTAS + col_tiles - 1) // col_tiles,
+                            (rows + rows_per_stage - 1) // rows_per_stage, 65535))
+    if col_tiles * 4 > q.COUNTER_BYTES:
+        raise ValueError("too many column tiles for the counter region")
+    counters, partials = q.scratch(row_blocks * cols * _acc_bytes(op, a.dtype))
+    q.launch(k, (col_tiles, row_blocks), (256,),
+             [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
+              _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
+
+
+def _launch_all(q, a, out, op, ty):
+    n = a.size
+    if a.ptr % 16 != 0:
+        _launch_generic(q, a.reshape(n), out, op, ty, 0, 1, n, 1)
+        return
+    k = q.builtin(f"nmb_reduce_all_{op}_{ty}")
+    tile = _TILE_BYTES // a.dtype.itemsize
+    grid = max(1, min(_CTAS, (n + tile - 1) // tile))
+    span = (n + grid - 1) // grid
+    span = (span + tile - 1) // tile * tile
+    counters, partials = q.scratch(grid * 16)
+    q.launch(k, (grid,), (256,),
+             [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
+              _I64(n), _I64(span), ("ptr", q.status_ptr)])
+
+
+def _launch_generic(q, a, out, op, ty, axis, outer, K, inner):
+    """Any strides / alignment.  The (outer, K, inner) decomposition needs the
+    outer and inner index groups to be addressable with one stride each, which
+    holds for 1-D/2-D arrays and C-contiguous N-D arrays; other layouts are
+    copied to C order first."""
+    it = a.dtype.itemsize
+    if a.ndim <= 2 or a.is_c_contiguous:
+        src = a
+    else:
+        src = a.copy()
+    st = [s // it for s in src.strides]
+    sk = st[axis]
+    if src.ndim == 1:
+        so, si = 0, 0
+    elif src.ndim == 2:
+        so, si = (st[0], 0) if axis == 1 else (0, st[1])
+    else:
+        so = st[axis - 1] if axis > 0 else 0
+        si = 1
+    k = q.builtin(f"nmb_reduce_generic_{op}_{ty}")
+    nout = outer * inner
+    mode = 0 if (abs(sk) == 1 and K >= 64) or inner == 1 else 1
+    threads = nout * 32 if mode == 0 else nout
+    q.launch(k, ((threads + 255) // 256,), (256,),
+             [("ptr", src.ptr), ("ptr", out.ptr), _I64(outer), _I64(K), _I64(inner),
+              _I64(so), _I64(sk), _I64(si), np.int32(mode)])

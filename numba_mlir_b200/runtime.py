@@ -227,6 +227,9 @@ class Queue:
         self._modules = {}
         self._kernels = {}
         self._builtin = None
+        self._scratch = None
+        self._scratch_bytes = 0
+        self._status = None
 
     # -- modules / kernels ---------------------------------------------------
     def load_module(self, blob):
@@ -343,6 +346,44 @@ class Queue:
     @property
     def stream(self):
         return self.lib.gpuxQueueGetStream(self.handle) or 0
+
+    # -- kernel scratch and status ---------------------------------------------
+    COUNTER_BYTES = 4096
+
+    def scratch(self, nbytes):
+        """Grow-only device scratch shared by the kernels of this queue (stream
+        order keeps consecutive users apart).  The first COUNTER_BYTES hold
+        ticket counters that start at zero and that every kernel leaves at
+        zero; the rest is uninitialised.  Returns (counters_ptr, data_ptr)."""
+        need = self.COUNTER_BYTES + int(nbytes)
+        if need > self._scratch_bytes:
+            if self._scratch:
+                self.free(self._scratch)
+            size = max(need, 1 << 20)
+            self._scratch = self.alloc(size)
+            self._scratch_bytes = size
+            self.memset(self._scratch, 0, self.COUNTER_BYTES)
+        return self._scratch, self._scratch + self.COUNTER_BYTES
+
+    @property
+    def status_ptr(self):
+        """Device word kernels with bounded waits set when a wait ran out."""
+        if self._status is None:
+            self._status = self.alloc(64)
+            self.memset(self._status, 0, 64)
+        return self._status
+
+    def check_status(self):
+        """Synchronises and raises if any kernel reported a timed-out wait."""
+        if self._status is None:
+            self.synchronize()
+            return
+        word = ctypes.c_uint32(0)
+        self.memcpy(ctypes.addressof(word), self._status, 4, COPY_D2H, wait=True)
+        check()
+        if word.value:
+            self.memset(self._status, 0, 64)
+            raise GpuRuntimeError(f"a device-side wait timed out (status {word.value})")
 
 
 _default_queues = {}
