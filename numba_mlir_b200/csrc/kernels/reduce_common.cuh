@@ -10,8 +10,7 @@
 //
 // Data movement: the reduced matrix is streamed through shared memory in 16 KB
 // tiles by the TMA bulk-copy engine (4-stage mbarrier ring per CTA), reduced
-// from shared memory with 128-bit reads, then combined with warp shuffles and
-// one shared-memory exchange per row.  Cross-CTA combination (column and full
+// from shared memory with 128-bit reads, then combined with warp shuffles.  Cross-CTA combination (column and full
 // reductions) goes through partials in scratch memory and a ticket counter:
 // the CTA that draws the last ticket merges the partials in index order, so
 // results do not depend on scheduling.
@@ -58,6 +57,12 @@ template <typename T> struct SumR {
   static __device__ __forceinline__ Acc merge(Acc a, Acc b) { return a + b; }
   static __device__ __forceinline__ Acc shfl(Acc a, int off) { return __shfl_xor_sync(0xffffffffu, a, off); }
   static __device__ __forceinline__ Out fin(Acc a) { return a; }
+  // Hot-loop accumulator: position k counts the thread's visits in increasing
+  // index order; only index-carrying reducers need it.
+  using Fast = Acc;
+  static __device__ __forceinline__ Fast fast_identity() { return identity(); }
+  static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
+  static __device__ __forceinline__ Acc widen(Fast f, int64_t, int64_t) { return f; }
 };
 template <typename T> struct ProdR {
   using In = T;
@@ -68,6 +73,12 @@ template <typename T> struct ProdR {
   static __device__ __forceinline__ Acc merge(Acc a, Acc b) { return a * b; }
   static __device__ __forceinline__ Acc shfl(Acc a, int off) { return __shfl_xor_sync(0xffffffffu, a, off); }
   static __device__ __forceinline__ Out fin(Acc a) { return a; }
+  // Hot-loop accumulator: position k counts the thread's visits in increasing
+  // index order; only index-carrying reducers need it.
+  using Fast = Acc;
+  static __device__ __forceinline__ Fast fast_identity() { return identity(); }
+  static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
+  static __device__ __forceinline__ Acc widen(Fast f, int64_t, int64_t) { return f; }
 };
 template <typename T> struct MinR {
   using In = T;
@@ -78,6 +89,12 @@ template <typename T> struct MinR {
   static __device__ __forceinline__ Acc merge(Acc a, Acc b) { return b < a ? b : a; }
   static __device__ __forceinline__ Acc shfl(Acc a, int off) { return __shfl_xor_sync(0xffffffffu, a, off); }
   static __device__ __forceinline__ Out fin(Acc a) { return a; }
+  // Hot-loop accumulator: position k counts the thread's visits in increasing
+  // index order; only index-carrying reducers need it.
+  using Fast = Acc;
+  static __device__ __forceinline__ Fast fast_identity() { return identity(); }
+  static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
+  static __device__ __forceinline__ Acc widen(Fast f, int64_t, int64_t) { return f; }
 };
 template <typename T> struct MaxR {
   using In = T;
@@ -88,6 +105,12 @@ template <typename T> struct MaxR {
   static __device__ __forceinline__ Acc merge(Acc a, Acc b) { return a < b ? b : a; }
   static __device__ __forceinline__ Acc shfl(Acc a, int off) { return __shfl_xor_sync(0xffffffffu, a, off); }
   static __device__ __forceinline__ Out fin(Acc a) { return a; }
+  // Hot-loop accumulator: position k counts the thread's visits in increasing
+  // index order; only index-carrying reducers need it.
+  using Fast = Acc;
+  static __device__ __forceinline__ Fast fast_identity() { return identity(); }
+  static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
+  static __device__ __forceinline__ Acc widen(Fast f, int64_t, int64_t) { return f; }
 };
 
 template <typename T> struct alignas(16) ValIdx {
@@ -120,6 +143,26 @@ template <typename T, bool MIN> struct ArgR {
     return r;
   }
   static __device__ __forceinline__ Out fin(Acc a) { return a.i; }
+  // A thread visits its elements in increasing index order, so a strict
+  // comparison keeps the first occurrence and a 32-bit visit counter is enough;
+  // the 64-bit index is rebuilt once at the end.
+  struct Fast {
+    T v;
+    int k;
+  };
+  static __device__ __forceinline__ Fast fast_identity() {
+    return Fast{MIN ? Limits<T>::highest() : Limits<T>::lowest(), -1};
+  }
+  static __device__ __forceinline__ void fast_acc(Fast &a, T x, int k) {
+    if (MIN ? (x < a.v) : (a.v < x)) {
+      a.v = x;
+      a.k = k;
+    }
+  }
+  // index of visit k = first + k * stride
+  static __device__ __forceinline__ Acc widen(Fast f, int64_t first, int64_t stride) {
+    return f.k < 0 ? identity() : Acc{f.v, first + (int64_t)f.k * stride};
+  }
 };
 
 // L2 (cache-global) load of an accumulator another CTA wrote.
@@ -192,223 +235,6 @@ __device__ __forceinline__ void drain_after_timeout(Smem &sm, int64_t issued) {
   if (threadIdx.x == 0)
     for (int64_t i = issued > kStages ? issued - kStages : 0; i < issued; ++i)
       (void)mbar_wait(&sm.full[i % kStages], (uint32_t)((i / kStages) & 1));
-}
-
-// ----------------------------------------------------------- row reduction ---
-// out[r] = reduce(a[r, :]) for a C-contiguous (rows, cols) matrix whose base is
-// 16-byte aligned and whose row size is a multiple of 16 bytes.
-// Grid: any number of CTAs <= rows; CTA b owns rows [rows*b/G, rows*(b+1)/G).
-template <typename R>
-__device__ __forceinline__ void reduce_rows_body(const typename R::In *__restrict__ a,
-                                                 typename R::Out *__restrict__ out, int64_t rows,
-                                                 int64_t cols, uint32_t *status,
-                                                 unsigned char *smem_raw) {
-  using T = typename R::In;
-  using Acc = typename R::Acc;
-  constexpr int VEC = 16 / sizeof(T);
-  constexpr int64_t TILE = kTileBytes / sizeof(T);
-  Smem sm(smem_raw);
-  T *tiles = reinterpret_cast<T *>(sm.tiles);
-  Acc *scratch = reinterpret_cast<Acc *>(sm.scratch);
-  sm.init();
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int64_t G = gridDim.x, b = blockIdx.x;
-  const int64_t r_begin = rows * b / G, r_end = rows * (b + 1) / G;
-  const int64_t nrows = r_end - r_begin;
-  const int64_t cpr = (cols + TILE - 1) / TILE;            // tiles per row
-  const int64_t rt = cpr == 1 ? (TILE / cols > 0 ? TILE / cols : 1) : 1; // rows per tile
-  const int64_t ntiles = cpr == 1 ? (nrows + rt - 1) / rt : nrows * cpr;
-  const bool warp_rows = cpr == 1 && cols * (int64_t)sizeof(T) <= 2048;
-
-  auto issue = [&](int64_t i) {
-    const int s = (int)(i % kStages);
-    const T *src;
-    uint32_t bytes;
-    if (cpr == 1) {
-      const int64_t r0 = r_begin + i * rt;
-      const int64_t nr = r_end - r0 < rt ? r_end - r0 : rt;
-      src = a + r0 * cols;
-      bytes = (uint32_t)(nr * cols * sizeof(T));
-    } else {
-      const int64_t r = r_begin + i / cpr, c0 = (i % cpr) * TILE;
-      const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
-      src = a + r * cols + c0;
-      bytes = (uint32_t)(ne * sizeof(T));
-    }
-    mbar_expect_tx(&sm.full[s], bytes);
-    bulk_load(tiles + (int64_t)s * TILE, src, bytes, &sm.full[s]);
-  };
-
-  int64_t issued = 0;
-  if (tid == 0)
-    for (; issued < kStages && issued < ntiles; ++issued)
-      issue(issued);
-
-  bool dead = false;
-  Acc racc = R::identity();
-  for (int64_t i = 0; i < ntiles; ++i) {
-    const int s = (int)(i % kStages);
-    stage_wait(&sm.full[s], i / kStages, dead, status);
-    const T *tile = tiles + (int64_t)s * TILE;
-    if (cpr == 1) {
-      const int64_t r0 = r_begin + i * rt;
-      const int nr = (int)(r_end - r0 < rt ? r_end - r0 : rt);
-      if (warp_rows) {
-        for (int j = warp; j < nr; j += kWarps) {
-          Acc acc = R::identity();
-          const T *row = tile + (int64_t)j * cols;
-          for (int64_t v = (int64_t)lane * VEC; v < cols; v += 32 * VEC) {
-            const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(row + v);
-#pragma unroll
-            for (int l = 0; l < VEC; ++l)
-              R::acc(acc, x.v[l], v + l);
-          }
-          acc = warp_merge<R>(acc);
-          if (lane == 0)
-            out[r0 + j] = R::fin(acc);
-        }
-      } else {
-        for (int j = 0; j < nr; ++j) {
-          const T *row = tile + (int64_t)j * cols;
-          Acc acc = R::identity();
-          for (int64_t v = (int64_t)tid * VEC; v < cols; v += kThreads * VEC) {
-            const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(row + v);
-#pragma unroll
-            for (int l = 0; l < VEC; ++l)
-              R::acc(acc, x.v[l], v + l);
-          }
-          acc = block_merge<R>(acc, scratch);
-          if (tid == 0)
-            out[r0 + j] = R::fin(acc);
-        }
-      }
-    } else {
-      const int64_t r = r_begin + i / cpr, ch = i % cpr, c0 = ch * TILE;
-      const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
-      for (int64_t v = (int64_t)tid * VEC; v < ne; v += kThreads * VEC) {
-        const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(tile + v);
-#pragma unroll
-        for (int l = 0; l < VEC; ++l)
-          R::acc(racc, x.v[l], c0 + v + l);
-      }
-      if (ch == cpr - 1) {
-        const Acc total = block_merge<R>(racc, scratch);
-        if (tid == 0)
-          out[r] = R::fin(total);
-        racc = R::identity();
-      }
-    }
-    __syncthreads(); // the whole CTA is done with stage s
-    if (tid == 0 && issued < ntiles)
-      issue(issued++);
-  }
-  if (__syncthreads_or(dead))
-    drain_after_timeout(sm, issued);
-}
-
-// -------------------------------------------------------- column reduction ---
-// out[c] = reduce(a[:, c]).  Grid (col_tiles, row_blocks): CTA (x, y) reduces
-// rows [rows*y/Gy, rows*(y+1)/Gy) of the 256*VEC columns starting at
-// x*256*VEC; partials[y][c] and counters[x] live in scratch memory (counters
-// start at zero and are left at zero).
-template <typename R>
-__device__ __forceinline__ void reduce_cols_body(const typename R::In *__restrict__ a,
-                                                 typename R::Out *__restrict__ out,
-                                                 typename R::Acc *partials, uint32_t *counters,
-                                                 int64_t rows, int64_t cols, uint32_t *status,
-                                                 unsigned char *smem_raw) {
-  using T = typename R::In;
-  using Acc = typename R::Acc;
-  constexpr int VEC = 16 / sizeof(T);
-  constexpr int COLS = kThreads * VEC;
-  constexpr int RS = kTileBytes / (COLS * (int)sizeof(T)); // rows per stage
-  constexpr int64_t TILE = kTileBytes / sizeof(T);
-  Smem sm(smem_raw);
-  T *tiles = reinterpret_cast<T *>(sm.tiles);
-  sm.init();
-
-  const int tid = threadIdx.x;
-  const int64_t c0 = (int64_t)blockIdx.x * COLS;
-  const int ncols = (int)(cols - c0 < COLS ? cols - c0 : COLS);
-  const int64_t Gy = gridDim.y, by = blockIdx.y;
-  const int64_t r_begin = rows * by / Gy, r_end = rows * (by + 1) / Gy;
-  const int64_t nsteps = (r_end - r_begin + RS - 1) / RS;
-
-  auto issue = [&](int64_t i) {
-    const int s = (int)(i % kStages);
-    const int64_t r0 = r_begin + i * RS;
-    const int nr = (int)(r_end - r0 < RS ? r_end - r0 : RS);
-    const uint32_t row_bytes = (uint32_t)(ncols * sizeof(T));
-    mbar_expect_tx(&sm.full[s], row_bytes * nr);
-    for (int j = 0; j < nr; ++j)
-      bulk_load(tiles + (int64_t)s * TILE + (int64_t)j * COLS, a + (r0 + j) * cols + c0, row_bytes,
-                &sm.full[s]);
-  };
-
-  int64_t issued = 0;
-  if (tid == 0)
-    for (; issued < kStages && issued < nsteps; ++issued)
-      issue(issued);
-
-  Acc acc[VEC];
-#pragma unroll
-  for (int l = 0; l < VEC; ++l)
-    acc[l] = R::identity();
-  const bool active = tid * VEC < ncols;
-  bool dead = false;
-  for (int64_t i = 0; i < nsteps; ++i) {
-    const int s = (int)(i % kStages);
-    stage_wait(&sm.full[s], i / kStages, dead, status);
-    const int64_t r0 = r_begin + i * RS;
-    const int nr = (int)(r_end - r0 < RS ? r_end - r0 : RS);
-    if (active) {
-      const T *tile = tiles + (int64_t)s * TILE + tid * VEC;
-      for (int j = 0; j < nr; ++j) {
-        const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(tile + (int64_t)j * COLS);
-#pragma unroll
-        for (int l = 0; l < VEC; ++l)
-          R::acc(acc[l], x.v[l], r0 + j);
-      }
-    }
-    __syncthreads();
-    if (tid == 0 && issued < nsteps)
-      issue(issued++);
-  }
-  if (__syncthreads_or(dead))
-    drain_after_timeout(sm, issued);
-
-  if (Gy == 1) {
-    if (active)
-#pragma unroll
-      for (int l = 0; l < VEC; ++l)
-        out[c0 + tid * VEC + l] = R::fin(acc[l]);
-    return;
-  }
-  if (active)
-#pragma unroll
-    for (int l = 0; l < VEC; ++l)
-      partials[by * cols + c0 + tid * VEC + l] = acc[l];
-  __threadfence();
-  __shared__ bool last;
-  __syncthreads();
-  if (tid == 0)
-    last = atomicAdd(&counters[blockIdx.x], 1u) == (uint32_t)(Gy - 1);
-  __syncthreads();
-  if (!last)
-    return;
-  __threadfence();
-  if (active) {
-#pragma unroll
-    for (int l = 0; l < VEC; ++l) {
-      Acc m = R::identity();
-      for (int64_t y = 0; y < Gy; ++y)
-        m = R::merge(m, load_cg(partials + y * cols + c0 + tid * VEC + l));
-      out[c0 + tid * VEC + l] = R::fin(m);
-    }
-  }
-  if (tid == 0)
-    counters[blockIdx.x] = 0;
 }
 
 // ---------------------------------------------------------- full reduction ---

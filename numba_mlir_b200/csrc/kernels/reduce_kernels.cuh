@@ -3,7 +3,7 @@
 #pragma once
 
 #include "../gpu_common.h"
-#include "reduce_common.cuh"
+#include "reduce_ws.cuh"
 
 #define NMB_RED_TYPES(X, kind, op, RT)                                                         \
   X(kind, op, f32, RT<float>)                                                                  \

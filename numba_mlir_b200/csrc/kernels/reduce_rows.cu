@@ -1,14 +1,14 @@
 // Row (last-axis) reductions: out[r] = reduce(a[r, :]).
-// Launch: grid.x = min(rows, 444) CTAs of 256 threads.
+// Launch: grid.x = min(rows, 148) CTAs of 288 threads (8 consumer warps + 1 producer).
 #include "reduce_kernels.cuh"
 
 #define ROWS_KERNEL(kind, op, ty, R)                                                           \
-  extern "C" __global__ void __launch_bounds__(nmb::red::kThreads)                             \
+  extern "C" __global__ void __launch_bounds__(nmb::red::kWsThreads, 1)                             \
       nmb_reduce_rows_##op##_##ty(const R::In *a, R::Out *out, int64_t rows, int64_t cols,     \
                                   uint32_t *status) {                                          \
     extern __shared__ __align__(128) unsigned char nmb_smem[];                                 \
-    nmb::red::reduce_rows_body<R>(a, out, rows, cols, status, nmb_smem);                       \
+    nmb::red::reduce_rows_ws<R>(a, out, rows, cols, status, nmb_smem);                       \
   }                                                                                            \
-  NMB_REGISTER_KERNEL(nmb_reduce_rows_##op##_##ty, nmb::red::kSmemBytes);
+  NMB_REGISTER_KERNEL(nmb_reduce_rows_##op##_##ty, nmb::red::kRowSmemBytes);
 
 NMB_RED_ALL_OPS(ROWS_KERNEL, rows)

@@ -17,7 +17,8 @@ _TY = {np.dtype(np.float32): "f32", np.dtype(np.float64): "f64",
        np.dtype(np.int32): "i32", np.dtype(np.int64): "i64"}
 OPS = ("sum", "prod", "min", "max", "argmin", "argmax")
 SMS = 148  # B200
-_CTAS = SMS * 3  # three 65 KB CTAs fit one SM
+_CTAS = SMS * 3  # full reduction: three 65 KB CTAs fit one SM
+_WS_THREADS = 288  # 8 consumer warps + 1 TMA producer warp
 _TILE_BYTES = 16384
 _I64 = np.int64
 
@@ -90,8 +91,8 @@ def reduce(a, op, axis=None, out=None):
 
 def _launch_rows(q, a, out, op, ty, rows, cols):
     k = q.builtin(f"nmb_reduce_rows_{op}_{ty}")
-    grid = max(1, min(rows, _CTAS))
-    q.launch(k, (grid,), (256,),
+    grid = max(1, min(rows, SMS))  # one 209 KB CTA per SM
+    q.launch(k, (grid,), (_WS_THREADS,),
              [("ptr", a.ptr), ("ptr", out.ptr), _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
 
 
@@ -101,12 +102,12 @@ def _launch_cols(q, a, out, op, ty, rows, cols):
     tile_cols = 256 * vec
     col_tiles = (cols + tile_cols - 1) // tile_cols
     rows_per_stage = _TILE_BYTES // (tile_cols * a.dtype.itemsize)
-    row_blocks = max(1, min((_CTAS + col_tiles - 1) // col_tiles,
+    row_blocks = max(1, min((2 * SMS + col_tiles - 1) // col_tiles,
                             (rows + rows_per_stage - 1) // rows_per_stage, 65535))
     if col_tiles * 4 > q.COUNTER_BYTES:
         raise ValueError("too many column tiles for the counter region")
     counters, partials = q.scratch(row_blocks * cols * _acc_bytes(op, a.dtype))
-    q.launch(k, (col_tiles, row_blocks), (256,),
+    q.launch(k, (col_tiles, row_blocks), (_WS_THREADS,),
              [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
               _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
 
