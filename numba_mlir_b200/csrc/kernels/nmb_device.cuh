@@ -212,4 +212,22 @@ __device__ __forceinline__ double f_sqrt(double x) { return __dsqrt_rn(x); }
 __device__ __forceinline__ double f_erf(double x) { return erf(x); }
 __device__ __forceinline__ double f_div(double a, double b) { return __ddiv_rn(a, b); }
 
+
+// NumPy's maximum/minimum propagate NaNs.
+template <typename T> __device__ __forceinline__ T np_max(T a, T b) { return (a > b || a != a) ? a : b; }
+template <typename T> __device__ __forceinline__ T np_min(T a, T b) { return (a < b || a != a) ? a : b; }
+template <typename T> __device__ __forceinline__ T i_abs(T a) { return a < 0 ? -a : a; }
+template <typename T> __device__ __forceinline__ T i_pow(T base, T e) {
+  if (e < 0)
+    return base == 1 ? 1 : (base == -1 ? ((e & 1) ? -1 : 1) : 0);
+  T r = 1;
+  while (e) {
+    if (e & 1)
+      r *= base;
+    base *= base;
+    e >>= 1;
+  }
+  return r;
+}
+
 } // namespace nmb

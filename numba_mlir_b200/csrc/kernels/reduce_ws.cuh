@@ -15,9 +15,13 @@ namespace red {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kWsThreads = (kConsumerWarps + 1) * 32;
-constexpr int kRowStages = 12; // one 209 KB CTA per SM
+// Row kernel: one stage per consumer warp.  A stage must always be consumed by
+// the same warp: a warp that met a stage for the first time in a later phase
+// could not tell that phase from the one before it (mbarrier waits only see
+// the phase parity).
+constexpr int kRowStages = kConsumerWarps;
 constexpr int kColStages = 6;  // two 99 KB CTAs per SM
-constexpr int kRowSmemBytes = kRowStages * kTileBytes + 2 * kRowStages * 8;
+constexpr int kRowSmemBytes = kRowStages * kTileBytes + 2 * kRowStages * 8 + 2 * kConsumerWarps * 16;
 constexpr int kColSmemBytes = kColStages * kTileBytes + 2 * kColStages * 8;
 
 template <int STAGES> struct Ring {
@@ -80,9 +84,11 @@ __device__ __forceinline__ typename R::Acc warp_reduce_span(const typename R::In
 // out[r] = reduce(a[r, :]) for a C-contiguous (rows, cols) matrix whose base is
 // 16-byte aligned and whose row size is a multiple of 16 bytes.
 // Grid: G <= rows CTAs of kWsThreads; CTA b owns rows [rows*b/G, rows*(b+1)/G).
-// A tile is either `rt` whole rows (row <= 16 KB) or one 16 KB chunk of a row;
-// every tile of a row goes to the same consumer warp, so no cross-warp merge
-// is needed.
+// Rows of at most 16 KB: a tile is `rt` whole rows, tile i lives in stage i % 8
+// and is reduced by warp i % 8 alone (no cross-warp traffic).  Longer rows: a
+// tile is one 16 KB chunk of a row, every warp reduces an eighth of every tile
+// and the eight partials of a row meet in shared memory behind one named
+// barrier per row.
 template <typename R>
 __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict__ a,
                                                typename R::Out *__restrict__ out, int64_t rows,
@@ -94,7 +100,7 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
   constexpr int S = kRowStages;
   Ring<S> ring(smem_raw);
   T *tiles = reinterpret_cast<T *>(ring.tiles);
-  ring.init(1);
+  Acc *parts = reinterpret_cast<Acc *>(smem_raw + S * kTileBytes + 2 * S * 8); // [2][8]
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t G = gridDim.x, b = blockIdx.x;
@@ -103,6 +109,7 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
   const int64_t cpr = (cols + TILE - 1) / TILE;
   const int64_t rt = cpr == 1 ? (TILE / cols > 0 ? TILE / cols : 1) : 1;
   const int64_t ntiles = cpr == 1 ? (nrows + rt - 1) / rt : nrows * cpr;
+  ring.init(cpr == 1 ? 1 : kConsumerWarps);
   bool dead = false;
 
   if (warp == kConsumerWarps) {
@@ -135,8 +142,9 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
   }
 
   if (cpr == 1) {
+    // warp == stage: tiles warp, warp + 8, ... in order
     for (int64_t i = warp; i < ntiles; i += kConsumerWarps) {
-      const int s = (int)(i % S);
+      const int s = warp;
       stage_wait(&ring.full[s], i / S, dead, status);
       const T *tile = tiles + (int64_t)s * TILE;
       const int64_t r0 = r_begin + i * rt;
@@ -151,7 +159,9 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
         mbar_arrive(&ring.empty[s]);
     }
   } else {
-    for (int64_t lr = warp; lr < nrows; lr += kConsumerWarps) {
+    constexpr int VEC = 16 / sizeof(T);
+    constexpr int64_t PART = TILE / kConsumerWarps; // elements of a full tile per warp
+    for (int64_t lr = 0; lr < nrows; ++lr) {
       Acc racc = R::identity();
       for (int64_t ch = 0; ch < cpr; ++ch) {
         const int64_t i = lr * cpr + ch;
@@ -159,14 +169,26 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
         stage_wait(&ring.full[s], i / S, dead, status);
         const int64_t c0 = ch * TILE;
         const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
-        racc = R::merge(racc, warp_reduce_span<R>(tiles + (int64_t)s * TILE, ne, c0));
+        const int64_t p0 = warp * PART < ne ? warp * PART : ne;
+        const int64_t p1 = (warp + 1) * PART < ne ? (warp + 1) * PART : ne;
+        racc = R::merge(racc, warp_reduce_span<R>(tiles + (int64_t)s * TILE + p0, p1 - p0, c0 + p0));
         __syncwarp();
         if (lane == 0)
           mbar_arrive(&ring.empty[s]);
       }
+      Acc *slot = parts + (lr & 1) * kConsumerWarps;
       if (lane == 0)
-        out[r_begin + lr] = R::fin(racc);
+        slot[warp] = racc;
+      // named barrier 1: the 256 consumer threads only
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+      if (warp == 0) {
+        Acc m = lane < kConsumerWarps ? slot[lane] : R::identity();
+        m = warp_merge<R>(m);
+        if (lane == 0)
+          out[r_begin + lr] = R::fin(m);
+      }
     }
+    (void)VEC;
   }
 }
 

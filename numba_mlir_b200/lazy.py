@@ -1,0 +1,886 @@
+"""Array-expression front-end: NumPy expressions on device arrays -> fused kernels.
+
+What the reference does with MLIR -- turn every NumPy call into a
+`linalg.generic`, fuse the chain into one loop nest
+(numba_mlir/mlir_compiler/lib/pipelines/PlierToLinalg.cpp:4439-4587; the
+Black-Scholes test asserts one `scf.parallel`,
+numba_mlir/mlir/tests/test_numpy.py:2796-2866) and outline it as one GPU
+kernel -- is done here by recording the expression graph while the Python
+function runs on symbolic arrays and emitting ONE CUDA kernel per group of
+same-shaped results.  The kernel is an instance of the hand-written vectorised
+loop `nmb::eltwise_tile` (csrc/kernels/nmb_device.cuh) around a generated
+per-element body, compiled by NVRTC inside gpuxModuleLoad and launched through
+gpuxLaunchKernel.
+
+Typing follows Numba, like the reference (which reuses Numba's type inference):
+ufunc loops are chosen by `numba.np.numpy_support.ufunc_find_matching_loop`,
+Python floats are float64 and Python ints int64.
+
+A traced call is recorded as a Plan (allocations + launches with argument
+slots) and cached per argument signature, the analogue of the per-function
+context in which the reference caches queue/module/kernel handles
+(numba_mlir/mlir_compiler/lib/pipelines/LowerToGpu.cpp:742-940).
+"""
+
+import math
+import struct
+import threading
+
+import numpy as np
+
+from . import runtime as _rt
+from .device_array import DeviceArray, empty
+
+# ----------------------------------------------------------------- dtypes ---
+_CTYPE = {
+    "float32": "float", "float64": "double", "int8": "int8_t", "int16": "int16_t",
+    "int32": "int32_t", "int64": "int64_t", "uint8": "uint8_t", "uint16": "uint16_t",
+    "uint32": "uint32_t", "uint64": "uint64_t", "bool": "bool",
+}
+
+
+def ctype(dtype):
+    try:
+        return _CTYPE[np.dtype(dtype).name]
+    except KeyError:
+        raise TypeError(f"dtype {dtype} is not supported on the device") from None
+
+
+def literal(value, dtype):
+    """Exact C literal of a NumPy scalar."""
+    dtype = np.dtype(dtype)
+    if dtype == np.float32:
+        bits = struct.unpack("<I", struct.pack("<f", float(value)))[0]
+        return f"__uint_as_float(0x{bits:08x}u)"
+    if dtype == np.float64:
+        bits = struct.unpack("<q", struct.pack("<d", float(value)))[0]
+        return f"__longlong_as_double({bits}ll)" if bits >= 0 else f"__longlong_as_double((long long)0x{bits & (2**64 - 1):016x}ull)"
+    if dtype == np.bool_:
+        return "true" if value else "false"
+    if dtype.kind == "u":
+        return f"({ctype(dtype)}){int(value)}ull"
+    return f"({ctype(dtype)}){int(value)}ll"
+
+
+def scalar_dtype(value):
+    """Numba's typing of Python scalars: float -> float64, int -> int64."""
+    if isinstance(value, (bool, np.bool_)):
+        return np.dtype(np.bool_)
+    if isinstance(value, np.generic):
+        return value.dtype
+    if isinstance(value, int):
+        return np.dtype(np.int64)
+    if isinstance(value, float):
+        return np.dtype(np.float64)
+    raise TypeError(f"unsupported scalar {type(value)}")
+
+
+_loop_cache = {}
+
+
+def find_loop(ufunc, in_dtypes):
+    """(loop input dtypes, output dtype) chosen the way Numba chooses."""
+    key = (ufunc, tuple(in_dtypes))
+    hit = _loop_cache.get(key)
+    if hit is None:
+        from numba.np import numpy_support as ns
+
+        loop = ns.ufunc_find_matching_loop(ufunc, tuple(ns.from_dtype(d) for d in in_dtypes))
+        if loop is None:
+            raise TypeError(f"no {ufunc.__name__} loop for {in_dtypes}")
+        hit = ([ns.as_dtype(t) for t in loop.inputs], ns.as_dtype(loop.outputs[0]))
+        _loop_cache[key] = hit
+    return hit
+
+
+# ------------------------------------------------------------------- ops ----
+def _flt(f32, f64):
+    return lambda dt, *a: (f32 if dt == np.float32 else f64).format(*a)
+
+
+def _int_or_float(int_expr, f32, f64):
+    def emit(dt, *a):
+        if dt.kind in "iub":
+            return int_expr.format(*a)
+        return (f32 if dt == np.float32 else f64).format(*a)
+
+    return emit
+
+
+# name -> (numpy ufunc, emitter(loop_dtype, *operand exprs))
+UFUNCS = {
+    "add": (np.add, lambda dt, a, b: f"({a} + {b})"),
+    "subtract": (np.subtract, lambda dt, a, b: f"({a} - {b})"),
+    "multiply": (np.multiply, lambda dt, a, b: f"({a} * {b})"),
+    "true_divide": (np.true_divide, lambda dt, a, b: f"nmb::f_div({a}, {b})"),
+    "negative": (np.negative, lambda dt, a: f"(-{a})"),
+    "positive": (np.positive, lambda dt, a: f"({a})"),
+    "absolute": (np.absolute, _int_or_float("nmb::i_abs({0})", "fabsf({0})", "fabs({0})")),
+    "sqrt": (np.sqrt, lambda dt, a: f"nmb::f_sqrt({a})"),
+    "log": (np.log, lambda dt, a: f"nmb::f_log({a})"),
+    "exp": (np.exp, lambda dt, a: f"nmb::f_exp({a})"),
+    "sin": (np.sin, _flt("sinf({0})", "sin({0})")),
+    "cos": (np.cos, _flt("cosf({0})", "cos({0})")),
+    "tan": (np.tan, _flt("tanf({0})", "tan({0})")),
+    "tanh": (np.tanh, _flt("tanhf({0})", "tanh({0})")),
+    "arctan2": (np.arctan2, _flt("atan2f({0}, {1})", "atan2({0}, {1})")),
+    "arccos": (np.arccos, _flt("acosf({0})", "acos({0})")),
+    "floor": (np.floor, _flt("floorf({0})", "floor({0})")),
+    "ceil": (np.ceil, _flt("ceilf({0})", "ceil({0})")),
+    "square": (np.square, lambda dt, a: f"({a} * {a})"),
+    "power": (np.power, _int_or_float("nmb::i_pow({0}, {1})", "powf({0}, {1})", "pow({0}, {1})")),
+    "maximum": (np.maximum, lambda dt, a, b: f"nmb::np_max({a}, {b})"),
+    "minimum": (np.minimum, lambda dt, a, b: f"nmb::np_min({a}, {b})"),
+    "less": (np.less, lambda dt, a, b: f"({a} < {b})"),
+    "less_equal": (np.less_equal, lambda dt, a, b: f"({a} <= {b})"),
+    "greater": (np.greater, lambda dt, a, b: f"({a} > {b})"),
+    "greater_equal": (np.greater_equal, lambda dt, a, b: f"({a} >= {b})"),
+    "equal": (np.equal, lambda dt, a, b: f"({a} == {b})"),
+    "not_equal": (np.not_equal, lambda dt, a, b: f"({a} != {b})"),
+    "logical_and": (np.logical_and, lambda dt, a, b: f"(({a} != 0) && ({b} != 0))"),
+    "logical_or": (np.logical_or, lambda dt, a, b: f"(({a} != 0) || ({b} != 0))"),
+    "logical_not": (np.logical_not, lambda dt, a: f"(!({a} != 0))"),
+}
+_UFUNC_BY_OBJ = {u: name for name, (u, _e) in UFUNCS.items()}
+_UFUNC_BY_OBJ[np.divide] = "true_divide"
+_UFUNC_BY_OBJ[np.abs] = "absolute"
+
+REDUCTIONS = {np.sum: "sum", np.prod: "prod", np.min: "min", np.max: "max", np.amin: "min",
+              np.amax: "max", np.argmin: "argmin", np.argmax: "argmax"}
+
+
+# ------------------------------------------------------------------ nodes ---
+class Node:
+    """Expression-graph node.  kind: 'leaf' (device array), 'arg' (scalar
+    argument, a kernel parameter), 'const' (literal), 'op' (ufunc), 'cast',
+    'where', 'call' (user scalar device function)."""
+
+    __slots__ = ("kind", "dtype", "shape", "inputs", "op", "value", "slot", "sig")
+
+    def __init__(self, kind, dtype, shape, inputs=(), op=None, value=None, slot=None):
+        self.kind = kind
+        self.dtype = np.dtype(dtype)
+        self.shape = tuple(shape)
+        self.inputs = tuple(inputs)
+        self.op = op
+        self.value = value
+        self.slot = slot
+        self.sig = None
+
+
+def broadcast_shapes(*shapes):
+    return np.broadcast_shapes(*shapes)
+
+
+class DeviceFunc:
+    """Scalar function compiled to a CUDA __device__ function and usable as an
+    elementwise operation (what @vectorize of a scalar body gives the
+    reference, numba_mlir/mlir/vectorize.py:45-70)."""
+
+    def __init__(self, name, source, arg_dtypes, ret_dtype):
+        self.name = name
+        self.source = source
+        self.arg_dtypes = tuple(np.dtype(d) for d in arg_dtypes)
+        self.ret_dtype = np.dtype(ret_dtype)
+
+
+# ---------------------------------------------------------------- tracing ---
+class Trace:
+    """State of one traced call: slot table, pending stores, recorded steps."""
+
+    def __init__(self, queue, args=None, dry=False):
+        self.queue = queue
+        self.dry = dry  # record and generate code only (no device)
+        self.slots = []          # slot -> ("arg", index, views) | ("tmp", shape, dtype, views)
+        self.arrays = []         # slot -> DeviceArray (this call's binding)
+        self.pending = []        # [(target LazyArray leaf, value Node)]
+        self.steps = []
+        self.value_dependent = False
+        self.args = args
+
+    # slots ---------------------------------------------------------------------
+    # slot -> ("arg", index) | ("tmp", shape, dtype) | ("view", base slot, op)
+    #         | ("captured",)
+    def add_arg_slot(self, index, array):
+        self.slots.append(("arg", index) if index is not None else ("captured",))
+        self.arrays.append(array)
+        return len(self.slots) - 1
+
+    def add_tmp_slot(self, shape, dtype):
+        if self.dry:
+            arr = fake_array(shape, dtype)
+        else:
+            arr = empty(shape, dtype, queue=self.queue)
+        self.slots.append(("tmp", tuple(shape), np.dtype(dtype)))
+        self.arrays.append(arr)
+        self.steps.append(("alloc", len(self.slots) - 1))
+        return len(self.slots) - 1
+
+    def add_view_slot(self, base_slot, view_op, array):
+        self.slots.append(("view", base_slot, view_op))
+        self.arrays.append(array)
+        return len(self.slots) - 1
+
+    def leaf(self, slot):
+        arr = self.arrays[slot]
+        return LazyArray(self, Node("leaf", arr.dtype, arr.shape, slot=slot))
+
+    def has_pending(self, slot):
+        return any(s == slot for s, _ in self.pending)
+
+    # stores ----------------------------------------------------------------------
+    def store(self, target_slot, node):
+        self.pending.append((target_slot, node))
+
+    def flush(self):
+        """Emits the pending stores, one fused kernel per output shape."""
+        pending, self.pending = self.pending, []
+        groups = {}
+        for slot, node in pending:
+            groups.setdefault(self.arrays[slot].shape, []).append((slot, node))
+        for shape, outs in groups.items():
+            _emit_eltwise(self, shape, outs)
+
+    def materialize(self, lazy):
+        """Device array (slot) holding the value of `lazy`."""
+        node = lazy.node
+        if node.kind == "leaf":
+            if self.has_pending(node.slot):
+                self.flush()
+            return node.slot
+        slot = self.add_tmp_slot(node.shape, node.dtype)
+        self.store(slot, node)
+        self.flush()
+        return slot
+
+
+_tls = threading.local()
+
+
+def current_trace():
+    return getattr(_tls, "trace", None)
+
+
+class _TraceScope:
+    def __init__(self, trace):
+        self.trace = trace
+
+    def __enter__(self):
+        self.prev = current_trace()
+        _tls.trace = self.trace
+        return self.trace
+
+    def __exit__(self, *exc):
+        _tls.trace = self.prev
+
+
+def _as_node(trace, x):
+    if isinstance(x, LazyArray):
+        if x.node.kind == "leaf" and trace.pending and trace.has_pending(x.node.slot):
+            trace.flush()  # the array is read after a recorded store to it
+        return x.node
+    if isinstance(x, DeviceArray):
+        slot = trace.add_arg_slot(None, x)
+        trace.value_dependent = True  # a captured array: not replayable
+        return Node("leaf", x.dtype, x.shape, slot=slot)
+    if isinstance(x, (bool, int, float, np.generic)):
+        dt = scalar_dtype(x)
+        return Node("const", dt, (), value=dt.type(x))
+    raise TypeError(f"cannot use {type(x)} in a device expression")
+
+
+class LazyArray:
+    """Symbolic array (or 0-d scalar) inside a traced function."""
+
+    __array_priority__ = 1000
+
+    def __init__(self, trace, node, concrete=None):
+        self.trace = trace
+        self.node = node
+        self.concrete = concrete  # value of scalar arguments, for control flow
+
+    # metadata ------------------------------------------------------------------
+    @property
+    def shape(self):
+        return self.node.shape
+
+    @property
+    def dtype(self):
+        return self.node.dtype
+
+    @property
+    def ndim(self):
+        return len(self.node.shape)
+
+    @property
+    def size(self):
+        return int(np.prod(self.node.shape, dtype=np.int64))
+
+    def __len__(self):
+        return self.node.shape[0]
+
+    # numpy protocols -------------------------------------------------------------
+    def __array_ufunc__(self, ufunc, method, *inputs, **kwargs):
+        if method != "__call__" or kwargs.get("out") is not None:
+            return NotImplemented
+        name = _UFUNC_BY_OBJ.get(ufunc)
+        if name is None:
+            raise TypeError(f"numpy.{ufunc.__name__} is not supported on device arrays")
+        return apply_ufunc(self.trace, name, inputs)
+
+    def __array_function__(self, func, types, args, kwargs):
+        if func in REDUCTIONS:
+            return reduce_lazy(self.trace, REDUCTIONS[func], *args, **kwargs)
+        if func is np.where and len(args) == 3:
+            return where(self.trace, *args)
+        if func is np.dot:
+            return dot(self.trace, *args, **kwargs)
+        if func in (np.empty_like, np.zeros_like):
+            like = args[0]
+            slot = self.trace.add_tmp_slot(like.shape, kwargs.get("dtype") or like.dtype)
+            out = self.trace.leaf(slot)
+            if func is np.zeros_like:
+                out[...] = like.dtype.type(0)
+            return out
+        if func is np.shape:
+            return self.shape
+        raise TypeError(f"numpy.{func.__name__} is not supported on device arrays")
+
+    # operators -------------------------------------------------------------------
+    def _bin(self, name, other, swap=False):
+        return apply_ufunc(self.trace, name, (other, self) if swap else (self, other))
+
+    def __add__(self, o): return self._bin("add", o)
+    def __radd__(self, o): return self._bin("add", o, True)
+    def __sub__(self, o): return self._bin("subtract", o)
+    def __rsub__(self, o): return self._bin("subtract", o, True)
+    def __mul__(self, o): return self._bin("multiply", o)
+    def __rmul__(self, o): return self._bin("multiply", o, True)
+    def __truediv__(self, o): return self._bin("true_divide", o)
+    def __rtruediv__(self, o): return self._bin("true_divide", o, True)
+    def __pow__(self, o): return self._bin("power", o)
+    def __rpow__(self, o): return self._bin("power", o, True)
+    def __neg__(self): return apply_ufunc(self.trace, "negative", (self,))
+    def __pos__(self): return self
+    def __abs__(self): return apply_ufunc(self.trace, "absolute", (self,))
+    def __lt__(self, o): return self._bin("less", o)
+    def __le__(self, o): return self._bin("less_equal", o)
+    def __gt__(self, o): return self._bin("greater", o)
+    def __ge__(self, o): return self._bin("greater_equal", o)
+    def __eq__(self, o): return self._bin("equal", o)
+    def __ne__(self, o): return self._bin("not_equal", o)
+    __hash__ = None
+
+    # concrete escapes (scalars only) ---------------------------------------------
+    def _escape(self):
+        if self.concrete is None:
+            raise TypeError("the value of a device expression is not available while tracing; "
+                            "only scalar arguments can drive Python control flow")
+        self.trace.value_dependent = True
+        return self.concrete
+
+    def __bool__(self): return bool(self._escape())
+    def __float__(self): return float(self._escape())
+    def __int__(self): return int(self._escape())
+    def __index__(self): return int(self._escape())
+
+    # reductions / methods ----------------------------------------------------------
+    def sum(self, axis=None, dtype=None): return reduce_lazy(self.trace, "sum", self, axis=axis, dtype=dtype)
+    def prod(self, axis=None, dtype=None): return reduce_lazy(self.trace, "prod", self, axis=axis, dtype=dtype)
+    def min(self, axis=None): return reduce_lazy(self.trace, "min", self, axis=axis)
+    def max(self, axis=None): return reduce_lazy(self.trace, "max", self, axis=axis)
+    def argmin(self, axis=None): return reduce_lazy(self.trace, "argmin", self, axis=axis)
+    def argmax(self, axis=None): return reduce_lazy(self.trace, "argmax", self, axis=axis)
+    def dot(self, other): return dot(self.trace, self, other)
+    def __matmul__(self, other): return dot(self.trace, self, other)
+
+    def astype(self, dtype):
+        dtype = np.dtype(dtype)
+        if dtype == self.dtype:
+            return self
+        return LazyArray(self.trace, Node("cast", dtype, self.shape, (self.node,)))
+
+    # views -------------------------------------------------------------------------
+    def _view(self, view_op, fn):
+        slot = self.trace.materialize(self)
+        arr = fn(self.trace.arrays[slot])
+        return self.trace.leaf(self.trace.add_view_slot(slot, view_op, arr))
+
+    @property
+    def T(self):
+        return self._view(("T",), lambda a: a.T)
+
+    def reshape(self, *shape):
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list)):
+            shape = tuple(shape[0])
+        return self._view(("reshape", shape), lambda a: a.reshape(shape))
+
+    def __getitem__(self, idx):
+        if idx is Ellipsis or (isinstance(idx, slice) and idx == slice(None)):
+            return self
+        return self._view(("getitem", idx), lambda a: a[idx])
+
+    def __setitem__(self, idx, value):
+        target = self if (idx is Ellipsis or idx == slice(None)) else self[idx]
+        if target.node.kind != "leaf":
+            raise TypeError("cannot assign into an expression")
+        vnode = _as_node(self.trace, value)
+        broadcast_shapes(vnode.shape, target.shape)  # raises on mismatch
+        if np.broadcast_shapes(vnode.shape, target.shape) != target.shape:
+            raise ValueError(f"could not broadcast {vnode.shape} into {target.shape}")
+        if vnode.dtype != target.dtype:
+            vnode = Node("cast", target.dtype, vnode.shape, (vnode,))
+        self.trace.store(target.node.slot, vnode)
+
+
+def apply_ufunc(trace, name, inputs):
+    nodes = [_as_node(trace, x) for x in inputs]
+    ufunc, _emit = UFUNCS[name]
+    loop_in, out_dt = find_loop(ufunc, [n.dtype for n in nodes])
+    cast = [n if n.dtype == d else Node("cast", d, n.shape, (n,)) for n, d in zip(nodes, loop_in)]
+    shape = broadcast_shapes(*[n.shape for n in nodes])
+    node = Node("op", out_dt, shape, cast, op=name)
+    concrete = None
+    if shape == () and all(isinstance(x, LazyArray) and x.concrete is not None or
+                           not isinstance(x, (LazyArray, DeviceArray)) for x in inputs):
+        vals = [x.concrete if isinstance(x, LazyArray) else x for x in inputs]
+        with np.errstate(all="ignore"):
+            concrete = out_dt.type(ufunc(*[d.type(v) for v, d in zip(vals, loop_in)]))
+    return LazyArray(trace, node, concrete)
+
+
+def where(trace, cond, x, y):
+    c, a, b = (_as_node(trace, v) for v in (cond, x, y))
+    out_dt = np.result_type(a.dtype, b.dtype)
+    a = a if a.dtype == out_dt else Node("cast", out_dt, a.shape, (a,))
+    b = b if b.dtype == out_dt else Node("cast", out_dt, b.shape, (b,))
+    shape = broadcast_shapes(c.shape, a.shape, b.shape)
+    return LazyArray(trace, Node("where", out_dt, shape, (c, a, b)))
+
+
+def call_device_func(trace, func, inputs):
+    nodes = [_as_node(trace, x) for x in inputs]
+    cast = [n if n.dtype == d else Node("cast", d, n.shape, (n,)) for n, d in zip(nodes, func.arg_dtypes)]
+    shape = broadcast_shapes(*[n.shape for n in nodes])
+    return LazyArray(trace, Node("call", func.ret_dtype, shape, cast, op=func))
+
+
+def reduce_lazy(trace, op, a, axis=None, dtype=None, keepdims=False, out=None):
+    if keepdims or out is not None:
+        raise TypeError("keepdims/out are not supported in device reductions")
+    from . import reduce_ops
+
+    if dtype is not None and np.dtype(dtype) != a.dtype:
+        a = a.astype(dtype)
+    src = trace.materialize(a)
+    arr = trace.arrays[src]
+    if isinstance(axis, LazyArray):
+        axis = int(axis)
+    oshape = () if axis is None else arr.shape[:axis % arr.ndim] + arr.shape[axis % arr.ndim + 1:]
+    dst = trace.add_tmp_slot(oshape, reduce_ops.out_dtype(op, arr.dtype))
+    trace.steps.append(("reduce", op, axis, src, dst))
+    if not trace.dry:
+        reduce_ops.reduce(arr, op, axis, out=trace.arrays[dst])
+    return trace.leaf(dst)
+
+
+def dot(trace, a, b, out=None):
+    from . import contraction
+
+    sa, sb = trace.materialize(a), trace.materialize(b)
+    A, B = trace.arrays[sa], trace.arrays[sb]
+    if A.ndim != 2 or B.ndim != 2 or A.shape[1] != B.shape[0]:
+        raise ValueError("dot needs 2-D operands with matching inner dimension")
+    if out is None:
+        dst = trace.add_tmp_slot((A.shape[0], B.shape[1]), np.result_type(A.dtype, B.dtype))
+    else:
+        dst = trace.materialize(out)
+    trace.steps.append(("dot", sa, sb, dst))
+    if not trace.dry:
+        contraction.gemm(A, B, trace.arrays[dst])
+    return trace.leaf(dst)
+
+
+# ---------------------------------------------------------------- codegen ---
+def _leaf_access(leaf_arr, out_shape):
+    """How a leaf is addressed from the flat C-order output index i.
+
+    Returns (kind, params): 'full' (same shape, contiguous: index i), 'splat'
+    (one element), 'row' (contiguous trailing block, leading dims broadcast:
+    i % size), 'col' (contiguous leading block, trailing dims broadcast:
+    i / inner), 'strided' (general: per-dimension element strides)."""
+    shape = (1,) * (len(out_shape) - leaf_arr.ndim) + leaf_arr.shape
+    it = leaf_arr.dtype.itemsize
+    strides = (0,) * (len(out_shape) - leaf_arr.ndim) + tuple(s // it for s in leaf_arr.strides)
+    strides = tuple(0 if d == 1 else s for d, s in zip(shape, strides))
+    n = int(np.prod(shape, dtype=np.int64))
+    if n == 1:
+        return "splat", ()
+    contiguous = leaf_arr.is_c_contiguous
+    if contiguous and shape == tuple(out_shape):
+        return "full", ()
+    if contiguous:
+        lead = 0
+        while lead < len(shape) and shape[lead] == 1:
+            lead += 1
+        if shape[lead:] == tuple(out_shape[lead:]):
+            return "row", (n,)
+        tail = len(shape)
+        while tail > 0 and shape[tail - 1] == 1:
+            tail -= 1
+        if shape[:tail] == tuple(out_shape[:tail]):
+            return "col", (int(np.prod(out_shape[tail:], dtype=np.int64)),)
+    return "strided", tuple(strides)
+
+
+class _Emitter:
+    def __init__(self, trace, out_shape):
+        self.trace = trace
+        self.out_shape = tuple(out_shape)
+        self.lines = []
+        self.names = {}          # id(node) -> C expression
+        self.leaves = []         # [(slot, kind, params, dtype)]
+        self.leaf_index = {}
+        self.scalar_args = []    # [(arg index, dtype)]
+        self.scalar_index = {}
+        self.funcs = {}
+        self.sig = []
+
+    def leaf(self, node):
+        key = node.slot
+        if key not in self.leaf_index:
+            arr = self.trace.arrays[node.slot]
+            kind, params = _leaf_access(arr, self.out_shape)
+            self.leaf_index[key] = len(self.leaves)
+            self.leaves.append((node.slot, kind, params, arr.dtype))
+        return self.leaf_index[key]
+
+    def emit(self, node):
+        key = id(node)
+        if key in self.names:
+            return self.names[key]
+        if node.kind == "leaf":
+            expr = f"r.in{self.leaf(node)}.v[l]"
+            self.sig.append(("leaf", self.leaf_index[node.slot]))
+        elif node.kind == "const":
+            expr = literal(node.value, node.dtype)
+            self.sig.append(("const", expr))
+        elif node.kind == "arg":
+            if node.value not in self.scalar_index:
+                self.scalar_index[node.value] = len(self.scalar_args)
+                self.scalar_args.append((node.value, node.dtype))
+            expr = f"s{self.scalar_index[node.value]}"
+            self.sig.append(("arg", self.scalar_index[node.value], node.dtype.name))
+        else:
+            ins = [self.emit(i) for i in node.inputs]
+            if node.kind == "cast":
+                rhs = f"static_cast<{ctype(node.dtype)}>({ins[0]})"
+                if node.inputs[0].dtype.kind == "f" and node.dtype.kind == "b":
+                    rhs = f"({ins[0]} != 0)"
+            elif node.kind == "where":
+                rhs = f"(({ins[0]}) ? {ins[1]} : {ins[2]})"
+            elif node.kind == "call":
+                self.funcs[node.op.name] = node.op.source
+                rhs = f"{node.op.name}({', '.join(ins)})"
+            else:
+                loop_dt = node.inputs[0].dtype
+                rhs = UFUNCS[node.op][1](loop_dt, *ins)
+            expr = f"t{len(self.lines)}"
+            self.lines.append(f"const {ctype(node.dtype)} {expr} = {rhs};")
+            self.sig.append((node.kind, node.op if node.kind == "op" else
+                             getattr(node.op, "name", None), node.dtype.name, tuple(ins)))
+        self.names[key] = expr
+        return expr
+
+
+_kernel_cache = {}
+
+
+def _emit_eltwise(trace, out_shape, outs):
+    """One fused kernel storing every (slot, node) of `outs` (same shape)."""
+    n = int(np.prod(out_shape, dtype=np.int64))
+    if n == 0:
+        return
+    em = _Emitter(trace, out_shape)
+    results = [(slot, em.emit(node), trace.arrays[slot]) for slot, node in outs]
+    for slot, _expr, arr in results:
+        if not arr.is_c_contiguous:
+            raise TypeError("assignment targets must be C-contiguous")
+    # vector width: 4 elements per step when every access allows it
+    vec_ok = True
+    for slot, kind, params, dt in em.leaves:
+        arr = trace.arrays[slot]
+        unit = 4 * dt.itemsize if dt.itemsize <= 4 else 16
+        if kind in ("full", "row") and arr.ptr % unit:
+            vec_ok = False
+        if kind in ("row", "col") and params[0] % 4:
+            vec_ok = False
+        if kind == "strided":
+            pass
+    for slot, _expr, arr in results:
+        unit = 4 * arr.dtype.itemsize if arr.dtype.itemsize <= 4 else 16
+        if arr.ptr % unit:
+            vec_ok = False
+    vec = 4 if vec_ok else 1
+    n_streams = sum(1 for _s, k, _p, _d in em.leaves if k == "full") + len(results)
+    unroll = 4 if n_streams <= 3 else 2
+
+    sig = (tuple(out_shape) if any(k == "strided" for _s, k, _p, _d in em.leaves) else len(out_shape),
+           tuple((k, p if k == "strided" else (), d.name) for _s, k, p, d in em.leaves),
+           tuple(em.sig), tuple((e, a.dtype.name) for _s, e, a in results), vec, unroll)
+    hit = _kernel_cache.get(sig)
+    if hit is None:
+        hit = _generate(em, results, out_shape, vec, unroll)
+        _kernel_cache[sig] = hit
+    blob, kname = hit
+
+    params = []
+    for slot, kind, p, dt in em.leaves:
+        params.append(("slot", slot))
+        if kind in ("row", "col"):
+            params.append(("i64", p[0]))
+    for index, dt in em.scalar_args:
+        params.append(("scalar", index, dt))
+    for slot, _expr, _arr in results:
+        params.append(("slot", slot))
+    params.append(("i64", n))
+    tile = 256 * vec * unroll
+    step = ("launch", blob, kname, ((n + tile - 1) // tile,), (256,), tuple(params))
+    trace.steps.append(step)
+    if not trace.dry:
+        run_launch(trace.queue, step, trace.arrays, trace.args)
+
+
+def _generate(em, results, out_shape, vec, unroll):
+    """CUDA C for one fused chain; returns (tagged source blob, kernel name)."""
+    members, ctor, kparams = [], [], []
+    in_fields, loads = [], []
+    nd = len(out_shape)
+    for i, (slot, kind, p, dt) in enumerate(em.leaves):
+        ct = ctype(dt)
+        members.append(f"const {ct}* __restrict__ in{i};")
+        kparams.append(f"const {ct}* __restrict__ in{i}")
+        ctor.append(f"in{i}")
+        in_fields.append(f"nmb::Vec<{ct}, V> in{i};")
+        if kind == "full":
+            loads.append(f"r.in{i} = nmb::load_stream<{ct}, V>(in{i} + i);")
+        elif kind == "splat":
+            loads.append(f"{{ const {ct} x = __ldg(in{i}); for (int l = 0; l < V; ++l) r.in{i}.v[l] = x; }}")
+        elif kind == "row":
+            members.append(f"int64_t m{i};")
+            kparams.append(f"int64_t m{i}")
+            ctor.append(f"m{i}")
+            loads.append(f"r.in{i} = nmb::load_reuse<{ct}, V>(in{i} + (i % m{i}));")
+        elif kind == "col":
+            members.append(f"int64_t m{i};")
+            kparams.append(f"int64_t m{i}")
+            ctor.append(f"m{i}")
+            loads.append(f"{{ const {ct} x = __ldg(in{i} + (i / m{i})); for (int l = 0; l < V; ++l) r.in{i}.v[l] = x; }}")
+        else:  # strided: decompose the flat index over the output shape
+            body = [f"for (int l = 0; l < V; ++l) {{ int64_t rem = i + l, off = 0, q;"]
+            for d in range(nd - 1, -1, -1):
+                if p[d] != 0:
+                    body.append(f"q = rem % {out_shape[d]}ll; off += q * ({p[d]}ll); rem /= {out_shape[d]}ll;")
+                else:
+                    body.append(f"rem /= {out_shape[d]}ll;")
+            body.append(f"r.in{i}.v[l] = __ldg(in{i} + off); }}")
+            loads.append(" ".join(body))
+    for j, (index, dt) in enumerate(em.scalar_args):
+        members.append(f"{ctype(dt)} s{j};")
+        kparams.append(f"{ctype(dt)} s{j}")
+        ctor.append(f"s{j}")
+    out_fields, stores, out_assign = [], [], []
+    for j, (slot, expr, arr) in enumerate(results):
+        ct = ctype(arr.dtype)
+        members.append(f"{ct}* __restrict__ out{j};")
+        kparams.append(f"{ct}* __restrict__ out{j}")
+        ctor.append(f"out{j}")
+        out_fields.append(f"nmb::Vec<{ct}, V> out{j};")
+        out_assign.append(f"o.out{j}.v[l] = {expr};")
+        stores.append(f"nmb::store_stream<{ct}, V>(out{j} + i, o.out{j});")
+    kparams.append("int64_t n")
+    nl = "\n      "
+    funcs = "\n".join(em.funcs.values())
+    src = f"""//NMB200:CUDA-SOURCE
+//NMB200:OPTIONS --fmad=false
+#include "nmb_device.cuh"
+{funcs}
+struct Chain {{
+  {(nl[:-4]).join(members)}
+  template <int V> struct In {{ {' '.join(in_fields) or 'int unused;'} }};
+  template <int V> struct Out {{ {' '.join(out_fields)} }};
+  template <int V> __device__ __forceinline__ void load(int64_t i, In<V>& r) const {{
+    {(nl[:-2]).join(loads)}
+  }}
+  template <int V> __device__ __forceinline__ void compute(const In<V>& r, Out<V>& o) const {{
+#pragma unroll
+    for (int l = 0; l < V; ++l) {{
+      {nl.join(em.lines)}
+      {nl.join(out_assign)}
+    }}
+  }}
+  template <int V> __device__ __forceinline__ void store(int64_t i, const Out<V>& o) const {{
+    {(nl[:-2]).join(stores)}
+  }}
+}};
+extern "C" __global__ void __launch_bounds__(256) nmb_fused({', '.join(kparams)}) {{
+  Chain chain{{{', '.join(ctor)}}};
+  nmb::eltwise_tile<256, {vec}, {unroll}>(chain, n);
+}}
+"""
+    return src.encode(), "nmb_fused"
+
+
+# ------------------------------------------------------------- execution ----
+def run_launch(queue, step, arrays, args):
+    _tag, blob, kname, grid, block, params = step
+    kernel = queue.get_kernel(queue.load_module(blob), kname)
+    packed = []
+    for p in params:
+        if p[0] == "slot":
+            packed.append(("ptr", arrays[p[1]].ptr))
+        elif p[0] == "i64":
+            packed.append(np.int64(p[1]))
+        else:
+            packed.append(p[2].type(args[p[1]]))
+    queue.launch(kernel, grid, block, packed)
+
+
+def assign(target, value):
+    """Eager `target[...] = value` outside a traced function."""
+    trace = Trace(target.queue)
+    with _TraceScope(trace):
+        slot = trace.add_arg_slot(None, target)
+        trace.leaf(slot)[...] = value if not isinstance(value, DeviceArray) else trace.leaf(
+            trace.add_arg_slot(None, value))
+        trace.flush()
+
+
+# ------------------------------------------------------------------ plans ---
+class Plan:
+    """Recorded launches of one traced call, replayable on new arguments of
+    the same signature."""
+
+    def __init__(self, trace, result_spec):
+        self.slots = trace.slots
+        self.steps = trace.steps
+        self.result_spec = result_spec
+        self.queue = trace.queue
+
+    def replay(self, args):
+        from . import contraction, reduce_ops
+
+        slots = self.slots
+        arrays = [None] * len(slots)
+
+        def get(i):
+            arr = arrays[i]
+            if arr is None:
+                s = slots[i]
+                if s[0] == "arg":
+                    arr = args[s[1]]
+                elif s[0] == "view":
+                    base, op = get(s[1]), s[2]
+                    arr = base.T if op[0] == "T" else base.reshape(op[1]) if op[0] == "reshape" else base[op[1]]
+                else:
+                    raise RuntimeError("plan slot used before its allocation")
+                arrays[i] = arr
+            return arr
+
+        q = self.queue
+        for step in self.steps:
+            tag = step[0]
+            if tag == "alloc":
+                s = slots[step[1]]
+                arrays[step[1]] = empty(s[1], s[2], queue=q)
+            elif tag == "launch":
+                for p in step[5]:
+                    if p[0] == "slot":
+                        get(p[1])
+                run_launch(q, step, arrays, args)
+            elif tag == "reduce":
+                reduce_ops.reduce(get(step[3]), step[1], step[2], out=get(step[4]))
+            elif tag == "dot":
+                contraction.gemm(get(step[1]), get(step[2]), get(step[3]))
+        for i in _result_slots(self.result_spec):
+            get(i)
+        return _build_result(self.result_spec, arrays)
+
+
+def _result_slots(spec):
+    if spec is None:
+        return []
+    if spec[0] == "slot":
+        return [spec[1]]
+    if spec[0] == "tuple":
+        return [i for s in spec[1] for i in _result_slots(s)]
+    return []
+
+
+def _build_result(spec, arrays):
+    if spec is None:
+        return None
+    if spec[0] == "slot":
+        return arrays[spec[1]]
+    if spec[0] == "tuple":
+        return tuple(_build_result(s, arrays) for s in spec[1])
+    return spec[1]  # ("value", x)
+
+
+def signature_of(args):
+    sig = []
+    for a in args:
+        if isinstance(a, DeviceArray):
+            sig.append(("arr", a.dtype.name, a.shape, a.strides, a.ptr % 16 == 0, a.queue.device))
+        elif isinstance(a, (bool, int, float, np.generic)):
+            sig.append(("scalar", scalar_dtype(a).name))
+        else:
+            return None
+    return tuple(sig)
+
+
+def fake_array(shape, dtype, ptr=0x7F0000000000):
+    """Array descriptor without memory, for code generation without a device."""
+    from .device_array import _Foreign
+
+    dtype = np.dtype(dtype)
+    n = int(np.prod(shape, dtype=np.int64))
+    return DeviceArray(_Foreign(None, ptr, n * dtype.itemsize, None), shape, dtype)
+
+
+def trace_call(func, args, queue, dry=False):
+    """Runs `func` on symbolic arguments, executing the device work as it is
+    recorded (unless `dry`).  Returns (result, plan or None)."""
+    trace = Trace(queue, args, dry=dry)
+    with _TraceScope(trace):
+        sym = []
+        for i, a in enumerate(args):
+            if isinstance(a, DeviceArray):
+                slot = trace.add_arg_slot(i, a)
+                sym.append(trace.leaf(slot))
+            elif isinstance(a, (bool, int, float, np.generic)):
+                dt = scalar_dtype(a)
+                sym.append(LazyArray(trace, Node("arg", dt, (), value=i), concrete=dt.type(a)))
+            else:
+                sym.append(a)
+        res = func(*sym)
+        spec = _result_spec(trace, res)
+        trace.flush()
+    result = _build_result(spec, trace.arrays)
+    plan = None if trace.value_dependent else Plan(trace, spec)
+    if dry:
+        return trace, plan
+    return result, plan
+
+
+def _result_spec(trace, res):
+    if res is None:
+        return None
+    if isinstance(res, LazyArray):
+        if res.shape == () and res.concrete is not None and res.node.kind != "leaf":
+            trace.value_dependent = True  # scalar computed on the host
+            return ("value", res.concrete)
+        return ("slot", trace.materialize(res))
+    if isinstance(res, tuple):
+        return ("tuple", tuple(_result_spec(trace, r) for r in res))
+    return ("value", res)
