@@ -1,0 +1,873 @@
+"""Typed Numba IR -> CUDA C, for `@kernel` bodies and scalar device functions.
+
+The reference types kernel bodies with Numba's own type inference and then
+lowers the typed IR through MLIR to SPIR-V (numba_mlir/mlir/inner_compiler.py:21-59,
+numba_mlir/mlir_compiler/lib/Lowering.cpp:311-1290).  Here the same typed IR
+(bytecode -> Numba IR -> SSA -> nopython type inference, Numba's stock passes)
+is translated to CUDA C: one labelled C block per IR block, every Numba
+variable a C local of its inferred type, every operation cast to the types its
+Numba signature names, so the arithmetic is the arithmetic Numba's CPU target
+performs.  The source is compiled by NVRTC inside gpuxModuleLoad.
+"""
+
+import math
+import operator
+import re
+
+import numpy as np
+
+from . import lazy
+
+
+class UnsupportedError(TypeError):
+    pass
+
+
+# ------------------------------------------------------------- typed IR -----
+_capture_pipeline = None
+
+
+def _get_pipeline():
+    global _capture_pipeline
+    if _capture_pipeline is not None:
+        return _capture_pipeline
+    from numba.core import ir
+    from numba.core.compiler import CompilerBase, DefaultPassBuilder
+    from numba.core.compiler_machinery import FunctionPass, register_pass
+    from numba.core.typed_passes import NopythonTypeInference, PreLowerStripPhis
+    from numba.core.untyped_passes import IRProcessing
+
+    from . import kernel_impl
+
+    @register_pass(mutates_CFG=False, analysis_only=False)
+    class ResolveKernelApiAttrs(FunctionPass):
+        """`atomic.add`, `local.array`, `group.reduce_add` ... written inline:
+        getattr on the API namespace objects becomes the global function, so
+        the plain `infer_global` typing applies (the reference leaves this form
+        unsupported, mlir/tests/test_gpu.py:848-855)."""
+
+        _name = "nmb_resolve_kernel_api_attrs"
+
+        def __init__(self):
+            FunctionPass.__init__(self)
+
+        def run_pass(self, state):
+            func_ir = state.func_ir
+            defs = {}
+            for blk in func_ir.blocks.values():
+                for inst in blk.body:
+                    if isinstance(inst, ir.Assign) and isinstance(inst.value, (ir.Global, ir.FreeVar)):
+                        defs[inst.target.name] = inst.value.value
+            changed = False
+            for blk in func_ir.blocks.values():
+                for inst in blk.body:
+                    if (isinstance(inst, ir.Assign) and isinstance(inst.value, ir.Expr)
+                            and inst.value.op == "getattr" and inst.value.value.name in defs):
+                        owner = defs[inst.value.value.name]
+                        fn = kernel_impl.API_ATTRS.get((owner, inst.value.attr))
+                        if fn is not None:
+                            inst.value = ir.Global(fn.__name__, fn, inst.loc)
+                            changed = True
+            return changed
+
+    @register_pass(mutates_CFG=False, analysis_only=True)
+    class CaptureTypedIR(FunctionPass):
+        _name = "nmb_capture_typed_ir"
+
+        def __init__(self):
+            FunctionPass.__init__(self)
+
+        def run_pass(self, state):
+            state.cr = TypedIR(state.func_ir, state.typemap, state.calltypes, state.return_type,
+                               state.args)
+            return False
+
+    class CapturePipeline(CompilerBase):
+        def define_pipelines(self):
+            pm = DefaultPassBuilder.define_untyped_pipeline(self.state, "nmb_untyped")
+            pm.add_pass_after(ResolveKernelApiAttrs, IRProcessing)
+            pm.add_pass(NopythonTypeInference, "nopython frontend")
+            pm.add_pass(PreLowerStripPhis, "remove phis nodes")
+            pm.add_pass(CaptureTypedIR, "capture typed IR")
+            pm.finalize()
+            return [pm]
+
+    _capture_pipeline = CapturePipeline
+    return CapturePipeline
+
+
+class TypedIR:
+    def __init__(self, func_ir, typemap, calltypes, return_type, args):
+        self.func_ir = func_ir
+        self.typemap = typemap
+        self.calltypes = calltypes
+        self.return_type = return_type
+        self.args = args
+
+
+def typed_ir(py_func, argtypes):
+    """Runs Numba's front-end and type inference on `py_func`."""
+    from numba.core import compiler
+    from numba.core.registry import cpu_target
+
+    from . import kernel_impl  # noqa: F401  (registers the API typing)
+
+    flags = compiler.Flags()
+    flags.nrt = True
+    return compiler.compile_extra(
+        cpu_target.typing_context, cpu_target.target_context, py_func, tuple(argtypes), None,
+        flags, {}, pipeline_class=_get_pipeline())
+
+
+# ----------------------------------------------------------- C helpers ------
+def _nb_types():
+    from numba.core import types
+
+    return types
+
+
+def c_scalar_type(t):
+    types = _nb_types()
+    t = types.unliteral(t)
+    if isinstance(t, types.Boolean):
+        return "bool"
+    if isinstance(t, types.Integer):
+        return ("int" if t.signed else "uint") + str(t.bitwidth) + "_t"
+    if isinstance(t, types.Float):
+        return {32: "float", 64: "double"}[t.bitwidth]
+    raise UnsupportedError(f"type {t} has no device representation")
+
+
+def _is_scalar(t):
+    types = _nb_types()
+    t = types.unliteral(t)
+    return isinstance(t, (types.Boolean, types.Integer, types.Float))
+
+
+def _const_literal(value, t):
+    types = _nb_types()
+    t = types.unliteral(t)
+    if isinstance(t, types.Boolean):
+        return "true" if value else "false"
+    if isinstance(t, types.Integer):
+        v = int(value)
+        if v == -(2**63):
+            return "(int64_t)0x8000000000000000ull"
+        suffix = "ll" if t.signed else "ull"
+        return f"({c_scalar_type(t)}){v}{suffix}"
+    if isinstance(t, types.Float):
+        return lazy.literal(value, np.float32 if t.bitwidth == 32 else np.float64)
+    raise UnsupportedError(f"constant of type {t}")
+
+
+class ArrayRep:
+    """C variables describing one array value: data pointer, shape, element
+    strides."""
+
+    def __init__(self, name, nbtype):
+        self.name = name
+        self.dtype = nbtype.dtype
+        self.ndim = nbtype.ndim
+        self.ctype = c_scalar_type(nbtype.dtype)
+        self.ptr = f"{name}_p"
+        self.shape = [f"{name}_s{d}" for d in range(self.ndim)]
+        self.strides = [f"{name}_t{d}" for d in range(self.ndim)]
+
+    def decls(self):
+        out = [f"{self.ctype}* {self.ptr};"]
+        if self.ndim:
+            out.append("int64_t " + ", ".join(self.shape + self.strides) + ";")
+        return out
+
+
+_MATH_FUNCS = {
+    # name: (float32 form, float64 form)
+    "sqrt": ("nmb::f_sqrt({0})", "nmb::f_sqrt({0})"), "exp": ("nmb::f_exp({0})", "nmb::f_exp({0})"),
+    "log": ("nmb::f_log({0})", "nmb::f_log({0})"), "erf": ("nmb::f_erf({0})", "nmb::f_erf({0})"),
+    "sin": ("sinf({0})", "sin({0})"), "cos": ("cosf({0})", "cos({0})"),
+    "tan": ("tanf({0})", "tan({0})"), "tanh": ("tanhf({0})", "tanh({0})"),
+    "floor": ("floorf({0})", "floor({0})"), "ceil": ("ceilf({0})", "ceil({0})"),
+    "fabs": ("fabsf({0})", "fabs({0})"), "acos": ("acosf({0})", "acos({0})"),
+    "asin": ("asinf({0})", "asin({0})"), "atan": ("atanf({0})", "atan({0})"),
+    "atan2": ("atan2f({0}, {1})", "atan2({0}, {1})"), "pow": ("powf({0}, {1})", "pow({0}, {1})"),
+    "log2": ("log2f({0})", "log2({0})"), "log10": ("log10f({0})", "log10({0})"),
+    "erfc": ("erfcf({0})", "erfc({0})"), "expm1": ("expm1f({0})", "expm1({0})"),
+    "log1p": ("log1pf({0})", "log1p({0})"), "sinh": ("sinhf({0})", "sinh({0})"),
+    "cosh": ("coshf({0})", "cosh({0})"),
+}
+_NP_TO_MATH = {"arccos": "acos", "arcsin": "asin", "arctan": "atan", "arctan2": "atan2",
+               "absolute": "fabs", "power": "pow"}
+
+_BINOPS = {
+    operator.add: "+", operator.sub: "-", operator.mul: "*", operator.iadd: "+", operator.isub: "-",
+    operator.imul: "*", operator.lt: "<", operator.le: "<=", operator.gt: ">", operator.ge: ">=",
+    operator.eq: "==", operator.ne: "!=", operator.and_: "&", operator.or_: "|", operator.xor: "^",
+    operator.iand: "&", operator.ior: "|", operator.ixor: "^", operator.lshift: "<<",
+    operator.rshift: ">>", operator.ilshift: "<<", operator.irshift: ">>",
+}
+_DIVS = {operator.truediv: "true", operator.itruediv: "true", operator.floordiv: "floor",
+         operator.ifloordiv: "floor", operator.mod: "mod", operator.imod: "mod",
+         operator.pow: "pow", operator.ipow: "pow"}
+
+
+class Translator:
+    """Translates one typed function to a C statement list.
+
+    mode 'kernel': parameters are the kernel's own, `return` leaves the kernel.
+    mode 'device': a `__device__` function returning a scalar."""
+
+    def __init__(self, tir, mode, func_name):
+        from numba.core import ir, types
+
+        self.ir = ir
+        self.types = types
+        self.tir = tir
+        self.mode = mode
+        self.func_name = func_name
+        self.typemap = tir.typemap
+        self.calltypes = tir.calltypes
+        self.cnames = {}
+        self.decls = []           # C declarations at function top
+        self.declared = set()
+        self.shared_decls = []
+        self.consts = {}          # var name -> compile-time Python object
+        self.tuples = {}          # var name -> list of element reps (C exprs / nested)
+        self.arrays = {}          # var name -> ArrayRep
+        self.written_params = set()
+        self.alias = {}           # array var -> root (param) var
+        self.uses_barrier = False
+        self.counter = 0
+
+    # naming -------------------------------------------------------------------
+    def cname(self, name):
+        c = self.cnames.get(name)
+        if c is None:
+            base = re.sub(r"[^0-9a-zA-Z_]", "_", name).strip("_") or "v"
+            c = f"v{len(self.cnames)}_{base}"[:60]
+            self.cnames[name] = c
+        return c
+
+    def fresh(self, prefix):
+        self.counter += 1
+        return f"{prefix}{self.counter}"
+
+    def vtype(self, name):
+        return self.typemap[name]
+
+    # value representation -------------------------------------------------------
+    def declare(self, name):
+        """Declares the C storage of Numba variable `name` once."""
+        if name in self.declared:
+            return
+        self.declared.add(name)
+        types = self.types
+        t = types.unliteral(self.vtype(name))
+        c = self.cname(name)
+        if _is_scalar(t):
+            self.decls.append(f"{c_scalar_type(t)} {c};")
+        elif isinstance(t, types.Array):
+            rep = ArrayRep(c, t)
+            self.arrays[name] = rep
+            self.decls.extend(rep.decls())
+        elif isinstance(t, (types.UniTuple, types.Tuple, types.NamedUniTuple)):
+            elems = []
+            for k, et in enumerate(t.types):
+                if not _is_scalar(et):
+                    raise UnsupportedError(f"tuple element type {et}")
+                self.decls.append(f"{c_scalar_type(et)} {c}_e{k};")
+                elems.append(f"{c}_e{k}")
+            self.tuples[name] = elems
+        elif isinstance(t, (types.RangeType, types.RangeIteratorType)):
+            self.decls.append(f"int64_t {c}_a, {c}_b, {c}_c;")
+        elif isinstance(t, types.Pair):
+            if not _is_scalar(t.first_type):
+                raise UnsupportedError(f"iteration over {t.first_type}")
+            self.decls.append(f"{c_scalar_type(t.first_type)} {c}_v; bool {c}_ok;")
+        # everything else (functions, modules, dtypes, None) lives at compile time
+
+    def scalar(self, var, as_type=None):
+        """C expression of a scalar Numba variable, optionally cast."""
+        name = var.name
+        t = self.types.unliteral(self.vtype(name))
+        if name in self.consts and _is_scalar(t):
+            expr = _const_literal(self.consts[name], t)
+        else:
+            if not _is_scalar(t):
+                raise UnsupportedError(f"{name}: {t} used as a scalar")
+            self.declare(name)
+            expr = self.cname(name)
+        if as_type is not None:
+            at = self.types.unliteral(as_type)
+            if at != t:
+                return self.cast_expr(expr, t, at)
+        return expr
+
+    def cast_expr(self, expr, from_t, to_t):
+        types = self.types
+        to_t = types.unliteral(to_t)
+        if isinstance(to_t, types.Boolean):
+            return f"(({expr}) != 0)"
+        return f"(({c_scalar_type(to_t)})({expr}))"
+
+    def tuple_elems(self, var):
+        name = var.name
+        if name in self.tuples:
+            return self.tuples[name]
+        if name in self.consts and isinstance(self.consts[name], tuple):
+            t = self.types.unliteral(self.vtype(name))
+            return [_const_literal(v, et) for v, et in zip(self.consts[name], t.types)]
+        raise UnsupportedError(f"{name} is not a tuple of scalars")
+
+    def index_list(self, var):
+        """Index variable -> list of int64 C expressions."""
+        t = self.types.unliteral(self.vtype(var.name))
+        if _is_scalar(t):
+            return [self.scalar(var, self.types.int64)]
+        return [f"((int64_t)({e}))" for e in self.tuple_elems(var)]
+
+    def element_ref(self, arr_var, idx_exprs):
+        rep = self.arrays[arr_var.name] if arr_var.name in self.arrays else None
+        if rep is None:
+            self.declare(arr_var.name)
+            rep = self.arrays[arr_var.name]
+        if len(idx_exprs) != rep.ndim:
+            raise UnsupportedError("only full scalar indexing of arrays is supported in kernels")
+        off = " + ".join(f"({i}) * {s}" for i, s in zip(idx_exprs, rep.strides)) or "0"
+        return f"{rep.ptr}[{off}]"
+
+    def root_of(self, name):
+        while name in self.alias:
+            name = self.alias[name]
+        return name
+
+    # expressions ------------------------------------------------------------------
+    def assign(self, target, value, out):
+        ir, types = self.ir, self.types
+        tname = target.name
+        ttype = types.unliteral(self.vtype(tname))
+
+        if isinstance(value, ir.Arg):
+            self.bind_arg(tname, value.index, out)
+            return
+        if isinstance(value, (ir.Global, ir.FreeVar, ir.Const)):
+            v = value.value
+            if _is_scalar(ttype) and isinstance(v, (bool, int, float, np.generic)):
+                self.declare(tname)
+                out.append(f"{self.cname(tname)} = {_const_literal(v, ttype)};")
+                self.consts[tname] = v
+            else:
+                self.consts[tname] = v
+            return
+        if isinstance(value, ir.Var):
+            self.copy_var(tname, value.name, out)
+            return
+        if not isinstance(value, ir.Expr):
+            raise UnsupportedError(f"IR node {type(value).__name__}")
+
+        op = value.op
+        if op in ("binop", "inplace_binop"):
+            sig = self.calltypes[value]
+            self.declare(tname)
+            out.append(f"{self.cname(tname)} = {self.binop(value.fn, value.lhs, value.rhs, sig)};")
+        elif op == "unary":
+            sig = self.calltypes[value]
+            a = self.scalar(value.value, sig.args[0])
+            self.declare(tname)
+            if value.fn is operator.neg:
+                e = f"(-{a})"
+            elif value.fn is operator.pos:
+                e = a
+            elif value.fn is operator.not_:
+                e = f"(!({a}))"
+            elif value.fn is operator.invert:
+                e = f"(~{a})"
+            else:
+                raise UnsupportedError(f"unary {value.fn}")
+            out.append(f"{self.cname(tname)} = {self.cast_expr(e, sig.args[0], sig.return_type)};")
+        elif op == "cast":
+            src_t = types.unliteral(self.vtype(value.value.name))
+            if isinstance(ttype, types.NoneType) or isinstance(src_t, types.NoneType):
+                self.consts[tname] = None
+            elif _is_scalar(ttype):
+                self.declare(tname)
+                out.append(f"{self.cname(tname)} = {self.scalar(value.value, ttype)};")
+            else:
+                self.copy_var(tname, value.value.name, out)
+        elif op == "call":
+            self.call(target, value, out)
+        elif op in ("getitem", "static_getitem"):
+            self.getitem(target, value, out)
+        elif op == "getattr":
+            self.getattr(target, value, out)
+        elif op == "build_tuple":
+            self.declare(tname)
+            for dst, item, et in zip(self.tuples[tname], value.items, ttype.types):
+                out.append(f"{dst} = {self.scalar(item, et)};")
+        elif op == "exhaust_iter":
+            self.copy_var(tname, value.value.name, out)
+        elif op == "getiter":
+            src_t = types.unliteral(self.vtype(value.value.name))
+            if not isinstance(src_t, types.RangeType):
+                raise UnsupportedError(f"iteration over {src_t}")
+            self.declare(tname)
+            s, d = self.cname(value.value.name), self.cname(tname)
+            out.append(f"{d}_a = {s}_a; {d}_b = {s}_b; {d}_c = {s}_c;")
+        elif op == "iternext":
+            self.declare(tname)
+            it, d = self.cname(value.value.name), self.cname(tname)
+            out.append(f"{d}_ok = {it}_c > 0 ? ({it}_a < {it}_b) : ({it}_a > {it}_b); "
+                       f"{d}_v = {it}_a; if ({d}_ok) {it}_a += {it}_c;")
+        elif op == "pair_first":
+            self.declare(tname)
+            out.append(f"{self.cname(tname)} = {self.cast_expr(self.cname(value.value.name) + '_v', None, ttype)};")
+        elif op == "pair_second":
+            self.declare(tname)
+            out.append(f"{self.cname(tname)} = {self.cname(value.value.name)}_ok;")
+        else:
+            raise UnsupportedError(f"expression '{op}' is not supported in device code")
+
+    def copy_var(self, tname, sname, out):
+        types = self.types
+        ttype = types.unliteral(self.vtype(tname))
+        if sname in self.consts and not _is_scalar(ttype):
+            self.consts[tname] = self.consts[sname]
+            if not isinstance(ttype, (types.UniTuple, types.Tuple)):
+                return
+        if _is_scalar(ttype):
+            self.declare(tname)
+            src = self.ir.Var(None, sname, None)
+            out.append(f"{self.cname(tname)} = {self.scalar(src, ttype)};")
+        elif isinstance(ttype, types.Array):
+            self.declare(tname)
+            self.declare(sname)
+            d, s = self.arrays[tname], self.arrays[sname]
+            self.alias[tname] = sname
+            stm = [f"{d.ptr} = {s.ptr};"]
+            stm += [f"{a} = {b};" for a, b in zip(d.shape + d.strides, s.shape + s.strides)]
+            out.append(" ".join(stm))
+        elif isinstance(ttype, (types.UniTuple, types.Tuple, types.NamedUniTuple)):
+            self.declare(tname)
+            src = self.tuple_elems(self.ir.Var(None, sname, None))
+            for a, b, et in zip(self.tuples[tname], src, ttype.types):
+                out.append(f"{a} = ({c_scalar_type(et)})({b});")
+        elif isinstance(ttype, (types.RangeType, types.RangeIteratorType)):
+            self.declare(tname)
+            d, s = self.cname(tname), self.cname(sname)
+            out.append(f"{d}_a = {s}_a; {d}_b = {s}_b; {d}_c = {s}_c;")
+        elif isinstance(ttype, types.NoneType):
+            self.consts[tname] = None
+        elif sname in self.consts:
+            self.consts[tname] = self.consts[sname]
+        else:
+            raise UnsupportedError(f"cannot copy a value of type {ttype}")
+
+    def binop(self, fn, lhs, rhs, sig):
+        types = self.types
+        a = self.scalar(lhs, sig.args[0])
+        b = self.scalar(rhs, sig.args[1])
+        rt = types.unliteral(sig.return_type)
+        at = types.unliteral(sig.args[0])
+        if fn in _BINOPS:
+            return self.cast_expr(f"({a} {_BINOPS[fn]} {b})", None, rt)
+        kind = _DIVS.get(fn)
+        if kind == "true":
+            return f"nmb::f_div(({c_scalar_type(rt)})({a}), ({c_scalar_type(rt)})({b}))"
+        if kind == "floor":
+            if isinstance(at, types.Integer):
+                return f"nmb::py_floordiv({a}, {b})"
+            return ("floorf" if rt.bitwidth == 32 else "floor") + f"(nmb::f_div({a}, {b}))"
+        if kind == "mod":
+            return f"nmb::py_mod({a}, {b})"
+        if kind == "pow":
+            if isinstance(rt, types.Integer):
+                return f"nmb::i_pow(({c_scalar_type(rt)})({a}), ({c_scalar_type(rt)})({b}))"
+            f = "powf" if rt.bitwidth == 32 else "pow"
+            return f"{f}(({c_scalar_type(rt)})({a}), ({c_scalar_type(rt)})({b}))"
+        raise UnsupportedError(f"binary operator {fn}")
+
+    def getitem(self, target, value, out):
+        types = self.types
+        src = value.value
+        st = types.unliteral(self.vtype(src.name))
+        tname = target.name
+        ttype = types.unliteral(self.vtype(tname))
+        if isinstance(st, types.Array):
+            if value.op == "static_getitem" and value.index_var is None:
+                idx = value.index if isinstance(value.index, tuple) else (value.index,)
+                idx_exprs = [f"{int(i)}ll" for i in idx]
+            else:
+                idx_exprs = self.index_list(value.index_var if value.op == "static_getitem" else value.index)
+            self.declare(tname)
+            out.append(f"{self.cname(tname)} = {self.cast_expr(self.element_ref(src, idx_exprs), None, ttype)};")
+        elif isinstance(st, (types.UniTuple, types.Tuple, types.NamedUniTuple)):
+            if value.op != "static_getitem" or not isinstance(value.index, int):
+                raise UnsupportedError("tuples need constant indices in device code")
+            elems = self.tuple_elems(src)
+            self.declare(tname)
+            out.append(f"{self.cname(tname)} = {self.cast_expr(elems[value.index], None, ttype)};")
+        else:
+            raise UnsupportedError(f"indexing of {st}")
+
+    def getattr(self, target, value, out):
+        types = self.types
+        src = value.value
+        st = types.unliteral(self.vtype(src.name))
+        tname = target.name
+        if isinstance(st, types.Array):
+            self.declare(src.name)
+            rep = self.arrays[src.name]
+            if value.attr == "shape":
+                self.declare(tname)
+                for dst, s in zip(self.tuples[tname], rep.shape):
+                    out.append(f"{dst} = {s};")
+            elif value.attr == "size":
+                self.declare(tname)
+                out.append(f"{self.cname(tname)} = " + (" * ".join(rep.shape) or "1") + ";")
+            elif value.attr == "ndim":
+                self.consts[tname] = rep.ndim
+                self.declare(tname)
+                out.append(f"{self.cname(tname)} = {rep.ndim};")
+            elif value.attr == "dtype":
+                self.consts[tname] = st.dtype
+            else:
+                raise UnsupportedError(f"array attribute .{value.attr}")
+        elif src.name in self.consts:
+            self.consts[tname] = getattr(self.consts[src.name], value.attr)
+        else:
+            raise UnsupportedError(f"attribute .{value.attr} of {st}")
+
+    # calls -------------------------------------------------------------------------
+    def callee(self, func_var):
+        if func_var.name in self.consts:
+            return self.consts[func_var.name]
+        t = self.vtype(func_var.name)
+        key = getattr(t, "typing_key", None)
+        if key is None:
+            key = getattr(t, "key", None)
+            if isinstance(key, tuple):
+                key = key[0]
+        return key
+
+    def call(self, target, expr, out):
+        from . import kernel_impl as K
+
+        types = self.types
+        fn = self.callee(expr.func)
+        sig = self.calltypes[expr]
+        tname = target.name
+        rt = types.unliteral(sig.return_type)
+        args = list(expr.args)
+        c = None
+
+        def sargs():
+            return [self.scalar(a, t) for a, t in zip(args, sig.args)]
+
+        if fn is range or (hasattr(fn, "__name__") and fn.__name__ == "prange"):
+            self.declare(tname)
+            d = self.cname(tname)
+            vals = [self.scalar(a, types.int64) for a in args]
+            if len(vals) == 1:
+                vals = ["0", vals[0], "1"]
+            elif len(vals) == 2:
+                vals = vals + ["1"]
+            out.append(f"{d}_a = {vals[0]}; {d}_b = {vals[1]}; {d}_c = {vals[2]};")
+            return
+        if fn in K.ID_FUNCS:
+            c = f"nmb::k_{fn.__name__}({self.scalar(args[0], types.int64)}, nmb_gs)"
+        elif fn in (K.atomic_add, K.atomic_sub):
+            arr, idx, val = args
+            self.declare(arr.name)
+            self.written_params.add(self.root_of(arr.name))
+            rep = self.arrays[arr.name]
+            ref = self.element_ref(arr, self.index_list(idx))
+            v = self.scalar(val, rep.dtype)
+            if fn is K.atomic_sub:
+                v = f"(-({v}))"
+            c = f"nmb::atomic_add(&{ref}, ({rep.ctype})({v}))"
+        elif fn is K.barrier:
+            self.uses_barrier = True
+            out.append("__syncthreads();")
+            self.consts[tname] = None
+            return
+        elif fn is K.mem_fence:
+            flags = self.consts.get(args[0].name, K.GLOBAL_MEM_FENCE) if args else K.GLOBAL_MEM_FENCE
+            out.append("__threadfence_block();" if flags == K.LOCAL_MEM_FENCE else "__threadfence();")
+            self.consts[tname] = None
+            return
+        elif fn in (K.local_array, K.private_array):
+            self.make_array(target, fn is K.local_array, args, out)
+            return
+        elif fn in K.GROUP_REDUCE:
+            self.uses_barrier = True
+            ct = c_scalar_type(rt)
+            scratch = self.fresh("nmb_red")
+            self.shared_decls.append(f"__shared__ {ct} {scratch}[32];")
+            opname, neutral = K.GROUP_REDUCE[fn]
+            c = (f"nmb::block_reduce(({ct})({self.scalar(args[0], rt)}), nmb::{opname}(), "
+                 f"nmb::neutral_{neutral}<{ct}>(), {scratch})")
+        elif fn in (math.sqrt, math.exp, math.log, math.erf, math.sin, math.cos, math.tan, math.tanh,
+                    math.floor, math.ceil, math.fabs, math.acos, math.asin, math.atan, math.atan2,
+                    math.pow, math.log2, math.log10, math.erfc, math.expm1, math.log1p, math.sinh,
+                    math.cosh) or isinstance(fn, np.ufunc):
+            name = fn.__name__
+            name = _NP_TO_MATH.get(name, name)
+            if name in ("floor", "ceil") and isinstance(rt, types.Integer):
+                a = self.scalar(args[0], types.float64)
+                c = f"(({c_scalar_type(rt)}){name}({a}))"
+            elif name in _MATH_FUNCS and isinstance(rt, types.Float):
+                forms = _MATH_FUNCS[name]
+                ops = [self.scalar(a, rt) for a in args]
+                c = forms[0 if rt.bitwidth == 32 else 1].format(*ops)
+            elif isinstance(fn, np.ufunc) and name in lazy.UFUNCS:
+                loop_t = sig.args[0]
+                ops = [self.scalar(a, loop_t) for a in args]
+                c = lazy.UFUNCS[name][1](np.dtype(str(types.unliteral(loop_t))), *ops)
+            else:
+                raise UnsupportedError(f"{name} is not supported in device code")
+        elif fn is abs:
+            a = self.scalar(args[0], rt)
+            c = f"nmb::i_abs({a})" if isinstance(rt, types.Integer) else (
+                f"fabsf({a})" if rt.bitwidth == 32 else f"fabs({a})")
+        elif fn in (min, max):
+            ops = [self.scalar(a, rt) for a in args]
+            cmp = "<" if fn is min else ">"
+            c = ops[0]
+            for o in ops[1:]:
+                # Python's min/max: keep the earlier operand on ties
+                c = f"(({o}) {cmp} ({c}) ? ({o}) : ({c}))"
+        elif fn in (int, float, bool) or isinstance(self.vtype(expr.func.name), types.NumberClass) \
+                or (isinstance(fn, type) and issubclass(fn, np.generic)):
+            src_t = types.unliteral(self.vtype(args[0].name))
+            c = self.cast_expr(self.scalar(args[0]), src_t, rt)
+        elif fn is len:
+            self.declare(args[0].name)
+            c = self.arrays[args[0].name].shape[0]
+        else:
+            raise UnsupportedError(f"call to {fn!r} is not supported in device code")
+
+        if isinstance(rt, types.NoneType):
+            out.append(f"{c};")
+            self.consts[tname] = None
+        else:
+            self.declare(tname)
+            out.append(f"{self.cname(tname)} = {self.cast_expr(c, None, rt)};")
+
+    def make_array(self, target, shared, args, out):
+        """local.array / private.array with a static shape (one buffer per call
+        site: numba_mlir/mlir/kernel_impl.py:366-437)."""
+        types = self.types
+        tname = target.name
+        ttype = types.unliteral(self.vtype(tname))
+        shape = self.static_value(args[0])
+        if isinstance(shape, (int, np.integer)):
+            shape = (int(shape),)
+        shape = tuple(int(s) for s in shape)
+        n = int(np.prod(shape)) if shape else 1
+        self.declare(tname)
+        rep = self.arrays[tname]
+        buf = self.fresh("nmb_local" if shared else "nmb_private")
+        if shared:
+            self.shared_decls.append(f"__shared__ __align__(16) {rep.ctype} {buf}[{max(n, 1)}];")
+        else:
+            # zero-filled like the reference's simulator (kernel_sim_impl.py:166-168)
+            self.decls.append(f"{rep.ctype} {buf}[{max(n, 1)}] = {{}};")
+        stm = [f"{rep.ptr} = {buf};"]
+        acc = 1
+        strides = []
+        for s in reversed(shape):
+            strides.append(acc)
+            acc *= s
+        strides.reverse()
+        for d, (s, st) in enumerate(zip(shape, strides)):
+            stm.append(f"{rep.shape[d]} = {s}; {rep.strides[d]} = {st};")
+        out.append(" ".join(stm))
+
+    def static_value(self, var):
+        from numba.core import ir_utils
+
+        if var.name in self.consts:
+            return self.consts[var.name]
+        t = self.vtype(var.name)
+        if hasattr(t, "literal_value"):
+            return t.literal_value
+        try:
+            return ir_utils.find_const(self.tir.func_ir, var)
+        except Exception:
+            pass
+        if isinstance(t, (self.types.Tuple, self.types.UniTuple)) and all(
+                hasattr(e, "literal_value") for e in t.types):
+            return tuple(e.literal_value for e in t.types)
+        defn = ir_utils.guard(ir_utils.get_definition, self.tir.func_ir, var)
+        if isinstance(defn, self.ir.Expr) and defn.op == "build_tuple":
+            return tuple(self.static_value(i) for i in defn.items)
+        raise UnsupportedError(f"{var.name} must be a compile-time constant")
+
+    # arguments ------------------------------------------------------------------------
+    def bind_arg(self, tname, index, out):
+        types = self.types
+        t = types.unliteral(self.vtype(tname))
+        p = self.param_names[index]
+        self.declare(tname)
+        if _is_scalar(t):
+            out.append(f"{self.cname(tname)} = {p};")
+        elif isinstance(t, types.Array):
+            rep = self.arrays[tname]
+            self.alias[tname] = f"<param{index}>"
+            stm = [f"{rep.ptr} = ({rep.ctype}*){p}_p;"]
+            for d in range(rep.ndim):
+                stm.append(f"{rep.shape[d]} = {p}_s{d};")
+            if t.layout == "C":
+                for d in range(rep.ndim - 1, -1, -1):
+                    stm.append(f"{rep.strides[d]} = " + ("1;" if d == rep.ndim - 1 else
+                                                         f"{rep.strides[d + 1]} * {p}_s{d + 1};"))
+            else:
+                for d in range(rep.ndim):
+                    stm.append(f"{rep.strides[d]} = {p}_t{d};")
+            out.append(" ".join(stm))
+        else:
+            raise UnsupportedError(f"argument of type {t}")
+
+    # statements -------------------------------------------------------------------------
+    def translate(self, param_names):
+        ir, types = self.ir, self.types
+        self.param_names = param_names
+        blocks = self.tir.func_ir.blocks
+        order = sorted(blocks)
+        body = []
+        for label in order:
+            out = [f"L{label}: ;"]
+            for inst in blocks[label].body:
+                if isinstance(inst, ir.Assign):
+                    if isinstance(inst.value, ir.Const) and inst.value.value is ir.UNDEFINED:
+                        continue
+                    self.assign(inst.target, inst.value, out)
+                elif isinstance(inst, (ir.SetItem, ir.StaticSetItem)):
+                    arr = inst.target
+                    self.declare(arr.name)
+                    self.written_params.add(self.root_of(arr.name))
+                    rep = self.arrays[arr.name]
+                    if isinstance(inst, ir.StaticSetItem) and inst.index_var is None:
+                        idx = inst.index if isinstance(inst.index, tuple) else (inst.index,)
+                        idx_exprs = [f"{int(i)}ll" for i in idx]
+                    else:
+                        idx_exprs = self.index_list(inst.index_var if isinstance(inst, ir.StaticSetItem)
+                                                    else inst.index)
+                    ref = self.element_ref(arr, idx_exprs)
+                    out.append(f"{ref} = {self.scalar(inst.value, rep.dtype)};")
+                elif isinstance(inst, ir.Del):
+                    continue
+                elif isinstance(inst, ir.Jump):
+                    out.append(f"goto L{inst.target};")
+                elif isinstance(inst, ir.Branch):
+                    out.append(f"if ({self.scalar(inst.cond, types.boolean)}) goto L{inst.truebr}; "
+                               f"else goto L{inst.falsebr};")
+                elif isinstance(inst, ir.Return):
+                    if self.mode == "kernel":
+                        out.append("return;")
+                    else:
+                        out.append(f"return {self.scalar(inst.value, self.tir.return_type)};")
+                elif isinstance(inst, (ir.Raise, ir.StaticRaise)):
+                    out.append("return;" if self.mode == "kernel" else "return 0;")
+                else:
+                    raise UnsupportedError(f"statement {type(inst).__name__} in device code")
+            body.append("\n    ".join(out))
+        return body
+
+
+# -------------------------------------------------------------- drivers -----
+def _argtype_of(a):
+    from numba import typeof
+    from numba.core import types
+
+    from .device_array import DeviceArray
+
+    if isinstance(a, DeviceArray):
+        from numba.np.numpy_support import from_dtype
+
+        layout = "C" if a.is_c_contiguous else "A"
+        return types.Array(from_dtype(a.dtype), a.ndim, layout)
+    if isinstance(a, bool):
+        return types.boolean
+    if isinstance(a, int):
+        return types.int64
+    if isinstance(a, float):
+        return types.float64
+    return typeof(a)
+
+
+_device_func_counter = [0]
+
+
+def compile_device_function(py_func, dtypes):
+    """Scalar Python function -> lazy.DeviceFunc (a CUDA __device__ function)."""
+    from numba.np.numpy_support import as_dtype, from_dtype
+
+    argtypes = [from_dtype(np.dtype(d)) for d in dtypes]
+    tir = typed_ir(py_func, argtypes)
+    _device_func_counter[0] += 1
+    name = f"nmb_dev_{re.sub(r'[^0-9a-zA-Z_]', '_', py_func.__name__)}_{_device_func_counter[0]}"
+    tr = Translator(tir, "device", name)
+    params = [f"a{i}" for i in range(len(argtypes))]
+    body = tr.translate(params)
+    if tr.shared_decls:
+        raise UnsupportedError("local memory is not available in scalar device functions")
+    rt = c_scalar_type(tir.return_type)
+    sig = ", ".join(f"{c_scalar_type(t)} a{i}" for i, t in enumerate(argtypes))
+    src = (f"__device__ __forceinline__ {rt} {name}({sig}) {{\n    " + "\n    ".join(tr.decls)
+           + "\n    " + "\n    ".join(body) + "\n}\n")
+    return lazy.DeviceFunc(name, src, dtypes, as_dtype(tir.return_type))
+
+
+class CompiledKernel:
+    def __init__(self, source, name, param_layout, uses_barrier):
+        self.source = source
+        self.name = name
+        self.param_layout = param_layout  # per Python argument: ("array", ndim, layout) | ("scalar", dtype)
+        self.uses_barrier = uses_barrier
+
+
+def compile_kernel(py_func, args, ndim, fastmath=False):
+    """@kernel body + concrete arguments -> CompiledKernel (tagged CUDA source).
+
+    The grid mapping is the reference's: get_global_id(d) is
+    blockIdx.d*blockDim.d + threadIdx.d (LowerToGpu.cpp:1113-1137), the grid is
+    ceil(global/local) groups and work-items past the global size are masked
+    off (mlir/lib/Conversion/GpuToGpuRuntime.cpp:1460-1546)."""
+    argtypes = [_argtype_of(a) for a in args]
+    tir = typed_ir(py_func, argtypes)
+    from numba.core import types
+
+    tr = Translator(tir, "kernel", "nmb_kernel")
+    pnames = [f"p{i}" for i in range(len(argtypes))]
+    body = tr.translate(pnames)
+    written = {int(r[6:-1]) for r in tr.written_params if r.startswith("<param")}
+    kparams, layout = [], []
+    for i, t in enumerate(argtypes):
+        t = types.unliteral(t)
+        if isinstance(t, types.Array):
+            ct = c_scalar_type(t.dtype)
+            qual = f"{ct}* __restrict__" if i in written else f"const {ct}* __restrict__"
+            kparams.append(f"{qual} p{i}_p")
+            kparams += [f"int64_t p{i}_s{d}" for d in range(t.ndim)]
+            if t.layout != "C":
+                kparams += [f"int64_t p{i}_t{d}" for d in range(t.ndim)]
+            layout.append(("array", t.ndim, t.layout))
+        else:
+            kparams.append(f"{c_scalar_type(t)} p{i}")
+            layout.append(("scalar", np.dtype(str(t))))
+    kparams += ["int64_t nmb_g0", "int64_t nmb_g1", "int64_t nmb_g2"]
+    opts = "" if fastmath else " --fmad=false"
+    src = f"""//NMB200:CUDA-SOURCE
+//NMB200:OPTIONS{opts}
+#include "nmb_device.cuh"
+extern "C" __global__ void nmb_kernel({', '.join(kparams)}) {{
+    const int64_t nmb_gs[3] = {{nmb_g0, nmb_g1, nmb_g2}};
+    // work-items past the global size are masked off
+    if (nmb::k_get_global_id(0, nmb_gs) >= nmb_g0 || nmb::k_get_global_id(1, nmb_gs) >= nmb_g1 ||
+        nmb::k_get_global_id(2, nmb_gs) >= nmb_g2) return;
+    {' '.join(tr.shared_decls)}
+    {chr(10).join('    ' + d for d in tr.decls)}
+    {(chr(10) + '    ').join(body)}
+}}
+"""
+    return CompiledKernel(src, "nmb_kernel", layout, tr.uses_barrier)

@@ -213,6 +213,80 @@ __device__ __forceinline__ double f_erf(double x) { return erf(x); }
 __device__ __forceinline__ double f_div(double a, double b) { return __ddiv_rn(a, b); }
 
 
+// ------------------------------------------------------------ @kernel API ---
+// get_global_id(d) = blockIdx.d * blockDim.d + threadIdx.d, the mapping of
+// numba_mlir/mlir_compiler/lib/pipelines/LowerToGpu.cpp:1113-1137; dimension 0
+// is x, the fastest-varying one.
+__device__ __forceinline__ int64_t k_get_local_id(int64_t d, const int64_t *) {
+  return d == 0 ? threadIdx.x : d == 1 ? threadIdx.y : threadIdx.z;
+}
+__device__ __forceinline__ int64_t k_get_group_id(int64_t d, const int64_t *) {
+  return d == 0 ? blockIdx.x : d == 1 ? blockIdx.y : blockIdx.z;
+}
+__device__ __forceinline__ int64_t k_get_local_size(int64_t d, const int64_t *) {
+  return d == 0 ? blockDim.x : d == 1 ? blockDim.y : blockDim.z;
+}
+__device__ __forceinline__ int64_t k_get_global_id(int64_t d, const int64_t *gs) {
+  return k_get_group_id(d, gs) * k_get_local_size(d, gs) + k_get_local_id(d, gs);
+}
+__device__ __forceinline__ int64_t k_get_global_size(int64_t d, const int64_t *gs) { return gs[d]; }
+
+// atomic.add returns the updated value, like the reference's simulator
+// (numba_mlir/mlir/kernel_sim.py:24-35).
+__device__ __forceinline__ int32_t atomic_add(int32_t *p, int32_t v) { return atomicAdd(p, v) + v; }
+__device__ __forceinline__ uint32_t atomic_add(uint32_t *p, uint32_t v) { return atomicAdd(p, v) + v; }
+__device__ __forceinline__ int64_t atomic_add(int64_t *p, int64_t v) {
+  return (int64_t)atomicAdd(reinterpret_cast<unsigned long long *>(p), (unsigned long long)v) + v;
+}
+__device__ __forceinline__ uint64_t atomic_add(uint64_t *p, uint64_t v) {
+  return (uint64_t)atomicAdd(reinterpret_cast<unsigned long long *>(p), (unsigned long long)v) + v;
+}
+__device__ __forceinline__ float atomic_add(float *p, float v) { return atomicAdd(p, v) + v; }
+__device__ __forceinline__ double atomic_add(double *p, double v) { return atomicAdd(p, v) + v; }
+
+template <typename T> __device__ __forceinline__ T neutral_add() { return T(0); }
+template <typename T> __device__ __forceinline__ T neutral_mul() { return T(1); }
+template <typename T> __device__ __forceinline__ T neutral_min();
+template <typename T> __device__ __forceinline__ T neutral_max();
+template <> __device__ __forceinline__ float neutral_min<float>() { return __int_as_float(0x7f800000); }
+template <> __device__ __forceinline__ float neutral_max<float>() { return __int_as_float(0xff800000); }
+template <> __device__ __forceinline__ double neutral_min<double>() { return __longlong_as_double(0x7ff0000000000000ll); }
+template <> __device__ __forceinline__ double neutral_max<double>() { return __longlong_as_double(0xfff0000000000000ll); }
+template <> __device__ __forceinline__ int32_t neutral_min<int32_t>() { return 0x7fffffff; }
+template <> __device__ __forceinline__ int32_t neutral_max<int32_t>() { return (int32_t)0x80000000; }
+template <> __device__ __forceinline__ int64_t neutral_min<int64_t>() { return 0x7fffffffffffffffll; }
+template <> __device__ __forceinline__ int64_t neutral_max<int64_t>() { return (int64_t)0x8000000000000000ll; }
+
+// Python's // and % on integers round toward minus infinity.
+template <typename T> __device__ __forceinline__ T py_floordiv(T a, T b) {
+  if (b == 0)
+    return 0;
+  T q = a / b;
+  if ((a % b != 0) && ((a < 0) != (b < 0)))
+    --q;
+  return q;
+}
+template <typename T> __device__ __forceinline__ T py_mod(T a, T b) {
+  if (b == 0)
+    return 0;
+  T r = a % b;
+  if (r != 0 && ((r < 0) != (b < 0)))
+    r += b;
+  return r;
+}
+__device__ __forceinline__ float py_mod(float a, float b) {
+  float r = fmodf(a, b);
+  if (r != 0.f && ((r < 0.f) != (b < 0.f)))
+    r += b;
+  return r;
+}
+__device__ __forceinline__ double py_mod(double a, double b) {
+  double r = fmod(a, b);
+  if (r != 0. && ((r < 0.) != (b < 0.)))
+    r += b;
+  return r;
+}
+
 // NumPy's maximum/minimum propagate NaNs.
 template <typename T> __device__ __forceinline__ T np_max(T a, T b) { return (a > b || a != a) ? a : b; }
 template <typename T> __device__ __forceinline__ T np_min(T a, T b) { return (a < b || a != a) ? a : b; }

@@ -15,21 +15,24 @@ namespace red {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kWsThreads = (kConsumerWarps + 1) * 32;
-// Row kernel: one stage per consumer warp.  A stage must always be consumed by
-// the same warp: a warp that met a stage for the first time in a later phase
-// could not tell that phase from the one before it (mbarrier waits only see
-// the phase parity).
-constexpr int kRowStages = kConsumerWarps;
-constexpr int kColStages = 6;  // two 99 KB CTAs per SM
-constexpr int kRowSmemBytes = kRowStages * kTileBytes + 2 * kRowStages * 8 + 2 * kConsumerWarps * 16;
+// Row kernel: every consumer warp owns a private ring of kRowDepth stages of
+// 8 KB.  A stage must always be consumed by the same warp: a warp that met a
+// stage for the first time in a later phase could not tell that phase from the
+// one before it (mbarrier waits only see the phase parity).
+constexpr int kRowDepth = 3;
+constexpr int kRowTileBytes = 8192;
+constexpr int kRowStages = kConsumerWarps * kRowDepth; // 192 KB in flight per SM
+constexpr int kColStages = 6;                          // two 99 KB CTAs per SM
+constexpr int kRowSmemBytes = kRowStages * kRowTileBytes + 2 * kRowStages * 8;
 constexpr int kColSmemBytes = kColStages * kTileBytes + 2 * kColStages * 8;
+constexpr int kColGroup = 8; // row blocks merged per first-level ticket
 
-template <int STAGES> struct Ring {
+template <int STAGES, int STAGE_BYTES> struct Ring {
   unsigned char *tiles;
   uint64_t *full;
   uint64_t *empty;
   __device__ __forceinline__ explicit Ring(unsigned char *raw)
-      : tiles(raw), full(reinterpret_cast<uint64_t *>(raw + STAGES * kTileBytes)),
+      : tiles(raw), full(reinterpret_cast<uint64_t *>(raw + STAGES * STAGE_BYTES)),
         empty(full + STAGES) {}
   __device__ __forceinline__ void init(uint32_t consumers_per_stage) {
     if (threadIdx.x == 0) {
@@ -84,11 +87,10 @@ __device__ __forceinline__ typename R::Acc warp_reduce_span(const typename R::In
 // out[r] = reduce(a[r, :]) for a C-contiguous (rows, cols) matrix whose base is
 // 16-byte aligned and whose row size is a multiple of 16 bytes.
 // Grid: G <= rows CTAs of kWsThreads; CTA b owns rows [rows*b/G, rows*(b+1)/G).
-// Rows of at most 16 KB: a tile is `rt` whole rows, tile i lives in stage i % 8
-// and is reduced by warp i % 8 alone (no cross-warp traffic).  Longer rows: a
-// tile is one 16 KB chunk of a row, every warp reduces an eighth of every tile
-// and the eight partials of a row meet in shared memory behind one named
-// barrier per row.
+// Work is cut into groups: `rt` whole rows in one 8 KB tile when a row fits a
+// tile, else one row as `tpr` consecutive tiles.  Group g belongs to consumer
+// warp g % 8, which reduces it alone (no cross-warp traffic) out of its private
+// stages; the producer warp feeds the eight rings in global tile order.
 template <typename R>
 __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict__ a,
                                                typename R::Out *__restrict__ out, int64_t rows,
@@ -96,99 +98,81 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
                                                unsigned char *smem_raw) {
   using T = typename R::In;
   using Acc = typename R::Acc;
-  constexpr int64_t TILE = kTileBytes / sizeof(T);
-  constexpr int S = kRowStages;
-  Ring<S> ring(smem_raw);
+  constexpr int64_t TILE = kRowTileBytes / sizeof(T);
+  constexpr int K = kRowDepth;
+  Ring<kRowStages, kRowTileBytes> ring(smem_raw);
   T *tiles = reinterpret_cast<T *>(ring.tiles);
-  Acc *parts = reinterpret_cast<Acc *>(smem_raw + S * kTileBytes + 2 * S * 8); // [2][8]
+  ring.init(1);
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t G = gridDim.x, b = blockIdx.x;
   const int64_t r_begin = rows * b / G, r_end = rows * (b + 1) / G;
   const int64_t nrows = r_end - r_begin;
-  const int64_t cpr = (cols + TILE - 1) / TILE;
-  const int64_t rt = cpr == 1 ? (TILE / cols > 0 ? TILE / cols : 1) : 1;
-  const int64_t ntiles = cpr == 1 ? (nrows + rt - 1) / rt : nrows * cpr;
-  ring.init(cpr == 1 ? 1 : kConsumerWarps);
+  const int64_t tpr = (cols + TILE - 1) / TILE;                           // tiles per row
+  const int64_t rt = tpr == 1 ? (TILE / cols > 0 ? TILE / cols : 1) : 1; // rows per tile
+  const int64_t ngroups = tpr == 1 ? (nrows + rt - 1) / rt : nrows;
   bool dead = false;
 
   if (warp == kConsumerWarps) {
     if (lane == 0) {
-      for (int64_t i = 0; i < ntiles; ++i) {
-        const int s = (int)(i % S);
-        const int64_t use = i / S;
-        if (use > 0)
-          stage_wait(&ring.empty[s], use - 1, dead, status);
-        const T *src;
-        uint32_t bytes;
-        if (cpr == 1) {
-          const int64_t r0 = r_begin + i * rt;
-          const int64_t nr = r_end - r0 < rt ? r_end - r0 : rt;
-          src = a + r0 * cols;
-          bytes = (uint32_t)(nr * cols * sizeof(T));
-        } else {
-          const int64_t r = r_begin + i / cpr, c0 = (i % cpr) * TILE;
-          const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
-          src = a + r * cols + c0;
-          bytes = (uint32_t)(ne * sizeof(T));
+      int64_t issued = 0;
+      for (int64_t g = 0; g < ngroups; ++g) {
+        const int w = (int)(g % kConsumerWarps);
+        for (int64_t ch = 0; ch < tpr; ++ch, ++issued) {
+          const int64_t j = (g / kConsumerWarps) * tpr + ch; // warp-local tile number
+          const int s = w * K + (int)(j % K);
+          if (j >= K)
+            stage_wait(&ring.empty[s], j / K - 1, dead, status);
+          const T *src;
+          uint32_t bytes;
+          if (tpr == 1) {
+            const int64_t r0 = r_begin + g * rt;
+            const int64_t nr = r_end - r0 < rt ? r_end - r0 : rt;
+            src = a + r0 * cols;
+            bytes = (uint32_t)(nr * cols * sizeof(T));
+          } else {
+            const int64_t c0 = ch * TILE;
+            const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
+            src = a + (r_begin + g) * cols + c0;
+            bytes = (uint32_t)(ne * sizeof(T));
+          }
+          mbar_expect_tx(&ring.full[s], bytes);
+          bulk_load(tiles + (int64_t)s * TILE, src, bytes, &ring.full[s]);
         }
-        mbar_expect_tx(&ring.full[s], bytes);
-        bulk_load(tiles + (int64_t)s * TILE, src, bytes, &ring.full[s]);
       }
-      if (dead)
-        ring.drain(ntiles);
+      if (dead) // bounded pause (about 2 ms) for whatever copy may still be in flight
+        for (int t = 0; t < 2000; ++t)
+          __nanosleep(1000);
     }
     return;
   }
 
-  if (cpr == 1) {
-    // warp == stage: tiles warp, warp + 8, ... in order
-    for (int64_t i = warp; i < ntiles; i += kConsumerWarps) {
-      const int s = warp;
-      stage_wait(&ring.full[s], i / S, dead, status);
+  for (int64_t g = warp; g < ngroups; g += kConsumerWarps) {
+    Acc racc = R::identity();
+    for (int64_t ch = 0; ch < tpr; ++ch) {
+      const int64_t j = (g / kConsumerWarps) * tpr + ch;
+      const int s = warp * K + (int)(j % K);
+      stage_wait(&ring.full[s], j / K, dead, status);
       const T *tile = tiles + (int64_t)s * TILE;
-      const int64_t r0 = r_begin + i * rt;
-      const int nr = (int)(r_end - r0 < rt ? r_end - r0 : rt);
-      for (int j = 0; j < nr; ++j) {
-        const Acc acc = warp_reduce_span<R>(tile + (int64_t)j * cols, cols, 0);
-        if (lane == 0)
-          out[r0 + j] = R::fin(acc);
+      if (tpr == 1) {
+        const int64_t r0 = r_begin + g * rt;
+        const int nr = (int)(r_end - r0 < rt ? r_end - r0 : rt);
+        for (int jr = 0; jr < nr; ++jr) {
+          const Acc acc = warp_reduce_span<R>(tile + (int64_t)jr * cols, cols, 0);
+          if (lane == 0)
+            out[r0 + jr] = R::fin(acc);
+        }
+      } else {
+        const int64_t c0 = ch * TILE;
+        const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
+        racc = R::merge(racc, warp_reduce_span<R>(tile, ne, c0));
       }
       __syncwarp();
       if (lane == 0)
         mbar_arrive(&ring.empty[s]);
     }
-  } else {
-    constexpr int VEC = 16 / sizeof(T);
-    constexpr int64_t PART = TILE / kConsumerWarps; // elements of a full tile per warp
-    for (int64_t lr = 0; lr < nrows; ++lr) {
-      Acc racc = R::identity();
-      for (int64_t ch = 0; ch < cpr; ++ch) {
-        const int64_t i = lr * cpr + ch;
-        const int s = (int)(i % S);
-        stage_wait(&ring.full[s], i / S, dead, status);
-        const int64_t c0 = ch * TILE;
-        const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
-        const int64_t p0 = warp * PART < ne ? warp * PART : ne;
-        const int64_t p1 = (warp + 1) * PART < ne ? (warp + 1) * PART : ne;
-        racc = R::merge(racc, warp_reduce_span<R>(tiles + (int64_t)s * TILE + p0, p1 - p0, c0 + p0));
-        __syncwarp();
-        if (lane == 0)
-          mbar_arrive(&ring.empty[s]);
-      }
-      Acc *slot = parts + (lr & 1) * kConsumerWarps;
-      if (lane == 0)
-        slot[warp] = racc;
-      // named barrier 1: the 256 consumer threads only
-      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-      if (warp == 0) {
-        Acc m = lane < kConsumerWarps ? slot[lane] : R::identity();
-        m = warp_merge<R>(m);
-        if (lane == 0)
-          out[r_begin + lr] = R::fin(m);
-      }
-    }
-    (void)VEC;
+    if (tpr > 1 && lane == 0)
+      out[r_begin + g] = R::fin(racc);
   }
 }
 
@@ -196,8 +180,9 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
 // out[c] = reduce(a[:, c]).  Grid (col_tiles, row_blocks) of kWsThreads: CTA
 // (x, y) reduces rows [rows*y/Gy, rows*(y+1)/Gy) of the 256*VEC columns that
 // start at x*256*VEC; each stage holds 4 row segments (one bulk copy each).
-// partials[y][c] and counters[x] live in scratch memory; counters start at
-// zero and are left at zero.
+// partials[y][c], then group_partials[ceil(Gy/8)][c], and the ticket counters
+// [x][1 + ceil(Gy/8)] live in scratch memory; counters start at zero and are
+// left at zero.
 template <typename R>
 __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict__ a,
                                                typename R::Out *__restrict__ out,
@@ -212,7 +197,7 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
   constexpr int RS = kTileBytes / (COLS * (int)sizeof(T));
   constexpr int64_t TILE = kTileBytes / sizeof(T);
   constexpr int S = kColStages;
-  Ring<S> ring(smem_raw);
+  Ring<S, kTileBytes> ring(smem_raw);
   T *tiles = reinterpret_cast<T *>(ring.tiles);
   ring.init(kConsumerWarps);
 
@@ -289,15 +274,53 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
         out[c0 + tid * VEC + l] = R::fin(acc[l]);
     return;
   }
+  // Two-level merge through scratch memory.  Level 1: the last CTA of each
+  // group of kColGroup row blocks merges the group's partials (independent
+  // loads, merged in row-block order) into group_partials; level 2: the last
+  // of those merges the groups.  counters = [x][1 + ngroups] tickets.
+  const int64_t ngroups = (Gy + kColGroup - 1) / kColGroup;
+  const int64_t grp = by / kColGroup;
+  const int64_t g_begin = grp * kColGroup;
+  const int64_t g_size = Gy - g_begin < kColGroup ? Gy - g_begin : kColGroup;
+  Acc *group_partials = partials + Gy * cols;
+  uint32_t *top = counters + (int64_t)blockIdx.x * (1 + ngroups);
+  uint32_t *mine = top + 1 + grp;
+  __shared__ bool last;
+
   if (active)
 #pragma unroll
     for (int l = 0; l < VEC; ++l)
       partials[by * cols + c0 + tid * VEC + l] = acc[l];
   __threadfence();
-  __shared__ bool last;
   __syncthreads();
   if (tid == 0)
-    last = atomicAdd(&counters[blockIdx.x], 1u) == (uint32_t)(Gy - 1);
+    last = atomicAdd(mine, 1u) == (uint32_t)(g_size - 1);
+  __syncthreads();
+  if (!last)
+    return;
+  __threadfence();
+  if (active) {
+#pragma unroll
+    for (int l = 0; l < VEC; ++l) {
+      Acc part[kColGroup];
+#pragma unroll
+      for (int y = 0; y < kColGroup; ++y)
+        if (y < g_size)
+          part[y] = load_cg(partials + (g_begin + y) * cols + c0 + tid * VEC + l);
+      Acc m = R::identity();
+#pragma unroll
+      for (int y = 0; y < kColGroup; ++y)
+        if (y < g_size)
+          m = R::merge(m, part[y]);
+      group_partials[grp * cols + c0 + tid * VEC + l] = m;
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    *mine = 0;
+    last = atomicAdd(top, 1u) == (uint32_t)(ngroups - 1);
+  }
   __syncthreads();
   if (!last)
     return;
@@ -306,13 +329,22 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
 #pragma unroll
     for (int l = 0; l < VEC; ++l) {
       Acc m = R::identity();
-      for (int64_t y = 0; y < Gy; ++y)
-        m = R::merge(m, load_cg(partials + y * cols + c0 + tid * VEC + l));
+      for (int64_t g0 = 0; g0 < ngroups; g0 += kColGroup) {
+        Acc part[kColGroup];
+#pragma unroll
+        for (int y = 0; y < kColGroup; ++y)
+          if (g0 + y < ngroups)
+            part[y] = load_cg(group_partials + (g0 + y) * cols + c0 + tid * VEC + l);
+#pragma unroll
+        for (int y = 0; y < kColGroup; ++y)
+          if (g0 + y < ngroups)
+            m = R::merge(m, part[y]);
+      }
       out[c0 + tid * VEC + l] = R::fin(m);
     }
   }
   if (tid == 0)
-    counters[blockIdx.x] = 0;
+    *top = 0;
 }
 
 } // namespace red

@@ -1,0 +1,153 @@
+"""`njit` / `jit` / `vectorize` / `njit_replace_parfors` for the CUDA offload path.
+
+Same names and call forms as numba_mlir/numba_mlir/decorators.py:25-107.  In the
+reference, offload is selected by argument type: a function compiled by `njit`
+goes to the GPU when its array arguments are device (USM) arrays
+(numba_mlir/mlir/dpctl_interop.py:210-234).  Here device arrays are
+`DeviceArray`s (anything exposing `__cuda_array_interface__` is accepted and
+wrapped).  There is no CPU path in this package: calling a decorated function
+without any device array raises instead of silently running on the host.
+"""
+
+import functools
+
+import numpy as np
+
+from . import lazy
+from . import runtime as _rt
+from .device_array import DeviceArray, as_device_array
+
+# Keyword options accepted for compatibility (numba_mlir/mlir/target.py:176-203):
+# parallel, fastmath, gpu_fp64_truncate, gpu_use_64bit_index,
+# enable_gpu_pipeline, mlir_force_inline, mlir_vectorize, cache, inline,
+# boundscheck, nogil, locals, nopython, forceobj.  B200 has native fp64, so
+# gpu_fp64_truncate has nothing to do.
+
+
+def _wrap_arg(a):
+    if isinstance(a, DeviceArray):
+        return a
+    if hasattr(a, "__cuda_array_interface__"):
+        return as_device_array(a)
+    return a
+
+
+def check_device_args(args):
+    """All device arrays of one call must live on one device
+    (check_usm_ndarray_args, numba_mlir/mlir/dpctl_interop.py:270-275)."""
+    devs = {a.queue.device for a in args if isinstance(a, DeviceArray)}
+    if len(devs) > 1:
+        raise ValueError(f"Device arrays have different devices: {sorted(devs)}")
+    return devs
+
+
+class Dispatcher:
+    """Callable returned by `njit`: traces the function on its first call per
+    argument signature, then replays the recorded launches."""
+
+    def __init__(self, py_func, options):
+        functools.update_wrapper(self, py_func)
+        self.py_func = py_func
+        self.options = dict(options)
+        self._plans = {}
+
+    def __call__(self, *args, **kwargs):
+        if kwargs:
+            raise TypeError("keyword arguments are not supported in offloaded calls")
+        args = tuple(_wrap_arg(a) for a in args)
+        devs = check_device_args(args)
+        if not devs:
+            raise TypeError(
+                f"{self.py_func.__name__}: no device array among the arguments; this package "
+                "only implements the GPU offload path (there is no CPU fallback) -- copy the "
+                "inputs with numba_mlir_b200.from_host first"
+            )
+        for a in args:
+            if isinstance(a, np.ndarray):
+                raise TypeError("host NumPy arrays cannot be mixed with device arrays")
+        key = lazy.signature_of(args)
+        plan = self._plans.get(key) if key is not None else None
+        if plan is not None:
+            return plan.replay(args)
+        queue = next(a.queue for a in args if isinstance(a, DeviceArray))
+        result, plan = lazy.trace_call(self.py_func, args, queue)
+        if plan is not None and key is not None:
+            self._plans[key] = plan
+        return result
+
+    def trace_dry(self, *args):
+        """Records the plan and generates the kernels without a device (used
+        by host-side tests of the code generator)."""
+        return lazy.trace_call(self.py_func, args, None, dry=True)
+
+
+def jit(signature_or_function=None, locals={}, cache=False, pipeline_class=None,
+        boundscheck=False, **options):
+    """Same call forms as mlir_jit (decorators.py:25-66)."""
+    if callable(signature_or_function) and not isinstance(signature_or_function, (str, tuple, list)):
+        return Dispatcher(signature_or_function, options)
+
+    def wrapper(func):
+        return Dispatcher(func, options)
+
+    return wrapper
+
+
+def njit(*args, **kws):
+    """Equivalent to jit(nopython=True) (mlir_njit, decorators.py:69-81)."""
+    kws.pop("forceobj", None)
+    kws["nopython"] = True
+    return jit(*args, **kws)
+
+
+# Numba keeps control and only parfors are offloaded in the reference
+# (decorators.py:84-104); with no host compiler here it is the same dispatcher.
+njit_replace_parfors = njit
+
+
+class Vectorized:
+    """Result of `vectorize`: a scalar Python function usable as an
+    elementwise operation on device arrays (mlir_vectorize,
+    numba_mlir/mlir/vectorize.py:45-70)."""
+
+    def __init__(self, py_func, options):
+        functools.update_wrapper(self, py_func)
+        self.py_func = py_func
+        self.options = options
+        self._funcs = {}
+
+    def _device_func(self, dtypes):
+        fn = self._funcs.get(dtypes)
+        if fn is None:
+            from . import codegen_ir
+
+            fn = codegen_ir.compile_device_function(self.py_func, dtypes)
+            self._funcs[dtypes] = fn
+        return fn
+
+    def __call__(self, *args):
+        trace = lazy.current_trace()
+        if trace is None:
+            args = tuple(_wrap_arg(a) for a in args)
+            if not any(isinstance(a, DeviceArray) for a in args):
+                raise TypeError("vectorize: no device array among the arguments (no CPU fallback)")
+            return Dispatcher(lambda *xs: self(*xs), {})(*args)
+        dtypes = []
+        for a in args:
+            if isinstance(a, lazy.LazyArray):
+                dtypes.append(a.dtype)
+            elif isinstance(a, DeviceArray):
+                dtypes.append(a.dtype)
+            else:
+                dtypes.append(lazy.scalar_dtype(a))
+        return lazy.call_device_func(trace, self._device_func(tuple(dtypes)), args)
+
+
+def vectorize(*args, **kwargs):
+    if len(args) == 1 and callable(args[0]) and not kwargs:
+        return Vectorized(args[0], {})
+
+    def wrapper(func):
+        return Vectorized(func, kwargs)
+
+    return wrapper

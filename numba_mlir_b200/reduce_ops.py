@@ -104,9 +104,10 @@ def _launch_cols(q, a, out, op, ty, rows, cols):
     rows_per_stage = _TILE_BYTES // (tile_cols * a.dtype.itemsize)
     row_blocks = max(1, min((2 * SMS + col_tiles - 1) // col_tiles,
                             (rows + rows_per_stage - 1) // rows_per_stage, 65535))
-    if col_tiles * 4 > q.COUNTER_BYTES:
+    ngroups = (row_blocks + 7) // 8
+    if col_tiles * (1 + ngroups) * 4 > q.COUNTER_BYTES:
         raise ValueError("too many column tiles for the counter region")
-    counters, partials = q.scratch(row_blocks * cols * _acc_bytes(op, a.dtype))
+    counters, partials = q.scratch((row_blocks + ngroups) * cols * _acc_bytes(op, a.dtype))
     q.launch(k, (col_tiles, row_blocks), (_WS_THREADS,),
              [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
               _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
