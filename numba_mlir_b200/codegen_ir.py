@@ -68,6 +68,15 @@ def _get_pipeline():
                         if fn is not None:
                             inst.value = ir.Global(fn.__name__, fn, inst.loc)
                             changed = True
+            # The namespace objects themselves have no Numba type; once their
+            # attribute reads are gone their loads are dead.
+            owners = {o for o, _a in kernel_impl.API_ATTRS}
+            for blk in func_ir.blocks.values():
+                for inst in blk.body:
+                    if (isinstance(inst, ir.Assign) and isinstance(inst.value, (ir.Global, ir.FreeVar))
+                            and inst.value.value in owners):
+                        inst.value = ir.Const(None, inst.loc)
+                        changed = True
             return changed
 
     @register_pass(mutates_CFG=False, analysis_only=True)
@@ -158,6 +167,13 @@ def _const_literal(value, t):
     if isinstance(t, types.Float):
         return lazy.literal(value, np.float32 if t.bitwidth == 32 else np.float64)
     raise UnsupportedError(f"constant of type {t}")
+
+
+class _NameRef:
+    """Stands in for an ir.Var where only the name is needed."""
+
+    def __init__(self, name):
+        self.name = name
 
 
 class ArrayRep:
@@ -435,7 +451,7 @@ class Translator:
                 return
         if _is_scalar(ttype):
             self.declare(tname)
-            src = self.ir.Var(None, sname, None)
+            src = _NameRef(sname)
             out.append(f"{self.cname(tname)} = {self.scalar(src, ttype)};")
         elif isinstance(ttype, types.Array):
             self.declare(tname)
@@ -447,7 +463,7 @@ class Translator:
             out.append(" ".join(stm))
         elif isinstance(ttype, (types.UniTuple, types.Tuple, types.NamedUniTuple)):
             self.declare(tname)
-            src = self.tuple_elems(self.ir.Var(None, sname, None))
+            src = self.tuple_elems(_NameRef(sname))
             for a, b, et in zip(self.tuples[tname], src, ttype.types):
                 out.append(f"{a} = ({c_scalar_type(et)})({b});")
         elif isinstance(ttype, (types.RangeType, types.RangeIteratorType)):

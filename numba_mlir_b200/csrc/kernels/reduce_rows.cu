@@ -1,9 +1,9 @@
 // Row (last-axis) reductions: out[r] = reduce(a[r, :]).
-// Launch: grid.x = min(rows, 148) CTAs of 288 threads (8 consumer warps + 1 producer).
+// Launch: grid.x = min(rows, 148) CTAs of 128 threads (4 self-feeding warps).
 #include "reduce_kernels.cuh"
 
 #define ROWS_KERNEL(kind, op, ty, R)                                                           \
-  extern "C" __global__ void __launch_bounds__(nmb::red::kWsThreads, 1)                             \
+  extern "C" __global__ void __launch_bounds__(nmb::red::kRowThreads, 1)                             \
       nmb_reduce_rows_##op##_##ty(const R::In *a, R::Out *out, int64_t rows, int64_t cols,     \
                                   uint32_t *status) {                                          \
     extern __shared__ __align__(128) unsigned char nmb_smem[];                                 \

@@ -15,15 +15,17 @@ namespace red {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kWsThreads = (kConsumerWarps + 1) * 32;
-// Row kernel: every consumer warp owns a private ring of kRowDepth stages of
-// 8 KB.  A stage must always be consumed by the same warp: a warp that met a
-// stage for the first time in a later phase could not tell that phase from the
-// one before it (mbarrier waits only see the phase parity).
-constexpr int kRowDepth = 3;
+// Row kernel: four warps, each with a private ring of kRowDepth stages of 8 KB
+// that it fills itself (lane 0 issues the bulk copy for tile j + kRowDepth as
+// soon as the warp has read tile j out of the stage), so no warp ever waits
+// for another one and about 160 KB per SM stay in flight.
+constexpr int kRowWarps = 4;
+constexpr int kRowThreads = kRowWarps * 32;
+constexpr int kRowDepth = 6;
 constexpr int kRowTileBytes = 8192;
-constexpr int kRowStages = kConsumerWarps * kRowDepth; // 192 KB in flight per SM
+constexpr int kRowStages = kRowWarps * kRowDepth;
 constexpr int kColStages = 6;                          // two 99 KB CTAs per SM
-constexpr int kRowSmemBytes = kRowStages * kRowTileBytes + 2 * kRowStages * 8;
+constexpr int kRowSmemBytes = kRowStages * kRowTileBytes + kRowStages * 8;
 constexpr int kColSmemBytes = kColStages * kTileBytes + 2 * kColStages * 8;
 constexpr int kColGroup = 8; // row blocks merged per first-level ticket
 
@@ -86,11 +88,10 @@ __device__ __forceinline__ typename R::Acc warp_reduce_span(const typename R::In
 // ----------------------------------------------------------- row reduction ---
 // out[r] = reduce(a[r, :]) for a C-contiguous (rows, cols) matrix whose base is
 // 16-byte aligned and whose row size is a multiple of 16 bytes.
-// Grid: G <= rows CTAs of kWsThreads; CTA b owns rows [rows*b/G, rows*(b+1)/G).
+// Grid: G <= rows CTAs of kRowThreads; CTA b owns rows [rows*b/G, rows*(b+1)/G).
 // Work is cut into groups: `rt` whole rows in one 8 KB tile when a row fits a
-// tile, else one row as `tpr` consecutive tiles.  Group g belongs to consumer
-// warp g % 8, which reduces it alone (no cross-warp traffic) out of its private
-// stages; the producer warp feeds the eight rings in global tile order.
+// tile, else one row as `tpr` consecutive tiles.  Group g belongs to warp
+// g % 4, which loads and reduces it alone (no cross-warp traffic).
 template <typename R>
 __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict__ a,
                                                typename R::Out *__restrict__ out, int64_t rows,
@@ -100,9 +101,14 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
   using Acc = typename R::Acc;
   constexpr int64_t TILE = kRowTileBytes / sizeof(T);
   constexpr int K = kRowDepth;
-  Ring<kRowStages, kRowTileBytes> ring(smem_raw);
-  T *tiles = reinterpret_cast<T *>(ring.tiles);
-  ring.init(1);
+  T *tiles = reinterpret_cast<T *>(smem_raw);
+  uint64_t *full = reinterpret_cast<uint64_t *>(smem_raw + kRowStages * kRowTileBytes);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRowStages; ++s)
+      mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t G = gridDim.x, b = blockIdx.x;
@@ -111,69 +117,66 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
   const int64_t tpr = (cols + TILE - 1) / TILE;                           // tiles per row
   const int64_t rt = tpr == 1 ? (TILE / cols > 0 ? TILE / cols : 1) : 1; // rows per tile
   const int64_t ngroups = tpr == 1 ? (nrows + rt - 1) / rt : nrows;
+  // this warp's groups: warp, warp + 4, ...; its tiles are numbered j = 0, 1, ...
+  const int64_t my_groups = ngroups > warp ? (ngroups - warp + kRowWarps - 1) / kRowWarps : 0;
+  const int64_t my_tiles = my_groups * tpr;
   bool dead = false;
 
-  if (warp == kConsumerWarps) {
-    if (lane == 0) {
-      int64_t issued = 0;
-      for (int64_t g = 0; g < ngroups; ++g) {
-        const int w = (int)(g % kConsumerWarps);
-        for (int64_t ch = 0; ch < tpr; ++ch, ++issued) {
-          const int64_t j = (g / kConsumerWarps) * tpr + ch; // warp-local tile number
-          const int s = w * K + (int)(j % K);
-          if (j >= K)
-            stage_wait(&ring.empty[s], j / K - 1, dead, status);
-          const T *src;
-          uint32_t bytes;
-          if (tpr == 1) {
-            const int64_t r0 = r_begin + g * rt;
-            const int64_t nr = r_end - r0 < rt ? r_end - r0 : rt;
-            src = a + r0 * cols;
-            bytes = (uint32_t)(nr * cols * sizeof(T));
-          } else {
-            const int64_t c0 = ch * TILE;
-            const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
-            src = a + (r_begin + g) * cols + c0;
-            bytes = (uint32_t)(ne * sizeof(T));
-          }
-          mbar_expect_tx(&ring.full[s], bytes);
-          bulk_load(tiles + (int64_t)s * TILE, src, bytes, &ring.full[s]);
-        }
-      }
-      if (dead) // bounded pause (about 2 ms) for whatever copy may still be in flight
-        for (int t = 0; t < 2000; ++t)
-          __nanosleep(1000);
+  auto issue = [&](int64_t j) {
+    const int64_t g = warp + (j / tpr) * kRowWarps, ch = j % tpr;
+    const int s = warp * K + (int)(j % K);
+    const T *src;
+    uint32_t bytes;
+    if (tpr == 1) {
+      const int64_t r0 = r_begin + g * rt;
+      const int64_t nr = r_end - r0 < rt ? r_end - r0 : rt;
+      src = a + r0 * cols;
+      bytes = (uint32_t)(nr * cols * sizeof(T));
+    } else {
+      const int64_t c0 = ch * TILE;
+      const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
+      src = a + (r_begin + g) * cols + c0;
+      bytes = (uint32_t)(ne * sizeof(T));
     }
-    return;
-  }
+    mbar_expect_tx(&full[s], bytes);
+    bulk_load(tiles + (int64_t)s * TILE, src, bytes, &full[s]);
+  };
 
-  for (int64_t g = warp; g < ngroups; g += kConsumerWarps) {
-    Acc racc = R::identity();
-    for (int64_t ch = 0; ch < tpr; ++ch) {
-      const int64_t j = (g / kConsumerWarps) * tpr + ch;
-      const int s = warp * K + (int)(j % K);
-      stage_wait(&ring.full[s], j / K, dead, status);
-      const T *tile = tiles + (int64_t)s * TILE;
-      if (tpr == 1) {
-        const int64_t r0 = r_begin + g * rt;
-        const int nr = (int)(r_end - r0 < rt ? r_end - r0 : rt);
-        for (int jr = 0; jr < nr; ++jr) {
-          const Acc acc = warp_reduce_span<R>(tile + (int64_t)jr * cols, cols, 0);
-          if (lane == 0)
-            out[r0 + jr] = R::fin(acc);
-        }
-      } else {
-        const int64_t c0 = ch * TILE;
-        const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
-        racc = R::merge(racc, warp_reduce_span<R>(tile, ne, c0));
+  if (lane == 0)
+    for (int64_t j = 0; j < K && j < my_tiles; ++j)
+      issue(j);
+
+  Acc racc = R::identity();
+  for (int64_t j = 0; j < my_tiles; ++j) {
+    const int64_t g = warp + (j / tpr) * kRowWarps, ch = j % tpr;
+    const int s = warp * K + (int)(j % K);
+    stage_wait(&full[s], j / K, dead, status);
+    const T *tile = tiles + (int64_t)s * TILE;
+    if (tpr == 1) {
+      const int64_t r0 = r_begin + g * rt;
+      const int nr = (int)(r_end - r0 < rt ? r_end - r0 : rt);
+      for (int jr = 0; jr < nr; ++jr) {
+        const Acc acc = warp_reduce_span<R>(tile + (int64_t)jr * cols, cols, 0);
+        if (lane == 0)
+          out[r0 + jr] = R::fin(acc);
       }
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(&ring.empty[s]);
+    } else {
+      const int64_t c0 = ch * TILE;
+      const int64_t ne = cols - c0 < TILE ? cols - c0 : TILE;
+      racc = R::merge(racc, warp_reduce_span<R>(tile, ne, c0));
+      if (ch == tpr - 1) {
+        if (lane == 0)
+          out[r_begin + g] = R::fin(racc);
+        racc = R::identity();
+      }
     }
-    if (tpr > 1 && lane == 0)
-      out[r_begin + g] = R::fin(racc);
+    __syncwarp(); // every lane has its data in registers: the stage is free
+    if (lane == 0 && j + K < my_tiles)
+      issue(j + K);
   }
+  if (dead && lane == 0) // bounded pause (about 2 ms) for copies that may still be in flight
+    for (int t = 0; t < 2000; ++t)
+      __nanosleep(1000);
 }
 
 // -------------------------------------------------------- column reduction ---

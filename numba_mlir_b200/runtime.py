@@ -348,7 +348,7 @@ class Queue:
         return self.lib.gpuxQueueGetStream(self.handle) or 0
 
     # -- kernel scratch and status ---------------------------------------------
-    COUNTER_BYTES = 4096
+    COUNTER_BYTES = 65536
 
     def scratch(self, nbytes):
         """Grow-only device scratch shared by the kernels of this queue (stream
