@@ -1,0 +1,9 @@
+"""`from numba_mlir.kernel import kernel, get_global_id, atomic, ...`
+(numba_mlir/numba_mlir/kernel.py:5-22)."""
+
+from numba_mlir_b200.kernel import *  # noqa: F401,F403
+from numba_mlir_b200.kernel import (  # noqa: F401
+    DEFAULT_LOCAL_SIZE, GLOBAL_MEM_FENCE, LOCAL_MEM_FENCE, atomic, barrier, get_global_id,
+    get_global_size, get_group_id, get_local_id, get_local_size, group, kernel, kernel_func,
+    local, mem_fence, private,
+)

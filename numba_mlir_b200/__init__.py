@@ -6,6 +6,7 @@ libnumba_mlir_gpu_runtime_cuda.so (include/numba_mlir_gpu_runtime_cuda.h).
 """
 
 from . import runtime  # noqa: F401
+from .decorators import jit, njit, njit_replace_parfors, vectorize  # noqa: F401
 from .device_array import (  # noqa: F401
     DeviceArray,
     as_device_array,

@@ -1,10 +1,11 @@
 // Column (first-axis) reductions: out[c] = reduce(a[:, c]).
-// Launch: grid = (ceil(cols / (256*VEC)), row_blocks), 288 threads; scratch
-// holds row_blocks*cols accumulators followed by grid.x zeroed counters.
+// Launch: grid = (ceil(cols / CT), row_blocks) with CT = min(cols, 16 KB of
+// elements), 256 threads, about 444 CTAs in all; the scratch layout is
+// described at reduce_cols_ws.
 #include "reduce_kernels.cuh"
 
 #define COLS_KERNEL(kind, op, ty, R)                                                           \
-  extern "C" __global__ void __launch_bounds__(nmb::red::kWsThreads, 2)                             \
+  extern "C" __global__ void __launch_bounds__(nmb::red::kThreads, 3)                             \
       nmb_reduce_cols_##op##_##ty(const R::In *a, R::Out *out, void *partials,                 \
                                   uint32_t *counters, int64_t rows, int64_t cols,              \
                                   uint32_t *status) {                                          \
@@ -12,6 +13,6 @@
     nmb::red::reduce_cols_ws<R>(a, out, static_cast<R::Acc *>(partials), counters, rows,     \
                                   cols, status, nmb_smem);                                     \
   }                                                                                            \
-  NMB_REGISTER_KERNEL(nmb_reduce_cols_##op##_##ty, nmb::red::kColSmemBytes);
+  NMB_REGISTER_KERNEL(nmb_reduce_cols_##op##_##ty, nmb::red::kSmemBytes);
 
 NMB_RED_ALL_OPS(COLS_KERNEL, cols)

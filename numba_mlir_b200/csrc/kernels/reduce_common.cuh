@@ -10,8 +10,9 @@
 //
 // Data movement: the reduced matrix is streamed through shared memory in 16 KB
 // tiles by the TMA bulk-copy engine (4-stage mbarrier ring per CTA), reduced
-// from shared memory with 128-bit reads, then combined with warp shuffles.  Cross-CTA combination (column and full
-// reductions) goes through partials in scratch memory and a ticket counter:
+// from shared memory with 128-bit reads, then combined with warp shuffles.
+// Cross-CTA combination (column and full reductions) goes through partials in
+// scratch memory and ticket counters:
 // the CTA that draws the last ticket merges the partials in index order, so
 // results do not depend on scheduling.
 #pragma once
@@ -62,7 +63,7 @@ template <typename T> struct SumR {
   using Fast = Acc;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
-  static __device__ __forceinline__ Acc widen(Fast f, int64_t, int64_t) { return f; }
+  template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
 };
 template <typename T> struct ProdR {
   using In = T;
@@ -78,7 +79,7 @@ template <typename T> struct ProdR {
   using Fast = Acc;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
-  static __device__ __forceinline__ Acc widen(Fast f, int64_t, int64_t) { return f; }
+  template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
 };
 template <typename T> struct MinR {
   using In = T;
@@ -94,7 +95,7 @@ template <typename T> struct MinR {
   using Fast = Acc;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
-  static __device__ __forceinline__ Acc widen(Fast f, int64_t, int64_t) { return f; }
+  template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
 };
 template <typename T> struct MaxR {
   using In = T;
@@ -110,7 +111,7 @@ template <typename T> struct MaxR {
   using Fast = Acc;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
-  static __device__ __forceinline__ Acc widen(Fast f, int64_t, int64_t) { return f; }
+  template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
 };
 
 template <typename T> struct alignas(16) ValIdx {
@@ -159,9 +160,9 @@ template <typename T, bool MIN> struct ArgR {
       a.k = k;
     }
   }
-  // index of visit k = first + k * stride
-  static __device__ __forceinline__ Acc widen(Fast f, int64_t first, int64_t stride) {
-    return f.k < 0 ? identity() : Acc{f.v, first + (int64_t)f.k * stride};
+  // index_of(k): index along the reduced axis of the thread's visit number k
+  template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F index_of) {
+    return f.k < 0 ? identity() : Acc{f.v, (int64_t)index_of(f.k)};
   }
 };
 

@@ -18,8 +18,6 @@ _TY = {np.dtype(np.float32): "f32", np.dtype(np.float64): "f64",
 OPS = ("sum", "prod", "min", "max", "argmin", "argmax")
 SMS = 148  # B200
 _CTAS = SMS * 3  # full reduction: three 65 KB CTAs fit one SM
-_WS_THREADS = 288  # column kernel: 8 consumer warps + 1 TMA producer warp
-_ROW_THREADS = 128  # row kernel: 4 self-feeding warps
 _TILE_BYTES = 16384
 _I64 = np.int64
 
@@ -92,24 +90,29 @@ def reduce(a, op, axis=None, out=None):
 
 def _launch_rows(q, a, out, op, ty, rows, cols):
     k = q.builtin(f"nmb_reduce_rows_{op}_{ty}")
-    grid = max(1, min(rows, SMS))  # one 209 KB CTA per SM
-    q.launch(k, (grid,), (_ROW_THREADS,),
+    it = a.dtype.itemsize
+    if cols * it > 2048:
+        units = (rows + 7) // 8              # blocks of 8 rows
+    else:
+        units = (rows + (_TILE_BYTES // (cols * it)) - 1) // (_TILE_BYTES // (cols * it))
+    grid = max(1, min(units, _CTAS))
+    q.launch(k, (grid,), (256,),
              [("ptr", a.ptr), ("ptr", out.ptr), _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
 
 
 def _launch_cols(q, a, out, op, ty, rows, cols):
     k = q.builtin(f"nmb_reduce_cols_{op}_{ty}")
-    vec = 16 // a.dtype.itemsize
-    tile_cols = 256 * vec
+    it = a.dtype.itemsize
+    tile_cols = min(cols, _TILE_BYTES // it)
     col_tiles = (cols + tile_cols - 1) // tile_cols
-    rows_per_stage = _TILE_BYTES // (tile_cols * a.dtype.itemsize)
-    row_blocks = max(1, min((2 * SMS + col_tiles - 1) // col_tiles,
+    rows_per_stage = (_TILE_BYTES // (cols * it)) if col_tiles == 1 else 1
+    row_blocks = max(1, min((_CTAS + col_tiles - 1) // col_tiles,
                             (rows + rows_per_stage - 1) // rows_per_stage, 65535))
     ngroups = (row_blocks + 7) // 8
     if row_blocks > 1 and col_tiles * (1 + ngroups) * 4 > q.COUNTER_BYTES:
         raise ValueError("too many column tiles for the counter region")
     counters, partials = q.scratch((row_blocks + ngroups) * cols * _acc_bytes(op, a.dtype))
-    q.launch(k, (col_tiles, row_blocks), (_WS_THREADS,),
+    q.launch(k, (col_tiles, row_blocks), (256,),
              [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
               _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
 
