@@ -155,6 +155,16 @@ void gpuxClearLastError(void);
 /* Number of kernels launched by this library since load (all queues). */
 uint64_t gpuxLaunchCount(void);
 
+/* CUDA graphs: gpuxGraphBegin starts recording everything submitted to the
+ * queue (nothing runs), gpuxGraphEnd returns a replayable graph handle,
+ * gpuxGraphLaunch replays it on the queue's stream and returns an event.
+ * Events returned by launches made while recording must only be destroyed,
+ * not waited on.  Do not allocate or free between Begin and End. */
+void gpuxGraphBegin(void *queue);
+void *gpuxGraphEnd(void *queue);
+void *gpuxGraphLaunch(void *queue, void *graph);
+void gpuxGraphDestroy(void *graph);
+
 /* Host-only: NVRTC-compiles a "//NMB200:CUDA-SOURCE" blob to an sm_100a cubin
  * without touching a device; the result is malloc()ed, release it with
  * gpuxFreeHostBlob. */

@@ -1107,6 +1107,72 @@ GPUX_EXPORT void gpuxClearLastError(void) {
 
 GPUX_EXPORT uint64_t gpuxLaunchCount(void) { return gLaunchCount.load(); }
 
+// CUDA graphs: record the launches submitted to a queue, then replay them with
+// one call (removes the per-launch host cost of short kernels).
+struct Graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  int device = 0;
+};
+
+GPUX_EXPORT void gpuxGraphBegin(void *queue) {
+  LOG_FUNC();
+  if (!queue) {
+    nmb::setError("gpuxGraphBegin: null queue");
+    return;
+  }
+  Queue *q = toQueue(queue);
+  if (!setDevice(q))
+    return;
+  CUDA_TRY(cudaStreamBeginCapture(q->stream, cudaStreamCaptureModeThreadLocal), return);
+}
+
+GPUX_EXPORT void *gpuxGraphEnd(void *queue) {
+  LOG_FUNC();
+  if (!queue) {
+    nmb::setError("gpuxGraphEnd: null queue");
+    return nullptr;
+  }
+  Queue *q = toQueue(queue);
+  if (!setDevice(q))
+    return nullptr;
+  auto g = std::make_unique<Graph>();
+  g->device = q->device;
+  CUDA_TRY(cudaStreamEndCapture(q->stream, &g->graph), return nullptr);
+  CUDA_TRY(cudaGraphInstantiate(&g->exec, g->graph, 0), {
+    cudaGraphDestroy(g->graph);
+    return nullptr;
+  });
+  return g.release();
+}
+
+GPUX_EXPORT void *gpuxGraphLaunch(void *queue, void *graph) {
+  LOG_FUNC();
+  if (!queue || !graph) {
+    nmb::setError("gpuxGraphLaunch: null queue or graph");
+    return nullptr;
+  }
+  Queue *q = toQueue(queue);
+  if (!setDevice(q))
+    return nullptr;
+  CUDA_TRY(cudaGraphLaunch(static_cast<Graph *>(graph)->exec, q->stream), return nullptr);
+  return recordEvent(q);
+}
+
+GPUX_EXPORT void gpuxGraphDestroy(void *graph) {
+  LOG_FUNC();
+  if (!graph)
+    return;
+  Graph *g = static_cast<Graph *>(graph);
+  cudaSetDevice(g->device);
+  if (g->exec)
+    cudaGraphExecDestroy(g->exec);
+  if (g->graph)
+    cudaGraphDestroy(g->graph);
+  (void)cudaGetLastError();
+  delete g;
+}
+
 // Host-only helper: compiles a tagged CUDA C blob to an sm_100a cubin without
 // touching a device.  The result is malloc()ed; release with gpuxFreeHostBlob.
 GPUX_EXPORT void *gpuxCompileToCubin(const void *data, size_t dataSize,

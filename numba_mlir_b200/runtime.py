@@ -82,6 +82,10 @@ SIGNATURES = {
     "gpuxGetLastError": (_cp, []),
     "gpuxClearLastError": (None, []),
     "gpuxLaunchCount": (ctypes.c_uint64, []),
+    "gpuxGraphBegin": (None, [_vp]),
+    "gpuxGraphEnd": (_vp, [_vp]),
+    "gpuxGraphLaunch": (_vp, [_vp, _vp]),
+    "gpuxGraphDestroy": (None, [_vp]),
     "gpuxCompileToCubin": (_vp, [_vp, _sz, ctypes.POINTER(_sz)]),
     "gpuxFreeHostBlob": (None, [_vp]),
     "gpuxBuiltinKernelNames": (_cp, []),
@@ -209,6 +213,54 @@ def pack_params(args):
     return descs, keep
 
 
+def _arg_kind(a):
+    if type(a) is tuple:
+        return "ptr"
+    if isinstance(a, LocalMem):
+        return "local"
+    return a.dtype if isinstance(a, np.generic) else np.asarray(a).dtype
+
+
+class _PreparedParams:
+    """A GPUParamDesc array with reusable value slots."""
+
+    def __init__(self, kinds):
+        n = len(kinds)
+        self.descs = (GPUParamDesc * (n + 1))()
+        self.slots = []
+        for i, k in enumerate(kinds):
+            if k == "local":
+                self.descs[i].data = None
+                self.descs[i].type = P_PTR
+                self.slots.append(None)
+                continue
+            if k == "ptr":
+                slot, ptype, size = ctypes.c_void_p(0), P_PTR, 8
+            else:
+                if k not in _PARAM_OF_DTYPE:
+                    raise TypeError(f"unsupported kernel argument type {k}")
+                ptype, ctype = _PARAM_OF_DTYPE[k]
+                slot, size = ctype(0), ctypes.sizeof(ctype)
+            self.slots.append(slot)
+            self.descs[i].data = ctypes.cast(ctypes.pointer(slot), ctypes.c_void_p)
+            self.descs[i].size = size
+            self.descs[i].type = ptype
+        self.descs[n].data = None
+        self.descs[n].size = 0
+        self.descs[n].type = P_NULL
+        self.descs_ptr = ctypes.cast(self.descs, ctypes.c_void_p)
+
+    def fill(self, args):
+        descs = self.descs
+        for i, (slot, a) in enumerate(zip(self.slots, args)):
+            if slot is None:
+                descs[i].size = a.nbytes
+            elif type(a) is tuple:
+                slot.value = a[1]
+            else:
+                slot.value = a.item() if hasattr(a, "item") else a
+
+
 class Queue:
     """Owning wrapper of a gpux queue handle plus the handles created from it.
 
@@ -227,6 +279,7 @@ class Queue:
         self._modules = {}
         self._kernels = {}
         self._builtin = None
+        self._prepared = {}
         self._scratch = None
         self._scratch_bytes = 0
         self._status = None
@@ -272,13 +325,23 @@ class Queue:
     def launch(self, kernel, grid, block, args, wait=False):
         """gpuxLaunchKernel; returns nothing (the event is waited on when
         `wait`, as the reference does after every launch,
-        GpuRuntimeToLlvm.cpp:619-622, and destroyed either way)."""
-        grid = tuple(grid) + (1,) * (3 - len(grid))
-        block = tuple(block) + (1,) * (3 - len(block))
-        descs, keep = pack_params(args)
+        GpuRuntimeToLlvm.cpp:619-622, and destroyed either way).
+
+        The GPUParamDesc array and its value slots are built once per
+        (kernel, argument kinds) and refilled in place on later launches: the
+        driver copies the values during the call, so reuse is safe."""
+        kinds = tuple(_arg_kind(a) for a in args)
+        key = (kernel, kinds)
+        prepared = self._prepared.get(key)
+        if prepared is None:
+            prepared = _PreparedParams(kinds)
+            self._prepared[key] = prepared
+        prepared.fill(args)
+        ng, nb = len(grid), len(block)
         ev = self.lib.gpuxLaunchKernel(
-            self.handle, kernel, grid[0], grid[1], grid[2], block[0], block[1], block[2],
-            None, ctypes.cast(descs, ctypes.c_void_p),
+            self.handle, kernel, grid[0], grid[1] if ng > 1 else 1, grid[2] if ng > 2 else 1,
+            block[0], block[1] if nb > 1 else 1, block[2] if nb > 2 else 1,
+            None, prepared.descs_ptr,
         )
         if not ev:
             check()
@@ -286,7 +349,29 @@ class Queue:
         if wait:
             self.lib.gpuxWait(self.handle, ev)
         self.lib.gpuxDestroyEvent(self.handle, ev)
-        del keep
+
+    # -- CUDA graphs -----------------------------------------------------------
+    def graph_begin(self):
+        """Starts recording the queue's launches into a CUDA graph."""
+        self.lib.gpuxGraphBegin(self.handle)
+        check()
+
+    def graph_end(self):
+        g = self.lib.gpuxGraphEnd(self.handle)
+        if not g:
+            check()
+            raise GpuRuntimeError("gpuxGraphEnd returned NULL")
+        return g
+
+    def graph_launch(self, graph):
+        ev = self.lib.gpuxGraphLaunch(self.handle, graph)
+        if not ev:
+            check()
+            raise GpuRuntimeError("gpuxGraphLaunch returned NULL")
+        self.lib.gpuxDestroyEvent(self.handle, ev)
+
+    def graph_destroy(self, graph):
+        self.lib.gpuxGraphDestroy(graph)
 
     # -- memory ----------------------------------------------------------------
     def alloc(self, nbytes, kind=ALLOC_DEVICE):
