@@ -183,8 +183,9 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
 // [x*CT, min(cols, (x+1)*CT)), CT = min(cols, 16 KB worth of elements); with
 // one column tile a stage holds 16 KB / row size whole rows.  The row size is
 // a multiple of 16 bytes.
-// Scratch: partials[Gy][cols], group_partials[ceil(Gy/8)][cols], and ticket
-// counters [x][1 + ceil(Gy/8)] that start at zero and are left at zero.
+// Scratch: the level buffers of the merge tree (partials[Gy][cols], then
+// [ceil(Gy/8)][cols], ... down to 2..8 rows) and the ticket counters, which
+// start at zero and are left at zero.
 template <typename R>
 __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict__ a,
                                                typename R::Out *__restrict__ out,
@@ -275,17 +276,19 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
     return;
   }
 
-  // Two-level merge through scratch memory.  Level 1: the last CTA of each
-  // group of kColGroup row blocks merges the group's partials (independent
-  // loads, merged in row-block order) into group_partials; level 2: the last
-  // of those merges the groups.
-  const int64_t ngroups = (Gy + kColGroup - 1) / kColGroup;
-  const int64_t grp = by / kColGroup;
-  const int64_t g_begin = grp * kColGroup;
-  const int g_size = (int)(Gy - g_begin < kColGroup ? Gy - g_begin : kColGroup);
-  Acc *group_partials = partials + Gy * cols;
-  uint32_t *top = counters + (int64_t)blockIdx.x * (1 + ngroups);
-  uint32_t *mine = top + 1 + grp;
+  // Merge tree through scratch memory, fan-in kColGroup per level: the CTA that
+  // draws the last ticket of a group merges the group's rows (independent
+  // loads, merged in row order, so the result does not depend on scheduling)
+  // into one row of the next level and moves up; the last CTA of the top
+  // level writes `out`.  Level buffers follow one another in `partials`
+  // ([Gy][cols], [ceil(Gy/8)][cols], ...); counters hold, per column tile, the
+  // tickets of all groups of all levels, start at zero and are left at zero.
+  int64_t tickets_per_tile = 0;
+  for (int64_t n = Gy; n > 1; n = (n + kColGroup - 1) / kColGroup)
+    tickets_per_tile += (n + kColGroup - 1) / kColGroup;
+  uint32_t *ticket = counters + (int64_t)blockIdx.x * tickets_per_tile;
+  Acc *level = partials;
+  int64_t n = Gy, idx = by;
   __shared__ bool last;
 
 #pragma unroll
@@ -294,56 +297,48 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
     if (cv < nvec)
 #pragma unroll
       for (int l = 0; l < VEC; ++l)
-        partials[by * cols + c0 + cv * VEC + l] = widen(m, l);
+        level[idx * cols + c0 + cv * VEC + l] = widen(m, l);
   }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0)
-    last = atomicAdd(mine, 1u) == (uint32_t)(g_size - 1);
-  __syncthreads();
-  if (!last)
-    return;
-  __threadfence();
-  for (int e = tid; e < ncols; e += kThreads) {
-    Acc part[kColGroup];
-#pragma unroll
-    for (int y = 0; y < kColGroup; ++y)
-      if (y < g_size)
-        part[y] = load_cg(partials + (g_begin + y) * cols + c0 + e);
-    Acc m = R::identity();
-#pragma unroll
-    for (int y = 0; y < kColGroup; ++y)
-      if (y < g_size)
-        m = R::merge(m, part[y]);
-    group_partials[grp * cols + c0 + e] = m;
-  }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    *mine = 0;
-    last = atomicAdd(top, 1u) == (uint32_t)(ngroups - 1);
-  }
-  __syncthreads();
-  if (!last)
-    return;
-  __threadfence();
-  for (int e = tid; e < ncols; e += kThreads) {
-    Acc m = R::identity();
-    for (int64_t g0 = 0; g0 < ngroups; g0 += kColGroup) {
+  while (true) {
+    const int64_t ngroups = (n + kColGroup - 1) / kColGroup;
+    const int64_t grp = idx / kColGroup, g_begin = grp * kColGroup;
+    const int g_size = (int)(n - g_begin < kColGroup ? n - g_begin : kColGroup);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0)
+      last = atomicAdd(ticket + grp, 1u) == (uint32_t)(g_size - 1);
+    __syncthreads();
+    if (!last)
+      return;
+    __threadfence();
+    if (tid == 0)
+      ticket[grp] = 0;
+    Acc *next = level + n * cols;
+    const bool top = ngroups == 1;
+#pragma unroll 2
+    for (int e = tid; e < ncols; e += kThreads) {
       Acc part[kColGroup];
 #pragma unroll
       for (int y = 0; y < kColGroup; ++y)
-        if (g0 + y < ngroups)
-          part[y] = load_cg(group_partials + (g0 + y) * cols + c0 + e);
+        if (y < g_size)
+          part[y] = load_cg(level + (g_begin + y) * cols + c0 + e);
+      Acc m = R::identity();
 #pragma unroll
       for (int y = 0; y < kColGroup; ++y)
-        if (g0 + y < ngroups)
+        if (y < g_size)
           m = R::merge(m, part[y]);
+      if (top)
+        out[c0 + e] = R::fin(m);
+      else
+        next[grp * cols + c0 + e] = m;
     }
-    out[c0 + e] = R::fin(m);
+    if (top)
+      return;
+    ticket += ngroups;
+    level = next;
+    idx = grp;
+    n = ngroups;
   }
-  if (tid == 0)
-    *top = 0;
 }
 
 } // namespace red

@@ -108,10 +108,15 @@ def _launch_cols(q, a, out, op, ty, rows, cols):
     rows_per_stage = (_TILE_BYTES // (cols * it)) if col_tiles == 1 else 1
     row_blocks = max(1, min((_CTAS + col_tiles - 1) // col_tiles,
                             (rows + rows_per_stage - 1) // rows_per_stage, 65535))
-    ngroups = (row_blocks + 7) // 8
-    if row_blocks > 1 and col_tiles * (1 + ngroups) * 4 > q.COUNTER_BYTES:
+    # merge tree with fan-in 8: level buffers and tickets
+    level_rows, tickets, n = 0, 0, row_blocks
+    while n > 1:
+        level_rows += n
+        n = (n + 7) // 8
+        tickets += n
+    if col_tiles * tickets * 4 > q.COUNTER_BYTES:
         raise ValueError("too many column tiles for the counter region")
-    counters, partials = q.scratch((row_blocks + ngroups) * cols * _acc_bytes(op, a.dtype))
+    counters, partials = q.scratch(max(level_rows, 1) * cols * _acc_bytes(op, a.dtype))
     q.launch(k, (col_tiles, row_blocks), (256,),
              [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
               _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
