@@ -149,6 +149,10 @@ void gpuxQueueSynchronize(void *queue);
  * GpuCommon.hpp:25-27) and its CUDA device ordinal. */
 void *gpuxQueueGetStream(void *queue);
 int gpuxQueueGetDevice(void *queue);
+/* Device address of a 4-byte status word owned by the queue.  Kernels of this
+ * library bound every device-side wait; one that gives up stores a non-zero
+ * code here instead of hanging.  Read it back with gpuxMemcpy. */
+void *gpuxQueueStatusPtr(void *queue);
 /* Sticky error message of the last failed call (NULL when none). */
 const char *gpuxGetLastError(void);
 void gpuxClearLastError(void);

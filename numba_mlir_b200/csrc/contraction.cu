@@ -1,21 +1,605 @@
-// Dense-contraction library entry points (placeholder translation unit: the
-// tcgen05 kernels land here).
+// Dense contraction on the 5th-generation tensor cores (tcgen05 + TMEM) with a
+// fused epilogue: the device GEMM entry of the reference
+// (numba_mlir/numba_mlir/math_runtime/sycl/lib/NumpyLinalg.cpp:67-176, a oneMKL
+// call there) and the pairwise Euclidean distance built on it
+// (D = sqrt(max(|x|^2 + |y|^2 - 2 X.Y^T, 0)); reference kernels:
+// numba_mlir/mlir/tests/test_gpu.py:1396-1430,2226-2266).
+//
+// float32 accuracy on TF32 tensor cores comes from the 3xTF32 split: every
+// operand is x = hi + lo with hi = tf32(x), lo = tf32(x - hi), and
+// X.Y^T ~= hi.hi + hi.lo + lo.hi accumulated in fp32 in TMEM (the dropped
+// lo.lo term is 2^-22 relative).
+//
+// Three kernels:
+//   pack      : (rows, K) operand with arbitrary element strides -> per
+//               128-row tile, the hi and lo images in the tcgen05 shared-
+//               memory operand layout (K-major, no swizzle: 8-row x 16-byte
+//               core matrices), zero padded, plus the fp32 row norms.  A
+//               whole tile (hi+lo) is then one contiguous TMA bulk copy.
+//   contract  : persistent, warp-specialised: warp 0 streams packed tiles in
+//               with TMA bulk copies (A resident per row tile, B double
+//               buffered), warp 1 issues tcgen05.mma (24 MMAs of 128x128x8
+//               per output tile at K = 64) into a double-buffered TMEM
+//               accumulator, warps 2-5 drain TMEM with tcgen05.ld, apply the
+//               epilogue and store 128x128 fp32 tiles straight to HBM.  The
+//               op is store bound (1 GiB out vs 8 MiB in at 16384^2 x 64), so
+//               the MMA work hides under the store stream.
+//   finish    : sqrt epilogue for K > 64, where the dot products are
+//               accumulated over K blocks in gemm mode first.
+//
+// Every wait on an mbarrier is bounded; on a timeout the kernel flags the
+// queue's status word, stops, pauses for copies in flight, frees TMEM, returns.
+
 #include "gpu_common.h"
+#include "kernels/bulk_pipe.cuh"
+
+#include <cuda_runtime.h>
 
 #define GPUX_EXPORT extern "C" __attribute__((visibility("default")))
 
-GPUX_EXPORT void _mlir_ciface_mkl_gemm_float32_device(void *, const GPUXMemref2f *,
-                                                      const GPUXMemref2f *, float,
-                                                      float, GPUXMemref2f *) {
-  nmb::setError("mkl_gemm_float32_device: not built yet");
+namespace {
+
+constexpr int kTile = 128;         // output tile is kTile x kTile
+constexpr int kMaxK = 64;          // K elements resident per launch
+constexpr int kChunkBytes = 2048;  // one K chunk (4 elements) of a 128-row tile: 16 groups x 128 B
+constexpr int kThreads = 192;      // producer warp, MMA warp, 4 epilogue warps
+constexpr int kEpilogueWarp0 = 2;
+constexpr uint64_t kWaitCycles = 4000000000ull; // about 2 s
+
+__host__ __device__ inline int padK(int k) { return (k + 7) / 8 * 8; }
+// bytes of one part (hi or lo) of a tile image
+__host__ __device__ inline int partBytes(int kpad) { return kpad / 4 * kChunkBytes; }
+
+// ------------------------------------------------------------------ pack ---
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
 }
-GPUX_EXPORT void mkl_gemm_float32_device(void *q, const GPUXMemref2f *a,
-                                         const GPUXMemref2f *b, float alpha,
-                                         float beta, GPUXMemref2f *c) {
+
+// src element (r, k) at src[r * ldr + k * ldk]; rows [0, rows), K range
+// [k0, k0 + kcount).  One CTA per 128-row tile.
+extern "C" __global__ void __launch_bounds__(256)
+    nmb_contract_pack_f32(const float *__restrict__ src, int64_t rows, int64_t ldr, int64_t ldk,
+                          int k0, int kcount, int kpad, unsigned char *__restrict__ packed) {
+  const int64_t tile = blockIdx.x;
+  const int pbytes = partBytes(kpad);
+  float *hi = reinterpret_cast<float *>(packed + tile * 2 * (int64_t)pbytes);
+  float *lo = reinterpret_cast<float *>(packed + tile * 2 * (int64_t)pbytes + pbytes);
+  const int chunks = kpad / 4;
+  for (int e = threadIdx.x; e < kTile * chunks; e += blockDim.x) {
+    const int r = e / chunks, kc = e % chunks;
+    const int64_t row = tile * kTile + r;
+    float4 h, l;
+    float *hp = &h.x, *lp = &l.x;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = kc * 4 + i;
+      const float v = (row < rows && k < kcount) ? src[row * ldr + (int64_t)(k0 + k) * ldk] : 0.f;
+      hp[i] = to_tf32(v);
+      lp[i] = to_tf32(v - hp[i]);
+    }
+    const int off = kc * (kChunkBytes / 4) + (r / 8) * 32 + (r % 8) * 4; // in floats
+    *reinterpret_cast<float4 *>(hi + off) = h;
+    *reinterpret_cast<float4 *>(lo + off) = l;
+  }
+}
+
+// norms[r] = sum_k src[r, k]^2 (fp32, k ascending); entries up to `padded` are
+// zero filled.
+extern "C" __global__ void __launch_bounds__(256)
+    nmb_contract_norms_f32(const float *__restrict__ src, int64_t rows, int64_t ldr, int64_t ldk,
+                           int K, int64_t padded, float *__restrict__ norms) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= padded)
+    return;
+  float s = 0.f;
+  if (r < rows)
+    for (int k = 0; k < K; ++k) {
+      const float v = src[r * ldr + (int64_t)k * ldk];
+      s = __fadd_rn(s, __fmul_rn(v, v));
+    }
+  norms[r] = s;
+}
+
+// -------------------------------------------------------------- contract ---
+// Bounded mbarrier wait on a clock budget (the hardware poll itself suspends
+// for a while, so counting polls alone would bound nothing useful).
+__device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity) {
+  const long long t0 = clock64();
+  uint32_t n = 0;
+  while (!nmb::mbar_try_wait(bar, parity))
+    if ((++n & 63u) == 0 && (uint64_t)(clock64() - t0) > kWaitCycles)
+      return false;
+  return true;
+}
+
+// K-major, no-swizzle shared-memory operand descriptor: core matrix = 8 rows x
+// 16 bytes stored contiguously; SBO = distance between 8-row groups (128 B),
+// LBO = distance between the two 16-byte K chunks of one MMA (2048 B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fff);            // start address, bits [0,14)
+  d |= (uint64_t)((kChunkBytes >> 4) & 0x3fff) << 16;    // leading byte offset, bits [16,30)
+  d |= (uint64_t)((128 >> 4) & 0x3fff) << 32;            // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+  return d;                                              // layout type 0: no swizzle
+}
+
+// kind::tf32, fp32 accumulate, A and B K-major, M = 128, N = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTile >> 3) << 17) |
+                                ((uint32_t)(kTile >> 4) << 24);
+
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+               :
+               : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
+               : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   nmb::smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane
+// (row) base + i, registers = columns.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
+  uint32_t *r = reinterpret_cast<uint32_t *>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float r;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+struct ContractParams {
+  const unsigned char *packedA; // [tiles_m][hi | lo]
+  const unsigned char *packedB; // [tiles_n][hi | lo]
+  const float *normA;           // pairwise: |x_i|^2, padded to tiles_m * 128
+  const float *normB;           // pairwise: |y_j|^2, padded to tiles_n * 128
+  float *out;                   // (M, N), row stride ldo elements
+  int64_t M, N, ldo;
+  int kpad;
+  int mode;                     // 0: pairwise distance, 1: gemm (alpha, beta)
+  float alpha, beta;
+  uint32_t *status;
+};
+
+extern "C" __global__ void __launch_bounds__(kThreads, 1)
+    nmb_contract_tf32x3(const ContractParams p) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const int pbytes = partBytes(p.kpad);
+  const int tile_bytes = 2 * pbytes;
+  unsigned char *smA = smem;
+  unsigned char *smB = smem + tile_bytes; // two stages
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 3 * tile_bytes);
+  uint64_t *a_full = bars + 0, *a_empty = bars + 1;
+  uint64_t *b_full = bars + 2, *b_empty = bars + 4;
+  uint64_t *acc_full = bars + 6, *acc_empty = bars + 8;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 10);
+  volatile uint32_t *abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t tiles_m = (p.M + kTile - 1) / kTile, tiles_n = (p.N + kTile - 1) / kTile;
+  const int64_t total = tiles_m * tiles_n;
+  const int64_t t_begin = total * blockIdx.x / gridDim.x, t_end = total * (blockIdx.x + 1) / gridDim.x;
+
+  if (threadIdx.x == 0) {
+    nmb::mbar_init(a_full, 1);
+    nmb::mbar_init(a_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      nmb::mbar_init(&b_full[s], 1);
+      nmb::mbar_init(&b_empty[s], 1);
+      nmb::mbar_init(&acc_full[s], 1);
+      nmb::mbar_init(&acc_empty[s], 4); // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    nmb::mbar_init_fence();
+  }
+  if (warp == 1) {
+    // 2 x 128 fp32 accumulator columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     nmb::smem_u32(tmem_slot)),
+                 "r"(256)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tmem_fence_before();
+  __syncthreads();
+  tmem_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto give_up = [&]() {
+    *abort_flag = 1;
+    atomicExch(p.status, (uint32_t)nmb::kStatusWaitTimeout);
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int64_t cur_i = -1, a_uses = 0;
+      for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
+        const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
+        if (i != cur_i) {
+          if (a_uses > 0 && !wait_bounded(a_empty, (uint32_t)((a_uses - 1) & 1))) {
+            give_up();
+            break;
+          }
+          nmb::mbar_expect_tx(a_full, (uint32_t)tile_bytes);
+          nmb::bulk_load(smA, p.packedA + i * (int64_t)tile_bytes, (uint32_t)tile_bytes, a_full);
+          cur_i = i;
+          ++a_uses;
+        }
+        const int s = (int)(n & 1);
+        const int64_t use = n >> 1;
+        if (use > 0 && !wait_bounded(&b_empty[s], (uint32_t)((use - 1) & 1))) {
+          give_up();
+          break;
+        }
+        nmb::mbar_expect_tx(&b_full[s], (uint32_t)tile_bytes);
+        nmb::bulk_load(smB + s * tile_bytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
+                       &b_full[s]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int64_t cur_i = -1, a_uses = 0;
+      const int ksteps = p.kpad / 8;
+      for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
+        const int64_t n = t - t_begin, i = t / tiles_n;
+        const int s = (int)(n & 1);
+        const int64_t use = n >> 1;
+        bool ok = true;
+        if (i != cur_i) {
+          ok = wait_bounded(a_full, (uint32_t)(a_uses & 1));
+          cur_i = i;
+          ++a_uses;
+        }
+        ok = ok && wait_bounded(&b_full[s], (uint32_t)(use & 1));
+        if (ok && use > 0)
+          ok = wait_bounded(&acc_empty[s], (uint32_t)((use - 1) & 1));
+        if (!ok) {
+          give_up();
+          break;
+        }
+        tmem_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(s * kTile);
+        const uint32_t a_addr = nmb::smem_u32(smA), b_addr = nmb::smem_u32(smB + s * tile_bytes);
+        uint32_t acc = 0;
+#pragma unroll 1
+        for (int prod = 0; prod < 3; ++prod) {
+          // hi.hi, hi.lo, lo.hi
+          const uint32_t a_part = a_addr + (prod == 2 ? pbytes : 0);
+          const uint32_t b_part = b_addr + (prod == 1 ? pbytes : 0);
+          for (int ks = 0; ks < ksteps; ++ks) {
+            mma_tf32(d_tmem, smem_desc(a_part + ks * 2 * kChunkBytes),
+                     smem_desc(b_part + ks * 2 * kChunkBytes), acc);
+            acc = 1;
+          }
+        }
+        mma_commit(&b_empty[s]);   // B stage reusable once these MMAs have read it
+        mma_commit(&acc_full[s]);  // accumulator ready for the epilogue
+        const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != i);
+        if (last_of_row)
+          mma_commit(a_empty);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: TMEM -> registers -> HBM ----------------
+    const int q = warp & 3; // TMEM lane quarter this warp may read
+    const bool vec_ok = (p.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
+      const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
+      const int s = (int)(n & 1);
+      const int64_t use = n >> 1;
+      if (!wait_bounded(&acc_full[s], (uint32_t)(use & 1))) {
+        give_up();
+        break;
+      }
+      tmem_fence_after();
+      const int64_t row = i * kTile + q * 32 + lane;
+      const float na = p.mode == 0 ? p.normA[row] : 0.f;
+      float *orow = p.out + row * p.ldo;
+#pragma unroll 1
+      for (int c = 0; c < kTile / 32; ++c) {
+        float v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * kTile + c * 32), v);
+        const int64_t col0 = j * kTile + c * 32;
+        if (p.mode == 0) {
+          const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
+#pragma unroll
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 y = __ldg(nb + e4);
+            v[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, v[e4 * 4 + 0], na + y.x), 0.f));
+            v[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, v[e4 * 4 + 1], na + y.y), 0.f));
+            v[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, v[e4 * 4 + 2], na + y.z), 0.f));
+            v[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, v[e4 * 4 + 3], na + y.w), 0.f));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float r = p.alpha * v[e];
+            if (p.beta != 0.f && row < p.M && col0 + e < p.N)
+              r = fmaf(p.beta, orow[col0 + e], r);
+            v[e] = r;
+          }
+        }
+        if (row < p.M) {
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int e4 = 0; e4 < 8; ++e4)
+              __stcs(reinterpret_cast<float4 *>(orow + col0) + e4,
+                     make_float4(v[e4 * 4], v[e4 * 4 + 1], v[e4 * 4 + 2], v[e4 * 4 + 3]));
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (col0 + e < p.N)
+                orow[col0 + e] = v[e];
+          }
+        }
+      }
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        nmb::mbar_arrive(&acc_empty[s]);
+    }
+  }
+
+  tmem_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) // bounded pause (about 2 ms) for copies or MMAs in flight
+    for (int t = 0; t < 2000; ++t)
+      __nanosleep(1000);
+  __syncthreads();
+  if (warp == 1) {
+    tmem_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256)
+                 : "memory");
+  }
+}
+
+// out[i, j] = sqrt(max(na[i] + nb[j] - 2 out[i, j], 0)) over an (M, N) matrix.
+extern "C" __global__ void __launch_bounds__(256)
+    nmb_contract_finish_distance(float *out, int64_t M, int64_t N, int64_t ldo,
+                                 const float *__restrict__ na, const float *__restrict__ nb) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= M * N)
+    return;
+  const int64_t i = idx / N, j = idx % N;
+  float *o = out + i * ldo + j;
+  *o = sqrt_approx(fmaxf(fmaf(-2.f, *o, na[i] + nb[j]), 0.f));
+}
+
+// ------------------------------------------------------------ host side ---
+struct Operand {
+  const float *data; // element (r, k) at data[r * ldr + k * ldk]
+  int64_t rows, K, ldr, ldk;
+};
+
+int smCount(int device) {
+  static int cached[64] = {0};
+  if (device < 64 && cached[device])
+    return cached[device];
+  int n = 148;
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+  if (device < 64)
+    cached[device] = n;
+  return n;
+}
+
+size_t alignUp(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Runs out = epilogue(A . B^T) with A (M, K), B (N, K) given as Operands.
+// mode 0: pairwise distance; mode 1: out = alpha * A.B^T + beta * out.
+bool runContraction(void *queue, const Operand &A, const Operand &B, float *out, int64_t ldo, int mode,
+                    float alpha, float beta) {
+  nmb::QueueView qv;
+  if (!nmb::queueView(queue, &qv))
+    return false;
+  cudaStream_t stream = static_cast<cudaStream_t>(qv.stream);
+  const int64_t M = A.rows, N = B.rows, K = A.K;
+  if (M == 0 || N == 0)
+    return true;
+  const int64_t tiles_m = (M + kTile - 1) / kTile, tiles_n = (N + kTile - 1) / kTile;
+  const int kblock = (int)(K < kMaxK ? K : kMaxK);
+  const int kpad_max = padK(kblock > 0 ? kblock : 1);
+  const size_t packA = (size_t)tiles_m * 2 * partBytes(kpad_max);
+  const size_t packB = (size_t)tiles_n * 2 * partBytes(kpad_max);
+  const size_t normA = alignUp((size_t)tiles_m * kTile * 4, 256);
+  const size_t normB = alignUp((size_t)tiles_n * kTile * 4, 256);
+  unsigned char *scratch =
+      static_cast<unsigned char *>(nmb::scratchGet(queue, packA + packB + normA + normB + 256));
+  if (!scratch)
+    return false;
+  unsigned char *dA = scratch, *dB = scratch + packA;
+  float *nA = reinterpret_cast<float *>(scratch + packA + packB);
+  float *nB = reinterpret_cast<float *>(scratch + packA + packB + normA);
+  uint32_t *status = nmb::statusWord(queue);
+  if (!status)
+    return false;
+
+  static bool attrSet[64] = {false};
+  const int smemBytes = 3 * 2 * partBytes(kpad_max) + 128;
+  if (qv.device >= 64 || !attrSet[qv.device]) {
+    if (cudaFuncSetAttribute(nmb_contract_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             3 * 2 * partBytes(padK(kMaxK)) + 128) != cudaSuccess) {
+      nmb::setError("cudaFuncSetAttribute(nmb_contract_tf32x3) failed: %s",
+                    cudaGetErrorString(cudaGetLastError()));
+      return false;
+    }
+    if (qv.device < 64)
+      attrSet[qv.device] = true;
+  }
+
+  if (mode == 0) {
+    nmb_contract_norms_f32<<<(unsigned)((tiles_m * kTile + 255) / 256), 256, 0, stream>>>(
+        A.data, M, A.ldr, A.ldk, (int)K, tiles_m * kTile, nA);
+    nmb_contract_norms_f32<<<(unsigned)((tiles_n * kTile + 255) / 256), 256, 0, stream>>>(
+        B.data, N, B.ldr, B.ldk, (int)K, tiles_n * kTile, nB);
+    nmb::noteLaunch();
+    nmb::noteLaunch();
+  }
+  const bool single = K <= kMaxK;
+  const int64_t total = tiles_m * tiles_n;
+  const int64_t sms = smCount(qv.device);
+  const unsigned grid = (unsigned)(total < sms ? total : sms);
+  int64_t k0 = 0;
+  bool first = true;
+  do {
+    const int kcount = (int)(K - k0 < kMaxK ? K - k0 : kMaxK);
+    const int kpad = padK(kcount > 0 ? kcount : 1);
+    nmb_contract_pack_f32<<<(unsigned)tiles_m, 256, 0, stream>>>(A.data, M, A.ldr, A.ldk, (int)k0,
+                                                                 kcount, kpad, dA);
+    nmb_contract_pack_f32<<<(unsigned)tiles_n, 256, 0, stream>>>(B.data, N, B.ldr, B.ldk, (int)k0,
+                                                                 kcount, kpad, dB);
+    ContractParams p;
+    p.packedA = dA;
+    p.packedB = dB;
+    p.normA = nA;
+    p.normB = nB;
+    p.out = out;
+    p.M = M;
+    p.N = N;
+    p.ldo = ldo;
+    p.kpad = kpad;
+    p.status = status;
+    if (mode == 0 && single) {
+      p.mode = 0;
+      p.alpha = 1.f;
+      p.beta = 0.f;
+    } else {
+      p.mode = 1;
+      p.alpha = mode == 0 ? 1.f : alpha;
+      p.beta = first ? (mode == 0 ? 0.f : beta) : 1.f;
+    }
+    nmb_contract_tf32x3<<<grid, kThreads, 3 * 2 * partBytes(kpad) + 128, stream>>>(p);
+    nmb::noteLaunch();
+    nmb::noteLaunch();
+    nmb::noteLaunch();
+    first = false;
+    k0 += kMaxK;
+  } while (k0 < K);
+  (void)smemBytes;
+  if (mode == 0 && !single) {
+    nmb_contract_finish_distance<<<(unsigned)((M * N + 255) / 256), 256, 0, stream>>>(out, M, N, ldo,
+                                                                                     nA, nB);
+    nmb::noteLaunch();
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    nmb::setError("contraction launch failed: %s", cudaGetErrorString(e));
+    return false;
+  }
+  return true;
+}
+
+bool unitStride(const GPUXMemref2f *m) { return m->strides[0] == 1 || m->strides[1] == 1; }
+
+} // namespace
+
+// C = alpha * A @ B + beta * C (NumpyLinalg.cpp:67-147); blocking like the
+// reference's `.wait()`.
+GPUX_EXPORT void _mlir_ciface_mkl_gemm_float32_device(void *queue, const GPUXMemref2f *a,
+                                                      const GPUXMemref2f *b, float alpha,
+                                                      float beta, GPUXMemref2f *c) {
+  if (!queue || !a || !b || !c) {
+    nmb::setError("mkl_gemm_float32_device: null argument");
+    return;
+  }
+  const GPUXMemref2f *ops[3] = {a, b, c};
+  const char names[3] = {'a', 'b', 'c'};
+  for (int i = 0; i < 3; ++i)
+    if (!unitStride(ops[i]) && ops[i]->dims[0] > 1 && ops[i]->dims[1] > 1) {
+      // NumpyLinalg.cpp:73-86
+      nmb::setError("mkl gemm suports only arrays contiguous on inner dimension; '%c' strides "
+                    "are %zu and %zu",
+                    names[i], ops[i]->strides[0], ops[i]->strides[1]);
+      return;
+    }
+  if (a->dims[1] != b->dims[0] || c->dims[0] != a->dims[0] || c->dims[1] != b->dims[1]) {
+    nmb::setError("mkl_gemm_float32_device: shape mismatch (%zu,%zu) @ (%zu,%zu) -> (%zu,%zu)",
+                  a->dims[0], a->dims[1], b->dims[0], b->dims[1], c->dims[0], c->dims[1]);
+    return;
+  }
+  const bool c_rowmajor = c->strides[1] == 1 || c->dims[1] == 1;
+  Operand A{a->data + a->offset, (int64_t)a->dims[0], (int64_t)a->dims[1], (int64_t)a->strides[0],
+            (int64_t)a->strides[1]};
+  // rows of the second operand are the columns of b
+  Operand B{b->data + b->offset, (int64_t)b->dims[1], (int64_t)b->dims[0], (int64_t)b->strides[1],
+            (int64_t)b->strides[0]};
+  float *out = c->data + c->offset;
+  bool ok;
+  if (c_rowmajor) {
+    ok = runContraction(queue, A, B, out, (int64_t)c->strides[0], 1, alpha, beta);
+  } else {
+    // column-major C: compute C^T = B^T . A^T, which is row-major
+    ok = runContraction(queue, B, A, out, (int64_t)c->strides[1], 1, alpha, beta);
+  }
+  if (!ok)
+    return;
+  nmb::QueueView qv;
+  if (nmb::queueView(queue, &qv)) {
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(qv.stream));
+    if (e != cudaSuccess)
+      nmb::setError("mkl_gemm_float32_device failed: %s", cudaGetErrorString(e));
+  }
+}
+
+GPUX_EXPORT void mkl_gemm_float32_device(void *q, const GPUXMemref2f *a, const GPUXMemref2f *b,
+                                         float alpha, float beta, GPUXMemref2f *c) {
   _mlir_ciface_mkl_gemm_float32_device(q, a, b, alpha, beta, c);
 }
-GPUX_EXPORT void *_mlir_ciface_nmb_pairwise_distance_float32_device(
-    void *, const GPUXMemref2f *, const GPUXMemref2f *, GPUXMemref2f *) {
-  nmb::setError("nmb_pairwise_distance_float32_device: not built yet");
-  return nullptr;
+
+GPUX_EXPORT void *_mlir_ciface_nmb_pairwise_distance_float32_device(void *queue,
+                                                                    const GPUXMemref2f *x,
+                                                                    const GPUXMemref2f *y,
+                                                                    GPUXMemref2f *d) {
+  if (!queue || !x || !y || !d) {
+    nmb::setError("nmb_pairwise_distance_float32_device: null argument");
+    return nullptr;
+  }
+  if (x->dims[1] != y->dims[1] || d->dims[0] != x->dims[0] || d->dims[1] != y->dims[0]) {
+    nmb::setError("nmb_pairwise_distance_float32_device: shape mismatch x (%zu,%zu), y (%zu,%zu), "
+                  "d (%zu,%zu)",
+                  x->dims[0], x->dims[1], y->dims[0], y->dims[1], d->dims[0], d->dims[1]);
+    return nullptr;
+  }
+  if (d->strides[1] != 1 && d->dims[1] > 1) {
+    nmb::setError("nmb_pairwise_distance_float32_device: d must be row-major");
+    return nullptr;
+  }
+  Operand X{x->data + x->offset, (int64_t)x->dims[0], (int64_t)x->dims[1], (int64_t)x->strides[0],
+            (int64_t)x->strides[1]};
+  Operand Y{y->data + y->offset, (int64_t)y->dims[0], (int64_t)y->dims[1], (int64_t)y->strides[0],
+            (int64_t)y->strides[1]};
+  if (!runContraction(queue, X, Y, d->data + d->offset, (int64_t)d->strides[0], 0, 1.f, 0.f))
+    return nullptr;
+  return nmb::recordEventOn(queue);
 }

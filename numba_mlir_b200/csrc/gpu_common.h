@@ -43,6 +43,7 @@ void *recordEventOn(void *queue);           // event at the stream tail
 void setError(const char *fmt, ...);        // sticky error + stderr
 void noteLaunch();                          // bumps gpuxLaunchCount
 void *scratchGet(void *queue, size_t bytes); // per-queue grow-only scratch
+uint32_t *statusWord(void *queue);            // per-queue device word set by timed-out waits
 
 } // namespace nmb
 

@@ -180,6 +180,7 @@ struct Queue {
   std::unordered_map<void *, int> allocs; // ptr -> GPUX_ALLOC_*
   void *scratch = nullptr;
   size_t scratchBytes = 0;
+  uint32_t *status = nullptr; // device word kernels set when a bounded wait ran out
 
   void retain() { ++refcount; }
   void release() {
@@ -198,6 +199,8 @@ struct Queue {
     }
     if (scratch)
       cudaFreeAsync(scratch, stream);
+    if (status)
+      cudaFreeAsync(status, stream);
     if (ownsStream && stream) {
       cudaStreamSynchronize(stream);
       cudaStreamDestroy(stream);
@@ -603,6 +606,17 @@ void *scratchGet(void *queue, size_t bytes) {
   CUDA_TRY(cudaMallocAsync(&q->scratch, want, q->stream), return nullptr);
   q->scratchBytes = want;
   return q->scratch;
+}
+
+uint32_t *statusWord(void *queue) {
+  Queue *q = toQueue(queue);
+  if (!q->status) {
+    void *p = nullptr;
+    CUDA_TRY(cudaMallocAsync(&p, 256, q->stream), return nullptr);
+    CUDA_TRY(cudaMemsetAsync(p, 0, 256, q->stream), return nullptr);
+    q->status = static_cast<uint32_t *>(p);
+  }
+  return q->status;
 }
 
 } // namespace nmb
@@ -1093,6 +1107,19 @@ GPUX_EXPORT void *gpuxQueueGetStream(void *queue) {
 
 GPUX_EXPORT int gpuxQueueGetDevice(void *queue) {
   return queue ? toQueue(queue)->device : -1;
+}
+
+// Device address of the queue's status word: 0 while every bounded device-side
+// wait succeeded; a kernel that gave up waiting stores a non-zero code.
+GPUX_EXPORT void *gpuxQueueStatusPtr(void *queue) {
+  LOG_FUNC();
+  if (!queue) {
+    nmb::setError("gpuxQueueStatusPtr: null queue");
+    return nullptr;
+  }
+  if (!setDevice(toQueue(queue)))
+    return nullptr;
+  return nmb::statusWord(queue);
 }
 
 GPUX_EXPORT const char *gpuxGetLastError(void) {

@@ -79,6 +79,7 @@ SIGNATURES = {
     "gpuxQueueSynchronize": (None, [_vp]),
     "gpuxQueueGetStream": (_vp, [_vp]),
     "gpuxQueueGetDevice": (_i, [_vp]),
+    "gpuxQueueStatusPtr": (_vp, [_vp]),
     "gpuxGetLastError": (_cp, []),
     "gpuxClearLastError": (None, []),
     "gpuxLaunchCount": (ctypes.c_uint64, []),
@@ -454,16 +455,16 @@ class Queue:
     def status_ptr(self):
         """Device word kernels with bounded waits set when a wait ran out."""
         if self._status is None:
-            self._status = self.alloc(64)
-            self.memset(self._status, 0, 64)
+            self._status = self.lib.gpuxQueueStatusPtr(self.handle)
+            if not self._status:
+                check()
+                raise GpuRuntimeError("gpuxQueueStatusPtr returned NULL")
         return self._status
 
     def check_status(self):
         """Synchronises and raises if any kernel reported a timed-out wait."""
-        if self._status is None:
-            self.synchronize()
-            return
         word = ctypes.c_uint32(0)
+        self.status_ptr
         self.memcpy(ctypes.addressof(word), self._status, 4, COPY_D2H, wait=True)
         check()
         if word.value:
