@@ -315,22 +315,34 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
       ticket[grp] = 0;
     Acc *next = level + n * cols;
     const bool top = ngroups == 1;
-#pragma unroll 2
-    for (int e = tid; e < ncols; e += kThreads) {
-      Acc part[kColGroup];
+    // kMergeBatch elements x kColGroup rows of independent loads are issued
+    // before the first merge/store, so a level costs a few memory round trips.
+    constexpr int kMergeBatch = 4;
+    for (int e0 = tid; e0 < ncols; e0 += kThreads * kMergeBatch) {
+      Acc part[kMergeBatch][kColGroup];
 #pragma unroll
-      for (int y = 0; y < kColGroup; ++y)
-        if (y < g_size)
-          part[y] = load_cg(level + (g_begin + y) * cols + c0 + e);
-      Acc m = R::identity();
+      for (int u = 0; u < kMergeBatch; ++u) {
+        const int e = e0 + u * kThreads;
 #pragma unroll
-      for (int y = 0; y < kColGroup; ++y)
-        if (y < g_size)
-          m = R::merge(m, part[y]);
-      if (top)
-        out[c0 + e] = R::fin(m);
-      else
-        next[grp * cols + c0 + e] = m;
+        for (int y = 0; y < kColGroup; ++y)
+          if (e < ncols && y < g_size)
+            part[u][y] = load_cg(level + (g_begin + y) * cols + c0 + e);
+      }
+#pragma unroll
+      for (int u = 0; u < kMergeBatch; ++u) {
+        const int e = e0 + u * kThreads;
+        if (e < ncols) {
+          Acc m = R::identity();
+#pragma unroll
+          for (int y = 0; y < kColGroup; ++y)
+            if (y < g_size)
+              m = R::merge(m, part[u][y]);
+          if (top)
+            out[c0 + e] = R::fin(m);
+          else
+            next[grp * cols + c0 + e] = m;
+        }
+      }
     }
     if (top)
       return;
