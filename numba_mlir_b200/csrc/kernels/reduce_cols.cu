@@ -1,6 +1,6 @@
 // Column (first-axis) reductions: out[c] = reduce(a[:, c]).
-// Launch: grid = (ceil(cols / CT), row_blocks) with CT = min(cols, 16 KB of
-// elements), 256 threads, about 444 CTAs in all; the scratch layout is
+// Launch: grid = (ceil(cols / ct), row_blocks) with ct the column-slab width
+// (<= 16 KB of elements), 256 threads, about 444 CTAs in all; the scratch layout is
 // described at reduce_cols_ws.
 #include "reduce_kernels.cuh"
 
@@ -8,10 +8,10 @@
   extern "C" __global__ void __launch_bounds__(nmb::red::kThreads, 3)                             \
       nmb_reduce_cols_##op##_##ty(const R::In *a, R::Out *out, void *partials,                 \
                                   uint32_t *counters, int64_t rows, int64_t cols,              \
-                                  uint32_t *status) {                                          \
+                                  int64_t ct, uint32_t *status) {                                          \
     extern __shared__ __align__(128) unsigned char nmb_smem[];                                 \
     nmb::red::reduce_cols_ws<R>(a, out, static_cast<R::Acc *>(partials), counters, rows,     \
-                                  cols, status, nmb_smem);                                     \
+                                  cols, ct, status, nmb_smem);                                     \
   }                                                                                            \
   NMB_REGISTER_KERNEL(nmb_reduce_cols_##op##_##ty, nmb::red::kSmemBytes);
 

@@ -180,9 +180,11 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
 // -------------------------------------------------------- column reduction ---
 // out[c] = reduce(a[:, c]).  Grid (col_tiles, row_blocks) of 256 threads: CTA
 // (x, y) reduces rows [rows*y/Gy, rows*(y+1)/Gy) of the columns
-// [x*CT, min(cols, (x+1)*CT)), CT = min(cols, 16 KB worth of elements); with
-// one column tile a stage holds 16 KB / row size whole rows.  The row size is
-// a multiple of 16 bytes.
+// [x*ct, min(cols, (x+1)*ct)); ct (a launch parameter, a multiple of 16 bytes
+// and at most 16 KB) is the column-slab width.  A stage holds 16 KB / slab
+// size row segments, one bulk copy each (a single copy when the slab spans
+// whole rows).  Narrow slabs keep the per-CTA partial rows short, so the merge
+// tree below costs one memory round trip per level.
 // Scratch: the level buffers of the merge tree (partials[Gy][cols], then
 // [ceil(Gy/8)][cols], ... down to 2..8 rows) and the ticket counters, which
 // start at zero and are left at zero.
@@ -190,8 +192,8 @@ template <typename R>
 __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict__ a,
                                                typename R::Out *__restrict__ out,
                                                typename R::Acc *partials, uint32_t *counters,
-                                               int64_t rows, int64_t cols, uint32_t *status,
-                                               unsigned char *smem_raw) {
+                                               int64_t rows, int64_t cols, int64_t ct,
+                                               uint32_t *status, unsigned char *smem_raw) {
   using T = typename R::In;
   using Acc = typename R::Acc;
   using Fast = typename R::Fast;
@@ -202,10 +204,11 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
   sm.init();
 
   const int tid = threadIdx.x;
-  const int64_t CT = cols < TILE ? cols : TILE;                 // columns per tile
+  const int64_t CT = ct;
   const int64_t c0 = (int64_t)blockIdx.x * CT;
   const int ncols = (int)(cols - c0 < CT ? cols - c0 : CT);     // this CTA's columns
-  const int64_t rs = CT == cols ? TILE / cols : 1;              // rows per stage
+  const int64_t rs = TILE / CT;                                 // rows per stage
+  const bool contiguous = CT == cols;
   const int64_t Gy = gridDim.y, by = blockIdx.y;
   const int64_t r_begin = rows * by / Gy, r_end = rows * (by + 1) / Gy;
   const int64_t nsteps = (r_end - r_begin + rs - 1) / rs;
@@ -214,11 +217,16 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
   auto issue = [&](int64_t i) {
     const int s = (int)(i % kStages);
     const int64_t r0 = r_begin + i * rs;
-    const int64_t nr = r_end - r0 < rs ? r_end - r0 : rs;
-    // whole rows are contiguous when the tile spans every column
-    const uint32_t bytes = (uint32_t)((CT == cols ? nr * cols : (int64_t)ncols) * sizeof(T));
-    mbar_expect_tx(&sm.full[s], bytes);
-    bulk_load(tiles + (int64_t)s * TILE, a + r0 * cols + c0, bytes, &sm.full[s]);
+    const int nr = (int)(r_end - r0 < rs ? r_end - r0 : rs);
+    const uint32_t row_bytes = (uint32_t)(ncols * sizeof(T));
+    mbar_expect_tx(&sm.full[s], row_bytes * nr);
+    if (contiguous) {
+      bulk_load(tiles + (int64_t)s * TILE, a + r0 * cols, row_bytes * nr, &sm.full[s]);
+    } else {
+      for (int j = 0; j < nr; ++j)
+        bulk_load(tiles + (int64_t)s * TILE + (int64_t)j * ncols, a + (r0 + j) * cols + c0, row_bytes,
+                  &sm.full[s]);
+    }
   };
   int64_t issued = 0;
   if (tid == 0)
@@ -317,7 +325,7 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
     const bool top = ngroups == 1;
     // kMergeBatch elements x kColGroup rows of independent loads are issued
     // before the first merge/store, so a level costs a few memory round trips.
-    constexpr int kMergeBatch = 4;
+    constexpr int kMergeBatch = sizeof(Acc) > 8 ? 1 : 4;
     for (int e0 = tid; e0 < ncols; e0 += kThreads * kMergeBatch) {
       Acc part[kMergeBatch][kColGroup];
 #pragma unroll

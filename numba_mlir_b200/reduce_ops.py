@@ -103,9 +103,11 @@ def _launch_rows(q, a, out, op, ty, rows, cols):
 def _launch_cols(q, a, out, op, ty, rows, cols):
     k = q.builtin(f"nmb_reduce_cols_{op}_{ty}")
     it = a.dtype.itemsize
-    tile_cols = min(cols, _TILE_BYTES // it)
+    # column slabs of 4 KB: each thread owns one 16-byte column vector and the
+    # per-CTA partial rows stay short
+    tile_cols = min(cols, 4096 // it)
     col_tiles = (cols + tile_cols - 1) // tile_cols
-    rows_per_stage = (_TILE_BYTES // (cols * it)) if col_tiles == 1 else 1
+    rows_per_stage = _TILE_BYTES // (tile_cols * it)
     row_blocks = max(1, min((_CTAS + col_tiles - 1) // col_tiles,
                             (rows + rows_per_stage - 1) // rows_per_stage, 65535))
     # merge tree with fan-in 8: level buffers and tickets
@@ -119,7 +121,7 @@ def _launch_cols(q, a, out, op, ty, rows, cols):
     counters, partials = q.scratch(max(level_rows, 1) * cols * _acc_bytes(op, a.dtype))
     q.launch(k, (col_tiles, row_blocks), (256,),
              [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
-              _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
+              _I64(rows), _I64(cols), _I64(tile_cols), ("ptr", q.status_ptr)])
 
 
 def _launch_all(q, a, out, op, ty):

@@ -1,0 +1,274 @@
+"""The decorator surface on the GPU: `njit` array expressions (fused ufunc
+chains, broadcasting, reductions, dot), `vectorize`, and plan replay, checked
+against the CPU oracle / NumPy."""
+
+import math
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a):
+    from numba_mlir_b200 import from_host
+
+    return from_host(a)
+
+
+def test_config1_broadcast_add_through_njit(queue):
+    import numba_mlir_b200 as nm
+    from oracle import configs as O
+
+    @nm.njit(parallel=True)
+    def add(a, b):
+        return a + b
+
+    a, b = O.make_inputs("bcast_add")
+    got = add(_dev(a), _dev(b))
+    assert isinstance(got, nm.DeviceArray) and got.dtype == np.float32
+    want = O.bcast_add(a, b)
+    assert np.array_equal(got.copy_to_host().view(np.uint32), want.view(np.uint32))
+    # second call replays the recorded plan on new data
+    a2 = a[::-1].copy()
+    assert np.array_equal(add(_dev(a2), _dev(b)).copy_to_host(), a2 + b)
+    assert len(add._plans) == 1
+
+
+def _black_scholes_body():
+    import numba_mlir_b200 as nm
+
+    @nm.vectorize(nopython=True)
+    def _nberf(x):
+        return math.erf(x)
+
+    # numba_mlir/mlir/tests/test_numpy.py:2827-2852 with float32 constants
+    def black_scholes(price, strike, t, rate, volatility, call, put):
+        mr = -rate
+        sig_sig_two = volatility * volatility * np.float32(2)
+        P = price
+        S = strike
+        T = t
+        a = np.log(P / S)
+        b = T * mr
+        z = T * sig_sig_two
+        c = np.float32(0.25) * z
+        y = np.float32(1.0) / np.sqrt(z)
+        w1 = (a - b + c) * y
+        w2 = (a - b - c) * y
+        d1 = np.float32(0.5) + np.float32(0.5) * _nberf(w1)
+        d2 = np.float32(0.5) + np.float32(0.5) * _nberf(w2)
+        Se = np.exp(b) * S
+        r = P * d1 - Se * d2
+        call[:] = r
+        put[:] = r - P + Se
+
+    return nm.njit(parallel=True)(black_scholes)
+
+
+@pytest.mark.parametrize("n", [524288, 1000003])
+def test_config2_black_scholes_fuses_into_one_kernel(queue, n):
+    """One launch for the whole chain (the reference asserts one scf.parallel,
+    mlir/tests/test_numpy.py:2865-2866); same tolerance as the builtin kernel."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import runtime
+    from oracle import configs as O
+
+    bs = _black_scholes_body()
+    price, strike, t, rate, vol = O.make_inputs("black_scholes", n / 2**24, seed=777777)
+    price, strike, t = price[:n], strike[:n], t[:n]
+    call, put = nm.empty(n), nm.empty(n)
+    args = (_dev(price), _dev(strike), _dev(t), rate, vol, call, put)
+    bs(*args)
+    before = runtime.launch_count()
+    bs(*args)  # replay
+    assert runtime.launch_count() - before == 1
+    ocall, oput = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    O.black_scholes(price, strike, t, rate, vol, ocall, oput)
+    np.testing.assert_allclose(call.copy_to_host(), ocall, rtol=1e-5, atol=2e-5)
+    np.testing.assert_allclose(put.copy_to_host(), oput, rtol=1e-5, atol=2e-5)
+    # scalar arguments are kernel parameters: a new rate needs no new plan
+    bs(_dev(price), _dev(strike), _dev(t), np.float32(0.05), vol, call, put)
+    O.black_scholes(price, strike, t, np.float32(0.05), vol, ocall, oput)
+    np.testing.assert_allclose(call.copy_to_host(), ocall, rtol=1e-5, atol=2e-5)
+    assert len(bs._plans) == 1
+
+
+def test_config3_reductions_through_njit(queue):
+    import numba_mlir_b200 as nm
+    from oracle import configs as O
+
+    @nm.njit(parallel=True)
+    def red(a):
+        return np.sum(a, axis=1), np.min(a, axis=0), np.argmin(a, axis=1)
+
+    @nm.njit(parallel=True)
+    def isum(a):
+        return a.sum()
+
+    (a,) = O.make_inputs("reduce_f32", 1 / 16)
+    s, m, am = red(_dev(a))
+    truth = a.astype(np.float64).sum(axis=1)
+    assert np.all(np.abs(s.copy_to_host() - truth) <= 1e-5 * np.abs(a).astype(np.float64).sum(axis=1))
+    assert np.array_equal(m.copy_to_host(), O.min_axis0(a))
+    assert np.array_equal(am.copy_to_host(), O.argmin_axis1(a))
+    (ai,) = O.make_inputs("reduce_i32", 1 / 64)
+    r = isum(_dev(ai))
+    assert r.dtype == np.int64 and int(r.copy_to_host()) == int(O.int_sum(ai))
+
+
+_bcast_arrays = [np.array([1]), np.array([[1]]), np.array([[1, 2], [3, 4]]), np.array([5, 6]),
+                 np.array([[5], [6]]), np.array([[5, 6]])]
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.int64, np.float32, np.float64])
+def test_reference_broadcast_matrix(queue, dtype):
+    # mlir/tests/test_numpy.py:483-514 (test_broadcast)
+    import numba_mlir_b200 as nm
+
+    @nm.njit
+    def add(a, b):
+        return np.add(a, b)
+
+    for a in _bcast_arrays:
+        for b in _bcast_arrays:
+            a_, b_ = a.astype(dtype), b.astype(dtype)
+            got = add(_dev(a_), _dev(b_)).copy_to_host()
+            want = np.add(a_, b_)
+            assert got.shape == want.shape and got.dtype == want.dtype
+            assert np.array_equal(got, want)
+        assert np.array_equal(add(_dev(a.astype(dtype)), 1).copy_to_host(), a.astype(dtype) + 1)
+
+
+@pytest.mark.parametrize("shapes", [((1, 1), (1, 7), (7, 1)), ((7, 7), (1, 7), (7, 7)),
+                                    ((7, 1), (7, 7), (1, 1)), ((2, 3, 4), (2, 1, 4), (3, 4))])
+def test_reference_broadcast_fusion(queue, shapes):
+    # mlir/tests/test_numpy.py:1270-1293 (a + b * c is one loop)
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import runtime
+
+    @nm.njit
+    def f(a, b, c):
+        return a + b * c
+
+    arrs = [np.arange(math.prod(s)).reshape(s) for s in shapes]
+    before = runtime.launch_count()
+    got = f(*[_dev(x) for x in arrs]).copy_to_host()
+    assert runtime.launch_count() - before == 1
+    assert np.array_equal(got, arrs[0] + arrs[1] * arrs[2])
+
+
+def test_numba_typing_of_python_scalars(queue):
+    """A Python float is float64 under Numba's rules, so float32 * 0.5 is
+    computed and returned in float64, exactly as the CPU oracle does."""
+    import numba
+    import numba_mlir_b200 as nm
+
+    def f(a):
+        return a * 0.5 + 1
+
+    a = np.linspace(-3, 3, 1000).astype(np.float32)
+    got = nm.njit(f)(_dev(a)).copy_to_host()
+    want = numba.njit(f)(a)
+    assert got.dtype == want.dtype == np.float64
+    assert np.array_equal(got, want)
+
+
+def test_unary_math_against_oracle_within_2ulp(queue):
+    """log, exp, sqrt, erf on float32: <= 2 ulp from the CPU oracle (libm via
+    Numba); the reference tolerates rtol 1e-5 (mlir/tests/test_gpu.py:501-548)."""
+    import numba
+    import numba_mlir_b200 as nm
+
+    @nm.vectorize
+    def gerf(x):
+        return math.erf(x)
+
+    @numba.vectorize(nopython=True)
+    def cerf(x):
+        return math.erf(x)
+
+    rng = np.random.default_rng(0)
+    cases = {
+        "log": (np.log, rng.uniform(0.01, 100, 200000)),
+        "exp": (np.exp, rng.uniform(-20, 20, 200000)),
+        "sqrt": (np.sqrt, rng.uniform(0, 1000, 200000)),
+    }
+
+    def ulps(x, y):
+        xi = x.view(np.int32).astype(np.int64)
+        yi = y.view(np.int32).astype(np.int64)
+        xi = np.where(xi < 0, -(xi & 0x7FFFFFFF), xi)
+        yi = np.where(yi < 0, -(yi & 0x7FFFFFFF), yi)
+        return np.abs(xi - yi).max()
+
+    for name, (fn, x) in cases.items():
+        x = x.astype(np.float32)
+        got = nm.njit(lambda a, fn=fn: fn(a))(_dev(x)).copy_to_host()
+        want = numba.njit(parallel=True)(lambda a, fn=fn: fn(a))(x)
+        assert got.dtype == np.float32
+        assert ulps(got, want) <= 2, name
+    x = rng.uniform(-4, 4, 200000).astype(np.float32)
+    got = nm.njit(lambda a: gerf(a))(_dev(x)).copy_to_host()
+    assert ulps(got, cerf(x)) <= 2
+
+
+def test_where_compare_cast_and_strided_operands(queue):
+    import numba_mlir_b200 as nm
+
+    @nm.njit
+    def f(a, b):
+        return np.where(a > b, a - b, np.float32(0)) + np.abs(b)
+
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((64, 48)).astype(np.float32)
+    b = rng.standard_normal((48, 64)).astype(np.float32)
+    got = f(_dev(a), _dev(b).T).copy_to_host()
+    want = np.where(a > b.T, a - b.T, np.float32(0)) + np.abs(b.T)
+    assert np.array_equal(got, want)
+    i = rng.integers(-5, 5, 1000).astype(np.int32)
+    got = nm.njit(lambda x: (x * x).astype(np.float32) / np.float32(2))(_dev(i)).copy_to_host()
+    assert np.array_equal(got, (i * i).astype(np.float32) / np.float32(2))
+
+
+def test_dot_and_norm_expansion_distance(queue):
+    """np.dot on device arrays reaches the tensor-core gemm (numpy/funcs.py:752-812);
+    the distance matrix written with it matches the direct loop to 1e-5."""
+    import numba_mlir_b200 as nm
+    from oracle import configs as O
+
+    @nm.njit(parallel=True)
+    def dist(x, y):
+        xx = np.sum(x * x, axis=1)
+        yy = np.sum(y * y, axis=1)
+        g = np.dot(x, y.T)
+        return np.sqrt(np.maximum(xx.reshape(-1, 1) + yy.reshape(1, -1) - np.float32(2) * g, np.float32(0)))
+
+    rng = np.random.default_rng(5)
+    x = rng.uniform(0, 1, (256, 64)).astype(np.float32)
+    y = rng.uniform(0, 1, (192, 64)).astype(np.float32)
+    got = dist(_dev(x), _dev(y)).copy_to_host()
+    want = np.zeros((256, 192), np.float32)
+    O.pairwise(x, y, want)
+    np.testing.assert_allclose(got, want, rtol=2e-5, atol=1e-6)
+
+
+def test_no_device_argument_is_an_error_not_a_cpu_run(queue):
+    import numba_mlir_b200 as nm
+
+    with pytest.raises(TypeError, match="no CPU fallback"):
+        nm.njit(lambda a: a + 1)(np.ones(4, np.float32))
+
+
+def test_value_dependent_control_flow_still_works(queue):
+    import numba_mlir_b200 as nm
+
+    @nm.njit
+    def f(a, flag):
+        if flag > 0:
+            return a + 1
+        return a - 1
+
+    a = np.arange(10, dtype=np.float32)
+    assert np.array_equal(f(_dev(a), 1).copy_to_host(), a + 1)
+    assert np.array_equal(f(_dev(a), -1).copy_to_host(), a - 1)
