@@ -85,21 +85,21 @@ extern "C" __global__ void __launch_bounds__(256)
   }
 }
 
-// norms[r] = sum_k src[r, k]^2 (fp32, k ascending); entries up to `padded` are
-// zero filled.
+// norms[r] = sum_k src[r, k]^2, accumulated in float64 and rounded once;
+// entries up to `padded` are zero filled.
 extern "C" __global__ void __launch_bounds__(256)
     nmb_contract_norms_f32(const float *__restrict__ src, int64_t rows, int64_t ldr, int64_t ldk,
                            int K, int64_t padded, float *__restrict__ norms) {
   const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= padded)
     return;
-  float s = 0.f;
+  double s = 0.;
   if (r < rows)
     for (int k = 0; k < K; ++k) {
-      const float v = src[r * ldr + (int64_t)k * ldk];
-      s = __fadd_rn(s, __fmul_rn(v, v));
+      const double v = (double)src[r * ldr + (int64_t)k * ldk];
+      s += v * v;
     }
-  norms[r] = s;
+  norms[r] = (float)s;
 }
 
 // -------------------------------------------------------------- contract ---

@@ -1,0 +1,139 @@
+"""User-level programs of the benchmark configurations, written against the
+public decorators (what a numba-mlir user would write).  bench.py, the smoke
+check and the tests import them from here so that they all run the same code.
+"""
+
+import math
+
+import numpy as np
+
+from .decorators import njit, vectorize
+from .kernel import atomic, barrier, get_global_id, get_local_id, get_local_size, kernel, local
+
+
+@vectorize(nopython=True)
+def _nberf(x):
+    return math.erf(x)
+
+
+# Black-Scholes chain of numba_mlir/mlir/tests/test_numpy.py:2827-2852; the
+# Python-float constants are written as float32 so that Numba's typing keeps
+# the whole chain in float32.
+@njit(parallel=True)
+def black_scholes(price, strike, t, rate, volatility, call, put):
+    mr = -rate
+    sig_sig_two = volatility * volatility * np.float32(2)
+
+    P = price
+    S = strike
+    T = t
+
+    a = np.log(P / S)
+    b = T * mr
+
+    z = T * sig_sig_two
+    c = np.float32(0.25) * z
+    y = np.float32(1.0) / np.sqrt(z)
+
+    w1 = (a - b + c) * y
+    w2 = (a - b - c) * y
+
+    d1 = np.float32(0.5) + np.float32(0.5) * _nberf(w1)
+    d2 = np.float32(0.5) + np.float32(0.5) * _nberf(w2)
+
+    Se = np.exp(b) * S
+
+    r = P * d1 - Se * d2
+    call[:] = r
+    put[:] = r - P + Se
+
+
+@njit(parallel=True)
+def broadcast_add(a, b):
+    return a + b
+
+
+@njit(parallel=True)
+def sum_axis1(a):
+    return np.sum(a, axis=1)
+
+
+@njit(parallel=True)
+def min_axis0(a):
+    return np.min(a, axis=0)
+
+
+@njit(parallel=True)
+def argmin_axis1(a):
+    return np.argmin(a, axis=1)
+
+
+@njit(parallel=True)
+def total(a):
+    return np.sum(a)
+
+
+# One Lloyd iteration as a @kernel program: nearest-centroid assignment in
+# float32 (index order over the dimensions, strict `<` so ties keep the lower
+# cluster), then per-cluster sums (float64) and counts (int64) accumulated with
+# atomics.  The work-group first accumulates into local memory so that the
+# global atomics are issued once per group and cluster, not once per point.
+_KM_K = 64
+_KM_D = 16
+KMEANS_LOCAL_SIZE = 256
+
+
+@kernel
+def _kmeans_kernel(points, centroids, labels, sums, counts):
+    i = get_global_id(0)
+    lid = get_local_id(0)
+    lsz = get_local_size(0)
+    K = centroids.shape[0]
+    D = centroids.shape[1]
+
+    lsum = local.array((_KM_K, _KM_D), np.float64)
+    lcnt = local.array(_KM_K, np.int64)
+    j = lid
+    while j < _KM_K * _KM_D:
+        lsum[j // _KM_D, j % _KM_D] = 0.0
+        j += lsz
+    if lid < _KM_K:
+        lcnt[lid] = 0
+    barrier()
+
+    best = 0
+    best_d = np.float32(np.inf)
+    for k in range(K):
+        d = np.float32(0.0)
+        for jj in range(D):
+            t = points[i, jj] - centroids[k, jj]
+            d += t * t
+        if d < best_d:
+            best_d = d
+            best = k
+    labels[i] = best
+    atomic.add(lcnt, best, 1)
+    for jj in range(D):
+        atomic.add(lsum, (best, jj), points[i, jj])
+    barrier()
+
+    j = lid
+    while j < _KM_K * _KM_D:
+        v = lsum[j // _KM_D, j % _KM_D]
+        if v != 0.0:
+            atomic.add(sums, (j // _KM_D, j % _KM_D), v)
+        j += lsz
+    if lid < _KM_K:
+        if lcnt[lid] != 0:
+            atomic.add(counts, lid, lcnt[lid])
+
+
+def kmeans_step(points, centroids, labels, sums, counts):
+    """Assignment + accumulation for every point (N must be a multiple of the
+    work-group size because the body uses barriers)."""
+    n = points.shape[0]
+    if centroids.shape != (_KM_K, _KM_D):
+        raise ValueError("this kernel is written for K = 64 clusters of D = 16 dimensions")
+    if n % KMEANS_LOCAL_SIZE:
+        raise ValueError("the number of points must be a multiple of 256")
+    _kmeans_kernel[n, KMEANS_LOCAL_SIZE](points, centroids, labels, sums, counts)
