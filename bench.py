@@ -2,14 +2,17 @@
 """Benchmark of the numba-mlir offload path on B200.
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
-                    [--workload NAME]
+                    [--workload NAME] [--no-extra] [--no-cpu]
 
 One "step" is one pass of the hot path over one batch of synthetic input.  The
 headline workload is the Black-Scholes fused ufunc chain over 2^24 float32
-options per GPU (20 algorithmic bytes per option); the metric is effective HBM
-GB/s = algorithmic bytes / device time, whole job over all N GPUs.  Inputs and
+options per GPU (20 algorithmic bytes per option), called through the
+`njit(parallel=True)` decorator; the metric is effective HBM GB/s =
+algorithmic bytes / device time, whole job over all N GPUs (weak scaling: every
+GPU holds a full-size shard, the workloads shard along axis 0).  Inputs and
 outputs (320 MB per GPU) exceed the 126 MB L2, so no flush is needed between
-iterations.  Rank 0 prints ONE JSON line.
+iterations.  Rank 0 prints ONE JSON line; with one GPU it also carries a short
+device-time table for the other benchmark configurations ("other_configs").
 
 `--impl reference` times the CPU implementation of the same workload (upstream
 Numba njit(parallel=True), which is what the reference's njit is with its MLIR
@@ -33,6 +36,7 @@ if ROOT not in sys.path:
 METRIC = "effective_hbm_bandwidth"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
+f32 = np.float32
 
 
 def measured_peaks():
@@ -43,13 +47,31 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture
-# summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = {"black_scholes": None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant
+# kernel, from the ncu captures summarised under profiles/ (scaled to the full
+# workload where the capture ran a smaller case).
+NCU_TRAFFIC_BYTES = {
+    "black_scholes": None,
+}
 
 
 # ------------------------------------------------------------- workloads ----
-class BlackScholes:
+class Workload:
+    """One benchmark configuration.  Sub-classes provide host inputs, the
+    device-resident step, the end-to-end step and the CPU oracle step."""
+
+    key = name = dtype = ""
+    bytes_per_step = units_per_step = 0
+    collective = None
+
+    def setup_device(self, queue, seed, dist=None):
+        raise NotImplementedError
+
+    def step_device(self):
+        raise NotImplementedError
+
+
+class BlackScholes(Workload):
     """Config: N = 2^24 float32 options per GPU; spot, strike ~ U[10,50],
     expiry ~ U[1,2], rate 0.1, volatility 0.2; outputs call and put."""
 
@@ -59,62 +81,52 @@ class BlackScholes:
     bytes_per_step = 20 * n  # 3 float32 reads + 2 float32 writes per option
     units_per_step = n
     dtype = "f32"
+    launches_per_step = 1
 
     def host_inputs(self, seed):
         rng = np.random.default_rng(seed)
-        f32 = np.float32
-        return (
-            rng.uniform(10, 50, self.n).astype(f32),
-            rng.uniform(10, 50, self.n).astype(f32),
-            rng.uniform(1, 2, self.n).astype(f32),
-            f32(0.1),
-            f32(0.2),
-        )
+        return (rng.uniform(10, 50, self.n).astype(f32), rng.uniform(10, 50, self.n).astype(f32),
+                rng.uniform(1, 2, self.n).astype(f32), f32(0.1), f32(0.2))
 
-    def setup_device(self, queue, seed):
+    def setup_device(self, queue, seed, dist=None):
         import numba_mlir_b200 as nm
 
         price, strike, t, self.rate, self.vol = self.host_inputs(seed)
         self.queue = queue
-        # pinned staging for the end-to-end leg
-        self.h_in = [nm.pinned_empty(self.n, np.float32, queue) for _ in range(3)]
+        self.h_in = [nm.pinned_empty(self.n, f32, queue) for _ in range(3)]
         for dst, src in zip(self.h_in, (price, strike, t)):
             dst[:] = src
-        self.h_out = [nm.pinned_empty(self.n, np.float32, queue) for _ in range(2)]
+        self.h_out = [nm.pinned_empty(self.n, f32, queue) for _ in range(2)]
         self.d_in = [nm.from_host(x, queue) for x in (price, strike, t)]
-        self.d_out = [nm.empty(self.n, np.float32, queue) for _ in range(2)]
+        self.d_out = [nm.empty(self.n, f32, queue) for _ in range(2)]
         self.h2d_bytes = 3 * 4 * self.n
         self.d2h_bytes = 2 * 4 * self.n
 
     def step_device(self):
-        from numba_mlir_b200 import builtin_ops
+        from numba_mlir_b200 import workloads
 
-        builtin_ops.black_scholes_f32(*self.d_in, self.rate, self.vol, *self.d_out)
-        return 1  # kernels launched
+        workloads.black_scholes(*self.d_in, self.rate, self.vol, *self.d_out)
 
     def step_e2e(self):
         """Host buffers in, host buffers out, through the public API."""
         for d, h in zip(self.d_in, self.h_in):
             d.copy_from_host(h, wait=False)
-        launches = self.step_device()
+        self.step_device()
         for d, h in zip(self.d_out, self.h_out):
             d.copy_to_host(h, wait=False)
         self.queue.synchronize()
-        return launches
 
     def check(self):
-        """Cheap sanity check of the last result (not the parity test)."""
         call = self.d_out[0][:1024].copy_to_host()
         assert np.isfinite(call).all()
 
-    # CPU side ---------------------------------------------------------------
     def cpu_setup(self, seed, fraction=1.0):
         from oracle import configs as O
 
         m = max(1, int(self.n * fraction))
         price, strike, t, rate, vol = self.host_inputs(seed)
         self.cpu_args = (price[:m].copy(), strike[:m].copy(), t[:m].copy(), rate, vol)
-        self.cpu_out = (np.zeros(m, np.float32), np.zeros(m, np.float32))
+        self.cpu_out = (np.zeros(m, f32), np.zeros(m, f32))
         self.cpu_units = m
         self.cpu_bytes = 20 * m
         self._cpu_fn = O.black_scholes
@@ -124,7 +136,180 @@ class BlackScholes:
         self._cpu_fn(*self.cpu_args, *self.cpu_out)
 
 
-WORKLOADS = {"black_scholes": BlackScholes}
+class BroadcastAdd(Workload):
+    """a (2048, 2048) + b (1, 2048), float32; 33.6 MB per call fits L2, so the
+    step rotates over 10 operand/result sets (336 MB)."""
+
+    name = "broadcast_add_f32_2048x2048"
+    key = "bcast_add"
+    bytes_per_step = 33562624
+    units_per_step = 2048 * 2048
+    dtype = "f32"
+    launches_per_step = 1
+
+    def setup_device(self, queue, seed, dist=None):
+        import numba_mlir_b200 as nm
+
+        rng = np.random.default_rng(seed)
+        self.sets = [nm.from_host(rng.uniform(-1, 1, (2048, 2048)).astype(f32), queue) for _ in range(10)]
+        self.b = nm.from_host(rng.uniform(-1, 1, (1, 2048)).astype(f32), queue)
+        self.outs = [nm.empty((2048, 2048), f32, queue) for _ in range(10)]
+        self.i = 0
+
+    # a recorded step must cover one full rotation to keep the working set >L2
+    launches_per_step = 1
+
+    def step_device(self):
+        from numba_mlir_b200 import workloads
+
+        workloads.broadcast_add(self.sets[self.i % 10], self.b, self.outs[self.i % 10])
+        self.i += 1
+
+
+class AxisReduction(Workload):
+    """float32 (16384, 4096) ~ N(0,1): sum(axis=1), min(axis=0), argmin(axis=1)."""
+
+    dtype = "f32"
+    units_per_step = 16384 * 4096
+    launches_per_step = 1
+
+    def __init__(self, which):
+        self.which = which
+        self.key = which
+        self.name = f"{which}_f32_16384x4096"
+        self.bytes_per_step = {"sum_axis1": 268500992, "min_axis0": 268451840,
+                               "argmin_axis1": 268566528}[which]
+
+    def setup_device(self, queue, seed, dist=None):
+        import numba_mlir_b200 as nm
+        from numba_mlir_b200 import workloads
+
+        rng = np.random.default_rng(seed)
+        self.a = nm.from_host(rng.standard_normal((16384, 4096)).astype(f32), queue)
+        self.fn = getattr(workloads, self.which)
+        self.dist = dist if self.which == "min_axis0" else None
+        shape, dt = {"sum_axis1": (16384, f32), "min_axis0": (4096, f32),
+                     "argmin_axis1": (16384, np.int64)}[self.which]
+        self.out = nm.empty(shape, dt, queue)
+
+    def step_device(self):
+        self.fn(self.a, self.out)
+        if self.dist is not None:
+            # rows are sharded: the per-GPU column minima meet in one all-reduce
+            import torch
+
+            t = torch.as_tensor(self.out, device="cuda")
+            self.a.queue.synchronize()
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+
+
+class IntSum(Workload):
+    """np.sum over 2^28 int32 in [-1000, 1000], int64 accumulation (bit-exact)."""
+
+    name = "int32_sum_n2^28"
+    key = "int_sum"
+    dtype = "int64"
+    bytes_per_step = (1 << 30) + 8
+    units_per_step = 1 << 28
+    launches_per_step = 1
+
+    def setup_device(self, queue, seed, dist=None):
+        import numba_mlir_b200 as nm
+        from numba_mlir_b200 import workloads
+
+        rng = np.random.default_rng(seed)
+        self.a = nm.from_host(rng.integers(-1000, 1001, 1 << 28, dtype=np.int32), queue)
+        self.fn = workloads.total
+        self.dist = dist
+        self.out = nm.empty((), np.int64, queue)
+
+    def step_device(self):
+        self.fn(self.a, self.out)
+        if self.dist is not None:
+            import torch
+
+            t = torch.as_tensor(self.out, device="cuda")
+            self.a.queue.synchronize()
+            self.dist.all_reduce(t)
+
+
+class Pairwise(Workload):
+    """X, Y float32 (16384, 64) ~ U[0,1]; D (16384, 16384) float32, 1 GiB out."""
+
+    name = "pairwise_distance_f32_16384x16384x64"
+    key = "pairwise"
+    dtype = "f32 (3xTF32 tensor cores)"
+    bytes_per_step = 1082130432
+    units_per_step = 16384 * 16384
+    launches_per_step = 5
+
+    def setup_device(self, queue, seed, dist=None):
+        import numba_mlir_b200 as nm
+
+        rng = np.random.default_rng(seed)
+        self.x = nm.from_host(rng.uniform(0, 1, (16384, 64)).astype(f32), queue)
+        self.y = nm.from_host(rng.uniform(0, 1, (16384, 64)).astype(f32), queue)
+        self.d = nm.empty((16384, 16384), f32, queue)
+
+    def step_device(self):
+        from numba_mlir_b200 import contraction
+
+        contraction.pairwise_distance(self.x, self.y, self.d)
+
+
+class KMeans(Workload):
+    """One Lloyd iteration: N = 2^22 float32 points, D = 16, K = 64, written
+    with @kernel; fused assignment + accumulation reads the points once and
+    writes the labels (285 MB)."""
+
+    name = "kmeans_iteration_n2^22_d16_k64"
+    key = "kmeans"
+    dtype = "f32"
+    bytes_per_step = 285212672
+    units_per_step = 1 << 22
+    launches_per_step = 3
+
+    def setup_device(self, queue, seed, dist=None):
+        import numba_mlir_b200 as nm
+
+        rng = np.random.default_rng(seed)
+        centres = rng.uniform(-10, 10, (64, 16)).astype(f32)
+        blob = rng.integers(0, 64, 1 << 22)
+        pts = (centres[blob] + rng.standard_normal((1 << 22, 16))).astype(f32)
+        self.pts = nm.from_host(pts, queue)
+        self.cent = nm.from_host(pts[:64].copy(), queue)
+        self.labels = nm.empty(1 << 22, np.int32, queue)
+        self.sums = nm.zeros((64, 16), np.float64, queue)
+        self.counts = nm.zeros(64, np.int64, queue)
+        self.dist = dist
+        self.queue = queue
+
+    def step_device(self):
+        from numba_mlir_b200 import workloads
+
+        q = self.queue
+        q.memset(self.sums.ptr, 0, self.sums.nbytes)
+        q.memset(self.counts.ptr, 0, self.counts.nbytes)
+        workloads.kmeans_step(self.pts, self.cent, self.labels, self.sums, self.counts)
+        if self.dist is not None:
+            import torch
+
+            q.synchronize()
+            self.dist.all_reduce(torch.as_tensor(self.sums, device="cuda"))
+            self.dist.all_reduce(torch.as_tensor(self.counts, device="cuda"))
+        workloads.kmeans_update(self.cent, self.sums, self.counts)
+
+
+WORKLOADS = {
+    "black_scholes": BlackScholes,
+    "bcast_add": BroadcastAdd,
+    "sum_axis1": lambda: AxisReduction("sum_axis1"),
+    "min_axis0": lambda: AxisReduction("min_axis0"),
+    "argmin_axis1": lambda: AxisReduction("argmin_axis1"),
+    "int_sum": IntSum,
+    "pairwise": Pairwise,
+    "kmeans": KMeans,
+}
 
 
 # ---------------------------------------------------------------- clocks ----
@@ -177,7 +362,7 @@ class ClockSampler:
                             self.reasons.add(k)
                 except Exception:
                     pass
-            time.sleep(0.01)
+            time.sleep(0.005)
 
     def start(self):
         if self.nv is not None:
@@ -220,7 +405,7 @@ def run_reference(args):
     minutes whatever --steps is."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    w = WORKLOADS[args.workload]()
+    w = BlackScholes()
     import numba
 
     steps = args.steps if args.steps is not None else 20
@@ -270,6 +455,45 @@ def run_reference(args):
 
 
 # ------------------------------------------------------------- GPU timing ---
+def time_device(queue, workload, steps, warmup, barrier, use_graph):
+    """Device time of `steps` steps (CUDA events on the launching stream).
+
+    With `use_graph` one step is recorded into a CUDA graph after the warm-up
+    and replayed `steps` times, so that the host cost of submitting short
+    kernels does not enter the device timeline."""
+    from numba_mlir_b200 import runtime
+
+    for _ in range(max(warmup, 3)):
+        workload.step_device()
+    barrier()
+    graph = None
+    if use_graph:
+        queue.graph_begin()
+        workload.step_device()
+        graph = queue.graph_end()
+        queue.graph_launch(graph)
+        barrier()
+    count0 = runtime.launch_count()
+    e0 = queue.record()
+    if graph is not None:
+        for _ in range(steps):
+            queue.graph_launch(graph)
+    else:
+        for _ in range(steps):
+            workload.step_device()
+    e1 = queue.record()
+    queue.wait(e1)
+    barrier()
+    ms = queue.elapsed_ms(e0, e1)
+    counted = runtime.launch_count() - count0
+    if graph is not None:
+        counted = steps * workload.launches_per_step
+        queue.graph_destroy(graph)
+    queue.destroy_event(e0)
+    queue.destroy_event(e1)
+    return ms, counted
+
+
 def run_gpu(args):
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -297,7 +521,10 @@ def run_gpu(args):
 
     queue = runtime.get_queue(f"cuda:{local_rank}")
     w = WORKLOADS[args.workload]()
-    w.setup_device(queue, seed=rank)
+    w.setup_device(queue, seed=rank, dist=dist)
+    # a step with a collective cannot be graph captured with the default stream
+    collective = dist is not None and getattr(w, "dist", None) is not None
+    use_graph = not collective and not args.no_graph
 
     def barrier():
         queue.synchronize()
@@ -308,51 +535,58 @@ def run_gpu(args):
 
     sampler = ClockSampler(local_rank)
     sampler.start()
-
-    # -- device-resident leg ---------------------------------------------------
-    for _ in range(max(args.warmup, 3)):
-        w.step_device()
-    barrier()
     sampler.active(True)
-    launches = 0
-    count0 = runtime.launch_count()
-    e0 = queue.record()
-    for _ in range(args.steps):
-        launches += w.step_device()
-    e1 = queue.record()
-    queue.wait(e1)
-    barrier()
+    dev_ms, counted = time_device(queue, w, args.steps, args.warmup, barrier, use_graph)
     sampler.active(False)
-    dev_ms = queue.elapsed_ms(e0, e1)
-    counted = runtime.launch_count() - count0
-    queue.destroy_event(e0)
-    queue.destroy_event(e1)
-    w.check()
+    if hasattr(w, "check"):
+        w.check()
+    queue.check_status()
 
     # -- end-to-end leg (host buffers, copies inside the timed region) ---------
-    e2e_steps = max(1, min(args.steps, 50))
-    for _ in range(2):
-        w.step_e2e()
-    barrier()
-    sampler.active(True)
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        w.step_e2e()
-    barrier()
-    e2e_s = time.perf_counter() - t0
-    sampler.active(False)
+    e2e = None
+    if hasattr(w, "step_e2e"):
+        e2e_steps = max(1, min(args.steps, 50))
+        for _ in range(2):
+            w.step_e2e()
+        barrier()
+        sampler.active(True)
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            w.step_e2e()
+        barrier()
+        e2e_s = time.perf_counter() - t0
+        sampler.active(False)
+        e2e = (e2e_s, e2e_steps)
     clocks = sampler.stop()
 
     if dist is not None:
-        t = torch.tensor([dev_ms, e2e_s], device="cuda", dtype=torch.float64)
+        t = torch.tensor([dev_ms, e2e[0] if e2e else 0.0], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_s = t.tolist()
+        dev_ms, e2e_max = t.tolist()
+        if e2e:
+            e2e = (e2e_max, e2e[1])
+
+    # -- the other configurations, device time only (single GPU) ---------------
+    others = {}
+    if world == 1 and not args.no_extra and args.workload == "black_scholes":
+        peak, _ = measured_peaks()
+        del w.d_in, w.d_out
+        for key in ("bcast_add", "sum_axis1", "min_axis0", "argmin_axis1", "int_sum", "pairwise",
+                    "kmeans"):
+            ow = WORKLOADS[key]()
+            ow.setup_device(queue, seed=0)
+            oms, _ = time_device(queue, ow, 40, 5, barrier, True)
+            queue.check_status()
+            gbs = ow.bytes_per_step / (oms / 40 * 1e-3) / 1e9
+            others[ow.name] = {"us_per_step": oms / 40 * 1e3, "GB/s": gbs,
+                               "frac_of_measured_peak": gbs / peak,
+                               "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS}
+            del ow
 
     if rank == 0:
         ms_per_step = dev_ms / args.steps
         total_bytes = w.bytes_per_step * world
         value = total_bytes / (ms_per_step * 1e-3) / 1e9
-        e2e_value = total_bytes / (e2e_s / e2e_steps) / 1e9
         peak, peak_kind = measured_peaks()
         achieved = w.bytes_per_step / (ms_per_step * 1e-3) / 1e9  # per GPU, per launch
         line = {
@@ -371,8 +605,12 @@ def run_gpu(args):
             "config": {
                 "workload": w.name,
                 "elements_per_step_per_gpu": w.units_per_step,
-                "sharding": "independent contiguous ranges per GPU, no collective",
-                "l2": "inputs+outputs (320 MB/GPU) exceed the 126 MB L2; no flush",
+                "api": "numba_mlir_b200.njit(parallel=True) / @kernel, launched through the gpux* C-ABI",
+                "sharding": "axis 0 split across GPUs, full-size shard per GPU"
+                + (", NCCL all-reduce of the partials each step" if collective else ", no collective"),
+                "l2": "working set per step exceeds the 126 MB L2 (or rotates over >2x L2); no flush",
+                "launch": "one step recorded in a CUDA graph, replayed per step" if use_graph
+                else "eager launches",
             },
             "elements_per_s": w.units_per_step * world / (ms_per_step * 1e-3),
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
@@ -385,17 +623,20 @@ def run_gpu(args):
                 "frac": achieved / peak,
                 "traffic": NCU_TRAFFIC_BYTES.get(w.key),
             },
-            "e2e": {
-                "value": e2e_value,
-                "unit": UNIT,
-                "h2d_bytes_per_step": w.h2d_bytes,
-                "d2h_bytes_per_step": w.d2h_bytes,
-                "steps": e2e_steps,
-            },
             "gpu_launches": counted,
             "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu:
+        if e2e:
+            line["e2e"] = {
+                "value": total_bytes / (e2e[0] / e2e[1]) / 1e9,
+                "unit": UNIT,
+                "h2d_bytes_per_step": w.h2d_bytes,
+                "d2h_bytes_per_step": w.d2h_bytes,
+                "steps": e2e[1],
+            }
+        if others:
+            line["other_configs"] = others
+        if world == 1 and not args.no_cpu and hasattr(w, "cpu_setup"):
             times, threads = time_cpu(w, 0, budget_s=12.0, max_steps=100)
             best = min(times)
             line["cpu_baseline"] = {
@@ -421,6 +662,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="black_scholes", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the other configurations")
+    ap.add_argument("--no-graph", action="store_true", help="eager launches instead of a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

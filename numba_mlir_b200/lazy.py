@@ -424,6 +424,8 @@ class LazyArray:
         target = self if (idx is Ellipsis or idx == slice(None)) else self[idx]
         if target.node.kind != "leaf":
             raise TypeError("cannot assign into an expression")
+        if _retarget_producer(self.trace, target, value):
+            return
         vnode = _as_node(self.trace, value)
         broadcast_shapes(vnode.shape, target.shape)  # raises on mismatch
         if np.broadcast_shapes(vnode.shape, target.shape) != target.shape:
@@ -431,6 +433,34 @@ class LazyArray:
         if vnode.dtype != target.dtype:
             vnode = Node("cast", target.dtype, vnode.shape, (vnode,))
         self.trace.store(target.node.slot, vnode)
+
+
+def _retarget_producer(trace, target, value):
+    """`out[:] = np.sum(a, axis=1)` (or np.dot): when the value is the fresh
+    temporary of the step recorded last, that step is made to write into the
+    assignment target directly instead of a temporary followed by a copy."""
+    if not isinstance(value, LazyArray) or value.node.kind != "leaf" or len(trace.steps) < 2:
+        return False
+    tmp = value.node.slot
+    step, alloc = trace.steps[-1], trace.steps[-2]
+    if alloc != ("alloc", tmp) or step[0] not in ("reduce", "dot") or step[-1] != tmp:
+        return False
+    dst_arr, tmp_arr = trace.arrays[target.node.slot], trace.arrays[tmp]
+    if (dst_arr.shape != tmp_arr.shape or dst_arr.dtype != tmp_arr.dtype
+            or not dst_arr.is_c_contiguous or trace.has_pending(target.node.slot)):
+        return False
+    new_step = step[:-1] + (target.node.slot,)
+    trace.steps[-2:] = [new_step]
+    if not trace.dry:
+        if step[0] == "reduce":
+            from . import reduce_ops
+
+            reduce_ops.reduce(trace.arrays[step[3]], step[1], step[2], out=dst_arr)
+        else:
+            from . import contraction
+
+            contraction.gemm(trace.arrays[step[1]], trace.arrays[step[2]], dst_arr)
+    return True
 
 
 def apply_ufunc(trace, name, inputs):

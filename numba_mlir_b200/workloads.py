@@ -48,29 +48,38 @@ def black_scholes(price, strike, t, rate, volatility, call, put):
     put[:] = r - P + Se
 
 
+# The result is written into an argument (as the reference's offload tests do,
+# mlir/tests/test_gpu.py:1538-1551), so a call allocates nothing.
 @njit(parallel=True)
-def broadcast_add(a, b):
-    return a + b
-
-
-@njit(parallel=True)
-def sum_axis1(a):
-    return np.sum(a, axis=1)
+def broadcast_add(a, b, out):
+    out[:] = a + b
 
 
 @njit(parallel=True)
-def min_axis0(a):
-    return np.min(a, axis=0)
+def sum_axis1(a, out):
+    out[:] = np.sum(a, axis=1)
 
 
 @njit(parallel=True)
-def argmin_axis1(a):
-    return np.argmin(a, axis=1)
+def min_axis0(a, out):
+    out[:] = np.min(a, axis=0)
 
 
 @njit(parallel=True)
-def total(a):
-    return np.sum(a)
+def argmin_axis1(a, out):
+    out[:] = np.argmin(a, axis=1)
+
+
+@njit(parallel=True)
+def total(a, out):
+    out[...] = np.sum(a)
+
+
+# New centroids = float32(sum / count); empty clusters keep their centre.
+@njit(parallel=True)
+def kmeans_update(centroids, sums, counts):
+    cnt = counts.reshape(-1, 1)
+    centroids[:] = np.where(cnt > 0, (sums / np.maximum(cnt, 1)).astype(np.float32), centroids)
 
 
 # One Lloyd iteration as a @kernel program: nearest-centroid assignment in

@@ -107,7 +107,7 @@ def test_atomics(queue, dtype, opname):
 
 def test_atomics_inline_attribute_and_2d_index(queue):
     # the `atomic.add(...)` spelling the reference marks xfail (test_gpu.py:848-855)
-    from numba_mlir_b200.kernel import atomic, get_global_id, kernel
+    from numba_mlir_b200.kernel import DEFAULT_LOCAL_SIZE, atomic, get_global_id, kernel
 
     def k_2d(a, b):
         i = get_global_id(0)
@@ -117,7 +117,7 @@ def test_atomics_inline_attribute_and_2d_index(queue):
     for dtype in ("int32", "int64", "float32"):
         a2 = np.array([[1, 2, 3], [4, 5, 6], [7, 8, 9]], dtype)
         res = _dev(np.zeros((2, 2), dtype))
-        kernel(k_2d)[a2.shape](_dev(a2), res)
+        kernel(k_2d)[a2.shape, DEFAULT_LOCAL_SIZE](_dev(a2), res)
         assert np.array_equal(res.copy_to_host(), GOLDEN[f"atomic_add_2d_{dtype}"])
 
 
