@@ -1,0 +1,61 @@
+"""Row sharding across the GPUs of one box and the few exchanges it needs.
+
+The reference has no multi-device code (one queue per device,
+mlir/lib/Conversion/GpuToGpuRuntime.cpp:169-197).  The benchmark workloads
+shard along axis 0 -- one process per GPU, every process runs the same
+single-GPU kernels on its rows -- and only three results span shards: a full
+sum, a column-wise min, and the per-cluster sums/counts of a k-means
+iteration.  Those partials are all-reduced with torch.distributed (NCCL over
+NVLink on GPUs, gloo in the CPU tests); they are at most a few KB, so the
+exchange is latency bound and no custom kernel is warranted.
+"""
+
+import numpy as np
+
+
+def row_range(n_rows, world, rank):
+    """Contiguous balanced split of `n_rows` rows: rows [begin, end) of `rank`."""
+    if not 0 <= rank < world:
+        raise ValueError("rank out of range")
+    begin = n_rows * rank // world
+    end = n_rows * (rank + 1) // world
+    return begin, end
+
+
+def shard_rows(array, world, rank):
+    """View of this rank's rows of a host or device array."""
+    begin, end = row_range(array.shape[0], world, rank)
+    return array[begin:end]
+
+
+_REDUCE_OPS = ("sum", "min", "max")
+
+
+def allreduce(partial, op="sum", dist=None):
+    """In-place all-reduce of a partial result (DeviceArray or NumPy array).
+
+    `dist` is an initialised torch.distributed module (or None / world 1: the
+    partial already is the result).  A DeviceArray is shared with torch through
+    __cuda_array_interface__; the caller's queue is synchronised first because
+    the collective runs on torch's stream."""
+    if op not in _REDUCE_OPS:
+        raise ValueError(f"unsupported reduction {op}")
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return partial
+    import torch
+
+    rop = {"sum": dist.ReduceOp.SUM, "min": dist.ReduceOp.MIN, "max": dist.ReduceOp.MAX}[op]
+    if isinstance(partial, np.ndarray):
+        t = torch.from_numpy(partial)
+        dist.all_reduce(t, op=rop)
+        return partial
+    partial.queue.synchronize()
+    t = torch.as_tensor(partial, device="cuda")
+    dist.all_reduce(t, op=rop)
+    torch.cuda.current_stream().synchronize()
+    return partial
+
+
+def offset_argmin(local_index, begin):
+    """Row-sharded argmin over axis 0 needs the shard offset added back."""
+    return local_index + begin

@@ -8,7 +8,8 @@ import math
 import numpy as np
 
 from .decorators import njit, vectorize
-from .kernel import atomic, barrier, get_global_id, get_local_id, get_local_size, kernel, local
+from .kernel import (atomic, barrier, get_global_id, get_local_id, get_local_size, kernel, local,
+                     private)
 
 
 @vectorize(nopython=True)
@@ -83,10 +84,11 @@ def kmeans_update(centroids, sums, counts):
 
 
 # One Lloyd iteration as a @kernel program: nearest-centroid assignment in
-# float32 (index order over the dimensions, strict `<` so ties keep the lower
-# cluster), then per-cluster sums (float64) and counts (int64) accumulated with
-# atomics.  The work-group first accumulates into local memory so that the
-# global atomics are issued once per group and cluster, not once per point.
+# float32 (index order over the dimensions, separate multiply and add, strict
+# `<` so ties keep the lower cluster), then per-cluster sums (float64) and
+# counts (int64) accumulated with atomics.  The work-group stages the
+# centroids in local memory and every work-item keeps its point in a private
+# array, so the 64 x 16 inner loop runs out of shared memory and registers.
 _KM_K = 64
 _KM_D = 16
 KMEANS_LOCAL_SIZE = 256
@@ -97,44 +99,32 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
     i = get_global_id(0)
     lid = get_local_id(0)
     lsz = get_local_size(0)
-    K = centroids.shape[0]
-    D = centroids.shape[1]
 
-    lsum = local.array((_KM_K, _KM_D), np.float64)
-    lcnt = local.array(_KM_K, np.int64)
+    cent = local.array((_KM_K, _KM_D), np.float32)
     j = lid
     while j < _KM_K * _KM_D:
-        lsum[j // _KM_D, j % _KM_D] = 0.0
+        cent[j // _KM_D, j % _KM_D] = centroids[j // _KM_D, j % _KM_D]
         j += lsz
-    if lid < _KM_K:
-        lcnt[lid] = 0
     barrier()
+
+    p = private.array(_KM_D, np.float32)
+    for jj in range(_KM_D):
+        p[jj] = points[i, jj]
 
     best = 0
     best_d = np.float32(np.inf)
-    for k in range(K):
+    for k in range(_KM_K):
         d = np.float32(0.0)
-        for jj in range(D):
-            t = points[i, jj] - centroids[k, jj]
+        for jj in range(_KM_D):
+            t = p[jj] - cent[k, jj]
             d += t * t
         if d < best_d:
             best_d = d
             best = k
     labels[i] = best
-    atomic.add(lcnt, best, 1)
-    for jj in range(D):
-        atomic.add(lsum, (best, jj), points[i, jj])
-    barrier()
-
-    j = lid
-    while j < _KM_K * _KM_D:
-        v = lsum[j // _KM_D, j % _KM_D]
-        if v != 0.0:
-            atomic.add(sums, (j // _KM_D, j % _KM_D), v)
-        j += lsz
-    if lid < _KM_K:
-        if lcnt[lid] != 0:
-            atomic.add(counts, lid, lcnt[lid])
+    atomic.add(counts, best, 1)
+    for jj in range(_KM_D):
+        atomic.add(sums, (best, jj), p[jj])
 
 
 def kmeans_step(points, centroids, labels, sums, counts):
