@@ -20,8 +20,9 @@
 //               with TMA bulk copies (A resident per row tile, B double
 //               buffered), warp 1 issues tcgen05.mma (24 MMAs of 128x128x8
 //               per output tile at K = 64) into a double-buffered TMEM
-//               accumulator, warps 2-5 drain TMEM with tcgen05.ld, apply the
-//               epilogue and store 128x128 fp32 tiles straight to HBM.  The
+//               accumulator, warps 2-9 drain TMEM with tcgen05.ld (a 32-row x
+//               64-column piece each), apply the epilogue and store the
+//               128x128 fp32 tile straight to HBM in 32-byte pieces.  The
 //               op is store bound (1 GiB out vs 8 MiB in at 16384^2 x 64), so
 //               the MMA work hides under the store stream.
 //   finish    : sqrt epilogue for K > 64, where the dot products are
@@ -42,7 +43,8 @@ namespace {
 constexpr int kTile = 128;         // output tile is kTile x kTile
 constexpr int kMaxK = 64;          // K elements resident per launch
 constexpr int kChunkBytes = 2048;  // one K chunk (4 elements) of a 128-row tile: 16 groups x 128 B
-constexpr int kThreads = 192;      // producer warp, MMA warp, 4 epilogue warps
+constexpr int kThreads = 320;      // producer warp, MMA warp, 8 epilogue warps
+constexpr int kEpilogueWarps = 8;
 constexpr int kEpilogueWarp0 = 2;
 constexpr uint64_t kWaitCycles = 4000000000ull; // about 2 s
 
@@ -167,7 +169,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 32-byte streaming store (one full sector per thread).
+__device__ __forceinline__ void store8(float *p, const float *v) {
+  asm volatile("st.global.L1::no_allocate.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p),
+               "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
+               : "memory");
 }
 
 __device__ __forceinline__ float sqrt_approx(float x) {
@@ -215,7 +226,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
       nmb::mbar_init(&b_full[s], 1);
       nmb::mbar_init(&b_empty[s], 1);
       nmb::mbar_init(&acc_full[s], 1);
-      nmb::mbar_init(&acc_empty[s], 4); // one arrival per epilogue warp
+      nmb::mbar_init(&acc_empty[s], kEpilogueWarps); // one arrival per epilogue warp
     }
     *abort_flag = 0;
     nmb::mbar_init_fence();
@@ -313,8 +324,13 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     __syncwarp();
   } else {
     // ---------------- epilogue: TMEM -> registers -> HBM ----------------
-    const int q = warp & 3; // TMEM lane quarter this warp may read
-    const bool vec_ok = (p.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    // Warp w may read TMEM lanes 32*(w%4)..+31 (its rows of the tile); two
+    // warps share a lane quarter and take one 64-column half each.
+    const int q = warp & 3;
+    const int half = (warp - kEpilogueWarp0) >> 2;
+    const uintptr_t base = reinterpret_cast<uintptr_t>(p.out);
+    const bool vec8_ok = (p.ldo % 8 == 0) && ((base & 31) == 0);
+    const bool vec4_ok = (p.ldo % 4 == 0) && ((base & 15) == 0);
     for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
       const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
       const int s = (int)(n & 1);
@@ -327,48 +343,57 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
       const int64_t row = i * kTile + q * 32 + lane;
       const float na = p.mode == 0 ? p.normA[row] : 0.f;
       float *orow = p.out + row * p.ldo;
-#pragma unroll 1
-      for (int c = 0; c < kTile / 32; ++c) {
-        float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * kTile + c * 32), v);
-        const int64_t col0 = j * kTile + c * 32;
+      float v[64];
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * kTile + half * 64);
+      tmem_ld32(taddr, v);
+      tmem_ld32(taddr + 32, v + 32);
+      tmem_ld_wait();
+      // the accumulator buffer is free as soon as it sits in registers
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        nmb::mbar_arrive(&acc_empty[s]);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float *w = v + c * 32;
+        const int64_t col0 = j * kTile + half * 64 + c * 32;
         if (p.mode == 0) {
           const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
 #pragma unroll
           for (int e4 = 0; e4 < 8; ++e4) {
             const float4 y = __ldg(nb + e4);
-            v[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, v[e4 * 4 + 0], na + y.x), 0.f));
-            v[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, v[e4 * 4 + 1], na + y.y), 0.f));
-            v[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, v[e4 * 4 + 2], na + y.z), 0.f));
-            v[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, v[e4 * 4 + 3], na + y.w), 0.f));
+            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], na + y.x), 0.f));
+            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], na + y.y), 0.f));
+            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], na + y.z), 0.f));
+            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], na + y.w), 0.f));
           }
         } else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            float r = p.alpha * v[e];
+            float r = p.alpha * w[e];
             if (p.beta != 0.f && row < p.M && col0 + e < p.N)
               r = fmaf(p.beta, orow[col0 + e], r);
-            v[e] = r;
+            w[e] = r;
           }
         }
         if (row < p.M) {
-          if (vec_ok && col0 + 32 <= p.N) {
+          if (vec8_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int e8 = 0; e8 < 4; ++e8)
+              store8(orow + col0 + e8 * 8, w + e8 * 8);
+          } else if (vec4_ok && col0 + 32 <= p.N) {
 #pragma unroll
             for (int e4 = 0; e4 < 8; ++e4)
               __stcs(reinterpret_cast<float4 *>(orow + col0) + e4,
-                     make_float4(v[e4 * 4], v[e4 * 4 + 1], v[e4 * 4 + 2], v[e4 * 4 + 3]));
+                     make_float4(w[e4 * 4], w[e4 * 4 + 1], w[e4 * 4 + 2], w[e4 * 4 + 3]));
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e)
               if (col0 + e < p.N)
-                orow[col0 + e] = v[e];
+                orow[col0 + e] = w[e];
           }
         }
       }
-      tmem_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        nmb::mbar_arrive(&acc_empty[s]);
     }
   }
 

@@ -8,8 +8,8 @@ import math
 import numpy as np
 
 from .decorators import njit, vectorize
-from .kernel import (atomic, barrier, get_global_id, get_local_id, get_local_size, kernel, local,
-                     private)
+from .kernel import (atomic, barrier, get_global_id, get_group_id, get_local_id, get_local_size,
+                     kernel, local, private)
 
 
 @vectorize(nopython=True)
@@ -89,50 +89,72 @@ def kmeans_update(centroids, sums, counts):
 # counts (int64) accumulated with atomics.  The work-group stages the
 # centroids in local memory and every work-item keeps its point in a private
 # array, so the 64 x 16 inner loop runs out of shared memory and registers.
+# Each work-item handles _KM_PTS points and the group accumulates into local
+# memory first: the global atomics are issued once per group and cluster.
 _KM_K = 64
 _KM_D = 16
+_KM_PTS = 8
 KMEANS_LOCAL_SIZE = 256
 
 
 @kernel
 def _kmeans_kernel(points, centroids, labels, sums, counts):
-    i = get_global_id(0)
     lid = get_local_id(0)
     lsz = get_local_size(0)
+    base = get_group_id(0) * (lsz * _KM_PTS)
 
     cent = local.array((_KM_K, _KM_D), np.float32)
+    lsum = local.array((_KM_K, _KM_D), np.float64)
+    lcnt = local.array(_KM_K, np.int64)
     j = lid
     while j < _KM_K * _KM_D:
         cent[j // _KM_D, j % _KM_D] = centroids[j // _KM_D, j % _KM_D]
+        lsum[j // _KM_D, j % _KM_D] = 0.0
         j += lsz
+    if lid < _KM_K:
+        lcnt[lid] = 0
     barrier()
 
     p = private.array(_KM_D, np.float32)
-    for jj in range(_KM_D):
-        p[jj] = points[i, jj]
-
-    best = 0
-    best_d = np.float32(np.inf)
-    for k in range(_KM_K):
-        d = np.float32(0.0)
+    for r in range(_KM_PTS):
+        i = base + r * lsz + lid
         for jj in range(_KM_D):
-            t = p[jj] - cent[k, jj]
-            d += t * t
-        if d < best_d:
-            best_d = d
-            best = k
-    labels[i] = best
-    atomic.add(counts, best, 1)
-    for jj in range(_KM_D):
-        atomic.add(sums, (best, jj), p[jj])
+            p[jj] = points[i, jj]
+        best = 0
+        best_d = np.float32(np.inf)
+        for k in range(_KM_K):
+            d = np.float32(0.0)
+            for jj in range(_KM_D):
+                t = p[jj] - cent[k, jj]
+                d += t * t
+            if d < best_d:
+                best_d = d
+                best = k
+        labels[i] = best
+        atomic.add(lcnt, best, 1)
+        for jj in range(_KM_D):
+            atomic.add(lsum, (best, jj), p[jj])
+    barrier()
+
+    j = lid
+    while j < _KM_K * _KM_D:
+        v = lsum[j // _KM_D, j % _KM_D]
+        if v != 0.0:
+            atomic.add(sums, (j // _KM_D, j % _KM_D), v)
+        j += lsz
+    if lid < _KM_K:
+        if lcnt[lid] != 0:
+            atomic.add(counts, lid, lcnt[lid])
 
 
 def kmeans_step(points, centroids, labels, sums, counts):
-    """Assignment + accumulation for every point (N must be a multiple of the
-    work-group size because the body uses barriers)."""
+    """Assignment + accumulation for every point.  N must be a multiple of
+    256 * 8 because every work-item of a group takes part in the barriers and
+    handles 8 points."""
     n = points.shape[0]
     if centroids.shape != (_KM_K, _KM_D):
         raise ValueError("this kernel is written for K = 64 clusters of D = 16 dimensions")
-    if n % KMEANS_LOCAL_SIZE:
-        raise ValueError("the number of points must be a multiple of 256")
-    _kmeans_kernel[n, KMEANS_LOCAL_SIZE](points, centroids, labels, sums, counts)
+    chunk = KMEANS_LOCAL_SIZE * _KM_PTS
+    if n % chunk:
+        raise ValueError(f"the number of points must be a multiple of {chunk}")
+    _kmeans_kernel[n // _KM_PTS, KMEANS_LOCAL_SIZE](points, centroids, labels, sums, counts)
