@@ -21,8 +21,10 @@
 //               buffered), warp 1 issues tcgen05.mma (24 MMAs of 128x128x8
 //               per output tile at K = 64) into a double-buffered TMEM
 //               accumulator, warps 2-9 drain TMEM with tcgen05.ld (a 32-row x
-//               64-column piece each), apply the epilogue and store the
-//               128x128 fp32 tile straight to HBM in 32-byte pieces.  The
+//               64-column piece each), apply the epilogue and stage the
+//               128x128 fp32 tile in the B stage the MMAs have just finished
+//               with (128-byte swizzled rows), from where four 2-D TMA stores
+//               stream it to HBM (unaligned outputs: 32-byte direct stores).  The
 //               op is store bound (1 GiB out vs 8 MiB in at 16384^2 x 64), so
 //               the MMA work hides under the store stream.
 //   finish    : sqrt epilogue for K > 64, where the dot products are
@@ -34,7 +36,10 @@
 #include "gpu_common.h"
 #include "kernels/bulk_pipe.cuh"
 
+#include <cuda.h>
 #include <cuda_runtime.h>
+
+#include <cstring>
 
 #define GPUX_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -47,6 +52,8 @@ constexpr int kThreads = 320;      // producer warp, MMA warp, 8 epilogue warps
 constexpr int kEpilogueWarps = 8;
 constexpr int kEpilogueWarp0 = 2;
 constexpr uint64_t kWaitCycles = 4000000000ull; // about 2 s
+constexpr int kStageBytes = 65536;  // one operand tile (hi+lo at K = 64) == one 128x128 fp32 output tile
+constexpr int kBoxCols = 32;        // TMA store box: 128 rows x 32 columns (128-byte swizzled rows)
 
 __host__ __device__ inline int padK(int k) { return (k + 7) / 8 * 8; }
 // bytes of one part (hi or lo) of a tile image
@@ -181,6 +188,16 @@ __device__ __forceinline__ void store8(float *p, const float *v) {
                : "memory");
 }
 
+// 2-D TMA store of one 128-row x 32-column box (shared -> global, clipped at
+// the tensor bounds), tracked by the thread's bulk async-group.
+__device__ __forceinline__ void tma_store_box(const CUtensorMap *tmap, int32_t col, int32_t row,
+                                              const void *smem_src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(col), "r"(row), "r"(nmb::smem_u32(smem_src))
+               : "memory");
+}
+
 __device__ __forceinline__ float sqrt_approx(float x) {
   float r;
   asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -198,21 +215,23 @@ struct ContractParams {
   int mode;                     // 0: pairwise distance, 1: gemm (alpha, beta)
   float alpha, beta;
   uint32_t *status;
+  int use_tma_store;            // out is 16-byte aligned with 16-byte row pitch: staged TMA stores
 };
 
 extern "C" __global__ void __launch_bounds__(kThreads, 1)
-    nmb_contract_tf32x3(const ContractParams p) {
+    nmb_contract_tf32x3(const ContractParams p, const __grid_constant__ CUtensorMap out_map) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int pbytes = partBytes(p.kpad);
   const int tile_bytes = 2 * pbytes;
   unsigned char *smA = smem;
-  unsigned char *smB = smem + tile_bytes; // two stages
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 3 * tile_bytes);
+  unsigned char *smB = smem + kStageBytes; // two stages of kStageBytes
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 3 * kStageBytes);
   uint64_t *a_full = bars + 0, *a_empty = bars + 1;
   uint64_t *b_full = bars + 2, *b_empty = bars + 4;
   uint64_t *acc_full = bars + 6, *acc_empty = bars + 8;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 10);
   volatile uint32_t *abort_flag = tmem_slot + 1;
+  volatile uint32_t *half_failed = tmem_slot + 2; // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t tiles_m = (p.M + kTile - 1) / kTile, tiles_n = (p.N + kTile - 1) / kTile;
@@ -224,11 +243,12 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     nmb::mbar_init(a_empty, 1);
     for (int s = 0; s < 2; ++s) {
       nmb::mbar_init(&b_full[s], 1);
-      nmb::mbar_init(&b_empty[s], 1);
+      nmb::mbar_init(&b_empty[s], 2); // one arrival per epilogue half
       nmb::mbar_init(&acc_full[s], 1);
       nmb::mbar_init(&acc_empty[s], kEpilogueWarps); // one arrival per epilogue warp
     }
     *abort_flag = 0;
+    half_failed[0] = half_failed[1] = 0;
     nmb::mbar_init_fence();
   }
   if (warp == 1) {
@@ -272,7 +292,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
         nmb::mbar_expect_tx(&b_full[s], (uint32_t)tile_bytes);
-        nmb::bulk_load(smB + s * tile_bytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
+        nmb::bulk_load(smB + s * kStageBytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
                        &b_full[s]);
       }
     }
@@ -301,7 +321,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         }
         tmem_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(s * kTile);
-        const uint32_t a_addr = nmb::smem_u32(smA), b_addr = nmb::smem_u32(smB + s * tile_bytes);
+        const uint32_t a_addr = nmb::smem_u32(smA), b_addr = nmb::smem_u32(smB + s * kStageBytes);
         uint32_t acc = 0;
 #pragma unroll 1
         for (int prod = 0; prod < 3; ++prod) {
@@ -314,8 +334,9 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
             acc = 1;
           }
         }
-        mma_commit(&b_empty[s]);   // B stage reusable once these MMAs have read it
-        mma_commit(&acc_full[s]);  // accumulator ready for the epilogue
+        // accumulator ready; the B stage becomes the epilogue's staging buffer
+        // and is handed back to the producer by the epilogue
+        mma_commit(&acc_full[s]);
         const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != i);
         if (last_of_row)
           mma_commit(a_empty);
@@ -331,30 +352,36 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     const uintptr_t base = reinterpret_cast<uintptr_t>(p.out);
     const bool vec8_ok = (p.ldo % 8 == 0) && ((base & 31) == 0);
     const bool vec4_ok = (p.ldo % 4 == 0) && ((base & 15) == 0);
-    for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
+    for (int64_t t = t_begin; t < t_end; ++t) {
       const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
       const int s = (int)(n & 1);
       const int64_t use = n >> 1;
-      if (!wait_bounded(&acc_full[s], (uint32_t)(use & 1))) {
-        give_up();
-        break;
-      }
+      // A warp whose wait ran out still joins the half's barrier below, so the
+      // four warps leave the loop in the same iteration.
+      const bool ok = wait_bounded(&acc_full[s], (uint32_t)(use & 1));
+      if (!ok)
+        half_failed[half] = 1;
       tmem_fence_after();
       const int64_t row = i * kTile + q * 32 + lane;
       const float na = p.mode == 0 ? p.normA[row] : 0.f;
       float *orow = p.out + row * p.ldo;
       float v[64];
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * kTile + half * 64);
-      tmem_ld32(taddr, v);
-      tmem_ld32(taddr + 32, v + 32);
-      tmem_ld_wait();
-      // the accumulator buffer is free as soon as it sits in registers
-      tmem_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        nmb::mbar_arrive(&acc_empty[s]);
+      if (ok) {
+        const uint32_t taddr =
+            tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * kTile + half * 64);
+        tmem_ld32(taddr, v);
+        tmem_ld32(taddr + 32, v + 32);
+        tmem_ld_wait();
+        // the accumulator buffer is free as soon as it sits in registers
+        tmem_fence_before();
+        __syncwarp();
+        if (lane == 0)
+          nmb::mbar_arrive(&acc_empty[s]);
+      }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
+        if (!ok)
+          break;
         float *w = v + c * 32;
         const int64_t col0 = j * kTile + half * 64 + c * 32;
         if (p.mode == 0) {
@@ -376,7 +403,17 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
             w[e] = r;
           }
         }
-        if (row < p.M) {
+        if (p.use_tma_store) {
+          // box (half*2 + c) of the staging tile: row r at r*128 bytes, its
+          // 16-byte chunk k at position k ^ (r & 7) (the 128-byte swizzle the
+          // tensor map undoes), so the 8 lanes of a store phase hit 8 banks groups
+          unsigned char *box = smB + s * kStageBytes + (half * 2 + c) * (kTile * kBoxCols * 4);
+          const int r = q * 32 + lane;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            *reinterpret_cast<float4 *>(box + r * 128 + ((k ^ (r & 7)) << 4)) =
+                make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
+        } else if (row < p.M) {
           if (vec8_ok && col0 + 32 <= p.N) {
 #pragma unroll
             for (int e8 = 0; e8 < 4; ++e8)
@@ -394,7 +431,31 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      // The four warps of this half meet; one thread then streams the half's
+      // two boxes out with TMA and gives the stage back to the producer once
+      // the copies have read shared memory.
+      if (p.use_tma_store)
+        nmb::fence_async_smem();
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+      if (half_failed[half]) {
+        give_up();
+        break;
+      }
+      if (q == 0 && lane == 0) {
+        if (p.use_tma_store) {
+          const unsigned char *stage = smB + s * kStageBytes;
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+            tma_store_box(&out_map, (int32_t)(j * kTile + (half * 2 + c) * kBoxCols),
+                          (int32_t)(i * kTile), stage + (half * 2 + c) * (kTile * kBoxCols * 4));
+          nmb::bulk_commit();
+          nmb::bulk_wait_read<0>();
+        }
+        nmb::mbar_arrive(&b_empty[s]);
+      }
     }
+    if (p.use_tma_store && q == 0 && lane == 0)
+      nmb::bulk_wait_all<0>(); // global writes complete before the CTA retires
   }
 
   tmem_fence_before();
@@ -427,6 +488,41 @@ struct Operand {
   const float *data; // element (r, k) at data[r * ldr + k * ldk]
   int64_t rows, K, ldr, ldk;
 };
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encodeTiled() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult st;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &st) != cudaSuccess ||
+        st != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Tensor map of the (M, N) fp32 output for 128-row x 32-column boxes with the
+// 128-byte swizzle; false when the output does not meet the TMA alignment rules.
+bool makeOutMap(float *out, int64_t M, int64_t N, int64_t ldo, CUtensorMap *map) {
+  memset(map, 0, sizeof(*map));
+  if ((reinterpret_cast<uintptr_t>(out) & 15) != 0 || (ldo * 4) % 16 != 0 || !encodeTiled())
+    return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)ldo * 4};
+  const cuuint32_t box[2] = {(cuuint32_t)kBoxCols, (cuuint32_t)kTile};
+  const cuuint32_t estr[2] = {1, 1};
+  return encodeTiled()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                       CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 int smCount(int device) {
   static int cached[64] = {0};
@@ -471,10 +567,12 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     return false;
 
   static bool attrSet[64] = {false};
-  const int smemBytes = 3 * 2 * partBytes(kpad_max) + 128;
+  const int smemBytes = 3 * kStageBytes + 128;
+  CUtensorMap outMap;
+  const bool useTma = makeOutMap(out, M, N, ldo, &outMap);
   if (qv.device >= 64 || !attrSet[qv.device]) {
     if (cudaFuncSetAttribute(nmb_contract_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             3 * 2 * partBytes(padK(kMaxK)) + 128) != cudaSuccess) {
+                             smemBytes) != cudaSuccess) {
       nmb::setError("cudaFuncSetAttribute(nmb_contract_tf32x3) failed: %s",
                     cudaGetErrorString(cudaGetLastError()));
       return false;
@@ -515,6 +613,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     p.ldo = ldo;
     p.kpad = kpad;
     p.status = status;
+    p.use_tma_store = useTma ? 1 : 0;
     if (mode == 0 && single) {
       p.mode = 0;
       p.alpha = 1.f;
@@ -524,14 +623,13 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
       p.alpha = mode == 0 ? 1.f : alpha;
       p.beta = first ? (mode == 0 ? 0.f : beta) : 1.f;
     }
-    nmb_contract_tf32x3<<<grid, kThreads, 3 * 2 * partBytes(kpad) + 128, stream>>>(p);
+    nmb_contract_tf32x3<<<grid, kThreads, smemBytes, stream>>>(p, outMap);
     nmb::noteLaunch();
     nmb::noteLaunch();
     nmb::noteLaunch();
     first = false;
     k0 += kMaxK;
   } while (k0 < K);
-  (void)smemBytes;
   if (mode == 0 && !single) {
     nmb_contract_finish_distance<<<(unsigned)((M * N + 255) / 256), 256, 0, stream>>>(out, M, N, ldo,
                                                                                      nA, nB);
