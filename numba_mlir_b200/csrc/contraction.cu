@@ -39,6 +39,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #define GPUX_EXPORT extern "C" __attribute__((visibility("default")))
@@ -216,6 +217,7 @@ struct ContractParams {
   float alpha, beta;
   uint32_t *status;
   int use_tma_store;            // out is 16-byte aligned with 16-byte row pitch: staged TMA stores
+  int debug_skip;               // development switch: 1 = skip the global stores
 };
 
 extern "C" __global__ void __launch_bounds__(kThreads, 1)
@@ -413,7 +415,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           for (int k = 0; k < 8; ++k)
             *reinterpret_cast<float4 *>(box + r * 128 + ((k ^ (r & 7)) << 4)) =
                 make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
-        } else if (row < p.M) {
+        } else if (row < p.M && !p.debug_skip) {
           if (vec8_ok && col0 + 32 <= p.N) {
 #pragma unroll
             for (int e8 = 0; e8 < 4; ++e8)
@@ -442,7 +444,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       if (q == 0 && lane == 0) {
-        if (p.use_tma_store) {
+        if (p.use_tma_store && !p.debug_skip) {
           const unsigned char *stage = smB + s * kStageBytes;
 #pragma unroll
           for (int c = 0; c < 2; ++c)
@@ -613,7 +615,8 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     p.ldo = ldo;
     p.kpad = kpad;
     p.status = status;
-    p.use_tma_store = useTma ? 1 : 0;
+    p.use_tma_store = (useTma && !getenv("NMB_DEBUG_NO_TMA_STORE")) ? 1 : 0;
+    p.debug_skip = getenv("NMB_DEBUG_SKIP_STORE") ? 1 : 0;
     if (mode == 0 && single) {
       p.mode = 0;
       p.alpha = 1.f;

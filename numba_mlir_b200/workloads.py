@@ -86,13 +86,16 @@ def kmeans_update(centroids, sums, counts):
 # One Lloyd iteration as a @kernel program: nearest-centroid assignment in
 # float32 (index order over the dimensions, separate multiply and add, strict
 # `<` so ties keep the lower cluster), then per-cluster sums (float64) and
-# counts (int64) accumulated with atomics.  The work-group stages the
-# centroids in local memory and every work-item keeps its point in a private
-# array, so the 64 x 16 inner loop runs out of shared memory and registers.
-# Each work-item handles _KM_PTS points and the group accumulates into local
-# memory first: the global atomics are issued once per group and cluster.
+# counts (int64).  The work-group stages the centroids in local memory and
+# every work-item keeps its point in a private array, so the 64 x 16 inner loop
+# runs out of shared memory and registers.  The sums are gathered without
+# per-point atomics: a batch of 256 labelled points is parked in local memory
+# and work-item (cluster group cg, column jcol) walks the batch in order, adding
+# the points of its four clusters into float64 registers; only these registers
+# meet the global arrays through atomics, once per group.
 _KM_K = 64
 _KM_D = 16
+_KM_DP = _KM_D + 1  # padded row of the parked batch
 _KM_PTS = 8
 KMEANS_LOCAL_SIZE = 256
 
@@ -104,17 +107,23 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
     base = get_group_id(0) * (lsz * _KM_PTS)
 
     cent = local.array((_KM_K, _KM_D), np.float32)
-    lsum = local.array((_KM_K, _KM_D), np.float64)
-    lcnt = local.array(_KM_K, np.int64)
+    lp = local.array((KMEANS_LOCAL_SIZE, _KM_DP), np.float32)  # padded rows: no bank conflicts
+    lbl = local.array(KMEANS_LOCAL_SIZE, np.int32)
+    lcnt = local.array(_KM_K, np.int32)
     j = lid
     while j < _KM_K * _KM_D:
         cent[j // _KM_D, j % _KM_D] = centroids[j // _KM_D, j % _KM_D]
-        lsum[j // _KM_D, j % _KM_D] = 0.0
         j += lsz
     if lid < _KM_K:
         lcnt[lid] = 0
     barrier()
 
+    jcol = lid % _KM_D
+    cg = lid // _KM_D
+    a0 = 0.0
+    a1 = 0.0
+    a2 = 0.0
+    a3 = 0.0
     p = private.array(_KM_D, np.float32)
     for r in range(_KM_PTS):
         i = base + r * lsz + lid
@@ -132,16 +141,33 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
                 best = k
         labels[i] = best
         atomic.add(lcnt, best, 1)
+        lbl[lid] = best
         for jj in range(_KM_D):
-            atomic.add(lsum, (best, jj), p[jj])
-    barrier()
+            lp[lid, jj] = p[jj]
+        barrier()
+        for m in range(KMEANS_LOCAL_SIZE):
+            b = lbl[m]
+            if b // 4 == cg:
+                v = lp[m, jcol]
+                w = b % 4
+                if w == 0:
+                    a0 += v
+                elif w == 1:
+                    a1 += v
+                elif w == 2:
+                    a2 += v
+                else:
+                    a3 += v
+        barrier()
 
-    j = lid
-    while j < _KM_K * _KM_D:
-        v = lsum[j // _KM_D, j % _KM_D]
-        if v != 0.0:
-            atomic.add(sums, (j // _KM_D, j % _KM_D), v)
-        j += lsz
+    if a0 != 0.0:
+        atomic.add(sums, (cg * 4, jcol), a0)
+    if a1 != 0.0:
+        atomic.add(sums, (cg * 4 + 1, jcol), a1)
+    if a2 != 0.0:
+        atomic.add(sums, (cg * 4 + 2, jcol), a2)
+    if a3 != 0.0:
+        atomic.add(sums, (cg * 4 + 3, jcol), a3)
     if lid < _KM_K:
         if lcnt[lid] != 0:
             atomic.add(counts, lid, lcnt[lid])
