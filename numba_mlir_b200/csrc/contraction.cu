@@ -16,17 +16,17 @@
 //               memory operand layout (K-major, no swizzle: 8-row x 16-byte
 //               core matrices), zero padded, plus the fp32 row norms.  A
 //               whole tile (hi+lo) is then one contiguous TMA bulk copy.
-//   contract  : persistent, warp-specialised: warp 0 streams packed tiles in
-//               with TMA bulk copies (A resident per row tile, B double
-//               buffered), warp 1 issues tcgen05.mma (24 MMAs of 128x128x8
-//               per output tile at K = 64) into a double-buffered TMEM
-//               accumulator, warps 2-9 drain TMEM with tcgen05.ld (a 32-row x
-//               64-column piece each), apply the epilogue and stage the
-//               128x128 fp32 tile in the B stage the MMAs have just finished
-//               with (128-byte swizzled rows), from where four 2-D TMA stores
-//               stream it to HBM (unaligned outputs: 32-byte direct stores).  The
-//               op is store bound (1 GiB out vs 8 MiB in at 16384^2 x 64), so
-//               the MMA work hides under the store stream.
+//   contract  : persistent, warp-specialised, one 256 x 128 output block per
+//               step: warp 0 streams packed tiles in with TMA bulk copies (two
+//               A tiles resident per block row, one B tile per step, so every
+//               64 KB B tile read from L2 feeds two output tiles), warp 1
+//               issues tcgen05.mma (2 x 24 MMAs of 128x128x8 at K = 64) into
+//               TMEM (2 buffers x 2 accumulators x 128 columns = all 512
+//               columns), warps 2-17 drain TMEM with tcgen05.ld (a 32-row x
+//               32-column piece per tile each), apply the epilogue and store
+//               straight to HBM in 32-byte pieces.  The op is store bound
+//               (1 GiB out vs 8 MiB in at 16384^2 x 64), so the MMA work hides
+//               under the store stream.
 //   finish    : sqrt epilogue for K > 64, where the dot products are
 //               accumulated over K blocks in gemm mode first.
 //
@@ -36,7 +36,6 @@
 #include "gpu_common.h"
 #include "kernels/bulk_pipe.cuh"
 
-#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdlib>
@@ -49,12 +48,11 @@ namespace {
 constexpr int kTile = 128;         // output tile is kTile x kTile
 constexpr int kMaxK = 64;          // K elements resident per launch
 constexpr int kChunkBytes = 2048;  // one K chunk (4 elements) of a 128-row tile: 16 groups x 128 B
-constexpr int kThreads = 320;      // producer warp, MMA warp, 8 epilogue warps
-constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 576;      // producer warp, MMA warp, 16 epilogue warps
+constexpr int kEpilogueWarps = 16;
 constexpr int kEpilogueWarp0 = 2;
 constexpr uint64_t kWaitCycles = 4000000000ull; // about 2 s
 constexpr int kStageBytes = 65536;  // one operand tile (hi+lo at K = 64) == one 128x128 fp32 output tile
-constexpr int kBoxCols = 32;        // TMA store box: 128 rows x 32 columns (128-byte swizzled rows)
 
 __host__ __device__ inline int padK(int k) { return (k + 7) / 8 * 8; }
 // bytes of one part (hi or lo) of a tile image
@@ -189,16 +187,6 @@ __device__ __forceinline__ void store8(float *p, const float *v) {
                : "memory");
 }
 
-// 2-D TMA store of one 128-row x 32-column box (shared -> global, clipped at
-// the tensor bounds), tracked by the thread's bulk async-group.
-__device__ __forceinline__ void tma_store_box(const CUtensorMap *tmap, int32_t col, int32_t row,
-                                              const void *smem_src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                   reinterpret_cast<uint64_t>(tmap)),
-               "r"(col), "r"(row), "r"(nmb::smem_u32(smem_src))
-               : "memory");
-}
-
 __device__ __forceinline__ float sqrt_approx(float x) {
   float r;
   asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -216,48 +204,49 @@ struct ContractParams {
   int mode;                     // 0: pairwise distance, 1: gemm (alpha, beta)
   float alpha, beta;
   uint32_t *status;
-  int use_tma_store;            // out is 16-byte aligned with 16-byte row pitch: staged TMA stores
   int debug_skip;               // development switch: 1 = skip the global stores
 };
 
+// One work unit is a 256 x 128 output block: two A tiles (resident while the
+// CTA walks a block row) against one B tile, so every 64 KB B tile pulled from
+// L2 feeds two output tiles.
 extern "C" __global__ void __launch_bounds__(kThreads, 1)
-    nmb_contract_tf32x3(const ContractParams p, const __grid_constant__ CUtensorMap out_map) {
+    nmb_contract_tf32x3(const ContractParams p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int pbytes = partBytes(p.kpad);
   const int tile_bytes = 2 * pbytes;
-  unsigned char *smA = smem;
-  unsigned char *smB = smem + kStageBytes; // two stages of kStageBytes
+  unsigned char *smA = smem;                   // two A tiles, tile_bytes apart
+  unsigned char *smB = smem + 2 * kStageBytes; // one B tile
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 3 * kStageBytes);
   uint64_t *a_full = bars + 0, *a_empty = bars + 1;
-  uint64_t *b_full = bars + 2, *b_empty = bars + 4;
-  uint64_t *acc_full = bars + 6, *acc_empty = bars + 8;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 10);
+  uint64_t *b_full = bars + 2, *b_empty = bars + 3;
+  uint64_t *acc_full = bars + 4, *acc_empty = bars + 6; // [2] each
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 8);
   volatile uint32_t *abort_flag = tmem_slot + 1;
-  volatile uint32_t *half_failed = tmem_slot + 2; // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t tiles_m = (p.M + kTile - 1) / kTile, tiles_n = (p.N + kTile - 1) / kTile;
-  const int64_t total = tiles_m * tiles_n;
+  const int64_t blocks_m = (tiles_m + 1) / 2;
+  const int64_t total = blocks_m * tiles_n;
   const int64_t t_begin = total * blockIdx.x / gridDim.x, t_end = total * (blockIdx.x + 1) / gridDim.x;
 
   if (threadIdx.x == 0) {
     nmb::mbar_init(a_full, 1);
     nmb::mbar_init(a_empty, 1);
+    nmb::mbar_init(b_full, 1);
+    nmb::mbar_init(b_empty, 1);
     for (int s = 0; s < 2; ++s) {
-      nmb::mbar_init(&b_full[s], 1);
-      nmb::mbar_init(&b_empty[s], 2); // one arrival per epilogue half
       nmb::mbar_init(&acc_full[s], 1);
       nmb::mbar_init(&acc_empty[s], kEpilogueWarps); // one arrival per epilogue warp
     }
     *abort_flag = 0;
-    half_failed[0] = half_failed[1] = 0;
     nmb::mbar_init_fence();
   }
   if (warp == 1) {
-    // 2 x 128 fp32 accumulator columns
+    // 2 buffers x 2 tiles x 128 fp32 accumulator columns: all of TMEM
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      nmb::smem_u32(tmem_slot)),
-                 "r"(256)
+                 "r"(512)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -276,26 +265,25 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       int64_t cur_i = -1, a_uses = 0;
       for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
-        const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
-        if (i != cur_i) {
+        const int64_t n = t - t_begin, bi = t / tiles_n, j = t % tiles_n;
+        if (bi != cur_i) {
           if (a_uses > 0 && !wait_bounded(a_empty, (uint32_t)((a_uses - 1) & 1))) {
             give_up();
             break;
           }
-          nmb::mbar_expect_tx(a_full, (uint32_t)tile_bytes);
-          nmb::bulk_load(smA, p.packedA + i * (int64_t)tile_bytes, (uint32_t)tile_bytes, a_full);
-          cur_i = i;
+          const int na = (int)(tiles_m - 2 * bi < 2 ? tiles_m - 2 * bi : 2);
+          nmb::mbar_expect_tx(a_full, (uint32_t)(na * tile_bytes));
+          nmb::bulk_load(smA, p.packedA + 2 * bi * (int64_t)tile_bytes, (uint32_t)(na * tile_bytes),
+                         a_full);
+          cur_i = bi;
           ++a_uses;
         }
-        const int s = (int)(n & 1);
-        const int64_t use = n >> 1;
-        if (use > 0 && !wait_bounded(&b_empty[s], (uint32_t)((use - 1) & 1))) {
+        if (n > 0 && !wait_bounded(b_empty, (uint32_t)((n - 1) & 1))) {
           give_up();
           break;
         }
-        nmb::mbar_expect_tx(&b_full[s], (uint32_t)tile_bytes);
-        nmb::bulk_load(smB + s * kStageBytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
-                       &b_full[s]);
+        nmb::mbar_expect_tx(b_full, (uint32_t)tile_bytes);
+        nmb::bulk_load(smB, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes, b_full);
       }
     }
     __syncwarp();
@@ -305,16 +293,16 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
       int64_t cur_i = -1, a_uses = 0;
       const int ksteps = p.kpad / 8;
       for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
-        const int64_t n = t - t_begin, i = t / tiles_n;
+        const int64_t n = t - t_begin, bi = t / tiles_n;
         const int s = (int)(n & 1);
         const int64_t use = n >> 1;
         bool ok = true;
-        if (i != cur_i) {
+        if (bi != cur_i) {
           ok = wait_bounded(a_full, (uint32_t)(a_uses & 1));
-          cur_i = i;
+          cur_i = bi;
           ++a_uses;
         }
-        ok = ok && wait_bounded(&b_full[s], (uint32_t)(use & 1));
+        ok = ok && wait_bounded(b_full, (uint32_t)(n & 1));
         if (ok && use > 0)
           ok = wait_bounded(&acc_empty[s], (uint32_t)((use - 1) & 1));
         if (!ok) {
@@ -322,24 +310,27 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
         tmem_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(s * kTile);
-        const uint32_t a_addr = nmb::smem_u32(smA), b_addr = nmb::smem_u32(smB + s * kStageBytes);
-        uint32_t acc = 0;
+        const int na = (int)(tiles_m - 2 * bi < 2 ? tiles_m - 2 * bi : 2);
+        const uint32_t b_addr = nmb::smem_u32(smB);
+        for (int h = 0; h < na; ++h) {
+          const uint32_t d_tmem = tmem_base + (uint32_t)((s * 2 + h) * kTile);
+          const uint32_t a_addr = nmb::smem_u32(smA + h * tile_bytes);
+          uint32_t acc = 0;
 #pragma unroll 1
-        for (int prod = 0; prod < 3; ++prod) {
-          // hi.hi, hi.lo, lo.hi
-          const uint32_t a_part = a_addr + (prod == 2 ? pbytes : 0);
-          const uint32_t b_part = b_addr + (prod == 1 ? pbytes : 0);
-          for (int ks = 0; ks < ksteps; ++ks) {
-            mma_tf32(d_tmem, smem_desc(a_part + ks * 2 * kChunkBytes),
-                     smem_desc(b_part + ks * 2 * kChunkBytes), acc);
-            acc = 1;
+          for (int prod = 0; prod < 3; ++prod) {
+            // hi.hi, hi.lo, lo.hi
+            const uint32_t a_part = a_addr + (prod == 2 ? pbytes : 0);
+            const uint32_t b_part = b_addr + (prod == 1 ? pbytes : 0);
+            for (int ks = 0; ks < ksteps; ++ks) {
+              mma_tf32(d_tmem, smem_desc(a_part + ks * 2 * kChunkBytes),
+                       smem_desc(b_part + ks * 2 * kChunkBytes), acc);
+              acc = 1;
+            }
           }
         }
-        // accumulator ready; the B stage becomes the epilogue's staging buffer
-        // and is handed back to the producer by the epilogue
-        mma_commit(&acc_full[s]);
-        const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != i);
+        mma_commit(b_empty);       // the B tile may be replaced once these MMAs have read it
+        mma_commit(&acc_full[s]);  // both accumulators of the block are ready
+        const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != bi);
         if (last_of_row)
           mma_commit(a_empty);
       }
@@ -347,75 +338,71 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     __syncwarp();
   } else {
     // ---------------- epilogue: TMEM -> registers -> HBM ----------------
-    // Warp w may read TMEM lanes 32*(w%4)..+31 (its rows of the tile); two
-    // warps share a lane quarter and take one 64-column half each.
+    // Warp w may read TMEM lanes 32*(w%4)..+31 (its rows of a tile); the four
+    // warps of a lane quarter take one 32-column strip each.
+    const int e = warp - kEpilogueWarp0;
     const int q = warp & 3;
-    const int half = (warp - kEpilogueWarp0) >> 2;
+    const int strip = e >> 2;
     const uintptr_t base = reinterpret_cast<uintptr_t>(p.out);
     const bool vec8_ok = (p.ldo % 8 == 0) && ((base & 31) == 0);
     const bool vec4_ok = (p.ldo % 4 == 0) && ((base & 15) == 0);
     for (int64_t t = t_begin; t < t_end; ++t) {
-      const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
+      const int64_t n = t - t_begin, bi = t / tiles_n, j = t % tiles_n;
       const int s = (int)(n & 1);
       const int64_t use = n >> 1;
-      // A warp whose wait ran out still joins the half's barrier below, so the
-      // four warps leave the loop in the same iteration.
-      const bool ok = wait_bounded(&acc_full[s], (uint32_t)(use & 1));
-      if (!ok)
-        half_failed[half] = 1;
+      if (!wait_bounded(&acc_full[s], (uint32_t)(use & 1))) {
+        give_up();
+        break;
+      }
       tmem_fence_after();
-      const int64_t row = i * kTile + q * 32 + lane;
-      const float na = p.mode == 0 ? p.normA[row] : 0.f;
-      float *orow = p.out + row * p.ldo;
-      float v[64];
-      if (ok) {
-        const uint32_t taddr =
-            tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(s * kTile + half * 64);
-        tmem_ld32(taddr, v);
-        tmem_ld32(taddr + 32, v + 32);
-        tmem_ld_wait();
-        // the accumulator buffer is free as soon as it sits in registers
-        tmem_fence_before();
-        __syncwarp();
-        if (lane == 0)
-          nmb::mbar_arrive(&acc_empty[s]);
+      const int na = (int)(tiles_m - 2 * bi < 2 ? tiles_m - 2 * bi : 2);
+      const int64_t col0 = j * kTile + strip * 32;
+      float v[2][32];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        if (h < na)
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) +
+                        (uint32_t)((s * 2 + h) * kTile + strip * 32),
+                    v[h]);
+      tmem_ld_wait();
+      // the accumulators are free as soon as they sit in registers
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        nmb::mbar_arrive(&acc_empty[s]);
+      float4 y[8];
+      if (p.mode == 0) {
+        const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4)
+          y[e4] = __ldg(nb + e4);
       }
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        if (!ok)
-          break;
-        float *w = v + c * 32;
-        const int64_t col0 = j * kTile + half * 64 + c * 32;
+      for (int h = 0; h < 2; ++h) {
+        if (h >= na)
+          continue;
+        float *w = v[h];
+        const int64_t row = (2 * bi + h) * kTile + q * 32 + lane;
+        float *orow = p.out + row * p.ldo;
         if (p.mode == 0) {
-          const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
+          const float xa = p.normA[row];
 #pragma unroll
           for (int e4 = 0; e4 < 8; ++e4) {
-            const float4 y = __ldg(nb + e4);
-            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], na + y.x), 0.f));
-            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], na + y.y), 0.f));
-            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], na + y.z), 0.f));
-            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], na + y.w), 0.f));
+            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + y[e4].x), 0.f));
+            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + y[e4].y), 0.f));
+            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + y[e4].z), 0.f));
+            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + y[e4].w), 0.f));
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            float r = p.alpha * w[e];
-            if (p.beta != 0.f && row < p.M && col0 + e < p.N)
-              r = fmaf(p.beta, orow[col0 + e], r);
-            w[e] = r;
+          for (int k = 0; k < 32; ++k) {
+            float r = p.alpha * w[k];
+            if (p.beta != 0.f && row < p.M && col0 + k < p.N)
+              r = fmaf(p.beta, orow[col0 + k], r);
+            w[k] = r;
           }
         }
-        if (p.use_tma_store) {
-          // box (half*2 + c) of the staging tile: row r at r*128 bytes, its
-          // 16-byte chunk k at position k ^ (r & 7) (the 128-byte swizzle the
-          // tensor map undoes), so the 8 lanes of a store phase hit 8 banks groups
-          unsigned char *box = smB + s * kStageBytes + (half * 2 + c) * (kTile * kBoxCols * 4);
-          const int r = q * 32 + lane;
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            *reinterpret_cast<float4 *>(box + r * 128 + ((k ^ (r & 7)) << 4)) =
-                make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
-        } else if (row < p.M && !p.debug_skip) {
+        if (row < p.M && !p.debug_skip) {
           if (vec8_ok && col0 + 32 <= p.N) {
 #pragma unroll
             for (int e8 = 0; e8 < 4; ++e8)
@@ -427,37 +414,13 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
                      make_float4(w[e4 * 4], w[e4 * 4 + 1], w[e4 * 4 + 2], w[e4 * 4 + 3]));
           } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e)
-              if (col0 + e < p.N)
-                orow[col0 + e] = w[e];
+            for (int k = 0; k < 32; ++k)
+              if (col0 + k < p.N)
+                orow[col0 + k] = w[k];
           }
         }
       }
-      // The four warps of this half meet; one thread then streams the half's
-      // two boxes out with TMA and gives the stage back to the producer once
-      // the copies have read shared memory.
-      if (p.use_tma_store)
-        nmb::fence_async_smem();
-      asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-      if (half_failed[half]) {
-        give_up();
-        break;
-      }
-      if (q == 0 && lane == 0) {
-        if (p.use_tma_store && !p.debug_skip) {
-          const unsigned char *stage = smB + s * kStageBytes;
-#pragma unroll
-          for (int c = 0; c < 2; ++c)
-            tma_store_box(&out_map, (int32_t)(j * kTile + (half * 2 + c) * kBoxCols),
-                          (int32_t)(i * kTile), stage + (half * 2 + c) * (kTile * kBoxCols * 4));
-          nmb::bulk_commit();
-          nmb::bulk_wait_read<0>();
-        }
-        nmb::mbar_arrive(&b_empty[s]);
-      }
     }
-    if (p.use_tma_store && q == 0 && lane == 0)
-      nmb::bulk_wait_all<0>(); // global writes complete before the CTA retires
   }
 
   tmem_fence_before();
@@ -468,7 +431,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   if (warp == 1) {
     tmem_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
                  : "memory");
   }
 }
@@ -490,41 +453,6 @@ struct Operand {
   const float *data; // element (r, k) at data[r * ldr + k * ldk]
   int64_t rows, K, ldr, ldk;
 };
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encodeTiled() {
-  static EncodeTiledFn fn = [] {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult st;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &st) != cudaSuccess ||
-        st != cudaDriverEntryPointSuccess) {
-      (void)cudaGetLastError();
-      p = nullptr;
-    }
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
-// Tensor map of the (M, N) fp32 output for 128-row x 32-column boxes with the
-// 128-byte swizzle; false when the output does not meet the TMA alignment rules.
-bool makeOutMap(float *out, int64_t M, int64_t N, int64_t ldo, CUtensorMap *map) {
-  memset(map, 0, sizeof(*map));
-  if ((reinterpret_cast<uintptr_t>(out) & 15) != 0 || (ldo * 4) % 16 != 0 || !encodeTiled())
-    return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
-  const cuuint64_t strides[1] = {(cuuint64_t)ldo * 4};
-  const cuuint32_t box[2] = {(cuuint32_t)kBoxCols, (cuuint32_t)kTile};
-  const cuuint32_t estr[2] = {1, 1};
-  return encodeTiled()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                       CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 int smCount(int device) {
   static int cached[64] = {0};
@@ -570,8 +498,6 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
 
   static bool attrSet[64] = {false};
   const int smemBytes = 3 * kStageBytes + 128;
-  CUtensorMap outMap;
-  const bool useTma = makeOutMap(out, M, N, ldo, &outMap);
   if (qv.device >= 64 || !attrSet[qv.device]) {
     if (cudaFuncSetAttribute(nmb_contract_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smemBytes) != cudaSuccess) {
@@ -592,7 +518,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     nmb::noteLaunch();
   }
   const bool single = K <= kMaxK;
-  const int64_t total = tiles_m * tiles_n;
+  const int64_t total = ((tiles_m + 1) / 2) * tiles_n; // 256 x 128 blocks
   const int64_t sms = smCount(qv.device);
   const unsigned grid = (unsigned)(total < sms ? total : sms);
   int64_t k0 = 0;
@@ -615,7 +541,6 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     p.ldo = ldo;
     p.kpad = kpad;
     p.status = status;
-    p.use_tma_store = (useTma && !getenv("NMB_DEBUG_NO_TMA_STORE")) ? 1 : 0;
     p.debug_skip = getenv("NMB_DEBUG_SKIP_STORE") ? 1 : 0;
     if (mode == 0 && single) {
       p.mode = 0;
@@ -626,7 +551,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
       p.alpha = mode == 0 ? 1.f : alpha;
       p.beta = first ? (mode == 0 ? 0.f : beta) : 1.f;
     }
-    nmb_contract_tf32x3<<<grid, kThreads, smemBytes, stream>>>(p, outMap);
+    nmb_contract_tf32x3<<<grid, kThreads, smemBytes, stream>>>(p);
     nmb::noteLaunch();
     nmb::noteLaunch();
     nmb::noteLaunch();
