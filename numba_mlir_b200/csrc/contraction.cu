@@ -38,6 +38,7 @@
 
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -187,6 +188,17 @@ __device__ __forceinline__ void store8(float *p, const float *v) {
                : "memory");
 }
 
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define NMB_TRACE(n, k)                                                                          \
+  do {                                                                                           \
+    if (p.trace && blockIdx.x == 0 && (n) < 64)                                                  \
+      p.trace[(n) * 8 + (k)] = gtime();                                                          \
+  } while (0)
+
 __device__ __forceinline__ float sqrt_approx(float x) {
   float r;
   asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
@@ -205,6 +217,7 @@ struct ContractParams {
   float alpha, beta;
   uint32_t *status;
   int debug_skip;               // development switch: 1 = skip the global stores
+  unsigned long long *trace;    // development: per-step timestamps of CTA 0 (or NULL)
 };
 
 // One work unit is a 256 x 128 output block: two A tiles (resident while the
@@ -278,12 +291,14 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           cur_i = bi;
           ++a_uses;
         }
+        NMB_TRACE(n, 0);
         if (n > 0 && !wait_bounded(b_empty, (uint32_t)((n - 1) & 1))) {
           give_up();
           break;
         }
         nmb::mbar_expect_tx(b_full, (uint32_t)tile_bytes);
         nmb::bulk_load(smB, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes, b_full);
+        NMB_TRACE(n, 1);
       }
     }
     __syncwarp();
@@ -303,8 +318,10 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           ++a_uses;
         }
         ok = ok && wait_bounded(b_full, (uint32_t)(n & 1));
+        NMB_TRACE(n, 2);
         if (ok && use > 0)
           ok = wait_bounded(&acc_empty[s], (uint32_t)((use - 1) & 1));
+        NMB_TRACE(n, 3);
         if (!ok) {
           give_up();
           break;
@@ -312,22 +329,32 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         tmem_fence_after();
         const int na = (int)(tiles_m - 2 * bi < 2 ? tiles_m - 2 * bi : 2);
         const uint32_t b_addr = nmb::smem_u32(smB);
+        // Descriptors differ only in the start-address field: one 64-bit add
+        // per K step (2 chunks of 2 KB = 256 units of 16 bytes).
+        constexpr uint64_t kStepUnits = (2 * kChunkBytes) >> 4;
+        const uint64_t b_hi = smem_desc(b_addr), b_lo = smem_desc(b_addr + pbytes);
         for (int h = 0; h < na; ++h) {
           const uint32_t d_tmem = tmem_base + (uint32_t)((s * 2 + h) * kTile);
           const uint32_t a_addr = nmb::smem_u32(smA + h * tile_bytes);
-          uint32_t acc = 0;
-#pragma unroll 1
-          for (int prod = 0; prod < 3; ++prod) {
-            // hi.hi, hi.lo, lo.hi
-            const uint32_t a_part = a_addr + (prod == 2 ? pbytes : 0);
-            const uint32_t b_part = b_addr + (prod == 1 ? pbytes : 0);
-            for (int ks = 0; ks < ksteps; ++ks) {
-              mma_tf32(d_tmem, smem_desc(a_part + ks * 2 * kChunkBytes),
-                       smem_desc(b_part + ks * 2 * kChunkBytes), acc);
-              acc = 1;
-            }
-          }
+          const uint64_t a_hi = smem_desc(a_addr), a_lo = smem_desc(a_addr + pbytes);
+          // hi.hi (overwrites the accumulator on its first step), hi.lo, lo.hi
+          uint64_t da = a_hi, db = b_hi;
+          mma_tf32(d_tmem, da, db, 0);
+#pragma unroll 4
+          for (int ks = 1; ks < ksteps; ++ks)
+            mma_tf32(d_tmem, da += kStepUnits, db += kStepUnits, 1);
+          da = a_hi;
+          db = b_lo;
+#pragma unroll 4
+          for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
+            mma_tf32(d_tmem, da, db, 1);
+          da = a_lo;
+          db = b_hi;
+#pragma unroll 4
+          for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
+            mma_tf32(d_tmem, da, db, 1);
         }
+        NMB_TRACE(n, 4);
         mma_commit(b_empty);       // the B tile may be replaced once these MMAs have read it
         mma_commit(&acc_full[s]);  // both accumulators of the block are ready
         const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != bi);
@@ -355,6 +382,8 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tmem_fence_after();
+      if (e == 0 && lane == 0)
+        NMB_TRACE(n, 5);
       const int na = (int)(tiles_m - 2 * bi < 2 ? tiles_m - 2 * bi : 2);
       const int64_t col0 = j * kTile + strip * 32;
       float v[2][32];
@@ -365,17 +394,30 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
                         (uint32_t)((s * 2 + h) * kTile + strip * 32),
                     v[h]);
       tmem_ld_wait();
+      if (e == 0 && lane == 0)
+        NMB_TRACE(n, 6);
       // the accumulators are free as soon as they sit in registers
       tmem_fence_before();
       __syncwarp();
       if (lane == 0)
         nmb::mbar_arrive(&acc_empty[s]);
-      float4 y[8];
       if (p.mode == 0) {
         const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
+        const float xa0 = p.normA[(2 * bi) * kTile + q * 32 + lane];
+        const float xa1 = p.normA[(2 * bi + (na > 1)) * kTile + q * 32 + lane];
 #pragma unroll
-        for (int e4 = 0; e4 < 8; ++e4)
-          y[e4] = __ldg(nb + e4);
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 y = __ldg(nb + e4);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float *w = v[h] + e4 * 4;
+            const float xa = h ? xa1 : xa0;
+            w[0] = sqrt_approx(fmaxf(fmaf(-2.f, w[0], xa + y.x), 0.f));
+            w[1] = sqrt_approx(fmaxf(fmaf(-2.f, w[1], xa + y.y), 0.f));
+            w[2] = sqrt_approx(fmaxf(fmaf(-2.f, w[2], xa + y.z), 0.f));
+            w[3] = sqrt_approx(fmaxf(fmaf(-2.f, w[3], xa + y.w), 0.f));
+          }
+        }
       }
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -384,16 +426,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         float *w = v[h];
         const int64_t row = (2 * bi + h) * kTile + q * 32 + lane;
         float *orow = p.out + row * p.ldo;
-        if (p.mode == 0) {
-          const float xa = p.normA[row];
-#pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4) {
-            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + y[e4].x), 0.f));
-            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + y[e4].y), 0.f));
-            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + y[e4].z), 0.f));
-            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + y[e4].w), 0.f));
-          }
-        } else {
+        if (p.mode != 0) {
 #pragma unroll
           for (int k = 0; k < 32; ++k) {
             float r = p.alpha * w[k];
@@ -420,6 +453,8 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      if (e == 0 && lane == 0)
+        NMB_TRACE(n, 7);
     }
   }
 
@@ -542,6 +577,13 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     p.kpad = kpad;
     p.status = status;
     p.debug_skip = getenv("NMB_DEBUG_SKIP_STORE") ? 1 : 0;
+    p.trace = nullptr;
+    unsigned long long *traceBuf = nullptr;
+    if (getenv("NMB_DEBUG_TRACE")) {
+      cudaMalloc(&traceBuf, 64 * 8 * 8);
+      cudaMemset(traceBuf, 0, 64 * 8 * 8);
+      p.trace = traceBuf;
+    }
     if (mode == 0 && single) {
       p.mode = 0;
       p.alpha = 1.f;
@@ -552,6 +594,19 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
       p.beta = first ? (mode == 0 ? 0.f : beta) : 1.f;
     }
     nmb_contract_tf32x3<<<grid, kThreads, smemBytes, stream>>>(p);
+    if (traceBuf) {
+      unsigned long long h[64 * 8];
+      cudaStreamSynchronize(stream);
+      cudaMemcpy(h, traceBuf, sizeof(h), cudaMemcpyDeviceToHost);
+      cudaFree(traceBuf);
+      unsigned long long t0 = h[0];
+      for (int n = 0; n < 24; ++n) {
+        fprintf(stderr, "step %2d:", n);
+        for (int k = 0; k < 8; ++k)
+          fprintf(stderr, " %7lld", h[n * 8 + k] ? (long long)(h[n * 8 + k] - t0) : -1ll);
+        fprintf(stderr, "\n");
+      }
+    }
     nmb::noteLaunch();
     nmb::noteLaunch();
     nmb::noteLaunch();

@@ -118,8 +118,8 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
         lcnt[lid] = 0
     barrier()
 
-    jcol = lid % _KM_D
-    cg = lid // _KM_D
+    jcol = lid & (_KM_D - 1)
+    cg = lid >> 4
     a0 = 0.0
     a1 = 0.0
     a2 = 0.0
@@ -147,9 +147,9 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
         barrier()
         for m in range(KMEANS_LOCAL_SIZE):
             b = lbl[m]
-            if b // 4 == cg:
+            if (b >> 2) == cg:
                 v = lp[m, jcol]
-                w = b % 4
+                w = b & 3
                 if w == 0:
                     a0 += v
                 elif w == 1:
