@@ -16,17 +16,16 @@
 //               memory operand layout (K-major, no swizzle: 8-row x 16-byte
 //               core matrices), zero padded, plus the fp32 row norms.  A
 //               whole tile (hi+lo) is then one contiguous TMA bulk copy.
-//   contract  : persistent, warp-specialised, one 256 x 128 output block per
-//               step: warp 0 streams packed tiles in with TMA bulk copies (two
-//               A tiles resident per block row, one B tile per step, so every
-//               64 KB B tile read from L2 feeds two output tiles), warp 1
-//               issues tcgen05.mma (2 x 24 MMAs of 128x128x8 at K = 64) into
-//               TMEM (2 buffers x 2 accumulators x 128 columns = all 512
-//               columns), warps 2-17 drain TMEM with tcgen05.ld (a 32-row x
-//               32-column piece per tile each), apply the epilogue and store
-//               straight to HBM in 32-byte pieces.  The op is store bound
-//               (1 GiB out vs 8 MiB in at 16384^2 x 64), so the MMA work hides
-//               under the store stream.
+//   contract  : persistent, warp-specialised: warp 0 streams packed tiles in
+//               with TMA bulk copies (A resident per row tile, B double
+//               buffered), warp 1 issues tcgen05.mma (24 MMAs of 128x128x8
+//               per output tile at K = 64) into one of four TMEM accumulators
+//               (4 x 128 columns = all of TMEM), warps 2-9 drain TMEM with
+//               tcgen05.ld in 32 x 32 pieces, apply the epilogue and pass each
+//               piece through a private swizzled shared-memory buffer so that
+//               the global stores are whole 128-byte lines.  The op is store
+//               bound (1 GiB out vs 8 MiB in at 16384^2 x 64); the 3xTF32 MMA
+//               work (about 1.3 us per tile) runs under the store stream.
 //   finish    : sqrt epilogue for K > 64, where the dot products are
 //               accumulated over K blocks in gemm mode first.
 //
@@ -49,8 +48,8 @@ namespace {
 constexpr int kTile = 128;         // output tile is kTile x kTile
 constexpr int kMaxK = 64;          // K elements resident per launch
 constexpr int kChunkBytes = 2048;  // one K chunk (4 elements) of a 128-row tile: 16 groups x 128 B
-constexpr int kThreads = 576;      // producer warp, MMA warp, 16 epilogue warps
-constexpr int kEpilogueWarps = 16;
+constexpr int kThreads = 320;      // producer warp, MMA warp, 8 epilogue warps
+constexpr int kEpilogueWarps = 8;
 constexpr int kEpilogueWarp0 = 2;
 constexpr uint64_t kWaitCycles = 4000000000ull; // about 2 s
 constexpr int kStageBytes = 65536;  // one operand tile (hi+lo at K = 64) == one 128x128 fp32 output tile
@@ -220,35 +219,38 @@ struct ContractParams {
   unsigned long long *trace;    // development: per-step timestamps of CTA 0 (or NULL)
 };
 
-// One work unit is a 256 x 128 output block: two A tiles (resident while the
-// CTA walks a block row) against one B tile, so every 64 KB B tile pulled from
-// L2 feeds two output tiles.
+constexpr int kAccBuffers = 4;                  // 4 x 128 fp32 columns: all of TMEM
+constexpr int kStagePitch = 128;                // bytes per staged row (32 floats)
+constexpr int kStagingBytes = 32 * kStagePitch; // one 32 x 32 piece per epilogue warp
+
 extern "C" __global__ void __launch_bounds__(kThreads, 1)
     nmb_contract_tf32x3(const ContractParams p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int pbytes = partBytes(p.kpad);
   const int tile_bytes = 2 * pbytes;
-  unsigned char *smA = smem;                   // two A tiles, tile_bytes apart
-  unsigned char *smB = smem + 2 * kStageBytes; // one B tile
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 3 * kStageBytes);
+  unsigned char *smA = smem;                   // one A tile, resident per tile row
+  unsigned char *smB = smem + kStageBytes;     // two B stages
+  unsigned char *smStage = smem + 3 * kStageBytes; // kEpilogueWarps x 4 KB
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smStage + kEpilogueWarps * kStagingBytes);
   uint64_t *a_full = bars + 0, *a_empty = bars + 1;
-  uint64_t *b_full = bars + 2, *b_empty = bars + 3;
-  uint64_t *acc_full = bars + 4, *acc_empty = bars + 6; // [2] each
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 8);
+  uint64_t *b_full = bars + 2, *b_empty = bars + 4;      // [2] each
+  uint64_t *acc_full = bars + 6, *acc_empty = bars + 10; // [kAccBuffers] each
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t tiles_m = (p.M + kTile - 1) / kTile, tiles_n = (p.N + kTile - 1) / kTile;
-  const int64_t blocks_m = (tiles_m + 1) / 2;
-  const int64_t total = blocks_m * tiles_n;
+  const int64_t total = tiles_m * tiles_n;
   const int64_t t_begin = total * blockIdx.x / gridDim.x, t_end = total * (blockIdx.x + 1) / gridDim.x;
 
   if (threadIdx.x == 0) {
     nmb::mbar_init(a_full, 1);
     nmb::mbar_init(a_empty, 1);
-    nmb::mbar_init(b_full, 1);
-    nmb::mbar_init(b_empty, 1);
     for (int s = 0; s < 2; ++s) {
+      nmb::mbar_init(&b_full[s], 1);
+      nmb::mbar_init(&b_empty[s], 1);
+    }
+    for (int s = 0; s < kAccBuffers; ++s) {
       nmb::mbar_init(&acc_full[s], 1);
       nmb::mbar_init(&acc_empty[s], kEpilogueWarps); // one arrival per epilogue warp
     }
@@ -256,10 +258,9 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     nmb::mbar_init_fence();
   }
   if (warp == 1) {
-    // 2 buffers x 2 tiles x 128 fp32 accumulator columns: all of TMEM
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      nmb::smem_u32(tmem_slot)),
-                 "r"(512)
+                 "r"(kAccBuffers * kTile)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -278,26 +279,27 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       int64_t cur_i = -1, a_uses = 0;
       for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
-        const int64_t n = t - t_begin, bi = t / tiles_n, j = t % tiles_n;
-        if (bi != cur_i) {
+        const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
+        if (i != cur_i) {
           if (a_uses > 0 && !wait_bounded(a_empty, (uint32_t)((a_uses - 1) & 1))) {
             give_up();
             break;
           }
-          const int na = (int)(tiles_m - 2 * bi < 2 ? tiles_m - 2 * bi : 2);
-          nmb::mbar_expect_tx(a_full, (uint32_t)(na * tile_bytes));
-          nmb::bulk_load(smA, p.packedA + 2 * bi * (int64_t)tile_bytes, (uint32_t)(na * tile_bytes),
-                         a_full);
-          cur_i = bi;
+          nmb::mbar_expect_tx(a_full, (uint32_t)tile_bytes);
+          nmb::bulk_load(smA, p.packedA + i * (int64_t)tile_bytes, (uint32_t)tile_bytes, a_full);
+          cur_i = i;
           ++a_uses;
         }
+        const int s = (int)(n & 1);
+        const int64_t use = n >> 1;
         NMB_TRACE(n, 0);
-        if (n > 0 && !wait_bounded(b_empty, (uint32_t)((n - 1) & 1))) {
+        if (use > 0 && !wait_bounded(&b_empty[s], (uint32_t)((use - 1) & 1))) {
           give_up();
           break;
         }
-        nmb::mbar_expect_tx(b_full, (uint32_t)tile_bytes);
-        nmb::bulk_load(smB, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes, b_full);
+        nmb::mbar_expect_tx(&b_full[s], (uint32_t)tile_bytes);
+        nmb::bulk_load(smB + s * kStageBytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
+                       &b_full[s]);
         NMB_TRACE(n, 1);
       }
     }
@@ -307,126 +309,114 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       int64_t cur_i = -1, a_uses = 0;
       const int ksteps = p.kpad / 8;
+      // Descriptors differ only in the start-address field: one 64-bit add
+      // per K step (2 chunks of 2 KB = 256 units of 16 bytes).
+      constexpr uint64_t kStepUnits = (2 * kChunkBytes) >> 4;
+      const uint64_t a_hi = smem_desc(nmb::smem_u32(smA)), a_lo = smem_desc(nmb::smem_u32(smA) + pbytes);
       for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
-        const int64_t n = t - t_begin, bi = t / tiles_n;
+        const int64_t n = t - t_begin, i = t / tiles_n;
         const int s = (int)(n & 1);
-        const int64_t use = n >> 1;
+        const int buf = (int)(n % kAccBuffers);
+        const int64_t buf_use = n / kAccBuffers;
         bool ok = true;
-        if (bi != cur_i) {
+        if (i != cur_i) {
           ok = wait_bounded(a_full, (uint32_t)(a_uses & 1));
-          cur_i = bi;
+          cur_i = i;
           ++a_uses;
         }
-        ok = ok && wait_bounded(b_full, (uint32_t)(n & 1));
+        ok = ok && wait_bounded(&b_full[s], (uint32_t)((n >> 1) & 1));
         NMB_TRACE(n, 2);
-        if (ok && use > 0)
-          ok = wait_bounded(&acc_empty[s], (uint32_t)((use - 1) & 1));
+        if (ok && buf_use > 0)
+          ok = wait_bounded(&acc_empty[buf], (uint32_t)((buf_use - 1) & 1));
         NMB_TRACE(n, 3);
         if (!ok) {
           give_up();
           break;
         }
         tmem_fence_after();
-        const int na = (int)(tiles_m - 2 * bi < 2 ? tiles_m - 2 * bi : 2);
-        const uint32_t b_addr = nmb::smem_u32(smB);
-        // Descriptors differ only in the start-address field: one 64-bit add
-        // per K step (2 chunks of 2 KB = 256 units of 16 bytes).
-        constexpr uint64_t kStepUnits = (2 * kChunkBytes) >> 4;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTile);
+        const uint32_t b_addr = nmb::smem_u32(smB + s * kStageBytes);
         const uint64_t b_hi = smem_desc(b_addr), b_lo = smem_desc(b_addr + pbytes);
-        for (int h = 0; h < na; ++h) {
-          const uint32_t d_tmem = tmem_base + (uint32_t)((s * 2 + h) * kTile);
-          const uint32_t a_addr = nmb::smem_u32(smA + h * tile_bytes);
-          const uint64_t a_hi = smem_desc(a_addr), a_lo = smem_desc(a_addr + pbytes);
-          // hi.hi (overwrites the accumulator on its first step), hi.lo, lo.hi
-          uint64_t da = a_hi, db = b_hi;
-          mma_tf32(d_tmem, da, db, 0);
+        // hi.hi (overwrites the accumulator on its first step), hi.lo, lo.hi
+        uint64_t da = a_hi, db = b_hi;
+        mma_tf32(d_tmem, da, db, 0);
 #pragma unroll 4
-          for (int ks = 1; ks < ksteps; ++ks)
-            mma_tf32(d_tmem, da += kStepUnits, db += kStepUnits, 1);
-          da = a_hi;
-          db = b_lo;
+        for (int ks = 1; ks < ksteps; ++ks)
+          mma_tf32(d_tmem, da += kStepUnits, db += kStepUnits, 1);
+        da = a_hi;
+        db = b_lo;
 #pragma unroll 4
-          for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
-            mma_tf32(d_tmem, da, db, 1);
-          da = a_lo;
-          db = b_hi;
+        for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
+          mma_tf32(d_tmem, da, db, 1);
+        da = a_lo;
+        db = b_hi;
 #pragma unroll 4
-          for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
-            mma_tf32(d_tmem, da, db, 1);
-        }
+        for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
+          mma_tf32(d_tmem, da, db, 1);
         NMB_TRACE(n, 4);
-        mma_commit(b_empty);       // the B tile may be replaced once these MMAs have read it
-        mma_commit(&acc_full[s]);  // both accumulators of the block are ready
-        const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != bi);
+        mma_commit(&b_empty[s]);     // B stage reusable once these MMAs have read it
+        mma_commit(&acc_full[buf]);  // accumulator ready for the epilogue
+        const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != i);
         if (last_of_row)
           mma_commit(a_empty);
       }
     }
     __syncwarp();
   } else {
-    // ---------------- epilogue: TMEM -> registers -> HBM ----------------
-    // Warp w may read TMEM lanes 32*(w%4)..+31 (its rows of a tile); the four
-    // warps of a lane quarter take one 32-column strip each.
+    // ---------------- epilogue: TMEM -> registers -> shared -> HBM ----------------
+    // Warp w may read TMEM lanes 32*(w%4)..+31 (32 rows of the tile); the two
+    // warps of a lane quarter take 64 columns each, as two 32 x 32 pieces.  A
+    // piece goes through the warp's private 4 KB staging buffer (16-byte chunk
+    // k of row r at position k ^ (r & 7): conflict-free both ways) so that the
+    // global stores are whole 128-byte lines, four rows per instruction.
     const int e = warp - kEpilogueWarp0;
     const int q = warp & 3;
-    const int strip = e >> 2;
-    const uintptr_t base = reinterpret_cast<uintptr_t>(p.out);
-    const bool vec8_ok = (p.ldo % 8 == 0) && ((base & 31) == 0);
-    const bool vec4_ok = (p.ldo % 4 == 0) && ((base & 15) == 0);
+    const int half = e >> 2;
+    unsigned char *stage = smStage + e * kStagingBytes;
+    const bool vec4_ok = (p.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
+    const int srow = lane >> 3, schunk = lane & 7; // this lane's part of a 4-row store
     for (int64_t t = t_begin; t < t_end; ++t) {
-      const int64_t n = t - t_begin, bi = t / tiles_n, j = t % tiles_n;
-      const int s = (int)(n & 1);
-      const int64_t use = n >> 1;
-      if (!wait_bounded(&acc_full[s], (uint32_t)(use & 1))) {
+      const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
+      const int buf = (int)(n % kAccBuffers);
+      const int64_t buf_use = n / kAccBuffers;
+      if (!wait_bounded(&acc_full[buf], (uint32_t)(buf_use & 1))) {
         give_up();
         break;
       }
       tmem_fence_after();
       if (e == 0 && lane == 0)
         NMB_TRACE(n, 5);
-      const int na = (int)(tiles_m - 2 * bi < 2 ? tiles_m - 2 * bi : 2);
-      const int64_t col0 = j * kTile + strip * 32;
       float v[2][32];
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-        if (h < na)
-          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) +
-                        (uint32_t)((s * 2 + h) * kTile + strip * 32),
-                    v[h]);
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTile + half * 64);
+      tmem_ld32(taddr, v[0]);
+      tmem_ld32(taddr + 32, v[1]);
       tmem_ld_wait();
       if (e == 0 && lane == 0)
         NMB_TRACE(n, 6);
-      // the accumulators are free as soon as they sit in registers
+      // the accumulator is free as soon as it sits in registers
       tmem_fence_before();
       __syncwarp();
       if (lane == 0)
-        nmb::mbar_arrive(&acc_empty[s]);
-      if (p.mode == 0) {
-        const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
-        const float xa0 = p.normA[(2 * bi) * kTile + q * 32 + lane];
-        const float xa1 = p.normA[(2 * bi + (na > 1)) * kTile + q * 32 + lane];
+        nmb::mbar_arrive(&acc_empty[buf]);
+      const int64_t row0 = i * kTile + q * 32; // first row of this warp's pieces
+      const int64_t row = row0 + lane;
+      const float xa = p.mode == 0 ? p.normA[row] : 0.f;
 #pragma unroll
-        for (int e4 = 0; e4 < 8; ++e4) {
-          const float4 y = __ldg(nb + e4);
+      for (int c = 0; c < 2; ++c) {
+        float *w = v[c];
+        const int64_t col0 = j * kTile + half * 64 + c * 32;
+        if (p.mode == 0) {
+          const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            float *w = v[h] + e4 * 4;
-            const float xa = h ? xa1 : xa0;
-            w[0] = sqrt_approx(fmaxf(fmaf(-2.f, w[0], xa + y.x), 0.f));
-            w[1] = sqrt_approx(fmaxf(fmaf(-2.f, w[1], xa + y.y), 0.f));
-            w[2] = sqrt_approx(fmaxf(fmaf(-2.f, w[2], xa + y.z), 0.f));
-            w[3] = sqrt_approx(fmaxf(fmaf(-2.f, w[3], xa + y.w), 0.f));
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 y = __ldg(nb + e4);
+            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + y.x), 0.f));
+            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + y.y), 0.f));
+            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + y.z), 0.f));
+            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + y.w), 0.f));
           }
-        }
-      }
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (h >= na)
-          continue;
-        float *w = v[h];
-        const int64_t row = (2 * bi + h) * kTile + q * 32 + lane;
-        float *orow = p.out + row * p.ldo;
-        if (p.mode != 0) {
+        } else {
+          const float *orow = p.out + row * p.ldo;
 #pragma unroll
           for (int k = 0; k < 32; ++k) {
             float r = p.alpha * w[k];
@@ -435,22 +425,31 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
             w[k] = r;
           }
         }
-        if (row < p.M && !p.debug_skip) {
-          if (vec8_ok && col0 + 32 <= p.N) {
+        if (p.debug_skip)
+          continue;
+        if (vec4_ok && col0 + 32 <= p.N) {
+          // registers (lane = row) -> staging
 #pragma unroll
-            for (int e8 = 0; e8 < 4; ++e8)
-              store8(orow + col0 + e8 * 8, w + e8 * 8);
-          } else if (vec4_ok && col0 + 32 <= p.N) {
+          for (int k = 0; k < 8; ++k)
+            *reinterpret_cast<float4 *>(stage + lane * kStagePitch + ((k ^ (lane & 7)) << 4)) =
+                make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
+          __syncwarp();
+          // staging -> HBM: per instruction four rows of 128 contiguous bytes
 #pragma unroll
-            for (int e4 = 0; e4 < 8; ++e4)
-              __stcs(reinterpret_cast<float4 *>(orow + col0) + e4,
-                     make_float4(w[e4 * 4], w[e4 * 4 + 1], w[e4 * 4 + 2], w[e4 * 4 + 3]));
-          } else {
-#pragma unroll
-            for (int k = 0; k < 32; ++k)
-              if (col0 + k < p.N)
-                orow[col0 + k] = w[k];
+          for (int r4 = 0; r4 < 8; ++r4) {
+            const int r = r4 * 4 + srow;
+            const float4 x =
+                *reinterpret_cast<const float4 *>(stage + r * kStagePitch + ((schunk ^ (r & 7)) << 4));
+            if (row0 + r < p.M)
+              __stcs(reinterpret_cast<float4 *>(p.out + (row0 + r) * p.ldo + col0) + schunk, x);
           }
+          __syncwarp();
+        } else if (row < p.M) {
+          float *orow = p.out + row * p.ldo;
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            if (col0 + k < p.N)
+              orow[col0 + k] = w[k];
         }
       }
       if (e == 0 && lane == 0)
@@ -466,7 +465,8 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   if (warp == 1) {
     tmem_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(kAccBuffers * kTile)
                  : "memory");
   }
 }
@@ -532,7 +532,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     return false;
 
   static bool attrSet[64] = {false};
-  const int smemBytes = 3 * kStageBytes + 128;
+  const int smemBytes = 3 * kStageBytes + kEpilogueWarps * 4096 + 128;
   if (qv.device >= 64 || !attrSet[qv.device]) {
     if (cudaFuncSetAttribute(nmb_contract_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smemBytes) != cudaSuccess) {
@@ -553,7 +553,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     nmb::noteLaunch();
   }
   const bool single = K <= kMaxK;
-  const int64_t total = ((tiles_m + 1) / 2) * tiles_n; // 256 x 128 blocks
+  const int64_t total = tiles_m * tiles_n;
   const int64_t sms = smCount(qv.device);
   const unsigned grid = (unsigned)(total < sms ? total : sms);
   int64_t k0 = 0;
