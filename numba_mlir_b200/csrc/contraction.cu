@@ -20,7 +20,7 @@
 //               with TMA bulk copies (A resident per row tile, B double
 //               buffered), warp 1 issues tcgen05.mma (24 MMAs of 128x128x8
 //               per output tile at K = 64) into one of four TMEM accumulators
-//               (4 x 128 columns = all of TMEM), warps 2-9 drain TMEM with
+//               (4 x 128 columns = all of TMEM), warps 2-17 drain TMEM with
 //               tcgen05.ld in 32 x 32 pieces, apply the epilogue and pass each
 //               piece through a private swizzled shared-memory buffer so that
 //               the global stores are whole 128-byte lines.  The op is store
@@ -48,8 +48,8 @@ namespace {
 constexpr int kTile = 128;         // output tile is kTile x kTile
 constexpr int kMaxK = 64;          // K elements resident per launch
 constexpr int kChunkBytes = 2048;  // one K chunk (4 elements) of a 128-row tile: 16 groups x 128 B
-constexpr int kThreads = 320;      // producer warp, MMA warp, 8 epilogue warps
-constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 576;      // producer warp, MMA warp, 16 epilogue warps
+constexpr int kEpilogueWarps = 16;
 constexpr int kEpilogueWarp0 = 2;
 constexpr uint64_t kWaitCycles = 4000000000ull; // about 2 s
 constexpr int kStageBytes = 65536;  // one operand tile (hi+lo at K = 64) == one 128x128 fp32 output tile
@@ -200,7 +200,7 @@ __device__ __forceinline__ unsigned long long gtime() {
 
 __device__ __forceinline__ float sqrt_approx(float x) {
   float r;
-  asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
 
@@ -221,7 +221,7 @@ struct ContractParams {
 
 constexpr int kAccBuffers = 4;                  // 4 x 128 fp32 columns: all of TMEM
 constexpr int kStagePitch = 128;                // bytes per staged row (32 floats)
-constexpr int kStagingBytes = 32 * kStagePitch; // one 32 x 32 piece per epilogue warp
+constexpr int kStagingBytes = 16 * kStagePitch; // half a 32 x 32 piece per epilogue warp
 
 extern "C" __global__ void __launch_bounds__(kThreads, 1)
     nmb_contract_tf32x3(const ContractParams p) {
@@ -230,7 +230,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
   const int tile_bytes = 2 * pbytes;
   unsigned char *smA = smem;                   // one A tile, resident per tile row
   unsigned char *smB = smem + kStageBytes;     // two B stages
-  unsigned char *smStage = smem + 3 * kStageBytes; // kEpilogueWarps x 4 KB
+  unsigned char *smStage = smem + 3 * kStageBytes; // kEpilogueWarps x 2 KB
   uint64_t *bars = reinterpret_cast<uint64_t *>(smStage + kEpilogueWarps * kStagingBytes);
   uint64_t *a_full = bars + 0, *a_empty = bars + 1;
   uint64_t *b_full = bars + 2, *b_empty = bars + 4;      // [2] each
@@ -364,21 +364,41 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     __syncwarp();
   } else {
     // ---------------- epilogue: TMEM -> registers -> shared -> HBM ----------------
-    // Warp w may read TMEM lanes 32*(w%4)..+31 (32 rows of the tile); the two
-    // warps of a lane quarter take 64 columns each, as two 32 x 32 pieces.  A
-    // piece goes through the warp's private 4 KB staging buffer (16-byte chunk
-    // k of row r at position k ^ (r & 7): conflict-free both ways) so that the
-    // global stores are whole 128-byte lines, four rows per instruction.
+    // Warp w may read TMEM lanes 32*(w%4)..+31 (32 rows of the tile); the four
+    // warps of a lane quarter take one 32-column strip each, i.e. every warp
+    // owns one 32 x 32 piece of every tile (16 warps keep enough instruction
+    // streams in flight to hide the latencies of the short dependent chains).
+    // A piece goes to HBM through the warp's private 2 KB staging buffer, 16
+    // rows at a time (16-byte chunk k of row r at position k ^ (r & 7):
+    // conflict-free both ways), so that the global stores are whole 128-byte
+    // lines, four rows per instruction.
     const int e = warp - kEpilogueWarp0;
     const int q = warp & 3;
-    const int half = e >> 2;
+    const int strip = e >> 2;
     unsigned char *stage = smStage + e * kStagingBytes;
     const bool vec4_ok = (p.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
     const int srow = lane >> 3, schunk = lane & 7; // this lane's part of a 4-row store
+    int64_t xa_row = -1;
+    float xa = 0.f;
     for (int64_t t = t_begin; t < t_end; ++t) {
       const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
       const int buf = (int)(n % kAccBuffers);
       const int64_t buf_use = n / kAccBuffers;
+      const int64_t row0 = i * kTile + q * 32; // first row of this warp's piece
+      const int64_t row = row0 + lane;
+      const int64_t col0 = j * kTile + strip * 32;
+      // norms first: their latency overlaps the wait for the accumulator
+      float4 y[8];
+      if (p.mode == 0) {
+        const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4)
+          y[e4] = __ldg(nb + e4);
+        if (row != xa_row) {
+          xa = p.normA[row];
+          xa_row = row;
+        }
+      }
       if (!wait_bounded(&acc_full[buf], (uint32_t)(buf_use & 1))) {
         give_up();
         break;
@@ -386,10 +406,8 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
       tmem_fence_after();
       if (e == 0 && lane == 0)
         NMB_TRACE(n, 5);
-      float v[2][32];
-      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTile + half * 64);
-      tmem_ld32(taddr, v[0]);
-      tmem_ld32(taddr + 32, v[1]);
+      float w[32];
+      tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTile + strip * 32), w);
       tmem_ld_wait();
       if (e == 0 && lane == 0)
         NMB_TRACE(n, 6);
@@ -398,52 +416,49 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
       __syncwarp();
       if (lane == 0)
         nmb::mbar_arrive(&acc_empty[buf]);
-      const int64_t row0 = i * kTile + q * 32; // first row of this warp's pieces
-      const int64_t row = row0 + lane;
-      const float xa = p.mode == 0 ? p.normA[row] : 0.f;
+      if (p.mode == 0) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        float *w = v[c];
-        const int64_t col0 = j * kTile + half * 64 + c * 32;
-        if (p.mode == 0) {
-          const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
-#pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4) {
-            const float4 y = __ldg(nb + e4);
-            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + y.x), 0.f));
-            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + y.y), 0.f));
-            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + y.z), 0.f));
-            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + y.w), 0.f));
-          }
-        } else {
-          const float *orow = p.out + row * p.ldo;
-#pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            float r = p.alpha * w[k];
-            if (p.beta != 0.f && row < p.M && col0 + k < p.N)
-              r = fmaf(p.beta, orow[col0 + k], r);
-            w[k] = r;
-          }
+        for (int e4 = 0; e4 < 8; ++e4) {
+          w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + y[e4].x), 0.f));
+          w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + y[e4].y), 0.f));
+          w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + y[e4].z), 0.f));
+          w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + y[e4].w), 0.f));
         }
-        if (p.debug_skip)
-          continue;
+      } else {
+        const float *orow = p.out + row * p.ldo;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          float r = p.alpha * w[k];
+          if (p.beta != 0.f && row < p.M && col0 + k < p.N)
+            r = fmaf(p.beta, orow[col0 + k], r);
+          w[k] = r;
+        }
+      }
+      if (!p.debug_skip) {
         if (vec4_ok && col0 + 32 <= p.N) {
-          // registers (lane = row) -> staging
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            *reinterpret_cast<float4 *>(stage + lane * kStagePitch + ((k ^ (lane & 7)) << 4)) =
-                make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
-          __syncwarp();
-          // staging -> HBM: per instruction four rows of 128 contiguous bytes
+          for (int hh = 0; hh < 2; ++hh) {
+            // registers (lane = row) -> staging, 16 rows per pass
+            if ((lane >> 4) == hh) {
+              const int r = lane & 15;
 #pragma unroll
-          for (int r4 = 0; r4 < 8; ++r4) {
-            const int r = r4 * 4 + srow;
-            const float4 x =
-                *reinterpret_cast<const float4 *>(stage + r * kStagePitch + ((schunk ^ (r & 7)) << 4));
-            if (row0 + r < p.M)
-              __stcs(reinterpret_cast<float4 *>(p.out + (row0 + r) * p.ldo + col0) + schunk, x);
+              for (int k = 0; k < 8; ++k)
+                *reinterpret_cast<float4 *>(stage + r * kStagePitch + ((k ^ (r & 7)) << 4)) =
+                    make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
+            }
+            __syncwarp();
+            // staging -> HBM: per instruction four rows of 128 contiguous bytes
+#pragma unroll
+            for (int r4 = 0; r4 < 4; ++r4) {
+              const int r = r4 * 4 + srow;
+              const float4 x = *reinterpret_cast<const float4 *>(stage + r * kStagePitch +
+                                                                 ((schunk ^ (r & 7)) << 4));
+              const int64_t grow = row0 + hh * 16 + r;
+              if (grow < p.M)
+                __stcs(reinterpret_cast<float4 *>(p.out + grow * p.ldo + col0) + schunk, x);
+            }
+            __syncwarp();
           }
-          __syncwarp();
         } else if (row < p.M) {
           float *orow = p.out + row * p.ldo;
 #pragma unroll
@@ -532,7 +547,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     return false;
 
   static bool attrSet[64] = {false};
-  const int smemBytes = 3 * kStageBytes + kEpilogueWarps * 4096 + 128;
+  const int smemBytes = 3 * kStageBytes + kEpilogueWarps * kStagingBytes + 256;
   if (qv.device >= 64 || !attrSet[qv.device]) {
     if (cudaFuncSetAttribute(nmb_contract_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smemBytes) != cudaSuccess) {
