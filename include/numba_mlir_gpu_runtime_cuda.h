@@ -190,6 +190,20 @@ void *_mlir_ciface_nmb_pairwise_distance_float32_device(void *queue,
                                                         const GPUXMemref2f *y,
                                                         GPUXMemref2f *d);
 
+/* No counterpart in the reference.  *out = sum of data[0..n) accumulated in
+ * int64, like the full integer reduction above, for callers that must not
+ * allocate: a host callback inside a stream, a thread that may not take the
+ * allocator's locks, a process whose memory was all handed out at start-up.
+ * The kernel's scratch lives in an 8 KB array inside the library image (held
+ * by every GPU that loads the library until exit), so the call allocates
+ * nothing on host or device; it runs asynchronously on the queue's stream.
+ * data must be 16-byte aligned, 1 <= n <= 2^32; anything else is refused with
+ * an error (non-zero return, gpuxGetLastError).  All calls on a device share
+ * the array: calls that overlap on the GPU race, so keep them on one stream.
+ * The first call on each device also resolves the array's device address;
+ * make it before any stream capture. */
+int gpuxSumInt32NoAlloc(void *queue, const int32_t *data, size_t n, int64_t *out);
+
 #ifdef __cplusplus
 }
 #endif

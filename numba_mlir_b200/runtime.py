@@ -90,6 +90,7 @@ SIGNATURES = {
     "gpuxCompileToCubin": (_vp, [_vp, _sz, ctypes.POINTER(_sz)]),
     "gpuxFreeHostBlob": (None, [_vp]),
     "gpuxBuiltinKernelNames": (_cp, []),
+    "gpuxSumInt32NoAlloc": (_i, [_vp, _vp, _sz, _vp]),
     "_mlir_ciface_nmb_pairwise_distance_float32_device": (
         _vp,
         [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f)],
