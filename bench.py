@@ -196,11 +196,9 @@ class AxisReduction(Workload):
         self.fn(self.a, self.out)
         if self.dist is not None:
             # rows are sharded: the per-GPU column minima meet in one all-reduce
-            import torch
+            from numba_mlir_b200 import sharding
 
-            t = torch.as_tensor(self.out, device="cuda")
-            self.a.queue.synchronize()
-            self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+            sharding.allreduce(self.out, "min", self.dist)
 
 
 class IntSum(Workload):
@@ -226,11 +224,9 @@ class IntSum(Workload):
     def step_device(self):
         self.fn(self.a, self.out)
         if self.dist is not None:
-            import torch
+            from numba_mlir_b200 import sharding
 
-            t = torch.as_tensor(self.out, device="cuda")
-            self.a.queue.synchronize()
-            self.dist.all_reduce(t)
+            sharding.allreduce(self.out, "sum", self.dist)
 
 
 class Pairwise(Workload):
@@ -292,11 +288,10 @@ class KMeans(Workload):
         q.memset(self.counts.ptr, 0, self.counts.nbytes)
         workloads.kmeans_step(self.pts, self.cent, self.labels, self.sums, self.counts)
         if self.dist is not None:
-            import torch
+            from numba_mlir_b200 import sharding
 
-            q.synchronize()
-            self.dist.all_reduce(torch.as_tensor(self.sums, device="cuda"))
-            self.dist.all_reduce(torch.as_tensor(self.counts, device="cuda"))
+            sharding.allreduce(self.sums, "sum", self.dist)
+            sharding.allreduce(self.counts, "sum", self.dist)
         workloads.kmeans_update(self.cent, self.sums, self.counts)
 
 
