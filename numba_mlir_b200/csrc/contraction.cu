@@ -204,6 +204,15 @@ __device__ __forceinline__ float sqrt_approx(float x) {
   return r;
 }
 
+// One operand tile as several bulk copies on the same mbarrier: more requests
+// in flight than a single 64 KB copy gives.
+__device__ __forceinline__ void load_split(unsigned char *dst, const unsigned char *src, uint32_t bytes,
+                                           uint64_t *bar) {
+  constexpr uint32_t kPiece = 8192;
+  for (uint32_t off = 0; off < bytes; off += kPiece)
+    nmb::bulk_load(dst + off, src + off, bytes - off < kPiece ? bytes - off : kPiece, bar);
+}
+
 struct ContractParams {
   const unsigned char *packedA; // [tiles_m][hi | lo]
   const unsigned char *packedB; // [tiles_n][hi | lo]
@@ -286,7 +295,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           nmb::mbar_expect_tx(a_full, (uint32_t)tile_bytes);
-          nmb::bulk_load(smA, p.packedA + i * (int64_t)tile_bytes, (uint32_t)tile_bytes, a_full);
+          load_split(smA, p.packedA + i * (int64_t)tile_bytes, (uint32_t)tile_bytes, a_full);
           cur_i = i;
           ++a_uses;
         }
@@ -298,8 +307,8 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
         nmb::mbar_expect_tx(&b_full[s], (uint32_t)tile_bytes);
-        nmb::bulk_load(smB + s * kStageBytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
-                       &b_full[s]);
+        load_split(smB + s * kStageBytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
+                   &b_full[s]);
         NMB_TRACE(n, 1);
       }
     }

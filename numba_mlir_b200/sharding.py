@@ -36,8 +36,8 @@ def allreduce(partial, op="sum", dist=None):
 
     `dist` is an initialised torch.distributed module (or None / world 1: the
     partial already is the result).  A DeviceArray is shared with torch through
-    __cuda_array_interface__; the caller's queue is synchronised first because
-    the collective runs on torch's stream."""
+    __cuda_array_interface__ and the collective is enqueued on the array's own
+    queue (stream)."""
     if op not in _REDUCE_OPS:
         raise ValueError(f"unsupported reduction {op}")
     if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
@@ -49,11 +49,28 @@ def allreduce(partial, op="sum", dist=None):
         t = torch.from_numpy(partial)
         dist.all_reduce(t, op=rop)
         return partial
-    partial.queue.synchronize()
-    t = torch.as_tensor(partial, device="cuda")
-    dist.all_reduce(t, op=rop)
-    torch.cuda.current_stream().synchronize()
+    # Run the collective in stream order behind the kernels that produced the
+    # partial: torch adopts the queue's stream for the duration of the call, so
+    # no host synchronisation is needed on either side.
+    stream = _external_stream(partial.queue)
+    with torch.cuda.stream(stream):
+        t = torch.as_tensor(partial, device=f"cuda:{partial.queue.device}")
+        dist.all_reduce(t, op=rop)
     return partial
+
+
+_streams = {}
+
+
+def _external_stream(queue):
+    import torch
+
+    key = (queue.device, int(queue.stream))
+    s = _streams.get(key)
+    if s is None:
+        s = torch.cuda.ExternalStream(int(queue.stream), device=f"cuda:{queue.device}")
+        _streams[key] = s
+    return s
 
 
 def offset_argmin(local_index, begin):
