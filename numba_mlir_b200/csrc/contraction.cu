@@ -19,13 +19,14 @@
 //   contract  : persistent, warp-specialised: warp 0 streams packed tiles in
 //               with TMA bulk copies (A resident per row tile, B double
 //               buffered), warp 1 issues tcgen05.mma (24 MMAs of 128x128x8
-//               per output tile at K = 64) into one of four TMEM accumulators
-//               (4 x 128 columns = all of TMEM), warps 2-17 drain TMEM with
-//               tcgen05.ld in 32 x 32 pieces, apply the epilogue and pass each
-//               piece through a private swizzled shared-memory buffer so that
-//               the global stores are whole 128-byte lines.  The op is store
-//               bound (1 GiB out vs 8 MiB in at 16384^2 x 64); the 3xTF32 MMA
-//               work (about 1.3 us per tile) runs under the store stream.
+//               per output tile at K = 64, one elected lane of a converged
+//               warp) into one of four TMEM accumulators (4 x 128 columns =
+//               all of TMEM), warps 2-17 drain TMEM with tcgen05.ld in
+//               32 x 32 pieces, apply the epilogue and hand each piece, 8 rows
+//               at a time, to asynchronous TMA tensor stores out of private
+//               swizzled staging buffers.  The op is store bound (1 GiB out
+//               vs 8 MiB in at 16384^2 x 64); the 3xTF32 MMA work (about
+//               0.8 us per tile) runs under the store stream.
 //   finish    : sqrt epilogue for K > 64, where the dot products are
 //               accumulated over K blocks in gemm mode first.
 //
@@ -35,6 +36,7 @@
 #include "gpu_common.h"
 #include "kernels/bulk_pipe.cuh"
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -180,23 +182,23 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// 32-byte streaming store (one full sector per thread).
-__device__ __forceinline__ void store8(float *p, const float *v) {
-  asm volatile("st.global.L1::no_allocate.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p),
-               "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7])
-               : "memory");
+// Exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(pred));
+  return pred != 0;
 }
 
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
+// Shared -> global tiled TMA store of one box at element coordinates (x, y);
+// x * 4 bytes must be a multiple of 16.
+__device__ __forceinline__ void tma_store_box(const CUtensorMap *map, const void *src_smem, int x,
+                                              int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   map),
+               "r"(nmb::smem_u32(src_smem)), "r"(x), "r"(y)
+               : "memory");
 }
-#define NMB_TRACE(n, k)                                                                          \
-  do {                                                                                           \
-    if (p.trace && blockIdx.x == 0 && (n) < 64)                                                  \
-      p.trace[(n) * 8 + (k)] = gtime();                                                          \
-  } while (0)
 
 __device__ __forceinline__ float sqrt_approx(float x) {
   float r;
@@ -224,16 +226,17 @@ struct ContractParams {
   int mode;                     // 0: pairwise distance, 1: gemm (alpha, beta)
   float alpha, beta;
   uint32_t *status;
-  int debug_skip;               // development switch: 1 = skip the global stores
-  unsigned long long *trace;    // development: per-step timestamps of CTA 0 (or NULL)
+  int tma_out;                  // 1: out_map is valid, results leave through TMA stores
 };
 
 constexpr int kAccBuffers = 4;                  // 4 x 128 fp32 columns: all of TMEM
 constexpr int kStagePitch = 128;                // bytes per staged row (32 floats)
-constexpr int kStagingBytes = 16 * kStagePitch; // half a 32 x 32 piece per epilogue warp
+constexpr int kStoreRows = 8;                   // rows per TMA store box
+constexpr int kStoreBufBytes = kStoreRows * kStagePitch;
+constexpr int kStagingBytes = 2 * kStoreBufBytes; // two store buffers per epilogue warp
 
 extern "C" __global__ void __launch_bounds__(kThreads, 1)
-    nmb_contract_tf32x3(const ContractParams p) {
+    nmb_contract_tf32x3(const ContractParams p, const __grid_constant__ CUtensorMap out_map) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int pbytes = partBytes(p.kpad);
   const int tile_bytes = 2 * pbytes;
@@ -301,7 +304,6 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         }
         const int s = (int)(n & 1);
         const int64_t use = n >> 1;
-        NMB_TRACE(n, 0);
         if (use > 0 && !wait_bounded(&b_empty[s], (uint32_t)((use - 1) & 1))) {
           give_up();
           break;
@@ -309,40 +311,45 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         nmb::mbar_expect_tx(&b_full[s], (uint32_t)tile_bytes);
         load_split(smB + s * kStageBytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
                    &b_full[s]);
-        NMB_TRACE(n, 1);
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      int64_t cur_i = -1, a_uses = 0;
-      const int ksteps = p.kpad / 8;
-      // Descriptors differ only in the start-address field: one 64-bit add
-      // per K step (2 chunks of 2 KB = 256 units of 16 bytes).
-      constexpr uint64_t kStepUnits = (2 * kChunkBytes) >> 4;
-      const uint64_t a_hi = smem_desc(nmb::smem_u32(smA)), a_lo = smem_desc(nmb::smem_u32(smA) + pbytes);
-      for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
-        const int64_t n = t - t_begin, i = t / tiles_n;
-        const int s = (int)(n & 1);
-        const int buf = (int)(n % kAccBuffers);
-        const int64_t buf_use = n / kAccBuffers;
-        bool ok = true;
-        if (i != cur_i) {
-          ok = wait_bounded(a_full, (uint32_t)(a_uses & 1));
-          cur_i = i;
-          ++a_uses;
-        }
-        ok = ok && wait_bounded(&b_full[s], (uint32_t)((n >> 1) & 1));
-        NMB_TRACE(n, 2);
-        if (ok && buf_use > 0)
-          ok = wait_bounded(&acc_empty[buf], (uint32_t)((buf_use - 1) & 1));
-        NMB_TRACE(n, 3);
-        if (!ok) {
+    // The whole warp runs the loop and the waits in lockstep and one elected
+    // lane issues: MMAs issued from a divergent single-lane branch went out
+    // at half the rate.
+    int64_t cur_i = -1, a_uses = 0;
+    const int ksteps = p.kpad / 8;
+    // Descriptors differ only in the start-address field: one 64-bit add
+    // per K step (2 chunks of 2 KB = 256 units of 16 bytes).
+    constexpr uint64_t kStepUnits = (2 * kChunkBytes) >> 4;
+    const uint64_t a_hi = smem_desc(nmb::smem_u32(smA)), a_lo = smem_desc(nmb::smem_u32(smA) + pbytes);
+    for (int64_t t = t_begin; t < t_end; ++t) {
+      if (*abort_flag)
+        break;
+      const int64_t n = t - t_begin, i = t / tiles_n;
+      const int s = (int)(n & 1);
+      const int buf = (int)(n % kAccBuffers);
+      const int64_t buf_use = n / kAccBuffers;
+      bool ok = true;
+      if (i != cur_i) {
+        ok = wait_bounded(a_full, (uint32_t)(a_uses & 1));
+        cur_i = i;
+        ++a_uses;
+      }
+      ok = ok && wait_bounded(&b_full[s], (uint32_t)((n >> 1) & 1));
+      if (ok && buf_use > 0)
+        ok = wait_bounded(&acc_empty[buf], (uint32_t)((buf_use - 1) & 1));
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0)
           give_up();
-          break;
-        }
-        tmem_fence_after();
+        break;
+      }
+      tmem_fence_after();
+      const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != i);
+      if (elect_one()) {
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTile);
         const uint32_t b_addr = nmb::smem_u32(smB + s * kStageBytes);
         const uint64_t b_hi = smem_desc(b_addr), b_lo = smem_desc(b_addr + pbytes);
@@ -362,31 +369,28 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll 4
         for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
           mma_tf32(d_tmem, da, db, 1);
-        NMB_TRACE(n, 4);
         mma_commit(&b_empty[s]);     // B stage reusable once these MMAs have read it
         mma_commit(&acc_full[buf]);  // accumulator ready for the epilogue
-        const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != i);
         if (last_of_row)
           mma_commit(a_empty);
       }
+      __syncwarp();
     }
-    __syncwarp();
   } else {
     // ---------------- epilogue: TMEM -> registers -> shared -> HBM ----------------
     // Warp w may read TMEM lanes 32*(w%4)..+31 (32 rows of the tile); the four
     // warps of a lane quarter take one 32-column strip each, i.e. every warp
     // owns one 32 x 32 piece of every tile (16 warps keep enough instruction
     // streams in flight to hide the latencies of the short dependent chains).
-    // A piece goes to HBM through the warp's private 2 KB staging buffer, 16
-    // rows at a time (16-byte chunk k of row r at position k ^ (r & 7):
-    // conflict-free both ways), so that the global stores are whole 128-byte
-    // lines, four rows per instruction.
+    // A piece leaves through the warp's private staging buffers, 8 rows at a
+    // time, as asynchronous TMA stores (16-byte chunk k of row r at position
+    // k ^ r, the 128-byte swizzle the tensor map undoes: conflict-free
+    // writes), so the warp is back at the next accumulator while the stores
+    // drain.  Outputs the tensor map cannot describe take plain stores.
     const int e = warp - kEpilogueWarp0;
     const int q = warp & 3;
     const int strip = e >> 2;
     unsigned char *stage = smStage + e * kStagingBytes;
-    const bool vec4_ok = (p.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-    const int srow = lane >> 3, schunk = lane & 7; // this lane's part of a 4-row store
     int64_t xa_row = -1;
     float xa = 0.f;
     for (int64_t t = t_begin; t < t_end; ++t) {
@@ -413,13 +417,9 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tmem_fence_after();
-      if (e == 0 && lane == 0)
-        NMB_TRACE(n, 5);
       float w[32];
       tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTile + strip * 32), w);
       tmem_ld_wait();
-      if (e == 0 && lane == 0)
-        NMB_TRACE(n, 6);
       // the accumulator is free as soon as it sits in registers
       tmem_fence_before();
       __syncwarp();
@@ -443,42 +443,41 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           w[k] = r;
         }
       }
-      if (!p.debug_skip) {
-        if (vec4_ok && col0 + 32 <= p.N) {
+      if (p.tma_out) {
+        // registers (lane = row) -> swizzled staging -> one TMA store per 8
+        // rows; the two buffers alternate, and a buffer is rewritten only once
+        // the store issued from it two passes earlier has read it.
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            // registers (lane = row) -> staging, 16 rows per pass
-            if ((lane >> 4) == hh) {
-              const int r = lane & 15;
+        for (int ps = 0; ps < 4; ++ps) {
+          unsigned char *sbuf = stage + (ps & 1) * kStoreBufBytes;
+          if (lane == 0)
+            nmb::bulk_wait_read<1>();
+          __syncwarp();
+          if ((lane >> 3) == ps) {
+            const int r = lane & 7;
 #pragma unroll
-              for (int k = 0; k < 8; ++k)
-                *reinterpret_cast<float4 *>(stage + r * kStagePitch + ((k ^ (r & 7)) << 4)) =
-                    make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
-            }
-            __syncwarp();
-            // staging -> HBM: per instruction four rows of 128 contiguous bytes
-#pragma unroll
-            for (int r4 = 0; r4 < 4; ++r4) {
-              const int r = r4 * 4 + srow;
-              const float4 x = *reinterpret_cast<const float4 *>(stage + r * kStagePitch +
-                                                                 ((schunk ^ (r & 7)) << 4));
-              const int64_t grow = row0 + hh * 16 + r;
-              if (grow < p.M)
-                __stcs(reinterpret_cast<float4 *>(p.out + grow * p.ldo + col0) + schunk, x);
-            }
-            __syncwarp();
+            for (int k = 0; k < 8; ++k)
+              *reinterpret_cast<float4 *>(sbuf + r * kStagePitch + ((k ^ r) << 4)) =
+                  make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
+            nmb::fence_async_smem();
           }
-        } else if (row < p.M) {
-          float *orow = p.out + row * p.ldo;
-#pragma unroll
-          for (int k = 0; k < 32; ++k)
-            if (col0 + k < p.N)
-              orow[col0 + k] = w[k];
+          __syncwarp();
+          if (lane == 0 && row0 + ps * kStoreRows < p.M && col0 < p.N) {
+            tma_store_box(&out_map, sbuf, (int)col0, (int)(row0 + ps * kStoreRows));
+            nmb::bulk_commit();
+          }
         }
+      } else if (row < p.M) {
+        float *orow = p.out + row * p.ldo;
+#pragma unroll
+        for (int k = 0; k < 32; ++k)
+          if (col0 + k < p.N)
+            orow[col0 + k] = w[k];
       }
-      if (e == 0 && lane == 0)
-        NMB_TRACE(n, 7);
     }
+    if (lane == 0)
+      nmb::bulk_wait_all<0>(); // shared memory must outlive the stores reading it
+    __syncwarp();
   }
 
   tmem_fence_before();
@@ -522,6 +521,25 @@ int smCount(int device) {
   if (device < 64)
     cached[device] = n;
   return n;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's entry-point lookup (the library
+// does not link against the driver); NULL when the driver lacks it.
+EncodeTiledFn encodeTiled() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void *f = nullptr;
+    cudaDriverEntryPointQueryResult st;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &st) != cudaSuccess ||
+        st != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
 }
 
 size_t alignUp(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -576,6 +594,23 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     nmb::noteLaunch();
     nmb::noteLaunch();
   }
+  // Tensor map of the output for the epilogue's TMA stores: needs a 16-byte
+  // aligned base and row pitch and 32-bit coordinates.
+  CUtensorMap out_map;
+  memset(&out_map, 0, sizeof(out_map));
+  bool tma_out = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ldo % 4 == 0 && ldo >= N &&
+                 M < (1ll << 31) && N < (1ll << 31) && ldo < (1ll << 36);
+  if (tma_out) {
+    EncodeTiledFn enc = encodeTiled();
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)ldo * 4};
+    const cuuint32_t box[2] = {32, (cuuint32_t)kStoreRows};
+    const cuuint32_t estr[2] = {1, 1};
+    tma_out = enc && enc(&out_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
   const bool single = K <= kMaxK;
   const int64_t total = tiles_m * tiles_n;
   const int64_t sms = smCount(qv.device);
@@ -600,14 +635,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     p.ldo = ldo;
     p.kpad = kpad;
     p.status = status;
-    p.debug_skip = getenv("NMB_DEBUG_SKIP_STORE") ? 1 : 0;
-    p.trace = nullptr;
-    unsigned long long *traceBuf = nullptr;
-    if (getenv("NMB_DEBUG_TRACE")) {
-      cudaMalloc(&traceBuf, 64 * 8 * 8);
-      cudaMemset(traceBuf, 0, 64 * 8 * 8);
-      p.trace = traceBuf;
-    }
+    p.tma_out = tma_out ? 1 : 0;
     if (mode == 0 && single) {
       p.mode = 0;
       p.alpha = 1.f;
@@ -617,20 +645,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
       p.alpha = mode == 0 ? 1.f : alpha;
       p.beta = first ? (mode == 0 ? 0.f : beta) : 1.f;
     }
-    nmb_contract_tf32x3<<<grid, kThreads, smemBytes, stream>>>(p);
-    if (traceBuf) {
-      unsigned long long h[64 * 8];
-      cudaStreamSynchronize(stream);
-      cudaMemcpy(h, traceBuf, sizeof(h), cudaMemcpyDeviceToHost);
-      cudaFree(traceBuf);
-      unsigned long long t0 = h[0];
-      for (int n = 0; n < 24; ++n) {
-        fprintf(stderr, "step %2d:", n);
-        for (int k = 0; k < 8; ++k)
-          fprintf(stderr, " %7lld", h[n * 8 + k] ? (long long)(h[n * 8 + k] - t0) : -1ll);
-        fprintf(stderr, "\n");
-      }
-    }
+    nmb_contract_tf32x3<<<grid, kThreads, smemBytes, stream>>>(p, out_map);
     nmb::noteLaunch();
     nmb::noteLaunch();
     nmb::noteLaunch();
