@@ -50,8 +50,8 @@ namespace {
 constexpr int kTile = 128;         // output tile is kTile x kTile
 constexpr int kMaxK = 64;          // K elements resident per launch
 constexpr int kChunkBytes = 2048;  // one K chunk (4 elements) of a 128-row tile: 16 groups x 128 B
-constexpr int kThreads = 576;      // producer warp, MMA warp, 16 epilogue warps
-constexpr int kEpilogueWarps = 16;
+constexpr int kThreads = 320;      // producer warp, MMA warp, 8 epilogue warps
+constexpr int kEpilogueWarps = 8;
 constexpr int kEpilogueWarp0 = 2;
 constexpr uint64_t kWaitCycles = 4000000000ull; // about 2 s
 constexpr int kStageBytes = 65536;  // one operand tile (hi+lo at K = 64) == one 128x128 fp32 output tile
@@ -231,9 +231,8 @@ struct ContractParams {
 
 constexpr int kAccBuffers = 4;                  // 4 x 128 fp32 columns: all of TMEM
 constexpr int kStagePitch = 128;                // bytes per staged row (32 floats)
-constexpr int kStoreRows = 8;                   // rows per TMA store box
-constexpr int kStoreBufBytes = kStoreRows * kStagePitch;
-constexpr int kStagingBytes = 2 * kStoreBufBytes; // two store buffers per epilogue warp
+constexpr int kStoreRows = 32;                  // rows per TMA store box: one 32 x 32 piece
+constexpr int kStagingBytes = kStoreRows * kStagePitch; // one staged piece per epilogue warp
 
 extern "C" __global__ void __launch_bounds__(kThreads, 1)
     nmb_contract_tf32x3(const ContractParams p, const __grid_constant__ CUtensorMap out_map) {
@@ -378,18 +377,17 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ---------------- epilogue: TMEM -> registers -> shared -> HBM ----------------
-    // Warp w may read TMEM lanes 32*(w%4)..+31 (32 rows of the tile); the four
-    // warps of a lane quarter take one 32-column strip each, i.e. every warp
-    // owns one 32 x 32 piece of every tile (16 warps keep enough instruction
-    // streams in flight to hide the latencies of the short dependent chains).
-    // A piece leaves through the warp's private staging buffers, 8 rows at a
-    // time, as asynchronous TMA stores (16-byte chunk k of row r at position
-    // k ^ r, the 128-byte swizzle the tensor map undoes: conflict-free
-    // writes), so the warp is back at the next accumulator while the stores
-    // drain.  Outputs the tensor map cannot describe take plain stores.
+    // Warp w may read TMEM lanes 32*(w%4)..+31 (32 rows of the tile); the two
+    // warps of a lane quarter take 64 columns each, as two 32 x 32 pieces.
+    // A piece leaves as one asynchronous TMA tensor store out of the warp's
+    // private 4 KB staging buffer (16-byte chunk k of row r at position
+    // k ^ (r & 7), the 128-byte swizzle the tensor map undoes: conflict-free
+    // writes), so the warp loads and computes its next piece while the store
+    // drains; it waits for the buffer only before restaging.  Outputs the
+    // tensor map cannot describe take plain stores.
     const int e = warp - kEpilogueWarp0;
     const int q = warp & 3;
-    const int strip = e >> 2;
+    const int half = e >> 2;
     unsigned char *stage = smStage + e * kStagingBytes;
     int64_t xa_row = -1;
     float xa = 0.f;
@@ -397,83 +395,85 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
       const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
       const int buf = (int)(n % kAccBuffers);
       const int64_t buf_use = n / kAccBuffers;
-      const int64_t row0 = i * kTile + q * 32; // first row of this warp's piece
+      const int64_t row0 = i * kTile + q * 32; // first row of this warp's pieces
       const int64_t row = row0 + lane;
-      const int64_t col0 = j * kTile + strip * 32;
-      // norms first: their latency overlaps the wait for the accumulator
-      float4 y[8];
-      if (p.mode == 0) {
-        const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
-#pragma unroll
-        for (int e4 = 0; e4 < 8; ++e4)
-          y[e4] = __ldg(nb + e4);
-        if (row != xa_row) {
-          xa = p.normA[row];
-          xa_row = row;
-        }
+      if (p.mode == 0 && row != xa_row) {
+        xa = p.normA[row];
+        xa_row = row;
       }
-      if (!wait_bounded(&acc_full[buf], (uint32_t)(buf_use & 1))) {
-        give_up();
-        break;
-      }
-      tmem_fence_after();
-      float w[32];
-      tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTile + strip * 32), w);
-      tmem_ld_wait();
-      // the accumulator is free as soon as it sits in registers
-      tmem_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        nmb::mbar_arrive(&acc_empty[buf]);
-      if (p.mode == 0) {
+      bool ok = true;
+#pragma unroll 1
+      for (int pc = 0; pc < 2; ++pc) {
+        const int strip = half * 2 + pc;
+        const int64_t col0 = j * kTile + strip * 32;
+        // norms first: their latency overlaps the wait for the accumulator
+        float4 y[8];
+        if (p.mode == 0) {
+          const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
 #pragma unroll
-        for (int e4 = 0; e4 < 8; ++e4) {
-          w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + y[e4].x), 0.f));
-          w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + y[e4].y), 0.f));
-          w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + y[e4].z), 0.f));
-          w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + y[e4].w), 0.f));
+          for (int e4 = 0; e4 < 8; ++e4)
+            y[e4] = __ldg(nb + e4);
         }
-      } else {
-        const float *orow = p.out + row * p.ldo;
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          float r = p.alpha * w[k];
-          if (p.beta != 0.f && row < p.M && col0 + k < p.N)
-            r = fmaf(p.beta, orow[col0 + k], r);
-          w[k] = r;
-        }
-      }
-      if (p.tma_out) {
-        // registers (lane = row) -> swizzled staging -> one TMA store per 8
-        // rows; the two buffers alternate, and a buffer is rewritten only once
-        // the store issued from it two passes earlier has read it.
-#pragma unroll
-        for (int ps = 0; ps < 4; ++ps) {
-          unsigned char *sbuf = stage + (ps & 1) * kStoreBufBytes;
-          if (lane == 0)
-            nmb::bulk_wait_read<1>();
-          __syncwarp();
-          if ((lane >> 3) == ps) {
-            const int r = lane & 7;
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              *reinterpret_cast<float4 *>(sbuf + r * kStagePitch + ((k ^ r) << 4)) =
-                  make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
-            nmb::fence_async_smem();
+        if (pc == 0) {
+          if (!wait_bounded(&acc_full[buf], (uint32_t)(buf_use & 1))) {
+            give_up();
+            ok = false;
+            break;
           }
+          tmem_fence_after();
+        }
+        float w[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTile + strip * 32), w);
+        tmem_ld_wait();
+        if (pc == 1) {
+          // the accumulator is free as soon as its last piece sits in registers
+          tmem_fence_before();
           __syncwarp();
-          if (lane == 0 && row0 + ps * kStoreRows < p.M && col0 < p.N) {
-            tma_store_box(&out_map, sbuf, (int)col0, (int)(row0 + ps * kStoreRows));
+          if (lane == 0)
+            nmb::mbar_arrive(&acc_empty[buf]);
+        }
+        if (p.mode == 0) {
+#pragma unroll
+          for (int e4 = 0; e4 < 8; ++e4) {
+            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + y[e4].x), 0.f));
+            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + y[e4].y), 0.f));
+            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + y[e4].z), 0.f));
+            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + y[e4].w), 0.f));
+          }
+        } else {
+          const float *orow = p.out + row * p.ldo;
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            float r = p.alpha * w[k];
+            if (p.beta != 0.f && row < p.M && col0 + k < p.N)
+              r = fmaf(p.beta, orow[col0 + k], r);
+            w[k] = r;
+          }
+        }
+        if (p.tma_out) {
+          if (lane == 0)
+            nmb::bulk_wait_read<0>(); // the previous store has read the buffer
+          __syncwarp();
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            *reinterpret_cast<float4 *>(stage + lane * kStagePitch + ((k ^ (lane & 7)) << 4)) =
+                make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
+          nmb::fence_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M && col0 < p.N) {
+            tma_store_box(&out_map, stage, (int)col0, (int)row0);
             nmb::bulk_commit();
           }
-        }
-      } else if (row < p.M) {
-        float *orow = p.out + row * p.ldo;
+        } else if (row < p.M) {
+          float *orow = p.out + row * p.ldo;
 #pragma unroll
-        for (int k = 0; k < 32; ++k)
-          if (col0 + k < p.N)
-            orow[col0 + k] = w[k];
+          for (int k = 0; k < 32; ++k)
+            if (col0 + k < p.N)
+              orow[col0 + k] = w[k];
+        }
       }
+      if (!ok)
+        break;
     }
     if (lane == 0)
       nmb::bulk_wait_all<0>(); // shared memory must outlive the stores reading it
