@@ -231,6 +231,8 @@ struct ContractParams {
 
 constexpr int kAccBuffers = 4;                  // 4 x 128 fp32 columns: all of TMEM
 constexpr int kStagePitch = 128;                // bytes per staged row (32 floats)
+constexpr int kNormSlots = 5;                   // ring of per-tile B norms (128 floats each)
+constexpr int kNormSlotBytes = kTile * 4;
 constexpr int kStoreRows = 32;                  // rows per TMA store box: one 32 x 32 piece
 constexpr int kStagingBytes = kStoreRows * kStagePitch; // one staged piece per epilogue warp
 
@@ -242,11 +244,13 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
   unsigned char *smA = smem;                   // one A tile, resident per tile row
   unsigned char *smB = smem + kStageBytes;     // two B stages
   unsigned char *smStage = smem + 3 * kStageBytes; // kEpilogueWarps x 2 KB
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smStage + kEpilogueWarps * kStagingBytes);
+  unsigned char *smNorm = smStage + kEpilogueWarps * kStagingBytes; // kNormSlots x 512 B
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smNorm + kNormSlots * kNormSlotBytes);
   uint64_t *a_full = bars + 0, *a_empty = bars + 1;
   uint64_t *b_full = bars + 2, *b_empty = bars + 4;      // [2] each
   uint64_t *acc_full = bars + 6, *acc_empty = bars + 10; // [kAccBuffers] each
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
+  uint64_t *norm_empty = bars + 14;                      // [kNormSlots]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14 + kNormSlots);
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -265,6 +269,8 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
       nmb::mbar_init(&acc_full[s], 1);
       nmb::mbar_init(&acc_empty[s], kEpilogueWarps); // one arrival per epilogue warp
     }
+    for (int s = 0; s < kNormSlots; ++s)
+      nmb::mbar_init(&norm_empty[s], kEpilogueWarps);
     *abort_flag = 0;
     nmb::mbar_init_fence();
   }
@@ -307,9 +313,18 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
           give_up();
           break;
         }
-        nmb::mbar_expect_tx(&b_full[s], (uint32_t)tile_bytes);
+        // the tile's B norms travel with it, into a ring slot the epilogue frees
+        const int r = (int)(n % kNormSlots);
+        const int64_t r_use = n / kNormSlots;
+        if (r_use > 0 && !wait_bounded(&norm_empty[r], (uint32_t)((r_use - 1) & 1))) {
+          give_up();
+          break;
+        }
+        nmb::mbar_expect_tx(&b_full[s], (uint32_t)tile_bytes + (p.mode == 0 ? kNormSlotBytes : 0));
         load_split(smB + s * kStageBytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
                    &b_full[s]);
+        if (p.mode == 0)
+          nmb::bulk_load(smNorm + r * kNormSlotBytes, p.normB + j * kTile, kNormSlotBytes, &b_full[s]);
       }
     }
     __syncwarp();
@@ -401,53 +416,43 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         xa = p.normA[row];
         xa_row = row;
       }
-      bool ok = true;
-#pragma unroll 1
-      for (int pc = 0; pc < 2; ++pc) {
-        const int strip = half * 2 + pc;
-        const int64_t col0 = j * kTile + strip * 32;
-        // norms first: their latency overlaps the wait for the accumulator
-        float4 y[8];
+      if (!wait_bounded(&acc_full[buf], (uint32_t)(buf_use & 1))) {
+        give_up();
+        break;
+      }
+      tmem_fence_after();
+      // both pieces into registers; the accumulator is free from then on
+      float w0[32], w1[32];
+      const uint32_t tsrc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTile + half * 64);
+      tmem_ld32(tsrc, w0);
+      tmem_ld32(tsrc + 32, w1);
+      tmem_ld_wait();
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        nmb::mbar_arrive(&acc_empty[buf]);
+      const int r = (int)(n % kNormSlots);
+      auto finish_piece = [&](float(&w)[32], int pc) {
+        const int64_t col0 = j * kTile + half * 64 + pc * 32;
         if (p.mode == 0) {
-          const float4 *nb = reinterpret_cast<const float4 *>(p.normB + col0);
-#pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4)
-            y[e4] = __ldg(nb + e4);
-        }
-        if (pc == 0) {
-          if (!wait_bounded(&acc_full[buf], (uint32_t)(buf_use & 1))) {
-            give_up();
-            ok = false;
-            break;
-          }
-          tmem_fence_after();
-        }
-        float w[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kTile + strip * 32), w);
-        tmem_ld_wait();
-        if (pc == 1) {
-          // the accumulator is free as soon as its last piece sits in registers
-          tmem_fence_before();
-          __syncwarp();
-          if (lane == 0)
-            nmb::mbar_arrive(&acc_empty[buf]);
-        }
-        if (p.mode == 0) {
+          // |y_j|^2 of the piece's 32 columns: broadcast reads of the ring slot
+          const float4 *y = reinterpret_cast<const float4 *>(smNorm + r * kNormSlotBytes) + half * 16 + pc * 8;
 #pragma unroll
           for (int e4 = 0; e4 < 8; ++e4) {
-            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + y[e4].x), 0.f));
-            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + y[e4].y), 0.f));
-            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + y[e4].z), 0.f));
-            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + y[e4].w), 0.f));
+            const float4 yv = y[e4];
+            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + yv.x), 0.f));
+            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + yv.y), 0.f));
+            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + yv.z), 0.f));
+            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + yv.w), 0.f));
           }
         } else {
           const float *orow = p.out + row * p.ldo;
 #pragma unroll
           for (int k = 0; k < 32; ++k) {
-            float r = p.alpha * w[k];
+            float v = p.alpha * w[k];
             if (p.beta != 0.f && row < p.M && col0 + k < p.N)
-              r = fmaf(p.beta, orow[col0 + k], r);
-            w[k] = r;
+              v = fmaf(p.beta, orow[col0 + k], v);
+            w[k] = v;
           }
         }
         if (p.tma_out) {
@@ -471,9 +476,12 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
             if (col0 + k < p.N)
               orow[col0 + k] = w[k];
         }
-      }
-      if (!ok)
-        break;
+      };
+      finish_piece(w0, 0);
+      finish_piece(w1, 1);
+      __syncwarp();
+      if (lane == 0)
+        nmb::mbar_arrive(&norm_empty[r]);
     }
     if (lane == 0)
       nmb::bulk_wait_all<0>(); // shared memory must outlive the stores reading it
@@ -574,7 +582,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     return false;
 
   static bool attrSet[64] = {false};
-  const int smemBytes = 3 * kStageBytes + kEpilogueWarps * kStagingBytes + 256;
+  const int smemBytes = 3 * kStageBytes + kEpilogueWarps * kStagingBytes + kNormSlots * kNormSlotBytes + 256;
   if (qv.device >= 64 || !attrSet[qv.device]) {
     if (cudaFuncSetAttribute(nmb_contract_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              smemBytes) != cudaSuccess) {
