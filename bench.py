@@ -2,7 +2,7 @@
 """Benchmark of the numba-mlir offload path on B200.
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
-                    [--workload NAME] [--no-extra] [--no-cpu]
+                    [--workload NAME] [--no-extra] [--no-cpu] [--profile]
 
 One "step" is one pass of the hot path over one batch of synthetic input.  The
 headline workload is the Black-Scholes fused ufunc chain over 2^24 float32
@@ -528,6 +528,17 @@ def run_gpu(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    if args.profile:
+        # For a profiler: eager launches of the device-resident step only.
+        for _ in range(args.warmup + args.steps):
+            w.step_device()
+        barrier()
+        queue.check_status()
+        if rank == 0:
+            print(json.dumps({"profile_run": w.name, "steps": args.steps, "warmup": args.warmup,
+                              "launches_per_step": w.launches_per_step}), flush=True)
+        return
+
     sampler = ClockSampler(local_rank)
     sampler.start()
     sampler.active(True)
@@ -659,12 +670,14 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations")
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of a CUDA graph")
+    ap.add_argument("--profile", action="store_true",
+                    help="run only warmup + steps eager device steps of --workload (for ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
     else:
         if args.steps is None:
-            args.steps = 2000
+            args.steps = 3 if args.profile else 2000
         run_gpu(args)
 
 

@@ -206,15 +206,6 @@ __device__ __forceinline__ float sqrt_approx(float x) {
   return r;
 }
 
-// One operand tile as several bulk copies on the same mbarrier: more requests
-// in flight than a single 64 KB copy gives.
-__device__ __forceinline__ void load_split(unsigned char *dst, const unsigned char *src, uint32_t bytes,
-                                           uint64_t *bar) {
-  constexpr uint32_t kPiece = 8192;
-  for (uint32_t off = 0; off < bytes; off += kPiece)
-    nmb::bulk_load(dst + off, src + off, bytes - off < kPiece ? bytes - off : kPiece, bar);
-}
-
 struct ContractParams {
   const unsigned char *packedA; // [tiles_m][hi | lo]
   const unsigned char *packedB; // [tiles_n][hi | lo]
@@ -231,6 +222,10 @@ struct ContractParams {
 
 constexpr int kAccBuffers = 4;                  // 4 x 128 fp32 columns: all of TMEM
 constexpr int kStagePitch = 128;                // bytes per staged row (32 floats)
+constexpr int kSlotChunks = 8;                  // K chunks (of 4 elements) per B slot: half of kMaxK
+constexpr int kSlotBytes = 2 * kSlotChunks * kChunkBytes; // hi + lo images of a K half: 32 KB
+constexpr int kBSlots = 4;                      // 128 KB of B slots
+constexpr uint32_t kPiece = 8192;               // bytes per bulk copy
 constexpr int kNormSlots = 5;                   // ring of per-tile B norms (128 floats each)
 constexpr int kNormSlotBytes = kTile * 4;
 constexpr int kStoreRows = 32;                  // rows per TMA store box: one 32 x 32 piece
@@ -242,15 +237,15 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
   const int pbytes = partBytes(p.kpad);
   const int tile_bytes = 2 * pbytes;
   unsigned char *smA = smem;                   // one A tile, resident per tile row
-  unsigned char *smB = smem + kStageBytes;     // two B stages
+  unsigned char *smB = smem + kStageBytes;     // kBSlots K-half slots
   unsigned char *smStage = smem + 3 * kStageBytes; // kEpilogueWarps x 2 KB
   unsigned char *smNorm = smStage + kEpilogueWarps * kStagingBytes; // kNormSlots x 512 B
   uint64_t *bars = reinterpret_cast<uint64_t *>(smNorm + kNormSlots * kNormSlotBytes);
   uint64_t *a_full = bars + 0, *a_empty = bars + 1;
-  uint64_t *b_full = bars + 2, *b_empty = bars + 4;      // [2] each
-  uint64_t *acc_full = bars + 6, *acc_empty = bars + 10; // [kAccBuffers] each
-  uint64_t *norm_empty = bars + 14;                      // [kNormSlots]
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14 + kNormSlots);
+  uint64_t *b_full = bars + 2, *b_empty = bars + 6;       // [kBSlots] each
+  uint64_t *acc_full = bars + 10, *acc_empty = bars + 14; // [kAccBuffers] each
+  uint64_t *norm_empty = bars + 18;                       // [kNormSlots]
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 18 + kNormSlots);
   volatile uint32_t *abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -261,7 +256,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) {
     nmb::mbar_init(a_full, 1);
     nmb::mbar_init(a_empty, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kBSlots; ++s) {
       nmb::mbar_init(&b_full[s], 1);
       nmb::mbar_init(&b_empty[s], 1);
     }
@@ -291,41 +286,78 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     atomicExch(p.status, (uint32_t)nmb::kStatusWaitTimeout);
   };
 
+  // B travels in K halves: a slot holds the hi and lo images of 32 K elements
+  // (8 chunks each) of one tile; the MMA warp frees a slot after the 12 MMAs
+  // that read it, so a reload starts half a tile earlier than with whole-tile
+  // stages and four loads are in flight.
+  const int nchunks = p.kpad / 4;
+  const int halves = nchunks > kSlotChunks ? 2 : 1;
+
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int64_t cur_i = -1, a_uses = 0;
-      for (int64_t t = t_begin; t < t_end && !*abort_flag; ++t) {
-        const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
-        if (i != cur_i) {
-          if (a_uses > 0 && !wait_bounded(a_empty, (uint32_t)((a_uses - 1) & 1))) {
+    // The whole warp runs the loop; the copies of one slot are issued by
+    // different lanes at once (issuing them one after another from one thread
+    // cost most of a microsecond per tile).
+    int64_t cur_i = -1, a_uses = 0, m = 0;
+    for (int64_t t = t_begin; t < t_end; ++t) {
+      if (*abort_flag)
+        break;
+      const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
+      bool ok = true;
+      if (i != cur_i) {
+        if (a_uses > 0)
+          ok = wait_bounded(a_empty, (uint32_t)((a_uses - 1) & 1));
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0)
             give_up();
-            break;
-          }
-          nmb::mbar_expect_tx(a_full, (uint32_t)tile_bytes);
-          load_split(smA, p.packedA + i * (int64_t)tile_bytes, (uint32_t)tile_bytes, a_full);
-          cur_i = i;
-          ++a_uses;
-        }
-        const int s = (int)(n & 1);
-        const int64_t use = n >> 1;
-        if (use > 0 && !wait_bounded(&b_empty[s], (uint32_t)((use - 1) & 1))) {
-          give_up();
           break;
         }
-        // the tile's B norms travel with it, into a ring slot the epilogue frees
+        if (lane == 0)
+          nmb::mbar_expect_tx(a_full, (uint32_t)tile_bytes);
+        __syncwarp();
+        for (uint32_t off = (uint32_t)lane * kPiece; off < (uint32_t)tile_bytes; off += 32 * kPiece)
+          nmb::bulk_load(smA + off, p.packedA + i * (int64_t)tile_bytes + off,
+                         (uint32_t)tile_bytes - off < kPiece ? (uint32_t)tile_bytes - off : kPiece, a_full);
+        cur_i = i;
+        ++a_uses;
+      }
+      for (int h = 0; h < halves; ++h, ++m) {
+        const int slot = (int)(m % kBSlots);
+        const int64_t use = m / kBSlots;
+        if (use > 0)
+          ok = wait_bounded(&b_empty[slot], (uint32_t)((use - 1) & 1));
+        // the tile's B norms travel with its first half, into a ring slot the
+        // epilogue frees
         const int r = (int)(n % kNormSlots);
         const int64_t r_use = n / kNormSlots;
-        if (r_use > 0 && !wait_bounded(&norm_empty[r], (uint32_t)((r_use - 1) & 1))) {
-          give_up();
+        const bool with_norms = h == 0 && p.mode == 0;
+        if (ok && with_norms && r_use > 0)
+          ok = wait_bounded(&norm_empty[r], (uint32_t)((r_use - 1) & 1));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0)
+            give_up();
           break;
         }
-        nmb::mbar_expect_tx(&b_full[s], (uint32_t)tile_bytes + (p.mode == 0 ? kNormSlotBytes : 0));
-        load_split(smB + s * kStageBytes, p.packedB + j * (int64_t)tile_bytes, (uint32_t)tile_bytes,
-                   &b_full[s]);
-        if (p.mode == 0)
-          nmb::bulk_load(smNorm + r * kNormSlotBytes, p.normB + j * kTile, kNormSlotBytes, &b_full[s]);
+        const int ch = nchunks - h * kSlotChunks < kSlotChunks ? nchunks - h * kSlotChunks : kSlotChunks;
+        const uint32_t part = (uint32_t)ch * kChunkBytes; // bytes of the hi (or lo) part
+        if (lane == 0)
+          nmb::mbar_expect_tx(&b_full[slot], 2 * part + (with_norms ? kNormSlotBytes : 0));
+        __syncwarp();
+        const int per = (int)((part + kPiece - 1) / kPiece); // pieces per part: 1 or 2
+        if (lane < 2 * per) {
+          const int which = lane / per;                      // 0: hi, 1: lo
+          const uint32_t off = (uint32_t)(lane % per) * kPiece;
+          nmb::bulk_load(smB + slot * kSlotBytes + which * (kSlotBytes / 2) + off,
+                         p.packedB + j * (int64_t)tile_bytes + which * pbytes +
+                             h * (kSlotBytes / 2) + off,
+                         part - off < kPiece ? part - off : kPiece, &b_full[slot]);
+        } else if (lane == 4 && with_norms) {
+          nmb::bulk_load(smNorm + r * kNormSlotBytes, p.normB + j * kTile, kNormSlotBytes, &b_full[slot]);
+        }
       }
+      if (!ok)
+        break;
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -333,62 +365,72 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     // The whole warp runs the loop and the waits in lockstep and one elected
     // lane issues: MMAs issued from a divergent single-lane branch went out
     // at half the rate.
-    int64_t cur_i = -1, a_uses = 0;
-    const int ksteps = p.kpad / 8;
-    // Descriptors differ only in the start-address field: one 64-bit add
-    // per K step (2 chunks of 2 KB = 256 units of 16 bytes).
+    int64_t cur_i = -1, a_uses = 0, m = 0;
+    // Descriptors differ only in the start-address field (units of 16 bytes):
+    // a K step is 2 chunks of 2 KB = 256 units, a K half 8 chunks = 1024.
     constexpr uint64_t kStepUnits = (2 * kChunkBytes) >> 4;
+    constexpr uint64_t kHalfUnits = (kSlotChunks * kChunkBytes) >> 4;
     const uint64_t a_hi = smem_desc(nmb::smem_u32(smA)), a_lo = smem_desc(nmb::smem_u32(smA) + pbytes);
     for (int64_t t = t_begin; t < t_end; ++t) {
       if (*abort_flag)
         break;
       const int64_t n = t - t_begin, i = t / tiles_n;
-      const int s = (int)(n & 1);
       const int buf = (int)(n % kAccBuffers);
       const int64_t buf_use = n / kAccBuffers;
+      const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != i);
       bool ok = true;
       if (i != cur_i) {
         ok = wait_bounded(a_full, (uint32_t)(a_uses & 1));
         cur_i = i;
         ++a_uses;
       }
-      ok = ok && wait_bounded(&b_full[s], (uint32_t)((n >> 1) & 1));
       if (ok && buf_use > 0)
         ok = wait_bounded(&acc_empty[buf], (uint32_t)((buf_use - 1) & 1));
-      ok = __all_sync(0xffffffffu, ok);
+      for (int h = 0; h < halves; ++h, ++m) {
+        const int slot = (int)(m % kBSlots);
+        ok = ok && wait_bounded(&b_full[slot], (uint32_t)((m / kBSlots) & 1));
+        if (!__all_sync(0xffffffffu, ok)) {
+          ok = false;
+          break;
+        }
+        tmem_fence_after();
+        if (elect_one()) {
+          const int ch = nchunks - h * kSlotChunks < kSlotChunks ? nchunks - h * kSlotChunks : kSlotChunks;
+          const int ksteps = ch / 2;
+          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTile);
+          const uint32_t b_addr = nmb::smem_u32(smB + slot * kSlotBytes);
+          const uint64_t b_hi = smem_desc(b_addr), b_lo = smem_desc(b_addr + kSlotBytes / 2);
+          const uint64_t ah = a_hi + h * kHalfUnits, al = a_lo + h * kHalfUnits;
+          // hi.hi (the tile's very first MMA overwrites the accumulator), hi.lo, lo.hi
+          uint64_t da = ah, db = b_hi;
+          mma_tf32(d_tmem, da, db, h == 0 ? 0u : 1u);
+#pragma unroll
+          for (int ks = 1; ks < ksteps; ++ks)
+            mma_tf32(d_tmem, da += kStepUnits, db += kStepUnits, 1);
+          da = ah;
+          db = b_lo;
+#pragma unroll
+          for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
+            mma_tf32(d_tmem, da, db, 1);
+          da = al;
+          db = b_hi;
+#pragma unroll
+          for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
+            mma_tf32(d_tmem, da, db, 1);
+          mma_commit(&b_empty[slot]);      // slot reusable once these MMAs have read it
+          if (h == halves - 1) {
+            mma_commit(&acc_full[buf]);    // accumulator ready for the epilogue
+            if (last_of_row)
+              mma_commit(a_empty);
+          }
+        }
+        __syncwarp();
+      }
       if (!ok) {
         if (lane == 0)
           give_up();
         break;
       }
-      tmem_fence_after();
-      const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != i);
-      if (elect_one()) {
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kTile);
-        const uint32_t b_addr = nmb::smem_u32(smB + s * kStageBytes);
-        const uint64_t b_hi = smem_desc(b_addr), b_lo = smem_desc(b_addr + pbytes);
-        // hi.hi (overwrites the accumulator on its first step), hi.lo, lo.hi
-        uint64_t da = a_hi, db = b_hi;
-        mma_tf32(d_tmem, da, db, 0);
-#pragma unroll 4
-        for (int ks = 1; ks < ksteps; ++ks)
-          mma_tf32(d_tmem, da += kStepUnits, db += kStepUnits, 1);
-        da = a_hi;
-        db = b_lo;
-#pragma unroll 4
-        for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
-          mma_tf32(d_tmem, da, db, 1);
-        da = a_lo;
-        db = b_hi;
-#pragma unroll 4
-        for (int ks = 0; ks < ksteps; ++ks, da += kStepUnits, db += kStepUnits)
-          mma_tf32(d_tmem, da, db, 1);
-        mma_commit(&b_empty[s]);     // B stage reusable once these MMAs have read it
-        mma_commit(&acc_full[buf]);  // accumulator ready for the epilogue
-        if (last_of_row)
-          mma_commit(a_empty);
-      }
-      __syncwarp();
     }
   } else {
     // ---------------- epilogue: TMEM -> registers -> shared -> HBM ----------------
