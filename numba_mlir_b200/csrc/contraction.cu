@@ -116,6 +116,8 @@ extern "C" __global__ void __launch_bounds__(256)
 // Bounded mbarrier wait on a clock budget (the hardware poll itself suspends
 // for a while, so counting polls alone would bound nothing useful).
 __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity) {
+  if (nmb::mbar_try_wait(bar, parity))
+    return true;
   const long long t0 = clock64();
   uint32_t n = 0;
   while (!nmb::mbar_try_wait(bar, parity))
@@ -252,6 +254,10 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
   const int64_t tiles_m = (p.M + kTile - 1) / kTile, tiles_n = (p.N + kTile - 1) / kTile;
   const int64_t total = tiles_m * tiles_n;
   const int64_t t_begin = total * blockIdx.x / gridDim.x, t_end = total * (blockIdx.x + 1) / gridDim.x;
+  // This CTA's tiles are t_begin + n, n in [0, count): tile row i, column j
+  // stepped along with n (no 64-bit divisions inside the role loops).
+  const uint32_t count = (uint32_t)(t_end - t_begin);
+  const int64_t i_first = t_begin / tiles_n, j_first = t_begin % tiles_n;
 
   if (threadIdx.x == 0) {
     nmb::mbar_init(a_full, 1);
@@ -298,11 +304,11 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     // The whole warp runs the loop; the copies of one slot are issued by
     // different lanes at once (issuing them one after another from one thread
     // cost most of a microsecond per tile).
-    int64_t cur_i = -1, a_uses = 0, m = 0;
-    for (int64_t t = t_begin; t < t_end; ++t) {
+    int64_t cur_i = -1, i = i_first, j = j_first;
+    uint32_t a_uses = 0, m = 0;
+    for (uint32_t n = 0; n < count; ++n, j = (j + 1 == tiles_n ? 0 : j + 1), i += (j == 0)) {
       if (*abort_flag)
         break;
-      const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
       bool ok = true;
       if (i != cur_i) {
         if (a_uses > 0)
@@ -323,13 +329,13 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
       }
       for (int h = 0; h < halves; ++h, ++m) {
         const int slot = (int)(m % kBSlots);
-        const int64_t use = m / kBSlots;
+        const uint32_t use = m / kBSlots;
         if (use > 0)
           ok = wait_bounded(&b_empty[slot], (uint32_t)((use - 1) & 1));
         // the tile's B norms travel with its first half, into a ring slot the
         // epilogue frees
         const int r = (int)(n % kNormSlots);
-        const int64_t r_use = n / kNormSlots;
+        const uint32_t r_use = n / kNormSlots;
         const bool with_norms = h == 0 && p.mode == 0;
         if (ok && with_norms && r_use > 0)
           ok = wait_bounded(&norm_empty[r], (uint32_t)((r_use - 1) & 1));
@@ -365,19 +371,19 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     // The whole warp runs the loop and the waits in lockstep and one elected
     // lane issues: MMAs issued from a divergent single-lane branch went out
     // at half the rate.
-    int64_t cur_i = -1, a_uses = 0, m = 0;
+    int64_t cur_i = -1, i = i_first, j = j_first;
+    uint32_t a_uses = 0, m = 0;
     // Descriptors differ only in the start-address field (units of 16 bytes):
     // a K step is 2 chunks of 2 KB = 256 units, a K half 8 chunks = 1024.
     constexpr uint64_t kStepUnits = (2 * kChunkBytes) >> 4;
     constexpr uint64_t kHalfUnits = (kSlotChunks * kChunkBytes) >> 4;
     const uint64_t a_hi = smem_desc(nmb::smem_u32(smA)), a_lo = smem_desc(nmb::smem_u32(smA) + pbytes);
-    for (int64_t t = t_begin; t < t_end; ++t) {
+    for (uint32_t n = 0; n < count; ++n, j = (j + 1 == tiles_n ? 0 : j + 1), i += (j == 0)) {
       if (*abort_flag)
         break;
-      const int64_t n = t - t_begin, i = t / tiles_n;
       const int buf = (int)(n % kAccBuffers);
-      const int64_t buf_use = n / kAccBuffers;
-      const bool last_of_row = (t + 1 == t_end) || ((t + 1) / tiles_n != i);
+      const uint32_t buf_use = n / kAccBuffers;
+      const bool last_of_row = (n + 1 == count) || (j + 1 == tiles_n);
       bool ok = true;
       if (i != cur_i) {
         ok = wait_bounded(a_full, (uint32_t)(a_uses & 1));
@@ -448,10 +454,10 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
     unsigned char *stage = smStage + e * kStagingBytes;
     int64_t xa_row = -1;
     float xa = 0.f;
-    for (int64_t t = t_begin; t < t_end; ++t) {
-      const int64_t n = t - t_begin, i = t / tiles_n, j = t % tiles_n;
+    int64_t i = i_first, j = j_first;
+    for (uint32_t n = 0; n < count; ++n, j = (j + 1 == tiles_n ? 0 : j + 1), i += (j == 0)) {
       const int buf = (int)(n % kAccBuffers);
-      const int64_t buf_use = n / kAccBuffers;
+      const uint32_t buf_use = n / kAccBuffers;
       const int64_t row0 = i * kTile + q * 32; // first row of this warp's pieces
       const int64_t row = row0 + lane;
       if (p.mode == 0 && row != xa_row) {
