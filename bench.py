@@ -237,7 +237,7 @@ class Pairwise(Workload):
     dtype = "f32 (3xTF32 tensor cores)"
     bytes_per_step = 1082130432
     units_per_step = 16384 * 16384
-    launches_per_step = 5
+    launches_per_step = 2
 
     def setup_device(self, queue, seed, dist=None):
         import numba_mlir_b200 as nm
