@@ -91,12 +91,63 @@ extern "C" __global__ void __launch_bounds__(256)
   const PackOperand &op = first ? a : b;
   const int64_t tile = first ? blockIdx.x : blockIdx.x - a.tiles;
   const bool k_fastest = op.ldk <= op.ldr;
-  for (int e = threadIdx.x; e < kTile * kpad; e += blockDim.x) {
-    const int r = k_fastest ? e / kpad : e % kTile;
-    const int k = k_fastest ? e % kpad : e / kTile;
-    const int64_t row = tile * kTile + r;
-    buf[r * kPackPitch + k] =
-        (row < op.rows && k < kcount) ? op.src[row * op.ldr + (int64_t)(k0 + k) * op.ldk] : 0.f;
+  const bool vec = op.ldk == 1 && op.ldr % 4 == 0 && k0 % 4 == 0 &&
+                   (reinterpret_cast<uintptr_t>(op.src) & 15) == 0;
+  if (vec) {
+    // rows are contiguous and 16-byte aligned: the whole tile is requested
+    // before the first value is used (8 x 16 bytes per thread at K = 64)
+    const int c4s = kpad / 4, total = kTile * c4s;
+    constexpr int kBatch = kTile * (kMaxK / 4) / 256;
+    float4 v[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int e = u * 256 + threadIdx.x;
+      const int r = e / c4s, c = e % c4s;
+      const int64_t row = tile * kTile + r;
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (e < total && row < op.rows) {
+        const float *src = op.src + row * op.ldr + k0 + c * 4;
+        if (c * 4 + 4 <= kcount) {
+          v[u] = __ldg(reinterpret_cast<const float4 *>(src));
+        } else {
+          float *vp = &v[u].x;
+          for (int i = 0; i < 4; ++i)
+            if (c * 4 + i < kcount)
+              vp[i] = __ldg(src + i);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int e = u * 256 + threadIdx.x;
+      if (e < total) {
+        float *dst = buf + (e / c4s) * kPackPitch + (e % c4s) * 4;
+        dst[0] = v[u].x;
+        dst[1] = v[u].y;
+        dst[2] = v[u].z;
+        dst[3] = v[u].w;
+      }
+    }
+  } else {
+    for (int base = 0; base < kTile * kpad; base += 4 * 256) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = base + u * 256 + threadIdx.x;
+        const int r = k_fastest ? e / kpad : e % kTile;
+        const int k = k_fastest ? e % kpad : e / kTile;
+        const int64_t row = tile * kTile + r;
+        v[u] = (e < kTile * kpad && row < op.rows && k < kcount)
+                   ? __ldg(op.src + row * op.ldr + (int64_t)(k0 + k) * op.ldk)
+                   : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = base + u * 256 + threadIdx.x;
+        if (e < kTile * kpad)
+          buf[(k_fastest ? e / kpad : e % kTile) * kPackPitch + (k_fastest ? e % kpad : e / kTile)] = v[u];
+      }
+    }
   }
   __syncthreads();
   if (op.norms && threadIdx.x < kTile) {
