@@ -253,6 +253,7 @@ class Translator:
         self.alias = {}           # array var -> root (param) var
         self.uses_barrier = False
         self.counter = 0
+        self.par_ranges = {}      # range variable -> (id expr, count expr): grid-strided loops
 
     # naming -------------------------------------------------------------------
     def cname(self, name):
@@ -586,7 +587,13 @@ class Translator:
                 vals = ["0", vals[0], "1"]
             elif len(vals) == 2:
                 vals = vals + ["1"]
-            out.append(f"{d}_a = {vals[0]}; {d}_b = {vals[1]}; {d}_c = {vals[2]};")
+            if tname in self.par_ranges:
+                # a parallel loop: this thread takes iterations id, id + count, ...
+                tid, cnt = self.par_ranges[tname]
+                out.append(f"{d}_c = {vals[2]}; {d}_a = {vals[0]} + {tid} * {d}_c; {d}_b = {vals[1]}; "
+                           f"{d}_c *= {cnt};")
+            else:
+                out.append(f"{d}_a = {vals[0]}; {d}_b = {vals[1]}; {d}_c = {vals[2]};")
             return
         if fn in K.ID_FUNCS:
             c = f"nmb::k_{fn.__name__}({self.scalar(args[0], types.int64)}, nmb_gs)"
@@ -743,6 +750,31 @@ class Translator:
         else:
             raise UnsupportedError(f"argument of type {t}")
 
+    def parallel_update(self, store, blocks):
+        """(sign, operand) when `store` writes `x[idx] (+|-)= operand` back to the
+        element it was read from, else None."""
+        import operator as op
+
+        ir = self.ir
+        if getattr(self, "_defs", None) is None:
+            self._defs = _single_defs(blocks, ir)
+        d = self._defs.get(store.value.name)
+        if d is None or len(d) != 1 or not isinstance(d[0], ir.Expr) or d[0].op != "inplace_binop":
+            return None
+        e = d[0]
+        if e.fn not in (op.iadd, op.isub):
+            return None
+        ld = _resolve(self._defs, ir, e.lhs.name)
+        if not (isinstance(ld, ir.Expr) and ld.op in ("getitem", "static_getitem")):
+            return None
+        if ld.value.name != store.target.name:
+            return None
+        st_idx = store.index_var if isinstance(store, ir.StaticSetItem) else store.index
+        ld_idx = ld.index_var if ld.op == "static_getitem" else ld.index
+        if st_idx is None or ld_idx is None or st_idx.name != ld_idx.name:
+            return None
+        return (1 if e.fn is op.iadd else -1), e.rhs
+
     # statements -------------------------------------------------------------------------
     def translate(self, param_names):
         ir, types = self.ir, self.types
@@ -769,7 +801,15 @@ class Translator:
                         idx_exprs = self.index_list(inst.index_var if isinstance(inst, ir.StaticSetItem)
                                                     else inst.index)
                     ref = self.element_ref(arr, idx_exprs)
-                    out.append(f"{ref} = {self.scalar(inst.value, rep.dtype)};")
+                    upd = self.parallel_update(inst, blocks) if self.mode == "parfor" else None
+                    if upd is not None:
+                        # `x[idx] += v` inside a parallel loop is an atomic update, as the
+                        # reference makes it (mlir/tests/test_numpy.py:1039-1057)
+                        sign, val = upd
+                        v = self.scalar(val, rep.dtype)
+                        out.append(f"nmb::atomic_add(&{ref}, ({rep.ctype})({'-' if sign < 0 else ''}({v})));")
+                    else:
+                        out.append(f"{ref} = {self.scalar(inst.value, rep.dtype)};")
                 elif isinstance(inst, ir.Del):
                     continue
                 elif isinstance(inst, ir.Jump):
@@ -778,12 +818,12 @@ class Translator:
                     out.append(f"if ({self.scalar(inst.cond, types.boolean)}) goto L{inst.truebr}; "
                                f"else goto L{inst.falsebr};")
                 elif isinstance(inst, ir.Return):
-                    if self.mode == "kernel":
+                    if self.mode in ("kernel", "parfor"):
                         out.append("return;")
                     else:
                         out.append(f"return {self.scalar(inst.value, self.tir.return_type)};")
                 elif isinstance(inst, (ir.Raise, ir.StaticRaise)):
-                    out.append("return;" if self.mode == "kernel" else "return 0;")
+                    out.append("return;" if self.mode in ("kernel", "parfor") else "return 0;")
                 else:
                     raise UnsupportedError(f"statement {type(inst).__name__} in device code")
             body.append("\n    ".join(out))
@@ -887,3 +927,301 @@ extern "C" __global__ void nmb_kernel({', '.join(kparams)}) {{
 }}
 """
     return CompiledKernel(src, "nmb_kernel", layout, tr.uses_barrier)
+
+
+# ------------------------------------------------------- prange loop nests ---
+class CompiledParfor(CompiledKernel):
+    """A function whose outermost `prange` loop is the grid.
+
+    `extents(args)` gives the trip counts of the parallel loops the host could
+    work out from the arguments (None where it could not); the loops are
+    grid-strided, so any launch shape is correct and the extents only size it."""
+
+    def __init__(self, source, name, param_layout, inner_parallel, extent_fns):
+        CompiledKernel.__init__(self, source, name, param_layout, False)
+        self.inner_parallel = inner_parallel
+        self.extent_fns = extent_fns
+
+    def extents(self, args):
+        out = []
+        for fn in self.extent_fns:
+            try:
+                out.append(None if fn is None else max(0, int(fn(args))))
+            except Exception:
+                out.append(None)
+        return out
+
+
+def uses_prange(py_func):
+    code = getattr(py_func, "__code__", None)
+    return code is not None and "prange" in code.co_names
+
+
+def _single_defs(blocks, ir):
+    defs = {}
+    for blk in blocks.values():
+        for inst in blk.body:
+            if isinstance(inst, ir.Assign):
+                defs.setdefault(inst.target.name, []).append(inst.value)
+    return defs
+
+
+def _resolve(defs, ir, name):
+    """Follows single-assignment copies to the defining expression."""
+    seen = 0
+    while seen < 64:
+        d = defs.get(name)
+        if d is None or len(d) != 1:
+            return None
+        if isinstance(d[0], ir.Var):
+            name = d[0].name
+            seen += 1
+            continue
+        return d[0]
+    return None
+
+
+def _extent_fn(tr, defs, call_expr):
+    """Host-side trip count of `prange(...)` as a function of the call's
+    Python arguments, for the common forms (argument scalars, shapes, len,
+    constants and + - * // of those); None when it cannot be told."""
+    import operator as op
+
+    ir, types = tr.ir, tr.types
+
+    def sym(var, depth=0):
+        if depth > 16:
+            return None
+        name = var.name
+        if name in tr.consts and isinstance(tr.consts[name], (int, np.integer)):
+            v = int(tr.consts[name])
+            return lambda args: v
+        e = _resolve(defs, ir, name)
+        if e is None:
+            return None
+        if isinstance(e, ir.Arg):
+            k = e.index
+            if _is_scalar(types.unliteral(tr.vtype(name))):
+                return lambda args: int(args[k])
+            return None
+        if isinstance(e, (ir.Const, ir.Global, ir.FreeVar)):
+            if isinstance(e.value, (int, np.integer)) and not isinstance(e.value, bool):
+                v = int(e.value)
+                return lambda args: v
+            return None
+        if not isinstance(e, ir.Expr):
+            return None
+        if e.op in ("static_getitem", "getitem"):
+            base = _resolve(defs, ir, e.value.name)
+            if (isinstance(base, ir.Expr) and base.op == "getattr" and base.attr == "shape"):
+                arr = _resolve(defs, ir, base.value.name)
+                idx = e.index if e.op == "static_getitem" else None
+                if isinstance(arr, ir.Arg) and isinstance(idx, int):
+                    k = arr.index
+                    return lambda args: args[k].shape[idx]
+            return None
+        if e.op == "call":
+            try:
+                fn = tr.callee(e.func)
+            except Exception:
+                return None
+            if fn is len and len(e.args) == 1:
+                arr = _resolve(defs, ir, e.args[0].name)
+                if isinstance(arr, ir.Arg):
+                    k = arr.index
+                    return lambda args: args[k].shape[0]
+            return None
+        if e.op == "getattr" and e.attr == "size":
+            arr = _resolve(defs, ir, e.value.name)
+            if isinstance(arr, ir.Arg):
+                k = arr.index
+                return lambda args: args[k].size
+            return None
+        if e.op in ("binop", "inplace_binop") and e.fn in (op.add, op.sub, op.mul, op.floordiv,
+                                                           op.iadd, op.isub, op.imul, op.ifloordiv):
+            a, b = sym(e.lhs, depth + 1), sym(e.rhs, depth + 1)
+            if a is None or b is None:
+                return None
+            f = {op.iadd: op.add, op.isub: op.sub, op.imul: op.mul, op.ifloordiv: op.floordiv}.get(e.fn, e.fn)
+            return lambda args: f(a(args), b(args))
+        return None
+
+    parts = [sym(a) for a in call_expr.args]
+    if any(p is None for p in parts):
+        return None
+    if len(parts) == 1:
+        return lambda args: parts[0](args)
+    if len(parts) == 2:
+        return lambda args: parts[1](args) - parts[0](args)
+
+    def trip(args):
+        lo, hi, st = (f(args) for f in parts)
+        return len(range(lo, hi, st))
+
+    return trip
+
+
+def compile_parfor(py_func, args, fastmath=False):
+    """njit function with `prange` loops -> one CUDA kernel.
+
+    The reference turns every parallel loop nest of an njit function into a
+    `gpu.launch` (mlir/tests/test_gpu.py:1523-1613: ConvertParallelLoopToGpu).
+    Here the function becomes one kernel: the outermost `prange` is
+    grid-strided over the y (or only) grid dimension; a `prange` directly
+    inside it is grid-strided over x when its iterations are independent and
+    nothing else in the outer body has side effects; deeper loops run
+    sequentially in the thread.  Statements before the loop run in every
+    thread, so they may only compute scalars."""
+    from numba.core import types
+    from numba.core.analysis import compute_cfg_from_blocks, compute_live_map, compute_use_defs
+
+    from . import kernel_impl as K
+
+    argtypes = [_argtype_of(a) for a in args]
+    tir = typed_ir(py_func, argtypes)
+    if not isinstance(tir.return_type, types.NoneType):
+        raise UnsupportedError(
+            f"{py_func.__name__}: a function with prange loops must return None (results go to "
+            "array arguments)")
+    tr = Translator(tir, "parfor", "nmb_parfor")
+    ir = tr.ir
+    blocks = tir.func_ir.blocks
+    cfg = compute_cfg_from_blocks(blocks)
+    loops = cfg.loops()
+    defs = _single_defs(blocks, ir)
+    usedefs = compute_use_defs(blocks)
+    live = compute_live_map(cfg, blocks, usedefs.usemap, usedefs.defmap)
+
+    def prange_call_of(loop):
+        """(name of the range variable, call expression) when `loop` iterates a prange."""
+        for inst in blocks[loop.header].body:
+            if (isinstance(inst, ir.Assign) and isinstance(inst.value, ir.Expr)
+                    and inst.value.op == "iternext"):
+                it = _resolve(defs, ir, inst.value.value.name)
+                if not (isinstance(it, ir.Expr) and it.op == "getiter"):
+                    return None
+                name = it.value.name
+                while True:  # the variable the call was assigned to
+                    d = defs.get(name)
+                    if d is None or len(d) != 1:
+                        return None
+                    if isinstance(d[0], ir.Var):
+                        name = d[0].name
+                        continue
+                    break
+                call = d[0]
+                if not (isinstance(call, ir.Expr) and call.op == "call"):
+                    return None
+                fn = tr.callee(call.func)
+                if getattr(fn, "__name__", "") == "prange":
+                    return name, call
+                return None
+        return None
+
+    def side_effects(labels):
+        for lb in labels:
+            for inst in blocks[lb].body:
+                if isinstance(inst, (ir.SetItem, ir.StaticSetItem)):
+                    return True
+                if (isinstance(inst, ir.Assign) and isinstance(inst.value, ir.Expr)
+                        and inst.value.op == "call"):
+                    try:
+                        fn = tr.callee(inst.value.func)
+                    except Exception:
+                        return True
+                    if fn in (K.atomic_add, K.atomic_sub, K.barrier, K.mem_fence) or fn in K.GROUP_REDUCE:
+                        return True
+        return False
+
+    def body_defs(loop):
+        out = set()
+        for lb in loop.body:
+            out |= usedefs.defmap[lb]
+        return out
+
+    def independent(loop):
+        """No scalar is carried from one iteration to the next or out of the loop."""
+        d = body_defs(loop)
+        carried = {v for v in live[loop.header] & d}
+        escaping = set()
+        for ex in loop.exits:
+            escaping |= live[ex] & d
+        return carried, escaping
+
+    top = [lp for lp in loops.values()
+           if not any(lp.header in o.body and o is not lp for o in loops.values())]
+    par_top = [(lp, prange_call_of(lp)) for lp in top]
+    par_top = [(lp, pc) for lp, pc in par_top if pc is not None]
+    if len(par_top) != 1:
+        raise UnsupportedError(
+            f"{py_func.__name__}: exactly one outermost prange loop per function is supported "
+            f"(found {len(par_top)})")
+    outer, (outer_name, outer_call) = par_top[0]
+    carried, escaping = independent(outer)
+    if carried or escaping:
+        raise UnsupportedError(
+            f"{py_func.__name__}: scalar(s) {sorted(carried | escaping)} are carried across or out of "
+            "the prange loop (reductions over prange are not supported; use an array reduction or "
+            "atomic.add)")
+    if side_effects(set(blocks) - set(outer.body)):
+        raise UnsupportedError(
+            f"{py_func.__name__}: array stores outside the prange loop are not supported")
+
+    inner = None
+    level2 = [lp for lp in loops.values() if lp is not outer and lp.header in outer.body
+              and not any(lp.header in o.body and o is not lp and o is not outer for o in loops.values())]
+    cands = [(lp, prange_call_of(lp)) for lp in level2]
+    cands = [(lp, pc) for lp, pc in cands if pc is not None]
+    if len(cands) == 1 and len(level2) == 1:
+        lp, (nm, call) = cands[0]
+        c2, e2 = independent(lp)
+        if not c2 and not e2 and not side_effects(set(outer.body) - set(lp.body)):
+            inner = (lp, nm, call)
+
+    if inner is not None:
+        tr.par_ranges[outer_name] = ("nmb_oid", "nmb_on")
+        tr.par_ranges[inner[1]] = ("nmb_iid", "nmb_in")
+        ids = ("const int64_t nmb_oid = (int64_t)blockIdx.y * blockDim.y + threadIdx.y, "
+               "nmb_on = (int64_t)gridDim.y * blockDim.y, "
+               "nmb_iid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, "
+               "nmb_in = (int64_t)gridDim.x * blockDim.x;")
+    else:
+        tr.par_ranges[outer_name] = ("nmb_oid", "nmb_on")
+        ids = ("const int64_t nmb_oid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, "
+               "nmb_on = (int64_t)gridDim.x * blockDim.x;")
+
+    pnames = [f"p{i}" for i in range(len(argtypes))]
+    body = tr.translate(pnames)
+    if tr.shared_decls or tr.uses_barrier:
+        raise UnsupportedError("work-group local memory and barriers belong to @kernel functions")
+    written = {int(r[6:-1]) for r in tr.written_params if r.startswith("<param")}
+    kparams, layout = [], []
+    for i, t in enumerate(argtypes):
+        t = types.unliteral(t)
+        if isinstance(t, types.Array):
+            ct = c_scalar_type(t.dtype)
+            # no __restrict__: the same buffer may be passed as input and output
+            kparams.append(f"{ct}* p{i}_p" if i in written else f"const {ct}* p{i}_p")
+            kparams += [f"int64_t p{i}_s{d}" for d in range(t.ndim)]
+            if t.layout != "C":
+                kparams += [f"int64_t p{i}_t{d}" for d in range(t.ndim)]
+            layout.append(("array", t.ndim, t.layout))
+        else:
+            kparams.append(f"{c_scalar_type(t)} p{i}")
+            layout.append(("scalar", np.dtype(str(t))))
+    opts = "" if fastmath else " --fmad=false"
+    src = f"""//NMB200:CUDA-SOURCE
+//NMB200:OPTIONS{opts}
+#include "nmb_device.cuh"
+extern "C" __global__ void nmb_parfor({', '.join(kparams)}) {{
+    {ids}
+    const int64_t nmb_gs[3] = {{1, 1, 1}};
+    (void)nmb_gs;
+    {chr(10).join('    ' + d for d in tr.decls)}
+    {(chr(10) + '    ').join(body)}
+}}
+"""
+    fns = [_extent_fn(tr, defs, outer_call)]
+    if inner is not None:
+        fns.append(_extent_fn(tr, defs, inner[2]))
+    return CompiledParfor(src, "nmb_parfor", layout, inner is not None, fns)

@@ -41,6 +41,32 @@ def check_device_args(args):
     return devs
 
 
+_MAX_PARFOR_BLOCKS = 148 * 32  # the loops are grid-strided: more blocks than this only add launch cost
+
+
+def parfor_launch_shape(extents, inner_parallel):
+    """Launch shape of a prange kernel from the trip counts the host knows
+    (None = unknown).  Returns (None, None) for an empty loop."""
+    def ceil_div(a, b):
+        return (a + b - 1) // b
+
+    n = extents[0]
+    if n == 0:
+        return None, None
+    if not inner_parallel:
+        blocks = 148 * 8 if n is None else min(ceil_div(n, 256), _MAX_PARFOR_BLOCKS)
+        return (blocks,), (256,)
+    m = extents[1]
+    if m == 0:
+        return None, None
+    bx = 32 if m is None else min(256, 1 << max(0, (m - 1).bit_length()))
+    by = 256 // bx
+    gx = 8 if m is None else min(ceil_div(m, bx), 1024)
+    gy = 148 if n is None else ceil_div(n, by)
+    gy = max(1, min(gy, _MAX_PARFOR_BLOCKS // gx, 65535))
+    return (gx, gy), (bx, by)
+
+
 class Dispatcher:
     """Callable returned by `njit`: traces the function on its first call per
     argument signature, then replays the recorded launches."""
@@ -50,6 +76,8 @@ class Dispatcher:
         self.py_func = py_func
         self.options = dict(options)
         self._plans = {}
+        self._parfor = None
+        self._parfor_kernels = {}
 
     def __call__(self, *args, **kwargs):
         if kwargs:
@@ -65,6 +93,12 @@ class Dispatcher:
         for a in args:
             if isinstance(a, np.ndarray):
                 raise TypeError("host NumPy arrays cannot be mixed with device arrays")
+        if self._parfor is None:
+            from . import codegen_ir
+
+            self._parfor = codegen_ir.uses_prange(self.py_func)
+        if self._parfor:
+            return self._call_parfor(args)
         key = lazy.signature_of(args)
         plan = self._plans.get(key) if key is not None else None
         if plan is not None:
@@ -74,6 +108,26 @@ class Dispatcher:
         if plan is not None and key is not None:
             self._plans[key] = plan
         return result
+
+    def _call_parfor(self, args):
+        """Functions written as `prange` loop nests are compiled as a whole:
+        the outermost parallel loop becomes the grid
+        (numba_mlir/mlir/tests/test_gpu.py:1523-1613)."""
+        from . import codegen_ir, kernel_impl
+
+        key = kernel_impl.call_signature(args)
+        ck = self._parfor_kernels.get(key)
+        if ck is None:
+            ck = codegen_ir.compile_parfor(self.py_func, args,
+                                           fastmath=bool(self.options.get("fastmath", False)))
+            self._parfor_kernels[key] = ck
+        queue = next(a.queue for a in args if isinstance(a, DeviceArray))
+        kernel = queue.get_kernel(queue.load_module(ck.source.encode()), ck.name)
+        grid, block = parfor_launch_shape(ck.extents(args), ck.inner_parallel)
+        if grid is None:
+            return None
+        queue.launch(kernel, grid, block, kernel_impl.marshal_params(args, ck.param_layout))
+        return None
 
     def trace_dry(self, *args):
         """Records the plan and generates the kernels without a device (used

@@ -230,6 +230,33 @@ def _process_dims(dims):
     _raise_error(f"Invalid dimentions type: {type(dims)}")
 
 
+def call_signature(args):
+    """Cache key of a compiled kernel: what its code depends on."""
+    sig = []
+    for a in args:
+        if isinstance(a, DeviceArray):
+            sig.append(("arr", a.dtype.name, a.ndim, a.is_c_contiguous))
+        else:
+            sig.append(("scalar", type(a).__name__, getattr(a, "dtype", None) and a.dtype.name))
+    return tuple(sig)
+
+
+def marshal_params(args, param_layout):
+    """Python arguments -> launch parameter list: an array is its pointer,
+    its shape and, unless C-contiguous, its element strides (the flattened
+    memref form of numba_mlir/mlir/lib/Conversion/GpuRuntimeToLlvm.cpp:507-536)."""
+    params = []
+    for a, lay in zip(args, param_layout):
+        if lay[0] == "array":
+            params.append(("ptr", a.ptr))
+            params += [np.int64(s) for s in a.shape]
+            if lay[2] != "C":
+                params += [np.int64(st // a.dtype.itemsize) for st in a.strides]
+        else:
+            params.append(lay[1].type(a))
+    return params
+
+
 class Kernel:
     """`kernel(func)`; configure with `k[global_size, local_size]`, then call."""
 
@@ -266,13 +293,7 @@ class Kernel:
         return self.configure(gs, ls)
 
     def _signature(self, args):
-        sig = []
-        for a in args:
-            if isinstance(a, DeviceArray):
-                sig.append(("arr", a.dtype.name, a.ndim, a.is_c_contiguous))
-            else:
-                sig.append(("scalar", type(a).__name__, getattr(a, "dtype", None) and a.dtype.name))
-        return tuple(sig)
+        return call_signature(args)
 
     def __call__(self, *args, **kwargs):
         if kwargs:
@@ -302,15 +323,7 @@ class Kernel:
         grid = tuple((g + l - 1) // l for g, l in zip(self.global_size, local))
         if any(g == 0 for g in self.global_size):
             return
-        params = []
-        for a, lay in zip(args, ck.param_layout):
-            if lay[0] == "array":
-                params.append(("ptr", a.ptr))
-                params += [np.int64(s) for s in a.shape]
-                if lay[2] != "C":
-                    params += [np.int64(st // a.dtype.itemsize) for st in a.strides]
-            else:
-                params.append(lay[1].type(a))
+        params = marshal_params(args, ck.param_layout)
         gs = tuple(self.global_size) + (1,) * (3 - ndim)
         params += [np.int64(g) for g in gs]
         queue.launch(kernel, grid, local, params)

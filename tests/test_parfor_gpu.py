@@ -1,0 +1,142 @@
+"""`prange` loop nests in `njit` functions on the GPU, after the reference's
+tests (numba_mlir/mlir/tests/test_gpu.py:1523-1613, test_numpy.py:1039-1057):
+the Python function run on NumPy arrays is the expected result."""
+
+import numba
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+_test_values = [True, False, -3, -2, -1, 0, 1, 2, 3, -2.5, -1.0, -0.5, -0.0, 0.0, 0.5, 1.0, 2.5]
+
+
+def _dev(a):
+    from numba_mlir_b200 import from_host
+
+    return from_host(a)
+
+
+def test_parfor_simple1(queue):
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import runtime
+
+    def py_func(a, b, c):
+        for i in numba.prange(len(a)):
+            c[i] = a[i] + b[i]
+
+    gpu_func = nm.njit(py_func)
+    a = np.arange(1024, dtype=np.float32)
+    b = np.arange(1024, dtype=np.float32) * 3
+    want = np.zeros(a.shape, a.dtype)
+    py_func(a, b, want)
+    got = _dev(np.zeros(a.shape, a.dtype))
+    before = runtime.launch_count()
+    gpu_func(_dev(a), _dev(b), got)
+    assert runtime.launch_count() - before == 1  # one launch for the loop nest
+    np.testing.assert_equal(got.copy_to_host(), want)
+
+
+@pytest.mark.parametrize("val", _test_values)
+def test_parfor_scalar(queue, val):
+    import numba_mlir_b200 as nm
+
+    def py_func(a, b, c, d):
+        for i in numba.prange(len(a)):
+            c[i] = a[i] + b[i] + d
+
+    a = np.arange(1024, dtype=np.float32)
+    b = np.arange(1024, dtype=np.float32) * 3
+    want = np.zeros(a.shape, a.dtype)
+    py_func(a, b, want, val)
+    got = _dev(np.zeros(a.shape, a.dtype))
+    nm.njit(py_func)(_dev(a), _dev(b), got, val)
+    np.testing.assert_equal(got.copy_to_host(), want)
+
+
+@pytest.mark.parametrize("val", [True, -3, 0, 2.5])
+def test_parfor_scalar_capture(queue, val):
+    import numba_mlir_b200 as nm
+
+    def py_func(a, b, c):
+        for i in numba.prange(len(a)):
+            c[i] = a[i] + b[i] + val
+
+    a = np.arange(1024, dtype=np.float32)
+    b = np.arange(1024, dtype=np.float32) * 3
+    want = np.zeros(a.shape, a.dtype)
+    py_func(a, b, want)
+    got = _dev(np.zeros(a.shape, a.dtype))
+    nm.njit(py_func)(_dev(a), _dev(b), got)
+    np.testing.assert_equal(got.copy_to_host(), want)
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (7, 5), (33, 1000), (1000, 33), (257, 513)])
+def test_parfor_2d_nest(queue, shape):
+    import numba_mlir_b200 as nm
+
+    def py_func(a, b, c):
+        for i in numba.prange(a.shape[0]):
+            for j in numba.prange(a.shape[1]):
+                c[i, j] = a[i, j] * 2 + b[j, i]
+
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal(shape).astype(np.float32)
+    b = rng.standard_normal(shape[::-1]).astype(np.float32)
+    want = np.zeros(shape, np.float32)
+    py_func(a, b, want)
+    got = _dev(np.zeros(shape, np.float32))
+    nm.njit(py_func, parallel=True)(_dev(a), _dev(b), got)
+    np.testing.assert_equal(got.copy_to_host(), want)
+
+
+def test_parfor_inner_sequential_reduction_and_strided_range(queue):
+    import numba_mlir_b200 as nm
+
+    def py_func(a, c):
+        for i in numba.prange(1, a.shape[0], 2):
+            s = np.float32(0)
+            for j in range(a.shape[1]):
+                s += a[i, j]
+            c[i] = s
+
+    rng = np.random.default_rng(4)
+    a = rng.integers(-8, 8, (301, 77)).astype(np.float32)  # exact in float32 in any order
+    want = np.full(301, -1, np.float32)
+    py_func(a, want)
+    got = _dev(np.full(301, -1, np.float32))
+    nm.njit(py_func, parallel=True)(_dev(a), got)
+    np.testing.assert_equal(got.copy_to_host(), want)
+
+
+def test_parfor_empty_and_large(queue):
+    import numba_mlir_b200 as nm
+
+    def py_func(a, c):
+        for i in numba.prange(len(a)):
+            c[i] = a[i] + 1
+
+    f = nm.njit(py_func, parallel=True)
+    e = _dev(np.zeros(0, np.int32))
+    f(e, e)  # empty loop: nothing launched, nothing raised
+    n = (1 << 22) + 3  # more iterations than threads in the grid: grid-strided
+    a = np.arange(n, dtype=np.int32)
+    got = _dev(np.zeros(n, np.int32))
+    f(_dev(a), got)
+    np.testing.assert_equal(got.copy_to_host(), a + 1)
+
+
+@pytest.mark.parametrize("dtype", [np.int32, np.int64, np.float32, np.float64])
+def test_prange_atomic(queue, dtype):
+    import numba_mlir_b200 as nm
+
+    def py_func(n, s, res):
+        for i in numba.prange(n):
+            res[i % s] += dtype(i)
+
+    N, S = 10000, 10
+    want = np.zeros(S, dtype)
+    py_func(N, S, want)
+    got = _dev(np.zeros(S, dtype))
+    nm.njit(py_func, parallel=True)(N, S, got)
+    np.testing.assert_allclose(got.copy_to_host(), want, rtol=1e-5)
