@@ -115,13 +115,13 @@ class BlackScholes(Workload):
         workloads.black_scholes(*self.d_in, self.rate, self.vol, *self.d_out)
 
     def step_e2e(self):
-        """Host buffers in, host buffers out, through the public API."""
-        for d, h in zip(self.d_in, self.h_in):
-            d.copy_from_host(h, wait=False)
-        self.step_device()
-        for d, h in zip(self.d_out, self.h_out):
-            d.copy_to_host(h, wait=False)
-        self.queue.synchronize()
+        """Host buffers in, host buffers out, through the public API: the
+        chunked pipeline overlaps copy-in, kernels and copy-out."""
+        import numba_mlir_b200 as nm
+        from numba_mlir_b200 import workloads
+
+        nm.map_host(workloads.black_scholes, self.h_in, self.h_out, scalars=(self.rate, self.vol),
+                    queue=self.queue)
 
     def check(self):
         call = self.d_out[0][:1024].copy_to_host()

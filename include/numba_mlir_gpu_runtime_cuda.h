@@ -141,6 +141,14 @@ void *gpuxMemcpy(void *queue, void *dst, const void *src, size_t bytes,
 void *gpuxMemset(void *queue, void *dst, int value, size_t bytes, void *events);
 /* Records an event at the current tail of the queue's stream. */
 void *gpuxRecordEvent(void *queue);
+/* Orders everything submitted to the queue from now on after the events of a
+ * NULL-terminated Event*[] (events of other queues of the same device become
+ * stream dependencies; nothing blocks on the host).  Returns 0 on success.
+ * The launch, alloc, memcpy and memset entries take the same kind of list;
+ * this entry is for callers that submit through a layer which does not pass
+ * one on.  No counterpart in the reference, whose host code waits on every
+ * event (GpuRuntimeToLlvm.cpp:619-622). */
+int gpuxQueueWaitEvents(void *queue, void *events);
 /* Milliseconds between two completed events of the same device. */
 float gpuxEventElapsedMs(void *startEvent, void *endEvent);
 /* Blocks until everything submitted to the queue has finished. */

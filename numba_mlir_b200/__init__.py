@@ -16,4 +16,6 @@ from .device_array import (  # noqa: F401
     zeros,
 )
 
+from .streaming import HostPipeline, map_host  # noqa: F401,E402
+
 __version__ = "0.1.0"

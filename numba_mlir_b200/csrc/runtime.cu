@@ -1066,6 +1066,16 @@ GPUX_EXPORT void *gpuxMemset(void *queue, void *dst, int value, size_t bytes,
   return recordEvent(q);
 }
 
+GPUX_EXPORT int gpuxQueueWaitEvents(void *queue, void *events) {
+  LOG_FUNC();
+  if (!queue) {
+    nmb::setError("gpuxQueueWaitEvents: null queue");
+    return 1;
+  }
+  Queue *q = toQueue(queue);
+  return setDevice(q) && waitDeps(q, events) ? 0 : 1;
+}
+
 GPUX_EXPORT void *gpuxRecordEvent(void *queue) {
   LOG_FUNC();
   if (!queue) {

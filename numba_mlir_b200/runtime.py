@@ -75,6 +75,7 @@ SIGNATURES = {
     "gpuxMemcpy": (_vp, [_vp, _vp, _vp, _sz, _i, _vp]),
     "gpuxMemset": (_vp, [_vp, _vp, _i, _sz, _vp]),
     "gpuxRecordEvent": (_vp, [_vp]),
+    "gpuxQueueWaitEvents": (_i, [_vp, _vp]),
     "gpuxEventElapsedMs": (ctypes.c_float, [_vp, _vp]),
     "gpuxQueueSynchronize": (None, [_vp]),
     "gpuxQueueGetStream": (_vp, [_vp]),
@@ -263,6 +264,15 @@ class _PreparedParams:
                 slot.value = a.item() if hasattr(a, "item") else a
 
 
+def _event_list(events):
+    """NULL-terminated Event*[] (GpuRuntimeToLlvm.cpp:196-225) or None."""
+    events = [e for e in (events or ()) if e]
+    if not events:
+        return None
+    arr = (ctypes.c_void_p * (len(events) + 1))(*events, None)
+    return ctypes.cast(arr, ctypes.c_void_p)
+
+
 class Queue:
     """Owning wrapper of a gpux queue handle plus the handles created from it.
 
@@ -390,14 +400,22 @@ class Queue:
     def free(self, ptr):
         self.lib.gpuxDeAlloc(self.handle, ptr)
 
-    def memcpy(self, dst, src, nbytes, kind=COPY_DEFAULT, wait=False):
-        ev = self.lib.gpuxMemcpy(self.handle, dst, src, int(nbytes), kind, None)
+    def memcpy(self, dst, src, nbytes, kind=COPY_DEFAULT, wait=False, deps=None):
+        """Asynchronous copy on the queue's stream, after the events in `deps`."""
+        ev = self.lib.gpuxMemcpy(self.handle, dst, src, int(nbytes), kind, _event_list(deps))
         if not ev:
             check()
             raise GpuRuntimeError("gpuxMemcpy returned NULL")
         if wait:
             self.lib.gpuxWait(self.handle, ev)
         self.lib.gpuxDestroyEvent(self.handle, ev)
+
+    def wait_events(self, events):
+        """Later submissions to this queue run after `events` (events of other
+        queues of the device included); the host does not block."""
+        if events and self.lib.gpuxQueueWaitEvents(self.handle, _event_list(events)):
+            check()
+            raise GpuRuntimeError("gpuxQueueWaitEvents failed")
 
     def memset(self, dst, value, nbytes):
         ev = self.lib.gpuxMemset(self.handle, dst, int(value), int(nbytes), None)

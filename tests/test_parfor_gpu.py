@@ -140,3 +140,34 @@ def test_prange_atomic(queue, dtype):
     got = _dev(np.zeros(S, dtype))
     nm.njit(py_func, parallel=True)(N, S, got)
     np.testing.assert_allclose(got.copy_to_host(), want, rtol=1e-5)
+
+
+def test_pairwise2(queue):
+    """The reference's direct-loop pairwise distance
+    (numba_mlir/mlir/tests/test_gpu.py:2226-2266): both prange loops map to
+    the grid, the k loop runs in the thread."""
+    import numba_mlir_b200 as nm
+
+    def py_func(X1, X2, D):
+        X1_rows = X1.shape[0]
+        X2_rows = X2.shape[0]
+        X1_cols = X1.shape[1]
+
+        for i in numba.prange(X1_rows):
+            for j in numba.prange(X2_rows):
+                d = 0.0
+                for k in range(X1_cols):
+                    tmp = X1[i, k] - X2[j, k]
+                    d += tmp * tmp
+                D[i, j] = np.sqrt(d)
+
+    jit_func = nm.njit(py_func)
+    dims, npoints = 3, 128
+    a = np.arange(npoints * dims, dtype=np.float32).reshape(npoints, dims)
+    b = a + 5
+    res = np.zeros((npoints, npoints), dtype=np.float32)
+    py_func(a, b, res)
+    got = _dev(np.zeros_like(res))
+    jit_func(_dev(a), _dev(b), got)
+    assert jit_func._parfor_kernels and all(k.inner_parallel for k in jit_func._parfor_kernels.values())
+    np.testing.assert_allclose(got.copy_to_host(), res, rtol=1e-5)
