@@ -127,21 +127,6 @@ class BlackScholes(Workload):
         call = self.d_out[0][:1024].copy_to_host()
         assert np.isfinite(call).all()
 
-    def cpu_setup(self, seed, fraction=1.0):
-        from oracle import configs as O
-
-        m = max(1, int(self.n * fraction))
-        price, strike, t, rate, vol = self.host_inputs(seed)
-        self.cpu_args = (price[:m].copy(), strike[:m].copy(), t[:m].copy(), rate, vol)
-        self.cpu_out = (np.zeros(m, f32), np.zeros(m, f32))
-        self.cpu_units = m
-        self.cpu_bytes = 20 * m
-        self._cpu_fn = O.black_scholes
-        self._cpu_fn(*self.cpu_args, *self.cpu_out)  # compile, excluded
-
-    def cpu_step(self):
-        self._cpu_fn(*self.cpu_args, *self.cpu_out)
-
 
 class BroadcastAdd(Workload):
     """a (2048, 2048) + b (1, 2048), float32; 33.6 MB per call fits L2, so the
@@ -387,46 +372,89 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------ CPU timing ----
-def time_cpu(workload, seed, budget_s, max_steps):
+def time_cpu(key, budget_s, max_steps):
     """Best-of timing of the CPU oracle on the full workload within a budget."""
     import numba
 
-    workload.cpu_setup(seed)
+    step, nbytes, units, _name = cpu_case(key, 1.0)
+    step()  # compiles; excluded
     times = []
     t_end = time.perf_counter() + budget_s
     while len(times) < max_steps and (len(times) < 3 or time.perf_counter() < t_end):
         t0 = time.perf_counter()
-        workload.cpu_step()
+        step()
         times.append(time.perf_counter() - t0)
-    return times, numba.get_num_threads()
+    return times, numba.get_num_threads(), nbytes, units
+
+
+def cpu_case(key, scale):
+    """The CPU oracle of one benchmark configuration on a `scale` fraction of
+    its leading dimension: (step function, algorithmic bytes, units, name)."""
+    from oracle import configs as O
+
+    if key == "black_scholes":
+        price, strike, t, rate, vol = O.make_inputs("black_scholes", scale)
+        call, put = np.zeros_like(price), np.zeros_like(price)
+        return (lambda: O.black_scholes(price, strike, t, rate, vol, call, put),
+                20 * price.size, price.size, BlackScholes.name)
+    if key == "bcast_add":
+        a, b = O.make_inputs("bcast_add", scale)
+        return lambda: O.bcast_add(a, b), 2 * a.nbytes + b.nbytes, a.size, BroadcastAdd.name
+    if key in ("sum_axis1", "min_axis0", "argmin_axis1"):
+        (a,) = O.make_inputs("reduce_f32", scale)
+        fn = getattr(O, key)
+        out_bytes = {"sum_axis1": 4 * a.shape[0], "min_axis0": 4 * a.shape[1],
+                     "argmin_axis1": 8 * a.shape[0]}[key]
+        return lambda: fn(a), a.nbytes + out_bytes, a.size, f"{key}_f32_16384x4096"
+    if key == "int_sum":
+        (a,) = O.make_inputs("reduce_i32", scale)
+        return lambda: O.int_sum(a), a.nbytes + 8, a.size, IntSum.name
+    if key == "pairwise":
+        x, y = O.make_inputs("pairwise", scale)
+        d = np.zeros((x.shape[0], y.shape[0]), f32)
+        return lambda: O.pairwise(x, y, d), d.nbytes + x.nbytes + y.nbytes, d.size, Pairwise.name
+    if key == "kmeans":
+        pts, cent = O.make_inputs("kmeans", scale)
+        labels = np.zeros(pts.shape[0], np.int32)
+
+        def step():
+            O.kmeans_assign(pts, cent, labels)
+            sums = np.zeros(cent.shape, np.float64)
+            counts = np.zeros(cent.shape[0], np.int64)
+            O.kmeans_accumulate(pts, labels, sums, counts)
+            O.kmeans_update(cent, sums, counts)
+
+        return step, pts.nbytes + labels.nbytes, pts.shape[0], KMeans.name
+    raise ValueError(key)
 
 
 def run_reference(args):
-    """CPU arm: the oracle on the host cores, rank 0 only.  Each step is a
-    bounded sample of the workload, sized so the whole run stays near two
-    minutes whatever --steps is."""
+    """CPU arm: the oracle of --workload on the host cores, rank 0 only.  Each
+    step is a bounded sample of the workload (the leading dimension is halved
+    until the whole run stays near two minutes whatever --steps is)."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    w = BlackScholes()
     import numba
 
     steps = args.steps if args.steps is not None else 20
-    w.cpu_setup(0)
-    t0 = time.perf_counter()
-    w.cpu_step()
-    t_full = time.perf_counter() - t0
-    fraction = 1.0
-    while fraction > 1 / 1024 and (steps + args.warmup) * t_full * fraction > 120.0:
-        fraction /= 2
-    if fraction < 1.0:
-        w.cpu_setup(0, fraction)
+    scale = 1.0
+    while True:
+        step, nbytes, units, name = cpu_case(args.workload, scale)
+        step()  # compiles; excluded
+        t0 = time.perf_counter()
+        step()
+        t_one = time.perf_counter() - t0
+        if scale <= 1 / 1024 or (steps + max(args.warmup, 1)) * t_one <= 120.0:
+            break
+        scale /= 2
+    full_units = WORKLOADS[args.workload]().units_per_step
     for _ in range(max(args.warmup, 1)):
-        w.cpu_step()
+        step()
     t0 = time.perf_counter()
     for _ in range(steps):
-        w.cpu_step()
+        step()
     dt = (time.perf_counter() - t0) / max(steps, 1)
-    value = w.cpu_bytes / dt / 1e9
+    value = nbytes / dt / 1e9
     line = {
         "impl": "reference",
         "metric": METRIC,
@@ -439,16 +467,16 @@ def run_reference(args):
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
-        "dtype": w.dtype,
+        "dtype": WORKLOADS[args.workload]().dtype,
         "data": "synthetic",
-        "config": {"workload": w.name, "elements_per_step": w.cpu_units},
-        "elements_per_s": w.cpu_units / dt,
+        "config": {"workload": name, "elements_per_step": units},
+        "elements_per_s": units / dt,
         "cpu_baseline": {
             "value": value,
             "unit": UNIT,
             "cores": numba.get_num_threads(),
             "kind": "port",
-            "sample": f"{w.cpu_units} of {w.units_per_step} elements per step; upstream "
+            "sample": f"{units} of {full_units} elements per step; upstream "
             f"numba.njit(parallel=True), threading layer {numba.threading_layer()}",
         },
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -649,15 +677,15 @@ def run_gpu(args):
             }
         if others:
             line["other_configs"] = others
-        if world == 1 and not args.no_cpu and hasattr(w, "cpu_setup"):
-            times, threads = time_cpu(w, 0, budget_s=12.0, max_steps=100)
+        if world == 1 and not args.no_cpu:
+            times, threads, cpu_bytes, cpu_units = time_cpu(args.workload, budget_s=12.0, max_steps=100)
             best = min(times)
             line["cpu_baseline"] = {
-                "value": w.cpu_bytes / best / 1e9,
+                "value": cpu_bytes / best / 1e9,
                 "unit": UNIT,
                 "cores": threads,
                 "kind": "port",
-                "sample": f"the full workload ({w.cpu_units} elements) per step, best of "
+                "sample": f"the full workload ({cpu_units} elements) per step, best of "
                 f"{len(times)}; upstream numba.njit(parallel=True)",
                 "ms_per_step": best * 1e3,
             }
