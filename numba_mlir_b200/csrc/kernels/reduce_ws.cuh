@@ -8,8 +8,8 @@
 // steady state needs no cross-warp exchange:
 //
 //   rows, wide (row > 2 KB):  a tile is 8 rows x one 2 KB column chunk (eight
-//       bulk copies); warp w owns row w of the block and accumulates it over
-//       the chunks, then five shuffles finish the row.
+//       bulk copies, one issued by each warp); warp w owns row w of the block
+//       and accumulates it over the chunks, then five shuffles finish the row.
 //   rows, narrow (row <= 2 KB): a tile is a contiguous run of whole rows; the
 //       warps take rows w, w+8, ... of the tile.
 //   columns: a tile is a contiguous run of whole rows (or one 16 KB piece of a
@@ -61,19 +61,25 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
     const int64_t cpr = (cols + CH - 1) / CH; // chunks per row
     const int64_t ntiles = (blk_end - blk_begin) * cpr;
 
+    // Lane 0 of warp w fetches row w's chunk of the tile (a bulk copy costs the
+    // issuing thread about 0.1 us, so one thread issuing all eight would hold
+    // the CTA back); thread 0 posts the byte count of the whole tile.  Every
+    // warp calls this for the same tiles in the same order.
     auto issue = [&](int64_t i) {
       const int s = (int)(i % kStages);
       const int64_t r0 = (blk_begin + i / cpr) * kRowsPerBlock, c0 = (i % cpr) * CH;
       const int nr = (int)(rows - r0 < kRowsPerBlock ? rows - r0 : kRowsPerBlock);
       const uint32_t bytes = (uint32_t)((cols - c0 < CH ? cols - c0 : CH) * sizeof(T));
-      mbar_expect_tx(&sm.full[s], bytes * nr);
-      for (int j = 0; j < nr; ++j)
-        bulk_load(tiles + (int64_t)s * TILE + (int64_t)j * CH, a + (r0 + j) * cols + c0, bytes,
+      if (tid == 0)
+        mbar_expect_tx(&sm.full[s], bytes * nr);
+      if (warp < nr)
+        bulk_load(tiles + (int64_t)s * TILE + (int64_t)warp * CH, a + (r0 + warp) * cols + c0, bytes,
                   &sm.full[s]);
     };
-    if (tid == 0)
+    if (lane == 0)
       for (; issued < kStages && issued < ntiles; ++issued)
         issue(issued);
+    issued = ntiles < kStages ? ntiles : kStages; // the same count in every thread
 
     Fast f[VEC];
 #pragma unroll
@@ -117,8 +123,11 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
         }
       }
       __syncthreads(); // the whole CTA is done with stage s
-      if (tid == 0 && issued < ntiles)
-        issue(issued++);
+      if (issued < ntiles) {
+        if (lane == 0)
+          issue(issued);
+        ++issued;
+      }
     }
   } else {
     // ---- narrow rows ----------------------------------------------------------

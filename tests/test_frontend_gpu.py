@@ -213,6 +213,38 @@ def test_unary_math_against_oracle_within_2ulp(queue):
     assert ulps(got, cerf(x)) <= 2
 
 
+def test_erf_float32_within_2ulp_of_the_true_value(queue):
+    """The library's own erf: every float32 in [2^-7, 4.5) at stride 3 (both
+    ranges, the switch at 1 and the saturation at 3.92), a logarithmic sweep
+    below, and the special values, against float64 erf rounded to float32."""
+    import numba_mlir_b200 as nm
+
+    @nm.vectorize
+    def gerf(x):
+        return math.erf(x)
+
+    lo, hi = np.float32(2.0**-7).view(np.int32), np.float32(4.5).view(np.int32)
+    pos = np.arange(lo, hi, 3, dtype=np.int32).view(np.float32)
+    tiny = np.logspace(-44, -2, 100000).astype(np.float32)
+    x = np.concatenate([pos, -pos[::7], tiny, -tiny[::3],
+                        np.array([0.0, -0.0, 1.0, -1.0, 0.99999994, 1.0000001, 3.9, 3.92, 4.0, 4.0000005,
+                                  10.0, -10.0, 1e30, np.inf, -np.inf], np.float32)])
+    got = nm.njit(lambda a: gerf(a))(_dev(x)).copy_to_host()
+    from scipy import special
+
+    truth = special.erf(x.astype(np.float64))
+    want = truth.astype(np.float32)
+    ulp = np.spacing(np.abs(want)).astype(np.float64)
+    ok = np.isfinite(truth) & (want != 0)
+    err = np.abs(got.astype(np.float64) - truth)[ok] / ulp[ok]
+    assert err.max() <= 2.0, (err.max(), x[ok][err.argmax()])
+    assert np.array_equal(np.signbit(got), np.signbit(x))
+    assert got[x == 0].tolist() == [0.0, -0.0] and np.signbit(got[x == 0]).tolist() == [False, True]
+    assert got[np.isinf(x)].tolist() == [1.0, -1.0]
+    nan = nm.njit(lambda a: gerf(a))(_dev(np.array([np.nan], np.float32))).copy_to_host()
+    assert np.isnan(nan[0])
+
+
 def test_where_compare_cast_and_strided_operands(queue):
     import numba_mlir_b200 as nm
 

@@ -96,7 +96,8 @@ def test_reference_reduce_matrix(queue, op, axis, dtype):
 
 
 @pytest.mark.parametrize("shape", [(3, 12000), (5, 4096 * 3 + 8), (1000, 4), (77, 516), (4100, 260),
-                                   (2, 1 << 20), (33, 13), (13, 33)])
+                                   (2, 1 << 20), (33, 13), (13, 33), (700, 4096), (37, 4100),
+                                   (9, 8192), (1, 4096), (600, 2052)])
 @pytest.mark.parametrize("op", ["sum", "min", "max", "argmin", "argmax"])
 def test_axis_shapes_float32(queue, shape, op):
     """Multi-tile rows, many-rows-per-tile, column tails and unaligned shapes
