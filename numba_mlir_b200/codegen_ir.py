@@ -252,6 +252,7 @@ class Translator:
         self.written_params = set()
         self.alias = {}           # array var -> root (param) var
         self.uses_barrier = False
+        self.uses_group_reduce = False
         self.counter = 0
         self.par_ranges = {}      # range variable -> (id expr, count expr): grid-strided loops
 
@@ -515,6 +516,21 @@ class Translator:
             else:
                 idx_exprs = self.index_list(value.index_var if value.op == "static_getitem" else value.index)
             self.declare(tname)
+            if isinstance(ttype, types.Array):
+                # fewer integer indices than dimensions: a view of the trailing dimensions
+                # (numba_mlir/mlir/tests/test_gpu.py:429-452)
+                self.declare(src.name)
+                srep, trep = self.arrays[src.name], self.arrays[tname]
+                k = len(idx_exprs)
+                if k + trep.ndim != srep.ndim:
+                    raise UnsupportedError("only integer indices (no slices) select sub-arrays in kernels")
+                off = " + ".join(f"({i}) * {st_}" for i, st_ in zip(idx_exprs, srep.strides)) or "0"
+                stm = [f"{trep.ptr} = {srep.ptr} + ({off});"]
+                for d in range(trep.ndim):
+                    stm.append(f"{trep.shape[d]} = {srep.shape[d + k]}; {trep.strides[d]} = {srep.strides[d + k]};")
+                out.append(" ".join(stm))
+                self.alias[tname] = src.name
+                return
             out.append(f"{self.cname(tname)} = {self.cast_expr(self.element_ref(src, idx_exprs), None, ttype)};")
         elif isinstance(st, (types.UniTuple, types.Tuple, types.NamedUniTuple)):
             if value.op != "static_getitem" or not isinstance(value.index, int):
@@ -574,6 +590,13 @@ class Translator:
         tname = target.name
         rt = types.unliteral(sig.return_type)
         args = list(expr.args)
+        if expr.kws:
+            # keyword arguments are folded into the positional order of the typed signature
+            pysig = getattr(sig, "pysig", None)
+            if pysig is None:
+                raise UnsupportedError(f"keyword arguments in a call to {fn!r}")
+            kw = dict(expr.kws)
+            args += [kw[n] for n in list(pysig.parameters)[len(args):] if n in kw]
         c = None
 
         def sargs():
@@ -626,8 +649,9 @@ class Translator:
             scratch = self.fresh("nmb_red")
             self.shared_decls.append(f"__shared__ {ct} {scratch}[32];")
             opname, neutral = K.GROUP_REDUCE[fn]
-            c = (f"nmb::block_reduce(({ct})({self.scalar(args[0], rt)}), nmb::{opname}(), "
-                 f"nmb::neutral_{neutral}<{ct}>(), {scratch})")
+            self.uses_group_reduce = True
+            c = (f"nmb::group_reduce(({ct})({self.scalar(args[0], rt)}), nmb::{opname}(), "
+                 f"nmb::neutral_{neutral}<{ct}>(), {scratch}, nmb_gr_vals, nmb_active, nmb_group_full)")
         elif fn in (math.sqrt, math.exp, math.log, math.erf, math.sin, math.cos, math.tan, math.tanh,
                     math.floor, math.ceil, math.fabs, math.acos, math.asin, math.atan, math.atan2,
                     math.pow, math.log2, math.log10, math.erfc, math.expm1, math.log1p, math.sinh,
@@ -913,14 +937,29 @@ def compile_kernel(py_func, args, ndim, fastmath=False):
             layout.append(("scalar", np.dtype(str(t))))
     kparams += ["int64_t nmb_g0", "int64_t nmb_g1", "int64_t nmb_g2"]
     opts = "" if fastmath else " --fmad=false"
+    group_prologue = ""
+    if tr.uses_group_reduce:
+        # group reductions need to know which work-items of the group exist
+        group_prologue = """__shared__ unsigned char nmb_active[1024];
+    __shared__ __align__(16) unsigned char nmb_gr_vals[8192];
+    {
+        const int nmb_tid = threadIdx.x + blockDim.x * (threadIdx.y + blockDim.y * threadIdx.z);
+        nmb_active[nmb_tid] = nmb_item_active;
+    }
+    const bool nmb_group_full = (blockDim.x * blockDim.y * blockDim.z) % 32 == 0 &&
+        (int64_t)(blockIdx.x + 1) * blockDim.x <= nmb_g0 && (int64_t)(blockIdx.y + 1) * blockDim.y <= nmb_g1 &&
+        (int64_t)(blockIdx.z + 1) * blockDim.z <= nmb_g2;
+    __syncthreads();"""
     src = f"""//NMB200:CUDA-SOURCE
 //NMB200:OPTIONS{opts}
 #include "nmb_device.cuh"
 extern "C" __global__ void nmb_kernel({', '.join(kparams)}) {{
     const int64_t nmb_gs[3] = {{nmb_g0, nmb_g1, nmb_g2}};
     // work-items past the global size are masked off
-    if (nmb::k_get_global_id(0, nmb_gs) >= nmb_g0 || nmb::k_get_global_id(1, nmb_gs) >= nmb_g1 ||
-        nmb::k_get_global_id(2, nmb_gs) >= nmb_g2) return;
+    const bool nmb_item_active = nmb::k_get_global_id(0, nmb_gs) < nmb_g0 &&
+        nmb::k_get_global_id(1, nmb_gs) < nmb_g1 && nmb::k_get_global_id(2, nmb_gs) < nmb_g2;
+    {group_prologue}
+    if (!nmb_item_active) return;
     {' '.join(tr.shared_decls)}
     {chr(10).join('    ' + d for d in tr.decls)}
     {(chr(10) + '    ').join(body)}

@@ -197,6 +197,35 @@ __device__ __forceinline__ T block_reduce(T v, Op op, T neutral, T *scratch) {
   return r;
 }
 
+// Work-group reduction that tolerates groups cut short by the global size and
+// groups whose size is not a multiple of the warp size.  `full` (uniform over
+// the block) selects the shuffle tree; otherwise every remaining work-item
+// parks its value in `vals` and the group's first work-item, which always
+// exists, combines the values of the active ones in work-item order.  Work-items
+// past the global size have left the kernel: a block barrier waits only for
+// the threads that have not exited.
+template <typename T, typename Op>
+__device__ __forceinline__ T group_reduce(T v, Op op, T neutral, T *scratch, void *vals_raw,
+                                          const unsigned char *active, bool full) {
+  if (full)
+    return block_reduce(v, op, neutral, scratch);
+  T *vals = reinterpret_cast<T *>(vals_raw);
+  const int nthreads = blockDim.x * blockDim.y * blockDim.z;
+  const int tid = threadIdx.x + blockDim.x * (threadIdx.y + blockDim.y * threadIdx.z);
+  __syncthreads(); // the previous reduction's result has been read
+  vals[tid] = v;
+  __syncthreads();
+  if (tid == 0) {
+    T acc = neutral;
+    for (int t = 0; t < nthreads; ++t)
+      if (active[t])
+        acc = op(acc, vals[t]);
+    scratch[0] = acc;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
 // ------------------------------------------------------------------- math ---
 // float32 stays float32 (numba_mlir/mlir/builtin/funcs.py:180-227); the CUDA
 // functions below are the IEEE-rounded (sqrt, div) or <= 2 ulp (log, exp)

@@ -139,9 +139,22 @@ def _parse_dtype(dtype):
     return None
 
 
+def _array_pysig(shape, dtype):
+    pass
+
+
 class _ArrayTemplate(AbstractTemplate):
     def generic(self, args, kws):
-        assert not kws
+        # positional or keyword form (local.array(shape=..., dtype=...),
+        # numba_mlir/mlir/tests/test_gpu.py:1140-1142)
+        kws = dict(kws)
+        args = list(args)
+        for name in ("shape", "dtype")[len(args):]:
+            if name not in kws:
+                return None
+            args.append(kws.pop(name))
+        if kws or len(args) != 2:
+            return None
         shape, dtype = args
         if isinstance(shape, types.Integer):
             ndim = 1
@@ -153,7 +166,10 @@ class _ArrayTemplate(AbstractTemplate):
         nb_dtype = _parse_dtype(dtype)
         if nb_dtype is None:
             return None
-        return signature(types.Array(nb_dtype, ndim, "C"), shape, dtype)
+        from numba.core.utils import pysignature
+
+        return signature(types.Array(nb_dtype, ndim, "C"), shape, dtype).replace(
+            pysig=pysignature(_array_pysig))
 
 
 infer_global(local_array)(_ArrayTemplate)
