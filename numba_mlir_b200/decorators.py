@@ -82,6 +82,16 @@ class Dispatcher:
     def __call__(self, *args, **kwargs):
         if kwargs:
             raise TypeError("keyword arguments are not supported in offloaded calls")
+        if lazy.current_trace() is not None:
+            # called from another offloaded function that is being traced: the
+            # body joins the caller's trace (the reference inlines nested njit
+            # calls into one module, mlir/tests/test_gpu.py:1673-1702)
+            from . import codegen_ir
+
+            if codegen_ir.uses_prange(self.py_func):
+                raise TypeError(f"{self.py_func.__name__}: a function with prange loops cannot be "
+                                "called from an array-expression function")
+            return self.py_func(*args)
         args = tuple(_wrap_arg(a) for a in args)
         devs = check_device_args(args)
         if not devs:
