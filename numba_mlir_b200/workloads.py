@@ -89,14 +89,14 @@ def kmeans_update(centroids, sums, counts):
 # counts (int64).  The work-group stages the centroids in local memory and
 # every work-item keeps its point in a private array, so the 64 x 16 inner loop
 # runs out of shared memory and registers.  The sums are gathered without
-# per-point atomics: a batch of 256 labelled points is parked in local memory
-# and work-item (cluster group cg, column jcol) walks the batch in order, adding
-# the points of its four clusters into float64 registers; only these registers
-# meet the global arrays through atomics, once per group.
+# per-point atomics: after a batch of 256 points is labelled, 64 work-items
+# (4 point phases x 16 dimensions) add the batch into float64 accumulator
+# columns in local memory that each of them owns, and only the 64 x 16 group
+# totals meet the global arrays through atomics, once per group.
 _KM_K = 64
 _KM_D = 16
-_KM_DP = _KM_D + 1  # padded row of the parked batch
 _KM_PTS = 8
+_KM_COLS = 64  # accumulator columns per cluster: 4 point phases x 16 dimensions
 KMEANS_LOCAL_SIZE = 256
 
 
@@ -107,26 +107,29 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
     base = get_group_id(0) * (lsz * _KM_PTS)
 
     cent = local.array((_KM_K, _KM_D), np.float32)
-    lp = local.array((KMEANS_LOCAL_SIZE, _KM_DP), np.float32)  # padded rows: no bank conflicts
     lbl = local.array(KMEANS_LOCAL_SIZE, np.int32)
     lcnt = local.array(_KM_K, np.int32)
+    # Column c = phase * 16 + dimension belongs to work-item c alone: it adds
+    # its points into acc[label, c] with plain read-modify-writes, no atomics.
+    acc = local.array((_KM_K, _KM_COLS), np.float64)
     j = lid
     while j < _KM_K * _KM_D:
         cent[j // _KM_D, j % _KM_D] = centroids[j // _KM_D, j % _KM_D]
+        j += lsz
+    j = lid
+    while j < _KM_K * _KM_COLS:
+        acc[j // _KM_COLS, j % _KM_COLS] = 0.0
         j += lsz
     if lid < _KM_K:
         lcnt[lid] = 0
     barrier()
 
     jcol = lid & (_KM_D - 1)
-    cg = lid >> 4
-    a0 = 0.0
-    a1 = 0.0
-    a2 = 0.0
-    a3 = 0.0
+    phase = lid >> 4
     p = private.array(_KM_D, np.float32)
     for r in range(_KM_PTS):
-        i = base + r * lsz + lid
+        row0 = base + r * lsz
+        i = row0 + lid
         for jj in range(_KM_D):
             p[jj] = points[i, jj]
         best = 0
@@ -142,32 +145,21 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
         labels[i] = best
         atomic.add(lcnt, best, 1)
         lbl[lid] = best
-        for jj in range(_KM_D):
-            lp[lid, jj] = p[jj]
         barrier()
-        for m in range(KMEANS_LOCAL_SIZE):
-            b = lbl[m]
-            if (b >> 2) == cg:
-                v = lp[m, jcol]
-                w = b & 3
-                if w == 0:
-                    a0 += v
-                elif w == 1:
-                    a1 += v
-                elif w == 2:
-                    a2 += v
-                else:
-                    a3 += v
+        if lid < _KM_COLS:
+            # the batch's rows were read a moment ago: these loads hit in L1
+            for m in range(phase, KMEANS_LOCAL_SIZE, _KM_COLS // _KM_D):
+                acc[lbl[m], lid] += points[row0 + m, jcol]
         barrier()
 
-    if a0 != 0.0:
-        atomic.add(sums, (cg * 4, jcol), a0)
-    if a1 != 0.0:
-        atomic.add(sums, (cg * 4 + 1, jcol), a1)
-    if a2 != 0.0:
-        atomic.add(sums, (cg * 4 + 2, jcol), a2)
-    if a3 != 0.0:
-        atomic.add(sums, (cg * 4 + 3, jcol), a3)
+    e = lid
+    while e < _KM_K * _KM_D:
+        k = e // _KM_D
+        jj = e % _KM_D
+        v = acc[k, jj] + acc[k, _KM_D + jj] + acc[k, 2 * _KM_D + jj] + acc[k, 3 * _KM_D + jj]
+        if v != 0.0:
+            atomic.add(sums, (k, jj), v)
+        e += lsz
     if lid < _KM_K:
         if lcnt[lid] != 0:
             atomic.add(counts, lid, lcnt[lid])
