@@ -747,6 +747,10 @@ class Translator:
         defn = ir_utils.guard(ir_utils.get_definition, self.tir.func_ir, var)
         if isinstance(defn, self.ir.Expr) and defn.op == "build_tuple":
             return tuple(self.static_value(i) for i in defn.items)
+        if isinstance(defn, self.ir.Expr) and defn.op == "binop" and defn.fn in (
+                operator.add, operator.sub, operator.mul, operator.floordiv):
+            # arithmetic on constants, e.g. a shape written as 4 * GROUP_SIZE
+            return defn.fn(self.static_value(defn.lhs), self.static_value(defn.rhs))
         raise UnsupportedError(f"{var.name} must be a compile-time constant")
 
     # arguments ------------------------------------------------------------------------
