@@ -228,19 +228,25 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
     const int64_t r0 = r_begin + i * rs;
     const int nr = (int)(r_end - r0 < rs ? r_end - r0 : rs);
     const uint32_t row_bytes = (uint32_t)(ncols * sizeof(T));
-    mbar_expect_tx(&sm.full[s], row_bytes * nr);
+    // Called by lane 0 of every warp: thread 0 posts the stage's byte count,
+    // the row segments are fetched by different warps (a bulk copy costs the
+    // issuing thread about 0.1 us).
+    if (tid == 0)
+      mbar_expect_tx(&sm.full[s], row_bytes * nr);
     if (contiguous) {
-      bulk_load(tiles + (int64_t)s * TILE, a + r0 * cols, row_bytes * nr, &sm.full[s]);
+      if (tid == 0)
+        bulk_load(tiles + (int64_t)s * TILE, a + r0 * cols, row_bytes * nr, &sm.full[s]);
     } else {
-      for (int j = 0; j < nr; ++j)
+      for (int j = tid >> 5; j < nr; j += kWarps)
         bulk_load(tiles + (int64_t)s * TILE + (int64_t)j * ncols, a + (r0 + j) * cols + c0, row_bytes,
                   &sm.full[s]);
     }
   };
   int64_t issued = 0;
-  if (tid == 0)
+  if ((tid & 31) == 0)
     for (; issued < kStages && issued < nsteps; ++issued)
       issue(issued);
+  issued = nsteps < kStages ? nsteps : kStages; // the same count in every thread
 
   Fast f[kColVecs][VEC];
 #pragma unroll
@@ -271,8 +277,11 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
       }
     }
     __syncthreads();
-    if (tid == 0 && issued < nsteps)
-      issue(issued++);
+    if (issued < nsteps) {
+      if ((tid & 31) == 0)
+        issue(issued);
+      ++issued;
+    }
   }
   if (__syncthreads_or(dead))
     drain_after_timeout(sm, issued);
