@@ -695,6 +695,57 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_dispatch(args):
+    """Host cost of one launch, after the reference's kernel-dispatcher
+    microbenchmark (benchmarks/benchmarks/microbenchmarks/kernel_dispatcher/
+    numba_mlir.py:17-75): a kernel of 1, 2, 6 or 12 array arguments on 8
+    int32 elements, called through a configured kernel object
+    ("dispatcher") and through `kernel[...]` each time ("full_dispatcher"),
+    plus an `njit` elementwise call replayed from its plan."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import runtime
+    from numba_mlir_b200.kernel import DEFAULT_LOCAL_SIZE, get_global_id, kernel
+
+    def make(count):
+        names = ", ".join(f"arg{i + 1}" for i in range(count))
+        scope = {"get_global_id": get_global_id}
+        exec(f"def func({names}):\n    i = get_global_id(0)\n    arg1[i] = i\n", scope)
+        return scope["func"]
+
+    queue = runtime.get_queue("cuda:0")
+    calls = args.steps if args.steps is not None else 20000
+    out = {}
+    for count in (1, 2, 6, 12):
+        array = nm.empty(8, np.int32, queue)
+        base = kernel(make(count))
+        fn = base[8, DEFAULT_LOCAL_SIZE]
+        a = (array,) * count
+        fn(*a)
+        queue.synchronize()
+        for name, call in (("dispatcher", lambda: fn(*a)),
+                           ("full_dispatcher", lambda: base[8, DEFAULT_LOCAL_SIZE](*a))):
+            t0 = time.perf_counter()
+            for _ in range(calls):
+                call()
+            host = time.perf_counter() - t0
+            queue.synchronize()
+            out[f"{name}_{count}_args_us"] = host / calls * 1e6
+
+    @nm.njit
+    def add(x, y, z):
+        z[:] = x + y
+
+    x = nm.empty(8, np.float32, queue)
+    add(x, x, x)
+    queue.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(calls):
+        add(x, x, x)
+    out["njit_add_3_args_us"] = (time.perf_counter() - t0) / calls * 1e6
+    queue.synchronize()
+    print(json.dumps({"metric": "host_time_per_launch", "unit": "us", "calls": calls, **out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -707,7 +758,12 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of a CUDA graph")
     ap.add_argument("--profile", action="store_true",
                     help="run only warmup + steps eager device steps of --workload (for ncu)")
+    ap.add_argument("--dispatch", action="store_true",
+                    help="host time per launch of tiny kernels (dispatcher microbenchmark)")
     args = ap.parse_args()
+    if args.dispatch:
+        run_dispatch(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -908,6 +908,33 @@ class CompiledKernel:
         self.name = name
         self.param_layout = param_layout  # per Python argument: ("array", ndim, layout) | ("scalar", dtype)
         self.uses_barrier = uses_barrier
+        self._handles = {}      # queue -> kernel handle (the queue owns and frees it)
+        self._block_sizes = {}  # (queue, global size) -> suggested local size
+        self._kinds = {}
+
+    def kinds(self, trailing_int64=0):
+        """Launch parameter kinds: the arguments, then `trailing_int64` sizes."""
+        k = self._kinds.get(trailing_int64)
+        if k is None:
+            from .kernel_impl import param_kinds
+
+            k = self._kinds[trailing_int64] = param_kinds(self.param_layout, trailing_int64)
+        return k
+
+    def handle_on(self, queue):
+        """Kernel handle on `queue`, loading the module on first use."""
+        h = self._handles.get(queue)
+        if h is None:
+            h = queue.get_kernel(queue.load_module(self.source.encode()), self.name)
+            self._handles[queue] = h
+        return h
+
+    def block_size_on(self, queue, kernel, global_size):
+        key = (queue, global_size)
+        b = self._block_sizes.get(key)
+        if b is None:
+            b = self._block_sizes[key] = queue.suggest_block_size(kernel, global_size)
+        return b
 
 
 def compile_kernel(py_func, args, ndim, fastmath=False):

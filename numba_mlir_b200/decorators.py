@@ -132,11 +132,12 @@ class Dispatcher:
                                            fastmath=bool(self.options.get("fastmath", False)))
             self._parfor_kernels[key] = ck
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
-        kernel = queue.get_kernel(queue.load_module(ck.source.encode()), ck.name)
+        kernel = ck.handle_on(queue)
         grid, block = parfor_launch_shape(ck.extents(args), ck.inner_parallel)
         if grid is None:
             return None
-        queue.launch(kernel, grid, block, kernel_impl.marshal_params(args, ck.param_layout))
+        queue.launch_values(kernel, grid, block, ck.kinds(),
+                            kernel_impl.marshal_values(args, ck.param_layout))
         return None
 
     def trace_dry(self, *args):

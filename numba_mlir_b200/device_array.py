@@ -68,6 +68,9 @@ class DeviceArray:
         self.dtype = np.dtype(dtype)
         self.strides = tuple(strides) if strides is not None else _c_strides(self.shape, self.dtype.itemsize)
         self._offset = int(offset)
+        self._contig = None if strides is not None else True
+        self._call_sig = None
+        self._trace_sig = None
 
     # -- basic properties ------------------------------------------------------
     @property
@@ -104,7 +107,30 @@ class DeviceArray:
         return "shared" if self._buf.kind == _rt.ALLOC_SHARED else "device"
 
     @property
+    def trace_sig(self):
+        """Everything a recorded plan is specialised on (a cache key)."""
+        sig = self._trace_sig
+        if sig is None:
+            sig = self._trace_sig = ("arr", self.dtype.name, self.shape, self.strides, self.ptr % 16 == 0,
+                                     getattr(self.queue, "device", None))
+        return sig
+
+    @property
+    def call_sig(self):
+        """What generated code depends on: dtype, rank, contiguity (a cache key)."""
+        sig = self._call_sig
+        if sig is None:
+            sig = self._call_sig = ("arr", self.dtype.name, len(self.shape), self.is_c_contiguous)
+        return sig
+
+    @property
     def is_c_contiguous(self):
+        c = self._contig
+        if c is None:
+            c = self._contig = self._compute_contiguity()
+        return c
+
+    def _compute_contiguity(self):
         return self.size <= 1 or self.strides == _c_strides(self.shape, self.dtype.itemsize) or all(
             st == cst for s, st, cst in zip(self.shape, self.strides, _c_strides(self.shape, self.dtype.itemsize)) if s != 1
         )

@@ -251,7 +251,7 @@ def call_signature(args):
     sig = []
     for a in args:
         if isinstance(a, DeviceArray):
-            sig.append(("arr", a.dtype.name, a.ndim, a.is_c_contiguous))
+            sig.append(a.call_sig)
         else:
             sig.append(("scalar", type(a).__name__, getattr(a, "dtype", None) and a.dtype.name))
     return tuple(sig)
@@ -271,6 +271,36 @@ def marshal_params(args, param_layout):
         else:
             params.append(lay[1].type(a))
     return params
+
+
+_I64 = np.dtype(np.int64)
+
+
+def param_kinds(param_layout, trailing_int64=0):
+    """Parameter kinds of a compiled kernel in launch order (see marshal_values)."""
+    kinds = []
+    for lay in param_layout:
+        if lay[0] == "array":
+            kinds.append("ptr")
+            kinds += [_I64] * (lay[1] * (1 if lay[2] == "C" else 2))
+        else:
+            kinds.append(lay[1])
+    return tuple(kinds + [_I64] * trailing_int64)
+
+
+def marshal_values(args, param_layout):
+    """Like marshal_params, as plain Python numbers for Queue.launch_values."""
+    vals = []
+    for a, lay in zip(args, param_layout):
+        if lay[0] == "array":
+            vals.append(a.ptr)
+            vals.extend(a.shape)
+            if lay[2] != "C":
+                it = a.dtype.itemsize
+                vals.extend(st // it for st in a.strides)
+        else:
+            vals.append(a.item() if isinstance(a, np.generic) else a)
+    return vals
 
 
 class Kernel:
@@ -331,18 +361,18 @@ class Kernel:
                                            fastmath=bool(self.options.get("fastmath", False)))
             self._compiled[key] = ck
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
-        kernel = queue.get_kernel(queue.load_module(ck.source.encode()), ck.name)
+        kernel = ck.handle_on(queue)
         if self.local_size:
             local = tuple(self.local_size)
         else:
-            local = queue.suggest_block_size(kernel, self.global_size)
+            local = ck.block_size_on(queue, kernel, tuple(self.global_size))
         grid = tuple((g + l - 1) // l for g, l in zip(self.global_size, local))
         if any(g == 0 for g in self.global_size):
             return
-        params = marshal_params(args, ck.param_layout)
-        gs = tuple(self.global_size) + (1,) * (3 - ndim)
-        params += [np.int64(g) for g in gs]
-        queue.launch(kernel, grid, local, params)
+        vals = marshal_values(args, ck.param_layout)
+        vals.extend(self.global_size)
+        vals.extend((1,) * (3 - ndim))
+        queue.launch_values(kernel, grid, local, ck.kinds(3), vals)
 
 
 def kernel(func=None, **kwargs):

@@ -861,7 +861,7 @@ def signature_of(args):
     sig = []
     for a in args:
         if isinstance(a, DeviceArray):
-            sig.append(("arr", a.dtype.name, a.shape, a.strides, a.ptr % 16 == 0, a.queue.device))
+            sig.append(a.trace_sig)
         elif isinstance(a, (bool, int, float, np.generic)):
             sig.append(("scalar", scalar_dtype(a).name))
         else:

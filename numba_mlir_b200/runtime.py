@@ -362,6 +362,28 @@ class Queue:
             self.lib.gpuxWait(self.handle, ev)
         self.lib.gpuxDestroyEvent(self.handle, ev)
 
+    def launch_values(self, kernel, grid, block, kinds, values):
+        """`launch` for callers that know the parameter kinds beforehand
+        (`kinds`: a hashable tuple of "ptr" / NumPy dtypes) and pass plain
+        Python numbers: skips the per-argument type discovery."""
+        key = (kernel, kinds)
+        prepared = self._prepared.get(key)
+        if prepared is None:
+            prepared = _PreparedParams(kinds)
+            self._prepared[key] = prepared
+        for slot, v in zip(prepared.slots, values):
+            slot.value = v
+        ng, nb = len(grid), len(block)
+        ev = self.lib.gpuxLaunchKernel(
+            self.handle, kernel, grid[0], grid[1] if ng > 1 else 1, grid[2] if ng > 2 else 1,
+            block[0], block[1] if nb > 1 else 1, block[2] if nb > 2 else 1,
+            None, prepared.descs_ptr,
+        )
+        if not ev:
+            check()
+            raise GpuRuntimeError("gpuxLaunchKernel returned NULL")
+        self.lib.gpuxDestroyEvent(self.handle, ev)
+
     # -- CUDA graphs -----------------------------------------------------------
     def graph_begin(self):
         """Starts recording the queue's launches into a CUDA graph."""
