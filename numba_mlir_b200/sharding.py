@@ -54,12 +54,26 @@ def allreduce(partial, op="sum", dist=None):
     # no host synchronisation is needed on either side.
     stream = _external_stream(partial.queue)
     with torch.cuda.stream(stream):
-        t = torch.as_tensor(partial, device=f"cuda:{partial.queue.device}")
-        dist.all_reduce(t, op=rop)
+        dist.all_reduce(_torch_view(partial), op=rop)
     return partial
 
 
 _streams = {}
+_views = {}
+
+
+def _torch_view(array):
+    """torch tensor over the array's memory; kept (with the array) per buffer so
+    that a step repeated every iteration does not rebuild it."""
+    import torch
+
+    key = (array.ptr, array.shape, array.strides, array.dtype.str)
+    hit = _views.get(key)
+    if hit is None or hit[0]._buf is not array._buf:
+        if len(_views) > 64:
+            _views.clear()
+        hit = _views[key] = (array, torch.as_tensor(array, device=f"cuda:{array.queue.device}"))
+    return hit[1]
 
 
 def _external_stream(queue):
