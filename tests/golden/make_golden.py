@@ -16,6 +16,11 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
+# Shared with the tests that replay these cases.
+SCALAR_VALUES = [True, False, -3, 0, 2, -2.5, -0.0, 0.5]
+MATH_UNARY = ["sqrt", "log", "exp", "sin", "cos", "erf", "tanh", "floor", "ceil", "acos"]
+BINARY_OPS = {"add": "+", "sub": "-", "mul": "*", "truediv": "/", "floordiv": "//", "mod": "%", "pow": "**"}
+
 
 def load_sim(ref_root):
     path = os.path.join(ref_root, "numba_mlir", "numba_mlir", "mlir", "kernel_sim_impl.py")
@@ -115,6 +120,111 @@ def main(ref_root):
     res = np.zeros((128, 128), np.float32)
     run(k_pair, (128, 128), (), (a, b, res))
     out["pairwise1"] = res
+
+    # scalar argument / captured scalar: mlir/tests/test_gpu.py:288-345
+    for dtype in ("int32", "int64", "float32", "float64"):
+        a = np.arange(-6, 6, dtype=dtype)
+        for vi, val in enumerate(SCALAR_VALUES):
+            def k_scalar(a, b, c):
+                i = sim.get_global_id(0)
+                c[i] = a[i] + b
+
+            res = np.zeros(a.shape, a.dtype)
+            run(k_scalar, a.shape, (), (a, val, res))
+            out[f"scalar_{dtype}_{vi}"] = res
+
+    # unary math: mlir/tests/test_gpu.py:484-556
+    import math
+
+    for dtype in ("float32", "float64"):
+        a = np.array([0.1, 0.2, 0.3, 0.4, 0.5, 0.6, 0.7, 0.8, 0.9], dtype)
+        for op in MATH_UNARY:
+            f = getattr(math, op)
+
+            def k_unary(a, b):
+                i = sim.get_global_id(0)
+                b[i] = f(a[i])
+
+            res = np.zeros(a.shape, dtype)
+            run(k_unary, a.shape, (), (a, res))
+            out[f"unary_{op}_{dtype}"] = res
+
+    # binary operators: mlir/tests/test_gpu.py:559-575
+    for dtype in ("int32", "float32", "float64"):
+        a = np.array([11, 12, 13, 14, 15], dtype)
+        b = np.array([1, 2, 3, 4, 5], dtype)
+        for name, op in BINARY_OPS.items():
+            f = eval(f"lambda a, b: a {op} b")
+
+            def k_binary(a, b, c):
+                i = sim.get_global_id(0)
+                c[i] = f(a[i], b[i])
+
+            res = np.zeros(a.shape, dtype)
+            run(k_binary, a.shape, (), (a, b, res))
+            out[f"binary_{name}_{dtype}"] = res
+
+    # inner loop with a data-dependent trip count: mlir/tests/test_gpu.py:455-481
+    def k_inner(a, b, c):
+        i = sim.get_global_id(0)
+        res = 0.0
+        for j in range(a[i]):
+            res = res + b[j]
+        c[i] = res
+
+    a = np.array([1, 2, 3, 4], np.int32)
+    b = np.array([5, 6, 7, 8, 9], np.float32)
+    res = np.zeros(a.shape, b.dtype)
+    run(k_inner, a.shape, (), (a, b, res))
+    out["inner_loop"] = res
+
+    # sub-array views: mlir/tests/test_gpu.py:429-452
+    def k_slice(a, b):
+        i = sim.get_global_id(0)
+        b1 = b[i]
+        j = sim.get_global_id(1)
+        b2 = b1[j]
+        k = sim.get_global_id(2)
+        b2[k] = a[i, j, k]
+
+    a = np.arange(3 * 4 * 5).reshape((3, 4, 5))
+    res = np.zeros(a.shape, a.dtype)
+    run(k_slice, a.shape, (), (a, res))
+    out["slice"] = res
+
+    # private arrays: mlir/tests/test_gpu.py:1255-1287 (the simulator's
+    # private.array is local_array's zero-filled buffer per work-item)
+    for blocksize in (1, 10, 17, 64, 67, 101):
+        for priv_size in (1, 11, 27):
+            def k_private(A):
+                i = sim.get_global_id(0)
+                prvt_mem = sim.private_array(priv_size, np.float32)
+                for j in range(priv_size):
+                    prvt_mem[j] = j + i
+                res = 0
+                for j in range(priv_size):
+                    res += prvt_mem[(j + i) % priv_size]
+                A[i] = res
+
+            res = np.zeros(blocksize, np.float32)
+            run(k_private, (blocksize,), (blocksize,), (res,))
+            out[f"private3_{blocksize}_{priv_size}"] = res
+
+    # ids and sizes in three dimensions with a (2, 4, 8) group: mlir/tests/test_gpu.py:578-803
+    def k_ids3(gid, lid, grp, gsz, lsz):
+        i = sim.get_global_id(0)
+        j = sim.get_global_id(1)
+        k = sim.get_global_id(2)
+        gid[i, j, k] = i + j * 100 + k * 10000
+        lid[i, j, k] = sim.get_local_id(0) + sim.get_local_id(1) * 100 + sim.get_local_id(2) * 10000
+        grp[i, j, k] = sim.get_group_id(0) + sim.get_group_id(1) * 100 + sim.get_group_id(2) * 10000
+        gsz[i, j, k] = sim.get_global_size(0) + sim.get_global_size(1) * 100 + sim.get_global_size(2) * 10000
+        lsz[i, j, k] = sim.get_local_size(0) + sim.get_local_size(1) * 100 + sim.get_local_size(2) * 10000
+
+    arrs = [np.zeros((7, 13, 23), np.int32) for _ in range(5)]
+    run(k_ids3, (7, 13, 23), (2, 4, 8), tuple(arrs))
+    for name, arr in zip(("gid", "lid", "grp", "gsz", "lsz"), arrs):
+        out[f"ids3d_7x13x23_2x4x8_{name}"] = arr
 
     np.savez_compressed(os.path.join(HERE, "kernel_sim.npz"), **out)
     print("wrote", len(out), "arrays")

@@ -423,3 +423,28 @@ def test_group_func(queue, name, dtype):
             _none, gpu = _run(func, (global_size,), (local_size,), [a, np.zeros_like(a)], sim=False)
             np.testing.assert_allclose(gpu[1], want, rtol=1e-5,
                                        err_msg=f"global {global_size} local {local_size}")
+
+
+def test_kernel_suite_against_the_reference_simulators_golden_vectors(queue):
+    """The cases of tests/kernel_cases.py on the device against what the
+    reference's own kernel_sim_impl.py produced (tests/golden/kernel_sim.npz):
+    exact for integer results and index bookkeeping, rtol 1e-5 (the reference's
+    tolerance) for floating-point math."""
+    import os
+
+    from kernel_cases import cases
+    from numba_mlir_b200.kernel import kernel
+
+    golden = np.load(os.path.join(os.path.dirname(__file__), "golden", "kernel_sim.npz"))
+    seen = 0
+    for key, func, gsize, lsize, args, out_index, exact in cases(for_device=True):
+        dev_args = [_dev(a) if isinstance(a, np.ndarray) else a for a in args]
+        kernel(func)[gsize, lsize](*dev_args)
+        got, want = dev_args[out_index].copy_to_host(), golden[key]
+        assert got.dtype == want.dtype, key
+        if exact:
+            np.testing.assert_equal(got, want, err_msg=key)
+        else:
+            np.testing.assert_allclose(got, want, rtol=1e-5, err_msg=key)
+        seen += 1
+    assert seen == 98

@@ -187,3 +187,19 @@ def test_kmeans_oracle_assignment_vs_float64_argmin():
     clear = (srt[:, 1] - srt[:, 0]) > 1e-4 * srt[:, 0]
     assert clear.mean() > 0.99
     assert np.array_equal(labels[clear], d.argmin(axis=1)[clear])
+
+
+def test_simulator_restatement_matches_the_reference_simulator_on_the_kernel_suite():
+    """Every non-barrier case of tests/kernel_cases.py: oracle/kernel_sim.py gives
+    what the reference's kernel_sim_impl.py gave (tests/golden/kernel_sim.npz)."""
+    from kernel_cases import cases
+    from oracle.kernel_sim import kernel_sim
+
+    seen = 0
+    for key, func, gsize, lsize, args, out_index, _exact in cases():
+        run_args = [a.copy() if isinstance(a, np.ndarray) else a for a in args]
+        kernel_sim(func)[gsize, lsize](*run_args)
+        got, want = run_args[out_index], GOLDEN[key]
+        assert got.dtype == want.dtype and np.array_equal(got, want, equal_nan=True), key
+        seen += 1
+    assert seen == 98
