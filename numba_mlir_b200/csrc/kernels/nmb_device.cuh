@@ -81,6 +81,11 @@ __device__ __forceinline__ void store_stream(T *p, const Vec<T, N> &r) {
     __stcs(reinterpret_cast<int2 *>(p), *reinterpret_cast<const int2 *>(&r));
   } else if constexpr (sizeof(T) * N == 4) {
     __stcs(reinterpret_cast<int *>(p), *reinterpret_cast<const int *>(&r));
+  } else if constexpr (sizeof(T) == 1) {
+    // no streaming store for 1-byte elements (bool results of comparisons)
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      p[i] = r.v[i];
   } else {
 #pragma unroll
     for (int i = 0; i < N; ++i)
@@ -350,6 +355,47 @@ __device__ __forceinline__ double py_mod(double a, double b) {
     r += b;
   return r;
 }
+
+// floor(a / b) the way NumPy's floor_divide computes it for floats: from the
+// remainder, so that the quotient and np.remainder agree.
+__device__ __forceinline__ float py_floordiv(float a, float b) {
+  if (b == 0.f)
+    return a / b;
+  float mod = fmodf(a, b);
+  float div = (a - mod) / b;
+  if (mod != 0.f && ((b < 0.f) != (mod < 0.f)))
+    div -= 1.f;
+  if (div == 0.f)
+    return copysignf(0.f, a / b);
+  float fl = floorf(div);
+  if (div - fl > 0.5f)
+    fl += 1.f;
+  return fl;
+}
+__device__ __forceinline__ double py_floordiv(double a, double b) {
+  if (b == 0.)
+    return a / b;
+  double mod = fmod(a, b);
+  double div = (a - mod) / b;
+  if (mod != 0. && ((b < 0.) != (mod < 0.)))
+    div -= 1.;
+  if (div == 0.)
+    return copysign(0., a / b);
+  double fl = floor(div);
+  if (div - fl > 0.5)
+    fl += 1.;
+  return fl;
+}
+// Shifts by at least the width give 0 (or the sign), as NumPy defines them.
+template <typename T> __device__ __forceinline__ T i_shl(T a, T n) {
+  return (n < 0 || n >= (T)(8 * sizeof(T))) ? T(0) : (T)(a << n);
+}
+template <typename T> __device__ __forceinline__ T i_shr(T a, T n) {
+  return (n < 0 || n >= (T)(8 * sizeof(T))) ? (a < 0 ? T(-1) : T(0)) : (T)(a >> n);
+}
+template <typename T> __device__ __forceinline__ T i_sign(T a) { return (T)((a > 0) - (a < 0)); }
+__device__ __forceinline__ float f_sign(float a) { return a != a ? a : (float)((a > 0.f) - (a < 0.f)); }
+__device__ __forceinline__ double f_sign(double a) { return a != a ? a : (double)((a > 0.) - (a < 0.)); }
 
 // NumPy's maximum/minimum propagate NaNs.
 template <typename T> __device__ __forceinline__ T np_max(T a, T b) { return (a > b || a != a) ? a : b; }

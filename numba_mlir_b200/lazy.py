@@ -140,10 +140,38 @@ UFUNCS = {
     "logical_and": (np.logical_and, lambda dt, a, b: f"(({a} != 0) && ({b} != 0))"),
     "logical_or": (np.logical_or, lambda dt, a, b: f"(({a} != 0) || ({b} != 0))"),
     "logical_not": (np.logical_not, lambda dt, a: f"(!({a} != 0))"),
+    "logical_xor": (np.logical_xor, lambda dt, a, b: f"(({a} != 0) != ({b} != 0))"),
+    "floor_divide": (np.floor_divide, lambda dt, a, b: f"nmb::py_floordiv({a}, {b})"),
+    "remainder": (np.remainder, lambda dt, a, b: f"nmb::py_mod({a}, {b})"),
+    "bitwise_and": (np.bitwise_and, lambda dt, a, b: f"({a} & {b})"),
+    "bitwise_or": (np.bitwise_or, lambda dt, a, b: f"({a} | {b})"),
+    "bitwise_xor": (np.bitwise_xor, lambda dt, a, b: f"({a} ^ {b})"),
+    "invert": (np.invert, lambda dt, a: f"(!{a})" if dt == np.bool_ else f"(~{a})"),
+    "left_shift": (np.left_shift, lambda dt, a, b: f"nmb::i_shl({a}, {b})"),
+    "right_shift": (np.right_shift, lambda dt, a, b: f"nmb::i_shr({a}, {b})"),
+    "isnan": (np.isnan, lambda dt, a: f"({a} != {a})"),
+    "isinf": (np.isinf, _flt("isinf({0})", "isinf({0})")),
+    "isfinite": (np.isfinite, _flt("isfinite({0})", "isfinite({0})")),
+    "sign": (np.sign, _int_or_float("nmb::i_sign({0})", "nmb::f_sign({0})", "nmb::f_sign({0})")),
+    "reciprocal": (np.reciprocal, _int_or_float("(1 / {0})", "nmb::f_div(1.0f, {0})", "nmb::f_div(1.0, {0})")),
+    "arcsin": (np.arcsin, _flt("asinf({0})", "asin({0})")),
+    "arctan": (np.arctan, _flt("atanf({0})", "atan({0})")),
+    "sinh": (np.sinh, _flt("sinhf({0})", "sinh({0})")),
+    "cosh": (np.cosh, _flt("coshf({0})", "cosh({0})")),
+    "expm1": (np.expm1, _flt("expm1f({0})", "expm1({0})")),
+    "log1p": (np.log1p, _flt("log1pf({0})", "log1p({0})")),
+    "log2": (np.log2, _flt("log2f({0})", "log2({0})")),
+    "log10": (np.log10, _flt("log10f({0})", "log10({0})")),
+    "rint": (np.rint, _flt("rintf({0})", "rint({0})")),
+    "trunc": (np.trunc, _flt("truncf({0})", "trunc({0})")),
+    "fmod": (np.fmod, _int_or_float("({1} == 0 ? 0 : {0} % {1})", "fmodf({0}, {1})", "fmod({0}, {1})")),
+    "hypot": (np.hypot, _flt("hypotf({0}, {1})", "hypot({0}, {1})")),
 }
 _UFUNC_BY_OBJ = {u: name for name, (u, _e) in UFUNCS.items()}
 _UFUNC_BY_OBJ[np.divide] = "true_divide"
 _UFUNC_BY_OBJ[np.abs] = "absolute"
+_UFUNC_BY_OBJ[np.mod] = "remainder"
+_UFUNC_BY_OBJ[np.bitwise_not] = "invert"
 
 REDUCTIONS = {np.sum: "sum", np.prod: "prod", np.min: "min", np.max: "max", np.amin: "min",
               np.amax: "max", np.argmin: "argmin", np.argmax: "argmax"}
@@ -333,6 +361,10 @@ class LazyArray:
             return reduce_lazy(self.trace, REDUCTIONS[func], *args, **kwargs)
         if func is np.where and len(args) == 3:
             return where(self.trace, *args)
+        if func is np.mean:
+            return mean_lazy(self.trace, *args, **kwargs)
+        if func is np.clip:
+            return clip_lazy(self.trace, *args, **kwargs)
         if func is np.dot:
             return dot(self.trace, *args, **kwargs)
         if func in (np.empty_like, np.zeros_like):
@@ -360,6 +392,21 @@ class LazyArray:
     def __rtruediv__(self, o): return self._bin("true_divide", o, True)
     def __pow__(self, o): return self._bin("power", o)
     def __rpow__(self, o): return self._bin("power", o, True)
+    def __floordiv__(self, o): return self._bin("floor_divide", o)
+    def __rfloordiv__(self, o): return self._bin("floor_divide", o, True)
+    def __mod__(self, o): return self._bin("remainder", o)
+    def __rmod__(self, o): return self._bin("remainder", o, True)
+    def __and__(self, o): return self._bin("bitwise_and", o)
+    def __rand__(self, o): return self._bin("bitwise_and", o, True)
+    def __or__(self, o): return self._bin("bitwise_or", o)
+    def __ror__(self, o): return self._bin("bitwise_or", o, True)
+    def __xor__(self, o): return self._bin("bitwise_xor", o)
+    def __rxor__(self, o): return self._bin("bitwise_xor", o, True)
+    def __lshift__(self, o): return self._bin("left_shift", o)
+    def __rlshift__(self, o): return self._bin("left_shift", o, True)
+    def __rshift__(self, o): return self._bin("right_shift", o)
+    def __rrshift__(self, o): return self._bin("right_shift", o, True)
+    def __invert__(self): return apply_ufunc(self.trace, "invert", (self,))
     def __neg__(self): return apply_ufunc(self.trace, "negative", (self,))
     def __pos__(self): return self
     def __abs__(self): return apply_ufunc(self.trace, "absolute", (self,))
@@ -385,10 +432,23 @@ class LazyArray:
     def __index__(self): return int(self._escape())
 
     # reductions / methods ----------------------------------------------------------
-    def sum(self, axis=None, dtype=None): return reduce_lazy(self.trace, "sum", self, axis=axis, dtype=dtype)
-    def prod(self, axis=None, dtype=None): return reduce_lazy(self.trace, "prod", self, axis=axis, dtype=dtype)
-    def min(self, axis=None): return reduce_lazy(self.trace, "min", self, axis=axis)
-    def max(self, axis=None): return reduce_lazy(self.trace, "max", self, axis=axis)
+    def sum(self, axis=None, dtype=None, keepdims=False):
+        return reduce_lazy(self.trace, "sum", self, axis=axis, dtype=dtype, keepdims=keepdims)
+
+    def prod(self, axis=None, dtype=None, keepdims=False):
+        return reduce_lazy(self.trace, "prod", self, axis=axis, dtype=dtype, keepdims=keepdims)
+
+    def min(self, axis=None, keepdims=False):
+        return reduce_lazy(self.trace, "min", self, axis=axis, keepdims=keepdims)
+
+    def max(self, axis=None, keepdims=False):
+        return reduce_lazy(self.trace, "max", self, axis=axis, keepdims=keepdims)
+
+    def mean(self, axis=None, dtype=None, keepdims=False):
+        return mean_lazy(self.trace, self, axis=axis, dtype=dtype, keepdims=keepdims)
+
+    def clip(self, a_min=None, a_max=None):
+        return clip_lazy(self.trace, self, a_min, a_max)
     def argmin(self, axis=None): return reduce_lazy(self.trace, "argmin", self, axis=axis)
     def argmax(self, axis=None): return reduce_lazy(self.trace, "argmax", self, axis=axis)
     def dot(self, other): return dot(self.trace, self, other)
@@ -495,17 +555,85 @@ def call_device_func(trace, func, inputs):
     return LazyArray(trace, Node("call", func.ret_dtype, shape, cast, op=func))
 
 
+_REDUCE_KERNEL_DTYPES = ("float32", "float64", "int32", "int64")
+
+
 def reduce_lazy(trace, op, a, axis=None, dtype=None, keepdims=False, out=None):
-    if keepdims or out is not None:
-        raise TypeError("keepdims/out are not supported in device reductions")
+    if out is not None:
+        raise TypeError("out= is not supported in device reductions")
     from . import reduce_ops
 
-    if dtype is not None and np.dtype(dtype) != a.dtype:
-        a = a.astype(dtype)
-    src = trace.materialize(a)
-    arr = trace.arrays[src]
+    if not isinstance(a, LazyArray):
+        a = LazyArray(trace, _as_node(trace, a))
     if isinstance(axis, LazyArray):
         axis = int(axis)
+    if isinstance(keepdims, LazyArray):
+        keepdims = bool(keepdims)
+    final = None
+    if dtype is not None and np.dtype(dtype) != a.dtype:
+        a = a.astype(dtype)  # NumPy casts the elements first, then reduces in `dtype`
+    if a.dtype.name not in _REDUCE_KERNEL_DTYPES:
+        # narrow integers and bool: reduce the values in a 32-bit type (sums and
+        # products wrap the same way modulo 2^16 or 2^8), cast the result back
+        if a.dtype.kind not in "iub":
+            raise TypeError(f"reductions of {a.dtype} are not supported on the device")
+        if op in ("sum", "prod"):
+            final = a.dtype if dtype is not None else None  # NumPy's default widens to the platform int
+            a = a.astype(np.int32 if a.dtype.itemsize < 4 else np.int64)
+        else:
+            final = a.dtype if not op.startswith("arg") else None
+            a = a.astype(np.int32 if a.dtype.itemsize < 4 else np.int64)
+    res = _reduce_node(trace, op, a, axis, reduce_ops)
+    if final is not None and res.dtype != final:
+        res = res.astype(final)
+    if keepdims:
+        nd = len(a.shape)
+        kept = (1,) * nd if axis is None else tuple(1 if d == axis % nd else s for d, s in enumerate(a.shape))
+        res = res.reshape(kept)
+    return res
+
+
+def mean_lazy(trace, a, axis=None, dtype=None, keepdims=False, out=None):
+    """NumPy's mean: the sum in `dtype` (float64 for integer input, the input
+    type for floats) divided by the element count; an integer `dtype` keeps
+    the truncated quotient."""
+    if out is not None:
+        raise TypeError("out= is not supported in device reductions")
+    if not isinstance(a, LazyArray):
+        a = LazyArray(trace, _as_node(trace, a))
+    if isinstance(axis, LazyArray):
+        axis = int(axis)
+    if dtype is None:
+        dtype = np.float64 if a.dtype.kind in "iub" else a.dtype
+    dtype = np.dtype(dtype)
+    count = a.size if axis is None else a.shape[axis % len(a.shape)]
+    total = reduce_lazy(trace, "sum", a, axis=axis, dtype=dtype, keepdims=keepdims)
+    if dtype.kind in "iub":
+        return (total / np.float64(count)).astype(dtype)
+    return total / dtype.type(count)
+
+
+def clip_lazy(trace, a, a_min=None, a_max=None, out=None):
+    """np.clip: bounds are converted to the array's type, as Numba types it."""
+    if out is not None:
+        raise TypeError("out= is not supported on device arrays")
+    if not isinstance(a, LazyArray):
+        a = LazyArray(trace, _as_node(trace, a))
+
+    def bound(b):
+        return a.dtype.type(b) if isinstance(b, (bool, int, float, np.generic)) else b
+
+    res = a
+    if a_min is not None:
+        res = apply_ufunc(trace, "maximum", (res, bound(a_min)))
+    if a_max is not None:
+        res = apply_ufunc(trace, "minimum", (res, bound(a_max)))
+    return res
+
+
+def _reduce_node(trace, op, a, axis, reduce_ops):
+    src = trace.materialize(a)
+    arr = trace.arrays[src]
     oshape = () if axis is None else arr.shape[:axis % arr.ndim] + arr.shape[axis % arr.ndim + 1:]
     dst = trace.add_tmp_slot(oshape, reduce_ops.out_dtype(op, arr.dtype))
     trace.steps.append(("reduce", op, axis, src, dst))
