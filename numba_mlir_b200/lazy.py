@@ -166,11 +166,17 @@ UFUNCS = {
     "trunc": (np.trunc, _flt("truncf({0})", "trunc({0})")),
     "fmod": (np.fmod, _int_or_float("({1} == 0 ? 0 : {0} % {1})", "fmodf({0}, {1})", "fmod({0}, {1})")),
     "hypot": (np.hypot, _flt("hypotf({0}, {1})", "hypot({0}, {1})")),
+    "exp2": (np.exp2, _flt("exp2f({0})", "exp2({0})")),
+    "cbrt": (np.cbrt, _flt("cbrtf({0})", "cbrt({0})")),
+    "degrees": (np.degrees, _flt("({0} * 57.29577951308232f)", "({0} * 57.29577951308232)")),
+    "radians": (np.radians, _flt("({0} * 0.017453292519943295f)", "({0} * 0.017453292519943295)")),
 }
 _UFUNC_BY_OBJ = {u: name for name, (u, _e) in UFUNCS.items()}
 _UFUNC_BY_OBJ[np.divide] = "true_divide"
 _UFUNC_BY_OBJ[np.abs] = "absolute"
 _UFUNC_BY_OBJ[np.mod] = "remainder"
+_UFUNC_BY_OBJ[np.rad2deg] = "degrees"
+_UFUNC_BY_OBJ[np.deg2rad] = "radians"
 _UFUNC_BY_OBJ[np.bitwise_not] = "invert"
 
 REDUCTIONS = {np.sum: "sum", np.prod: "prod", np.min: "min", np.max: "max", np.amin: "min",
@@ -314,6 +320,15 @@ def _as_node(trace, x):
     if isinstance(x, (bool, int, float, np.generic)):
         dt = scalar_dtype(x)
         return Node("const", dt, (), value=dt.type(x))
+    if isinstance(x, np.ndarray) and x.dtype.name in _CTYPE:
+        # a host array built inside the function (np.zeros, np.arange, ...):
+        # uploaded for this call; like a captured device array it is not replayable
+        from .device_array import from_host
+
+        arr = fake_array(x.shape, x.dtype) if trace.dry else from_host(np.ascontiguousarray(x), queue=trace.queue)
+        slot = trace.add_arg_slot(None, arr)
+        trace.value_dependent = True
+        return Node("leaf", arr.dtype, arr.shape, slot=slot)
     raise TypeError(f"cannot use {type(x)} in a device expression")
 
 
@@ -363,6 +378,27 @@ class LazyArray:
             return where(self.trace, *args)
         if func is np.mean:
             return mean_lazy(self.trace, *args, **kwargs)
+        if func in (np.var, np.std):
+            v = var_lazy(self.trace, *args, **kwargs)
+            return apply_ufunc(self.trace, "sqrt", (v,)) if func is np.std else v
+        if func in (np.any, np.all, np.count_nonzero):
+            return truth_reduce(self.trace, func, *args, **kwargs)
+        if func is np.transpose and len(args) == 1 and not kwargs:
+            return args[0].T
+        if func is np.ravel and len(args) == 1:
+            return args[0].ravel()
+        if func is np.reshape:
+            return args[0].reshape(*args[1:], **kwargs)
+        if func is np.copy and len(args) == 1:
+            return args[0].copy()
+        if func in (np.ones_like, np.full_like):
+            like = args[0]
+            dt = np.dtype(kwargs.get("dtype") or like.dtype)
+            out = self.trace.leaf(self.trace.add_tmp_slot(like.shape, dt))
+            out[...] = dt.type(1) if func is np.ones_like else dt.type(args[1])
+            return out
+        if func is np.concatenate:
+            return concatenate_lazy(self.trace, *args, **kwargs)
         if func is np.clip:
             return clip_lazy(self.trace, *args, **kwargs)
         if func is np.dot:
@@ -407,6 +443,27 @@ class LazyArray:
     def __rshift__(self, o): return self._bin("right_shift", o)
     def __rrshift__(self, o): return self._bin("right_shift", o, True)
     def __invert__(self): return apply_ufunc(self.trace, "invert", (self,))
+
+    # in-place operators write through to the array they name
+    def _inplace(self, name, other):
+        res = apply_ufunc(self.trace, name, (self, other))
+        if self.node.kind != "leaf":
+            return res  # a temporary: rebinding the name is all there is to do
+        self[...] = res
+        return self
+
+    def __iadd__(self, o): return self._inplace("add", o)
+    def __isub__(self, o): return self._inplace("subtract", o)
+    def __imul__(self, o): return self._inplace("multiply", o)
+    def __itruediv__(self, o): return self._inplace("true_divide", o)
+    def __ifloordiv__(self, o): return self._inplace("floor_divide", o)
+    def __imod__(self, o): return self._inplace("remainder", o)
+    def __ipow__(self, o): return self._inplace("power", o)
+    def __iand__(self, o): return self._inplace("bitwise_and", o)
+    def __ior__(self, o): return self._inplace("bitwise_or", o)
+    def __ixor__(self, o): return self._inplace("bitwise_xor", o)
+    def __ilshift__(self, o): return self._inplace("left_shift", o)
+    def __irshift__(self, o): return self._inplace("right_shift", o)
     def __neg__(self): return apply_ufunc(self.trace, "negative", (self,))
     def __pos__(self): return self
     def __abs__(self): return apply_ufunc(self.trace, "absolute", (self,))
@@ -449,6 +506,22 @@ class LazyArray:
 
     def clip(self, a_min=None, a_max=None):
         return clip_lazy(self.trace, self, a_min, a_max)
+
+    def var(self, axis=None): return var_lazy(self.trace, self, axis=axis)
+    def std(self, axis=None): return apply_ufunc(self.trace, "sqrt", (var_lazy(self.trace, self, axis=axis),))
+    def any(self, axis=None): return truth_reduce(self.trace, np.any, self, axis=axis)
+    def all(self, axis=None): return truth_reduce(self.trace, np.all, self, axis=axis)
+
+    def copy(self):
+        out = self.trace.leaf(self.trace.add_tmp_slot(self.shape, self.dtype))
+        out[...] = self
+        return out
+
+    def ravel(self):
+        return self.reshape(-1)
+
+    def flatten(self):
+        return self.copy().reshape(-1)
     def argmin(self, axis=None): return reduce_lazy(self.trace, "argmin", self, axis=axis)
     def argmax(self, axis=None): return reduce_lazy(self.trace, "argmax", self, axis=axis)
     def dot(self, other): return dot(self.trace, self, other)
@@ -613,6 +686,47 @@ def mean_lazy(trace, a, axis=None, dtype=None, keepdims=False, out=None):
     return total / dtype.type(count)
 
 
+def var_lazy(trace, a, axis=None, dtype=None, keepdims=False, ddof=0, out=None):
+    """np.var as NumPy computes it: mean(|x - mean(x)|^2)."""
+    if out is not None or ddof != 0:
+        raise TypeError("out= and ddof are not supported on device arrays")
+    if not isinstance(a, LazyArray):
+        a = LazyArray(trace, _as_node(trace, a))
+    m = mean_lazy(trace, a, axis=axis, dtype=dtype, keepdims=True)
+    d = a - m
+    return mean_lazy(trace, d * d, axis=axis, dtype=dtype, keepdims=keepdims)
+
+
+def truth_reduce(trace, func, a, axis=None, keepdims=False, out=None):
+    """np.any / np.all / np.count_nonzero through the min / max / sum kernels."""
+    if out is not None:
+        raise TypeError("out= is not supported on device arrays")
+    if not isinstance(a, LazyArray):
+        a = LazyArray(trace, _as_node(trace, a))
+    nz = a if a.dtype == np.bool_ else (a != a.dtype.type(0))
+    if func is np.count_nonzero:
+        return reduce_lazy(trace, "sum", nz.astype(np.int64), axis=axis, keepdims=keepdims)
+    return reduce_lazy(trace, "max" if func is np.any else "min", nz, axis=axis, keepdims=keepdims)
+
+
+def concatenate_lazy(trace, arrays, axis=0, out=None, dtype=None):
+    if out is not None:
+        raise TypeError("out= is not supported on device arrays")
+    parts = [x if isinstance(x, LazyArray) else LazyArray(trace, _as_node(trace, x)) for x in arrays]
+    nd = len(parts[0].shape)
+    axis %= nd
+    dt = np.dtype(dtype) if dtype is not None else np.result_type(*[p.dtype for p in parts])
+    shape = list(parts[0].shape)
+    shape[axis] = sum(p.shape[axis] for p in parts)
+    res = trace.leaf(trace.add_tmp_slot(tuple(shape), dt))
+    pos = 0
+    for p in parts:
+        idx = tuple(slice(pos, pos + p.shape[axis]) if d == axis else slice(None) for d in range(nd))
+        res[idx] = p
+        pos += p.shape[axis]
+    return res
+
+
 def clip_lazy(trace, a, a_min=None, a_max=None, out=None):
     """np.clip: bounds are converted to the array's type, as Numba types it."""
     if out is not None:
@@ -645,6 +759,15 @@ def _reduce_node(trace, op, a, axis, reduce_ops):
 def dot(trace, a, b, out=None):
     from . import contraction
 
+    a = a if isinstance(a, LazyArray) else LazyArray(trace, _as_node(trace, a))
+    b = b if isinstance(b, LazyArray) else LazyArray(trace, _as_node(trace, b))
+    if out is None and (len(a.shape) == 1 or len(b.shape) == 1):
+        # vector operands: the matrix product of the reshaped operands
+        if len(a.shape) == 1 and len(b.shape) == 1:
+            return reduce_lazy(trace, "sum", a * b)
+        if len(a.shape) == 1:
+            return dot(trace, a.reshape(1, a.shape[0]), b).reshape(b.shape[1])
+        return dot(trace, a, b.reshape(b.shape[0], 1)).reshape(a.shape[0])
     sa, sb = trace.materialize(a), trace.materialize(b)
     A, B = trace.arrays[sa], trace.arrays[sb]
     if A.ndim != 2 or B.ndim != 2 or A.shape[1] != B.shape[0]:
