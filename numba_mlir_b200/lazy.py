@@ -884,9 +884,15 @@ def _emit_eltwise(trace, out_shape, outs):
         return
     em = _Emitter(trace, out_shape)
     results = [(slot, em.emit(node), trace.arrays[slot]) for slot, node in outs]
-    for slot, _expr, arr in results:
-        if not arr.is_c_contiguous:
-            raise TypeError("assignment targets must be C-contiguous")
+
+    def out_strides(arr):
+        """Element strides of a non-contiguous assignment target (a sliced or
+        transposed view), None for a contiguous one."""
+        if arr.is_c_contiguous:
+            return None
+        return tuple(st // arr.dtype.itemsize for st in arr.strides)
+
+    ostrides = [out_strides(arr) for _s, _e, arr in results]
     # vector width: 4 elements per step when every access allows it
     vec_ok = True
     for slot, kind, params, dt in em.leaves:
@@ -898,20 +904,21 @@ def _emit_eltwise(trace, out_shape, outs):
             vec_ok = False
         if kind == "strided":
             pass
-    for slot, _expr, arr in results:
+    for (slot, _expr, arr), st in zip(results, ostrides):
         unit = 4 * arr.dtype.itemsize if arr.dtype.itemsize <= 4 else 16
-        if arr.ptr % unit:
+        if st is None and arr.ptr % unit:
             vec_ok = False
     vec = 4 if vec_ok else 1
     n_streams = sum(1 for _s, k, _p, _d in em.leaves if k == "full") + len(results)
     unroll = 4 if n_streams <= 3 else 2
 
-    sig = (tuple(out_shape) if any(k == "strided" for _s, k, _p, _d in em.leaves) else len(out_shape),
+    shaped = any(k == "strided" for _s, k, _p, _d in em.leaves) or any(st is not None for st in ostrides)
+    sig = (tuple(out_shape) if shaped else len(out_shape),
            tuple((k, p if k == "strided" else (), d.name) for _s, k, p, d in em.leaves),
-           tuple(em.sig), tuple((e, a.dtype.name) for _s, e, a in results), vec, unroll)
+           tuple(em.sig), tuple((e, a.dtype.name, st) for (_s, e, a), st in zip(results, ostrides)), vec, unroll)
     hit = _kernel_cache.get(sig)
     if hit is None:
-        hit = _generate(em, results, out_shape, vec, unroll)
+        hit = _generate(em, results, out_shape, vec, unroll, ostrides)
         _kernel_cache[sig] = hit
     blob, kname = hit
 
@@ -932,7 +939,7 @@ def _emit_eltwise(trace, out_shape, outs):
         run_launch(trace.queue, step, trace.arrays, trace.args)
 
 
-def _generate(em, results, out_shape, vec, unroll):
+def _generate(em, results, out_shape, vec, unroll, ostrides):
     """CUDA C for one fused chain; returns (tagged source blob, kernel name)."""
     members, ctor, kparams = [], [], []
     in_fields, loads = [], []
@@ -978,7 +985,14 @@ def _generate(em, results, out_shape, vec, unroll):
         ctor.append(f"out{j}")
         out_fields.append(f"nmb::Vec<{ct}, V> out{j};")
         out_assign.append(f"o.out{j}.v[l] = {expr};")
-        stores.append(f"nmb::store_stream<{ct}, V>(out{j} + i, o.out{j});")
+        if ostrides[j] is None:
+            stores.append(f"nmb::store_stream<{ct}, V>(out{j} + i, o.out{j});")
+        else:  # a strided view: decompose the flat index over the output shape
+            body = ["for (int l = 0; l < V; ++l) { int64_t rem = i + l, off = 0;"]
+            for d in range(nd - 1, -1, -1):
+                body.append(f"off += (rem % {out_shape[d]}ll) * ({ostrides[j][d]}ll); rem /= {out_shape[d]}ll;")
+            body.append(f"out{j}[off] = o.out{j}.v[l]; }}")
+            stores.append(" ".join(body))
     kparams.append("int64_t n")
     nl = "\n      "
     funcs = "\n".join(em.funcs.values())

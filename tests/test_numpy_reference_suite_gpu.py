@@ -194,3 +194,19 @@ def test_in_place_operators_and_slice_assignment_write_through(queue):
     nm.njit(f)(_dev(_A), do, dp)
     np.testing.assert_equal(do.copy_to_host(), o)
     np.testing.assert_equal(dp.copy_to_host(), p)
+
+
+def test_assignment_into_strided_views(queue):
+    import numba_mlir_b200 as nm
+
+    def f(a, o, t):
+        o[:, 1:4] = a[:, 0:3] * 2
+        o[::2, 5] = np.float32(7)
+        t.T[:] = a
+
+    o, t = np.zeros_like(_A), np.zeros((6, 4), np.float32)
+    f(_A, o, t)
+    do, dt = _dev(np.zeros_like(_A)), _dev(np.zeros((6, 4), np.float32))
+    nm.njit(f)(_dev(_A), do, dt)
+    np.testing.assert_equal(do.copy_to_host(), o)
+    np.testing.assert_equal(dt.copy_to_host(), t)
