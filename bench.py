@@ -51,14 +51,14 @@ def measured_peaks():
 # kernel, from the ncu captures summarised under profiles/ (scaled to the full
 # workload where the capture ran a smaller case).
 NCU_TRAFFIC_BYTES = {
-    "black_scholes": 201364992 + 91566336,   # output partly still dirty in L2 at kernel end
+    "black_scholes": 201363968 + 91807744,   # output partly still dirty in L2 at kernel end
     "bcast_add": 16794112 + 0,               # two-launch capture: the result stays in L2
-    "sum_axis1": 268469760 + 3785216,
-    "min_axis0": 268467200 + 3999744,
-    "argmin_axis1": 268478464 + 3777536,
-    "int_sum": 1073763328 + 3568896,
-    "pairwise": 28242432 + 1014891264,       # nmb_contract_tf32x3 (prepass: 8409856 + 0)
-    "kmeans": 268473344 + 16820736,
+    "sum_axis1": 268465152 + 4111360,
+    "min_axis0": 268462592 + 3502848,
+    "argmin_axis1": 268475392 + 3548416,
+    "int_sum": 1073784576 + 4129280,
+    "pairwise": 27649280 + 1015031552,       # nmb_contract_tf32x3 (prepass: 8409856 + 0)
+    "kmeans": 268464128 + 15941376,
 }
 
 
