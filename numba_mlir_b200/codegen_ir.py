@@ -255,6 +255,9 @@ class Translator:
         self.uses_group_reduce = False
         self.counter = 0
         self.par_ranges = {}      # range variable -> (id expr, count expr): grid-strided loops
+        self.block_prologue = {}  # block label -> C statements placed at its start
+        self.block_epilogue = {}  # block label -> C statements placed before its terminator
+        self.return_store = None  # parfor mode: C lvalue the scalar return value is written to
 
     # naming -------------------------------------------------------------------
     def cname(self, name):
@@ -811,8 +814,10 @@ class Translator:
         order = sorted(blocks)
         body = []
         for label in order:
-            out = [f"L{label}: ;"]
+            out = [f"L{label}: ;"] + list(self.block_prologue.get(label, ()))
             for inst in blocks[label].body:
+                if isinstance(inst, (ir.Jump, ir.Branch, ir.Return)) and label in self.block_epilogue:
+                    out.extend(self.block_epilogue[label])
                 if isinstance(inst, ir.Assign):
                     if isinstance(inst.value, ir.Const) and inst.value.value is ir.UNDEFINED:
                         continue
@@ -846,7 +851,9 @@ class Translator:
                     out.append(f"if ({self.scalar(inst.cond, types.boolean)}) goto L{inst.truebr}; "
                                f"else goto L{inst.falsebr};")
                 elif isinstance(inst, ir.Return):
-                    if self.mode in ("kernel", "parfor"):
+                    if self.mode == "parfor" and self.return_store is not None:
+                        out.append(f"{self.return_store} = {self.scalar(inst.value, self.tir.return_type)}; return;")
+                    elif self.mode in ("kernel", "parfor"):
                         out.append("return;")
                     else:
                         out.append(f"return {self.scalar(inst.value, self.tir.return_type)};")
@@ -1007,10 +1014,15 @@ class CompiledParfor(CompiledKernel):
     work out from the arguments (None where it could not); the loops are
     grid-strided, so any launch shape is correct and the extents only size it."""
 
-    def __init__(self, source, name, param_layout, inner_parallel, extent_fns):
+    def __init__(self, source, name, param_layout, inner_parallel, extent_fns, epilogue=None,
+                 return_dtype=None):
         CompiledKernel.__init__(self, source, name, param_layout, False)
         self.inner_parallel = inner_parallel
         self.extent_fns = extent_fns
+        # epilogue: None, or the bytes of per-block partials the kernel needs (it then
+        # takes three more pointers: partials, ticket counter, return cell)
+        self.epilogue = epilogue
+        self.return_dtype = return_dtype
 
     def extents(self, args):
         out = []
@@ -1149,10 +1161,11 @@ def compile_parfor(py_func, args, fastmath=False):
 
     argtypes = [_argtype_of(a) for a in args]
     tir = typed_ir(py_func, argtypes)
-    if not isinstance(tir.return_type, types.NoneType):
+    returns_scalar = _is_scalar(types.unliteral(tir.return_type))
+    if not returns_scalar and not isinstance(tir.return_type, types.NoneType):
         raise UnsupportedError(
-            f"{py_func.__name__}: a function with prange loops must return None (results go to "
-            "array arguments)")
+            f"{py_func.__name__}: a function with prange loops returns None or a scalar (array "
+            "results go to array arguments)")
     tr = Translator(tir, "parfor", "nmb_parfor")
     ir = tr.ir
     blocks = tir.func_ir.blocks
@@ -1228,14 +1241,28 @@ def compile_parfor(py_func, args, fastmath=False):
             f"(found {len(par_top)})")
     outer, (outer_name, outer_call) = par_top[0]
     carried, escaping = independent(outer)
-    if carried or escaping:
+    reductions = _find_reductions(tr, blocks, defs, outer, carried, escaping)
+    if reductions is None:
         raise UnsupportedError(
             f"{py_func.__name__}: scalar(s) {sorted(carried | escaping)} are carried across or out of "
-            "the prange loop (reductions over prange are not supported; use an array reduction or "
-            "atomic.add)")
-    if side_effects(set(blocks) - set(outer.body)):
+            "the prange loop in a form that is not a reduction (supported: s += x, s -= x, s *= x, "
+            "s = min(s, x), s = max(s, x), with s not read otherwise inside the loop)")
+    before = set()  # blocks that can run before the loop: every thread executes them
+    work = list(outer.entries)
+    while work:
+        lb = work.pop()
+        if lb not in before:
+            before.add(lb)
+            work.extend(p_ for p_, _ in cfg.predecessors(lb))
+    if side_effects(before):
         raise UnsupportedError(
-            f"{py_func.__name__}: array stores outside the prange loop are not supported")
+            f"{py_func.__name__}: array stores before the prange loop are not supported (every "
+            "thread runs that code)")
+    after = set(blocks) - set(outer.body) - before
+    # Code after the loop must run once, after every thread has finished: it is
+    # left to the last thread block to arrive (a ticket), which also combines
+    # the reduction partials.
+    needs_epilogue = bool(reductions) or returns_scalar or side_effects(after)
 
     inner = None
     level2 = [lp for lp in loops.values() if lp is not outer and lp.header in outer.body
@@ -1248,6 +1275,8 @@ def compile_parfor(py_func, args, fastmath=False):
         if not c2 and not e2 and not side_effects(set(outer.body) - set(lp.body)):
             inner = (lp, nm, call)
 
+    if needs_epilogue:
+        inner = None  # the epilogue assumes a one-dimensional grid
     if inner is not None:
         tr.par_ranges[outer_name] = ("nmb_oid", "nmb_on")
         tr.par_ranges[inner[1]] = ("nmb_iid", "nmb_in")
@@ -1260,9 +1289,14 @@ def compile_parfor(py_func, args, fastmath=False):
         ids = ("const int64_t nmb_oid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, "
                "nmb_on = (int64_t)gridDim.x * blockDim.x;")
 
+    epilogue_bytes = None
+    if needs_epilogue:
+        epilogue_bytes = _install_epilogue(tr, outer, reductions)
+        if returns_scalar:
+            tr.return_store = f"*({c_scalar_type(tir.return_type)}*)nmb_ret"
     pnames = [f"p{i}" for i in range(len(argtypes))]
     body = tr.translate(pnames)
-    if tr.shared_decls or tr.uses_barrier:
+    if (tr.shared_decls and not needs_epilogue) or tr.uses_barrier:
         raise UnsupportedError("work-group local memory and barriers belong to @kernel functions")
     written = {int(r[6:-1]) for r in tr.written_params if r.startswith("<param")}
     kparams, layout = [], []
@@ -1279,14 +1313,17 @@ def compile_parfor(py_func, args, fastmath=False):
         else:
             kparams.append(f"{c_scalar_type(t)} p{i}")
             layout.append(("scalar", np.dtype(str(t))))
+    if needs_epilogue:
+        kparams += ["unsigned char* nmb_partials", "unsigned int* nmb_ticket", "void* nmb_ret"]
     opts = "" if fastmath else " --fmad=false"
     src = f"""//NMB200:CUDA-SOURCE
 //NMB200:OPTIONS{opts}
 #include "nmb_device.cuh"
-extern "C" __global__ void nmb_parfor({', '.join(kparams)}) {{
+extern "C" __global__ void __launch_bounds__(256) nmb_parfor({', '.join(kparams)}) {{
     {ids}
     const int64_t nmb_gs[3] = {{1, 1, 1}};
     (void)nmb_gs;
+    {' '.join(tr.shared_decls)}
     {chr(10).join('    ' + d for d in tr.decls)}
     {(chr(10) + '    ').join(body)}
 }}
@@ -1294,4 +1331,126 @@ extern "C" __global__ void nmb_parfor({', '.join(kparams)}) {{
     fns = [_extent_fn(tr, defs, outer_call)]
     if inner is not None:
         fns.append(_extent_fn(tr, defs, inner[2]))
-    return CompiledParfor(src, "nmb_parfor", layout, inner is not None, fns)
+    from numba.np.numpy_support import as_dtype
+
+    return CompiledParfor(src, "nmb_parfor", layout, inner is not None, fns, epilogue=epilogue_bytes,
+                          return_dtype=as_dtype(tir.return_type) if returns_scalar else None)
+
+
+_REDUCTION_OPS = {operator.add: ("OpAdd", "add"), operator.iadd: ("OpAdd", "add"),
+                  operator.sub: ("OpAdd", "add"), operator.isub: ("OpAdd", "add"),
+                  operator.mul: ("OpMul", "mul"), operator.imul: ("OpMul", "mul")}
+
+
+def _find_reductions(tr, blocks, defs, loop, carried, escaping):
+    """Reduction variables of a parallel loop: [(variable, op struct, neutral name)], or
+    None when a carried or escaping scalar is anything else.
+
+    After SSA and phi stripping a reduction `s += x` reads
+        s.2 = s              (before the loop)
+        t = s.2 + x ; s.1 = t ; s.2 = s.1      (in the body)
+    i.e. the carried variable is assigned once in the body, from a value
+    computed by one + - * (or min / max call) that has the carried variable as
+    an operand, and is not read anywhere else in the body."""
+    ir, types = tr.ir, tr.types
+    if escaping - carried:
+        return None
+    body_insts = [inst for lb in loop.body for inst in blocks[lb].body]
+    found = []
+    for v in sorted(carried):
+        if not _is_scalar(types.unliteral(tr.vtype(v))):
+            return None
+        assigns = [inst for inst in body_insts if isinstance(inst, ir.Assign) and inst.target.name == v]
+        if len(assigns) != 1 or not isinstance(assigns[0].value, ir.Var):
+            return None
+        # the update expression, through single-assignment copies made in the body
+        name, upd, chain = assigns[0].value.name, None, []
+        for _ in range(8):
+            chain.append(name)
+            d = [inst.value for inst in body_insts if isinstance(inst, ir.Assign) and inst.target.name == name]
+            if len(d) != 1:
+                return None
+            if isinstance(d[0], ir.Var):
+                name = d[0].name
+                continue
+            upd = d[0]
+            break
+        # the running value must not be observed on its way (that would be a scan)
+        for c in chain:
+            uses = sum(1 for inst in body_insts for u in inst.list_vars() if u.name == c)
+            if uses != 2 or c in escaping:  # its definition and the copy onwards
+                return None
+        if not isinstance(upd, ir.Expr):
+            return None
+        if upd.op in ("binop", "inplace_binop") and upd.fn in _REDUCTION_OPS:
+            operands = [upd.lhs.name, upd.rhs.name]
+            if upd.fn in (operator.sub, operator.isub) and upd.lhs.name != v:
+                return None
+            opinfo = _REDUCTION_OPS[upd.fn]
+        elif upd.op == "call" and len(upd.args) == 2 and not upd.kws:
+            fn = tr.callee(upd.func)
+            if fn is min:
+                opinfo = ("OpMin", "min")
+            elif fn is max:
+                opinfo = ("OpMax", "max")
+            else:
+                return None
+            operands = [a.name for a in upd.args]
+        else:
+            return None
+        if operands.count(v) != 1:
+            return None
+        reads = sum(1 for inst in body_insts for u in inst.list_vars() if u.name == v) - 1  # its own assignment
+        if reads != 1:
+            return None
+        found.append((v, opinfo[0], opinfo[1]))
+    return found
+
+
+def _install_epilogue(tr, loop, reductions):
+    """Hooks the grid-wide epilogue of a prange kernel into the translation and
+    returns the bytes of partials one thread block contributes.
+
+    Before the loop every thread swaps each reduction variable for the neutral
+    element and keeps the incoming value.  At the loop exit the block reduces
+    its threads' partials, thread 0 publishes them and draws a ticket; every
+    block but the last to arrive leaves.  The last block combines the
+    published partials in block order (so the result does not depend on
+    scheduling), applies the incoming value, resets the ticket and its thread
+    0 alone runs what follows the loop."""
+    types = tr.types
+    pre, post = [], []
+    slot = 0
+    tr.decls.append("bool nmb_last_block;")
+    tr.shared_decls.append("__shared__ bool nmb_is_last;")
+    for k, (v, opname, neutral) in enumerate(reductions):
+        t = types.unliteral(tr.vtype(v))
+        ct = c_scalar_type(t)
+        tr.declare(v)
+        c = tr.cname(v)
+        tr.decls.append(f"{ct} nmb_init{k};")
+        tr.shared_decls.append(f"__shared__ {ct} nmb_rs{k}[32];")
+        pre.append(f"nmb_init{k} = {c}; {c} = nmb::neutral_{neutral}<{ct}>();")
+        post.append(f"{c} = nmb::block_reduce(({ct}){c}, nmb::{opname}(), nmb::neutral_{neutral}<{ct}>(), nmb_rs{k});")
+        post.append(f"if (threadIdx.x == 0) (({ct}*)(nmb_partials + {slot} * (size_t)gridDim.x))[blockIdx.x] = {c};")
+        slot += 8
+    post.append("if (threadIdx.x == 0) { __threadfence(); "
+                "nmb_is_last = atomicAdd(nmb_ticket, 1u) == gridDim.x - 1; }")
+    post.append("__syncthreads(); nmb_last_block = nmb_is_last; if (!nmb_last_block) return; __threadfence();")
+    slot = 0
+    for k, (v, opname, neutral) in enumerate(reductions):
+        t = types.unliteral(tr.vtype(v))
+        ct = c_scalar_type(t)
+        c = tr.cname(v)
+        post.append(f"{c} = nmb::neutral_{neutral}<{ct}>(); "
+                    f"for (unsigned nmb_b = threadIdx.x; nmb_b < gridDim.x; nmb_b += blockDim.x) "
+                    f"{c} = nmb::{opname}()({c}, __ldcg((const {ct}*)(nmb_partials + {slot} * (size_t)gridDim.x) + nmb_b)); "
+                    f"{c} = nmb::block_reduce(({ct}){c}, nmb::{opname}(), nmb::neutral_{neutral}<{ct}>(), nmb_rs{k}); "
+                    f"{c} = nmb::{opname}()(nmb_init{k}, {c});")
+        slot += 8
+    post.append("if (threadIdx.x != 0) return; *nmb_ticket = 0u;")
+    for lb in loop.entries:
+        tr.block_epilogue.setdefault(lb, []).extend(pre)
+    for lb in loop.exits:
+        tr.block_prologue.setdefault(lb, []).extend(post)
+    return max(slot, 8)

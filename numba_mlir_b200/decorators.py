@@ -134,11 +134,25 @@ class Dispatcher:
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
         kernel = ck.handle_on(queue)
         grid, block = parfor_launch_shape(ck.extents(args), ck.inner_parallel)
-        if grid is None:
+        values = kernel_impl.marshal_values(args, ck.param_layout)
+        if ck.epilogue is None:
+            if grid is not None:
+                queue.launch_values(kernel, grid, block, ck.kinds(), values)
             return None
-        queue.launch_values(kernel, grid, block, ck.kinds(),
-                            kernel_impl.marshal_values(args, ck.param_layout))
-        return None
+        # Reductions, code after the loop, a scalar result: the kernel needs room
+        # for one partial per block and reduction, a ticket and the result cell;
+        # an empty loop still runs (one block) for what follows it.
+        if grid is None:
+            grid, block = (1,), (256,)
+        counters, data = queue.scratch(ck.epilogue * grid[0] + 16)
+        ret = data + ck.epilogue * grid[0]
+        ret += -ret % 8
+        queue.launch_values(kernel, grid, block, ck.kinds() + ("ptr", "ptr", "ptr"), values + [data, counters, ret])
+        if ck.return_dtype is None:
+            return None
+        host = np.zeros(1, ck.return_dtype)
+        queue.memcpy(host.ctypes.data, ret, host.nbytes, _rt.COPY_D2H, wait=True)
+        return host[0]
 
     def trace_dry(self, *args):
         """Records the plan and generates the kernels without a device (used

@@ -62,29 +62,24 @@ def test_update_of_an_element_becomes_an_atomic(runtime_lib):
     assert ck.extents((10000, 10, None)) == [10000]
 
 
-def test_scalar_reduction_over_prange_is_rejected():
+def test_store_before_the_loop_is_rejected_and_after_it_runs_once(runtime_lib):
     from numba_mlir_b200 import codegen_ir
 
-    def f(a, out):
-        s = 0.0
-        for i in numba.prange(len(a)):
-            s += a[i]
-        out[0] = s
-
-    with pytest.raises(codegen_ir.UnsupportedError, match="carried"):
-        codegen_ir.compile_parfor(f, (np.zeros(4, np.float32), np.zeros(1, np.float32)))
-
-
-def test_store_outside_the_loop_is_rejected():
-    from numba_mlir_b200 import codegen_ir
-
-    def f(a):
+    def before(a):
         a[0] = 1.0
         for i in numba.prange(len(a)):
             a[i] = 2.0
 
-    with pytest.raises(codegen_ir.UnsupportedError, match="outside"):
-        codegen_ir.compile_parfor(f, (np.zeros(4, np.float32),))
+    with pytest.raises(codegen_ir.UnsupportedError, match="before"):
+        codegen_ir.compile_parfor(before, (np.zeros(4, np.float32),))
+
+    def after(a, out):
+        for i in numba.prange(len(a)):
+            a[i] = 2.0
+        out[0] = 5.0
+
+    ck = _compile(after, (np.zeros(4, np.float32), np.zeros(1, np.float32)))
+    assert ck.epilogue == 8  # no reductions, but the tail needs the ticket
 
 
 def test_launch_shapes():
@@ -98,3 +93,30 @@ def test_launch_shapes():
     assert shape([8, 16], True) == ((1, 1), (16, 16))
     grid, block = shape([1 << 22, 3], True)
     assert block == (4, 64) and grid[0] == 1
+
+
+def test_reductions_are_recognised_and_get_the_grid_epilogue(runtime_lib):
+    def f(a):
+        s = 0.0
+        m = a[0]
+        for i in numba.prange(len(a)):
+            s += a[i]
+            m = min(m, a[i])
+        return s + m
+
+    ck = _compile(f, (np.zeros(100, np.float32),))
+    assert ck.epilogue == 16 and ck.return_dtype == np.float64 and not ck.inner_parallel
+    assert "nmb_ticket" in ck.source and "nmb::block_reduce" in ck.source
+
+
+def test_running_value_read_inside_the_loop_is_not_a_reduction():
+    from numba_mlir_b200 import codegen_ir
+
+    def f(a, out):
+        s = 0.0
+        for i in numba.prange(len(a)):
+            s += a[i]
+            out[i] = s  # a prefix sum: order dependent
+
+    with pytest.raises(codegen_ir.UnsupportedError, match="not a reduction"):
+        codegen_ir.compile_parfor(f, (np.zeros(4, np.float32), np.zeros(4, np.float32)))

@@ -171,3 +171,64 @@ def test_pairwise2(queue):
     jit_func(_dev(a), _dev(b), got)
     assert jit_func._parfor_kernels and all(k.inner_parallel for k in jit_func._parfor_kernels.values())
     np.testing.assert_allclose(got.copy_to_host(), res, rtol=1e-5)
+
+
+@pytest.mark.parametrize("n", [0, 1, 255, 256, 1000, (1 << 20) + 7])
+def test_prange_scalar_reductions(queue, n):
+    """Sums, products, minima and maxima carried across a prange loop (the loop
+    form of what the reference lowers through its GPU global reduce,
+    mlir/lib/Conversion/GpuToGpuRuntime.cpp:2002-2277), combined per block and
+    then in block order by the last block to finish."""
+    import numba_mlir_b200 as nm
+
+    def total(a):
+        s = 0
+        for i in numba.prange(len(a)):
+            s += a[i]
+        return s
+
+    def fsum_min_max(a):
+        s = 0.0
+        lo = np.float32(np.inf)
+        hi = np.float32(-np.inf)
+        for i in numba.prange(len(a)):
+            s += a[i]
+            lo = min(lo, a[i])
+            hi = max(hi, a[i])
+        return s * 2 + lo - hi
+
+    rng = np.random.default_rng(n)
+    ints = rng.integers(-1000, 1001, n).astype(np.int32)
+    got = nm.njit(total, parallel=True)(_dev(ints))
+    assert int(got) == int(ints.sum(dtype=np.int64))
+
+    x = (rng.integers(-64, 64, n) / 8).astype(np.float32)  # sums exactly in float64 in any order
+    if n:
+        got = nm.njit(fsum_min_max, parallel=True)(_dev(x))
+        assert got == x.astype(np.float64).sum() * 2 + float(x.min()) - float(x.max())
+
+
+def test_prange_reduction_with_start_value_product_and_tail_store(queue):
+    import numba_mlir_b200 as nm
+
+    def f(a, start, out):
+        s = start
+        p = 1.0
+        for i in numba.prange(len(a)):
+            s -= a[i]
+            p *= np.float64(1.0) + a[i] * 0
+        out[0] = s      # runs once, after every thread is done
+        out[1] = p
+        return s
+
+    a = np.arange(5000, dtype=np.float64)
+    out = _dev(np.zeros(2, np.float64))
+    got = nm.njit(f, parallel=True)(_dev(a), 10.0, out)
+    assert got == 10.0 - a.sum()
+    np.testing.assert_equal(out.copy_to_host(), [10.0 - a.sum(), 1.0])
+    # the ticket is back at zero: the same kernel runs again and so do the reductions
+    got = nm.njit(f, parallel=True)(_dev(a), 1.0, out)
+    assert got == 1.0 - a.sum()
+    from numba_mlir_b200 import reduce_ops
+
+    assert reduce_ops.reduce(_dev(a), "sum").copy_to_host() == a.sum()
