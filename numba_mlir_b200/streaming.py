@@ -111,10 +111,21 @@ class HostPipeline:
 _pipelines = {}
 
 
-def map_host(func, inputs, outputs, scalars=(), chunk=1 << 22, queue=None):
+def auto_chunk(n):
+    """About four chunks per call (enough for the copy-in of one to hide behind
+    the copy-out of another), between 2^18 and 2^22 elements, a multiple of 1024."""
+    c = -(-int(n) // 4)
+    c = max(1 << 18, min(1 << 22, c))
+    return -(-c // 1024) * 1024
+
+
+def map_host(func, inputs, outputs, scalars=(), chunk=None, queue=None):
     """One call: `func(*inputs, *scalars, *outputs)` with host arrays in and
     out, copies overlapped with the kernels.  Pipelines (device buffers and
-    queues) are kept per function and dtype list."""
+    queues) are kept per function, dtype list and chunk size (`chunk=None`
+    picks one from the length)."""
+    if chunk is None:
+        chunk = auto_chunk(inputs[0].shape[0] if inputs else outputs[0].shape[0])
     key = (id(func), tuple(a.dtype.str for a in inputs), tuple(a.dtype.str for a in outputs), int(chunk),
            None if queue is None else id(queue))
     entry = _pipelines.get(key)
