@@ -19,6 +19,8 @@
 
 #include "bulk_pipe.cuh"
 
+#include <type_traits>
+
 namespace nmb {
 namespace red {
 
@@ -61,6 +63,7 @@ template <typename T> struct SumR {
   // Hot-loop accumulator: position k counts the thread's visits in increasing
   // index order; only index-carrying reducers need it.
   using Fast = Acc;
+  static constexpr bool kTwoPass = false;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
   template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
@@ -77,6 +80,7 @@ template <typename T> struct ProdR {
   // Hot-loop accumulator: position k counts the thread's visits in increasing
   // index order; only index-carrying reducers need it.
   using Fast = Acc;
+  static constexpr bool kTwoPass = false;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
   template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
@@ -93,6 +97,7 @@ template <typename T> struct MinR {
   // Hot-loop accumulator: position k counts the thread's visits in increasing
   // index order; only index-carrying reducers need it.
   using Fast = Acc;
+  static constexpr bool kTwoPass = false;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
   template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
@@ -109,6 +114,7 @@ template <typename T> struct MaxR {
   // Hot-loop accumulator: position k counts the thread's visits in increasing
   // index order; only index-carrying reducers need it.
   using Fast = Acc;
+  static constexpr bool kTwoPass = false;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
   template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
@@ -143,7 +149,23 @@ template <typename T, bool MIN> struct ArgR {
     r.i = __shfl_xor_sync(0xffffffffu, a.i, off);
     return r;
   }
-  static __device__ __forceinline__ Out fin(Acc a) { return a.i; }
+  // no element compared below (above) the identity: the first one is as good as any
+  static __device__ __forceinline__ Out fin(Acc a) { return a.i == 0x7fffffffffffffffll ? 0 : a.i; }
+  // Two-pass form for a batch of values a thread visits in index order: one
+  // min (max) instruction per value, and only when the batch beats the
+  // running value (rare after the first batches) a scan for the first value
+  // equal to the batch extreme.
+  static constexpr bool kTwoPass = true;
+  static __device__ __forceinline__ T pick(T a, T b) {
+    if constexpr (std::is_same<T, float>::value) {
+      return MIN ? fminf(a, b) : fmaxf(a, b); // NaNs lose, as they do against `<`
+    } else if constexpr (std::is_same<T, double>::value) {
+      return MIN ? fmin(a, b) : fmax(a, b);
+    } else {
+      return MIN ? (b < a ? b : a) : (a < b ? b : a);
+    }
+  }
+  static __device__ __forceinline__ bool beats(T x, T running) { return MIN ? (x < running) : (running < x); }
   // A thread visits its elements in increasing index order, so a strict
   // comparison keeps the first occurrence and a 32-bit visit counter is enough;
   // the 64-bit index is rebuilt once at the end.

@@ -94,15 +94,50 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
       const int nvec = (int)((cols - c0 < CH ? cols - c0 : CH) / VEC);
       if (r < rows) {
         const T *src = tiles + (int64_t)s * TILE + (int64_t)warp * CH;
+        if constexpr (R::kTwoPass) {
+          // index-carrying reducers: extreme of the batch first, position only
+          // if the batch wins (visits past the row's end hold the identity)
+          Vec<T, VEC> x[VPC];
+          int nvis = 0;
 #pragma unroll
-        for (int v = 0; v < VPC; ++v) {
-          const int vi = lane + 32 * v;
-          if (vi < nvec) {
-            const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(src + vi * VEC);
+          for (int v = 0; v < VPC; ++v) {
+            const int vi = lane + 32 * v;
+            if (vi < nvec) {
+              x[v] = *reinterpret_cast<const Vec<T, VEC> *>(src + vi * VEC);
+              ++nvis;
+            } else {
 #pragma unroll
-            for (int l = 0; l < VEC; ++l)
-              R::fast_acc(f[l], x.v[l], k);
-            ++k;
+              for (int l = 0; l < VEC; ++l)
+                x[v].v[l] = R::fast_identity().v;
+            }
+          }
+#pragma unroll
+          for (int l = 0; l < VEC; ++l) {
+            T m = x[0].v[l];
+#pragma unroll
+            for (int v = 1; v < VPC; ++v)
+              m = R::pick(m, x[v].v[l]);
+            if (R::beats(m, f[l].v)) {
+              int first = VPC - 1;
+#pragma unroll
+              for (int v = VPC - 2; v >= 0; --v)
+                first = (x[v].v[l] == m) ? v : first;
+              f[l].v = m;
+              f[l].k = k + first;
+            }
+          }
+          k += nvis;
+        } else {
+#pragma unroll
+          for (int v = 0; v < VPC; ++v) {
+            const int vi = lane + 32 * v;
+            if (vi < nvec) {
+              const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(src + vi * VEC);
+#pragma unroll
+              for (int l = 0; l < VEC; ++l)
+                R::fast_acc(f[l], x.v[l], k);
+              ++k;
+            }
           }
         }
         if (ch == cpr - 1) {

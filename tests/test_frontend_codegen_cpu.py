@@ -1,0 +1,60 @@
+"""The array front end without a device: every function of the GPU suite's
+tables is traced on shape-only arrays and each generated kernel is compiled
+for sm_100a by NVRTC (library loaded, no GPU needed)."""
+
+import numpy as np
+import pytest
+
+import test_numpy_reference_suite_gpu as suite
+
+
+def _trace_and_compile(py_func, shapes_dtypes, scalars=()):
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import lazy, runtime
+
+    args = [lazy.fake_array(shape, dt) for shape, dt in shapes_dtypes] + list(scalars)
+    trace, _plan = nm.njit(py_func).trace_dry(*args)
+    launches = [s for s in trace.steps if s[0] == "launch"]
+    for step in launches:
+        assert len(runtime.compile_to_cubin(step[1])) > 0
+    return trace, launches
+
+
+@pytest.mark.parametrize("src", suite._unary)
+def test_unary_functions_generate_valid_kernels(runtime_lib, src):
+    _trace, launches = _trace_and_compile(eval("lambda a: " + src), [((2, 3), np.float32)])
+    assert len(launches) <= 1  # one fused kernel per expression (none for the identity)
+
+
+@pytest.mark.parametrize("src", suite._binary)
+@pytest.mark.parametrize("dtype", [np.int32, np.float32])
+def test_binary_functions_generate_valid_kernels(runtime_lib, src, dtype):
+    _trace, launches = _trace_and_compile(eval("lambda a, b: " + src), [((2, 3), dtype), ((2, 3), dtype)])
+    assert len(launches) == 1
+
+
+@pytest.mark.parametrize("src", suite._bitwise)
+def test_bitwise_functions_generate_valid_kernels(runtime_lib, src):
+    _trace_and_compile(eval("lambda a, b: " + src), [((2, 3), np.int32), ((2, 3), np.int32)])
+
+
+@pytest.mark.parametrize("src", suite._reduce_axis_funcs())
+def test_reductions_record_reduce_steps(runtime_lib, src):
+    trace, _launches = _trace_and_compile(eval(src), [((2, 3), np.float32)])
+    assert any(s[0] == "reduce" for s in trace.steps)
+
+
+def test_black_scholes_chain_is_one_kernel(runtime_lib):
+    from numba_mlir_b200 import workloads
+
+    arrs = [((1 << 16,), np.float32)] * 3
+    outs = [((1 << 16,), np.float32)] * 2
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import lazy, runtime
+
+    args = ([lazy.fake_array(s, d) for s, d in arrs] + [np.float32(0.1), np.float32(0.2)]
+            + [lazy.fake_array(s, d) for s, d in outs])
+    trace, plan = workloads.black_scholes.trace_dry(*args)
+    launches = [s for s in trace.steps if s[0] == "launch"]
+    assert len(launches) == 1 and plan is not None
+    assert len(runtime.compile_to_cubin(launches[0][1])) > 0

@@ -132,6 +132,33 @@ def test_argmin_ties_pick_first_occurrence(queue):
     assert np.array_equal(reduce_ops.reduce(_dev(b), "argmin", 0).copy_to_host(), np.full(64, 123))
 
 
+@pytest.mark.parametrize("cols", [600, 4096, 5000])
+def test_argmin_argmax_special_values_and_dense_ties(queue, cols):
+    """Rows of equal values, signed zeros, infinities and NaNs (which never win
+    a `<` comparison, numba_mlir/mlir/builtin/funcs.py:126-146), and many ties
+    inside one 16-byte vector and one tile."""
+    from numba_mlir_b200 import reduce_ops
+
+    rng = np.random.default_rng(cols)
+    a = rng.integers(0, 3, (40, cols)).astype(np.float32)      # dense ties
+    a[1] = 7.0                                                 # one value everywhere
+    a[2] = np.inf
+    a[3] = -np.inf
+    a[4, ::2] = -0.0
+    a[4, 1::2] = 0.0
+    a[5] = np.nan
+    a[5, 123] = 4.0                                            # the only ordered value
+    a[6, 17] = np.nan                                          # a NaN among ordinary values
+    for op, fn in (("argmin", np.argmin), ("argmax", np.argmax)):
+        got = reduce_ops.reduce(_dev(a), op, 1).copy_to_host()
+        want = fn(a, axis=1)
+        want[5] = 123                                          # NumPy would return the first NaN
+        b = a[6].copy()
+        b[17] = 1.0                                            # neither the minimum nor the maximum of the row
+        want[6] = fn(b)
+        np.testing.assert_array_equal(got, want)
+
+
 @pytest.mark.parametrize("dtype", [np.float64, np.int64, np.int32])
 def test_other_dtypes(queue, dtype):
     from numba_mlir_b200 import reduce_ops
