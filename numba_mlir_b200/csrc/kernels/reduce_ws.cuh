@@ -63,23 +63,29 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
 
     // Lane 0 of warp w fetches row w's chunk of the tile (a bulk copy costs the
     // issuing thread about 0.1 us, so one thread issuing all eight would hold
-    // the CTA back); thread 0 posts the byte count of the whole tile.  Every
-    // warp calls this for the same tiles in the same order.
+    // the CTA back); thread 0 posts the byte count of the whole tile.
+    // (row block, chunk) of the next tile to fetch and of the tile being reduced
+    // advance with the tile counters: no 64-bit division in the per-tile path
+    int64_t iblk = blk_begin, ich = 0, cblk = blk_begin, cch = 0;
     auto issue = [&](int64_t i) {
       const int s = (int)(i % kStages);
-      const int64_t r0 = (blk_begin + i / cpr) * kRowsPerBlock, c0 = (i % cpr) * CH;
+      const int64_t r0 = iblk * kRowsPerBlock, c0 = ich * CH;
+      if (++ich == cpr) {
+        ich = 0;
+        ++iblk;
+      }
       const int nr = (int)(rows - r0 < kRowsPerBlock ? rows - r0 : kRowsPerBlock);
       const uint32_t bytes = (uint32_t)((cols - c0 < CH ? cols - c0 : CH) * sizeof(T));
       if (tid == 0)
         mbar_expect_tx(&sm.full[s], bytes * nr);
-      if (warp < nr)
+      if (lane == 0 && warp < nr)
         bulk_load(tiles + (int64_t)s * TILE + (int64_t)warp * CH, a + (r0 + warp) * cols + c0, bytes,
                   &sm.full[s]);
     };
-    if (lane == 0)
-      for (; issued < kStages && issued < ntiles; ++issued)
-        issue(issued);
-    issued = ntiles < kStages ? ntiles : kStages; // the same count in every thread
+    // every thread runs `issue` (so that the counters stay in step); the copies
+    // themselves are made by lane 0 of each warp
+    for (; issued < kStages && issued < ntiles; ++issued)
+      issue(issued);
 
     Fast f[VEC];
 #pragma unroll
@@ -89,7 +95,11 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
     for (int64_t i = 0; i < ntiles; ++i) {
       const int s = (int)(i % kStages);
       stage_wait(&sm.full[s], i / kStages, dead, status);
-      const int64_t r = (blk_begin + i / cpr) * kRowsPerBlock + warp, ch = i % cpr;
+      const int64_t r = cblk * kRowsPerBlock + warp, ch = cch;
+      if (++cch == cpr) {
+        cch = 0;
+        ++cblk;
+      }
       const int64_t c0 = ch * CH;
       const int nvec = (int)((cols - c0 < CH ? cols - c0 : CH) / VEC);
       if (r < rows) {
@@ -158,11 +168,8 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
         }
       }
       __syncthreads(); // the whole CTA is done with stage s
-      if (issued < ntiles) {
-        if (lane == 0)
-          issue(issued);
-        ++issued;
-      }
+      if (issued < ntiles)
+        issue(issued++);
     }
   } else {
     // ---- narrow rows ----------------------------------------------------------

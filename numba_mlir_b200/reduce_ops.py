@@ -105,8 +105,7 @@ def _launch_cols(q, a, out, op, ty, rows, cols):
     it = a.dtype.itemsize
     # column slabs of 4 KB: each thread owns one 16-byte column vector and the
     # per-CTA partial rows stay short
-    import os as _os
-    tile_cols = min(cols, int(_os.environ.get('NMB_DEBUG_SLAB', '4096')) // it)
+    tile_cols = min(cols, 4096 // it)
     col_tiles = (cols + tile_cols - 1) // tile_cols
     rows_per_stage = _TILE_BYTES // (tile_cols * it)
     row_blocks = max(1, min((_CTAS + col_tiles - 1) // col_tiles,
