@@ -8,10 +8,10 @@
   extern "C" __global__ void __launch_bounds__(nmb::red::kThreads, 3)                             \
       nmb_reduce_cols_##op##_##ty(const R::In *a, R::Out *out, void *partials,                 \
                                   uint32_t *counters, int64_t rows, int64_t cols,              \
-                                  int64_t ct, uint32_t *status) {                                          \
+                                  int64_t ct, int64_t fanin, uint32_t *status) {                \
     extern __shared__ __align__(128) unsigned char nmb_smem[];                                 \
     nmb::red::reduce_cols_ws<R>(a, out, static_cast<R::Acc *>(partials), counters, rows,     \
-                                  cols, ct, status, nmb_smem);                                     \
+                                  cols, ct, fanin, status, nmb_smem);                          \
   }                                                                                            \
   NMB_REGISTER_KERNEL(nmb_reduce_cols_##op##_##ty, nmb::red::kSmemBytes);
 

@@ -26,7 +26,7 @@ namespace red {
 
 constexpr int kChunkBytes = 2048; // per-row piece of a wide-row tile
 constexpr int kRowsPerBlock = kWarps;
-constexpr int kColGroup = 8;      // row blocks merged per first-level ticket
+constexpr int kMaxFanIn = 32;      // upper bound of the merge tree's fan-in (a launch parameter)
 constexpr int kColVecs = 4;       // column vectors per thread
 
 // ----------------------------------------------------------- row reduction ---
@@ -243,7 +243,7 @@ template <typename R>
 __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict__ a,
                                                typename R::Out *__restrict__ out,
                                                typename R::Acc *partials, uint32_t *counters,
-                                               int64_t rows, int64_t cols, int64_t ct,
+                                               int64_t rows, int64_t cols, int64_t ct, int64_t fanin,
                                                uint32_t *status, unsigned char *smem_raw) {
   using T = typename R::In;
   using Acc = typename R::Acc;
@@ -304,17 +304,33 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
     const int64_t r0 = r_begin + i * rs;
     const int nr = (int)(r_end - r0 < rs ? r_end - r0 : rs);
     const T *tile = tiles + (int64_t)s * TILE;
-    for (int j = 0; j < nr; ++j) {
-      const int k = (int)(r0 - r_begin) + j; // row number within this CTA's range
-#pragma unroll
-      for (int m = 0; m < kColVecs; ++m) {
-        const int cv = tid + kThreads * m;
-        if (cv < nvec) {
-          const Vec<T, VEC> x =
-              *reinterpret_cast<const Vec<T, VEC> *>(tile + (int64_t)j * ncols + cv * VEC);
+    if (nvec <= kThreads) {
+      // slabs of up to 256 column vectors (the usual 4 KB slab): one vector per
+      // thread and row, nothing else in the loop
+      if (tid < nvec) {
+        const T *src = tile + tid * VEC;
+        int k = (int)(r0 - r_begin); // row number within this CTA's range
+#pragma unroll 4
+        for (int j = 0; j < nr; ++j, src += ncols, ++k) {
+          const Vec<T, VEC> x = *reinterpret_cast<const Vec<T, VEC> *>(src);
 #pragma unroll
           for (int l = 0; l < VEC; ++l)
-            R::fast_acc(f[m][l], x.v[l], k);
+            R::fast_acc(f[0][l], x.v[l], k);
+        }
+      }
+    } else {
+      for (int j = 0; j < nr; ++j) {
+        const int k = (int)(r0 - r_begin) + j;
+#pragma unroll
+        for (int m = 0; m < kColVecs; ++m) {
+          const int cv = tid + kThreads * m;
+          if (cv < nvec) {
+            const Vec<T, VEC> x =
+                *reinterpret_cast<const Vec<T, VEC> *>(tile + (int64_t)j * ncols + cv * VEC);
+#pragma unroll
+            for (int l = 0; l < VEC; ++l)
+              R::fast_acc(f[m][l], x.v[l], k);
+          }
         }
       }
     }
@@ -344,16 +360,18 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
     return;
   }
 
-  // Merge tree through scratch memory, fan-in kColGroup per level: the CTA that
+  // Merge tree through scratch memory, fan-in `fanin` per level (chosen by the
+  // host, which sizes the level buffers and the tickets with it): the CTA that
   // draws the last ticket of a group merges the group's rows (independent
   // loads, merged in row order, so the result does not depend on scheduling)
   // into one row of the next level and moves up; the last CTA of the top
   // level writes `out`.  Level buffers follow one another in `partials`
-  // ([Gy][cols], [ceil(Gy/8)][cols], ...); counters hold, per column tile, the
+  // ([Gy][cols], [ceil(Gy/fanin)][cols], ...); counters hold, per column tile, the
   // tickets of all groups of all levels, start at zero and are left at zero.
   int64_t tickets_per_tile = 0;
-  for (int64_t n = Gy; n > 1; n = (n + kColGroup - 1) / kColGroup)
-    tickets_per_tile += (n + kColGroup - 1) / kColGroup;
+  const int64_t F = fanin < 2 ? 2 : (fanin > kMaxFanIn ? kMaxFanIn : fanin);
+  for (int64_t n = Gy; n > 1; n = (n + F - 1) / F)
+    tickets_per_tile += (n + F - 1) / F;
   uint32_t *ticket = counters + (int64_t)blockIdx.x * tickets_per_tile;
   Acc *level = partials;
   int64_t n = Gy, idx = by;
@@ -368,9 +386,9 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
         level[idx * cols + c0 + cv * VEC + l] = widen(m, l);
   }
   while (true) {
-    const int64_t ngroups = (n + kColGroup - 1) / kColGroup;
-    const int64_t grp = idx / kColGroup, g_begin = grp * kColGroup;
-    const int g_size = (int)(n - g_begin < kColGroup ? n - g_begin : kColGroup);
+    const int64_t ngroups = (n + F - 1) / F;
+    const int64_t grp = idx / F, g_begin = grp * F;
+    const int g_size = (int)(n - g_begin < F ? n - g_begin : F);
     __threadfence();
     __syncthreads();
     if (tid == 0)
@@ -383,32 +401,42 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
       ticket[grp] = 0;
     Acc *next = level + n * cols;
     const bool top = ngroups == 1;
-    // kMergeBatch elements x kColGroup rows of independent loads are issued
-    // before the first merge/store, so a level costs a few memory round trips.
-    constexpr int kMergeBatch = sizeof(Acc) > 8 ? 1 : 4;
+    // kMergeBatch elements x kRowBatch rows of independent loads are issued
+    // before the first merge, so a level costs a few memory round trips; the
+    // batch sizes keep the loaded values in registers.
+    constexpr int kMergeBatch = sizeof(Acc) > 8 ? 1 : 2;
+    constexpr int kRowBatch = 8;
     for (int e0 = tid; e0 < ncols; e0 += kThreads * kMergeBatch) {
-      Acc part[kMergeBatch][kColGroup];
+      Acc m[kMergeBatch];
 #pragma unroll
-      for (int u = 0; u < kMergeBatch; ++u) {
-        const int e = e0 + u * kThreads;
+      for (int u = 0; u < kMergeBatch; ++u)
+        m[u] = R::identity();
+#pragma unroll 1
+      for (int y0 = 0; y0 < g_size; y0 += kRowBatch) {
+        Acc part[kMergeBatch][kRowBatch];
 #pragma unroll
-        for (int y = 0; y < kColGroup; ++y)
-          if (e < ncols && y < g_size)
-            part[u][y] = load_cg(level + (g_begin + y) * cols + c0 + e);
+        for (int u = 0; u < kMergeBatch; ++u) {
+          const int e = e0 + u * kThreads;
+#pragma unroll
+          for (int y = 0; y < kRowBatch; ++y)
+            if (e < ncols && y0 + y < g_size)
+              part[u][y] = load_cg(level + (g_begin + y0 + y) * cols + c0 + e);
+        }
+#pragma unroll
+        for (int u = 0; u < kMergeBatch; ++u)
+#pragma unroll
+          for (int y = 0; y < kRowBatch; ++y)
+            if (y0 + y < g_size)
+              m[u] = R::merge(m[u], part[u][y]); // row order: the result does not depend on scheduling
       }
 #pragma unroll
       for (int u = 0; u < kMergeBatch; ++u) {
         const int e = e0 + u * kThreads;
         if (e < ncols) {
-          Acc m = R::identity();
-#pragma unroll
-          for (int y = 0; y < kColGroup; ++y)
-            if (y < g_size)
-              m = R::merge(m, part[u][y]);
           if (top)
-            out[c0 + e] = R::fin(m);
+            out[c0 + e] = R::fin(m[u]);
           else
-            next[grp * cols + c0 + e] = m;
+            next[grp * cols + c0 + e] = m[u];
         }
       }
     }

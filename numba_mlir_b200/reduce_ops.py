@@ -19,6 +19,7 @@ OPS = ("sum", "prod", "min", "max", "argmin", "argmax")
 SMS = 148  # B200
 _CTAS = SMS * 3  # full reduction: three 65 KB CTAs fit one SM
 _TILE_BYTES = 16384
+_COL_FANIN = 16  # rows merged per ticket of the column merge tree (at most 32)
 _I64 = np.int64
 
 
@@ -110,18 +111,18 @@ def _launch_cols(q, a, out, op, ty, rows, cols):
     rows_per_stage = _TILE_BYTES // (tile_cols * it)
     row_blocks = max(1, min((_CTAS + col_tiles - 1) // col_tiles,
                             (rows + rows_per_stage - 1) // rows_per_stage, 65535))
-    # merge tree with fan-in 8: level buffers and tickets
+    # merge tree: level buffers and tickets for the fan-in handed to the kernel
     level_rows, tickets, n = 0, 0, row_blocks
     while n > 1:
         level_rows += n
-        n = (n + 7) // 8
+        n = (n + _COL_FANIN - 1) // _COL_FANIN
         tickets += n
     if col_tiles * tickets * 4 > q.COUNTER_BYTES:
         raise ValueError("too many column tiles for the counter region")
     counters, partials = q.scratch(max(level_rows, 1) * cols * _acc_bytes(op, a.dtype))
     q.launch(k, (col_tiles, row_blocks), (256,),
              [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
-              _I64(rows), _I64(cols), _I64(tile_cols), ("ptr", q.status_ptr)])
+              _I64(rows), _I64(cols), _I64(tile_cols), _I64(_COL_FANIN), ("ptr", q.status_ptr)])
 
 
 def _launch_all(q, a, out, op, ty):
