@@ -93,6 +93,17 @@ __device__ __forceinline__ void store_stream(T *p, const Vec<T, N> &r) {
   }
 }
 
+// i % m for a broadcast operand of m elements: a mask when m is a power of
+// two, a 32-bit remainder when both fit, the 64-bit remainder otherwise (the
+// branches are uniform over the grid).
+__device__ __forceinline__ int64_t wrap_index(int64_t i, int64_t m) {
+  if ((m & (m - 1)) == 0)
+    return i & (m - 1);
+  if (((uint64_t)i | (uint64_t)m) >> 32 == 0)
+    return (int64_t)((uint32_t)i % (uint32_t)m);
+  return i % m;
+}
+
 // ------------------------------------------------- fused elementwise loop ---
 // A Chain describes one fused ufunc chain over a flat, C-contiguous output
 // index space of n elements:

@@ -958,7 +958,8 @@ def _generate(em, results, out_shape, vec, unroll, ostrides):
             members.append(f"int64_t m{i};")
             kparams.append(f"int64_t m{i}")
             ctor.append(f"m{i}")
-            loads.append(f"r.in{i} = nmb::load_reuse<{ct}, V>(in{i} + (i % m{i}));")
+            # i % m without a 64-bit division when m is a power of two or the index fits 32 bits
+            loads.append(f"r.in{i} = nmb::load_reuse<{ct}, V>(in{i} + nmb::wrap_index(i, m{i}));")
         elif kind == "col":
             members.append(f"int64_t m{i};")
             kparams.append(f"int64_t m{i}")
