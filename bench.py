@@ -53,10 +53,10 @@ def measured_peaks():
 NCU_TRAFFIC_BYTES = {
     "black_scholes": 201363968 + 91807744,   # output partly still dirty in L2 at kernel end
     "bcast_add": 16794112 + 0,               # two-launch capture: the result stays in L2
-    "sum_axis1": 268465152 + 4111360,
-    "min_axis0": 268462592 + 3502848,
-    "argmin_axis1": 268475392 + 3548416,
-    "int_sum": 1073784576 + 4129280,
+    "sum_axis1": 268460800 + 3494144,
+    "min_axis0": 268463104 + 3504640,
+    "argmin_axis1": 268470272 + 3379456,
+    "int_sum": 1073763328 + 3475968,
     "pairwise": 27649280 + 1015031552,       # nmb_contract_tf32x3 (prepass: 8409856 + 0)
     "kmeans": 268464128 + 15941376,
 }
