@@ -9,8 +9,7 @@ goes through the C-ABI; nothing here computes on the host.
 
 import numpy as np
 
-from . import runtime as _rt
-from .device_array import DeviceArray, empty
+from .device_array import empty
 
 _I64 = np.int64
 

@@ -11,7 +11,7 @@ import ctypes
 import numpy as np
 
 from . import runtime as _rt
-from .device_array import DeviceArray, empty
+from .device_array import empty
 
 
 def _memref(a):

@@ -14,8 +14,7 @@ import numpy as np
 from numba.core import types
 from numba.core.typing.templates import AbstractTemplate, ConcreteTemplate, infer_global, signature
 
-from . import runtime as _rt
-from .device_array import DeviceArray, as_device_array
+from .device_array import DeviceArray
 
 
 def _stub_error():

@@ -22,13 +22,11 @@ context in which the reference caches queue/module/kernel handles
 (numba_mlir/mlir_compiler/lib/pipelines/LowerToGpu.cpp:742-940).
 """
 
-import math
 import struct
 import threading
 
 import numpy as np
 
-from . import runtime as _rt
 from .device_array import DeviceArray, empty
 
 # ----------------------------------------------------------------- dtypes ---

@@ -10,8 +10,7 @@ work-group partials in a host loop, mlir/lib/Conversion/GpuToGpuRuntime.cpp:2232
 
 import numpy as np
 
-from . import runtime as _rt
-from .device_array import DeviceArray, empty
+from .device_array import empty
 
 _TY = {np.dtype(np.float32): "f32", np.dtype(np.float64): "f64",
        np.dtype(np.int32): "i32", np.dtype(np.int64): "i64"}

@@ -8,8 +8,7 @@ import math
 import numpy as np
 
 from .decorators import njit, vectorize
-from .kernel import (atomic, barrier, get_global_id, get_group_id, get_local_id, get_local_size,
-                     kernel, local, private)
+from .kernel import atomic, barrier, get_group_id, get_local_id, get_local_size, kernel, local, private
 
 
 @vectorize(nopython=True)
