@@ -149,6 +149,14 @@ void *gpuxRecordEvent(void *queue);
  * one on.  No counterpart in the reference, whose host code waits on every
  * event (GpuRuntimeToLlvm.cpp:619-622). */
 int gpuxQueueWaitEvents(void *queue, void *events);
+/* Orders everything submitted to the queue from now on after the work already
+ * submitted to another CUDA stream of the same device (cudaStream_t; NULL, 1
+ * and 2 name the default streams as in the CUDA array interface).  This is how
+ * an array imported from another library is consumed on the producer's terms:
+ * version 3 of __cuda_array_interface__ carries the stream the data is ready
+ * on.  Returns 0 on success.  No counterpart in the reference, where dpctl
+ * owns the queues of imported arrays. */
+int gpuxQueueWaitStream(void *queue, void *nativeStream);
 /* Milliseconds between two completed events of the same device. */
 float gpuxEventElapsedMs(void *startEvent, void *endEvent);
 /* Blocks until everything submitted to the queue has finished. */

@@ -1076,6 +1076,31 @@ GPUX_EXPORT int gpuxQueueWaitEvents(void *queue, void *events) {
   return setDevice(q) && waitDeps(q, events) ? 0 : 1;
 }
 
+GPUX_EXPORT int gpuxQueueWaitStream(void *queue, void *nativeStream) {
+  LOG_FUNC();
+  if (!queue) {
+    nmb::setError("gpuxQueueWaitStream: null queue");
+    return 1;
+  }
+  Queue *q = toQueue(queue);
+  cudaStream_t other = static_cast<cudaStream_t>(nativeStream);
+  if (other == q->stream)
+    return 0;
+  if (!setDevice(q))
+    return 1;
+  Event *e = q->getEvent();
+  if (!e) {
+    nmb::setError("failed to create a CUDA event");
+    return 1;
+  }
+  bool ok = true;
+  CUDA_TRY(cudaEventRecord(e->ev, other), ok = false);
+  if (ok)
+    CUDA_TRY(cudaStreamWaitEvent(q->stream, e->ev, 0), ok = false);
+  q->returnEvent(e);
+  return ok ? 0 : 1;
+}
+
 GPUX_EXPORT void *gpuxRecordEvent(void *queue) {
   LOG_FUNC();
   if (!queue) {

@@ -290,11 +290,15 @@ def from_host(host, queue=None, usm_type="device", wait=True):
 
 def as_device_array(obj, queue=None):
     """Zero-copy view of any exporter of __cuda_array_interface__ (torch, cupy,
-    numba.cuda ...)."""
+    numba.cuda ...).  When the exporter names the stream its data is ready on
+    (version 3 of the interface), the queue is ordered after that stream."""
     if isinstance(obj, DeviceArray):
         return obj
     iface = obj.__cuda_array_interface__
     queue = queue or _rt.get_queue()
+    stream = iface.get("stream")
+    if stream is not None and int(stream) != int(queue.stream or 0):
+        queue.wait_stream(stream)
     dtype = np.dtype(iface["typestr"])
     shape = tuple(iface["shape"])
     ptr = iface["data"][0] or 0

@@ -76,6 +76,7 @@ SIGNATURES = {
     "gpuxMemset": (_vp, [_vp, _vp, _i, _sz, _vp]),
     "gpuxRecordEvent": (_vp, [_vp]),
     "gpuxQueueWaitEvents": (_i, [_vp, _vp]),
+    "gpuxQueueWaitStream": (_i, [_vp, _vp]),
     "gpuxEventElapsedMs": (ctypes.c_float, [_vp, _vp]),
     "gpuxQueueSynchronize": (None, [_vp]),
     "gpuxQueueGetStream": (_vp, [_vp]),
@@ -438,6 +439,14 @@ class Queue:
         if events and self.lib.gpuxQueueWaitEvents(self.handle, _event_list(events)):
             check()
             raise GpuRuntimeError("gpuxQueueWaitEvents failed")
+
+    def wait_stream(self, stream):
+        """Later submissions to this queue run after the work already submitted
+        to the CUDA stream `stream` (an integer handle; 1 and 2 are the legacy
+        and per-thread default streams)."""
+        if self.lib.gpuxQueueWaitStream(self.handle, ctypes.c_void_p(int(stream))):
+            check()
+            raise GpuRuntimeError("gpuxQueueWaitStream failed")
 
     def memset(self, dst, value, nbytes):
         ev = self.lib.gpuxMemset(self.handle, dst, int(value), int(nbytes), None)

@@ -137,3 +137,45 @@ def test_cuda_array_interface_interop_with_torch(queue):
     queue.synchronize()
     torch.cuda.synchronize()
     assert np.array_equal(back.copy_to_host(), host * 2)
+
+
+class _StreamedExport:
+    """Exporter of version 3 of the CUDA array interface: names the stream the
+    data is ready on, as cupy and numba.cuda do."""
+
+    def __init__(self, tensor, stream):
+        self._tensor = tensor
+        iface = dict(tensor.__cuda_array_interface__)
+        iface["version"] = 3
+        iface["stream"] = stream
+        self.__cuda_array_interface__ = iface
+
+
+def test_import_orders_queue_after_producer_stream(queue):
+    import torch
+
+    import numba_mlir_b200 as nm
+
+    n = 1 << 24
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        t = torch.zeros(n, dtype=torch.float32, device="cuda")
+        for k in range(1, 41):  # enough queued work that a missing dependency shows
+            t.add_(float(k) - float(k - 1))
+    d = nm.as_device_array(_StreamedExport(t, side.cuda_stream))
+
+    @nm.njit(parallel=True)
+    def twice(x):
+        return x + x
+
+    got = twice(d).copy_to_host()
+    side.synchronize()
+    assert got.min() == 80.0 and got.max() == 80.0
+
+
+def test_wait_stream_accepts_default_stream_names(queue):
+    # 1 and 2 name the legacy and the per-thread default streams
+    queue.wait_stream(1)
+    queue.wait_stream(2)
+    queue.wait_stream(queue.stream or 0)
+    queue.synchronize()
