@@ -128,6 +128,27 @@ class BlackScholes(Workload):
         assert np.isfinite(call).all()
 
 
+class BlackScholesFastmath(BlackScholes):
+    """The same chain compiled with fastmath=True, the flags of the
+    reference's benchmark driver (numba_mlir/mlir/benchmarking.py:43).  A
+    secondary line: the headline keeps the default (IEEE division and sqrt)."""
+
+    name = "black_scholes_f32_n2^24_fastmath"
+    key = "black_scholes_fastmath"
+
+    def step_device(self):
+        from numba_mlir_b200 import workloads
+
+        workloads.black_scholes_fastmath(*self.d_in, self.rate, self.vol, *self.d_out)
+
+    def step_e2e(self):
+        import numba_mlir_b200 as nm
+        from numba_mlir_b200 import workloads
+
+        nm.map_host(workloads.black_scholes_fastmath, self.h_in, self.h_out,
+                    scalars=(self.rate, self.vol), queue=self.queue)
+
+
 class BroadcastAdd(Workload):
     """a (2048, 2048) + b (1, 2048), float32; 33.6 MB per call fits L2, so the
     step rotates over 10 operand/result sets (336 MB)."""
@@ -289,6 +310,7 @@ class KMeans(Workload):
 
 WORKLOADS = {
     "black_scholes": BlackScholes,
+    "black_scholes_fastmath": BlackScholesFastmath,
     "bcast_add": BroadcastAdd,
     "sum_axis1": lambda: AxisReduction("sum_axis1"),
     "min_axis0": lambda: AxisReduction("min_axis0"),
@@ -392,7 +414,7 @@ def cpu_case(key, scale):
     its leading dimension: (step function, algorithmic bytes, units, name)."""
     from oracle import configs as O
 
-    if key == "black_scholes":
+    if key in ("black_scholes", "black_scholes_fastmath"):  # one CPU form for both
         price, strike, t, rate, vol = O.make_inputs("black_scholes", scale)
         call, put = np.zeros_like(price), np.zeros_like(price)
         return (lambda: O.black_scholes(price, strike, t, rate, vol, call, put),
@@ -612,7 +634,7 @@ def run_gpu(args):
     if world == 1 and not args.no_extra and args.workload == "black_scholes":
         peak, _ = measured_peaks()
         del w.d_in, w.d_out
-        for key in ("bcast_add", "sum_axis1", "min_axis0", "argmin_axis1", "int_sum", "pairwise",
+        for key in ("black_scholes_fastmath", "bcast_add", "sum_axis1", "min_axis0", "argmin_axis1", "int_sum", "pairwise",
                     "kmeans"):
             ow = WORKLOADS[key]()
             ow.setup_device(queue, seed=0)

@@ -974,7 +974,7 @@ def compile_kernel(py_func, args, ndim, fastmath=False):
             kparams.append(f"{c_scalar_type(t)} p{i}")
             layout.append(("scalar", np.dtype(str(t))))
     kparams += ["int64_t nmb_g0", "int64_t nmb_g1", "int64_t nmb_g2"]
-    opts = "" if fastmath else " --fmad=false"
+    opts = "\n#define NMB_FASTMATH 1" if fastmath else " --fmad=false"
     group_prologue = ""
     if tr.uses_group_reduce:
         # group reductions need to know which work-items of the group exist
@@ -1315,7 +1315,7 @@ def compile_parfor(py_func, args, fastmath=False):
             layout.append(("scalar", np.dtype(str(t))))
     if needs_epilogue:
         kparams += ["unsigned char* nmb_partials", "unsigned int* nmb_ticket", "void* nmb_ret"]
-    opts = "" if fastmath else " --fmad=false"
+    opts = "\n#define NMB_FASTMATH 1" if fastmath else " --fmad=false"
     src = f"""//NMB200:CUDA-SOURCE
 //NMB200:OPTIONS{opts}
 #include "nmb_device.cuh"

@@ -248,7 +248,25 @@ __device__ __forceinline__ T group_reduce(T v, Op op, T neutral, T *scratch, voi
 // library versions, never the -use_fast_math intrinsics; erf is this file's own.
 __device__ __forceinline__ float f_log(float x) { return logf(x); }
 __device__ __forceinline__ float f_exp(float x) { return expf(x); }
+#ifdef NMB_FASTMATH
+// fastmath=True: the approximate instructions (sqrt.approx and rsqrt.approx:
+// 1 ulp; div.full: 2 ulp over the whole range), the counterpart of the fast
+// floating-point mode the reference sets on its device code for that flag
+// (mlir/tests/test_gpu.py:1900-1934).
+__device__ __forceinline__ float f_sqrt(float x) {
+  float r;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float f_rsqrt(float x) {
+  float r;
+  asm("rsqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+#else
 __device__ __forceinline__ float f_sqrt(float x) { return __fsqrt_rn(x); }
+__device__ __forceinline__ float f_rsqrt(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
+#endif
 // erf in float32, branch free (both ranges are evaluated and one is selected, so
 // a warp whose lanes straddle the ranges pays nothing extra):
 //   |x| <  1: erf(x) = x + x * p(x^2), p a degree-6 polynomial for erf(x)/x - 1;
@@ -285,7 +303,15 @@ __device__ __forceinline__ float f_erf(float x) {
   const float large = copysignf(1.0f - e, x);
   return t < 1.0f ? small : large;
 }
+#ifdef NMB_FASTMATH
+__device__ __forceinline__ float f_div(float a, float b) {
+  float r;
+  asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+#else
 __device__ __forceinline__ float f_div(float a, float b) { return __fdiv_rn(a, b); }
+#endif
 __device__ __forceinline__ double f_log(double x) { return log(x); }
 __device__ __forceinline__ double f_exp(double x) { return exp(x); }
 __device__ __forceinline__ double f_sqrt(double x) { return __dsqrt_rn(x); }

@@ -114,7 +114,8 @@ class Dispatcher:
         if plan is not None:
             return plan.replay(args)
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
-        result, plan = lazy.trace_call(self.py_func, args, queue)
+        result, plan = lazy.trace_call(self.py_func, args, queue,
+                                        fastmath=bool(self.options.get("fastmath", False)))
         if plan is not None and key is not None:
             self._plans[key] = plan
         return result
@@ -157,7 +158,8 @@ class Dispatcher:
     def trace_dry(self, *args):
         """Records the plan and generates the kernels without a device (used
         by host-side tests of the code generator)."""
-        return lazy.trace_call(self.py_func, args, None, dry=True)
+        return lazy.trace_call(self.py_func, args, None, dry=True,
+                               fastmath=bool(self.options.get("fastmath", False)))
 
 
 def jit(signature_or_function=None, locals={}, cache=False, pipeline_class=None,

@@ -177,6 +177,9 @@ _UFUNC_BY_OBJ[np.rad2deg] = "degrees"
 _UFUNC_BY_OBJ[np.deg2rad] = "radians"
 _UFUNC_BY_OBJ[np.bitwise_not] = "invert"
 
+# 1/sqrt(x) under fastmath (never produced by NumPy dispatch)
+UFUNCS["rsqrt"] = (None, _flt("nmb::f_rsqrt({0})", "(1.0 / sqrt({0}))"))
+
 REDUCTIONS = {np.sum: "sum", np.prod: "prod", np.min: "min", np.max: "max", np.amin: "min",
               np.amax: "max", np.argmin: "argmin", np.argmax: "argmax"}
 
@@ -220,9 +223,10 @@ class DeviceFunc:
 class Trace:
     """State of one traced call: slot table, pending stores, recorded steps."""
 
-    def __init__(self, queue, args=None, dry=False):
+    def __init__(self, queue, args=None, dry=False, fastmath=False):
         self.queue = queue
         self.dry = dry  # record and generate code only (no device)
+        self.fastmath = fastmath  # relaxed division/sqrt and a*b+c contraction
         self.slots = []          # slot -> ("arg", index, views) | ("tmp", shape, dtype, views)
         self.arrays = []         # slot -> DeviceArray (this call's binding)
         self.pending = []        # [(target LazyArray leaf, value Node)]
@@ -594,6 +598,12 @@ def _retarget_producer(trace, target, value):
     return True
 
 
+def _is_one(node):
+    while node.kind == "cast":
+        node = node.inputs[0]
+    return node.kind == "const" and node.value == 1
+
+
 def apply_ufunc(trace, name, inputs):
     nodes = [_as_node(trace, x) for x in inputs]
     ufunc, _emit = UFUNCS[name]
@@ -601,6 +611,9 @@ def apply_ufunc(trace, name, inputs):
     cast = [n if n.dtype == d else Node("cast", d, n.shape, (n,)) for n, d in zip(nodes, loop_in)]
     shape = broadcast_shapes(*[n.shape for n in nodes])
     node = Node("op", out_dt, shape, cast, op=name)
+    if trace.fastmath and name == "true_divide" and _is_one(cast[0]) and cast[1].kind == "op" \
+            and cast[1].op == "sqrt" and out_dt == np.float32 and cast[1].shape == shape:
+        node = Node("op", out_dt, shape, cast[1].inputs, op="rsqrt")  # 1/sqrt(x): one instruction
     concrete = None
     if shape == () and all(isinstance(x, LazyArray) and x.concrete is not None or
                            not isinstance(x, (LazyArray, DeviceArray)) for x in inputs):
@@ -913,10 +926,11 @@ def _emit_eltwise(trace, out_shape, outs):
     shaped = any(k == "strided" for _s, k, _p, _d in em.leaves) or any(st is not None for st in ostrides)
     sig = (tuple(out_shape) if shaped else len(out_shape),
            tuple((k, p if k == "strided" else (), d.name) for _s, k, p, d in em.leaves),
-           tuple(em.sig), tuple((e, a.dtype.name, st) for (_s, e, a), st in zip(results, ostrides)), vec, unroll)
+           tuple(em.sig), tuple((e, a.dtype.name, st) for (_s, e, a), st in zip(results, ostrides)), vec, unroll,
+           trace.fastmath)
     hit = _kernel_cache.get(sig)
     if hit is None:
-        hit = _generate(em, results, out_shape, vec, unroll, ostrides)
+        hit = _generate(em, results, out_shape, vec, unroll, ostrides, trace.fastmath)
         _kernel_cache[sig] = hit
     blob, kname = hit
 
@@ -937,7 +951,7 @@ def _emit_eltwise(trace, out_shape, outs):
         run_launch(trace.queue, step, trace.arrays, trace.args)
 
 
-def _generate(em, results, out_shape, vec, unroll, ostrides):
+def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False):
     """CUDA C for one fused chain; returns (tagged source blob, kernel name)."""
     members, ctor, kparams = [], [], []
     in_fields, loads = [], []
@@ -995,8 +1009,11 @@ def _generate(em, results, out_shape, vec, unroll, ostrides):
     kparams.append("int64_t n")
     nl = "\n      "
     funcs = "\n".join(em.funcs.values())
+    # fastmath: a*b+c may contract and division/sqrt take the approximate
+    # instructions (<= 2 ulp), as the reference's fast SPIR-V mode allows
+    head = "//NMB200:OPTIONS\n#define NMB_FASTMATH 1" if fastmath else "//NMB200:OPTIONS --fmad=false"
     src = f"""//NMB200:CUDA-SOURCE
-//NMB200:OPTIONS --fmad=false
+{head}
 #include "nmb_device.cuh"
 {funcs}
 struct Chain {{
@@ -1142,10 +1159,10 @@ def fake_array(shape, dtype, ptr=0x7F0000000000):
     return DeviceArray(_Foreign(None, ptr, n * dtype.itemsize, None), shape, dtype)
 
 
-def trace_call(func, args, queue, dry=False):
+def trace_call(func, args, queue, dry=False, fastmath=False):
     """Runs `func` on symbolic arguments, executing the device work as it is
     recorded (unless `dry`).  Returns (result, plan or None)."""
-    trace = Trace(queue, args, dry=dry)
+    trace = Trace(queue, args, dry=dry, fastmath=fastmath)
     with _TraceScope(trace):
         sym = []
         for i, a in enumerate(args):

@@ -48,6 +48,12 @@ def black_scholes(price, strike, t, rate, volatility, call, put):
     put[:] = r - P + Se
 
 
+# The same chain under fastmath=True, the flags the reference's benchmark driver
+# compiles every kernel with (numba_mlir/mlir/benchmarking.py:43): division and
+# square root take the approximate instructions and a*b+c contracts.
+black_scholes_fastmath = njit(parallel=True, fastmath=True)(black_scholes.py_func)
+
+
 # The result is written into an argument (as the reference's offload tests do,
 # mlir/tests/test_gpu.py:1538-1551), so a call allocates nothing.
 @njit(parallel=True)

@@ -58,3 +58,25 @@ def test_black_scholes_chain_is_one_kernel(runtime_lib):
     launches = [s for s in trace.steps if s[0] == "launch"]
     assert len(launches) == 1 and plan is not None
     assert len(runtime.compile_to_cubin(launches[0][1])) > 0
+
+
+def test_fastmath_selects_the_approximate_division_and_sqrt(runtime_lib):
+    """fastmath=True compiles without --fmad=false, with the approximate
+    division and square root, and folds 1/sqrt(x) into one rsqrt
+    (numba_mlir/mlir/tests/test_gpu.py:1900-1934 checks the flag reaches the
+    device code); the default keeps the IEEE forms."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import lazy, runtime
+
+    def f(a, b):
+        return a / b + np.float32(1.0) / np.sqrt(a)
+
+    args = [lazy.fake_array((64,), np.float32), lazy.fake_array((64,), np.float32)]
+    for fast in (False, True):
+        trace, _plan = nm.njit(f, fastmath=fast).trace_dry(*args)
+        (step,) = [s for s in trace.steps if s[0] == "launch"]
+        src = bytes(step[1]).decode()
+        assert ("#define NMB_FASTMATH 1" in src) == fast
+        assert ("--fmad=false" in src) != fast
+        assert ("nmb::f_rsqrt" in src) == fast
+        assert len(runtime.compile_to_cubin(step[1])) > 0

@@ -94,6 +94,65 @@ def test_config2_black_scholes_fuses_into_one_kernel(queue, n):
     assert len(bs._plans) == 1
 
 
+def _ulps(got, want64):
+    want = want64.astype(np.float32)
+    return np.abs(got.astype(np.float64) - want64) / np.spacing(np.abs(want)).astype(np.float64)
+
+
+def test_fastmath_division_and_sqrt_stay_within_two_ulp(queue):
+    """fastmath=True (numba_mlir/mlir/tests/test_gpu.py:981-1010,1900-1934):
+    division, sqrt and 1/sqrt take the approximate instructions, whose error
+    stays within 2 ulp of the exact float32 result; the default is bit-exact."""
+    import numba_mlir_b200 as nm
+
+    def f(a, b):
+        return a / b, np.sqrt(a), np.float32(1.0) / np.sqrt(a)
+
+    rng = np.random.default_rng(11)
+    a = np.exp(rng.uniform(-60, 60, 1 << 18)).astype(np.float32)
+    b = (np.exp(rng.uniform(-40, 40, 1 << 18)) * rng.choice([-1.0, 1.0], 1 << 18)).astype(np.float32)
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    truth = (a64 / b64, np.sqrt(a64), 1.0 / np.sqrt(a64))
+    exact = nm.njit(f)(_dev(a), _dev(b))
+    with np.errstate(over="ignore"):
+        want = (a / b, np.sqrt(a), np.float32(1.0) / np.sqrt(a))
+    for got, w in zip(exact, want):
+        assert np.array_equal(got.copy_to_host(), w)
+    fast = nm.njit(f, fastmath=True)(_dev(a), _dev(b))
+    for got, t in zip(fast, truth):
+        g = got.copy_to_host()
+        with np.errstate(over="ignore"):
+            ok = np.isfinite(t.astype(np.float32)) & (np.abs(t) > 1e-37)
+        assert _ulps(g[ok], t[ok]).max() <= 2.0
+
+
+@pytest.mark.parametrize("n", [524288, 1000003])
+def test_black_scholes_fastmath_matches_oracle(queue, n):
+    """The benchmark-driver flags (numba_mlir/mlir/benchmarking.py:43) on the
+    chain of mlir/tests/test_numpy.py:2827-2852: one kernel, same tolerance
+    against the oracle as the default build and well inside the reference's
+    own atol of 1e-3 (test_numpy.py:2861-2862)."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import runtime, workloads
+    from oracle import configs as O
+
+    price, strike, t, rate, vol = O.make_inputs("black_scholes", n / 2**24, seed=777777)
+    price, strike, t = price[:n], strike[:n], t[:n]
+    call, put = nm.empty(n), nm.empty(n)
+    args = (_dev(price), _dev(strike), _dev(t), rate, vol, call, put)
+    workloads.black_scholes_fastmath(*args)
+    before = runtime.launch_count()
+    workloads.black_scholes_fastmath(*args)
+    assert runtime.launch_count() - before == 1
+    ocall, oput = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    O.black_scholes(price, strike, t, rate, vol, ocall, oput)
+    np.testing.assert_allclose(call.copy_to_host(), ocall, rtol=1e-5, atol=2e-5)
+    np.testing.assert_allclose(put.copy_to_host(), oput, rtol=1e-5, atol=2e-5)
+    c64, p64 = O.black_scholes_f64(price, strike, t, rate, vol)
+    for got, orc, truth in ((call.copy_to_host(), ocall, c64), (put.copy_to_host(), oput, p64)):
+        assert np.abs(got - truth).max() <= 2 * np.abs(orc - truth).max() + 1e-6
+
+
 def test_config3_reductions_through_njit(queue):
     import numba_mlir_b200 as nm
     from oracle import configs as O
