@@ -54,7 +54,7 @@ NCU_TRAFFIC_BYTES = {
     "black_scholes": 201363968 + 91807744,   # output partly still dirty in L2 at kernel end
     "bcast_add": 16794112 + 0,               # two-launch capture: the result stays in L2
     "sum_axis1": 268460800 + 3494144,
-    "min_axis0": 268463104 + 3504640,
+    "min_axis0": 268477184 + 3869184,
     "argmin_axis1": 268470272 + 3379456,
     "int_sum": 1073763328 + 3475968,
     "pairwise": 27649280 + 1015031552,       # nmb_contract_tf32x3 (prepass: 8409856 + 0)

@@ -48,6 +48,48 @@ template <> struct Limits<int64_t> {
   static __device__ __forceinline__ int64_t highest() { return 0x7fffffffffffffffll; }
 };
 
+// Atomic minimum and maximum in global memory.  Floats go through their bit
+// patterns: values with a clear sign bit order like signed integers, values with
+// the sign bit set in reverse like unsigned integers, and every pattern of the
+// second kind is below every pattern of the first, so one integer atomic per
+// call keeps the order (-0.0 counts as below +0.0).  NaNs must not be passed.
+__device__ __forceinline__ void atomic_min(int32_t *p, int32_t v) { atomicMin(p, v); }
+__device__ __forceinline__ void atomic_max(int32_t *p, int32_t v) { atomicMax(p, v); }
+__device__ __forceinline__ void atomic_min(int64_t *p, int64_t v) {
+  atomicMin(reinterpret_cast<long long *>(p), (long long)v);
+}
+__device__ __forceinline__ void atomic_max(int64_t *p, int64_t v) {
+  atomicMax(reinterpret_cast<long long *>(p), (long long)v);
+}
+__device__ __forceinline__ void atomic_min(float *p, float v) {
+  const int b = __float_as_int(v);
+  if (b >= 0)
+    atomicMin(reinterpret_cast<int *>(p), b);
+  else
+    atomicMax(reinterpret_cast<unsigned int *>(p), (unsigned int)b);
+}
+__device__ __forceinline__ void atomic_max(float *p, float v) {
+  const int b = __float_as_int(v);
+  if (b >= 0)
+    atomicMax(reinterpret_cast<int *>(p), b);
+  else
+    atomicMin(reinterpret_cast<unsigned int *>(p), (unsigned int)b);
+}
+__device__ __forceinline__ void atomic_min(double *p, double v) {
+  const long long b = __double_as_longlong(v);
+  if (b >= 0)
+    atomicMin(reinterpret_cast<long long *>(p), b);
+  else
+    atomicMax(reinterpret_cast<unsigned long long *>(p), (unsigned long long)b);
+}
+__device__ __forceinline__ void atomic_max(double *p, double v) {
+  const long long b = __double_as_longlong(v);
+  if (b >= 0)
+    atomicMax(reinterpret_cast<long long *>(p), b);
+  else
+    atomicMin(reinterpret_cast<unsigned long long *>(p), (unsigned long long)b);
+}
+
 template <typename T> struct WideAcc { using type = T; };
 template <> struct WideAcc<int32_t> { using type = int64_t; };
 
@@ -64,6 +106,7 @@ template <typename T> struct SumR {
   // index order; only index-carrying reducers need it.
   using Fast = Acc;
   static constexpr bool kTwoPass = false;
+  static constexpr bool kAtomicCols = false;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
   template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
@@ -81,6 +124,7 @@ template <typename T> struct ProdR {
   // index order; only index-carrying reducers need it.
   using Fast = Acc;
   static constexpr bool kTwoPass = false;
+  static constexpr bool kAtomicCols = false;
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
   template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
@@ -98,6 +142,10 @@ template <typename T> struct MinR {
   // index order; only index-carrying reducers need it.
   using Fast = Acc;
   static constexpr bool kTwoPass = false;
+  // Column reductions of different row blocks meet in `out` through atomics
+  // (any order gives the same value) instead of a merge tree.
+  static constexpr bool kAtomicCols = true;
+  static __device__ __forceinline__ void atomic_merge(Out *p, Acc v) { atomic_min(p, v); }
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
   template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
@@ -115,6 +163,10 @@ template <typename T> struct MaxR {
   // index order; only index-carrying reducers need it.
   using Fast = Acc;
   static constexpr bool kTwoPass = false;
+  // Column reductions of different row blocks meet in `out` through atomics
+  // (any order gives the same value) instead of a merge tree.
+  static constexpr bool kAtomicCols = true;
+  static __device__ __forceinline__ void atomic_merge(Out *p, Acc v) { atomic_max(p, v); }
   static __device__ __forceinline__ Fast fast_identity() { return identity(); }
   static __device__ __forceinline__ void fast_acc(Fast &a, T x, int) { acc(a, x, 0); }
   template <typename F> static __device__ __forceinline__ Acc widen_fn(Fast f, F) { return f; }
@@ -156,6 +208,7 @@ template <typename T, bool MIN> struct ArgR {
   // running value (rare after the first batches) a scan for the first value
   // equal to the batch extreme.
   static constexpr bool kTwoPass = true;
+  static constexpr bool kAtomicCols = false;
   static __device__ __forceinline__ T pick(T a, T b) {
     if constexpr (std::is_same<T, float>::value) {
       return MIN ? fminf(a, b) : fmaxf(a, b); // NaNs lose, as they do against `<`

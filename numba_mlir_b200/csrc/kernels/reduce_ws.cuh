@@ -265,6 +265,30 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
   const int64_t nsteps = (r_end - r_begin + rs - 1) / rs;
   const int nvec = ncols / VEC;
 
+  // Scratch counters of this column tile: one word per group of every level of
+  // the merge tree (the host sizes the region with the same loop).
+  int64_t tickets_per_tile = 0;
+  const int64_t F = fanin < 2 ? 2 : (fanin > kMaxFanIn ? kMaxFanIn : fanin);
+  for (int64_t n = Gy; n > 1; n = (n + F - 1) / F)
+    tickets_per_tile += (n + F - 1) / F;
+  uint32_t *ticket = counters + (int64_t)blockIdx.x * tickets_per_tile;
+
+  // Order-independent reducers (min, max) skip the tree: the first row block
+  // stores the identity into `out` before it starts streaming and raises the top
+  // bit of the tile's first counter; every row block ends with one atomic per
+  // column, and the last one to arrive clears the counter again.
+  constexpr uint32_t kOutReady = 0x80000000u;
+  if constexpr (R::kAtomicCols) {
+    if (Gy > 1 && by == 0) {
+      for (int e = tid; e < ncols; e += kThreads)
+        out[c0 + e] = R::fin(R::identity());
+      __threadfence();
+      __syncthreads();
+      if (tid == 0)
+        atomicOr(ticket, kOutReady);
+    }
+  }
+
   auto issue = [&](int64_t i) {
     const int s = (int)(i % kStages);
     const int64_t r0 = r_begin + i * rs;
@@ -360,6 +384,43 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
     return;
   }
 
+  if constexpr (R::kAtomicCols) {
+    __shared__ bool out_ready;
+    if (tid == 0) {
+      // bounded: the first row block is resident from the start of the grid
+      bool ok = false;
+      for (int spin = 0; spin < (1 << 22) && !ok; ++spin) {
+        uint32_t w;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(w) : "l"(ticket) : "memory");
+        ok = (w & kOutReady) != 0;
+        if (!ok)
+          __nanosleep(64);
+      }
+      if (!ok)
+        atomicExch(status, (uint32_t)kStatusWaitTimeout);
+      out_ready = ok;
+    }
+    __syncthreads();
+    if (out_ready) {
+#pragma unroll
+      for (int m = 0; m < kColVecs; ++m) {
+        const int cv = tid + kThreads * m;
+        if (cv < nvec)
+#pragma unroll
+          for (int l = 0; l < VEC; ++l)
+            R::atomic_merge(out + c0 + cv * VEC + l, widen(m, l));
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t arrived = atomicAdd(ticket, 1u) & ~kOutReady;
+      if (arrived == (uint32_t)(Gy - 1))
+        atomicExch(ticket, 0u); // everyone has read the flag and added its ticket
+    }
+    return;
+  }
+
   // Merge tree through scratch memory, fan-in `fanin` per level (chosen by the
   // host, which sizes the level buffers and the tickets with it): the CTA that
   // draws the last ticket of a group merges the group's rows (independent
@@ -368,11 +429,6 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
   // level writes `out`.  Level buffers follow one another in `partials`
   // ([Gy][cols], [ceil(Gy/fanin)][cols], ...); counters hold, per column tile, the
   // tickets of all groups of all levels, start at zero and are left at zero.
-  int64_t tickets_per_tile = 0;
-  const int64_t F = fanin < 2 ? 2 : (fanin > kMaxFanIn ? kMaxFanIn : fanin);
-  for (int64_t n = Gy; n > 1; n = (n + F - 1) / F)
-    tickets_per_tile += (n + F - 1) / F;
-  uint32_t *ticket = counters + (int64_t)blockIdx.x * tickets_per_tile;
   Acc *level = partials;
   int64_t n = Gy, idx = by;
   __shared__ bool last;

@@ -5,6 +5,7 @@ ill-posed for sums that cancel to ~0) and float min/max are bit-exact."""
 
 import itertools
 import math
+import warnings
 
 import numpy as np
 import pytest
@@ -157,6 +158,49 @@ def test_argmin_argmax_special_values_and_dense_ties(queue, cols):
         b[17] = 1.0                                            # neither the minimum nor the maximum of the row
         want[6] = fn(b)
         np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64, np.int32, np.int64])
+@pytest.mark.parametrize("cols", [1024, 4096, 5000])
+def test_column_min_max_across_row_blocks(queue, dtype, cols):
+    """min/max over axis 0 with enough rows that many row blocks meet in the
+    result: columns of one sign and of mixed signs, infinities, signed zeros,
+    NaNs (ignored: they never win `x < m`, numba_mlir/mlir/builtin/funcs.py:140-160,
+    and the reduction starts from +-inf, numpy/funcs.py:278-295), an all-NaN
+    column (the identity comes back), twice in a row (the scratch counters must be
+    back at zero)."""
+    from numba_mlir_b200 import reduce_ops
+
+    rng = np.random.default_rng(cols)
+    rows = 9000
+    if np.dtype(dtype).kind == "f":
+        a = (rng.standard_normal((rows, cols)) * 100).astype(dtype)
+        a[:, 0] = np.abs(a[:, 0]) + 1          # all positive
+        a[:, 1] = -np.abs(a[:, 1]) - 1         # all negative
+        a[:, 2] = 0.0
+        a[4000, 2] = -0.0
+        a[5000, 3] = np.inf
+        a[6000, 3] = -np.inf
+        a[::7, 4] = np.nan
+        a[:, 5] = np.nan
+        a[:, 6] = np.abs(a[:, 6])
+        a[8999, 6] = -1e-30                    # the only negative value, in the last row block
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")  # All-NaN slice
+            want_min, want_max = np.nanmin(a, axis=0), np.nanmax(a, axis=0)
+        want_min[5], want_max[5] = np.inf, -np.inf
+    else:
+        a = rng.integers(-10**6, 10**6, (rows, cols)).astype(dtype)
+        a[:, 0] = np.abs(a[:, 0]) + 1
+        a[:, 1] = -np.abs(a[:, 1]) - 1
+        a[123, 2] = np.iinfo(dtype).min
+        a[8123, 3] = np.iinfo(dtype).max
+        want_min, want_max = a.min(axis=0), a.max(axis=0)
+    d = _dev(a)
+    for _ in range(2):
+        assert np.array_equal(reduce_ops.reduce(d, "min", 0).copy_to_host(), want_min)
+        assert np.array_equal(reduce_ops.reduce(d, "max", 0).copy_to_host(), want_max)
+    queue.check_status()
 
 
 @pytest.mark.parametrize("dtype", [np.float64, np.int64, np.int32])
