@@ -92,16 +92,20 @@ def kmeans_update(centroids, sums, counts):
 # float32 (index order over the dimensions, separate multiply and add, strict
 # `<` so ties keep the lower cluster), then per-cluster sums (float64) and
 # counts (int64).  The work-group stages the centroids in local memory and
-# every work-item keeps its point in a private array, so the 64 x 16 inner loop
-# runs out of shared memory and registers.  The sums are gathered without
-# per-point atomics: after a batch of 256 points is labelled, 64 work-items
-# (4 point phases x 16 dimensions) add the batch into float64 accumulator
-# columns in local memory that each of them owns, and only the 64 x 16 group
-# totals meet the global arrays through atomics, once per group.
+# every work-item keeps two points in private arrays, so the 64 x 16 inner loop
+# runs out of shared memory and registers and one read of a centroid value
+# serves both points.  The sums are gathered without per-point atomics: after a
+# batch of 256 x 2 points is labelled, 64 work-items (4 point phases x 16
+# dimensions) add the batch into float64 accumulator columns in local memory
+# that each of them owns, and only the 64 x 16 group totals meet the global
+# arrays through atomics, once per group.  (The accumulator is 32 KB: local
+# arrays are static shared memory, 48 KB per group at most.)
 _KM_K = 64
 _KM_D = 16
 _KM_PTS = 8
-_KM_COLS = 64  # accumulator columns per cluster: 4 point phases x 16 dimensions
+_KM_Q = 2  # points a work-item takes through the centroid loop at once
+_KM_PH = 4     # point phases of the accumulation
+_KM_COLS = _KM_PH * _KM_D  # accumulator columns per cluster: phases x dimensions
 KMEANS_LOCAL_SIZE = 256
 
 
@@ -112,7 +116,7 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
     base = get_group_id(0) * (lsz * _KM_PTS)
 
     cent = local.array((_KM_K, _KM_D), np.float32)
-    lbl = local.array(KMEANS_LOCAL_SIZE, np.int32)
+    lbl = local.array(KMEANS_LOCAL_SIZE * _KM_Q, np.int32)
     lcnt = local.array(_KM_K, np.int32)
     # Column c = phase * 16 + dimension belongs to work-item c alone: it adds
     # its points into acc[label, c] with plain read-modify-writes, no atomics.
@@ -131,37 +135,63 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
 
     jcol = lid & (_KM_D - 1)
     phase = lid >> 4
-    p = private.array(_KM_D, np.float32)
-    for r in range(_KM_PTS):
-        row0 = base + r * lsz
-        i = row0 + lid
-        for jj in range(_KM_D):
-            p[jj] = points[i, jj]
-        best = 0
-        best_d = np.float32(np.inf)
-        for k in range(_KM_K):
-            d = np.float32(0.0)
+    # _KM_Q points per work-item go through the centroid loop together, so one
+    # read of a centroid value from local memory serves all of them; each point's
+    # distance still accumulates over the dimensions in index order.
+    p = private.array((_KM_Q, _KM_D), np.float32)
+    d = private.array(_KM_Q, np.float32)
+    best_d = private.array(_KM_Q, np.float32)
+    best = private.array(_KM_Q, np.int32)
+    for r in range(_KM_PTS // _KM_Q):
+        row0 = base + r * (lsz * _KM_Q)
+        for q in range(_KM_Q):
             for jj in range(_KM_D):
-                t = p[jj] - cent[k, jj]
-                d += t * t
-            if d < best_d:
-                best_d = d
-                best = k
-        labels[i] = best
-        atomic.add(lcnt, best, 1)
-        lbl[lid] = best
+                p[q, jj] = points[row0 + q * lsz + lid, jj]
+            best[q] = 0
+            best_d[q] = np.float32(np.inf)
+        for k in range(_KM_K):
+            for q in range(_KM_Q):
+                d[q] = np.float32(0.0)
+            for jj in range(_KM_D):
+                c = cent[k, jj]
+                for q in range(_KM_Q):
+                    t = p[q, jj] - c
+                    d[q] += t * t
+            for q in range(_KM_Q):
+                if d[q] < best_d[q]:
+                    best_d[q] = d[q]
+                    best[q] = k
+        for q in range(_KM_Q):
+            labels[row0 + q * lsz + lid] = best[q]
+            atomic.add(lcnt, best[q], 1)
+            lbl[q * lsz + lid] = best[q]
         barrier()
         if lid < _KM_COLS:
             # the batch's rows were read a moment ago: these loads hit in L1
-            for m in range(phase, KMEANS_LOCAL_SIZE, _KM_COLS // _KM_D):
-                acc[lbl[m], lid] += points[row0 + m, jcol]
+            # four rows per step: their labels and values are fetched before the
+            # first read-modify-write, which would otherwise order every load behind it
+            for m in range(phase, KMEANS_LOCAL_SIZE * _KM_Q, 4 * _KM_PH):
+                l0 = lbl[m]
+                l1 = lbl[m + _KM_PH]
+                l2 = lbl[m + 2 * _KM_PH]
+                l3 = lbl[m + 3 * _KM_PH]
+                x0 = points[row0 + m, jcol]
+                x1 = points[row0 + m + _KM_PH, jcol]
+                x2 = points[row0 + m + 2 * _KM_PH, jcol]
+                x3 = points[row0 + m + 3 * _KM_PH, jcol]
+                acc[l0, lid] += x0
+                acc[l1, lid] += x1
+                acc[l2, lid] += x2
+                acc[l3, lid] += x3
         barrier()
 
     e = lid
     while e < _KM_K * _KM_D:
         k = e // _KM_D
         jj = e % _KM_D
-        v = acc[k, jj] + acc[k, _KM_D + jj] + acc[k, 2 * _KM_D + jj] + acc[k, 3 * _KM_D + jj]
+        v = acc[k, jj]
+        for ph in range(1, _KM_PH):
+            v += acc[k, ph * _KM_D + jj]
         if v != 0.0:
             atomic.add(sums, (k, jj), v)
         e += lsz
