@@ -246,6 +246,7 @@ class Translator:
         self.decls = []           # C declarations at function top
         self.declared = set()
         self.shared_decls = []
+        self.local_arrays = []   # (index in shared_decls, name, C type, bytes) of local.array buffers
         self.consts = {}          # var name -> compile-time Python object
         self.tuples = {}          # var name -> list of element reps (C exprs / nested)
         self.arrays = {}          # var name -> ArrayRep
@@ -717,6 +718,8 @@ class Translator:
         rep = self.arrays[tname]
         buf = self.fresh("nmb_local" if shared else "nmb_private")
         if shared:
+            self.local_arrays.append((len(self.shared_decls), buf, rep.ctype,
+                                      max(n, 1) * np.dtype(str(ttype.dtype)).itemsize))
             self.shared_decls.append(f"__shared__ __align__(16) {rep.ctype} {buf}[{max(n, 1)}];")
         else:
             # zero-filled like the reference's simulator (kernel_sim_impl.py:166-168)
@@ -918,14 +921,22 @@ class CompiledKernel:
         self._handles = {}      # queue -> kernel handle (the queue owns and frees it)
         self._block_sizes = {}  # (queue, global size) -> suggested local size
         self._kinds = {}
+        # bytes of work-group-local memory requested at launch (local arrays too
+        # large for static shared memory); the kernel then takes one more
+        # parameter, the offset the runtime placed them at
+        self.local_bytes = 0
 
     def kinds(self, trailing_int64=0):
-        """Launch parameter kinds: the arguments, then `trailing_int64` sizes."""
+        """Launch parameter kinds: the arguments, then `trailing_int64` sizes,
+        then the local-memory request if there is one."""
         k = self._kinds.get(trailing_int64)
         if k is None:
             from .kernel_impl import param_kinds
 
-            k = self._kinds[trailing_int64] = param_kinds(self.param_layout, trailing_int64)
+            k = param_kinds(self.param_layout, trailing_int64)
+            if self.local_bytes:
+                k = k + (("local", self.local_bytes),)
+            self._kinds[trailing_int64] = k
         return k
 
     def handle_on(self, queue):
@@ -942,6 +953,9 @@ class CompiledKernel:
         if b is None:
             b = self._block_sizes[key] = queue.suggest_block_size(kernel, global_size)
         return b
+
+
+_STATIC_LOCAL_LIMIT = 36 * 1024  # local-array bytes kept as static shared memory
 
 
 def compile_kernel(py_func, args, ndim, fastmath=False):
@@ -974,6 +988,19 @@ def compile_kernel(py_func, args, ndim, fastmath=False):
             kparams.append(f"{c_scalar_type(t)} p{i}")
             layout.append(("scalar", np.dtype(str(t))))
     kparams += ["int64_t nmb_g0", "int64_t nmb_g1", "int64_t nmb_g2"]
+    # Local arrays are static shared memory while they fit beside the kernel's
+    # other static buffers (48 KB per group in all); larger ones are carved out
+    # of the dynamic shared memory the launch asks for through a local-memory
+    # parameter ({NULL, size, ptr}, GpuRuntimeToLlvm.cpp:514-528), up to the
+    # device's limit per group.
+    local_bytes = 0
+    if sum(nb for _i, _b, _c, nb in tr.local_arrays) > _STATIC_LOCAL_LIMIT:
+        for idx, buf, ct, nb in tr.local_arrays:
+            tr.shared_decls[idx] = (f"{ct}* const {buf} = reinterpret_cast<{ct}*>"
+                                    f"(nmb_dyn_local + nmb_local_off + {local_bytes}ull);")
+            local_bytes += (nb + 15) // 16 * 16
+        tr.shared_decls.insert(0, "extern __shared__ __align__(16) unsigned char nmb_dyn_local[];")
+        kparams.append("unsigned long long nmb_local_off")
     opts = "\n#define NMB_FASTMATH 1" if fastmath else " --fmad=false"
     group_prologue = ""
     if tr.uses_group_reduce:
@@ -1003,7 +1030,9 @@ extern "C" __global__ void nmb_kernel({', '.join(kparams)}) {{
     {(chr(10) + '    ').join(body)}
 }}
 """
-    return CompiledKernel(src, "nmb_kernel", layout, tr.uses_barrier)
+    ck = CompiledKernel(src, "nmb_kernel", layout, tr.uses_barrier)
+    ck.local_bytes = local_bytes
+    return ck
 
 
 # ------------------------------------------------------- prange loop nests ---

@@ -233,9 +233,12 @@ class _PreparedParams:
         self.descs = (GPUParamDesc * (n + 1))()
         self.slots = []
         for i, k in enumerate(kinds):
-            if k == "local":
+            if k == "local" or (type(k) is tuple and k[0] == "local"):
+                # ("local", nbytes): a size fixed for the kernel; "local": set by fill()
                 self.descs[i].data = None
                 self.descs[i].type = P_PTR
+                if type(k) is tuple:
+                    self.descs[i].size = int(k[1])
                 self.slots.append(None)
                 continue
             if k == "ptr":

@@ -80,3 +80,30 @@ def test_fastmath_selects_the_approximate_division_and_sqrt(runtime_lib):
         assert ("--fmad=false" in src) != fast
         assert ("nmb::f_rsqrt" in src) == fast
         assert len(runtime.compile_to_cubin(step[1])) > 0
+
+
+def test_large_local_arrays_move_to_the_local_memory_parameter(runtime_lib):
+    """Up to 36 KB of local arrays stay static shared memory; above that the
+    kernel takes an offset parameter and the launch carries a local-memory
+    request of the arrays' total size (16-byte aligned pieces)."""
+    from numba_mlir_b200 import codegen_ir, lazy, runtime
+    from numba_mlir_b200.kernel import get_local_id, local
+
+    def small(a):
+        t = local.array(1024, np.float32)
+        t[get_local_id(0)] = a[get_local_id(0)]
+
+    def big(a):
+        t = local.array(20000, np.float32)
+        u = local.array(3, np.int32)
+        t[get_local_id(0)] = a[get_local_id(0)]
+        u[0] = 1
+
+    args = [lazy.fake_array((256,), np.float32)]
+    ck = codegen_ir.compile_kernel(small, args, 1)
+    assert ck.local_bytes == 0 and "nmb_local_off" not in ck.source
+    assert ck.kinds(3)[-1] == np.dtype(np.int64)
+    ck = codegen_ir.compile_kernel(big, args, 1)
+    assert ck.local_bytes == 80000 + 16 and "unsigned long long nmb_local_off" in ck.source
+    assert ck.kinds(3)[-1] == ("local", 80016)
+    assert len(runtime.compile_to_cubin(ck.source.encode())) > 0

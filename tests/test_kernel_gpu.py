@@ -190,6 +190,52 @@ def test_local_memory_barrier_and_group_reduce(queue):
     assert np.array_equal(c.copy_to_host(), want_c)
 
 
+_BIG_LOCAL = 20000  # float32 elements: 80 KB, above the 48 KB of static shared memory
+
+
+def _big_local_kernel():
+    from numba_mlir_b200.kernel import barrier, get_group_id, get_local_id, get_local_size, local
+
+    def func(a, out):
+        lid = get_local_id(0)
+        lsz = get_local_size(0)
+        g = get_group_id(0)
+        buf = local.array(_BIG_LOCAL, np.float32)
+        idx = local.array(64, np.int32)
+        j = lid
+        while j < _BIG_LOCAL:
+            buf[j] = a[g * _BIG_LOCAL + j]
+            j += lsz
+        if lid < 64:
+            idx[lid] = lid
+        barrier()
+        j = lid
+        while j < _BIG_LOCAL:
+            out[g * _BIG_LOCAL + j] = buf[_BIG_LOCAL - 1 - j] + idx[j % 64]
+            j += lsz
+
+    return func
+
+
+def test_local_arrays_beyond_static_shared_memory(queue):
+    """Local arrays larger than 48 KB per group (the reference's local memory
+    is bounded only by the device, mlir/kernel_impl.py:366-437) come out of the
+    dynamic shared memory requested with a {NULL, size, ptr} launch parameter
+    (GpuRuntimeToLlvm.cpp:514-528)."""
+    from numba_mlir_b200.kernel import kernel
+
+    groups = 6
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal(groups * _BIG_LOCAL).astype(np.float32)
+    out = _dev(np.zeros_like(a))
+    k = kernel(_big_local_kernel())
+    k[groups * 256, 256](_dev(a), out)
+    blocks = a.reshape(groups, _BIG_LOCAL)
+    want = blocks[:, ::-1] + (np.arange(_BIG_LOCAL) % 64).astype(np.float32)
+    assert np.array_equal(out.copy_to_host(), want.reshape(-1))
+    queue.check_status()
+
+
 def test_private_array_and_kernel_func(queue):
     from numba_mlir_b200.kernel import get_global_id, kernel, kernel_func, private
 
