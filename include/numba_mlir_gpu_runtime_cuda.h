@@ -157,6 +157,22 @@ int gpuxQueueWaitEvents(void *queue, void *events);
  * on.  Returns 0 on success.  No counterpart in the reference, where dpctl
  * owns the queues of imported arrays. */
 int gpuxQueueWaitStream(void *queue, void *nativeStream);
+/* Memory that the other GPU processes of the box can map (one process per
+ * GPU): gpuxPeerAlloc returns zero-filled device memory outside the
+ * stream-ordered pool, gpuxPeerExport writes an opaque handle of
+ * GPUX_PEER_HANDLE_BYTES bytes that another process passes to gpuxPeerOpen to
+ * obtain the address of the same memory in its own address space (peer access
+ * over NVLink is enabled on first use), gpuxPeerClose unmaps it and
+ * gpuxPeerFree releases the owner's allocation.  Export and open return 0 /
+ * non-NULL on success.  They carry the mailboxes of the small all-reduce
+ * between shards; no counterpart in the reference, which drives one device
+ * per process and has no exchange between devices. */
+#define GPUX_PEER_HANDLE_BYTES 64
+void *gpuxPeerAlloc(void *queue, size_t size);
+void gpuxPeerFree(void *queue, void *ptr);
+int gpuxPeerExport(void *ptr, void *handle);
+void *gpuxPeerOpen(void *queue, const void *handle);
+void gpuxPeerClose(void *queue, void *ptr);
 /* Milliseconds between two completed events of the same device. */
 float gpuxEventElapsedMs(void *startEvent, void *endEvent);
 /* Blocks until everything submitted to the queue has finished. */

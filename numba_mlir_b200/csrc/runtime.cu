@@ -1101,6 +1101,70 @@ GPUX_EXPORT int gpuxQueueWaitStream(void *queue, void *nativeStream) {
   return ok ? 0 : 1;
 }
 
+// ------------------------------------------------------------ peer memory ---
+GPUX_EXPORT void *gpuxPeerAlloc(void *queue, size_t size) {
+  LOG_FUNC();
+  if (!queue || !size) {
+    nmb::setError("gpuxPeerAlloc: null queue or zero size");
+    return nullptr;
+  }
+  Queue *q = toQueue(queue);
+  if (!setDevice(q))
+    return nullptr;
+  void *p = nullptr;
+  // plain cudaMalloc: memory of a stream-ordered pool cannot be exported
+  CUDA_TRY(cudaMalloc(&p, size), return nullptr);
+  CUDA_TRY(cudaMemset(p, 0, size), cudaFree(p); return nullptr);
+  CUDA_TRY(cudaDeviceSynchronize(), cudaFree(p); return nullptr);
+  return p;
+}
+
+GPUX_EXPORT void gpuxPeerFree(void *queue, void *ptr) {
+  LOG_FUNC();
+  if (!queue || !ptr)
+    return;
+  if (!setDevice(toQueue(queue)))
+    return;
+  CUDA_TRY(cudaFree(ptr), return);
+}
+
+GPUX_EXPORT int gpuxPeerExport(void *ptr, void *handle) {
+  LOG_FUNC();
+  static_assert(sizeof(cudaIpcMemHandle_t) == GPUX_PEER_HANDLE_BYTES, "handle size");
+  if (!ptr || !handle) {
+    nmb::setError("gpuxPeerExport: null argument");
+    return 1;
+  }
+  cudaIpcMemHandle_t h;
+  CUDA_TRY(cudaIpcGetMemHandle(&h, ptr), return 1);
+  memcpy(handle, &h, sizeof(h));
+  return 0;
+}
+
+GPUX_EXPORT void *gpuxPeerOpen(void *queue, const void *handle) {
+  LOG_FUNC();
+  if (!queue || !handle) {
+    nmb::setError("gpuxPeerOpen: null argument");
+    return nullptr;
+  }
+  if (!setDevice(toQueue(queue)))
+    return nullptr;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  void *p = nullptr;
+  CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), return nullptr);
+  return p;
+}
+
+GPUX_EXPORT void gpuxPeerClose(void *queue, void *ptr) {
+  LOG_FUNC();
+  if (!queue || !ptr)
+    return;
+  if (!setDevice(toQueue(queue)))
+    return;
+  CUDA_TRY(cudaIpcCloseMemHandle(ptr), return);
+}
+
 GPUX_EXPORT void *gpuxRecordEvent(void *queue) {
   LOG_FUNC();
   if (!queue) {

@@ -77,6 +77,11 @@ SIGNATURES = {
     "gpuxRecordEvent": (_vp, [_vp]),
     "gpuxQueueWaitEvents": (_i, [_vp, _vp]),
     "gpuxQueueWaitStream": (_i, [_vp, _vp]),
+    "gpuxPeerAlloc": (_vp, [_vp, ctypes.c_size_t]),
+    "gpuxPeerFree": (None, [_vp, _vp]),
+    "gpuxPeerExport": (_i, [_vp, _vp]),
+    "gpuxPeerOpen": (_vp, [_vp, _vp]),
+    "gpuxPeerClose": (None, [_vp, _vp]),
     "gpuxEventElapsedMs": (ctypes.c_float, [_vp, _vp]),
     "gpuxQueueSynchronize": (None, [_vp]),
     "gpuxQueueGetStream": (_vp, [_vp]),

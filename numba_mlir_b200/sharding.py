@@ -5,10 +5,17 @@ mlir/lib/Conversion/GpuToGpuRuntime.cpp:169-197).  The benchmark workloads
 shard along axis 0 -- one process per GPU, every process runs the same
 single-GPU kernels on its rows -- and only three results span shards: a full
 sum, a column-wise min, and the per-cluster sums/counts of a k-means
-iteration.  Those partials are all-reduced with torch.distributed (NCCL over
-NVLink on GPUs, gloo in the CPU tests); they are at most a few KB, so the
-exchange is latency bound and no custom kernel is warranted.
+iteration.  Those partials are a few KB, so the exchange is latency bound.  On
+GPUs it is one launch of the library's own peer-memory kernel
+(csrc/kernels/peer_allreduce.cu: every rank publishes its partial in a mailbox
+the others map over NVLink, waits for their flags and combines all partials in
+rank order); torch.distributed carries only the one-time exchange of the
+mailbox handles, and remains the path for host arrays (gloo in the CPU tests),
+for partials above 64 KB and when peer mapping is unavailable (NCCL).
 """
+
+import ctypes
+import os
 
 import numpy as np
 
@@ -49,6 +56,10 @@ def allreduce(partial, op="sum", dist=None):
         t = torch.from_numpy(partial)
         dist.all_reduce(t, op=rop)
         return partial
+    group = peer_group(partial.queue, dist)
+    if group is not None and group.accepts(partial):
+        group.allreduce(partial, op)
+        return partial
     # Run the collective in stream order behind the kernels that produced the
     # partial: torch adopts the queue's stream for the duration of the call, so
     # no host synchronisation is needed on either side.
@@ -56,6 +67,101 @@ def allreduce(partial, op="sum", dist=None):
     with torch.cuda.stream(stream):
         dist.all_reduce(_torch_view(partial), op=rop)
     return partial
+
+
+PEER_SLOT_BYTES = 65536                       # payload of one mailbox slot
+PEER_MAILBOX_BYTES = 256 + 2 * PEER_SLOT_BYTES  # two flags (128 B apart) + two slots
+_PEER_TYPES = {"float32": "f32", "float64": "f64", "int32": "i32", "int64": "i64"}
+
+
+class PeerGroup:
+    """The mailboxes of one queue's ranks for the peer-memory all-reduce.
+
+    Built collectively (every rank of `dist` constructs it at the same point):
+    each rank allocates its mailbox, the 64-byte handles travel through
+    `dist.all_gather_object`, and every rank maps the others' mailboxes.
+    `ok` is False on every rank if any rank failed to map a peer."""
+
+    def __init__(self, queue, dist):
+        from .device_array import from_host
+
+        self.queue = queue
+        self.rank = dist.get_rank()
+        self.world = dist.get_world_size()
+        self.seq = 0
+        self.ok = False
+        self._opened = []
+        lib = queue.lib
+        self._lib = lib
+        self.mailbox = lib.gpuxPeerAlloc(queue.handle, PEER_MAILBOX_BYTES)
+        handle = (ctypes.c_ubyte * 64)()
+        mine = None
+        if self.mailbox and self.world <= 16 and lib.gpuxPeerExport(self.mailbox, handle) == 0:
+            mine = bytes(handle)
+        lib.gpuxClearLastError()
+        handles = [None] * self.world
+        dist.all_gather_object(handles, mine)
+        bases = [0] * self.world
+        good = all(h is not None for h in handles)
+        if good:
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    bases[r] = self.mailbox
+                    continue
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                p = lib.gpuxPeerOpen(queue.handle, buf)
+                if not p:
+                    good = False
+                    lib.gpuxClearLastError()
+                    break
+                self._opened.append(p)
+                bases[r] = p
+        flags = [None] * self.world
+        dist.all_gather_object(flags, bool(good))
+        if all(flags):
+            self.table = from_host(np.asarray(bases, dtype=np.uint64), queue=queue)
+            self.ok = True
+        else:
+            self.close()
+
+    def accepts(self, partial):
+        return (self.ok and partial.dtype.name in _PEER_TYPES and partial.is_c_contiguous
+                and 0 < partial.nbytes <= PEER_SLOT_BYTES and partial.queue is self.queue)
+
+    def allreduce(self, partial, op):
+        """One launch on the partial's queue; the result is bit-identical on
+        every rank (the partials are combined in rank order)."""
+        self.seq += 1
+        q = self.queue
+        k = q.builtin(f"nmb_peer_allreduce_{op}_{_PEER_TYPES[partial.dtype.name]}")
+        q.launch(k, (1,), (1024,),
+                 [("ptr", partial.ptr), np.int64(partial.size), ("ptr", self.table.ptr),
+                  np.int32(self.rank), np.int32(self.world), np.uint64(self.seq),
+                  ("ptr", q.status_ptr)])
+
+    def close(self):
+        for p in self._opened:
+            self._lib.gpuxPeerClose(self.queue.handle, p)
+        self._opened = []
+        if self.mailbox:
+            self._lib.gpuxPeerFree(self.queue.handle, self.mailbox)
+            self.mailbox = None
+        self.ok = False
+
+
+_peer_groups = {}
+
+
+def peer_group(queue, dist):
+    """The queue's PeerGroup, built on first use (collectively: every rank
+    reaches its first device all-reduce at the same point of the program), or
+    None when NUMBA_MLIR_B200_PEER_ALLREDUCE=0 or the mapping failed."""
+    if os.environ.get("NUMBA_MLIR_B200_PEER_ALLREDUCE", "1") == "0":
+        return None
+    g = _peer_groups.get(queue)
+    if g is None:
+        g = _peer_groups[queue] = PeerGroup(queue, dist)
+    return g if g.ok else None
 
 
 _streams = {}

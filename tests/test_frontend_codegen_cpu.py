@@ -83,8 +83,8 @@ def test_fastmath_selects_the_approximate_division_and_sqrt(runtime_lib):
 
 
 def test_large_local_arrays_move_to_the_local_memory_parameter(runtime_lib):
-    """Up to 36 KB of local arrays stay static shared memory; above that the
-    kernel takes an offset parameter and the launch carries a local-memory
+    """Local arrays stay static shared memory while the kernel's static total
+    fits 48 KB; above that the kernel takes an offset parameter and the launch carries a local-memory
     request of the arrays' total size (16-byte aligned pieces)."""
     from numba_mlir_b200 import codegen_ir, lazy, runtime
     from numba_mlir_b200.kernel import get_local_id, local

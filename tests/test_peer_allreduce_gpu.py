@@ -1,0 +1,133 @@
+"""The peer-memory all-reduce kernel (csrc/kernels/peer_allreduce.cu).
+
+On one GPU the ranks are not run as separate launches (they would wait on one
+another); the peers' mailboxes are filled from the host before the one launch
+under test, which then finds every flag already set.  With two or more GPUs
+the real exchange runs as one process per GPU."""
+
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = 256
+SLOT = 65536
+
+
+def _mailboxes(world):
+    import numba_mlir_b200 as nm
+
+    return [nm.zeros(HEADER + 2 * SLOT, np.uint8) for _ in range(world)]
+
+
+def _post(box, mirror, seq, payload):
+    """What the rank owning `box` would have published for call `seq`
+    (`mirror` is the host copy of the mailbox, kept between calls)."""
+    slot = seq & 1
+    raw = payload.view(np.uint8)
+    mirror[HEADER + slot * SLOT: HEADER + slot * SLOT + raw.size] = raw
+    mirror[slot * 128: slot * 128 + 8] = np.asarray([seq], np.uint64).view(np.uint8)
+    box.copy_from_host(mirror)
+
+
+def _launch(queue, op, ty, data, table, rank, world, seq):
+    k = queue.builtin(f"nmb_peer_allreduce_{op}_{ty}")
+    queue.launch(k, (1,), (1024,),
+                 [("ptr", data.ptr), np.int64(data.size), ("ptr", table.ptr), np.int32(rank),
+                  np.int32(world), np.uint64(seq), ("ptr", queue.status_ptr)])
+
+
+_TYPES = {"f32": np.float32, "f64": np.float64, "i32": np.int32, "i64": np.int64}
+
+
+@pytest.mark.parametrize("op", ["sum", "min", "max"])
+@pytest.mark.parametrize("ty", sorted(_TYPES))
+def test_combines_all_ranks_in_rank_order(queue, op, ty):
+    import numba_mlir_b200 as nm
+
+    world, rank, n = 4, 2, 4099
+    dt = _TYPES[ty]
+    rng = np.random.default_rng(7)
+    boxes = _mailboxes(world)
+    mirrors = [np.zeros(HEADER + 2 * SLOT, np.uint8) for _ in range(world)]
+    table = nm.from_host(np.asarray([b.ptr for b in boxes], np.uint64))
+    for seq in (1, 2, 3):  # slots 1, 0, 1: the second use of a slot overwrites the first
+        parts = [(rng.standard_normal(n) * 1000).astype(dt) for _ in range(world)]
+        for r in range(world):
+            if r != rank:
+                _post(boxes[r], mirrors[r], seq, parts[r])
+        data = nm.from_host(parts[rank])
+        _launch(queue, op, ty, data, table, rank, world, seq)
+        want = parts[0].copy()
+        for r in range(1, world):  # rank order, the kernel's own order
+            if op == "sum":
+                want = want + parts[r]
+            elif op == "min":
+                want = np.where(parts[r] < want, parts[r], want)
+            else:
+                want = np.where(want < parts[r], parts[r], want)
+        assert np.array_equal(data.copy_to_host(), want)
+        slot = seq & 1
+        mine = boxes[rank].copy_to_host()
+        assert mine[slot * 128: slot * 128 + 8].view(np.uint64)[0] == seq
+        assert np.array_equal(mine[HEADER + slot * SLOT: HEADER + slot * SLOT + n * dt().itemsize].view(dt),
+                              parts[rank])
+    queue.check_status()
+
+
+def test_missing_peer_runs_out_and_reports(queue):
+    """A flag that nothing sets: the wait gives up after its bound (about two
+    seconds), the status word is raised and the data are left as they were."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200.runtime import GpuRuntimeError
+
+    world, rank, n = 2, 0, 100
+    boxes = _mailboxes(world)
+    table = nm.from_host(np.asarray([b.ptr for b in boxes], np.uint64))
+    part = np.arange(n, dtype=np.float32)
+    data = nm.from_host(part)
+    _launch(queue, "sum", "f32", data, table, rank, world, 1)
+    with pytest.raises(GpuRuntimeError):
+        queue.check_status()
+    assert np.array_equal(data.copy_to_host(), part)
+    queue.check_status()  # the status word was cleared: the queue stays usable
+
+
+def test_bad_arguments_are_reported_not_run(queue):
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200.runtime import GpuRuntimeError
+
+    boxes = _mailboxes(1)
+    table = nm.from_host(np.asarray([boxes[0].ptr], np.uint64))
+    data = nm.zeros(8, np.float32)
+    k = queue.builtin("nmb_peer_allreduce_sum_f32")
+    for n, rank, world in ((20000, 0, 1), (8, 1, 1), (8, 0, 17)):  # > 64 KB, rank >= world, world > 16
+        queue.launch(k, (1,), (1024,), [("ptr", data.ptr), np.int64(n), ("ptr", table.ptr), np.int32(rank),
+                                        np.int32(world), np.uint64(1), ("ptr", queue.status_ptr)])
+        with pytest.raises(GpuRuntimeError):
+            queue.check_status()
+
+
+def test_ranks_on_separate_gpus_agree():
+    """One process per GPU: sum, min and max of float32 / float64 / int64
+    partials through sharding.allreduce, many calls in a row (both slots reused),
+    results equal to the host's rank-ordered combination on every rank."""
+    import torch
+
+    n_gpus = torch.cuda.device_count()
+    if n_gpus < 2:
+        pytest.skip("needs two GPUs")
+    world = min(n_gpus, 4)
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""),
+               NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29671",
+           os.path.join(ROOT, "tests", "peer_allreduce_ranks.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert res.stdout.count("PEER-ALLREDUCE-OK") == world, res.stdout[-3000:] + res.stderr[-3000:]
