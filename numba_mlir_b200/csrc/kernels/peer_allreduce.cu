@@ -84,14 +84,28 @@ __device__ __forceinline__ void peer_allreduce(T *data, int64_t n, const unsigne
   const unsigned long long slot = seq & 1ull;
   const unsigned long long payload = kHeaderBytes + slot * kSlotBytes;
 
+  // 16-byte chunks when the partial allows it: a thread then has the loads of
+  // four ranks in flight for each chunk, so the combine costs one trip over the
+  // link per four ranks.
+  constexpr int kPerChunk = 16 / sizeof(T);
+  const bool chunked = (reinterpret_cast<unsigned long long>(data) & 15ull) == 0 && n % kPerChunk == 0;
+  const int64_t nchunks = chunked ? n / kPerChunk : 0;
+
   // 1. publish this rank's partial
   T *mine = reinterpret_cast<T *>(base[rank] + payload);
-  for (int64_t i = tid; i < n; i += kThreads)
-    mine[i] = data[i];
-  __threadfence_system();
+  if (chunked) {
+    for (int64_t c = tid; c < nchunks; c += kThreads)
+      reinterpret_cast<uint4 *>(mine)[c] = reinterpret_cast<const uint4 *>(data)[c];
+  } else {
+    for (int64_t i = tid; i < n; i += kThreads)
+      mine[i] = data[i];
+  }
   __syncthreads();
-  if (tid == 0)
+  if (tid == 0) {
+    // the block's stores above are ordered before this release through the barrier
+    __threadfence_system();
     store_flag(reinterpret_cast<unsigned long long *>(base[rank] + slot * kFlagStride), seq);
+  }
 
   // 2. one thread per peer waits for that peer's flag
   if (tid < world && tid != rank) {
@@ -117,11 +131,35 @@ __device__ __forceinline__ void peer_allreduce(T *data, int64_t n, const unsigne
 
   // 3. combine in rank order; peers' payloads are read over the link, uncached
   const Op op;
-  for (int64_t i = tid; i < n; i += kThreads) {
-    T acc = __ldcv(reinterpret_cast<const T *>(base[0] + payload) + i);
-    for (int p = 1; p < world; ++p)
-      acc = op(acc, __ldcv(reinterpret_cast<const T *>(base[p] + payload) + i));
-    data[i] = acc;
+  if (chunked) {
+    for (int64_t c = tid; c < nchunks; c += kThreads) {
+      // ranks in batches of four: four loads in flight, combined in rank order
+      uint4 acc = __ldcv(reinterpret_cast<const uint4 *>(base[0] + payload) + c);
+      for (int p0 = 1; p0 < world; p0 += 4) {
+        uint4 part[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (p0 + k < world)
+            part[k] = __ldcv(reinterpret_cast<const uint4 *>(base[p0 + k] + payload) + c);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (p0 + k < world) {
+            T *a = reinterpret_cast<T *>(&acc);
+            const T *b = reinterpret_cast<const T *>(&part[k]);
+#pragma unroll
+            for (int l = 0; l < kPerChunk; ++l)
+              a[l] = op(a[l], b[l]);
+          }
+      }
+      reinterpret_cast<uint4 *>(data)[c] = acc;
+    }
+  } else {
+    for (int64_t i = tid; i < n; i += kThreads) {
+      T acc = __ldcv(reinterpret_cast<const T *>(base[0] + payload) + i);
+      for (int p = 1; p < world; ++p)
+        acc = op(acc, __ldcv(reinterpret_cast<const T *>(base[p] + payload) + i));
+      data[i] = acc;
+    }
   }
 }
 
