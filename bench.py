@@ -519,10 +519,13 @@ def time_device(queue, workload, steps, warmup, barrier, use_graph):
         workload.step_device()
     barrier()
     graph = None
+    captured = 0
     if use_graph:
+        before = runtime.launch_count()
         queue.graph_begin()
         workload.step_device()
         graph = queue.graph_end()
+        captured = runtime.launch_count() - before  # kernel launches recorded in one step
         queue.graph_launch(graph)
         barrier()
     count0 = runtime.launch_count()
@@ -539,7 +542,7 @@ def time_device(queue, workload, steps, warmup, barrier, use_graph):
     ms = queue.elapsed_ms(e0, e1)
     counted = runtime.launch_count() - count0
     if graph is not None:
-        counted = steps * workload.launches_per_step
+        counted = steps * captured
         queue.graph_destroy(graph)
     queue.destroy_event(e0)
     queue.destroy_event(e1)
@@ -574,9 +577,16 @@ def run_gpu(args):
     queue = runtime.get_queue(f"cuda:{local_rank}")
     w = WORKLOADS[args.workload]()
     w.setup_device(queue, seed=rank, dist=dist)
-    # a step with a collective cannot be graph captured with the default stream
+    # A step with an exchange between shards is recorded in a graph like the
+    # others when the exchange is the library's own peer-memory kernel (its call
+    # counter lives on the device); a torch.distributed collective is not captured.
     collective = dist is not None and getattr(w, "dist", None) is not None
-    use_graph = not collective and not args.no_graph
+    peer_exchange = False
+    if collective:
+        from numba_mlir_b200 import sharding
+
+        peer_exchange = sharding.peer_group(queue, dist) is not None  # built here by every rank
+    use_graph = (not collective or peer_exchange) and not args.no_graph
 
     def barrier():
         queue.synchronize()
@@ -670,7 +680,9 @@ def run_gpu(args):
                 "elements_per_step_per_gpu": w.units_per_step,
                 "api": "numba_mlir_b200.njit(parallel=True) / @kernel, launched through the gpux* C-ABI",
                 "sharding": "axis 0 split across GPUs, full-size shard per GPU"
-                + (", NCCL all-reduce of the partials each step" if collective else ", no collective"),
+                + ((", all-reduce of the partials each step by the library's peer-memory kernel"
+                    if peer_exchange else ", NCCL all-reduce of the partials each step")
+                   if collective else ", no collective"),
                 "l2": "working set per step exceeds the 126 MB L2 (or rotates over >2x L2); no flush",
                 "launch": "one step recorded in a CUDA graph, replayed per step" if use_graph
                 else "eager launches",

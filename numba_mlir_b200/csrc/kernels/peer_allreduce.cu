@@ -8,12 +8,17 @@
 //
 // Every rank owns a mailbox in its own memory that the other ranks map:
 //
-//   bytes [0, 128)     flag of slot 0 (a 64-bit sequence number)
-//   bytes [128, 256)   flag of slot 1
+//   bytes [0, 8)       flag of slot 0 (a 64-bit sequence number)
+//   bytes [64, 72)     the owner's call counter (read and written by the owner only)
+//   bytes [128, 136)   flag of slot 1
 //   bytes [256, +64K)  payload of slot 0
 //   then               payload of slot 1
 //
-// Call number `seq` (1, 2, ...; the same on every rank) uses slot seq & 1:
+// Every launch increments the rank's own call counter; the new value `seq`
+// (1, 2, ...; the same on every rank, since every rank takes part in every
+// call) is the call's number.  Keeping it on the device makes the launch
+// identical from call to call, so a step that contains it can be recorded in a
+// CUDA graph and replayed.  Call `seq` uses slot seq & 1:
 //   1. the rank copies its partial into its own payload and then stores `seq`
 //      into its own flag with release semantics at system scope;
 //   2. it waits, with a bound, until every peer's flag of that slot reads `seq`;
@@ -38,6 +43,7 @@ namespace {
 constexpr int kThreads = 1024;
 constexpr int kMaxRanks = 16;
 constexpr unsigned long long kFlagStride = 128;
+constexpr unsigned long long kCounterOffset = 64;
 constexpr unsigned long long kHeaderBytes = 256;
 constexpr unsigned long long kSlotBytes = 65536;
 constexpr int kSpinLimit = 1 << 22; // x ~0.5 us of back-off: about two seconds
@@ -65,9 +71,9 @@ __device__ __forceinline__ void store_flag(unsigned long long *p, unsigned long 
 
 template <typename T, typename Op>
 __device__ __forceinline__ void peer_allreduce(T *data, int64_t n, const unsigned long long *peers,
-                                               int rank, int world, unsigned long long seq,
-                                               uint32_t *status) {
+                                               int rank, int world, uint32_t *status) {
   __shared__ unsigned long long base[kMaxRanks];
+  __shared__ unsigned long long seq_shared;
   __shared__ int arrived;
   const int tid = threadIdx.x;
   if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world ||
@@ -81,6 +87,13 @@ __device__ __forceinline__ void peer_allreduce(T *data, int64_t n, const unsigne
   if (tid == 0)
     arrived = 1;
   __syncthreads();
+  if (tid == 0) {
+    unsigned long long *counter = reinterpret_cast<unsigned long long *>(base[rank] + kCounterOffset);
+    seq_shared = *counter + 1;
+    *counter = seq_shared;
+  }
+  __syncthreads();
+  const unsigned long long seq = seq_shared;
   const unsigned long long slot = seq & 1ull;
   const unsigned long long payload = kHeaderBytes + slot * kSlotBytes;
 
@@ -170,9 +183,8 @@ __device__ __forceinline__ void peer_allreduce(T *data, int64_t n, const unsigne
 #define NMB_PEER_ALLREDUCE(op, OP, ty, T)                                                        \
   extern "C" __global__ void __launch_bounds__(kThreads)                                         \
       nmb_peer_allreduce_##op##_##ty(T *data, int64_t n, const unsigned long long *peers,       \
-                                     int32_t rank, int32_t world, unsigned long long seq,       \
-                                     uint32_t *status) {                                         \
-    peer_allreduce<T, OP>(data, n, peers, rank, world, seq, status);                            \
+                                     int32_t rank, int32_t world, uint32_t *status) {            \
+    peer_allreduce<T, OP>(data, n, peers, rank, world, status);                                 \
   }                                                                                              \
   NMB_REGISTER_KERNEL(nmb_peer_allreduce_##op##_##ty, 0);
 

@@ -130,14 +130,15 @@ class PeerGroup:
 
     def allreduce(self, partial, op):
         """One launch on the partial's queue; the result is bit-identical on
-        every rank (the partials are combined in rank order)."""
+        every rank (the partials are combined in rank order).  The call number
+        lives in the mailbox, so the launch can be recorded in a CUDA graph;
+        `seq` here only counts the calls submitted from the host."""
         self.seq += 1
         q = self.queue
         k = q.builtin(f"nmb_peer_allreduce_{op}_{_PEER_TYPES[partial.dtype.name]}")
         q.launch(k, (1,), (1024,),
                  [("ptr", partial.ptr), np.int64(partial.size), ("ptr", self.table.ptr),
-                  np.int32(self.rank), np.int32(self.world), np.uint64(self.seq),
-                  ("ptr", q.status_ptr)])
+                  np.int32(self.rank), np.int32(self.world), ("ptr", q.status_ptr)])
 
     def close(self):
         for p in self._opened:

@@ -35,11 +35,12 @@ def _post(box, mirror, seq, payload):
     box.copy_from_host(mirror)
 
 
-def _launch(queue, op, ty, data, table, rank, world, seq):
+def _launch(queue, op, ty, data, table, rank, world):
+    """The rank's own mailbox counts its calls: launch number k is call k."""
     k = queue.builtin(f"nmb_peer_allreduce_{op}_{ty}")
     queue.launch(k, (1,), (1024,),
                  [("ptr", data.ptr), np.int64(data.size), ("ptr", table.ptr), np.int32(rank),
-                  np.int32(world), np.uint64(seq), ("ptr", queue.status_ptr)])
+                  np.int32(world), ("ptr", queue.status_ptr)])
 
 
 _TYPES = {"f32": np.float32, "f64": np.float64, "i32": np.int32, "i64": np.int64}
@@ -62,7 +63,7 @@ def test_combines_all_ranks_in_rank_order(queue, op, ty):
             if r != rank:
                 _post(boxes[r], mirrors[r], seq, parts[r])
         data = nm.from_host(parts[rank])
-        _launch(queue, op, ty, data, table, rank, world, seq)
+        _launch(queue, op, ty, data, table, rank, world)
         want = parts[0].copy()
         for r in range(1, world):  # rank order, the kernel's own order
             if op == "sum":
@@ -75,6 +76,7 @@ def test_combines_all_ranks_in_rank_order(queue, op, ty):
         slot = seq & 1
         mine = boxes[rank].copy_to_host()
         assert mine[slot * 128: slot * 128 + 8].view(np.uint64)[0] == seq
+        assert mine[64:72].view(np.uint64)[0] == seq  # the rank's own call counter
         assert np.array_equal(mine[HEADER + slot * SLOT: HEADER + slot * SLOT + n * dt().itemsize].view(dt),
                               parts[rank])
     queue.check_status()
@@ -91,7 +93,7 @@ def test_missing_peer_runs_out_and_reports(queue):
     table = nm.from_host(np.asarray([b.ptr for b in boxes], np.uint64))
     part = np.arange(n, dtype=np.float32)
     data = nm.from_host(part)
-    _launch(queue, "sum", "f32", data, table, rank, world, 1)
+    _launch(queue, "sum", "f32", data, table, rank, world)
     with pytest.raises(GpuRuntimeError):
         queue.check_status()
     assert np.array_equal(data.copy_to_host(), part)
@@ -108,7 +110,7 @@ def test_bad_arguments_are_reported_not_run(queue):
     k = queue.builtin("nmb_peer_allreduce_sum_f32")
     for n, rank, world in ((20000, 0, 1), (8, 1, 1), (8, 0, 17)):  # > 64 KB, rank >= world, world > 16
         queue.launch(k, (1,), (1024,), [("ptr", data.ptr), np.int64(n), ("ptr", table.ptr), np.int32(rank),
-                                        np.int32(world), np.uint64(1), ("ptr", queue.status_ptr)])
+                                        np.int32(world), ("ptr", queue.status_ptr)])
         with pytest.raises(GpuRuntimeError):
             queue.check_status()
 
