@@ -24,6 +24,36 @@ def test_row_range_is_a_balanced_partition():
             assert max(sizes) - min(sizes) <= 1
 
 
+def test_peer_exchange_takes_only_what_fits_a_mailbox_slot(monkeypatch):
+    """Which partials the peer-memory all-reduce accepts (the rest go through
+    torch.distributed), and the switch that turns the path off; host-side
+    logic only, no device."""
+    from numba_mlir_b200 import lazy, sharding
+
+    queue = object()
+    group = sharding.PeerGroup.__new__(sharding.PeerGroup)
+    group.ok, group.queue = True, queue
+
+    def part(shape, dtype, q=queue):
+        a = lazy.fake_array(shape, dtype)
+        a._buf.queue = q
+        return a
+
+    assert group.accepts(part((4096,), np.float32))       # 16 KB column minima
+    assert group.accepts(part((), np.int64))              # a full sum
+    assert group.accepts(part((64, 16), np.float64))      # k-means sums
+    assert group.accepts(part((16384,), np.float32))      # exactly one slot
+    assert not group.accepts(part((16385,), np.float32))  # above 64 KB
+    assert not group.accepts(part((0,), np.float32))
+    assert not group.accepts(part((64,), np.int16))       # no kernel for the type
+    assert not group.accepts(part((64, 16), np.float64).T)
+    assert not group.accepts(part((64,), np.float32, q=object()))  # another queue
+    group.ok = False
+    assert not group.accepts(part((64,), np.float32))
+    monkeypatch.setenv("NUMBA_MLIR_B200_PEER_ALLREDUCE", "0")
+    assert sharding.peer_group(queue, None) is None       # returns before touching `dist`
+
+
 _WORKER = textwrap.dedent(
     """
     import os, sys
