@@ -46,7 +46,8 @@ constexpr unsigned long long kFlagStride = 128;
 constexpr unsigned long long kCounterOffset = 64;
 constexpr unsigned long long kHeaderBytes = 256;
 constexpr unsigned long long kSlotBytes = 65536;
-constexpr int kSpinLimit = 1 << 22; // x ~0.5 us of back-off: about two seconds
+constexpr int kSpinLimit = 1 << 22; // x (0.5 us of back-off + one flag read): two seconds at the least,
+                                    // several when the flag is read over the link
 
 struct OpSum {
   template <typename T> __device__ __forceinline__ T operator()(T a, T b) const { return a + b; }
