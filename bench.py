@@ -169,8 +169,9 @@ class BroadcastAdd(Workload):
         self.outs = [nm.empty((2048, 2048), f32, queue) for _ in range(10)]
         self.i = 0
 
-    # a recorded step must cover one full rotation to keep the working set >L2
-    launches_per_step = 1
+    # a recorded graph must cover one full rotation to keep the working set >L2
+    # (a step count that is not a multiple of it is launched eagerly instead)
+    graph_steps = 10
 
     def step_device(self):
         from numba_mlir_b200 import workloads
@@ -520,18 +521,24 @@ def time_device(queue, workload, steps, warmup, barrier, use_graph):
     barrier()
     graph = None
     captured = 0
-    if use_graph:
+    # steps recorded per graph: a workload that rotates over several operand sets
+    # to stay larger than L2 records one full rotation
+    per_graph = getattr(workload, "graph_steps", 1)
+    if steps % per_graph:
+        per_graph = 1 if per_graph == 1 else 0
+    if use_graph and per_graph:
         before = runtime.launch_count()
         queue.graph_begin()
-        workload.step_device()
+        for _ in range(per_graph):
+            workload.step_device()
         graph = queue.graph_end()
-        captured = runtime.launch_count() - before  # kernel launches recorded in one step
+        captured = runtime.launch_count() - before  # kernel launches recorded in the graph
         queue.graph_launch(graph)
         barrier()
     count0 = runtime.launch_count()
     e0 = queue.record()
     if graph is not None:
-        for _ in range(steps):
+        for _ in range(steps // per_graph):
             queue.graph_launch(graph)
     else:
         for _ in range(steps):
@@ -542,7 +549,7 @@ def time_device(queue, workload, steps, warmup, barrier, use_graph):
     ms = queue.elapsed_ms(e0, e1)
     counted = runtime.launch_count() - count0
     if graph is not None:
-        counted = steps * captured
+        counted = (steps // per_graph) * captured
         queue.graph_destroy(graph)
     queue.destroy_event(e0)
     queue.destroy_event(e1)
@@ -684,8 +691,11 @@ def run_gpu(args):
                     if peer_exchange else ", NCCL all-reduce of the partials each step")
                    if collective else ", no collective"),
                 "l2": "working set per step exceeds the 126 MB L2 (or rotates over >2x L2); no flush",
-                "launch": "one step recorded in a CUDA graph, replayed per step" if use_graph
-                else "eager launches",
+                "launch": ("one step recorded in a CUDA graph, replayed per step"
+                           if getattr(w, "graph_steps", 1) == 1 else
+                           f"{w.graph_steps} steps (one rotation over the operand sets) recorded in a CUDA "
+                           "graph and replayed; eager when the step count is not a multiple of that")
+                if use_graph else "eager launches",
             },
             "elements_per_s": w.units_per_step * world / (ms_per_step * 1e-3),
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
