@@ -224,17 +224,31 @@ void *_mlir_ciface_nmb_pairwise_distance_float32_device(void *queue,
 
 /* No counterpart in the reference.  *out = sum of data[0..n) accumulated in
  * int64, like the full integer reduction above, for callers that must not
- * allocate: a host callback inside a stream, a thread that may not take the
- * allocator's locks, a process whose memory was all handed out at start-up.
- * The kernel's scratch lives in an 8 KB array inside the library image (held
- * by every GPU that loads the library until exit), so the call allocates
- * nothing on host or device; it runs asynchronously on the queue's stream.
+ * allocate: a thread that may not wait on the CUDA allocator (a monitor or a
+ * real-time loop with a latency budget), a process whose device memory was all
+ * handed out at start-up.  The kernel's scratch lives in an 8 KB array inside
+ * the library image (held by every GPU that loads the library until exit), so
+ * the call makes no device allocation and, on its success path, no host
+ * allocation (it takes one short mutex; only the error path formats a
+ * message); it runs asynchronously on the queue's stream.
  * data must be 16-byte aligned, 1 <= n <= 2^32; anything else is refused with
  * an error (non-zero return, gpuxGetLastError).  All calls on a device share
  * the array: calls that overlap on the GPU race, so keep them on one stream.
  * The first call on each device also resolves the array's device address;
- * make it before any stream capture. */
+ * make it before any stream capture.
+ * Every wait inside the kernel is bounded.  A call whose wait ran out leaves
+ * *out untouched and sets a status word in the array that only
+ * gpuxSumInt32NoAllocStatus reports (the queue's own status word is not
+ * involved). */
 int gpuxSumInt32NoAlloc(void *queue, const int32_t *data, size_t n, int64_t *out);
+
+/* No counterpart in the reference.  Failure report of gpuxSumInt32NoAlloc:
+ * waits for the queue's stream, then returns 0 when every call issued so far
+ * on the queue's device completed, 1 when a bounded wait inside one of them
+ * ran out (that call did not write *out), -1 on a CUDA error
+ * (gpuxGetLastError).  A non-zero status is cleared by being read.  Allocates
+ * nothing: the word is read with a 4-byte copy into a local variable. */
+int gpuxSumInt32NoAllocStatus(void *queue);
 
 #ifdef __cplusplus
 }

@@ -317,8 +317,10 @@ __device__ __forceinline__ void drain_after_timeout(Smem &sm, int64_t issued) {
 // out[0] = reduce(a[0:n]).  CTA b streams the span [b*span, (b+1)*span) with
 // span a multiple of the tile size; partials[G] and one counter live in
 // scratch memory.  a is 16-byte aligned; the last n % VEC elements are read
-// directly by the merging CTA.
-template <typename R>
+// directly by the merging CTA.  With GuardOut the merging CTA leaves out[0]
+// untouched when any CTA's bounded wait ran out (the status word is set), for
+// callers whose only failure report is that word.
+template <typename R, bool GuardOut = false>
 __device__ __forceinline__ void reduce_all_body(const typename R::In *__restrict__ a,
                                                 typename R::Out *__restrict__ out,
                                                 typename R::Acc *partials, uint32_t *counter,
@@ -392,7 +394,8 @@ __device__ __forceinline__ void reduce_all_body(const typename R::In *__restrict
       R::acc(m, a[e], e);
   m = block_merge<R>(m, scratch);
   if (tid == 0) {
-    out[0] = R::fin(m);
+    if (!GuardOut || load_cg(status) == (uint32_t)kStatusOk)
+      out[0] = R::fin(m);
     *counter = 0;
   }
 }

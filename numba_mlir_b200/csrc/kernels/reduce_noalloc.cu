@@ -1,22 +1,22 @@
 // gpuxSumInt32NoAlloc: the full int32 -> int64 sum for callers that cannot
 // allocate device memory.
 //
-// Who cannot allocate: code that runs where a device allocation is forbidden
-// or would deadlock -- a host callback running inside a stream, a thread that
-// must not take the CUDA allocator's locks (a signal-safe monitor, a real-time
-// loop with a latency budget), a process whose memory budget was handed out in
-// full at start-up, or a caller between cudaStreamBeginCapture and
-// EndCapture, where an allocation would become part of the graph.  The other
-// entry points of this library reach the same kernel through per-queue scratch
-// memory that grows on demand; this one keeps its scratch (CTA partials, the
-// ticket counter, the status word) in a fixed array that is part of the
-// library image, so calling it allocates nothing, on the host or the device.
+// Who cannot allocate: a thread that must not wait on the CUDA allocator (a
+// monitor with a latency budget, a real-time loop), or a process whose device
+// memory was handed out in full at start-up, so that any later allocation
+// fails.  The other entry points of this library reach the same kernel through
+// per-queue scratch memory that grows on demand; this one keeps its scratch
+// (CTA partials, the ticket counter, the status word) in a fixed array that is
+// part of the library image, so a call makes no device allocation and no host
+// allocation on its success path (it takes one short mutex; only the error
+// path formats a message).
 //
 // The cost: every GPU that loads the library holds the 8 KB array until the
 // process exits, every call on a device shares it (two calls that overlap on
 // the GPU, e.g. from two streams, race on it -- serialise them), and it keeps
-// whatever the last call left, so each call clears the words that must start
-// at zero before launching.
+// whatever the last call left, so each call clears the ticket counter before
+// launching.  The status word is the exception: it stays set until
+// gpuxSumInt32NoAllocStatus has reported it.
 
 #include "../gpu_common.h"
 #include "reduce_common.cuh"
@@ -46,7 +46,8 @@ extern "C" __global__ void __launch_bounds__(nmb::red::kThreads, 3)
     nmb_noalloc_sum_i32(const int32_t *a, int64_t *out, unsigned char *scratch, int64_t n,
                         int64_t span) {
   extern __shared__ __align__(128) unsigned char nmb_smem[];
-  nmb::red::reduce_all_body<SumI32>(a, out, reinterpret_cast<int64_t *>(scratch),
+  // GuardOut: a call whose bounded wait ran out leaves *out untouched
+  nmb::red::reduce_all_body<SumI32, true>(a, out, reinterpret_cast<int64_t *>(scratch),
                                     reinterpret_cast<uint32_t *>(scratch + kCounterOffset), n, span,
                                     reinterpret_cast<uint32_t *>(scratch + kStatusOffset), nmb_smem);
 }
@@ -57,6 +58,36 @@ struct DeviceSetup {
 };
 std::mutex gSetupMutex;
 DeviceSetup gSetup[64];
+
+// Resolves the array's device address once per device (that device current).
+bool setupDevice(int device, DeviceSetup **out) {
+  if (device < 0 || device >= 64) {
+    nmb::setError("gpuxSumInt32NoAlloc: device index %d not supported", device);
+    return false;
+  }
+  DeviceSetup &dev = gSetup[device];
+  std::lock_guard<std::mutex> lock(gSetupMutex);
+  if (!dev.ready) {
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr) {
+      nmb::setError("gpuxSumInt32NoAlloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      (void)cudaGetLastError();
+      return false;
+    }
+    e = cudaFuncSetAttribute(nmb_noalloc_sum_i32, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             nmb::red::kSmemBytes);
+    if (e != cudaSuccess) {
+      nmb::setError("gpuxSumInt32NoAlloc: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+      (void)cudaGetLastError();
+      return false;
+    }
+    dev.scratch = static_cast<unsigned char *>(ptr);
+    dev.ready = true;
+  }
+  *out = &dev;
+  return true;
+}
 
 } // namespace
 
@@ -81,36 +112,15 @@ GPUX_EXPORT int gpuxSumInt32NoAlloc(void *queue, const int32_t *data, size_t n, 
   nmb::QueueView qv;
   if (!nmb::queueView(queue, &qv)) // also makes the queue's device current
     return 1;
-  if (qv.device < 0 || qv.device >= 64) {
-    nmb::setError("gpuxSumInt32NoAlloc: device index %d not supported", qv.device);
-    return 1;
-  }
   cudaStream_t stream = static_cast<cudaStream_t>(qv.stream);
-  DeviceSetup &dev = gSetup[qv.device];
-  {
-    std::lock_guard<std::mutex> lock(gSetupMutex);
-    if (!dev.ready) {
-      void *ptr = nullptr;
-      cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-      if (e != cudaSuccess || !ptr) {
-        nmb::setError("gpuxSumInt32NoAlloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-        (void)cudaGetLastError();
-        return 1;
-      }
-      e = cudaFuncSetAttribute(nmb_noalloc_sum_i32, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               nmb::red::kSmemBytes);
-      if (e != cudaSuccess) {
-        nmb::setError("gpuxSumInt32NoAlloc: cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-        (void)cudaGetLastError();
-        return 1;
-      }
-      dev.scratch = static_cast<unsigned char *>(ptr);
-      dev.ready = true;
-    }
-  }
-  // The array keeps the previous call's contents: the ticket counter and the
-  // status word must start at zero (the partials are fully rewritten).
-  cudaError_t e = cudaMemsetAsync(dev.scratch + kCounterOffset, 0, kScratchBytes - kCounterOffset, stream);
+  DeviceSetup *devp = nullptr;
+  if (!setupDevice(qv.device, &devp))
+    return 1;
+  DeviceSetup &dev = *devp;
+  // The array keeps the previous call's contents: the ticket counter must start
+  // at zero (the partials are fully rewritten).  The status word is left alone:
+  // it belongs to gpuxSumInt32NoAllocStatus.
+  cudaError_t e = cudaMemsetAsync(dev.scratch + kCounterOffset, 0, kStatusOffset - kCounterOffset, stream);
   if (e != cudaSuccess) {
     nmb::setError("gpuxSumInt32NoAlloc: cudaMemsetAsync failed: %s", cudaGetErrorString(e));
     (void)cudaGetLastError();
@@ -131,4 +141,36 @@ GPUX_EXPORT int gpuxSumInt32NoAlloc(void *queue, const int32_t *data, size_t n, 
   }
   nmb::noteLaunch();
   return 0;
+}
+
+// Reports whether every gpuxSumInt32NoAlloc call issued so far on the queue's
+// device ran to completion: 0 = yes; 1 = a bounded wait inside a call ran out
+// (that call left *out untouched); -1 = a CUDA error (gpuxGetLastError).
+// Waits for the queue's stream, reads the word with a 4-byte copy into a
+// variable of its own and, when the word was set, clears it.  No allocation.
+GPUX_EXPORT int gpuxSumInt32NoAllocStatus(void *queue) {
+  if (!queue) {
+    nmb::setError("gpuxSumInt32NoAllocStatus: null queue");
+    return -1;
+  }
+  nmb::QueueView qv;
+  if (!nmb::queueView(queue, &qv))
+    return -1;
+  cudaStream_t stream = static_cast<cudaStream_t>(qv.stream);
+  DeviceSetup *dev = nullptr;
+  if (!setupDevice(qv.device, &dev))
+    return -1;
+  uint32_t word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, dev->scratch + kStatusOffset, sizeof(word),
+                                  cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess)
+    e = cudaStreamSynchronize(stream);
+  if (e == cudaSuccess && word != 0)
+    e = cudaMemsetAsync(dev->scratch + kStatusOffset, 0, sizeof(word), stream);
+  if (e != cudaSuccess) {
+    nmb::setError("gpuxSumInt32NoAllocStatus failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return -1;
+  }
+  return (int)word;
 }

@@ -111,9 +111,9 @@ class Dispatcher:
             return self._call_parfor(args)
         key = lazy.signature_of(args)
         plan = self._plans.get(key) if key is not None else None
-        if plan is not None:
-            return plan.replay(args)
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
+        if plan is not None:
+            return plan.replay(args, queue)
         result, plan = lazy.trace_call(self.py_func, args, queue,
                                         fastmath=bool(self.options.get("fastmath", False)))
         if plan is not None and key is not None:

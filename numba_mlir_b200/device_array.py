@@ -71,6 +71,7 @@ class DeviceArray:
         self._contig = None if strides is not None else True
         self._call_sig = None
         self._trace_sig = None
+        self._extent = None
 
     # -- basic properties ------------------------------------------------------
     @property
@@ -114,6 +115,22 @@ class DeviceArray:
             sig = self._trace_sig = ("arr", self.dtype.name, self.shape, self.strides, self.ptr % 16 == 0,
                                      getattr(self.queue, "device", None))
         return sig
+
+    @property
+    def extent(self):
+        """Byte range (lo, hi) of device addresses the view can touch."""
+        ext = self._extent
+        if ext is None:
+            lo = hi = self.ptr
+            if self.size:
+                for n, st in zip(self.shape, self.strides):
+                    if st >= 0:
+                        hi += (n - 1) * st
+                    else:
+                        lo += (n - 1) * st
+                hi += self.dtype.itemsize
+            ext = self._extent = (lo, hi)
+        return ext
 
     @property
     def call_sig(self):
@@ -248,7 +265,7 @@ class DeviceArray:
         else:
             from . import lazy
 
-            lazy.assign(out, lazy.LazyArray.leaf(self))
+            lazy.assign(out, self)
         return out
 
     def __array__(self, dtype=None, copy=None):

@@ -22,8 +22,10 @@ context in which the reference caches queue/module/kernel handles
 (numba_mlir/mlir_compiler/lib/pipelines/LowerToGpu.cpp:742-940).
 """
 
+import itertools
 import struct
 import threading
+import weakref
 
 import numpy as np
 
@@ -190,7 +192,7 @@ class Node:
     argument, a kernel parameter), 'const' (literal), 'op' (ufunc), 'cast',
     'where', 'call' (user scalar device function)."""
 
-    __slots__ = ("kind", "dtype", "shape", "inputs", "op", "value", "slot", "sig")
+    __slots__ = ("kind", "dtype", "shape", "inputs", "op", "value", "slot", "sig", "reads")
 
     def __init__(self, kind, dtype, shape, inputs=(), op=None, value=None, slot=None):
         self.kind = kind
@@ -201,6 +203,26 @@ class Node:
         self.value = value
         self.slot = slot
         self.sig = None
+        self.reads = None
+
+
+def node_reads(node):
+    """Slots of the device arrays an expression reads."""
+    r = node.reads
+    if r is None:
+        if node.kind == "leaf":
+            r = frozenset((node.slot,))
+        elif node.inputs:
+            r = frozenset().union(*[node_reads(i) for i in node.inputs])
+        else:
+            r = frozenset()
+        node.reads = r
+    return r
+
+
+def _extent(arr):
+    """Byte range [lo, hi) that a strided view can touch."""
+    return arr.extent
 
 
 def broadcast_shapes(*shapes):
@@ -233,6 +255,74 @@ class Trace:
         self.steps = []
         self.value_dependent = False
         self.args = args
+        self.live = []           # weak references to the unevaluated expressions
+        self._extents = {}
+
+    # aliasing --------------------------------------------------------------------
+    # Expressions are evaluated late (at the next flush), stores are queued: the
+    # order of reads and writes the program wrote is kept by three rules.  (1) An
+    # expression that reads memory a queued store will write is built only after
+    # that store has been emitted.  (2) Before a store is queued, every unevaluated
+    # expression still reachable from the program that reads the store's memory is
+    # given a temporary of its own, evaluated no later than the store.  (3) Within
+    # one fused kernel an output may share memory with an input only element for
+    # element (each thread reads its elements before it writes them); anything
+    # else is split over consecutive kernels, through a temporary where a store's
+    # own value reads other elements of its target (NumPy copies on overlap).
+    def overlap(self, s1, s2):
+        """0: the two arrays share no memory; 1: they are the same elements in
+        the same order; 2: they overlap in some other way."""
+        if s1 == s2:
+            return 1
+        a, b = self.arrays[s1], self.arrays[s2]
+        ea, eb = self._extents.get(s1), self._extents.get(s2)
+        if ea is None:
+            ea = self._extents[s1] = _extent(a)
+        if eb is None:
+            eb = self._extents[s2] = _extent(b)
+        if ea[0] >= eb[1] or eb[0] >= ea[1]:
+            return 0
+        if a.ptr == b.ptr and a.shape == b.shape and a.strides == b.strides and a.dtype == b.dtype:
+            return 1
+        return 2
+
+    def pending_touches(self, slot, reads_too=False):
+        """A queued store writes (or, with `reads_too`, its value reads) memory of `slot`."""
+        for s, node in self.pending:
+            if self.overlap(s, slot):
+                return True
+            if reads_too and any(self.overlap(r, slot) for r in node_reads(node)):
+                return True
+        return False
+
+    def detach_readers(self, slot, value=None):
+        """Rule (2): expressions that read the memory of `slot` and can still be
+        used later get their values stored into temporaries, queued before
+        whatever writes `slot` next.  `value` is the expression being stored
+        into `slot` itself."""
+        if not self.live:
+            return
+        alive = []
+        for ref in self.live:
+            lz = ref()
+            if lz is None or lz.node.kind == "leaf":
+                continue
+            alive.append(ref)
+            if lz is value:
+                continue
+            if any(self.overlap(r, slot) for r in node_reads(lz.node)):
+                tmp = self.add_tmp_slot(lz.node.shape, lz.node.dtype)
+                self.pending.append((tmp, lz.node))
+                lz.node = Node("leaf", lz.node.dtype, lz.node.shape, slot=tmp)
+        self.live = alive
+
+    def before_direct_write(self, slot):
+        """A step that writes `slot` as soon as it is recorded (a reduction or a
+        contraction into an existing array) comes after everything queued that
+        reads or writes that memory."""
+        self.detach_readers(slot)
+        if self.pending_touches(slot, reads_too=True):
+            self.flush()
 
     # slots ---------------------------------------------------------------------
     # slot -> ("arg", index) | ("tmp", shape, dtype) | ("view", base slot, op)
@@ -262,20 +352,47 @@ class Trace:
         return LazyArray(self, Node("leaf", arr.dtype, arr.shape, slot=slot))
 
     def has_pending(self, slot):
-        return any(s == slot for s, _ in self.pending)
+        return any(self.overlap(s, slot) for s, _ in self.pending)
 
     # stores ----------------------------------------------------------------------
-    def store(self, target_slot, node):
+    def store(self, target_slot, node, value=None):
+        self.detach_readers(target_slot, value)
         self.pending.append((target_slot, node))
 
     def flush(self):
-        """Emits the pending stores, one fused kernel per output shape."""
-        pending, self.pending = self.pending, []
-        groups = {}
-        for slot, node in pending:
-            groups.setdefault(self.arrays[slot].shape, []).append((slot, node))
-        for shape, outs in groups.items():
-            _emit_eltwise(self, shape, outs)
+        """Emits the pending stores in order: one fused kernel per output shape
+        for every run of stores that rule (3) allows in one kernel."""
+        queue, self.pending = self.pending, []
+        batch, reads, writes = [], set(), set()
+
+        def emit():
+            groups = {}
+            for slot, node in batch:
+                groups.setdefault(self.arrays[slot].shape, []).append((slot, node))
+            for shape, outs in groups.items():
+                _emit_eltwise(self, shape, outs)
+            batch.clear()
+            reads.clear()
+            writes.clear()
+
+        i = 0
+        while i < len(queue):
+            slot, node = queue[i]
+            i += 1
+            nreads = node_reads(node)
+            if any(self.overlap(r, slot) == 2 for r in nreads):
+                # the value reads other elements of the target than it writes
+                tmp = self.add_tmp_slot(node.shape, node.dtype)
+                queue.insert(i, (slot, Node("leaf", node.dtype, node.shape, slot=tmp)))
+                slot = tmp
+            if batch and (any(self.overlap(r, slot) == 2 for r in reads)
+                          or any(self.overlap(w, slot) == 2 for w in writes)
+                          or any(self.overlap(r, w) for r in nreads for w in writes)):
+                emit()
+            batch.append((slot, node))
+            reads |= nreads
+            writes.add(slot)
+        emit()
 
     def materialize(self, lazy):
         """Device array (slot) holding the value of `lazy`."""
@@ -313,7 +430,7 @@ class _TraceScope:
 def _as_node(trace, x):
     if isinstance(x, LazyArray):
         if x.node.kind == "leaf" and trace.pending and trace.has_pending(x.node.slot):
-            trace.flush()  # the array is read after a recorded store to it
+            trace.flush()  # the array is read after a recorded store to its memory
         return x.node
     if isinstance(x, DeviceArray):
         slot = trace.add_arg_slot(None, x)
@@ -343,6 +460,8 @@ class LazyArray:
         self.trace = trace
         self.node = node
         self.concrete = concrete  # value of scalar arguments, for control flow
+        if node.kind not in ("leaf", "arg", "const") and node_reads(node):
+            trace.live.append(weakref.ref(self))  # an unevaluated expression over device memory
 
     # metadata ------------------------------------------------------------------
     @property
@@ -567,7 +686,7 @@ class LazyArray:
             raise ValueError(f"could not broadcast {vnode.shape} into {target.shape}")
         if vnode.dtype != target.dtype:
             vnode = Node("cast", target.dtype, vnode.shape, (vnode,))
-        self.trace.store(target.node.slot, vnode)
+        self.trace.store(target.node.slot, vnode, value if isinstance(value, LazyArray) else None)
 
 
 def _retarget_producer(trace, target, value):
@@ -582,8 +701,18 @@ def _retarget_producer(trace, target, value):
         return False
     dst_arr, tmp_arr = trace.arrays[target.node.slot], trace.arrays[tmp]
     if (dst_arr.shape != tmp_arr.shape or dst_arr.dtype != tmp_arr.dtype
-            or not dst_arr.is_c_contiguous or trace.has_pending(target.node.slot)):
+            or not dst_arr.is_c_contiguous or trace.pending_touches(target.node.slot, reads_too=True)):
         return False
+    # the step would write the target at once: not when its own operands, or an
+    # expression that is still to be evaluated, read that memory
+    operands = (step[3],) if step[0] == "reduce" else step[1:3]
+    if any(trace.overlap(s, target.node.slot) for s in operands):
+        return False
+    for ref in trace.live:
+        lz = ref()
+        if lz is not None and lz.node.kind != "leaf" and any(
+                trace.overlap(r, target.node.slot) for r in node_reads(lz.node)):
+            return False
     new_step = step[:-1] + (target.node.slot,)
     trace.steps[-2:] = [new_step]
     if not trace.dry:
@@ -787,6 +916,7 @@ def dot(trace, a, b, out=None):
         dst = trace.add_tmp_slot((A.shape[0], B.shape[1]), np.result_type(A.dtype, B.dtype))
     else:
         dst = trace.materialize(out)
+        trace.before_direct_write(dst)
     trace.steps.append(("dot", sa, sb, dst))
     if not trace.dry:
         contraction.gemm(A, B, trace.arrays[dst])
@@ -923,14 +1053,21 @@ def _emit_eltwise(trace, out_shape, outs):
     n_streams = sum(1 for _s, k, _p, _d in em.leaves if k == "full") + len(results)
     unroll = 4 if n_streams <= 3 else 2
 
+    # inputs that are also written by this kernel (element for element, rule (3)
+    # of Trace): their pointers are not `__restrict__` and their loads do not
+    # take the read-only path
+    shared_in = frozenset(i for i, (slot, _k, _p, _d) in enumerate(em.leaves)
+                          if any(trace.overlap(slot, o) for o, _e, _a in results))
+    shared_out = frozenset(j for j, (o, _e, _a) in enumerate(results)
+                           if any(trace.overlap(slot, o) for slot, _k, _p, _d in em.leaves))
     shaped = any(k == "strided" for _s, k, _p, _d in em.leaves) or any(st is not None for st in ostrides)
-    sig = (tuple(out_shape) if shaped else len(out_shape),
+    sig = (tuple(out_shape) if shaped else len(out_shape), shared_in, shared_out,
            tuple((k, p if k == "strided" else (), d.name) for _s, k, p, d in em.leaves),
            tuple(em.sig), tuple((e, a.dtype.name, st) for (_s, e, a), st in zip(results, ostrides)), vec, unroll,
            trace.fastmath)
     hit = _kernel_cache.get(sig)
     if hit is None:
-        hit = _generate(em, results, out_shape, vec, unroll, ostrides, trace.fastmath)
+        hit = _generate(em, results, out_shape, vec, unroll, ostrides, trace.fastmath, shared_in, shared_out)
         _kernel_cache[sig] = hit
     blob, kname = hit
 
@@ -951,21 +1088,24 @@ def _emit_eltwise(trace, out_shape, outs):
         run_launch(trace.queue, step, trace.arrays, trace.args)
 
 
-def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False):
+def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, shared_in=frozenset(),
+              shared_out=frozenset()):
     """CUDA C for one fused chain; returns (tagged source blob, kernel name)."""
     members, ctor, kparams = [], [], []
     in_fields, loads = [], []
     nd = len(out_shape)
     for i, (slot, kind, p, dt) in enumerate(em.leaves):
         ct = ctype(dt)
-        members.append(f"const {ct}* __restrict__ in{i};")
-        kparams.append(f"const {ct}* __restrict__ in{i}")
+        restrict = "" if i in shared_in else " __restrict__"
+        ldg = "*" if i in shared_in else "__ldg"
+        members.append(f"const {ct}*{restrict} in{i};")
+        kparams.append(f"const {ct}*{restrict} in{i}")
         ctor.append(f"in{i}")
         in_fields.append(f"nmb::Vec<{ct}, V> in{i};")
         if kind == "full":
             loads.append(f"r.in{i} = nmb::load_stream<{ct}, V>(in{i} + i);")
         elif kind == "splat":
-            loads.append(f"{{ const {ct} x = __ldg(in{i}); for (int l = 0; l < V; ++l) r.in{i}.v[l] = x; }}")
+            loads.append(f"{{ const {ct} x = {ldg}(in{i}); for (int l = 0; l < V; ++l) r.in{i}.v[l] = x; }}")
         elif kind == "row":
             members.append(f"int64_t m{i};")
             kparams.append(f"int64_t m{i}")
@@ -984,7 +1124,7 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False):
                     body.append(f"q = rem % {out_shape[d]}ll; off += q * ({p[d]}ll); rem /= {out_shape[d]}ll;")
                 else:
                     body.append(f"rem /= {out_shape[d]}ll;")
-            body.append(f"r.in{i}.v[l] = __ldg(in{i} + off); }}")
+            body.append(f"r.in{i}.v[l] = {ldg}(in{i} + off); }}")
             loads.append(" ".join(body))
     for j, (index, dt) in enumerate(em.scalar_args):
         members.append(f"{ctype(dt)} s{j};")
@@ -993,8 +1133,9 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False):
     out_fields, stores, out_assign = [], [], []
     for j, (slot, expr, arr) in enumerate(results):
         ct = ctype(arr.dtype)
-        members.append(f"{ct}* __restrict__ out{j};")
-        kparams.append(f"{ct}* __restrict__ out{j}")
+        restrict = "" if j in shared_out else " __restrict__"
+        members.append(f"{ct}*{restrict} out{j};")
+        kparams.append(f"{ct}*{restrict} out{j}")
         ctor.append(f"out{j}")
         out_fields.append(f"nmb::Vec<{ct}, V> out{j};")
         out_assign.append(f"o.out{j}.v[l] = {expr};")
@@ -1078,7 +1219,10 @@ class Plan:
         self.result_spec = result_spec
         self.queue = trace.queue
 
-    def replay(self, args):
+    def replay(self, args, queue=None):
+        """Runs the recorded steps on `args`; allocations and launches go to
+        `queue` (the queue of the call's arguments), the recording queue by
+        default."""
         from . import contraction, reduce_ops
 
         slots = self.slots
@@ -1098,7 +1242,7 @@ class Plan:
                 arrays[i] = arr
             return arr
 
-        q = self.queue
+        q = queue if queue is not None else self.queue
         for step in self.steps:
             tag = step[0]
             if tag == "alloc":
@@ -1139,23 +1283,41 @@ def _build_result(spec, arrays):
 
 
 def signature_of(args):
+    """Cache key of a recorded plan: per-argument layout plus, when array
+    arguments share memory, how they overlap (the order of the recorded
+    kernels depends on it)."""
     sig = []
-    for a in args:
+    extents = []
+    for i, a in enumerate(args):
         if isinstance(a, DeviceArray):
             sig.append(a.trace_sig)
+            extents.append(a.extent + (i,))
         elif isinstance(a, (bool, int, float, np.generic)):
             sig.append(("scalar", scalar_dtype(a).name))
         else:
             return None
+    if len(extents) > 1:
+        extents.sort()
+        for k in range(len(extents) - 1):
+            j = k + 1
+            while j < len(extents) and extents[j][0] < extents[k][1]:
+                sig.append(("alias", extents[k][2], extents[j][2], extents[j][0] - extents[k][0]))
+                j += 1
     return tuple(sig)
 
 
-def fake_array(shape, dtype, ptr=0x7F0000000000):
-    """Array descriptor without memory, for code generation without a device."""
+_fake_addresses = itertools.count(0x7F0000000000, 1 << 36)
+
+
+def fake_array(shape, dtype, ptr=None):
+    """Array descriptor without memory, for code generation without a device;
+    every one gets an address range of its own."""
     from .device_array import _Foreign
 
     dtype = np.dtype(dtype)
     n = int(np.prod(shape, dtype=np.int64))
+    if ptr is None:
+        ptr = next(_fake_addresses)
     return DeviceArray(_Foreign(None, ptr, n * dtype.itemsize, None), shape, dtype)
 
 

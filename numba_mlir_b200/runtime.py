@@ -98,6 +98,7 @@ SIGNATURES = {
     "gpuxFreeHostBlob": (None, [_vp]),
     "gpuxBuiltinKernelNames": (_cp, []),
     "gpuxSumInt32NoAlloc": (_i, [_vp, _vp, _sz, _vp]),
+    "gpuxSumInt32NoAllocStatus": (_i, [_vp]),
     "_mlir_ciface_nmb_pairwise_distance_float32_device": (
         _vp,
         [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f)],

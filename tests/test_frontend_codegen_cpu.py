@@ -107,3 +107,82 @@ def test_large_local_arrays_move_to_the_local_memory_parameter(runtime_lib):
     assert ck.local_bytes == 80000 + 16 and "unsigned long long nmb_local_off" in ck.source
     assert ck.kinds(3)[-1] == ("local", 80016)
     assert len(runtime.compile_to_cubin(ck.source.encode())) > 0
+
+
+# ---------------------------------------------------- ordering of reads/writes ---
+def _dry(py_func, arrays):
+    import numba_mlir_b200 as nm
+
+    trace, _plan = nm.njit(py_func).trace_dry(*arrays)
+    return trace
+
+
+def test_store_after_an_unevaluated_read_keeps_the_old_values():
+    """`b = a + 1; a[:] = 0; a.sum(); o[:] = b`: b is evaluated from the
+    values a had when b was written down, not from the zeros."""
+    from numba_mlir_b200 import lazy
+
+    def g(a, o):
+        b = a + np.float32(1)
+        a[:] = np.float32(0)
+        s = a.sum()
+        o[:] = b
+        return s
+
+    a, o = lazy.fake_array((64,), np.float32), lazy.fake_array((64,), np.float32)
+    trace = _dry(g, [a, o])
+    launches = [s for s in trace.steps if s[0] == "launch"]
+    # first launch: the temporary for b (reads a) together with the zeroing of a
+    first = [p[1] for p in launches[0][5] if p[0] == "slot"]
+    assert 0 in first and any(trace.slots[s][0] == "tmp" for s in first)
+    # the launch that writes o reads that temporary, not a
+    last = [p[1] for p in launches[-1][5] if p[0] == "slot"]
+    assert 1 in last and 0 not in last
+    assert any(trace.slots[s][0] == "tmp" for s in last)
+
+
+def test_shifted_self_assignment_goes_through_a_temporary():
+    """`a[1:] = a[:-1]`: two kernels (NumPy copies on overlap), never one
+    kernel reading and writing shifted views of one buffer."""
+
+    from numba_mlir_b200 import lazy
+
+    def shift(a):
+        a[1:] = a[:-1]
+
+    def rev(a):
+        b = a[::-1] + np.float32(1)
+        a[:] = np.float32(0)
+        return b
+
+    for fn in (shift, rev):
+        trace = _dry(fn, [lazy.fake_array((64,), np.float32)])
+        launches = [s for s in trace.steps if s[0] == "launch"]
+        assert len(launches) == 2, fn.__name__
+        for step in launches:
+            slots = [p[1] for p in step[5] if p[0] == "slot"]
+            for x in slots:
+                for y in slots:
+                    assert trace.overlap(x, y) != 2
+
+
+def test_in_place_update_stays_one_kernel_without_restrict():
+    from numba_mlir_b200 import lazy
+
+    def f(a, b):
+        a[:] = a * np.float32(2) + b
+
+    trace = _dry(f, [lazy.fake_array((256,), np.float32), lazy.fake_array((256,), np.float32)])
+    (step,) = [s for s in trace.steps if s[0] == "launch"]
+    src = bytes(step[1]).decode()
+    assert "const float* in0," in src and "float* out0," in src  # a: read and written
+    assert "const float* __restrict__ in1" in src
+
+
+def test_plan_key_sees_overlapping_arguments():
+    from numba_mlir_b200 import lazy
+
+    a = lazy.fake_array((64,), np.float32)
+    b = lazy.fake_array((64,), np.float32)
+    assert lazy.signature_of((a, b)) != lazy.signature_of((a, a))
+    assert lazy.signature_of((a[1:], a[:-1])) != lazy.signature_of((a[1:], b[:-1]))

@@ -363,3 +363,142 @@ def test_value_dependent_control_flow_still_works(queue):
     a = np.arange(10, dtype=np.float32)
     assert np.array_equal(f(_dev(a), 1).copy_to_host(), a + 1)
     assert np.array_equal(f(_dev(a), -1).copy_to_host(), a - 1)
+
+
+# --------------------------------------------- order of reads and writes ------
+def test_store_after_an_unevaluated_read_keeps_the_old_values(queue):
+    """NumPy semantics when an array is overwritten while an expression that
+    reads it has not been evaluated yet (first call and plan replay)."""
+    import numba_mlir_b200 as nm
+
+    @nm.njit
+    def g(a, o):
+        b = a + np.float32(1)
+        a[:] = np.float32(0)
+        s = a.sum()
+        o[:] = b
+        return s
+
+    for _ in range(2):
+        a = np.arange(1000, dtype=np.float32)
+        da, do = _dev(a), _dev(np.zeros_like(a))
+        s = g(da, do)
+        assert float(s.copy_to_host()) == 0.0
+        assert np.array_equal(do.copy_to_host(), a + 1)
+        assert not da.copy_to_host().any()
+
+
+def test_overlapping_self_assignment_copies_like_numpy(queue):
+    import numba_mlir_b200 as nm
+
+    @nm.njit
+    def shift(a):
+        a[1:] = a[:-1]
+
+    @nm.njit
+    def rev(a):
+        b = a[::-1] + np.float32(1)
+        a[:] = np.float32(0)
+        return b
+
+    @nm.njit
+    def flip_in_place(a):
+        a[:] = a[::-1]
+
+    @nm.njit
+    def rows_down(m):
+        m[1:, :] = m[:-1, :] * np.float32(2)
+
+    for n in (5, 1000, 100003):
+        a = np.arange(n, dtype=np.float32)
+        da = _dev(a)
+        shift(da)
+        want = a.copy()
+        want[1:] = a[:-1]
+        assert np.array_equal(da.copy_to_host(), want)
+        da = _dev(a)
+        assert np.array_equal(rev(da).copy_to_host(), a[::-1] + 1)
+        assert not da.copy_to_host().any()
+        da = _dev(a)
+        flip_in_place(da)
+        assert np.array_equal(da.copy_to_host(), a[::-1])
+    m = np.arange(37 * 64, dtype=np.float32).reshape(37, 64)
+    dm = _dev(m)
+    rows_down(dm)
+    want = m.copy()
+    want[1:, :] = m[:-1, :] * 2
+    assert np.array_equal(dm.copy_to_host(), want)
+
+
+def test_arguments_that_share_memory_get_their_own_plan(queue):
+    """The same function called with disjoint and with overlapping views: the
+    recorded plan of the first must not be replayed for the second."""
+    import numba_mlir_b200 as nm
+
+    @nm.njit
+    def copy_to(dst, src):
+        dst[:] = src + np.float32(1)
+
+    a = np.arange(4096, dtype=np.float32)
+    d1, d2 = _dev(a), _dev(a)
+    copy_to(d1[1:], d2[:-1])
+    want = a.copy()
+    want[1:] = a[:-1] + 1
+    assert np.array_equal(d1.copy_to_host(), want)
+    d3 = _dev(a)
+    copy_to(d3[1:], d3[:-1])
+    assert np.array_equal(d3.copy_to_host(), want)
+    assert len(copy_to._plans) == 2
+
+
+def test_reduction_into_an_array_an_expression_still_reads(queue):
+    import numba_mlir_b200 as nm
+
+    @nm.njit
+    def f(a, out, c):
+        c[:] = out + np.float32(1)
+        out[:] = np.sum(a, axis=1)
+
+    rng = np.random.default_rng(9)
+    a = rng.integers(-4, 5, (64, 128)).astype(np.float32)
+    o = rng.integers(-4, 5, 64).astype(np.float32)
+    for _ in range(2):
+        do, dc = _dev(o), _dev(np.zeros_like(o))
+        f(_dev(a), do, dc)
+        assert np.array_equal(dc.copy_to_host(), o + 1)
+        assert np.array_equal(do.copy_to_host(), a.sum(axis=1))
+
+
+def test_plan_replays_on_the_queue_of_its_arguments(queue):
+    """One njit function called with arrays of two queues of one device: the
+    second call's kernels run on the second queue (its events order them)."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import runtime
+
+    @nm.njit
+    def axpy(x, y, out):
+        out[:] = x * np.float32(3) + y
+
+    q2 = runtime.Queue(f"cuda:{queue.device}")
+    rng = np.random.default_rng(10)
+    x = rng.standard_normal(1 << 20).astype(np.float32)
+    y = rng.standard_normal(1 << 20).astype(np.float32)
+    out1 = nm.empty(x.size, np.float32, queue)
+    axpy(nm.from_host(x, queue), nm.from_host(y, queue), out1)
+    before = runtime.launch_count()
+    out2 = nm.empty(x.size, np.float32, q2)
+    axpy(nm.from_host(x, q2), nm.from_host(y, q2), out2)
+    assert len(axpy._plans) == 1 and runtime.launch_count() == before + 1
+    # synchronising the second queue alone is enough to read its result
+    q2.synchronize()
+    host = np.empty_like(x)
+    q2.memcpy(host.ctypes.data, out2.ptr, host.nbytes, runtime.COPY_D2H, wait=True)
+    assert np.array_equal(host, x * np.float32(3) + y)
+    assert np.array_equal(out1.copy_to_host(), host)
+
+
+def test_noncontiguous_device_copy(queue):
+    a = np.arange(48, dtype=np.float32).reshape(6, 8)
+    d = _dev(a)
+    assert np.array_equal(d.T.copy().copy_to_host(), a.T)
+    assert np.array_equal(d[::2, 1::3].copy_to_host(), a[::2, 1::3])

@@ -1,8 +1,8 @@
 """gpuxSumInt32NoAlloc: the entry point for callers that cannot allocate.
 
-Some callers of the runtime must not trigger a device allocation: a host
-callback running inside a stream, a monitoring thread that may not block on the
-CUDA allocator, a process whose memory was all handed out at start-up.  This
+Some callers of the runtime must not trigger a device allocation: a monitoring
+or real-time thread that may not wait on the CUDA allocator, a process whose
+device memory was all handed out at start-up.  This
 entry point keeps its scratch in a fixed array inside the library, so it can
 be called from there.  It is checked here through the C-ABI against the
 regular full-sum path (per-queue scratch), bit-exactly (integer sums), on two
@@ -40,6 +40,8 @@ def test_no_alloc_sum_matches_regular_entry_point_twice(queue, runtime_lib):
         queue.synchronize()
         got, want = int(out_a.copy_to_host()), int(out_b.copy_to_host())
         assert got == want == int(host.sum(dtype=np.int64))
+        # the entry point's own failure report: no bounded wait ran out
+        assert runtime_lib.gpuxSumInt32NoAllocStatus(queue.handle) == 0
     queue.check_status()
 
 
