@@ -222,6 +222,31 @@ void *_mlir_ciface_nmb_pairwise_distance_float32_device(void *queue,
                                                         const GPUXMemref2f *y,
                                                         GPUXMemref2f *d);
 
+/* The product of mkl_gemm_float32_device without its host-side wait
+ * (NumpyLinalg.cpp:143-146 waits on the oneMKL event): asynchronous on the
+ * queue's stream, so a step that contains it can be recorded with
+ * gpuxGraphBegin/End; returns an event. */
+void *_mlir_ciface_nmb_gemm_float32_device_async(void *queue, const GPUXMemref2f *a,
+                                                 const GPUXMemref2f *b, float alpha,
+                                                 float beta, GPUXMemref2f *c);
+
+/* The contraction with the elementwise chain around the product fused as its
+ * epilogue, what the reference gets by fusing the linalg.generic ops around a
+ * device library call (external_call + "gpu_runtime.device_func",
+ * mlir/numpy/funcs.py:780-785):
+ *   d[i,j] = func(alpha * sum_k x[i,k] y[j,k] + row[i] + col[j])
+ * x: (M,K), y: (N,K), d: (M,N) row-major float32.  rowKind / colKind: 0 no
+ * term, 1 the squared norms of the operand's rows (taken from the packing
+ * prepass; rowv / colv ignored), 2 a contiguous float32 device vector of M
+ * (rowv) or N (colv) values.  func: 0 identity, 1 sqrt(max(., 0)).  The
+ * pairwise distance above is alpha = -2, both kinds 1, func 1.  Asynchronous
+ * on the queue's stream; returns an event. */
+void *_mlir_ciface_nmb_contract_rowcol_float32_device(void *queue, const GPUXMemref2f *x,
+                                                      const GPUXMemref2f *y, float alpha,
+                                                      int rowKind, const float *rowv,
+                                                      int colKind, const float *colv, int func,
+                                                      GPUXMemref2f *d);
+
 /* No counterpart in the reference.  *out = sum of data[0..n) accumulated in
  * int64, like the full integer reduction above, for callers that must not
  * allocate: a thread that may not wait on the CUDA allocator (a monitor or a

@@ -30,15 +30,60 @@ def _memref(a):
     return m
 
 
-def gemm(a, b, c, alpha=1.0, beta=0.0):
-    """c = alpha * a @ b + beta * c (blocking, like the reference's call)."""
+def gemm(a, b, c, alpha=1.0, beta=0.0, blocking=True):
+    """c = alpha * a @ b + beta * c.  Blocking like the reference's call by
+    default; `blocking=False` only enqueues it on the queue's stream."""
     lib = _rt.load()
     ma, mb, mc = _memref(a), _memref(b), _memref(c)
-    lib._mlir_ciface_mkl_gemm_float32_device(c.queue.handle, ctypes.byref(ma), ctypes.byref(mb),
-                                             ctypes.c_float(alpha), ctypes.c_float(beta),
-                                             ctypes.byref(mc))
-    _rt.check()
+    if blocking:
+        lib._mlir_ciface_mkl_gemm_float32_device(c.queue.handle, ctypes.byref(ma), ctypes.byref(mb),
+                                                 ctypes.c_float(alpha), ctypes.c_float(beta),
+                                                 ctypes.byref(mc))
+        _rt.check()
+        return c
+    ev = lib._mlir_ciface_nmb_gemm_float32_device_async(c.queue.handle, ctypes.byref(ma), ctypes.byref(mb),
+                                                        ctypes.c_float(alpha), ctypes.c_float(beta),
+                                                        ctypes.byref(mc))
+    if not ev:
+        _rt.check()
+        raise _rt.GpuRuntimeError("gemm launch failed")
+    lib.gpuxDestroyEvent(c.queue.handle, ev)
     return c
+
+
+TERM_NONE, TERM_NORMS, TERM_VECTOR = 0, 1, 2
+FUNC_IDENTITY, FUNC_SQRT_MAX0 = 0, 1
+
+
+def contract_rowcol(x, y, out, alpha=1.0, row=None, col=None, func=FUNC_IDENTITY):
+    """out[i, j] = func(alpha * x[i] . y[j] + row[i] + col[j]) for float32
+    x (M, K), y (N, K): the contraction with its surrounding elementwise chain
+    as the epilogue.  `row` / `col`: None, the string "norms" (squared norms of
+    the operand's rows, from the packing prepass) or a contiguous float32
+    device vector."""
+    def term(t, n):
+        if t is None:
+            return TERM_NONE, None
+        if isinstance(t, str):
+            if t != "norms":
+                raise ValueError("a term is None, 'norms' or a device vector")
+            return TERM_NORMS, None
+        if t.dtype != np.float32 or t.size != n or not t.is_c_contiguous:
+            raise ValueError("a row/column term must be a contiguous float32 vector of matching length")
+        return TERM_VECTOR, t.ptr
+
+    rk, rp = term(row, x.shape[0])
+    ck, cp = term(col, y.shape[0])
+    lib = _rt.load()
+    mx, my, mo = _memref(x), _memref(y), _memref(out)
+    ev = lib._mlir_ciface_nmb_contract_rowcol_float32_device(
+        out.queue.handle, ctypes.byref(mx), ctypes.byref(my), ctypes.c_float(alpha), rk, rp, ck, cp, func,
+        ctypes.byref(mo))
+    if not ev:
+        _rt.check()
+        raise _rt.GpuRuntimeError("contraction launch failed")
+    lib.gpuxDestroyEvent(out.queue.handle, ev)
+    return out
 
 
 def pairwise_distance(x, y, out=None):

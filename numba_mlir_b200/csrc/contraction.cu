@@ -17,18 +17,18 @@
 //               core matrices), zero padded, plus the fp32 row norms.  A
 //               whole tile (hi+lo) is then one contiguous TMA bulk copy.
 //   contract  : persistent, warp-specialised: warp 0 streams packed tiles in
-//               with TMA bulk copies (A resident per row tile, B double
-//               buffered), warp 1 issues tcgen05.mma (24 MMAs of 128x128x8
-//               per output tile at K = 64, one elected lane of a converged
-//               warp) into one of four TMEM accumulators (4 x 128 columns =
-//               all of TMEM), warps 2-17 drain TMEM with tcgen05.ld in
-//               32 x 32 pieces, apply the epilogue and hand each piece, 8 rows
-//               at a time, to asynchronous TMA tensor stores out of private
-//               swizzled staging buffers.  The op is store bound (1 GiB out
-//               vs 8 MiB in at 16384^2 x 64); the 3xTF32 MMA work (about
-//               0.8 us per tile) runs under the store stream.
-//   finish    : sqrt epilogue for K > 64, where the dot products are
-//               accumulated over K blocks in gemm mode first.
+//               with TMA bulk copies (A resident per row tile, B in four
+//               K-half slots of 32 KB), warp 1 issues tcgen05.mma (24 MMAs of
+//               128x128x8 per output tile at K = 64, one elected lane of a
+//               converged warp) into one of four TMEM accumulators (4 x 128
+//               columns = all of TMEM), warps 2-9 drain TMEM with tcgen05.ld
+//               in 32 x 32 pieces, apply the epilogue and hand each piece to
+//               one asynchronous TMA tensor store out of a private swizzled
+//               staging buffer.  The op is store bound (1 GiB out vs 8 MiB in
+//               at 16384^2 x 64); the 3xTF32 MMA work (about 0.8 us per tile)
+//               runs under the store stream.
+//   finish    : the row/column-term epilogue for K > 64, where the dot
+//               products are accumulated over K blocks in gemm mode first.
 //
 // Every wait on an mbarrier is bounded; on a timeout the kernel flags the
 // queue's status word, stops, pauses for copies in flight, frees TMEM, returns.
@@ -295,12 +295,13 @@ __device__ __forceinline__ float sqrt_approx(float x) {
 struct ContractParams {
   const unsigned char *packedA; // [tiles_m][hi | lo]
   const unsigned char *packedB; // [tiles_n][hi | lo]
-  const float *normA;           // pairwise: |x_i|^2, padded to tiles_m * 128
-  const float *normB;           // pairwise: |y_j|^2, padded to tiles_n * 128
+  const float *normA;           // mode 0: the row term (|x_i|^2 for distances), padded to tiles_m * 128
+  const float *normB;           // mode 0: the column term (|y_j|^2), padded to tiles_n * 128
   float *out;                   // (M, N), row stride ldo elements
   int64_t M, N, ldo;
   int kpad;
-  int mode;                     // 0: pairwise distance, 1: gemm (alpha, beta)
+  int mode;                     // 0: func(alpha * acc + normA[i] + normB[j]), 1: gemm (alpha, beta)
+  int func;                     // mode 0: 0 = identity, 1 = sqrt(max(., 0))
   float alpha, beta;
   uint32_t *status;
   int tma_out;                  // 1: out_map is valid, results leave through TMA stores
@@ -569,13 +570,25 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         if (p.mode == 0) {
           // |y_j|^2 of the piece's 32 columns: broadcast reads of the ring slot
           const float4 *y = reinterpret_cast<const float4 *>(smNorm + r * kNormSlotBytes) + half * 16 + pc * 8;
+          const float al = p.alpha;
+          if (p.func == 1) {
 #pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4) {
-            const float4 yv = y[e4];
-            w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 0], xa + yv.x), 0.f));
-            w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 1], xa + yv.y), 0.f));
-            w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 2], xa + yv.z), 0.f));
-            w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(-2.f, w[e4 * 4 + 3], xa + yv.w), 0.f));
+            for (int e4 = 0; e4 < 8; ++e4) {
+              const float4 yv = y[e4];
+              w[e4 * 4 + 0] = sqrt_approx(fmaxf(fmaf(al, w[e4 * 4 + 0], xa + yv.x), 0.f));
+              w[e4 * 4 + 1] = sqrt_approx(fmaxf(fmaf(al, w[e4 * 4 + 1], xa + yv.y), 0.f));
+              w[e4 * 4 + 2] = sqrt_approx(fmaxf(fmaf(al, w[e4 * 4 + 2], xa + yv.z), 0.f));
+              w[e4 * 4 + 3] = sqrt_approx(fmaxf(fmaf(al, w[e4 * 4 + 3], xa + yv.w), 0.f));
+            }
+          } else {
+#pragma unroll
+            for (int e4 = 0; e4 < 8; ++e4) {
+              const float4 yv = y[e4];
+              w[e4 * 4 + 0] = fmaf(al, w[e4 * 4 + 0], xa + yv.x);
+              w[e4 * 4 + 1] = fmaf(al, w[e4 * 4 + 1], xa + yv.y);
+              w[e4 * 4 + 2] = fmaf(al, w[e4 * 4 + 2], xa + yv.z);
+              w[e4 * 4 + 3] = fmaf(al, w[e4 * 4 + 3], xa + yv.w);
+            }
           }
         } else {
           const float *orow = p.out + row * p.ldo;
@@ -634,16 +647,18 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-// out[i, j] = sqrt(max(na[i] + nb[j] - 2 out[i, j], 0)) over an (M, N) matrix.
+// out[i, j] = func(alpha * out[i, j] + na[i] + nb[j]) over an (M, N) matrix.
 extern "C" __global__ void __launch_bounds__(256)
-    nmb_contract_finish_distance(float *out, int64_t M, int64_t N, int64_t ldo,
-                                 const float *__restrict__ na, const float *__restrict__ nb) {
+    nmb_contract_finish_rowcol(float *out, int64_t M, int64_t N, int64_t ldo,
+                               const float *__restrict__ na, const float *__restrict__ nb, float alpha,
+                               int func) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= M * N)
     return;
   const int64_t i = idx / N, j = idx % N;
   float *o = out + i * ldo + j;
-  *o = sqrt_approx(fmaxf(fmaf(-2.f, *o, na[i] + nb[j]), 0.f));
+  const float v = fmaf(alpha, *o, na[i] + nb[j]);
+  *o = func == 1 ? sqrt_approx(fmaxf(v, 0.f)) : v;
 }
 
 // ------------------------------------------------------------ host side ---
@@ -684,10 +699,36 @@ EncodeTiledFn encodeTiled() {
 
 size_t alignUp(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// What mode 0 adds to alpha * A.B^T: a row term and a column term, each either
+// absent, the squared norms of the operand's rows (from the packing prepass) or
+// a contiguous vector the caller gives, and the final function.
+enum { kTermNone = 0, kTermNorms = 1, kTermVector = 2 };
+struct RowCol {
+  int rowKind = kTermNone, colKind = kTermNone;
+  const float *rowv = nullptr, *colv = nullptr;
+  int func = 0; // 0: identity, 1: sqrt(max(., 0))
+};
+
+// Fills a padded term vector: `n` values from `src` (or zeros), zeros up to `padded`.
+bool fillTerm(float *dst, const float *src, int64_t n, int64_t padded, cudaStream_t stream) {
+  cudaError_t e = cudaSuccess;
+  if (src)
+    e = cudaMemcpyAsync(dst, src, (size_t)n * 4, cudaMemcpyDeviceToDevice, stream);
+  const int64_t z0 = src ? n : 0;
+  if (e == cudaSuccess && padded > z0)
+    e = cudaMemsetAsync(dst + z0, 0, (size_t)(padded - z0) * 4, stream);
+  if (e != cudaSuccess) {
+    nmb::setError("contraction: filling a row/column term failed: %s", cudaGetErrorString(e));
+    return false;
+  }
+  return true;
+}
+
 // Runs out = epilogue(A . B^T) with A (M, K), B (N, K) given as Operands.
-// mode 0: pairwise distance; mode 1: out = alpha * A.B^T + beta * out.
+// mode 0: out = func(alpha * A.B^T + row term + column term) (`rc`);
+// mode 1: out = alpha * A.B^T + beta * out.
 bool runContraction(void *queue, const Operand &A, const Operand &B, float *out, int64_t ldo, int mode,
-                    float alpha, float beta) {
+                    float alpha, float beta, const RowCol &rc = RowCol()) {
   nmb::QueueView qv;
   if (!nmb::queueView(queue, &qv))
     return false;
@@ -727,14 +768,26 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
   }
 
   const bool single = K <= kMaxK;
-  if (mode == 0 && !single) {
-    // K spans several blocks: the norms over the whole K come from their own kernel
-    nmb_contract_norms_f32<<<(unsigned)((tiles_m * kTile + 255) / 256), 256, 0, stream>>>(
-        A.data, M, A.ldr, A.ldk, (int)K, tiles_m * kTile, nA);
-    nmb_contract_norms_f32<<<(unsigned)((tiles_n * kTile + 255) / 256), 256, 0, stream>>>(
-        B.data, N, B.ldr, B.ldk, (int)K, tiles_n * kTile, nB);
-    nmb::noteLaunch();
-    nmb::noteLaunch();
+  if (mode == 0) {
+    // terms that do not come from the prepass: given vectors and absent terms
+    // (zeros), padded to whole tiles; with K in several blocks the norms over
+    // the whole K come from their own kernel
+    if (rc.rowKind != kTermNorms && !fillTerm(nA, rc.rowKind == kTermVector ? rc.rowv : nullptr, M,
+                                              tiles_m * kTile, stream))
+      return false;
+    if (rc.colKind != kTermNorms && !fillTerm(nB, rc.colKind == kTermVector ? rc.colv : nullptr, N,
+                                              tiles_n * kTile, stream))
+      return false;
+    if (!single && rc.rowKind == kTermNorms) {
+      nmb_contract_norms_f32<<<(unsigned)((tiles_m * kTile + 255) / 256), 256, 0, stream>>>(
+          A.data, M, A.ldr, A.ldk, (int)K, tiles_m * kTile, nA);
+      nmb::noteLaunch();
+    }
+    if (!single && rc.colKind == kTermNorms) {
+      nmb_contract_norms_f32<<<(unsigned)((tiles_n * kTile + 255) / 256), 256, 0, stream>>>(
+          B.data, N, B.ldr, B.ldk, (int)K, tiles_n * kTile, nB);
+      nmb::noteLaunch();
+    }
   }
   // Tensor map of the output for the epilogue's TMA stores: needs a 16-byte
   // aligned base and row pitch and 32-bit coordinates.
@@ -762,8 +815,10 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     const int kcount = (int)(K - k0 < kMaxK ? K - k0 : kMaxK);
     const int kpad = padK(kcount > 0 ? kcount : 1);
     const bool fused_norms = mode == 0 && single;
-    const PackOperand pa{A.data, M, A.ldr, A.ldk, dA, fused_norms ? nA : nullptr, (int)tiles_m};
-    const PackOperand pb{B.data, N, B.ldr, B.ldk, dB, fused_norms ? nB : nullptr, (int)tiles_n};
+    const PackOperand pa{A.data, M, A.ldr, A.ldk, dA, fused_norms && rc.rowKind == kTermNorms ? nA : nullptr,
+                         (int)tiles_m};
+    const PackOperand pb{B.data, N, B.ldr, B.ldk, dB, fused_norms && rc.colKind == kTermNorms ? nB : nullptr,
+                         (int)tiles_n};
     nmb_contract_pack_f32<<<(unsigned)(tiles_m + tiles_n), 256, 0, stream>>>(pa, pb, (int)k0, kcount,
                                                                              kpad);
     ContractParams p;
@@ -778,9 +833,10 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     p.kpad = kpad;
     p.status = status;
     p.tma_out = tma_out ? 1 : 0;
+    p.func = rc.func;
     if (mode == 0 && single) {
       p.mode = 0;
-      p.alpha = 1.f;
+      p.alpha = alpha;
       p.beta = 0.f;
     } else {
       p.mode = 1;
@@ -794,8 +850,8 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     k0 += kMaxK;
   } while (k0 < K);
   if (mode == 0 && !single) {
-    nmb_contract_finish_distance<<<(unsigned)((M * N + 255) / 256), 256, 0, stream>>>(out, M, N, ldo,
-                                                                                     nA, nB);
+    nmb_contract_finish_rowcol<<<(unsigned)((M * N + 255) / 256), 256, 0, stream>>>(out, M, N, ldo, nA, nB,
+                                                                                   alpha, rc.func);
     nmb::noteLaunch();
   }
   cudaError_t e = cudaGetLastError();
@@ -810,14 +866,13 @@ bool unitStride(const GPUXMemref2f *m) { return m->strides[0] == 1 || m->strides
 
 } // namespace
 
-// C = alpha * A @ B + beta * C (NumpyLinalg.cpp:67-147); blocking like the
-// reference's `.wait()`.
-GPUX_EXPORT void _mlir_ciface_mkl_gemm_float32_device(void *queue, const GPUXMemref2f *a,
-                                                      const GPUXMemref2f *b, float alpha,
-                                                      float beta, GPUXMemref2f *c) {
+namespace {
+// Enqueues C = alpha * A @ B + beta * C on the queue's stream.
+bool enqueueGemm(void *queue, const GPUXMemref2f *a, const GPUXMemref2f *b, float alpha, float beta,
+                 GPUXMemref2f *c) {
   if (!queue || !a || !b || !c) {
     nmb::setError("mkl_gemm_float32_device: null argument");
-    return;
+    return false;
   }
   const GPUXMemref2f *ops[3] = {a, b, c};
   const char names[3] = {'a', 'b', 'c'};
@@ -827,12 +882,12 @@ GPUX_EXPORT void _mlir_ciface_mkl_gemm_float32_device(void *queue, const GPUXMem
       nmb::setError("mkl gemm suports only arrays contiguous on inner dimension; '%c' strides "
                     "are %zu and %zu",
                     names[i], ops[i]->strides[0], ops[i]->strides[1]);
-      return;
+      return false;
     }
   if (a->dims[1] != b->dims[0] || c->dims[0] != a->dims[0] || c->dims[1] != b->dims[1]) {
     nmb::setError("mkl_gemm_float32_device: shape mismatch (%zu,%zu) @ (%zu,%zu) -> (%zu,%zu)",
                   a->dims[0], a->dims[1], b->dims[0], b->dims[1], c->dims[0], c->dims[1]);
-    return;
+    return false;
   }
   const bool c_rowmajor = c->strides[1] == 1 || c->dims[1] == 1;
   Operand A{a->data + a->offset, (int64_t)a->dims[0], (int64_t)a->dims[1], (int64_t)a->strides[0],
@@ -841,14 +896,19 @@ GPUX_EXPORT void _mlir_ciface_mkl_gemm_float32_device(void *queue, const GPUXMem
   Operand B{b->data + b->offset, (int64_t)b->dims[1], (int64_t)b->dims[0], (int64_t)b->strides[1],
             (int64_t)b->strides[0]};
   float *out = c->data + c->offset;
-  bool ok;
-  if (c_rowmajor) {
-    ok = runContraction(queue, A, B, out, (int64_t)c->strides[0], 1, alpha, beta);
-  } else {
-    // column-major C: compute C^T = B^T . A^T, which is row-major
-    ok = runContraction(queue, B, A, out, (int64_t)c->strides[1], 1, alpha, beta);
-  }
-  if (!ok)
+  if (c_rowmajor)
+    return runContraction(queue, A, B, out, (int64_t)c->strides[0], 1, alpha, beta);
+  // column-major C: compute C^T = B^T . A^T, which is row-major
+  return runContraction(queue, B, A, out, (int64_t)c->strides[1], 1, alpha, beta);
+}
+} // namespace
+
+// C = alpha * A @ B + beta * C (NumpyLinalg.cpp:67-147); blocking like the
+// reference's `.wait()`.
+GPUX_EXPORT void _mlir_ciface_mkl_gemm_float32_device(void *queue, const GPUXMemref2f *a,
+                                                      const GPUXMemref2f *b, float alpha,
+                                                      float beta, GPUXMemref2f *c) {
+  if (!enqueueGemm(queue, a, b, alpha, beta, c))
     return;
   nmb::QueueView qv;
   if (nmb::queueView(queue, &qv)) {
@@ -856,6 +916,16 @@ GPUX_EXPORT void _mlir_ciface_mkl_gemm_float32_device(void *queue, const GPUXMem
     if (e != cudaSuccess)
       nmb::setError("mkl_gemm_float32_device failed: %s", cudaGetErrorString(e));
   }
+}
+
+// The same product without the host-side wait: asynchronous on the queue's
+// stream (so it can be recorded in a CUDA graph); returns an event.
+GPUX_EXPORT void *_mlir_ciface_nmb_gemm_float32_device_async(void *queue, const GPUXMemref2f *a,
+                                                             const GPUXMemref2f *b, float alpha,
+                                                             float beta, GPUXMemref2f *c) {
+  if (!enqueueGemm(queue, a, b, alpha, beta, c))
+    return nullptr;
+  return nmb::recordEventOn(queue);
 }
 
 GPUX_EXPORT void mkl_gemm_float32_device(void *q, const GPUXMemref2f *a, const GPUXMemref2f *b,
@@ -885,7 +955,52 @@ GPUX_EXPORT void *_mlir_ciface_nmb_pairwise_distance_float32_device(void *queue,
             (int64_t)x->strides[1]};
   Operand Y{y->data + y->offset, (int64_t)y->dims[0], (int64_t)y->dims[1], (int64_t)y->strides[0],
             (int64_t)y->strides[1]};
-  if (!runContraction(queue, X, Y, d->data + d->offset, (int64_t)d->strides[0], 0, 1.f, 0.f))
+  RowCol rc;
+  rc.rowKind = rc.colKind = kTermNorms;
+  rc.func = 1;
+  if (!runContraction(queue, X, Y, d->data + d->offset, (int64_t)d->strides[0], 0, -2.f, 0.f, rc))
+    return nullptr;
+  return nmb::recordEventOn(queue);
+}
+
+// d[i, j] = func(alpha * sum_k x[i, k] y[j, k] + row term[i] + column term[j]):
+// the contraction with the elementwise chain around the product run as its
+// epilogue.  Term kinds: 0 none, 1 the squared norms of the operand's rows
+// (taken from the packing prepass), 2 a contiguous float32 vector of M (row) or
+// N (column) values.  func: 0 identity, 1 sqrt(max(., 0)).
+GPUX_EXPORT void *_mlir_ciface_nmb_contract_rowcol_float32_device(
+    void *queue, const GPUXMemref2f *x, const GPUXMemref2f *y, float alpha, int rowKind, const float *rowv,
+    int colKind, const float *colv, int func, GPUXMemref2f *d) {
+  if (!queue || !x || !y || !d) {
+    nmb::setError("nmb_contract_rowcol_float32_device: null argument");
+    return nullptr;
+  }
+  if (x->dims[1] != y->dims[1] || d->dims[0] != x->dims[0] || d->dims[1] != y->dims[0]) {
+    nmb::setError("nmb_contract_rowcol_float32_device: shape mismatch x (%zu,%zu), y (%zu,%zu), "
+                  "d (%zu,%zu)",
+                  x->dims[0], x->dims[1], y->dims[0], y->dims[1], d->dims[0], d->dims[1]);
+    return nullptr;
+  }
+  if (d->strides[1] != 1 && d->dims[1] > 1) {
+    nmb::setError("nmb_contract_rowcol_float32_device: d must be row-major");
+    return nullptr;
+  }
+  if (rowKind < 0 || rowKind > 2 || colKind < 0 || colKind > 2 || func < 0 || func > 1 ||
+      (rowKind == kTermVector && !rowv) || (colKind == kTermVector && !colv)) {
+    nmb::setError("nmb_contract_rowcol_float32_device: bad term kind or function");
+    return nullptr;
+  }
+  Operand X{x->data + x->offset, (int64_t)x->dims[0], (int64_t)x->dims[1], (int64_t)x->strides[0],
+            (int64_t)x->strides[1]};
+  Operand Y{y->data + y->offset, (int64_t)y->dims[0], (int64_t)y->dims[1], (int64_t)y->strides[0],
+            (int64_t)y->strides[1]};
+  RowCol rc;
+  rc.rowKind = rowKind;
+  rc.colKind = colKind;
+  rc.rowv = rowv;
+  rc.colv = colv;
+  rc.func = func;
+  if (!runContraction(queue, X, Y, d->data + d->offset, (int64_t)d->strides[0], 0, alpha, 0.f, rc))
     return nullptr;
   return nmb::recordEventOn(queue);
 }

@@ -190,9 +190,15 @@ REDUCTIONS = {np.sum: "sum", np.prod: "prod", np.min: "min", np.max: "max", np.a
 class Node:
     """Expression-graph node.  kind: 'leaf' (device array), 'arg' (scalar
     argument, a kernel parameter), 'const' (literal), 'op' (ufunc), 'cast',
-    'where', 'call' (user scalar device function)."""
+    'where', 'call' (user scalar device function): these make up fused
+    elementwise kernels.  'reduce' (op = the reduction, value = the axis),
+    'dot' (matrix product) and 'reshape' (C-order reshape of a value that is
+    not an array yet) are turned into arrays when a flush reaches them
+    (Trace.lower), or, where a whole pattern is recognised, into one launch.
+    `borrowed` marks a leaf that stands for an array of the caller into which
+    the node's value was written directly."""
 
-    __slots__ = ("kind", "dtype", "shape", "inputs", "op", "value", "slot", "sig", "reads")
+    __slots__ = ("kind", "dtype", "shape", "inputs", "op", "value", "slot", "sig", "reads", "borrowed")
 
     def __init__(self, kind, dtype, shape, inputs=(), op=None, value=None, slot=None):
         self.kind = kind
@@ -204,6 +210,18 @@ class Node:
         self.slot = slot
         self.sig = None
         self.reads = None
+        self.borrowed = False
+
+    def become_leaf(self, slot, borrowed=False):
+        """The node's value now lives in the array of `slot`."""
+        self.kind = "leaf"
+        self.slot = slot
+        self.inputs = ()
+        self.op = None
+        self.value = None
+        self.reads = None
+        self.sig = None
+        self.borrowed = borrowed
 
 
 def node_reads(node):
@@ -305,7 +323,7 @@ class Trace:
         alive = []
         for ref in self.live:
             lz = ref()
-            if lz is None or lz.node.kind == "leaf":
+            if lz is None or (lz.node.kind == "leaf" and not lz.node.borrowed):
                 continue
             alive.append(ref)
             if lz is value:
@@ -361,7 +379,10 @@ class Trace:
 
     def flush(self):
         """Emits the pending stores in order: one fused kernel per output shape
-        for every run of stores that rule (3) allows in one kernel."""
+        for every run of stores that rule (3) allows in one kernel.  Reductions
+        and matrix products inside the stored values are run first (each into
+        a temporary, or straight into the store's target when it is the whole
+        value and the target's layout allows)."""
         queue, self.pending = self.pending, []
         batch, reads, writes = [], set(), set()
 
@@ -379,6 +400,9 @@ class Trace:
         while i < len(queue):
             slot, node = queue[i]
             i += 1
+            if self._store_direct(slot, node, emit):
+                continue
+            self.lower(node)
             nreads = node_reads(node)
             if any(self.overlap(r, slot) == 2 for r in nreads):
                 # the value reads other elements of the target than it writes
@@ -394,6 +418,130 @@ class Trace:
             writes.add(slot)
         emit()
 
+    # lowering --------------------------------------------------------------------
+    # Steps emitted here run at once, ahead of the elementwise stores still
+    # batched by the flush in progress.  That is their program order: by rule (1)
+    # no value reads memory that an earlier queued store writes, and the steps
+    # themselves write only fresh temporaries (a direct store into the target
+    # first emits the batch).
+    def lower(self, node):
+        """Turns every reduction, product and reshape inside `node` into a leaf."""
+        kind = node.kind
+        if kind in ("leaf", "arg", "const"):
+            return
+        if kind == "reduce":
+            self._lower_reduce(node, None)
+        elif kind == "dot":
+            self._lower_dot(node, None)
+        elif kind == "reshape":
+            src = self.force(node.inputs[0])
+            arr = self.arrays[src].reshape(node.shape)
+            node.become_leaf(self.add_view_slot(src, ("reshape", node.shape), arr))
+        else:
+            spec = _match_rowcol(self, node)
+            if spec is not None:
+                self._lower_rowcol(node, spec, None)
+                return
+            for inp in node.inputs:
+                self.lower(inp)
+
+    def force(self, node):
+        """Slot of an array that holds the value of `node`."""
+        self.lower(node)
+        if node.kind == "leaf":
+            return node.slot
+        if node.kind in ("arg", "const"):
+            raise TypeError("a scalar was used where an array is needed")
+        tmp = self.add_tmp_slot(node.shape, node.dtype)
+        _emit_eltwise(self, node.shape, [(tmp, node)])
+        node.become_leaf(tmp)
+        return tmp
+
+    def _lower_reduce(self, node, dst):
+        from . import reduce_ops
+
+        op, axis = node.op, node.value
+        src = self.force(node.inputs[0])
+        borrowed = dst is not None
+        if dst is None:
+            dst = self.add_tmp_slot(node.shape, node.dtype)
+        self.steps.append(("reduce", op, axis, src, dst))
+        if not self.dry:
+            reduce_ops.reduce(self.arrays[src], op, axis, out=self.arrays[dst])
+        node.become_leaf(dst, borrowed)
+
+    def _lower_dot(self, node, dst):
+        from . import contraction
+
+        sa, sb = self.force(node.inputs[0]), self.force(node.inputs[1])
+        for s in (sa, sb):
+            if self.arrays[s].dtype != np.float32:
+                raise TypeError("np.dot on device arrays is implemented for float32 operands")
+        borrowed = dst is not None
+        if dst is None:
+            dst = self.add_tmp_slot(node.shape, node.dtype)
+        self.steps.append(("dot", sa, sb, dst))
+        if not self.dry:
+            contraction.gemm(self.arrays[sa], self.arrays[sb], self.arrays[dst], blocking=False)
+        node.become_leaf(dst, borrowed)
+
+    def _lower_rowcol(self, node, spec, dst):
+        """One contraction launch for func(alpha * a @ b + row + col)."""
+        from . import contraction
+
+        alpha, dot_node, row, col, func = spec
+        sa, sb = self.force(dot_node.inputs[0]), self.force(dot_node.inputs[1])
+
+        def term(t, operand, transposed):
+            if t is None:
+                return None
+            if _is_row_norms(self, t, operand, transposed):
+                return "norms"
+            s = self.force(t)
+            if not self.arrays[s].is_c_contiguous:
+                tmp = self.add_tmp_slot(self.arrays[s].shape, np.float32)
+                _emit_eltwise(self, self.arrays[s].shape, [(tmp, Node("leaf", np.float32, self.arrays[s].shape, slot=s))])
+                s = tmp
+            return s
+
+        rspec, cspec = term(row, sa, False), term(col, sb, True)
+        borrowed = dst is not None
+        if dst is None:
+            dst = self.add_tmp_slot(node.shape, node.dtype)
+        step = ("contract", sa, sb, float(alpha), rspec, cspec, func, dst)
+        self.steps.append(step)
+        if not self.dry:
+            run_contract(step, self.arrays.__getitem__)
+        node.become_leaf(dst, borrowed)
+
+    def _store_direct(self, slot, node, emit):
+        """A store whose whole value is a reduction, a product or a product with
+        its epilogue writes the target itself when the layouts allow."""
+        kind = node.kind
+        spec = None
+        if kind not in ("reduce", "dot"):
+            spec = _match_rowcol(self, node)
+            if spec is None:
+                return False
+        dst = self.arrays[slot]
+        if dst.shape != node.shape or dst.dtype != node.dtype or dst.size == 0:
+            return False
+        if kind == "reduce":
+            if not dst.is_c_contiguous:
+                return False
+        elif dst.ndim != 2 or (dst.strides[1] != dst.dtype.itemsize and dst.shape[1] > 1) or dst.strides[0] < 0:
+            return False
+        if any(self.overlap(r, slot) for r in node_reads(node)):
+            return False
+        emit()
+        if kind == "reduce":
+            self._lower_reduce(node, slot)
+        elif kind == "dot":
+            self._lower_dot(node, slot)
+        else:
+            self._lower_rowcol(node, spec, slot)
+        return True
+
     def materialize(self, lazy):
         """Device array (slot) holding the value of `lazy`."""
         node = lazy.node
@@ -404,7 +552,9 @@ class Trace:
         slot = self.add_tmp_slot(node.shape, node.dtype)
         self.store(slot, node)
         self.flush()
-        return slot
+        if node.kind != "leaf":
+            node.become_leaf(slot)  # later uses read the array instead of recomputing
+        return node.slot
 
 
 _tls = threading.local()
@@ -667,19 +817,37 @@ class LazyArray:
     def reshape(self, *shape):
         if len(shape) == 1 and isinstance(shape[0], (tuple, list)):
             shape = tuple(shape[0])
+        if self.node.kind != "leaf":
+            # a value that is not an array yet: reshaped when it becomes one
+            shape = [int(d) for d in shape]
+            if shape.count(-1) > 1:
+                raise ValueError("can only specify one unknown dimension")
+            if -1 in shape:
+                known = int(np.prod([d for d in shape if d != -1], dtype=np.int64))
+                shape[shape.index(-1)] = self.size // max(known, 1)
+            if int(np.prod(shape, dtype=np.int64)) != self.size:
+                raise ValueError(f"cannot reshape array of size {self.size} into {tuple(shape)}")
+            if tuple(shape) == self.shape:
+                return self
+            return LazyArray(self.trace, Node("reshape", self.dtype, shape, (self.node,)))
         return self._view(("reshape", shape), lambda a: a.reshape(shape))
 
     def __getitem__(self, idx):
         if idx is Ellipsis or (isinstance(idx, slice) and idx == slice(None)):
             return self
+        if self.node.kind != "leaf" and isinstance(idx, tuple) and all(
+                i is None or (isinstance(i, slice) and i == slice(None)) for i in idx) \
+                and sum(1 for i in idx if i is not None) <= self.ndim:
+            # only new axes (x[:, None]): a reshape
+            dims = iter(self.shape)
+            shape = [1 if i is None else next(dims) for i in idx] + list(dims)
+            return self.reshape(shape)
         return self._view(("getitem", idx), lambda a: a[idx])
 
     def __setitem__(self, idx, value):
         target = self if (idx is Ellipsis or idx == slice(None)) else self[idx]
         if target.node.kind != "leaf":
             raise TypeError("cannot assign into an expression")
-        if _retarget_producer(self.trace, target, value):
-            return
         vnode = _as_node(self.trace, value)
         broadcast_shapes(vnode.shape, target.shape)  # raises on mismatch
         if np.broadcast_shapes(vnode.shape, target.shape) != target.shape:
@@ -687,44 +855,6 @@ class LazyArray:
         if vnode.dtype != target.dtype:
             vnode = Node("cast", target.dtype, vnode.shape, (vnode,))
         self.trace.store(target.node.slot, vnode, value if isinstance(value, LazyArray) else None)
-
-
-def _retarget_producer(trace, target, value):
-    """`out[:] = np.sum(a, axis=1)` (or np.dot): when the value is the fresh
-    temporary of the step recorded last, that step is made to write into the
-    assignment target directly instead of a temporary followed by a copy."""
-    if not isinstance(value, LazyArray) or value.node.kind != "leaf" or len(trace.steps) < 2:
-        return False
-    tmp = value.node.slot
-    step, alloc = trace.steps[-1], trace.steps[-2]
-    if alloc != ("alloc", tmp) or step[0] not in ("reduce", "dot") or step[-1] != tmp:
-        return False
-    dst_arr, tmp_arr = trace.arrays[target.node.slot], trace.arrays[tmp]
-    if (dst_arr.shape != tmp_arr.shape or dst_arr.dtype != tmp_arr.dtype
-            or not dst_arr.is_c_contiguous or trace.pending_touches(target.node.slot, reads_too=True)):
-        return False
-    # the step would write the target at once: not when its own operands, or an
-    # expression that is still to be evaluated, read that memory
-    operands = (step[3],) if step[0] == "reduce" else step[1:3]
-    if any(trace.overlap(s, target.node.slot) for s in operands):
-        return False
-    for ref in trace.live:
-        lz = ref()
-        if lz is not None and lz.node.kind != "leaf" and any(
-                trace.overlap(r, target.node.slot) for r in node_reads(lz.node)):
-            return False
-    new_step = step[:-1] + (target.node.slot,)
-    trace.steps[-2:] = [new_step]
-    if not trace.dry:
-        if step[0] == "reduce":
-            from . import reduce_ops
-
-            reduce_ops.reduce(trace.arrays[step[3]], step[1], step[2], out=dst_arr)
-        else:
-            from . import contraction
-
-            contraction.gemm(trace.arrays[step[1]], trace.arrays[step[2]], dst_arr)
-    return True
 
 
 def _is_one(node):
@@ -886,19 +1016,27 @@ def clip_lazy(trace, a, a_min=None, a_max=None, out=None):
 
 
 def _reduce_node(trace, op, a, axis, reduce_ops):
-    src = trace.materialize(a)
-    arr = trace.arrays[src]
-    oshape = () if axis is None else arr.shape[:axis % arr.ndim] + arr.shape[axis % arr.ndim + 1:]
-    dst = trace.add_tmp_slot(oshape, reduce_ops.out_dtype(op, arr.dtype))
-    trace.steps.append(("reduce", op, axis, src, dst))
-    if not trace.dry:
-        reduce_ops.reduce(arr, op, axis, out=trace.arrays[dst])
-    return trace.leaf(dst)
+    """The reduction as a graph node; it runs when a flush reaches it."""
+    src = _as_node(trace, a)
+    shape = src.shape
+    if axis is None:
+        if int(np.prod(shape, dtype=np.int64)) == 0:
+            raise ValueError("zero-size array to reduction operation")
+        oshape = ()
+    else:
+        axis = int(axis)
+        if not -len(shape) <= axis < len(shape):
+            raise ValueError("axis out of range")
+        axis %= len(shape)
+        if shape[axis] == 0:
+            raise ValueError("zero-size reduction axis")
+        oshape = shape[:axis] + shape[axis + 1:]
+    return LazyArray(trace, Node("reduce", reduce_ops.out_dtype(op, src.dtype), oshape, (src,), op=op, value=axis))
 
 
 def dot(trace, a, b, out=None):
-    from . import contraction
-
+    """np.dot as a graph node: the product runs when a flush reaches it, alone
+    (the tensor-core gemm) or together with the elementwise chain around it."""
     a = a if isinstance(a, LazyArray) else LazyArray(trace, _as_node(trace, a))
     b = b if isinstance(b, LazyArray) else LazyArray(trace, _as_node(trace, b))
     if out is None and (len(a.shape) == 1 or len(b.shape) == 1):
@@ -908,19 +1046,133 @@ def dot(trace, a, b, out=None):
         if len(a.shape) == 1:
             return dot(trace, a.reshape(1, a.shape[0]), b).reshape(b.shape[1])
         return dot(trace, a, b.reshape(b.shape[0], 1)).reshape(a.shape[0])
-    sa, sb = trace.materialize(a), trace.materialize(b)
-    A, B = trace.arrays[sa], trace.arrays[sb]
-    if A.ndim != 2 or B.ndim != 2 or A.shape[1] != B.shape[0]:
+    if len(a.shape) != 2 or len(b.shape) != 2 or a.shape[1] != b.shape[0]:
         raise ValueError("dot needs 2-D operands with matching inner dimension")
-    if out is None:
-        dst = trace.add_tmp_slot((A.shape[0], B.shape[1]), np.result_type(A.dtype, B.dtype))
+    node = Node("dot", np.result_type(a.dtype, b.dtype), (a.shape[0], b.shape[1]),
+                (_as_node(trace, a), _as_node(trace, b)))
+    res = LazyArray(trace, node)
+    if out is not None:
+        out[...] = res
+        return out
+    return res
+
+
+# ---- the elementwise chain around a product, as the contraction's epilogue ----
+def _const_value(node):
+    while node.kind == "cast":
+        node = node.inputs[0]
+    return node.value if node.kind == "const" else None
+
+
+def _scaled_dot(node):
+    """(c, dot node) when `node` is c * dot (either order), -dot or dot."""
+    if node.kind == "dot":
+        return 1.0, node
+    if node.kind == "op" and node.op == "negative" and node.inputs[0].kind == "dot":
+        return -1.0, node.inputs[0]
+    if node.kind == "op" and node.op == "multiply":
+        x, y = node.inputs
+        for c, d in ((x, y), (y, x)):
+            v = _const_value(c)
+            if v is not None and d.kind == "dot" and c.dtype == np.float32:
+                return float(v), d
+    return None, None
+
+
+def _match_rowcol(trace, node):
+    """Recognises func(alpha * dot(a, b) + row + col) with func the identity or
+    sqrt(maximum(., 0)), `row` of shape (M, 1) and `col` of shape (1, N) or
+    (N,), all float32.  Returns (alpha, dot node, row, col, func) or None."""
+    if node.kind != "op" or len(node.shape) != 2 or node.dtype != np.float32:
+        return None
+    m, n = node.shape
+    if m <= 1 or n <= 1:
+        return None
+    func, body = 0, node
+    if node.op == "sqrt":
+        inner = node.inputs[0]
+        if inner.kind != "op" or inner.op != "maximum":
+            return None
+        x, y = inner.inputs
+        if _const_value(y) == 0:
+            body = x
+        elif _const_value(x) == 0:
+            body = y
+        else:
+            return None
+        func = 1
+    terms = []
+
+    def collect(t, sign):
+        if t.kind == "op" and t.op == "add":
+            collect(t.inputs[0], sign)
+            collect(t.inputs[1], sign)
+        elif t.kind == "op" and t.op == "subtract":
+            collect(t.inputs[0], sign)
+            collect(t.inputs[1], -sign)
+        else:
+            terms.append((sign, t))
+
+    collect(body, 1.0)
+    if len(terms) > 3:
+        return None
+    alpha = product = row = col = None
+    for sign, t in terms:
+        c, d = _scaled_dot(t)
+        if d is not None:
+            if product is not None or d.shape != (m, n) or d.dtype != np.float32:
+                return None
+            alpha, product = sign * c, d
+        elif sign != 1.0 or t.dtype != np.float32 or t.kind in ("arg", "const"):
+            return None
+        elif t.shape == (m, 1) and row is None:
+            row = t
+        elif t.shape in ((1, n), (n,)) and col is None:
+            col = t
+        else:
+            return None
+    if product is None or (func == 0 and row is None and col is None and alpha == 1.0):
+        return None
+    if any(i.dtype != np.float32 for i in product.inputs):
+        return None
+    return alpha, product, row, col, func
+
+
+def _is_row_norms(trace, term, operand_slot, transposed):
+    """`term` is sum(x * x, axis=1) (possibly reshaped) of the matrix x whose
+    rows the contraction's operand holds: x is the array of `operand_slot`, or
+    its transpose when the operand is the second factor of the product."""
+    while term.kind == "reshape":
+        term = term.inputs[0]
+    if term.kind != "reduce" or term.op != "sum" or term.value != 1:
+        return False
+    sq = term.inputs[0]
+    if sq.kind != "op" or len(sq.shape) != 2:
+        return False
+    if sq.op == "square":
+        x, y = sq.inputs[0], sq.inputs[0]
+    elif sq.op == "multiply":
+        x, y = sq.inputs
     else:
-        dst = trace.materialize(out)
-        trace.before_direct_write(dst)
-    trace.steps.append(("dot", sa, sb, dst))
-    if not trace.dry:
-        contraction.gemm(A, B, trace.arrays[dst])
-    return trace.leaf(dst)
+        return False
+    if x.kind != "leaf" or y.kind != "leaf" or trace.overlap(x.slot, y.slot) != 1:
+        return False
+    arr, op_arr = trace.arrays[x.slot], trace.arrays[operand_slot]
+    if transposed:
+        op_arr = op_arr.T
+    return (arr.ptr == op_arr.ptr and arr.shape == op_arr.shape and arr.strides == op_arr.strides
+            and arr.dtype == np.float32)
+
+
+def run_contract(step, get):
+    from . import contraction
+
+    _tag, sa, sb, alpha, row, col, func, dst = step
+
+    def term(t):
+        return t if t is None or isinstance(t, str) else get(t)
+
+    contraction.contract_rowcol(get(sa), get(sb).T, get(dst), alpha, term(row), term(col), func)
 
 
 # ---------------------------------------------------------------- codegen ---
@@ -1256,7 +1508,9 @@ class Plan:
             elif tag == "reduce":
                 reduce_ops.reduce(get(step[3]), step[1], step[2], out=get(step[4]))
             elif tag == "dot":
-                contraction.gemm(get(step[1]), get(step[2]), get(step[3]))
+                contraction.gemm(get(step[1]), get(step[2]), get(step[3]), blocking=False)
+            elif tag == "contract":
+                run_contract(step, get)
         for i in _result_slots(self.result_spec):
             get(i)
         return _build_result(self.result_spec, arrays)

@@ -72,6 +72,16 @@ SIGNATURES = {
         [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.c_float, ctypes.c_float,
          ctypes.POINTER(Memref2f)],
     ),
+    "_mlir_ciface_nmb_gemm_float32_device_async": (
+        _vp,
+        [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.c_float, ctypes.c_float,
+         ctypes.POINTER(Memref2f)],
+    ),
+    "_mlir_ciface_nmb_contract_rowcol_float32_device": (
+        _vp,
+        [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.c_float, _i, _vp, _i, _vp, _i,
+         ctypes.POINTER(Memref2f)],
+    ),
     "gpuxMemcpy": (_vp, [_vp, _vp, _vp, _sz, _i, _vp]),
     "gpuxMemset": (_vp, [_vp, _vp, _i, _sz, _vp]),
     "gpuxRecordEvent": (_vp, [_vp]),

@@ -8,7 +8,8 @@ import math
 import numpy as np
 
 from .decorators import njit, vectorize
-from .kernel import atomic, barrier, get_group_id, get_local_id, get_local_size, kernel, local, private
+from .kernel import (atomic, barrier, get_global_id, get_group_id, get_local_id, get_local_size, kernel, local,
+                     private)
 
 
 @vectorize(nopython=True)
@@ -79,6 +80,19 @@ def argmin_axis1(a, out):
 @njit(parallel=True)
 def total(a, out):
     out[...] = np.sum(a)
+
+
+# Pairwise Euclidean distances through the norm expansion |x|^2 + |y|^2 - 2 x.y
+# with the dot products from np.dot, the route to the device gemm in the
+# reference (numba_mlir/mlir/numpy/funcs.py:752-812).  The array front end
+# recognises the chain around the product and runs it as the epilogue of the
+# tensor-core contraction, with the row norms taken from its packing prepass.
+@njit(parallel=True)
+def pairwise_distance(x, y, d):
+    xx = np.sum(x * x, axis=1)
+    yy = np.sum(y * y, axis=1)
+    g = np.dot(x, y.T)
+    d[:] = np.sqrt(np.maximum(xx.reshape(-1, 1) + yy.reshape(1, -1) - np.float32(2) * g, np.float32(0)))
 
 
 # New centroids = float32(sum / count); empty clusters keep their centre.
@@ -198,6 +212,31 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
     if lid < _KM_K:
         if lcnt[lid] != 0:
             atomic.add(counts, lid, lcnt[lid])
+
+
+# The same iteration in the plain form: one point per work-item, every point
+# adds itself to its cluster's sum and count with global atomics.
+@kernel
+def _kmeans_naive_kernel(points, centroids, labels, sums, counts):
+    i = get_global_id(0)
+    best = 0
+    best_d = np.float32(np.inf)
+    for k in range(centroids.shape[0]):
+        d = np.float32(0.0)
+        for j in range(points.shape[1]):
+            t = points[i, j] - centroids[k, j]
+            d += t * t
+        if d < best_d:
+            best_d = d
+            best = k
+    labels[i] = best
+    atomic.add(counts, best, 1)
+    for j in range(points.shape[1]):
+        atomic.add(sums, (best, j), points[i, j])
+
+
+def kmeans_step_naive(points, centroids, labels, sums, counts):
+    _kmeans_naive_kernel[points.shape[0], KMEANS_LOCAL_SIZE](points, centroids, labels, sums, counts)
 
 
 def kmeans_step(points, centroids, labels, sums, counts):

@@ -43,5 +43,37 @@ def test_map_host_accepts_pageable_arrays_and_checks_arguments(queue):
     assert np.array_equal(out, a * 2)
     with pytest.raises(ValueError):
         nm.map_host(twice, [a], [out[:5].copy()], chunk=3000, queue=queue)
-    with pytest.raises(TypeError):
+    with pytest.raises(ValueError):  # 100 rows in, 10000 out
         nm.map_host(twice, [a.reshape(100, 100)], [out], chunk=3000, queue=queue)
+    with pytest.raises(TypeError):   # not contiguous
+        nm.map_host(twice, [a[::2]], [out[::2]], chunk=3000, queue=queue)
+
+
+def test_map_host_row_chunks_of_a_matrix_and_a_resident_operand(queue):
+    """Inputs and outputs cut along axis 0 with different row shapes (a row
+    reduction; the distance rows of a block of points against a second operand
+    that stays whole on the device)."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import contraction, workloads
+    from oracle import configs as O
+
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((1000, 512)).astype(np.float32)
+    out = np.zeros(1000, np.float32)
+    for _ in range(2):
+        nm.map_host(workloads.sum_axis1, [a], [out], chunk=192, queue=queue)
+    whole = nm.empty(1000, np.float32)
+    workloads.sum_axis1(nm.from_host(a), whole)
+    assert np.array_equal(out.view(np.uint32), whole.copy_to_host().view(np.uint32))
+
+    x = rng.uniform(0, 1, (700, 64)).astype(np.float32)
+    y = rng.uniform(0, 1, (300, 64)).astype(np.float32)
+    d = np.zeros((700, 300), np.float32)
+
+    def rows(xc, yw, dc):
+        contraction.pairwise_distance(xc, yw, dc)
+
+    nm.map_host(rows, [x], [d], resident=[y], chunk=256, queue=queue)
+    want = np.zeros_like(d)
+    O.pairwise(x, y, want)
+    np.testing.assert_allclose(d, want, rtol=1e-5, atol=1e-6)
