@@ -242,6 +242,170 @@ __device__ __forceinline__ T group_reduce(T v, Op op, T neutral, T *scratch, voi
   return scratch[0];
 }
 
+// ------------------------------------------- reduce(f(inputs)), one pass ---
+// A reduction whose operand is an elementwise chain reads the chain's inputs
+// once (what the reference gets by fusing the producer into the reduction's
+// loop nest, numba_mlir/mlir/tests/test_gpu.py:2198-2224): the generated Chain
+// (load and compute as above, one output field `out0`) yields the operand's
+// values in registers and they are combined on the way.  `op(acc, x)` is the
+// library's sequential step (OpMin/OpMax: select(x < acc), NaNs never win), A
+// the accumulator and result type.  Partials of different blocks meet through
+// scratch memory and ticket counters that every kernel leaves at zero; the
+// block that draws the last ticket combines them in index order, so a result
+// does not depend on scheduling.
+template <typename A> __device__ __forceinline__ A load_partial(const A *p) {
+  if constexpr (sizeof(A) == 4) {
+    const int raw = __ldcg(reinterpret_cast<const int *>(p));
+    return *reinterpret_cast<const A *>(&raw);
+  } else {
+    const long long raw = __ldcg(reinterpret_cast<const long long *>(p));
+    return *reinterpret_cast<const A *>(&raw);
+  }
+}
+
+// One step of UNROLL vectors at flat indices i0 + u * stride (all loads issued
+// before the first use), folded into acc[l] (l = position inside the vector;
+// SPLIT keeps the V positions apart, for column reductions).
+template <int V, int UNROLL, bool SPLIT, typename A, typename Op, typename Chain>
+__device__ __forceinline__ void reduce_step(const Chain &chain, int64_t i0, int64_t stride, A *acc, Op op) {
+  typename Chain::template In<V> in[UNROLL];
+  typename Chain::template Out<V> val[UNROLL];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u)
+    chain.template load<V>(i0 + (int64_t)u * stride, in[u]);
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u)
+    chain.template compute<V>(in[u], val[u]);
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+    for (int l = 0; l < V; ++l)
+      acc[SPLIT ? l : 0] = op(acc[SPLIT ? l : 0], (A)val[u].out0.v[l]);
+}
+
+// out[r] = reduce_k value[r * cols + k].  A row belongs to one warp (or, with
+// BLOCK_ROW, to the whole block: few long rows); rows are taken round robin.
+// cols % V == 0.
+template <int BLOCK, int V, int UNROLL, bool BLOCK_ROW, typename A, typename Op, typename Chain>
+__device__ __forceinline__ void reduce_rows_fused(const Chain &chain, int64_t rows, int64_t cols, A *out, Op op,
+                                                  A identity, A *scratch) {
+  constexpr int L = BLOCK_ROW ? BLOCK : 32;
+  const int t = BLOCK_ROW ? threadIdx.x : (threadIdx.x & 31);
+  const int64_t first = BLOCK_ROW ? blockIdx.x : (int64_t)blockIdx.x * (BLOCK / 32) + (threadIdx.x >> 5);
+  const int64_t step = BLOCK_ROW ? gridDim.x : (int64_t)gridDim.x * (BLOCK / 32);
+  constexpr int64_t span = (int64_t)L * V * UNROLL;
+  for (int64_t r = first; r < rows; r += step) {
+    A acc = identity;
+    const int64_t base = r * cols;
+    int64_t k0 = 0;
+    for (; k0 + span <= cols; k0 += span)
+      reduce_step<V, UNROLL, false>(chain, base + k0 + (int64_t)t * V, (int64_t)L * V, &acc, op);
+    for (int64_t k = k0 + (int64_t)t * V; k < cols; k += (int64_t)L * V)
+      reduce_step<V, 1, false>(chain, base + k, 0, &acc, op);
+    if (BLOCK_ROW) {
+      acc = block_reduce(acc, op, identity, scratch);
+      if (threadIdx.x == 0)
+        out[r] = acc;
+    } else {
+      acc = warp_reduce(acc, op);
+      if (t == 0)
+        out[r] = acc;
+    }
+  }
+}
+
+// out[0] = reduce_i value[i], i < n.  Blocks take tiles of BLOCK*V*UNROLL
+// elements round robin; n % V may be anything (the tail is read one by one).
+template <int BLOCK, int V, int UNROLL, typename A, typename Op, typename Chain>
+__device__ __forceinline__ void reduce_all_fused(const Chain &chain, int64_t n, A *out, A *partials,
+                                                 uint32_t *counter, Op op, A identity, A *scratch) {
+  constexpr int64_t tile = (int64_t)BLOCK * V * UNROLL;
+  A acc = identity;
+  for (int64_t t0 = (int64_t)blockIdx.x * tile; t0 < n; t0 += (int64_t)gridDim.x * tile) {
+    const int64_t base = t0 + (int64_t)threadIdx.x * V;
+    if (t0 + tile <= n) {
+      reduce_step<V, UNROLL, false>(chain, base, (int64_t)BLOCK * V, &acc, op);
+    } else {
+      for (int u = 0; u < UNROLL; ++u) {
+        const int64_t i = base + (int64_t)u * BLOCK * V;
+        if (i + V <= n)
+          reduce_step<V, 1, false>(chain, i, 0, &acc, op);
+        else
+          for (int64_t j = i; j < n; ++j)
+            reduce_step<1, 1, false>(chain, j, 0, &acc, op);
+      }
+    }
+  }
+  acc = block_reduce(acc, op, identity, scratch);
+  __shared__ bool last;
+  if (threadIdx.x == 0) {
+    partials[blockIdx.x] = acc;
+    __threadfence();
+    last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!last)
+    return;
+  __threadfence();
+  A m = identity;
+  for (unsigned g = threadIdx.x; g < gridDim.x; g += BLOCK)
+    m = op(m, load_partial(partials + g));
+  m = block_reduce(m, op, identity, scratch);
+  if (threadIdx.x == 0) {
+    out[0] = m;
+    *counter = 0;
+  }
+}
+
+// out[c] = reduce_r value[r * cols + c].  A thread owns V adjacent columns;
+// blockIdx.y splits the rows, and the row blocks of a column tile meet in
+// partials[gridDim.y][cols] behind one ticket counter per column tile.
+// cols % V == 0.
+template <int BLOCK, int V, int UNROLL, typename A, typename Op, typename Chain>
+__device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t rows, int64_t cols, A *out,
+                                                  A *partials, uint32_t *counters, Op op, A identity) {
+  const int64_t c = ((int64_t)blockIdx.x * BLOCK + threadIdx.x) * V;
+  const int64_t Y = gridDim.y, y = blockIdx.y;
+  const int64_t r0 = rows * y / Y, r1 = rows * (y + 1) / Y;
+  A acc[V];
+#pragma unroll
+  for (int l = 0; l < V; ++l)
+    acc[l] = identity;
+  if (c < cols) {
+    int64_t r = r0;
+    for (; r + UNROLL <= r1; r += UNROLL)
+      reduce_step<V, UNROLL, true>(chain, r * cols + c, cols, acc, op);
+    for (; r < r1; ++r)
+      reduce_step<V, 1, true>(chain, r * cols + c, 0, acc, op);
+    A *dst = Y == 1 ? out + c : partials + y * cols + c;
+#pragma unroll
+    for (int l = 0; l < V; ++l)
+      dst[l] = acc[l];
+  }
+  if (Y == 1)
+    return;
+  __shared__ bool last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0)
+    last = atomicAdd(counters + blockIdx.x, 1u) == (unsigned)(Y - 1);
+  __syncthreads();
+  if (!last)
+    return;
+  __threadfence();
+  if (c < cols) {
+#pragma unroll
+    for (int l = 0; l < V; ++l) {
+      A m = identity;
+      for (int64_t yy = 0; yy < Y; ++yy)
+        m = op(m, load_partial(partials + yy * cols + c + l));
+      out[c + l] = m;
+    }
+  }
+  if (threadIdx.x == 0)
+    counters[blockIdx.x] = 0;
+}
+
 // ------------------------------------------------------------------- math ---
 // float32 stays float32 (numba_mlir/mlir/builtin/funcs.py:180-227); the CUDA
 // functions below are the IEEE-rounded (sqrt, div) or <= 2 ulp (log, exp)

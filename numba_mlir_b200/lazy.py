@@ -461,8 +461,17 @@ class Trace:
         from . import reduce_ops
 
         op, axis = node.op, node.value
-        src = self.force(node.inputs[0])
         borrowed = dst is not None
+        self.lower(node.inputs[0])
+        mode = fused_reduce_mode(node)
+        if mode is not None:
+            # the operand is an elementwise chain: reduced while it is computed
+            out = dst if dst is not None else self.add_tmp_slot(node.shape, node.dtype)
+            if _emit_reduce_fused(self, node, mode, out):
+                node.become_leaf(out, borrowed)
+                return
+            dst = out
+        src = self.force(node.inputs[0])
         if dst is None:
             dst = self.add_tmp_slot(node.shape, node.dtype)
         self.steps.append(("reduce", op, axis, src, dst))
@@ -1340,9 +1349,109 @@ def _emit_eltwise(trace, out_shape, outs):
         run_launch(trace.queue, step, trace.arrays, trace.args)
 
 
+class _ValueHolder:
+    """Stands where an output array does for a chain whose value is not stored."""
+
+    def __init__(self, dtype):
+        self.dtype = np.dtype(dtype)
+
+
+_SMS = 148
+_FUSED_REDUCE_OPS = ("sum", "prod", "min", "max")
+
+
+def fused_reduce_mode(node):
+    """How reduce(f(inputs)) can run in one pass over the inputs: 'rows' (the
+    last axis), 'cols' (the first axis), 'all', or None (run the chain into a
+    temporary first)."""
+    src = node.inputs[0]
+    if node.op not in _FUSED_REDUCE_OPS or src.kind in ("leaf", "arg", "const") or not node_reads(src):
+        return None
+    if src.dtype.name not in _REDUCE_KERNEL_DTYPES:
+        return None
+    nd, axis = len(src.shape), node.value
+    if axis is None or nd == 1:
+        return "all"
+    if axis == nd - 1:
+        return "rows"
+    if axis == 0:
+        return "cols"
+    return None
+
+
+def _emit_reduce_fused(trace, node, mode, dst):
+    """One kernel for reduce(chain): the chain's inputs are read once."""
+    src = node.inputs[0]
+    shape = src.shape
+    n = int(np.prod(shape, dtype=np.int64))
+    em = _Emitter(trace, shape)
+    expr = em.emit(src)
+    results = [(None, expr, _ValueHolder(src.dtype))]
+    if mode == "rows":
+        rows, cols = n // shape[-1], shape[-1]
+    elif mode == "cols":
+        rows, cols = shape[0], n // shape[0]
+    else:
+        rows, cols = 1, n
+    vec_ok = mode == "all" or cols % 4 == 0
+    for slot, kind, params, dt in em.leaves:
+        arr = trace.arrays[slot]
+        unit = 4 * dt.itemsize if dt.itemsize <= 4 else 16
+        if kind in ("full", "row") and arr.ptr % unit:
+            vec_ok = False
+        if kind in ("row", "col") and params[0] % 4:
+            vec_ok = False
+    vec = 4 if vec_ok else 1
+    n_streams = sum(1 for _s, k, _p, _d in em.leaves if k == "full")
+    unroll = 4 if n_streams <= 2 else 2
+    block_row = mode == "rows" and cols >= 8192 and rows < _SMS * 8
+    acc_dt = node.dtype
+    shaped = any(k == "strided" for _s, k, _p, _d in em.leaves)
+    sig = ("reduce", mode, node.op, acc_dt.name, block_row, tuple(shape) if shaped else len(shape),
+           tuple((k, p if k == "strided" else (), d.name) for _s, k, p, d in em.leaves),
+           tuple(em.sig), (expr, src.dtype.name), vec, unroll, trace.fastmath)
+    hit = _kernel_cache.get(sig)
+    if hit is None:
+        hit = _generate(em, results, shape, vec, unroll, [None], trace.fastmath,
+                        reduce=(mode, node.op, acc_dt, block_row))
+        _kernel_cache[sig] = hit
+    blob, kname = hit
+
+    params = []
+    for slot, kind, p, dt in em.leaves:
+        params.append(("slot", slot))
+        if kind in ("row", "col"):
+            params.append(("i64", p[0]))
+    for index, dt in em.scalar_args:
+        params.append(("scalar", index, dt))
+    params.append(("slot", dst))
+    if mode == "rows":
+        units = rows if block_row else (rows + 7) // 8
+        grid = (max(1, min(units, _SMS * 8)),)
+        params += [("i64", rows), ("i64", cols)]
+    elif mode == "cols":
+        gx = (cols + 256 * vec - 1) // (256 * vec)
+        gy = max(1, min((_SMS * 8 + gx - 1) // gx, (rows + 31) // 32, 65535))
+        if gx * 4 > 65536:
+            return False  # more column tiles than ticket counters
+        grid = (gx, gy)
+        params += [("scratch", gy * cols * acc_dt.itemsize), ("i64", rows), ("i64", cols)]
+    else:
+        tile = 256 * vec * unroll
+        grid = (max(1, min((n + tile - 1) // tile, _SMS * 8)),)
+        params += [("scratch", grid[0] * acc_dt.itemsize), ("i64", n)]
+    step = ("launch", blob, kname, grid, (256,), tuple(params))
+    trace.steps.append(step)
+    if not trace.dry:
+        run_launch(trace.queue, step, trace.arrays, trace.args)
+    return True
+
+
 def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, shared_in=frozenset(),
-              shared_out=frozenset()):
-    """CUDA C for one fused chain; returns (tagged source blob, kernel name)."""
+              shared_out=frozenset(), reduce=None):
+    """CUDA C for one fused chain; returns (tagged source blob, kernel name).
+    With `reduce` = (mode, op, accumulator dtype, block_row) the single result
+    is not stored but reduced on the way (nmb::reduce_*_fused)."""
     members, ctor, kparams = [], [], []
     in_fields, loads = [], []
     nd = len(out_shape)
@@ -1385,12 +1494,14 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
     out_fields, stores, out_assign = [], [], []
     for j, (slot, expr, arr) in enumerate(results):
         ct = ctype(arr.dtype)
+        out_fields.append(f"nmb::Vec<{ct}, V> out{j};")
+        out_assign.append(f"o.out{j}.v[l] = {expr};")
+        if reduce is not None:
+            continue
         restrict = "" if j in shared_out else " __restrict__"
         members.append(f"{ct}*{restrict} out{j};")
         kparams.append(f"{ct}*{restrict} out{j}")
         ctor.append(f"out{j}")
-        out_fields.append(f"nmb::Vec<{ct}, V> out{j};")
-        out_assign.append(f"o.out{j}.v[l] = {expr};")
         if ostrides[j] is None:
             stores.append(f"nmb::store_stream<{ct}, V>(out{j} + i, o.out{j});")
         else:  # a strided view: decompose the flat index over the output shape
@@ -1399,9 +1510,39 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
                 body.append(f"off += (rem % {out_shape[d]}ll) * ({ostrides[j][d]}ll); rem /= {out_shape[d]}ll;")
             body.append(f"out{j}[off] = o.out{j}.v[l]; }}")
             stores.append(" ".join(body))
-    kparams.append("int64_t n")
     nl = "\n      "
     funcs = "\n".join(em.funcs.values())
+    if reduce is None:
+        kparams.append("int64_t n")
+        kernel = f"""extern "C" __global__ void __launch_bounds__(256) nmb_fused({', '.join(kparams)}) {{
+  Chain chain{{{', '.join(ctor)}}};
+  nmb::eltwise_tile<256, {vec}, {unroll}>(chain, n);
+}}"""
+        kname = "nmb_fused"
+    else:
+        mode, op, acc_dt, block_row = reduce
+        act = ctype(acc_dt)
+        opc, ident = {"sum": ("nmb::OpAdd", f"{act}(0)"), "prod": ("nmb::OpMul", f"{act}(1)"),
+                      "min": ("nmb::OpMin", f"nmb::neutral_min<{act}>()"),
+                      "max": ("nmb::OpMax", f"nmb::neutral_max<{act}>()")}[op]
+        kname = "nmb_fused_reduce"
+        if mode == "rows":
+            tail = f"{act}* __restrict__ out, int64_t rows, int64_t cols"
+            call = (f"__shared__ {act} scratch[32];\n  nmb::reduce_rows_fused<256, {vec}, {unroll}, "
+                    f"{'true' if block_row else 'false'}>(chain, rows, cols, out, {opc}(), {ident}, scratch);")
+        elif mode == "cols":
+            tail = (f"{act}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t rows, "
+                    "int64_t cols")
+            call = (f"nmb::reduce_cols_fused<256, {vec}, {unroll}>(chain, rows, cols, out, partials, "
+                    f"counters, {opc}(), {ident});")
+        else:
+            tail = f"{act}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t n"
+            call = (f"__shared__ {act} scratch[32];\n  nmb::reduce_all_fused<256, {vec}, {unroll}>(chain, n, "
+                    f"out, partials, counters, {opc}(), {ident}, scratch);")
+        kernel = f"""extern "C" __global__ void __launch_bounds__(256) nmb_fused_reduce({', '.join(kparams + [tail])}) {{
+  Chain chain{{{', '.join(ctor)}}};
+  {call}
+}}"""
     # fastmath: a*b+c may contract and division/sqrt take the approximate
     # instructions (<= 2 ulp), as the reference's fast SPIR-V mode allows
     head = "//NMB200:OPTIONS\n#define NMB_FASTMATH 1" if fastmath else "//NMB200:OPTIONS --fmad=false"
@@ -1427,12 +1568,9 @@ struct Chain {{
     {(nl[:-2]).join(stores)}
   }}
 }};
-extern "C" __global__ void __launch_bounds__(256) nmb_fused({', '.join(kparams)}) {{
-  Chain chain{{{', '.join(ctor)}}};
-  nmb::eltwise_tile<256, {vec}, {unroll}>(chain, n);
-}}
+{kernel}
 """
-    return src.encode(), "nmb_fused"
+    return src.encode(), kname
 
 
 # ------------------------------------------------------------- execution ----
@@ -1445,6 +1583,11 @@ def run_launch(queue, step, arrays, args):
             packed.append(("ptr", arrays[p[1]].ptr))
         elif p[0] == "i64":
             packed.append(np.int64(p[1]))
+        elif p[0] == "scratch":
+            # partials of `p[1]` bytes, then the ticket counters, in the queue's scratch
+            counters, data = queue.scratch(p[1])
+            packed.append(("ptr", data))
+            packed.append(("ptr", counters))
         else:
             packed.append(p[2].type(args[p[1]]))
     queue.launch(kernel, grid, block, packed)

@@ -40,8 +40,9 @@ def test_bitwise_functions_generate_valid_kernels(runtime_lib, src):
 
 @pytest.mark.parametrize("src", suite._reduce_axis_funcs())
 def test_reductions_record_reduce_steps(runtime_lib, src):
-    trace, _launches = _trace_and_compile(eval(src), [((2, 3), np.float32)])
-    assert any(s[0] == "reduce" for s in trace.steps)
+    trace, launches = _trace_and_compile(eval(src), [((2, 3), np.float32)])
+    # a library reduction kernel, or a generated one when a chain feeds the reduction
+    assert any(s[0] == "reduce" for s in trace.steps) or any(s[2] == "nmb_fused_reduce" for s in launches)
 
 
 def test_black_scholes_chain_is_one_kernel(runtime_lib):

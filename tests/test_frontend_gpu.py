@@ -502,3 +502,143 @@ def test_noncontiguous_device_copy(queue):
     d = _dev(a)
     assert np.array_equal(d.T.copy().copy_to_host(), a.T)
     assert np.array_equal(d[::2, 1::3].copy_to_host(), a[::2, 1::3])
+
+
+# ------------------------------------- producers fused into reductions --------
+def _launches(fn, *args):
+    from numba_mlir_b200 import runtime
+
+    before = runtime.launch_count()
+    out = fn(*args)
+    return out, runtime.launch_count() - before
+
+
+def test_reduction_of_an_elementwise_chain_is_one_pass(queue):
+    """np.sqrt(np.square(a).sum(axis=1)) and friends read their inputs once:
+    one reduction kernel over the chain (mlir/tests/test_gpu.py:2198-2224 is
+    the reference's fused form), no temporary for the chain."""
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(12)
+    a = rng.standard_normal((257, 1000)).astype(np.float32)
+    b = rng.standard_normal((257, 1000)).astype(np.float32)
+    da, db = _dev(a), _dev(b)
+
+    norm = nm.njit(lambda x: np.sqrt(np.square(x).sum(axis=1)))
+    norm(da)  # traced; the second call replays the plan
+    got, n = _launches(norm, da)
+    assert n == 2  # the reduction over the chain + the sqrt of the row sums
+    np.testing.assert_allclose(got.copy_to_host(), np.sqrt((a.astype(np.float64) ** 2).sum(1)), rtol=1e-5)
+
+    rowsq = nm.njit(lambda x, out: out.__setitem__(slice(None), np.sum(x * x, axis=1)))
+    out = nm.empty(257, np.float32)
+    rowsq(da, out)
+    _, n = _launches(rowsq, da, out)
+    assert n == 1
+    np.testing.assert_allclose(out.copy_to_host(), (a.astype(np.float64) ** 2).sum(1), rtol=1e-5)
+
+    count = nm.njit(lambda x: (x > 0).sum())
+    count(da)
+    got, n = _launches(count, da)
+    assert n == 1 and int(got.copy_to_host()) == int((a > 0).sum())
+
+    mse = nm.njit(lambda x, y: np.mean((x - y) ** 2))
+    mse(da, db)
+    got, n = _launches(mse, da, db)
+    assert n == 2  # reduction, then the division by the element count
+    np.testing.assert_allclose(float(got.copy_to_host()), np.mean((a.astype(np.float64) - b) ** 2), rtol=1e-5)
+
+    colmin = nm.njit(lambda x, y: np.min(x * y, axis=0))
+    colmin(da, db)
+    got, n = _launches(colmin, da, db)
+    assert n == 1
+    assert np.array_equal(got.copy_to_host(), (a * b).min(axis=0))
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (3, 5), (64, 63), (1000, 8), (5, 40000), (2, 3, 17), (1031,)])
+@pytest.mark.parametrize("op", ["sum", "prod", "min", "max"])
+def test_fused_reductions_match_numpy_on_every_axis(queue, shape, op):
+    """reduce(f(a, b)) against NumPy for the row, column and full forms, ragged
+    sizes, a broadcast operand, integer accumulation in int64."""
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(hash((shape, op)) % 2**32)
+    fn = getattr(np, op)
+    for dtype in (np.float32, np.int32):
+        if dtype == np.int32:
+            a = rng.integers(-3, 4, shape).astype(dtype)
+            b = rng.integers(1, 3, shape[-1:]).astype(dtype)
+        else:
+            a = rng.uniform(0.5, 1.5, shape).astype(dtype)
+            b = rng.uniform(0.9, 1.1, shape[-1:]).astype(dtype)
+        if op == "prod":
+            a = np.where(rng.random(shape) < 0.02, a, dtype(1)).astype(dtype)  # keep products in range
+        for axis in [None] + list(range(len(shape))):
+            got = nm.njit(lambda x, y: fn(x * y + dtype(1), axis=axis))(_dev(a), _dev(b)).copy_to_host()
+            want = fn((a * b + dtype(1)).astype(np.int64 if dtype == np.int32 and op in ("sum", "prod") else dtype),
+                      axis=axis)
+            if dtype == np.int32 or op in ("min", "max"):
+                assert np.array_equal(got, want), (shape, op, axis, dtype)
+            else:
+                np.testing.assert_allclose(got, want, rtol=2e-5)
+    queue.check_status()
+
+
+def test_fused_min_max_ignore_nans_like_the_library_reductions(queue):
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import reduce_ops
+
+    a = np.array([[3.0, np.nan, -1.0, 2.0], [np.nan, np.nan, 5.0, 4.0]], np.float32)
+    da = _dev(a)
+    for op in ("min", "max"):
+        fused = nm.njit(lambda x: getattr(np, op)(x * np.float32(1), axis=1))(da).copy_to_host()
+        plain = reduce_ops.reduce(da, op, 1).copy_to_host()
+        assert np.array_equal(fused, plain)
+
+
+def test_pairwise_distance_through_njit_is_one_contraction(queue):
+    """Config 4 as a user writes it: np.dot inside njit with the norm
+    expansion around it runs as the contraction's packing prepass plus one
+    tensor-core launch (numpy/funcs.py:752-812 routes np.dot to the device
+    gemm; the chain around it is the epilogue)."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import contraction, workloads
+    from oracle import configs as O
+
+    rng = np.random.default_rng(13)
+    x = rng.uniform(0, 1, (1500, 64)).astype(np.float32)
+    y = rng.uniform(0, 1, (700, 64)).astype(np.float32)
+    dx, dy = _dev(x), _dev(y)
+    d = nm.empty((1500, 700), np.float32)
+    workloads.pairwise_distance(dx, dy, d)
+    _, n = _launches(workloads.pairwise_distance, dx, dy, d)
+    assert n == 2
+    want = np.zeros((1500, 700), np.float32)
+    O.pairwise(x, y, want)
+    np.testing.assert_allclose(d.copy_to_host(), want, rtol=1e-5, atol=1e-6)
+    assert np.array_equal(d.copy_to_host(), contraction.pairwise_distance(dx, dy).copy_to_host())
+
+
+def test_product_with_bias_and_scale_epilogues(queue):
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(14)
+    a = rng.standard_normal((300, 40)).astype(np.float32)
+    b = rng.standard_normal((40, 200)).astype(np.float32)
+    bias = rng.standard_normal(200).astype(np.float32)
+    rowb = rng.standard_normal((300, 1)).astype(np.float32)
+    truth = a.astype(np.float64) @ b.astype(np.float64)
+    scale = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+
+    f = nm.njit(lambda p, q, c: np.dot(p, q) + c)
+    got, n = _launches(f, _dev(a), _dev(b), _dev(bias))
+    assert np.all(np.abs(got.copy_to_host() - (truth + bias)) <= 1e-5 * (scale + np.abs(bias)))
+    g = nm.njit(lambda p, q, r, c: r + c - np.float32(0.5) * np.dot(p, q))
+    got = g(_dev(a), _dev(b), _dev(rowb), _dev(bias)).copy_to_host()
+    assert np.all(np.abs(got - (rowb + bias - 0.5 * truth)) <= 1e-5 * (scale + np.abs(bias) + np.abs(rowb)))
+    _, n = _launches(g, _dev(a), _dev(b), _dev(rowb), _dev(bias))
+    assert n == 2  # prepass + contraction: the chain is the epilogue
+    # a chain the epilogue does not cover still works (product, then a kernel)
+    h = nm.njit(lambda p, q: np.exp(np.dot(p, q) * np.float32(0.01)))
+    np.testing.assert_allclose(h(_dev(a), _dev(b)).copy_to_host(), np.exp(truth * 0.01), rtol=1e-4)
+    queue.check_status()
