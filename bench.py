@@ -298,13 +298,13 @@ class AxisReduction(Workload):
         nm.map_host(self.fn, [self.h_in], [self.h_out], queue=self.queue)
 
     def step_device(self):
-        self.fn(self.sets[self.i % len(self.sets)], self.out)
-        self.i += 1
-        if self.dist is not None:
-            # rows are sharded: the per-GPU column minima meet in one all-reduce
-            from numba_mlir_b200 import sharding
+        from numba_mlir_b200 import sharding
 
-            sharding.allreduce(self.out, "min", self.dist)
+        # rows are sharded: inside `across` the column minima of all GPUs meet
+        # in the reduction kernel's last block (one launch per step)
+        with sharding.across(self.dist, self.queue):
+            self.fn(self.sets[self.i % len(self.sets)], self.out)
+        self.i += 1
 
     def check(self, dist=None):
         from oracle import configs as O
@@ -360,12 +360,11 @@ class IntSum(Workload):
         self.i = 0
 
     def step_device(self):
-        self.fn(self.sets[self.i % len(self.sets)], self.out)
-        self.i += 1
-        if self.dist is not None:
-            from numba_mlir_b200 import sharding
+        from numba_mlir_b200 import sharding
 
-            sharding.allreduce(self.out, "sum", self.dist)
+        with sharding.across(self.dist, self.queue):
+            self.fn(self.sets[self.i % len(self.sets)], self.out)
+        self.i += 1
 
     def check(self, dist=None):
         from oracle import configs as O
@@ -489,8 +488,8 @@ class KMeans(Workload):
         if self.dist is not None:
             from numba_mlir_b200 import sharding
 
-            sharding.allreduce(self.sums, "sum", self.dist)
-            sharding.allreduce(self.counts, "sum", self.dist)
+            # sums and counts of all GPUs behind one flag round trip
+            sharding.allreduce_many([(self.sums, "sum"), (self.counts, "sum")], self.dist)
         workloads.kmeans_update(self.cent, self.sums, self.counts)
 
     def check(self, dist=None):
@@ -817,7 +816,13 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
     torch.cuda.set_device(local_rank)
     dist = None
+    numa_node = None
     if world > 1:
+        # before any host buffer exists: this rank's cores and page-locked
+        # memory sit next to its GPU
+        from numba_mlir_b200 import sharding as _sharding
+
+        numa_node = _sharding.bind_host_to_gpu(local_rank)
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -919,7 +924,9 @@ def run_gpu(args):
             rec = {"us_per_step": us, "GB/s": gbs, "frac_of_measured_peak": gbs / world / peak,
                    "frac_of_nominal_8TBs": gbs / world / NOMINAL_HBM_GBS, "timed_blocks": nblocks}
             if coll:
-                rec["exchange"] = ow.exchange + (" by the library's peer-memory kernel, inside the recorded graph"
+                how = ("in the last block of the reduction kernel" if ow.key in ("min_axis0", "int_sum")
+                       else "in one launch of the library's peer-memory kernel")
+                rec["exchange"] = ow.exchange + (f" over peer memory, {how}, inside the recorded graph"
                                                  if peer else " by NCCL (torch.distributed), eager launches")
             if hasattr(ow, "step_e2e"):
                 s = max_over_ranks(time_e2e(ow, barrier, 5))
@@ -984,6 +991,7 @@ def run_gpu(args):
                 "timing": f"median of {blocks} timed blocks of {args.steps} steps (at least {MIN_TIMED_MS:.0f} ms "
                           "of device time in all), CUDA events on the launching stream, max over ranks",
                 "verified": "one step's output equals the CPU oracle's (checked outside the timed region)",
+                "host_numa_node_of_rank0": numa_node,
             },
             "elements_per_s": w.units_per_step * world / (ms_per_step * 1e-3),
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,

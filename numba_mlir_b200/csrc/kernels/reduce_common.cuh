@@ -18,6 +18,7 @@
 #pragma once
 
 #include "bulk_pipe.cuh"
+#include "peer_exchange.cuh"
 
 #include <type_traits>
 
@@ -320,12 +321,20 @@ __device__ __forceinline__ void drain_after_timeout(Smem &sm, int64_t issued) {
 // directly by the merging CTA.  With GuardOut the merging CTA leaves out[0]
 // untouched when any CTA's bounded wait ran out (the status word is set), for
 // callers whose only failure report is that word.
+// With px.world > 1 the elements are one GPU's shard: the merging CTA goes on
+// to all-reduce out[0] across the GPUs (peer_exchange.cuh).
+template <typename R> struct MergeOf {
+  using A = typename R::Acc;
+  __device__ __forceinline__ A operator()(A a, A b) const { return R::merge(a, b); }
+};
+
 template <typename R, bool GuardOut = false>
 __device__ __forceinline__ void reduce_all_body(const typename R::In *__restrict__ a,
                                                 typename R::Out *__restrict__ out,
                                                 typename R::Acc *partials, uint32_t *counter,
                                                 int64_t n, int64_t span, uint32_t *status,
-                                                unsigned char *smem_raw) {
+                                                unsigned char *smem_raw,
+                                                const peer::Args px = peer::Args{nullptr, 0, 0}) {
   using T = typename R::In;
   using Acc = typename R::Acc;
   constexpr int VEC = 16 / sizeof(T);
@@ -397,6 +406,12 @@ __device__ __forceinline__ void reduce_all_body(const typename R::In *__restrict
     if (!GuardOut || load_cg(status) == (uint32_t)kStatusOk)
       out[0] = R::fin(m);
     *counter = 0;
+  }
+  if constexpr (std::is_same<typename R::Acc, typename R::Out>::value) {
+    if (px.world > 1) {
+      __syncthreads();
+      peer::allreduce_block<typename R::Out>(out, 1, px.peers, px.rank, px.world, status, MergeOf<R>());
+    }
   }
 }
 

@@ -228,6 +228,35 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
     drain_after_timeout(sm, issued);
 }
 
+// ------------------------------------------ exchange between the GPUs' shards ---
+// The last word of the 64 KB counter region every queue's scratch starts with.
+constexpr int kExchangeTicket = 16383;
+
+// Called (by every thread) of a CTA that has completed one of the grid's
+// gridDim.x column tiles of `out`.  With an exchange pending, the CTA that
+// completes the last tile all-reduces out[0:n] across the GPUs.
+template <typename R>
+__device__ __forceinline__ void tile_done(typename R::Out *out, int64_t n, uint32_t *grid_ticket,
+                                          const peer::Args px, uint32_t *status) {
+  if constexpr (std::is_same<typename R::Acc, typename R::Out>::value) {
+    if (px.world <= 1)
+      return;
+    __shared__ bool last_tile;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      last_tile = atomicAdd(grid_ticket, 1u) == gridDim.x - 1;
+      if (last_tile)
+        *grid_ticket = 0;
+    }
+    __syncthreads();
+    if (!last_tile)
+      return;
+    __threadfence();
+    peer::allreduce_block<typename R::Out>(out, n, px.peers, px.rank, px.world, status, MergeOf<R>());
+  }
+}
+
 // -------------------------------------------------------- column reduction ---
 // out[c] = reduce(a[:, c]).  Grid (col_tiles, row_blocks) of 256 threads: CTA
 // (x, y) reduces rows [rows*y/Gy, rows*(y+1)/Gy) of the columns
@@ -239,12 +268,17 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
 // Scratch: the level buffers of the merge tree (partials[Gy][cols], then
 // [ceil(Gy/8)][cols], ... down to 2..8 rows) and the ticket counters, which
 // start at zero and are left at zero.
+// With px.world > 1 the rows are one GPU's shard: the CTA that finishes the
+// grid's last column tile (one more ticket, the last word of the counter
+// region) exchanges `out` with the other GPUs' results (peer_exchange.cuh), so
+// the reduction over the sharded axis is this one launch.
 template <typename R>
 __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict__ a,
                                                typename R::Out *__restrict__ out,
                                                typename R::Acc *partials, uint32_t *counters,
                                                int64_t rows, int64_t cols, int64_t ct, int64_t fanin,
-                                               uint32_t *status, unsigned char *smem_raw) {
+                                               uint32_t *status, unsigned char *smem_raw,
+                                               const peer::Args px = peer::Args{nullptr, 0, 0}) {
   using T = typename R::In;
   using Acc = typename R::Acc;
   using Fast = typename R::Fast;
@@ -381,6 +415,7 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
         for (int l = 0; l < VEC; ++l)
           out[c0 + cv * VEC + l] = R::fin(widen(m, l));
     }
+    tile_done<R>(out, cols, counters + kExchangeTicket, px, status);
     return;
   }
 
@@ -413,10 +448,17 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
     }
     __threadfence();
     __syncthreads();
+    __shared__ bool last_block;
     if (tid == 0) {
       const uint32_t arrived = atomicAdd(ticket, 1u) & ~kOutReady;
-      if (arrived == (uint32_t)(Gy - 1))
+      last_block = arrived == (uint32_t)(Gy - 1);
+      if (last_block)
         atomicExch(ticket, 0u); // everyone has read the flag and added its ticket
+    }
+    if (px.world > 1) {
+      __syncthreads();
+      if (last_block)
+        tile_done<R>(out, cols, counters + kExchangeTicket, px, status);
     }
     return;
   }
@@ -496,8 +538,10 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
         }
       }
     }
-    if (top)
+    if (top) {
+      tile_done<R>(out, cols, counters + kExchangeTicket, px, status);
       return;
+    }
     ticket += ngroups;
     level = next;
     idx = grp;

@@ -44,15 +44,42 @@ def _kernel_type(dtype):
         raise TypeError(f"reductions support float32/float64/int32/int64, not {dtype}") from None
 
 
+_NO_PEERS = [("ptr", 0), np.int32(0), np.int32(0)]
+_EXCHANGED_OPS = ("sum", "prod", "min", "max")
+
+
+def _peer_params(q, op, nbytes):
+    """Kernel arguments of the exchange between the GPUs' shards that ends a
+    reduction over the sharded axis (numba_mlir_b200.sharding.across), or the
+    arguments that switch it off.  Returns (params, exchange still owed)."""
+    ex = getattr(q, "shard_exchange", None)
+    if ex is None:
+        return _NO_PEERS, None
+    group = ex.group
+    if op in _EXCHANGED_OPS and group is not None and 0 < nbytes <= ex.slot_bytes:
+        return [("ptr", group.table.ptr), np.int32(group.rank), np.int32(group.world)], None
+    return _NO_PEERS, ex
+
+
 def reduce(a, op, axis=None, out=None):
     """Reduces DeviceArray `a` with `op` over `axis` (None = all elements).
 
-    Returns a DeviceArray; a 0-d one for axis=None."""
+    Returns a DeviceArray; a 0-d one for axis=None.  Inside
+    `numba_mlir_b200.sharding.across(...)` the array is one GPU's shard of rows:
+    a full reduction or a reduction over axis 0 ends with the all-reduce of the
+    GPUs' results, inside the same kernel when the result fits a mailbox slot."""
     if op not in OPS:
         raise ValueError(f"unknown reduction {op}")
     ty = _kernel_type(a.dtype)
     odt = out_dtype(op, a.dtype)
     q = a.queue
+    ex = getattr(q, "shard_exchange", None)
+    if ex is not None:
+        if axis is not None and int(axis) % max(a.ndim, 1) != 0:
+            raise ValueError("inside sharding.across only reductions over axis 0 (the sharded axis) or over "
+                             "all elements are exchanged; reduce along other axes outside it")
+        if op not in _EXCHANGED_OPS:
+            raise ValueError(f"{op} over a sharded axis is not supported (the shards' offsets are needed)")
     if axis is None:
         if a.size == 0:
             raise ValueError("zero-size array to reduction operation")
@@ -101,6 +128,7 @@ def _launch_rows(q, a, out, op, ty, rows, cols):
 
 
 def _launch_cols(q, a, out, op, ty, rows, cols):
+    peers, owed = _peer_params(q, op, out.nbytes)
     k = q.builtin(f"nmb_reduce_cols_{op}_{ty}")
     it = a.dtype.itemsize
     # column slabs of 4 KB: each thread owns one 16-byte column vector and the
@@ -116,12 +144,14 @@ def _launch_cols(q, a, out, op, ty, rows, cols):
         level_rows += n
         n = (n + _COL_FANIN - 1) // _COL_FANIN
         tickets += n
-    if col_tiles * tickets * 4 > q.COUNTER_BYTES:
+    if col_tiles * tickets * 4 > q.COUNTER_BYTES - 4:  # the last word is the exchange's ticket
         raise ValueError("too many column tiles for the counter region")
     counters, partials = q.scratch(max(level_rows, 1) * cols * _acc_bytes(op, a.dtype))
     q.launch(k, (col_tiles, row_blocks), (256,),
              [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
-              _I64(rows), _I64(cols), _I64(tile_cols), _I64(_COL_FANIN), ("ptr", q.status_ptr)])
+              _I64(rows), _I64(cols), _I64(tile_cols), _I64(_COL_FANIN), ("ptr", q.status_ptr)] + peers)
+    if owed is not None:
+        owed.allreduce(out, op)
 
 
 def _launch_all(q, a, out, op, ty):
@@ -129,6 +159,7 @@ def _launch_all(q, a, out, op, ty):
     if a.ptr % 16 != 0:
         _launch_generic(q, a.reshape(n), out, op, ty, 0, 1, n, 1)
         return
+    peers, owed = _peer_params(q, op, out.nbytes)
     k = q.builtin(f"nmb_reduce_all_{op}_{ty}")
     tile = _TILE_BYTES // a.dtype.itemsize
     grid = max(1, min(_CTAS, (n + tile - 1) // tile))
@@ -137,7 +168,9 @@ def _launch_all(q, a, out, op, ty):
     counters, partials = q.scratch(grid * 16)
     q.launch(k, (grid,), (256,),
              [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters),
-              _I64(n), _I64(span), ("ptr", q.status_ptr)])
+              _I64(n), _I64(span), ("ptr", q.status_ptr)] + peers)
+    if owed is not None:
+        owed.allreduce(out, op)
 
 
 def _launch_generic(q, a, out, op, ty, axis, outer, K, inner):
@@ -166,3 +199,6 @@ def _launch_generic(q, a, out, op, ty, axis, outer, K, inner):
     q.launch(k, ((threads + 255) // 256,), (256,),
              [("ptr", src.ptr), ("ptr", out.ptr), _I64(outer), _I64(K), _I64(inner),
               _I64(so), _I64(sk), _I64(si), np.int32(mode)])
+    ex = getattr(q, "shard_exchange", None)
+    if ex is not None:
+        ex.allreduce(out, op)

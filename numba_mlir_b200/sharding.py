@@ -6,13 +6,19 @@ shard along axis 0 -- one process per GPU, every process runs the same
 single-GPU kernels on its rows -- and only three results span shards: a full
 sum, a column-wise min, and the per-cluster sums/counts of a k-means
 iteration.  Those partials are a few KB, so the exchange is latency bound.  On
-GPUs it is one launch of the library's own peer-memory kernel
-(csrc/kernels/peer_allreduce.cu: every rank publishes its partial in a mailbox
-the others map over NVLink, waits for their flags and combines all partials in
-rank order); torch.distributed carries only the one-time exchange of the
-mailbox handles, and remains the path for host arrays (gloo in the CPU tests),
-for partials above 64 KB and when peer mapping is unavailable (NCCL).
+GPUs it is the library's own peer-memory routine (csrc/kernels/peer_exchange.cuh:
+every rank publishes its partial in a mailbox the others map over NVLink,
+waits for their flags and combines all partials in rank order).  Inside
+`across(dist)` the library's reductions over the sharded axis run it in the
+block that finishes the reduction, so reduction and exchange are one launch;
+`allreduce` / `allreduce_many` launch it on its own for partials produced by
+other kernels (one flag round trip for up to four arrays).  torch.distributed
+carries only the one-time exchange of the mailbox handles, and remains the
+path for host arrays (gloo in the CPU tests), for partials above 64 KB and when
+peer mapping is unavailable (NCCL).
 """
+
+import contextlib
 
 import ctypes
 import os
@@ -67,6 +73,62 @@ def allreduce(partial, op="sum", dist=None):
     with torch.cuda.stream(stream):
         dist.all_reduce(_torch_view(partial), op=rop)
     return partial
+
+
+class _ShardExchange:
+    """State a queue carries inside `across`: how reductions over the sharded
+    axis reach the other GPUs' results."""
+
+    slot_bytes = 65536
+
+    def __init__(self, dist, queue):
+        self.dist = dist
+        self.group = peer_group(queue, dist)  # None: NCCL through torch.distributed
+
+    def allreduce(self, out, op):
+        allreduce(out, op, self.dist)
+
+
+@contextlib.contextmanager
+def across(dist, queue=None):
+    """Inside the block, arrays on `queue` are the process's shard of rows of a
+    larger array split over the ranks of `dist`: a full reduction or a reduction
+    over axis 0 (np.sum(a), np.min(a, axis=0) in an `njit` function, or
+    `reduce_ops.reduce`) returns the result over ALL shards, identical on every
+    rank.  Sums, products, minima and maxima whose result fits 64 KB are
+    exchanged by the reduction kernel itself (its last block runs the
+    peer-memory all-reduce); anything else is followed by `allreduce`.  With
+    `dist` None or a world of one the block changes nothing.  Every rank must
+    run the same reductions in the same order."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        yield
+        return
+    from . import runtime as _rt
+
+    queue = queue if queue is not None else _rt.get_queue()
+    previous = getattr(queue, "shard_exchange", None)
+    queue.shard_exchange = _ShardExchange(dist, queue)
+    try:
+        yield
+    finally:
+        queue.shard_exchange = previous
+
+
+def allreduce_many(partials, dist=None):
+    """In-place all-reduce of up to four partial results `[(array, op), ...]`
+    (device arrays on one queue) behind a single flag round trip; falls back to
+    one `allreduce` per array when the peer mailboxes cannot carry them."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return
+    arrays = [a for a, _op in partials]
+    group = peer_group(arrays[0].queue, dist) if arrays and not isinstance(arrays[0], np.ndarray) else None
+    if group is not None and len(partials) <= 4 and all(group.accepts(a) for a in arrays) and \
+            sum(-(-a.nbytes // 16) * 16 for a in arrays) <= PEER_SLOT_BYTES and \
+            all(op in _REDUCE_OPS for _a, op in partials):
+        group.allreduce_many(partials)
+        return
+    for a, op in partials:
+        allreduce(a, op, dist)
 
 
 PEER_SLOT_BYTES = 65536                       # payload of one mailbox slot
@@ -140,6 +202,23 @@ class PeerGroup:
                  [("ptr", partial.ptr), np.int64(partial.size), ("ptr", self.table.ptr),
                   np.int32(self.rank), np.int32(self.world), ("ptr", q.status_ptr)])
 
+    def allreduce_many(self, partials):
+        """One launch for up to four (array, op) pairs: all payloads travel
+        behind one flag."""
+        self.seq += 1
+        q = self.queue
+        k = q.builtin("nmb_peer_allreduce_multi")
+        args = []
+        for i in range(4):
+            if i < len(partials):
+                a, op = partials[i]
+                code = list(_PEER_TYPES).index(a.dtype.name) + 4 * _REDUCE_OPS.index(op)
+                args += [("ptr", a.ptr), np.int64(a.size), np.int32(code)]
+            else:
+                args += [("ptr", 0), np.int64(0), np.int32(0)]
+        q.launch(k, (1,), (1024,), args + [("ptr", self.table.ptr), np.int32(self.rank), np.int32(self.world),
+                                           ("ptr", q.status_ptr)])
+
     def close(self):
         for p in self._opened:
             self._lib.gpuxPeerClose(self.queue.handle, p)
@@ -192,6 +271,47 @@ def _external_stream(queue):
         s = torch.cuda.ExternalStream(int(queue.stream), device=f"cuda:{queue.device}")
         _streams[key] = s
     return s
+
+
+def bind_host_to_gpu(device_index):
+    """Runs this process on the CPU cores next to GPU `device_index` (the cores
+    of the NUMA node its PCIe slot hangs off), so that host buffers allocated
+    afterwards, page-locked ones included, land in that node's memory and the
+    copies of several ranks do not all cross one socket's memory and links.
+    Reads the topology from NVML and sysfs; changes only this process's CPU
+    affinity.  Returns the NUMA node, or None when the topology is not visible
+    (nothing is changed then)."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        idx = int(device_index)
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            ids = [v.strip() for v in visible.split(",") if v.strip()]
+            if idx < len(ids) and ids[idx].isdigit():
+                idx = int(ids[idx])
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(idx)).busId
+        bus = bus.decode() if isinstance(bus, bytes) else bus
+        bus = bus.lower()
+        if len(bus.split(":")[0]) == 8:  # NVML prints an 8-digit PCI domain, sysfs a 4-digit one
+            bus = bus[4:]
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
 
 
 def offset_argmin(local_index, begin):

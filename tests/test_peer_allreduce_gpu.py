@@ -82,6 +82,116 @@ def test_combines_all_ranks_in_rank_order(queue, op, ty):
     queue.check_status()
 
 
+class _FakeGroup:
+    """Stands for sharding.PeerGroup on one GPU: the mailbox table and this
+    process's place among the ranks."""
+
+    def __init__(self, table, rank, world):
+        self.table, self.rank, self.world = table, rank, world
+
+
+class _FakeExchange:
+    slot_bytes = SLOT
+
+    def __init__(self, group):
+        self.group = group
+
+    def allreduce(self, out, op):
+        raise AssertionError("the reduction was expected to carry the exchange itself")
+
+
+def _combine(parts, op):
+    want = parts[0].copy()
+    for p in parts[1:]:  # rank order, the kernel's own order
+        if op == "sum":
+            want = want + p
+        elif op == "min":
+            want = np.where(p < want, p, want)
+        else:
+            want = np.where(want < p, p, want)
+    return want
+
+
+@pytest.mark.parametrize("case", ["min_axis0", "max_axis0_one_row_block", "sum_axis0", "int_sum_all",
+                                  "min_all_f32"])
+def test_reduction_kernels_finish_with_the_exchange(queue, case):
+    """A reduction over the sharded axis inside `sharding.across` is ONE launch:
+    the block that completes the reduction publishes the result, waits for
+    the peers' flags and combines all ranks' results in rank order.  Here the
+    peers' results are posted from the host before the launch."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import reduce_ops, runtime
+
+    world, rank = 3, 1
+    rng = np.random.default_rng(21)
+    boxes = _mailboxes(world)
+    mirrors = [np.zeros(HEADER + 2 * SLOT, np.uint8) for _ in range(world)]
+    table = nm.from_host(np.asarray([b.ptr for b in boxes], np.uint64))
+    queue.shard_exchange = _FakeExchange(_FakeGroup(table, rank, world))
+    try:
+        for seq in (1, 2, 3):
+            if case == "min_axis0":
+                a, op, axis = rng.standard_normal((3000, 4096)).astype(np.float32), "min", 0
+            elif case == "max_axis0_one_row_block":
+                a, op, axis = rng.standard_normal((3, 2048)).astype(np.float32), "max", 0
+            elif case == "sum_axis0":
+                a, op, axis = rng.integers(-9, 10, (2000, 512)).astype(np.int32), "sum", 0
+            elif case == "int_sum_all":
+                a, op, axis = rng.integers(-1000, 1001, 1 << 22).astype(np.int32), "sum", None
+            else:
+                a, op, axis = rng.standard_normal(100003).astype(np.float32), "min", None
+            mine = getattr(np, op)(a.astype(np.int64) if a.dtype == np.int32 else a, axis=axis)
+            mine = np.asarray(mine)
+            parts = [(mine + (r - rank) * 3).astype(mine.dtype) if a.dtype == np.int32
+                     else (mine + np.float32(0.25) * (r - rank) * np.sign(rng.standard_normal(mine.shape))).astype(mine.dtype)
+                     for r in range(world)]
+            parts[rank] = mine
+            for r in range(world):
+                if r != rank:
+                    _post(boxes[r], mirrors[r], seq, np.ascontiguousarray(parts[r]).reshape(-1))
+            before = runtime.launch_count()
+            got = reduce_ops.reduce(nm.from_host(a), op, axis)
+            assert runtime.launch_count() == before + 1
+            assert np.array_equal(got.copy_to_host(), _combine(parts, op))
+        queue.check_status()
+    finally:
+        queue.shard_exchange = None
+
+
+def test_several_partials_behind_one_flag(queue):
+    """nmb_peer_allreduce_multi: float64 sums and int64 counts (a k-means
+    step's partials) plus a float32 minimum in one launch."""
+    import numba_mlir_b200 as nm
+
+    world, rank = 4, 0
+    rng = np.random.default_rng(22)
+    boxes = _mailboxes(world)
+    mirrors = [np.zeros(HEADER + 2 * SLOT, np.uint8) for _ in range(world)]
+    table = nm.from_host(np.asarray([b.ptr for b in boxes], np.uint64))
+    k = queue.builtin("nmb_peer_allreduce_multi")
+    for seq in (1, 2):
+        sums = [rng.standard_normal((64, 16)) * 1e5 for _ in range(world)]
+        counts = [rng.integers(0, 1 << 40, 64) for _ in range(world)]
+        mins = [rng.standard_normal(7).astype(np.float32) for _ in range(world)]
+        for r in range(1, world):
+            payload = np.zeros(64 * 16 * 8 + 64 * 8 + 32, np.uint8)
+            payload[:8192] = sums[r].view(np.uint8).reshape(-1)
+            payload[8192:8704] = counts[r].view(np.uint8)
+            payload[8704:8704 + 28] = mins[r].view(np.uint8)
+            _post(boxes[r], mirrors[r], seq, payload)
+        d_s, d_c, d_m = nm.from_host(sums[0]), nm.from_host(counts[0]), nm.from_host(mins[0])
+        queue.launch(k, (1,), (1024,),
+                     [("ptr", d_s.ptr), np.int64(1024), np.int32(1 + 4 * 0),
+                      ("ptr", d_c.ptr), np.int64(64), np.int32(3 + 4 * 0),
+                      ("ptr", d_m.ptr), np.int64(7), np.int32(0 + 4 * 1),
+                      ("ptr", 0), np.int64(0), np.int32(0),
+                      ("ptr", table.ptr), np.int32(rank), np.int32(world), ("ptr", queue.status_ptr)])
+        assert np.array_equal(d_s.copy_to_host(), _combine(sums, "sum"))
+        assert np.array_equal(d_c.copy_to_host(), _combine(counts, "sum"))
+        assert np.array_equal(d_m.copy_to_host(), _combine(mins, "min"))
+    queue.check_status()
+
+
 def test_missing_peer_runs_out_and_reports(queue):
     """A flag that nothing sets: the wait gives up after its bound (about two
     seconds), the status word is raised and the data are left as they were."""
