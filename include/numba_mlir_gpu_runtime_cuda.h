@@ -101,7 +101,13 @@ void gpuxKernelDestroy(void *kernel);
 void *gpuxLaunchKernel(void *queue, void *kernel, size_t gridX, size_t gridY,
                        size_t gridZ, size_t blockX, size_t blockY,
                        size_t blockZ, void *events, void *params);
-/* GpuRuntime.cpp:412 */
+/* GpuRuntime.cpp:412.  Blocks until the event is reached.  With the
+ * environment variable NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS set to a positive number
+ * the wait is bounded on the host: past that many milliseconds the call
+ * returns with the error set (gpuxGetLastError) and the device work is left
+ * running.  NUMBA_MLIR_GPU_RUNTIME_NVTX=1 wraps every gpux* call in an NVTX
+ * range of its name; NUMBA_MLIR_LOG_GPU_RUNTIME_CALLS=1 prints the
+ * reference's enter/exit lines (GpuRuntime.cpp:29-35,61-82). */
 void gpuxWait(void *queue, void *event);
 /* GpuRuntime.cpp:419 */
 void gpuxDestroyEvent(void *queue, void *event);
@@ -181,6 +187,9 @@ void gpuxQueueSynchronize(void *queue);
  * GpuCommon.hpp:25-27) and its CUDA device ordinal. */
 void *gpuxQueueGetStream(void *queue);
 int gpuxQueueGetDevice(void *queue);
+/* Multiprocessor count of the queue's device (-1 on error); launch shapes are
+ * sized in multiples of it. */
+int gpuxQueueGetSmCount(void *queue);
 /* Device address of a 4-byte status word owned by the queue.  Kernels of this
  * library bound every device-side wait; one that gives up stores a non-zero
  * code here instead of hanging.  Read it back with gpuxMemcpy. */
@@ -190,6 +199,12 @@ const char *gpuxGetLastError(void);
 void gpuxClearLastError(void);
 /* Number of kernels launched by this library since load (all queues). */
 uint64_t gpuxLaunchCount(void);
+/* Test hook, host side only: the next `count` calls this library makes to the
+ * CUDA driver entry point `name` ("cuLaunchKernel", "cuModuleLoadDataEx",
+ * "cuModuleGetFunction") return the CUresult `code` without reaching the
+ * driver; count 0 clears a pending injection.  The reference has no such
+ * hook; its failures abort (numba_mlir_gpu_runtime_sycl/lib/Utils.hpp:8-21). */
+void gpuxTestInjectDriverFault(const char *name, int code, int count);
 
 /* CUDA graphs: gpuxGraphBegin starts recording everything submitted to the
  * queue (nothing runs), gpuxGraphEnd returns a replayable graph handle,

@@ -86,19 +86,21 @@ extern "C" __global__ void __launch_bounds__(kThreads)
     return;
   }
   px::begin(call, peers, rank, world);
+  // everything is pushed before the first wait: the peers' waits overlap
   for (int s = 0; s < 4; ++s)
     if (n[s] > 0)
       with_type_op(code[s] & 3, code[s] >> 2, [&](auto zero, auto) {
         using T = decltype(zero);
-        px::publish(call, rank, static_cast<const T *>(data[s]), n[s], off[s]);
+        px::push(call, rank, world, static_cast<const T *>(data[s]), n[s], off[s]);
       });
-  if (!px::signal_and_wait(call, rank, world, status))
-    return;
-  for (int s = 0; s < 4; ++s)
+  bool ok = true;
+  for (int s = 0; s < 4 && ok; ++s)
     if (n[s] > 0)
       with_type_op(code[s] & 3, code[s] >> 2, [&](auto zero, auto op) {
         using T = decltype(zero);
-        px::combine(call, world, static_cast<T *>(data[s]), n[s], off[s], op);
+        ok = px::pull(call, rank, world, static_cast<T *>(data[s]), n[s], off[s], op, status);
       });
+  if (threadIdx.x == 0)
+    px::end_call(call, rank);
 }
 NMB_REGISTER_KERNEL(nmb_peer_allreduce_multi, 0);

@@ -233,27 +233,37 @@ __device__ __forceinline__ void reduce_rows_ws(const typename R::In *__restrict_
 constexpr int kExchangeTicket = 16383;
 
 // Called (by every thread) of a CTA that has completed one of the grid's
-// gridDim.x column tiles of `out`.  With an exchange pending, the CTA that
-// completes the last tile all-reduces out[0:n] across the GPUs.
+// gridDim.x column tiles of `out`, columns [c0, c0 + ncols).  With an exchange
+// pending, the CTA all-reduces its tile across the GPUs (every tile has its
+// own range of the mailbox payload, so the tiles' exchanges run side by
+// side); the CTA that completes the grid's last tile closes the call.
 template <typename R>
-__device__ __forceinline__ void tile_done(typename R::Out *out, int64_t n, uint32_t *grid_ticket,
+__device__ __forceinline__ void tile_done(typename R::Out *out, int64_t c0, int64_t ncols, uint32_t *grid_ticket,
                                           const peer::Args px, uint32_t *status) {
   if constexpr (std::is_same<typename R::Acc, typename R::Out>::value) {
     if (px.world <= 1)
       return;
+    using Out = typename R::Out;
+    __shared__ peer::Call call;
     __shared__ bool last_tile;
     __threadfence();
+    const unsigned long long off = (unsigned long long)c0 * sizeof(Out);
+    if (!peer::args_ok(px.rank, px.world, off + (unsigned long long)ncols * sizeof(Out))) {
+      if (threadIdx.x == 0)
+        atomicExch(status, (uint32_t)kStatusWaitTimeout);
+      return;
+    }
+    peer::begin(call, px.peers, px.rank, px.world);
+    peer::push(call, px.rank, px.world, out + c0, ncols, off);
+    peer::pull(call, px.rank, px.world, out + c0, ncols, off, MergeOf<R>(), status);
     __syncthreads();
     if (threadIdx.x == 0) {
       last_tile = atomicAdd(grid_ticket, 1u) == gridDim.x - 1;
-      if (last_tile)
+      if (last_tile) {
         *grid_ticket = 0;
+        peer::end_call(call, px.rank);
+      }
     }
-    __syncthreads();
-    if (!last_tile)
-      return;
-    __threadfence();
-    peer::allreduce_block<typename R::Out>(out, n, px.peers, px.rank, px.world, status, MergeOf<R>());
   }
 }
 
@@ -268,10 +278,11 @@ __device__ __forceinline__ void tile_done(typename R::Out *out, int64_t n, uint3
 // Scratch: the level buffers of the merge tree (partials[Gy][cols], then
 // [ceil(Gy/8)][cols], ... down to 2..8 rows) and the ticket counters, which
 // start at zero and are left at zero.
-// With px.world > 1 the rows are one GPU's shard: the CTA that finishes the
-// grid's last column tile (one more ticket, the last word of the counter
-// region) exchanges `out` with the other GPUs' results (peer_exchange.cuh), so
-// the reduction over the sharded axis is this one launch.
+// With px.world > 1 the rows are one GPU's shard: the CTA that finishes a
+// column tile exchanges the tile's results with the other GPUs'
+// (peer_exchange.cuh), so the reduction over the sharded axis is this one
+// launch; one more ticket (the last word of the counter region) tells the last
+// of them to close the call.
 template <typename R>
 __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict__ a,
                                                typename R::Out *__restrict__ out,
@@ -415,7 +426,7 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
         for (int l = 0; l < VEC; ++l)
           out[c0 + cv * VEC + l] = R::fin(widen(m, l));
     }
-    tile_done<R>(out, cols, counters + kExchangeTicket, px, status);
+    tile_done<R>(out, c0, ncols, counters + kExchangeTicket, px, status);
     return;
   }
 
@@ -458,7 +469,7 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
     if (px.world > 1) {
       __syncthreads();
       if (last_block)
-        tile_done<R>(out, cols, counters + kExchangeTicket, px, status);
+        tile_done<R>(out, c0, ncols, counters + kExchangeTicket, px, status);
     }
     return;
   }
@@ -539,7 +550,7 @@ __device__ __forceinline__ void reduce_cols_ws(const typename R::In *__restrict_
       }
     }
     if (top) {
-      tile_done<R>(out, cols, counters + kExchangeTicket, px, status);
+      tile_done<R>(out, c0, ncols, counters + kExchangeTicket, px, status);
       return;
     }
     ticket += ngroups;

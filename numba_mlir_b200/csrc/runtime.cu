@@ -11,6 +11,7 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <dlfcn.h>
 #include <sys/stat.h>
 #include <unistd.h>
@@ -56,19 +57,27 @@ void vsetError(const char *fmt, va_list ap) {
     abort();
 }
 
-// Call tracing, as NUMBA_MLIR_LOG_GPU_RUNTIME_CALLS in GpuRuntime.cpp:29-35.
+// Call tracing, as NUMBA_MLIR_LOG_GPU_RUNTIME_CALLS in GpuRuntime.cpp:29-35;
+// NUMBA_MLIR_GPU_RUNTIME_NVTX=1 wraps every export in an NVTX range of its
+// name instead (or as well), so the calls show up on a profiler's timeline.
 struct FuncLog {
   const char *name;
-  bool on;
+  bool on, nvtx;
   explicit FuncLog(const char *n) : name(n) {
     static bool enabled = envFlag("NUMBA_MLIR_LOG_GPU_RUNTIME_CALLS");
+    static bool ranges = envFlag("NUMBA_MLIR_GPU_RUNTIME_NVTX");
     on = enabled;
+    nvtx = ranges;
     if (on) {
       fprintf(stdout, "%s enter\n", name);
       fflush(stdout);
     }
+    if (nvtx)
+      nvtxRangePushA(name);
   }
   ~FuncLog() {
+    if (nvtx)
+      nvtxRangePop();
     if (on) {
       fprintf(stdout, "%s exit\n", name);
       fflush(stdout);
@@ -133,6 +142,37 @@ DriverApi &driver() {
   });
   return api;
 }
+
+// Host-side failure injection for tests: the next `remaining` calls of the
+// named driver entry point return `code` without reaching the driver.
+struct DriverFault {
+  std::mutex mutex;
+  std::string name;
+  int code = 0;
+  int remaining = 0;
+};
+DriverFault gDriverFault;
+
+// True (and *out set) when the call `name` is to fail by injection.
+bool injectedFault(const char *name, CUresult *out) {
+  if (gDriverFault.remaining <= 0) // unlocked fast path: tests set it before the calls they aim at
+    return false;
+  std::lock_guard<std::mutex> g(gDriverFault.mutex);
+  if (gDriverFault.remaining <= 0 || gDriverFault.name != name)
+    return false;
+  --gDriverFault.remaining;
+  *out = static_cast<CUresult>(gDriverFault.code);
+  return true;
+}
+
+// A driver call that the injection hook can replace.
+#define DRV(fn, ...)                                                           \
+  ([&]() -> CUresult {                                                         \
+    CUresult _inj;                                                             \
+    if (injectedFault("cu" #fn, &_inj))                                        \
+      return _inj;                                                             \
+    return driver().fn(__VA_ARGS__);                                           \
+  }())
 
 const char *cuErr(CUresult r) {
   const char *s = nullptr;
@@ -735,7 +775,7 @@ GPUX_EXPORT void *gpuxModuleLoad(void *queue, const void *data,
   CUjit_option jitOpts[] = {CU_JIT_ERROR_LOG_BUFFER,
                             CU_JIT_ERROR_LOG_BUFFER_SIZE_BYTES};
   void *jitVals[] = {errLog, (void *)(uintptr_t)sizeof(errLog)};
-  CUresult r = driver().ModuleLoadDataEx(&cuMod, image, 2, jitOpts, jitVals);
+  CUresult r = DRV(ModuleLoadDataEx, &cuMod, image, 2, jitOpts, jitVals);
   if (r != CUDA_SUCCESS) {
     nmb::setError("cuModuleLoadDataEx failed: %s\n%s", cuErr(r), errLog);
     return nullptr;
@@ -786,7 +826,7 @@ GPUX_EXPORT void *gpuxKernelGet(void *module, const char *name) {
     k->func = reinterpret_cast<CUfunction>(fn);
     k->dynSmemBytes = found->dynSmemBytes;
   } else {
-    CUresult r = driver().ModuleGetFunction(&k->func, m->cuModule, name);
+    CUresult r = DRV(ModuleGetFunction, &k->func, m->cuModule, name);
     if (r != CUDA_SUCCESS) {
       nmb::setError("kernel '%s' not found in module: %s", name, cuErr(r));
       return nullptr;
@@ -874,7 +914,7 @@ GPUX_EXPORT void *gpuxLaunchKernel(void *queue, void *kernel, size_t gridX,
                     gridX, gridY, gridZ);
       return nullptr;
     }
-    CU_TRY(driver().LaunchKernel(k->func, (unsigned)gridX, (unsigned)gridY,
+    CU_TRY(DRV(LaunchKernel, k->func, (unsigned)gridX, (unsigned)gridY,
                                  (unsigned)gridZ, (unsigned)blockX,
                                  (unsigned)blockY, (unsigned)blockZ,
                                  (unsigned)dynSmem, (CUstream)q->stream, args,
@@ -885,13 +925,47 @@ GPUX_EXPORT void *gpuxLaunchKernel(void *queue, void *kernel, size_t gridX,
   return recordEvent(q);
 }
 
+// Host-side bound on gpuxWait: NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS (read at every
+// call, 0 or unset = wait for as long as it takes, like the reference's
+// event.wait(), GpuRuntime.cpp:395-404).  With a bound the event is polled;
+// when the time runs out the call returns with the sticky error set and the
+// device work is left running.
 GPUX_EXPORT void gpuxWait(void *queue, void *event) {
   LOG_FUNC();
   (void)queue;
   if (!event)
     return;
   Event *e = static_cast<Event *>(event);
-  CUDA_TRY(cudaEventSynchronize(e->ev), return);
+  const char *limit = getenv("NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS");
+  const long ms = limit && *limit ? strtol(limit, nullptr, 10) : 0;
+  if (ms <= 0) {
+    CUDA_TRY(cudaEventSynchronize(e->ev), return);
+    return;
+  }
+  timespec t0;
+  clock_gettime(CLOCK_MONOTONIC, &t0);
+  for (unsigned spins = 0;; ++spins) {
+    cudaError_t st = cudaEventQuery(e->ev);
+    if (st == cudaSuccess)
+      return;
+    if (st != cudaErrorNotReady) {
+      nmb::setError("gpuxWait: cudaEventQuery failed: %s", cudaGetErrorString(st));
+      (void)cudaGetLastError();
+      return;
+    }
+    (void)cudaGetLastError();
+    timespec t1;
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    const double waited = (t1.tv_sec - t0.tv_sec) * 1e3 + (t1.tv_nsec - t0.tv_nsec) * 1e-6;
+    if (waited > (double)ms) {
+      nmb::setError("gpuxWait: the event was not reached within %ld ms "
+                    "(NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS); the device work is still in flight",
+                    ms);
+      return;
+    }
+    if (spins > 1000)
+      usleep(50); // the first polls are back to back: short waits stay short
+  }
 }
 
 GPUX_EXPORT void gpuxDestroyEvent(void *queue, void *event) {
@@ -982,9 +1056,12 @@ GPUX_EXPORT void gpuxDeAlloc(void *queue, void *ptr) {
       cudaFree(ptr);
     else if (type == GPUX_ALLOC_HOST)
       cudaFreeHost(ptr);
-    else
+    else {
+      // not a buffer of this queue (or freed before): it holds no reference
       nmb::setError("gpuxDeAlloc: pointer %p was not allocated by this queue",
                     ptr);
+      return;
+    }
     (void)cudaGetLastError();
   }
   q->release();
@@ -1206,6 +1283,30 @@ GPUX_EXPORT void *gpuxQueueGetStream(void *queue) {
 
 GPUX_EXPORT int gpuxQueueGetDevice(void *queue) {
   return queue ? toQueue(queue)->device : -1;
+}
+
+// Number of multiprocessors of the queue's device (launch shapes are sized in
+// multiples of it); -1 on error.
+GPUX_EXPORT int gpuxQueueGetSmCount(void *queue) {
+  if (!queue) {
+    nmb::setError("gpuxQueueGetSmCount: null queue");
+    return -1;
+  }
+  int n = 0;
+  CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, toQueue(queue)->device), return -1);
+  return n;
+}
+
+// Test hook for host-side failure injection: the next `count` calls of the
+// driver entry point `name` ("cuLaunchKernel", "cuModuleLoadDataEx",
+// "cuModuleGetFunction") made by this library return `code` (a CUresult)
+// without reaching the driver; count 0 clears a pending injection.  Nothing on
+// the device is made to fail.
+GPUX_EXPORT void gpuxTestInjectDriverFault(const char *name, int code, int count) {
+  std::lock_guard<std::mutex> g(gDriverFault.mutex);
+  gDriverFault.name = name ? name : "";
+  gDriverFault.code = code;
+  gDriverFault.remaining = name && count > 0 ? count : 0;
 }
 
 // Device address of the queue's status word: 0 while every bounded device-side

@@ -41,20 +41,21 @@ def check_device_args(args):
     return devs
 
 
-_MAX_PARFOR_BLOCKS = 148 * 32  # the loops are grid-strided: more blocks than this only add launch cost
-
-
-def parfor_launch_shape(extents, inner_parallel):
+def parfor_launch_shape(extents, inner_parallel, sms=148):
     """Launch shape of a prange kernel from the trip counts the host knows
-    (None = unknown).  Returns (None, None) for an empty loop."""
+    (None = unknown) and the device's multiprocessor count.  Returns
+    (None, None) for an empty loop."""
     def ceil_div(a, b):
         return (a + b - 1) // b
+
+    # the loops are grid-strided: more blocks than this only add launch cost
+    _MAX_PARFOR_BLOCKS = sms * 32
 
     n = extents[0]
     if n == 0:
         return None, None
     if not inner_parallel:
-        blocks = 148 * 8 if n is None else min(ceil_div(n, 256), _MAX_PARFOR_BLOCKS)
+        blocks = sms * 8 if n is None else min(ceil_div(n, 256), _MAX_PARFOR_BLOCKS)
         return (blocks,), (256,)
     m = extents[1]
     if m == 0:
@@ -62,7 +63,7 @@ def parfor_launch_shape(extents, inner_parallel):
     bx = 32 if m is None else min(256, 1 << max(0, (m - 1).bit_length()))
     by = 256 // bx
     gx = 8 if m is None else min(ceil_div(m, bx), 1024)
-    gy = 148 if n is None else ceil_div(n, by)
+    gy = sms if n is None else ceil_div(n, by)
     gy = max(1, min(gy, _MAX_PARFOR_BLOCKS // gx, 65535))
     return (gx, gy), (bx, by)
 
@@ -134,7 +135,7 @@ class Dispatcher:
             self._parfor_kernels[key] = ck
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
         kernel = ck.handle_on(queue)
-        grid, block = parfor_launch_shape(ck.extents(args), ck.inner_parallel)
+        grid, block = parfor_launch_shape(ck.extents(args), ck.inner_parallel, queue.sm_count)
         values = kernel_impl.marshal_values(args, ck.param_layout)
         if ck.epilogue is None:
             if grid is not None:

@@ -1356,7 +1356,6 @@ class _ValueHolder:
         self.dtype = np.dtype(dtype)
 
 
-_SMS = 148
 _FUSED_REDUCE_OPS = ("sum", "prod", "min", "max")
 
 
@@ -1404,7 +1403,8 @@ def _emit_reduce_fused(trace, node, mode, dst):
     vec = 4 if vec_ok else 1
     n_streams = sum(1 for _s, k, _p, _d in em.leaves if k == "full")
     unroll = 4 if n_streams <= 2 else 2
-    block_row = mode == "rows" and cols >= 8192 and rows < _SMS * 8
+    sms = 148 if trace.dry else trace.queue.sm_count
+    block_row = mode == "rows" and cols >= 8192 and rows < sms * 8
     acc_dt = node.dtype
     shaped = any(k == "strided" for _s, k, _p, _d in em.leaves)
     sig = ("reduce", mode, node.op, acc_dt.name, block_row, tuple(shape) if shaped else len(shape),
@@ -1427,18 +1427,18 @@ def _emit_reduce_fused(trace, node, mode, dst):
     params.append(("slot", dst))
     if mode == "rows":
         units = rows if block_row else (rows + 7) // 8
-        grid = (max(1, min(units, _SMS * 8)),)
+        grid = (max(1, min(units, sms * 8)),)
         params += [("i64", rows), ("i64", cols)]
     elif mode == "cols":
         gx = (cols + 256 * vec - 1) // (256 * vec)
-        gy = max(1, min((_SMS * 8 + gx - 1) // gx, (rows + 31) // 32, 65535))
+        gy = max(1, min((sms * 8 + gx - 1) // gx, (rows + 31) // 32, 65535))
         if gx * 4 > 65536:
             return False  # more column tiles than ticket counters
         grid = (gx, gy)
         params += [("scratch", gy * cols * acc_dt.itemsize), ("i64", rows), ("i64", cols)]
     else:
         tile = 256 * vec * unroll
-        grid = (max(1, min((n + tile - 1) // tile, _SMS * 8)),)
+        grid = (max(1, min((n + tile - 1) // tile, sms * 8)),)
         params += [("scratch", grid[0] * acc_dt.itemsize), ("i64", n)]
     step = ("launch", blob, kname, grid, (256,), tuple(params))
     trace.steps.append(step)

@@ -15,8 +15,7 @@ from .device_array import empty
 _TY = {np.dtype(np.float32): "f32", np.dtype(np.float64): "f64",
        np.dtype(np.int32): "i32", np.dtype(np.int64): "i64"}
 OPS = ("sum", "prod", "min", "max", "argmin", "argmax")
-SMS = 148  # B200
-_CTAS = SMS * 3  # full reduction: three 65 KB CTAs fit one SM
+_CTAS_PER_SM = 3  # three 65 KB CTAs fit one SM
 _TILE_BYTES = 16384
 _COL_FANIN = 16  # rows merged per ticket of the column merge tree (at most 32)
 _I64 = np.int64
@@ -122,7 +121,7 @@ def _launch_rows(q, a, out, op, ty, rows, cols):
         units = (rows + 7) // 8              # blocks of 8 rows
     else:
         units = (rows + (_TILE_BYTES // (cols * it)) - 1) // (_TILE_BYTES // (cols * it))
-    grid = max(1, min(units, _CTAS))
+    grid = max(1, min(units, q.sm_count * _CTAS_PER_SM))
     q.launch(k, (grid,), (256,),
              [("ptr", a.ptr), ("ptr", out.ptr), _I64(rows), _I64(cols), ("ptr", q.status_ptr)])
 
@@ -136,7 +135,7 @@ def _launch_cols(q, a, out, op, ty, rows, cols):
     tile_cols = min(cols, 4096 // it)
     col_tiles = (cols + tile_cols - 1) // tile_cols
     rows_per_stage = _TILE_BYTES // (tile_cols * it)
-    row_blocks = max(1, min((_CTAS + col_tiles - 1) // col_tiles,
+    row_blocks = max(1, min((q.sm_count * _CTAS_PER_SM + col_tiles - 1) // col_tiles,
                             (rows + rows_per_stage - 1) // rows_per_stage, 65535))
     # merge tree: level buffers and tickets for the fan-in handed to the kernel
     level_rows, tickets, n = 0, 0, row_blocks
@@ -162,7 +161,7 @@ def _launch_all(q, a, out, op, ty):
     peers, owed = _peer_params(q, op, out.nbytes)
     k = q.builtin(f"nmb_reduce_all_{op}_{ty}")
     tile = _TILE_BYTES // a.dtype.itemsize
-    grid = max(1, min(_CTAS, (n + tile - 1) // tile))
+    grid = max(1, min(q.sm_count * _CTAS_PER_SM, (n + tile - 1) // tile))
     span = (n + grid - 1) // grid
     span = (span + tile - 1) // tile * tile
     counters, partials = q.scratch(grid * 16)

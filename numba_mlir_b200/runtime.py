@@ -96,6 +96,8 @@ SIGNATURES = {
     "gpuxQueueSynchronize": (None, [_vp]),
     "gpuxQueueGetStream": (_vp, [_vp]),
     "gpuxQueueGetDevice": (_i, [_vp]),
+    "gpuxQueueGetSmCount": (_i, [_vp]),
+    "gpuxTestInjectDriverFault": (None, [_cp, _i, _i]),
     "gpuxQueueStatusPtr": (_vp, [_vp]),
     "gpuxGetLastError": (_cp, []),
     "gpuxClearLastError": (None, []),
@@ -308,6 +310,7 @@ class Queue:
             check()
             raise GpuRuntimeError("gpuxQueueCreate returned NULL")
         self.device = self.lib.gpuxQueueGetDevice(self.handle)
+        self._sm_count = None
         self._modules = {}
         self._kernels = {}
         self._builtin = None
@@ -315,6 +318,41 @@ class Queue:
         self._scratch = None
         self._scratch_bytes = 0
         self._status = None
+
+    @classmethod
+    def from_stream(cls, stream):
+        """Queue over an existing CUDA stream (an integer cudaStream_t handle,
+        e.g. `torch.cuda.current_stream().cuda_stream`) of the current device:
+        gpuxDuplicateQueue, what generated code gets for a queue it did not
+        create (GpuRuntime.cpp:455-463).  The stream stays the caller's."""
+        self = cls.__new__(cls)
+        self.lib = load()
+        self.handle = self.lib.gpuxDuplicateQueue(ctypes.c_void_p(int(stream)))
+        if not self.handle:
+            check()
+            raise GpuRuntimeError("gpuxDuplicateQueue returned NULL")
+        self.device = self.lib.gpuxQueueGetDevice(self.handle)
+        self._sm_count = None
+        self._modules = {}
+        self._kernels = {}
+        self._builtin = None
+        self._prepared = {}
+        self._scratch = None
+        self._scratch_bytes = 0
+        self._status = None
+        return self
+
+    @property
+    def sm_count(self):
+        """Multiprocessors of the queue's device; launch shapes are sized by it."""
+        n = self._sm_count
+        if n is None:
+            n = self.lib.gpuxQueueGetSmCount(self.handle)
+            if n <= 0:
+                check()
+                raise GpuRuntimeError("gpuxQueueGetSmCount failed")
+            self._sm_count = n
+        return n
 
     # -- modules / kernels ---------------------------------------------------
     def load_module(self, blob):

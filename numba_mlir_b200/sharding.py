@@ -131,8 +131,9 @@ def allreduce_many(partials, dist=None):
         allreduce(a, op, dist)
 
 
-PEER_SLOT_BYTES = 65536                       # payload of one mailbox slot
-PEER_MAILBOX_BYTES = 256 + 2 * PEER_SLOT_BYTES  # two flags (128 B apart) + two slots
+PEER_SLOT_BYTES = 65536                       # payload one call can carry
+# header + 2 slots x 16 source ranks x the payload as tagged 8-byte words
+PEER_MAILBOX_BYTES = 256 + 2 * 16 * 2 * PEER_SLOT_BYTES
 _PEER_TYPES = {"float32": "f32", "float64": "f64", "int32": "i32", "int64": "i64"}
 
 

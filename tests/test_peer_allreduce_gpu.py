@@ -1,9 +1,10 @@
-"""The peer-memory all-reduce kernel (csrc/kernels/peer_allreduce.cu).
+"""The peer-memory all-reduce (csrc/kernels/peer_exchange.cuh, peer_allreduce.cu).
 
 On one GPU the ranks are not run as separate launches (they would wait on one
-another); the peers' mailboxes are filled from the host before the one launch
-under test, which then finds every flag already set.  With two or more GPUs
-the real exchange runs as one process per GPU."""
+another); what the peers would have pushed into this rank's mailbox is written
+there from the host before the one launch under test, which then finds every
+word already tagged.  With two or more GPUs the real exchange runs as one
+process per GPU."""
 
 import os
 import subprocess
@@ -16,22 +17,31 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 HEADER = 256
-SLOT = 65536
+SLOT = 65536            # payload bytes a call can carry
+REGION = 2 * SLOT       # the same payload as tagged 8-byte words
+MAX_RANKS = 16
+MAILBOX = HEADER + 2 * MAX_RANKS * REGION
 
 
 def _mailboxes(world):
     import numba_mlir_b200 as nm
 
-    return [nm.zeros(HEADER + 2 * SLOT, np.uint8) for _ in range(world)]
+    return [nm.zeros(MAILBOX, np.uint8) for _ in range(world)]
 
 
-def _post(box, mirror, seq, payload):
-    """What the rank owning `box` would have published for call `seq`
+def _region(seq, src):
+    return HEADER + ((seq & 1) * MAX_RANKS + src) * REGION
+
+
+def _post(box, mirror, seq, src, payload, off=0):
+    """What rank `src` pushes into the mailbox `box` for call `seq`: every
+    4-byte word of its payload with the call number in the upper half
     (`mirror` is the host copy of the mailbox, kept between calls)."""
-    slot = seq & 1
-    raw = payload.view(np.uint8)
-    mirror[HEADER + slot * SLOT: HEADER + slot * SLOT + raw.size] = raw
-    mirror[slot * 128: slot * 128 + 8] = np.asarray([seq], np.uint64).view(np.uint8)
+    words = np.ascontiguousarray(payload).view(np.uint8).reshape(-1)
+    words = np.concatenate([words, np.zeros(-words.size % 4, np.uint8)]).view(np.uint32)
+    tagged = (np.uint64(seq & 0xFFFFFFFF) << np.uint64(32)) | words.astype(np.uint64)
+    start = _region(seq, src) + 2 * off
+    mirror[start: start + tagged.nbytes] = tagged.view(np.uint8)
     box.copy_from_host(mirror)
 
 
@@ -41,6 +51,18 @@ def _launch(queue, op, ty, data, table, rank, world):
     queue.launch(k, (1,), (1024,),
                  [("ptr", data.ptr), np.int64(data.size), ("ptr", table.ptr), np.int32(rank),
                   np.int32(world), ("ptr", queue.status_ptr)])
+
+
+def _combine(parts, op):
+    want = parts[0].copy()
+    for p in parts[1:]:  # rank order, the kernel's own order
+        if op == "sum":
+            want = want + p
+        elif op == "min":
+            want = np.where(p < want, p, want)
+        else:
+            want = np.where(want < p, p, want)
+    return want
 
 
 _TYPES = {"f32": np.float32, "f64": np.float64, "i32": np.int32, "i64": np.int64}
@@ -55,30 +77,27 @@ def test_combines_all_ranks_in_rank_order(queue, op, ty):
     dt = _TYPES[ty]
     rng = np.random.default_rng(7)
     boxes = _mailboxes(world)
-    mirrors = [np.zeros(HEADER + 2 * SLOT, np.uint8) for _ in range(world)]
+    mirror = np.zeros(MAILBOX, np.uint8)
     table = nm.from_host(np.asarray([b.ptr for b in boxes], np.uint64))
     for seq in (1, 2, 3):  # slots 1, 0, 1: the second use of a slot overwrites the first
         parts = [(rng.standard_normal(n) * 1000).astype(dt) for _ in range(world)]
+        mirror[0:8] = np.asarray([seq - 1], np.uint64).view(np.uint8)  # the rank's own call counter so far
         for r in range(world):
             if r != rank:
-                _post(boxes[r], mirrors[r], seq, parts[r])
+                _post(boxes[rank], mirror, seq, r, parts[r])
         data = nm.from_host(parts[rank])
         _launch(queue, op, ty, data, table, rank, world)
-        want = parts[0].copy()
-        for r in range(1, world):  # rank order, the kernel's own order
-            if op == "sum":
-                want = want + parts[r]
-            elif op == "min":
-                want = np.where(parts[r] < want, parts[r], want)
-            else:
-                want = np.where(want < parts[r], parts[r], want)
-        assert np.array_equal(data.copy_to_host(), want)
-        slot = seq & 1
+        assert np.array_equal(data.copy_to_host(), _combine(parts, op))
         mine = boxes[rank].copy_to_host()
-        assert mine[slot * 128: slot * 128 + 8].view(np.uint64)[0] == seq
-        assert mine[64:72].view(np.uint64)[0] == seq  # the rank's own call counter
-        assert np.array_equal(mine[HEADER + slot * SLOT: HEADER + slot * SLOT + n * dt().itemsize].view(dt),
-                              parts[rank])
+        assert mine[0:8].view(np.uint64)[0] == seq  # the call counter advanced
+        # every peer's mailbox holds this rank's partial as words tagged with the call number
+        for r in range(world):
+            if r != rank:
+                got = boxes[r].copy_to_host()[_region(seq, rank): _region(seq, rank) + 2 * parts[rank].nbytes]
+                got = got.view(np.uint64)
+                assert np.all(got >> np.uint64(32) == seq)
+                assert np.array_equal((got & np.uint64(0xFFFFFFFF)).astype(np.uint32),
+                                      parts[rank].view(np.uint32))
     queue.check_status()
 
 
@@ -100,18 +119,6 @@ class _FakeExchange:
         raise AssertionError("the reduction was expected to carry the exchange itself")
 
 
-def _combine(parts, op):
-    want = parts[0].copy()
-    for p in parts[1:]:  # rank order, the kernel's own order
-        if op == "sum":
-            want = want + p
-        elif op == "min":
-            want = np.where(p < want, p, want)
-        else:
-            want = np.where(want < p, p, want)
-    return want
-
-
 @pytest.mark.parametrize("case", ["min_axis0", "max_axis0_one_row_block", "sum_axis0", "int_sum_all",
                                   "min_all_f32"])
 def test_reduction_kernels_finish_with_the_exchange(queue, case):
@@ -125,7 +132,7 @@ def test_reduction_kernels_finish_with_the_exchange(queue, case):
     world, rank = 3, 1
     rng = np.random.default_rng(21)
     boxes = _mailboxes(world)
-    mirrors = [np.zeros(HEADER + 2 * SLOT, np.uint8) for _ in range(world)]
+    mirror = np.zeros(MAILBOX, np.uint8)
     table = nm.from_host(np.asarray([b.ptr for b in boxes], np.uint64))
     queue.shard_exchange = _FakeExchange(_FakeGroup(table, rank, world))
     try:
@@ -146,9 +153,10 @@ def test_reduction_kernels_finish_with_the_exchange(queue, case):
                      else (mine + np.float32(0.25) * (r - rank) * np.sign(rng.standard_normal(mine.shape))).astype(mine.dtype)
                      for r in range(world)]
             parts[rank] = mine
+            mirror[0:8] = np.asarray([seq - 1], np.uint64).view(np.uint8)
             for r in range(world):
                 if r != rank:
-                    _post(boxes[r], mirrors[r], seq, np.ascontiguousarray(parts[r]).reshape(-1))
+                    _post(boxes[rank], mirror, seq, r, np.ascontiguousarray(parts[r]).reshape(-1))
             before = runtime.launch_count()
             got = reduce_ops.reduce(nm.from_host(a), op, axis)
             assert runtime.launch_count() == before + 1
@@ -166,19 +174,20 @@ def test_several_partials_behind_one_flag(queue):
     world, rank = 4, 0
     rng = np.random.default_rng(22)
     boxes = _mailboxes(world)
-    mirrors = [np.zeros(HEADER + 2 * SLOT, np.uint8) for _ in range(world)]
+    mirror = np.zeros(MAILBOX, np.uint8)
     table = nm.from_host(np.asarray([b.ptr for b in boxes], np.uint64))
     k = queue.builtin("nmb_peer_allreduce_multi")
     for seq in (1, 2):
         sums = [rng.standard_normal((64, 16)) * 1e5 for _ in range(world)]
         counts = [rng.integers(0, 1 << 40, 64) for _ in range(world)]
         mins = [rng.standard_normal(7).astype(np.float32) for _ in range(world)]
+        mirror[0:8] = np.asarray([seq - 1], np.uint64).view(np.uint8)
         for r in range(1, world):
             payload = np.zeros(64 * 16 * 8 + 64 * 8 + 32, np.uint8)
             payload[:8192] = sums[r].view(np.uint8).reshape(-1)
             payload[8192:8704] = counts[r].view(np.uint8)
             payload[8704:8704 + 28] = mins[r].view(np.uint8)
-            _post(boxes[r], mirrors[r], seq, payload)
+            _post(boxes[rank], mirror, seq, r, payload)
         d_s, d_c, d_m = nm.from_host(sums[0]), nm.from_host(counts[0]), nm.from_host(mins[0])
         queue.launch(k, (1,), (1024,),
                      [("ptr", d_s.ptr), np.int64(1024), np.int32(1 + 4 * 0),
@@ -193,7 +202,7 @@ def test_several_partials_behind_one_flag(queue):
 
 
 def test_missing_peer_runs_out_and_reports(queue):
-    """A flag that nothing sets: the wait gives up after its bound (about two
+    """Words that nothing sends: the wait gives up after its bound (about two
     seconds), the status word is raised and the data are left as they were."""
     import numba_mlir_b200 as nm
     from numba_mlir_b200.runtime import GpuRuntimeError

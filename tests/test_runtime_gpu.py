@@ -179,3 +179,111 @@ def test_wait_stream_accepts_default_stream_names(queue):
     queue.wait_stream(2)
     queue.wait_stream(queue.stream or 0)
     queue.synchronize()
+
+
+def test_duplicate_queue_wraps_a_foreign_stream_in_order(queue, runtime_lib):
+    """gpuxDuplicateQueue (GpuRuntime.cpp:455-463 hands generated code a queue
+    over a stream it did not create): work launched on the duplicate runs on
+    torch's current stream, in order with torch's own work on it."""
+    import ctypes
+
+    import torch
+
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import runtime
+
+    stream = torch.cuda.Stream()
+    n = 1 << 22
+    with torch.cuda.stream(stream):
+        t = torch.zeros(n, dtype=torch.float32, device="cuda")
+        for _ in range(20):
+            t += 1.0  # torch work queued on the stream first
+        q2 = runtime.Queue.from_stream(stream.cuda_stream)
+        assert q2.stream == stream.cuda_stream and q2.device == queue.device
+        arr = nm.as_device_array(t, queue=q2)
+        out = nm.empty((), np.float32, q2)
+        from numba_mlir_b200 import reduce_ops
+
+        reduce_ops.reduce(arr, "sum", None, out=out)  # launched through the duplicate: after the adds
+        t += 1.0  # and torch work after it
+        stream.synchronize()
+    assert float(out.copy_to_host()) == 20.0 * n
+    assert float(t[0]) == 21.0
+    del ctypes
+
+
+def test_wait_gives_up_after_the_configured_time(queue, runtime_lib, monkeypatch):
+    """NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS bounds gpuxWait on the host.  The event
+    waited on sits behind a few hundred milliseconds of ordinary work (nothing
+    hangs): with a 1 ms bound the call returns with the error set while the
+    work goes on; without the bound the same wait completes."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import reduce_ops, runtime
+
+    a = nm.zeros(1 << 28, np.int32, queue)  # 1 GiB: about 0.17 ms per reduction
+    out = nm.empty((), np.int64, queue)
+    reduce_ops.reduce(a, "sum", None, out=out)
+    queue.synchronize()
+    for _ in range(1500):
+        reduce_ops.reduce(a, "sum", None, out=out)
+    ev = queue.record()
+    monkeypatch.setenv("NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS", "1")
+    runtime_lib.gpuxWait(queue.handle, ev)
+    with pytest.raises(runtime.GpuRuntimeError, match="not reached within 1 ms"):
+        runtime.check()
+    monkeypatch.setenv("NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS", "60000")
+    queue.wait(ev)  # bounded, long enough
+    monkeypatch.delenv("NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS")
+    queue.wait(ev)
+    queue.destroy_event(ev)
+    assert int(out.copy_to_host()) == 0
+    queue.check_status()
+
+
+def test_injected_driver_faults_are_reported_and_leave_the_queue_usable(queue, runtime_lib):
+    """Host-side failure injection: a driver call made to return CUDA_ERROR_*
+    surfaces as an error of the gpux* call (NULL result + message); the next
+    call works."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import runtime
+
+    CUDA_ERROR_LAUNCH_OUT_OF_RESOURCES, CUDA_ERROR_INVALID_IMAGE, CUDA_ERROR_NOT_FOUND = 701, 200, 500
+    add = nm.njit(lambda a, out: out.__setitem__(slice(None), a + np.float32(1)))
+    a, out = nm.zeros(1000, np.float32, queue), nm.zeros(1000, np.float32, queue)
+    add(a, out)  # compiled and loaded
+    runtime_lib.gpuxTestInjectDriverFault(b"cuLaunchKernel", CUDA_ERROR_LAUNCH_OUT_OF_RESOURCES, 1)
+    with pytest.raises(runtime.GpuRuntimeError, match="too many resources|LaunchKernel"):
+        add(a, out)
+    add(a, out)
+    assert np.all(out.copy_to_host() == 1)
+    src = b"//NMB200:CUDA-SOURCE\nextern \"C\" __global__ void probe_k(int *p) { p[0] = 1; }\n"
+    runtime_lib.gpuxTestInjectDriverFault(b"cuModuleLoadDataEx", CUDA_ERROR_INVALID_IMAGE, 1)
+    q2 = runtime.Queue(f"cuda:{queue.device}")
+    with pytest.raises(runtime.GpuRuntimeError):
+        q2.load_module(src)
+    mod = q2.load_module(src)
+    runtime_lib.gpuxTestInjectDriverFault(b"cuModuleGetFunction", CUDA_ERROR_NOT_FOUND, 1)
+    with pytest.raises(runtime.GpuRuntimeError):
+        q2.get_kernel(mod, "probe_k")
+    assert q2.get_kernel(mod, "probe_k")
+    runtime_lib.gpuxTestInjectDriverFault(None, 0, 0)
+    queue.check_status()
+
+
+def test_double_dealloc_keeps_the_queue_alive(queue, runtime_lib):
+    """A pointer freed twice (or never allocated here) is reported and does not
+    drop a second reference of the queue."""
+    from numba_mlir_b200 import runtime
+
+    q2 = runtime.Queue(f"cuda:{queue.device}")
+    p = q2.alloc(4096)
+    keep = q2.alloc(4096)
+    q2.free(p)
+    q2.free(p)
+    with pytest.raises(runtime.GpuRuntimeError, match="not allocated by this queue"):
+        runtime.check()
+    # the queue still works and still owns `keep`
+    q2.memset(keep, 0, 4096)
+    q2.synchronize()
+    q2.free(keep)
+    assert queue.sm_count >= 1
