@@ -180,11 +180,12 @@ class ArrayRep:
     """C variables describing one array value: data pointer, shape, element
     strides."""
 
-    def __init__(self, name, nbtype):
+    def __init__(self, name, nbtype, index_ctype="int64_t"):
         self.name = name
         self.dtype = nbtype.dtype
         self.ndim = nbtype.ndim
         self.ctype = c_scalar_type(nbtype.dtype)
+        self.index_ctype = index_ctype
         self.ptr = f"{name}_p"
         self.shape = [f"{name}_s{d}" for d in range(self.ndim)]
         self.strides = [f"{name}_t{d}" for d in range(self.ndim)]
@@ -192,7 +193,7 @@ class ArrayRep:
     def decls(self):
         out = [f"{self.ctype}* {self.ptr};"]
         if self.ndim:
-            out.append("int64_t " + ", ".join(self.shape + self.strides) + ";")
+            out.append(f"{self.index_ctype} " + ", ".join(self.shape + self.strides) + ";")
         return out
 
 
@@ -226,13 +227,127 @@ _DIVS = {operator.truediv: "true", operator.itruediv: "true", operator.floordiv:
          operator.pow: "pow", operator.ipow: "pow"}
 
 
+_NARROW_BINOPS = (operator.add, operator.sub, operator.mul, operator.iadd, operator.isub, operator.imul,
+                  operator.floordiv, operator.ifloordiv, operator.mod, operator.imod, operator.and_,
+                  operator.or_, operator.xor, operator.iand, operator.ior, operator.ixor, operator.lshift,
+                  operator.rshift, operator.ilshift, operator.irshift)
+
+
+def index_like_vars(tir):
+    """Names of the integer variables (and tuples, ranges, iterators of them)
+    whose every definition is an index computation: work-item ids and sizes,
+    array shapes, loop counters of ranges over such values, integer constants
+    below 2^31, and sums, products, quotients, shifts, min/max of those.  They
+    can live in 32 bits when the caller promised 32-bit indexing.  Values read
+    from arrays, scalar kernel arguments and results of other calls stay wide.
+    Greatest fixed point: every candidate starts narrow and is dropped when one
+    of its definitions depends on something wide."""
+    from numba.core import ir, types
+
+    from . import kernel_impl as K
+
+    typemap = tir.typemap
+
+    def candidate(name):
+        t = types.unliteral(typemap.get(name))
+        if isinstance(t, types.Integer) and t.bitwidth == 64:
+            return True
+        if isinstance(t, (types.UniTuple, types.Tuple, types.NamedUniTuple)):
+            return len(t.types) > 0 and all(isinstance(types.unliteral(e), types.Integer) for e in t.types)
+        if isinstance(t, (types.RangeType, types.RangeIteratorType)):
+            return True
+        if isinstance(t, types.Pair):
+            return isinstance(types.unliteral(t.first_type), types.Integer)
+        return False
+
+    defs = {}
+    consts = {}
+    for blk in tir.func_ir.blocks.values():
+        for inst in blk.body:
+            if isinstance(inst, ir.Assign):
+                defs.setdefault(inst.target.name, []).append(inst.value)
+                if isinstance(inst.value, (ir.Global, ir.FreeVar, ir.Const)):
+                    consts[inst.target.name] = inst.value.value
+    narrow = {name for name in defs if candidate(name)}
+
+    def small(v):
+        if isinstance(v, (bool, np.bool_)):
+            return True
+        if isinstance(v, (int, np.integer)):
+            return -2**31 < int(v) < 2**31
+        if isinstance(v, tuple):
+            return all(small(x) for x in v)
+        return False
+
+    def ok(var):
+        """`var` (an operand) is narrow, or of a type that fits 32 bits anyway."""
+        if var.name in narrow:
+            return True
+        t = types.unliteral(typemap.get(var.name))
+        return isinstance(t, types.Boolean) or (isinstance(t, types.Integer) and t.bitwidth <= 32)
+
+    def callee(expr):
+        fv = expr.func.name
+        if fv in consts:
+            return consts[fv]
+        t = typemap.get(fv)
+        key = getattr(t, "typing_key", None)
+        if key is None:
+            key = getattr(t, "key", None)
+            if isinstance(key, tuple):
+                key = key[0]
+        return key
+
+    def def_ok(value):
+        if isinstance(value, ir.Arg):
+            return False
+        if isinstance(value, (ir.Global, ir.FreeVar, ir.Const)):
+            return small(value.value)
+        if isinstance(value, ir.Var):
+            return ok(value)
+        if not isinstance(value, ir.Expr):
+            return False
+        op = value.op
+        if op in ("binop", "inplace_binop"):
+            return value.fn in _NARROW_BINOPS and ok(value.lhs) and ok(value.rhs)
+        if op == "unary":
+            return value.fn in (operator.neg, operator.pos, operator.invert) and ok(value.value)
+        if op in ("cast", "exhaust_iter", "getiter", "iternext", "pair_first"):
+            return ok(value.value)
+        if op == "build_tuple":
+            return all(ok(i) for i in value.items)
+        if op in ("getitem", "static_getitem"):
+            st = types.unliteral(typemap.get(value.value.name))
+            return not isinstance(st, types.Array) and ok(value.value)
+        if op == "getattr":
+            st = types.unliteral(typemap.get(value.value.name))
+            return isinstance(st, types.Array) and value.attr in ("shape", "size", "ndim", "strides")
+        if op == "call":
+            fn = callee(value)
+            if fn is range or getattr(fn, "__name__", "") == "prange" or fn in (min, max, abs, int):
+                return all(ok(a) for a in value.args)
+            if fn in K.ID_FUNCS or fn is len:
+                return True
+            return False
+        return False
+
+    changed = True
+    while changed:
+        changed = False
+        for name in list(narrow):
+            if not all(def_ok(v) for v in defs[name]):
+                narrow.discard(name)
+                changed = True
+    return frozenset(narrow)
+
+
 class Translator:
     """Translates one typed function to a C statement list.
 
     mode 'kernel': parameters are the kernel's own, `return` leaves the kernel.
     mode 'device': a `__device__` function returning a scalar."""
 
-    def __init__(self, tir, mode, func_name):
+    def __init__(self, tir, mode, func_name, index32=False):
         from numba.core import ir, types
 
         self.ir = ir
@@ -240,6 +355,13 @@ class Translator:
         self.tir = tir
         self.mode = mode
         self.func_name = func_name
+        # gpu_use_64bit_index=False (numba_mlir/mlir/target.py:176-203; the
+        # reference then types `index` values as i32 in device code,
+        # mlir/lib/Conversion/GpuToGpuRuntime.cpp:976-1030): work-item ids, loop
+        # counters, shapes, strides and whatever is computed from them alone
+        # are 32-bit C variables, and element offsets are 32-bit products.
+        self.index32 = bool(index32)
+        self.narrow = index_like_vars(tir) if self.index32 else frozenset()
         self.typemap = tir.typemap
         self.calltypes = tir.calltypes
         self.cnames = {}
@@ -285,10 +407,11 @@ class Translator:
         types = self.types
         t = types.unliteral(self.vtype(name))
         c = self.cname(name)
+        narrow = name in self.narrow
         if _is_scalar(t):
-            self.decls.append(f"{c_scalar_type(t)} {c};")
+            self.decls.append(f"{'int32_t' if narrow else c_scalar_type(t)} {c};")
         elif isinstance(t, types.Array):
-            rep = ArrayRep(c, t)
+            rep = ArrayRep(c, t, "int32_t" if self.index32 else "int64_t")
             self.arrays[name] = rep
             self.decls.extend(rep.decls())
         elif isinstance(t, (types.UniTuple, types.Tuple, types.NamedUniTuple)):
@@ -296,15 +419,15 @@ class Translator:
             for k, et in enumerate(t.types):
                 if not _is_scalar(et):
                     raise UnsupportedError(f"tuple element type {et}")
-                self.decls.append(f"{c_scalar_type(et)} {c}_e{k};")
+                self.decls.append(f"{'int32_t' if narrow else c_scalar_type(et)} {c}_e{k};")
                 elems.append(f"{c}_e{k}")
             self.tuples[name] = elems
         elif isinstance(t, (types.RangeType, types.RangeIteratorType)):
-            self.decls.append(f"int64_t {c}_a, {c}_b, {c}_c;")
+            self.decls.append(f"{'int32_t' if narrow else 'int64_t'} {c}_a, {c}_b, {c}_c;")
         elif isinstance(t, types.Pair):
             if not _is_scalar(t.first_type):
                 raise UnsupportedError(f"iteration over {t.first_type}")
-            self.decls.append(f"{c_scalar_type(t.first_type)} {c}_v; bool {c}_ok;")
+            self.decls.append(f"{'int32_t' if narrow else c_scalar_type(t.first_type)} {c}_v; bool {c}_ok;")
         # everything else (functions, modules, dtypes, None) lives at compile time
 
     def scalar(self, var, as_type=None):
@@ -354,7 +477,10 @@ class Translator:
             rep = self.arrays[arr_var.name]
         if len(idx_exprs) != rep.ndim:
             raise UnsupportedError("only full scalar indexing of arrays is supported in kernels")
-        off = " + ".join(f"({i}) * {s}" for i, s in zip(idx_exprs, rep.strides)) or "0"
+        if self.index32:
+            off = " + ".join(f"(int32_t)({i}) * {s}" for i, s in zip(idx_exprs, rep.strides)) or "0"
+        else:
+            off = " + ".join(f"({i}) * {s}" for i, s in zip(idx_exprs, rep.strides)) or "0"
         return f"{rep.ptr}[{off}]"
 
     def root_of(self, name):
@@ -390,7 +516,8 @@ class Translator:
         if op in ("binop", "inplace_binop"):
             sig = self.calltypes[value]
             self.declare(tname)
-            out.append(f"{self.cname(tname)} = {self.binop(value.fn, value.lhs, value.rhs, sig)};")
+            out.append(f"{self.cname(tname)} = "
+                       f"{self.binop(value.fn, value.lhs, value.rhs, sig, tname in self.narrow)};")
         elif op == "unary":
             sig = self.calltypes[value]
             a = self.scalar(value.value, sig.args[0])
@@ -483,7 +610,9 @@ class Translator:
         else:
             raise UnsupportedError(f"cannot copy a value of type {ttype}")
 
-    def binop(self, fn, lhs, rhs, sig):
+    def binop(self, fn, lhs, rhs, sig, narrow=False):
+        """C expression of a binary operation; `narrow`: the result is a 32-bit
+        index value (both operands are)."""
         types = self.types
         a = self.scalar(lhs, sig.args[0])
         b = self.scalar(rhs, sig.args[1])
@@ -496,9 +625,13 @@ class Translator:
             return f"nmb::f_div(({c_scalar_type(rt)})({a}), ({c_scalar_type(rt)})({b}))"
         if kind == "floor":
             if isinstance(at, types.Integer):
-                return f"nmb::py_floordiv({a}, {b})"
+                ct = "int32_t" if narrow else c_scalar_type(at)
+                return f"nmb::py_floordiv(({ct})({a}), ({ct})({b}))"
             return ("floorf" if rt.bitwidth == 32 else "floor") + f"(nmb::f_div({a}, {b}))"
         if kind == "mod":
+            if isinstance(at, types.Integer):
+                ct = "int32_t" if narrow else c_scalar_type(at)
+                return f"nmb::py_mod(({ct})({a}), ({ct})({b}))"
             return f"nmb::py_mod({a}, {b})"
         if kind == "pow":
             if isinstance(rt, types.Integer):
@@ -961,7 +1094,7 @@ class CompiledKernel:
 _STATIC_SHARED_LIMIT = 48 * 1024
 
 
-def compile_kernel(py_func, args, ndim, fastmath=False):
+def compile_kernel(py_func, args, ndim, fastmath=False, index32=False, max_threads=None):
     """@kernel body + concrete arguments -> CompiledKernel (tagged CUDA source).
 
     The grid mapping is the reference's: get_global_id(d) is
@@ -972,7 +1105,7 @@ def compile_kernel(py_func, args, ndim, fastmath=False):
     tir = typed_ir(py_func, argtypes)
     from numba.core import types
 
-    tr = Translator(tir, "kernel", "nmb_kernel")
+    tr = Translator(tir, "kernel", "nmb_kernel", index32=index32)
     pnames = [f"p{i}" for i in range(len(argtypes))]
     body = tr.translate(pnames)
     written = {int(r[6:-1]) for r in tr.written_params if r.startswith("<param")}
@@ -1176,7 +1309,7 @@ def _extent_fn(tr, defs, call_expr):
     return trip
 
 
-def compile_parfor(py_func, args, fastmath=False):
+def compile_parfor(py_func, args, fastmath=False, index32=False):
     """njit function with `prange` loops -> one CUDA kernel.
 
     The reference turns every parallel loop nest of an njit function into a
@@ -1199,7 +1332,7 @@ def compile_parfor(py_func, args, fastmath=False):
         raise UnsupportedError(
             f"{py_func.__name__}: a function with prange loops returns None or a scalar (array "
             "results go to array arguments)")
-    tr = Translator(tir, "parfor", "nmb_parfor")
+    tr = Translator(tir, "parfor", "nmb_parfor", index32=index32)
     ir = tr.ir
     blocks = tir.func_ir.blocks
     cfg = compute_cfg_from_blocks(blocks)

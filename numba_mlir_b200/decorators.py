@@ -21,7 +21,8 @@ from .device_array import DeviceArray, as_device_array
 # parallel, fastmath, gpu_fp64_truncate, gpu_use_64bit_index,
 # enable_gpu_pipeline, mlir_force_inline, mlir_vectorize, cache, inline,
 # boundscheck, nogil, locals, nopython, forceobj.  B200 has native fp64, so
-# gpu_fp64_truncate has nothing to do.
+# gpu_fp64_truncate has nothing to do.  gpu_use_64bit_index=False makes the
+# index arithmetic of `prange` and `@kernel` code 32-bit (codegen_ir.index_like_vars).
 
 
 def _wrap_arg(a):
@@ -79,6 +80,8 @@ class Dispatcher:
         self._plans = {}
         self._parfor = None
         self._parfor_kernels = {}
+        self._split = True if options.get("split_parfors") else None
+        self._split_func = None
 
     def __call__(self, *args, **kwargs):
         if kwargs:
@@ -90,8 +93,7 @@ class Dispatcher:
             from . import codegen_ir
 
             if codegen_ir.uses_prange(self.py_func):
-                raise TypeError(f"{self.py_func.__name__}: a function with prange loops cannot be "
-                                "called from an array-expression function")
+                return self._call_parfor_in_trace(lazy.current_trace(), args)
             return self.py_func(*args)
         args = tuple(_wrap_arg(a) for a in args)
         devs = check_device_args(args)
@@ -109,7 +111,20 @@ class Dispatcher:
 
             self._parfor = codegen_ir.uses_prange(self.py_func)
         if self._parfor:
-            return self._call_parfor(args)
+            from . import codegen_ir, parfor_split
+
+            if self._split is None:
+                self._split = parfor_split.count_outer_prange_loops(self.py_func) > 1
+            if not self._split:
+                try:
+                    return self._call_parfor(args)
+                except codegen_ir.UnsupportedError:
+                    # loops mixed with array expressions or host-side code: cut the
+                    # loops out and run the rest as a traced function
+                    if parfor_split.count_outer_prange_loops(self.py_func) < 1:
+                        raise
+                    self._split = True
+            return self._call_split(args)
         key = lazy.signature_of(args)
         plan = self._plans.get(key) if key is not None else None
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
@@ -131,7 +146,8 @@ class Dispatcher:
         ck = self._parfor_kernels.get(key)
         if ck is None:
             ck = codegen_ir.compile_parfor(self.py_func, args,
-                                           fastmath=bool(self.options.get("fastmath", False)))
+                                           fastmath=bool(self.options.get("fastmath", False)),
+                                           index32=not self.options.get("gpu_use_64bit_index", True))
             self._parfor_kernels[key] = ck
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
         kernel = ck.handle_on(queue)
@@ -155,6 +171,51 @@ class Dispatcher:
         host = np.zeros(1, ck.return_dtype)
         queue.memcpy(host.ctypes.data, ret, host.nbytes, _rt.COPY_D2H, wait=True)
         return host[0]
+
+    def _call_split(self, args):
+        """Several parallel loops, or loops next to array expressions: every
+        outermost `prange` loop is its own kernel, the code between them runs
+        here on the host (mlir_compiler/lib/pipelines/LowerToGpu.cpp:742-940
+        makes one `gpu.launch` per loop nest)."""
+        from . import parfor_split
+
+        if self._split_func is None:
+            opts = {k: v for k, v in self.options.items() if k != "split_parfors"}
+            try:
+                self._split_func, _n = parfor_split.split(self.py_func, lambda f: Dispatcher(f, opts))
+            except parfor_split.SplitError as e:
+                raise TypeError(str(e)) from None
+        queue = next(a.queue for a in args if isinstance(a, DeviceArray))
+        result, _plan = lazy.trace_call(self._split_func, args, queue,
+                                        fastmath=bool(self.options.get("fastmath", False)))
+        return result
+
+    def _call_parfor_in_trace(self, trace, args):
+        """A loop function called while an array-expression function is being
+        traced: its operands are evaluated, the loop's kernel is launched, and
+        its scalar result (if any) comes back as a host value."""
+        if trace.dry:
+            raise TypeError("prange loops cannot be traced without a device")
+        real = []
+        for a in args:
+            if isinstance(a, lazy.LazyArray):
+                if a.shape == () and a.concrete is not None and a.node.kind != "leaf":
+                    real.append(a.concrete)
+                    continue
+                slot = trace.materialize(a)
+                arr = trace.arrays[slot]
+                if a.shape == ():
+                    real.append(arr.copy_to_host()[()])  # a device scalar: the loop takes its value
+                else:
+                    trace.before_direct_write(slot)  # the loop may write it
+                    real.append(arr)
+            else:
+                real.append(a)
+        trace.value_dependent = True  # the launch is not part of a replayable plan
+        trace.flush()
+        if not any(isinstance(a, DeviceArray) for a in real):
+            raise TypeError(f"{self.py_func.__name__}: a prange loop needs at least one device array")
+        return self._call_parfor(tuple(real))
 
     def trace_dry(self, *args):
         """Records the plan and generates the kernels without a device (used
@@ -182,9 +243,15 @@ def njit(*args, **kws):
     return jit(*args, **kws)
 
 
-# Numba keeps control and only parfors are offloaded in the reference
-# (decorators.py:84-104); with no host compiler here it is the same dispatcher.
-njit_replace_parfors = njit
+def njit_replace_parfors(*args, **kws):
+    """Only the parallel loops are offloaded; the code around them stays with
+    the host (mlir_njit_replace_parfors, decorators.py:84-104, where Numba
+    keeps control and numba_mlir/mlir/passes.py:332-416 hands each parfor to the
+    MLIR pipeline).  Every outermost `prange` loop of the function becomes its
+    own kernel and the rest of the body runs on the host around them, whatever
+    the number of loops; functions without loops behave as under `njit`."""
+    kws["split_parfors"] = True
+    return njit(*args, **kws)
 
 
 class Vectorized:

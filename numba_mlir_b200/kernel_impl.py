@@ -357,7 +357,8 @@ class Kernel:
         ck = self._compiled.get(key)
         if ck is None:
             ck = codegen_ir.compile_kernel(self.py_func, args, ndim,
-                                           fastmath=bool(self.options.get("fastmath", False)))
+                                           fastmath=bool(self.options.get("fastmath", False)),
+                                           index32=not self.options.get("gpu_use_64bit_index", True))
             self._compiled[key] = ck
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
         kernel = ck.handle_on(queue)

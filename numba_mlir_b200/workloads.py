@@ -123,7 +123,7 @@ _KM_COLS = _KM_PH * _KM_D  # accumulator columns per cluster: phases x dimension
 KMEANS_LOCAL_SIZE = 256
 
 
-@kernel
+@kernel(gpu_use_64bit_index=False)  # 2^22 x 16 elements: every offset fits 32 bits
 def _kmeans_kernel(points, centroids, labels, sums, counts):
     lid = get_local_id(0)
     lsz = get_local_size(0)
@@ -216,7 +216,7 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
 
 # The same iteration in the plain form: one point per work-item, every point
 # adds itself to its cluster's sum and count with global atomics.
-@kernel
+@kernel(gpu_use_64bit_index=False)
 def _kmeans_naive_kernel(points, centroids, labels, sums, counts):
     i = get_global_id(0)
     best = 0

@@ -187,3 +187,38 @@ def test_plan_key_sees_overlapping_arguments():
     b = lazy.fake_array((64,), np.float32)
     assert lazy.signature_of((a, b)) != lazy.signature_of((a, a))
     assert lazy.signature_of((a[1:], a[:-1])) != lazy.signature_of((a[1:], b[:-1]))
+
+
+# ------------------------------------------------ gpu_use_64bit_index=False ---
+def test_32bit_index_mode_narrows_index_values_only(runtime_lib):
+    """With gpu_use_64bit_index=False ids, loop counters, shapes and what is
+    computed from them are 32-bit C variables; values read from arrays and
+    scalar arguments keep their 64 bits
+    (numba_mlir/mlir/lib/Conversion/GpuToGpuRuntime.cpp:976-1030 types `index`
+    as i32 under that flag)."""
+    import re
+
+    from numba_mlir_b200 import codegen_ir, lazy, runtime
+    from numba_mlir_b200.kernel import get_global_id
+
+    def body(a, table, big, out):
+        i = get_global_id(0)
+        n = a.shape[0]
+        acc = 0
+        for j in range(n // 4):
+            acc += table[(i + j) % n]      # a value read from an int64 array: wide
+        out[i] = acc + big                 # big: a scalar int64 argument: wide
+
+    args = [lazy.fake_array((64,), np.float32), lazy.fake_array((64,), np.int64), np.int64(1 << 40),
+            lazy.fake_array((64,), np.int64)]
+    wide = codegen_ir.compile_kernel(body, args, 1).source
+    narrow = codegen_ir.compile_kernel(body, args, 1, index32=True).source
+    assert "int32_t v" not in wide
+    decl = {m.group(2): m.group(1) for m in re.finditer(r"\b(int32_t|int64_t) (v\d+_\w+?)(?:, |;)", narrow)}
+    kinds = {name.split("_", 1)[1]: ct for name, ct in decl.items()}
+    assert kinds["i"] == "int32_t" and kinds["n"] == "int32_t"
+    assert any(k.startswith("j") and ct == "int32_t" for k, ct in kinds.items())
+    assert any(k.startswith("acc") and ct == "int64_t" for k, ct in kinds.items())
+    assert "(int32_t)(" in narrow and "int32_t v1_table_s0" in narrow.replace("  ", " ")
+    for src in (wide, narrow):
+        assert len(runtime.compile_to_cubin(src)) > 0

@@ -232,3 +232,168 @@ def test_prange_reduction_with_start_value_product_and_tail_store(queue):
     from numba_mlir_b200 import reduce_ops
 
     assert reduce_ops.reduce(_dev(a), "sum").copy_to_host() == a.sum()
+
+
+def test_use_64bit_index_prange_and_kernel(queue):
+    """mlir/tests/test_gpu.py:1788-1898: the same program under
+    gpu_use_64bit_index True, False and the default gives the same array; with
+    False the generated code carries 32-bit index arithmetic."""
+    import numba
+
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200.kernel import get_global_id, kernel
+
+    def py_func(a):
+        ah, aw = a.shape
+        for h in numba.prange(ah):
+            for w in numba.prange(aw):
+                a[h, w] = w + h * aw
+
+    def kern(a):
+        aw = a.shape[1]
+        h = get_global_id(0)
+        w = get_global_id(1)
+        a[h, w] = w + h * aw
+
+    for shape in ((6, 8), (257, 1031)):
+        want = np.arange(shape[0] * shape[1], dtype=np.float32).reshape(shape)
+        for opts in ({}, {"gpu_use_64bit_index": True}, {"gpu_use_64bit_index": False}):
+            d = nm.zeros(shape, np.float32)
+            nm.njit(py_func, **opts)(d)
+            assert np.array_equal(d.copy_to_host(), want), opts
+            d = nm.zeros(shape, np.float32)
+            kernel(kern, **opts)[shape, ()](d)
+            assert np.array_equal(d.copy_to_host(), want), opts
+    queue.check_status()
+
+
+def test_kmeans_kernel_with_32bit_indices_keeps_labels(queue):
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import workloads
+    from numba_mlir_b200.kernel import kernel
+    from oracle import configs as O
+
+    pts, c0 = O.make_inputs("kmeans", 1 / 64)
+    n = pts.shape[0]
+    labels = nm.zeros(n, np.int32)
+    sums, counts = nm.zeros((64, 16), np.float64), nm.zeros(64, np.int64)
+    k32 = kernel(workloads._kmeans_kernel.py_func, gpu_use_64bit_index=False)
+    k32[n // 8, workloads.KMEANS_LOCAL_SIZE](nm.from_host(pts), nm.from_host(c0), labels, sums, counts)
+    want = np.zeros(n, np.int32)
+    O.kmeans_assign(pts, c0, want)
+    assert np.array_equal(labels.copy_to_host(), want)
+    ws, wc = np.zeros((64, 16)), np.zeros(64, np.int64)
+    O.kmeans_accumulate(pts, want, ws, wc)
+    assert np.array_equal(counts.copy_to_host(), wc)
+    np.testing.assert_allclose(sums.copy_to_host(), ws, rtol=1e-12, atol=1e-8)
+
+
+# --------------------- several loops per function, loops next to expressions ---
+def _launched(fn, *args):
+    from numba_mlir_b200 import runtime
+
+    before = runtime.launch_count()
+    res = fn(*args)
+    return res, runtime.launch_count() - before
+
+
+def test_two_parallel_loops_are_two_kernels(queue):
+    """One `gpu.launch` per parallel loop nest of a function
+    (mlir_compiler/lib/pipelines/LowerToGpu.cpp:742-940); the scalar the second
+    loop carries out comes back to the host."""
+    import numba
+
+    import numba_mlir_b200 as nm
+
+    def py_func(a, b, out):
+        n = len(a)
+        for i in numba.prange(n):
+            out[i] = a[i] * 2 + b[i]
+        total = 0.0
+        for i in numba.prange(n):
+            total += out[i]
+        return total
+
+    rng = np.random.default_rng(3)
+    a = rng.integers(-5, 6, 5000).astype(np.float32)
+    b = rng.integers(-5, 6, 5000).astype(np.float32)
+    want = np.zeros_like(a)
+    want_total = py_func(a, b, want)
+    f = nm.njit(py_func)
+    out = nm.zeros(5000, np.float32)
+    f(_dev(a), _dev(b), out)
+    (total, n) = _launched(f, _dev(a), _dev(b), out)
+    assert n == 2
+    assert np.array_equal(out.copy_to_host(), want) and total == want_total
+
+
+def test_loops_mixed_with_array_expressions_and_host_scalars(queue):
+    import numba
+
+    import numba_mlir_b200 as nm
+
+    def py_func(a, w, out):
+        scaled = a * w                      # array expression
+        m = 0.0
+        for i in numba.prange(a.shape[0]):  # loop reading the expression's value
+            m = max(m, scaled[i])
+        if m > 100.0:                       # host control flow on the loop's result
+            m = 100.0
+        for i in numba.prange(a.shape[0]):
+            out[i] = scaled[i] / m
+        out[:] = out + np.float32(1)        # array expression after the loops
+        return m
+
+    rng = np.random.default_rng(4)
+    a = rng.uniform(1, 9, 3000).astype(np.float32)
+    for w in (np.float32(2.0), np.float32(50.0)):
+        want = np.zeros_like(a)
+        scaled = a * w
+        m = min(float(scaled.max()), 100.0)
+        want = (scaled / np.float32(m)).astype(np.float32) + np.float32(1)
+        out = nm.zeros(3000, np.float32)
+        got_m = nm.njit(py_func)(_dev(a), w, out)
+        assert float(got_m) == m
+        np.testing.assert_allclose(out.copy_to_host(), want, rtol=1e-6)
+
+
+def test_njit_replace_parfors_offloads_only_the_loops(queue):
+    """mlir_njit_replace_parfors (decorators.py:84-104): the loops go to the
+    device, the code around them stays on the host, also when there is only
+    one loop and host code before it stores to an array."""
+    import numba
+
+    import numba_mlir_b200 as nm
+
+    @nm.njit_replace_parfors(parallel=True)
+    def f(a, out):
+        out[:] = a - np.float32(1)          # a store before the loop: rejected when the whole
+        s = 0.0                             # function is one kernel, fine when only the loop is
+        for i in numba.prange(a.shape[0]):
+            s += out[i] * out[i]
+        return s
+
+    a = np.arange(1, 2001, dtype=np.float32)
+    out = nm.zeros(2000, np.float32)
+    s = f(_dev(a), out)
+    assert np.array_equal(out.copy_to_host(), a - 1)
+    assert s == float(((a - 1).astype(np.float64) ** 2).sum())
+
+
+def test_loop_function_carrying_two_scalars_is_refused_clearly(queue):
+    import numba
+
+    import numba_mlir_b200 as nm
+
+    def py_func(a, out):
+        s = 0.0
+        t = 0.0
+        for i in numba.prange(a.shape[0]):
+            s += a[i]
+            t += a[i] * 2
+        for i in numba.prange(a.shape[0]):
+            out[i] = s + t
+        return s
+
+    with pytest.raises(TypeError, match="several scalars"):
+        nm.njit(py_func)(_dev(np.ones(8, np.float32)), nm.zeros(8, np.float32))
