@@ -21,6 +21,10 @@ CSRC = os.path.join(HERE, "csrc")
 BUILD = os.path.join(CSRC, "build")
 LIB_NAME = "libnumba_mlir_gpu_runtime_cuda.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
+# CPython extension with the native launch path of the Python front end
+# (argument unboxing + GPUParamDesc + launch); plain C++, no CUDA.
+FASTCALL_SRC = os.path.join(CSRC, "fastcall", "fastcall.cpp")
+FASTCALL_PATH = os.path.join(HERE, "_fastcall.so")
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # -fmad=false: a*b+c is contracted only under fastmath in the reference
@@ -86,6 +90,27 @@ def _write_device_header_inc():
             f.write(body)
 
 
+def build_fastcall(force=False):
+    """Compiles the `_fastcall` extension next to the package; returns its path."""
+    import sysconfig
+
+    if (not force and os.path.exists(FASTCALL_PATH)
+            and os.path.getmtime(FASTCALL_PATH) > os.path.getmtime(FASTCALL_SRC)
+            and os.path.getmtime(FASTCALL_PATH) > os.path.getmtime(os.path.abspath(__file__))):
+        return FASTCALL_PATH
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        raise RuntimeError("g++ not found; the native launch path cannot be built")
+    tmp = FASTCALL_PATH + ".tmp"
+    cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall",
+           "-I", sysconfig.get_paths()["include"], FASTCALL_SRC, "-o", tmp]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("building _fastcall failed:\n%s\n%s" % (proc.stdout, proc.stderr))
+    os.replace(tmp, FASTCALL_PATH)
+    return FASTCALL_PATH
+
+
 def needs_build():
     if not os.path.exists(LIB_PATH):
         return True
@@ -95,7 +120,9 @@ def needs_build():
 
 
 def build(force=False, verbose=False):
-    """Compiles and links the runtime library; returns its path."""
+    """Compiles and links the runtime library (and the `_fastcall` extension);
+    returns the library's path."""
+    build_fastcall(force)
     if not force and not needs_build():
         return LIB_PATH
     os.makedirs(BUILD, exist_ok=True)

@@ -1072,6 +1072,23 @@ class CompiledKernel:
             self._kinds[trailing_int64] = k
         return k
 
+    def layout_code(self):
+        """The argument layout as the native launch path reads it: per array
+        'A', its rank, 'C' (shape follows the pointer) or 'S' (shape and
+        element strides follow); per scalar its type letter."""
+        code = getattr(self, "_layout_code", None)
+        if code is None:
+            from .runtime import param_code
+
+            parts = []
+            for lay in self.param_layout:
+                if lay[0] == "array":
+                    parts.append(b"A" + bytes([lay[1]]) + (b"C" if lay[2] == "C" else b"S"))
+                else:
+                    parts.append(param_code(lay[1]))
+            code = self._layout_code = b"".join(parts)
+        return code
+
     def handle_on(self, queue):
         """Kernel handle on `queue`, loading the module on first use."""
         h = self._handles.get(queue)

@@ -78,6 +78,7 @@ class Dispatcher:
         self.py_func = py_func
         self.options = dict(options)
         self._plans = {}
+        self._native_plans = {}
         self._parfor = None
         self._parfor_kernels = {}
         self._split = True if options.get("split_parfors") else None
@@ -86,6 +87,14 @@ class Dispatcher:
     def __call__(self, *args, **kwargs):
         if kwargs:
             raise TypeError("keyword arguments are not supported in offloaded calls")
+        if self._native_plans and lazy.current_trace() is None:
+            # a call seen before whose plan is launches over its own arguments: the
+            # key, the pointers and the launches are all handled natively
+            key = _rt.fastcall().signature(args, DeviceArray)
+            if key is not None:
+                plan = self._native_plans.get(key)
+                if plan is not None:
+                    return plan.replay_native(args, next(a for a in args if type(a) is DeviceArray).queue)
         if lazy.current_trace() is not None:
             # called from another offloaded function that is being traced: the
             # body joins the caller's trace (the reference inlines nested njit
@@ -134,6 +143,8 @@ class Dispatcher:
                                         fastmath=bool(self.options.get("fastmath", False)))
         if plan is not None and key is not None:
             self._plans[key] = plan
+            if plan.native_ok:
+                self._native_plans[key] = plan
         return result
 
     def _call_parfor(self, args):

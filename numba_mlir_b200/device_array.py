@@ -68,6 +68,7 @@ class DeviceArray:
         self.dtype = np.dtype(dtype)
         self.strides = tuple(strides) if strides is not None else _c_strides(self.shape, self.dtype.itemsize)
         self._offset = int(offset)
+        self._addr = (buffer.ptr or 0) + self._offset  # device address, read by the native launch path
         self._contig = None if strides is not None else True
         self._call_sig = None
         self._trace_sig = None

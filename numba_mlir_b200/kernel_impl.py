@@ -11,6 +11,8 @@ the body can be type-inferred, and codegen_ir lowers them to CUDA.
 import copy
 
 import numpy as np
+
+from . import runtime as _rt
 from numba.core import types
 from numba.core.typing.templates import AbstractTemplate, ConcreteTemplate, infer_global, signature
 
@@ -369,10 +371,16 @@ class Kernel:
         grid = tuple((g + l - 1) // l for g, l in zip(self.global_size, local))
         if any(g == 0 for g in self.global_size):
             return
-        vals = marshal_values(args, ck.param_layout)
-        vals.extend(self.global_size)
-        vals.extend((1,) * (3 - ndim))
-        queue.launch_values(kernel, grid, local, ck.kinds(3), vals)
+        # pointers, shapes and scalars go from the argument objects into the
+        # GPUParamDesc array in the native launch path
+        tail = tuple(self.global_size) + (1,) * (3 - ndim)
+        if ck.local_bytes:
+            tail += (-ck.local_bytes,)
+        try:
+            _rt.fastcall().launch_kernel(queue.handle, kernel, grid, local, ck.layout_code(), args, tail)
+        except RuntimeError:
+            _rt.check()
+            raise
 
 
 def kernel(func=None, **kwargs):

@@ -1613,6 +1613,63 @@ class Plan:
         self.steps = trace.steps
         self.result_spec = result_spec
         self.queue = trace.queue
+        self._native = {}  # queue -> launches as the native launch path takes them
+        self.native_ok = self._native_form() is not None
+
+    def _native_form(self):
+        """The plan as (kernel source, kernel name, grid, block, codes, sources)
+        per launch when it consists only of launches over the call's own
+        arguments (no temporaries, reductions or products) and returns nothing
+        or arguments: such a plan is replayed by the native launch path.  None
+        otherwise."""
+        from .runtime import param_code
+
+        launches = []
+        for step in self.steps:
+            if step[0] != "launch":
+                return None
+            _tag, blob, kname, grid, block, params = step
+            codes, sources = [], []
+            for p in params:
+                if p[0] == "slot":
+                    s = self.slots[p[1]]
+                    if s[0] != "arg":
+                        return None
+                    codes.append(b"p")
+                    sources.append(s[1])
+                elif p[0] == "i64":
+                    codes.append(b"k")
+                    sources.append(int(p[1]))
+                elif p[0] == "scalar":
+                    codes.append(param_code(p[2]))
+                    sources.append(p[1])
+                else:
+                    return None
+            launches.append((blob, kname, tuple(grid), tuple(block), b"".join(codes), tuple(sources)))
+        for i in _result_slots(self.result_spec):
+            if self.slots[i][0] != "arg":
+                return None
+        return launches
+
+    def replay_native(self, args, queue):
+        """`replay` for a plan in native form: one call into the native launch
+        path, which reads the pointers and scalars out of `args` itself."""
+        from . import runtime as _rt
+
+        spec = self._native.get(queue)
+        if spec is None:
+            spec = self._native[queue] = tuple(
+                (queue.get_kernel(queue.load_module(blob), kname), grid, block, codes, sources)
+                for blob, kname, grid, block, codes, sources in self._native_form())
+        try:
+            _rt.fastcall().replay(queue.handle, spec, args)
+        except RuntimeError:
+            _rt.check()
+            raise
+        spec_r = self.result_spec
+        if spec_r is None:
+            return None
+        return _build_result(spec_r, _ArgSlots(self.slots, args))
 
     def replay(self, args, queue=None):
         """Runs the recorded steps on `args`; allocations and launches go to
@@ -1657,6 +1714,16 @@ class Plan:
         for i in _result_slots(self.result_spec):
             get(i)
         return _build_result(self.result_spec, arrays)
+
+
+class _ArgSlots:
+    """Indexable like a plan's array list, for plans whose slots are arguments."""
+
+    def __init__(self, slots, args):
+        self.slots, self.args = slots, args
+
+    def __getitem__(self, i):
+        return self.args[self.slots[i][1]]
 
 
 def _result_slots(spec):

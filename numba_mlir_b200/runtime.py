@@ -166,6 +166,40 @@ def load(optional_symbols=()):
         return lib
 
 
+_fast = None
+
+
+def fastcall():
+    """The native launch path (`_fastcall` extension: argument unboxing,
+    GPUParamDesc building and the launch in C++), bound to this library's
+    gpuxLaunchKernel / gpuxDestroyEvent.  Built by numba_mlir_b200.build."""
+    global _fast
+    if _fast is None:
+        lib = load()
+        try:
+            from . import _fastcall
+        except ImportError as e:
+            raise GpuRuntimeError(
+                f"the native launch path is missing ({e}): build it with `python -m numba_mlir_b200.build`"
+            ) from None
+        _fastcall.init(ctypes.cast(lib.gpuxLaunchKernel, ctypes.c_void_p).value,
+                       ctypes.cast(lib.gpuxDestroyEvent, ctypes.c_void_p).value)
+        _fast = _fastcall
+    return _fast
+
+
+_CODE_OF_DTYPE = {"bool": b"b", "int8": b"c", "uint8": b"C", "int16": b"h", "uint16": b"H", "int32": b"i",
+                  "uint32": b"I", "int64": b"q", "uint64": b"Q", "float32": b"f", "float64": b"d"}
+
+
+def param_code(dtype):
+    """One-letter parameter code of the native launch path for a scalar dtype."""
+    try:
+        return _CODE_OF_DTYPE[np.dtype(dtype).name]
+    except KeyError:
+        raise TypeError(f"unsupported kernel argument type {dtype}") from None
+
+
 def check():
     """Raises GpuRuntimeError if the library recorded an error."""
     lib = load()
