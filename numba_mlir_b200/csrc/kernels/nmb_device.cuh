@@ -162,98 +162,6 @@ __device__ __forceinline__ void eltwise_tile(const Chain &chain, int64_t n) {
   }
 }
 
-// The same loop for a grid smaller than the number of tiles (a problem of a few
-// waves, where the ramp and the tail of one-tile blocks are a large part of the
-// run): block b takes the tiles b, b + gridDim.x, ...
-template <int BLOCK, int V, int UNROLL, typename Chain>
-__device__ __forceinline__ void eltwise_persistent(const Chain &chain, int64_t n) {
-  const int64_t tile = (int64_t)BLOCK * V * UNROLL;
-  for (int64_t t0 = (int64_t)blockIdx.x * tile; t0 < n; t0 += (int64_t)gridDim.x * tile) {
-    const int64_t base = t0 + (int64_t)threadIdx.x * V;
-    if (t0 + tile <= n) {
-      typename Chain::template In<V> in[UNROLL];
-      typename Chain::template Out<V> out[UNROLL];
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u)
-        chain.template load<V>(base + (int64_t)u * BLOCK * V, in[u]);
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u)
-        chain.template compute<V>(in[u], out[u]);
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u)
-        chain.template store<V>(base + (int64_t)u * BLOCK * V, out[u]);
-    } else {
-#pragma unroll 1
-      for (int u = 0; u < UNROLL; ++u) {
-        const int64_t i = base + (int64_t)u * BLOCK * V;
-        if (i + V <= n) {
-          typename Chain::template In<V> in;
-          typename Chain::template Out<V> out;
-          chain.template load<V>(i, in);
-          chain.template compute<V>(in, out);
-          chain.template store<V>(i, out);
-        } else {
-          for (int64_t j = i; j < n && j < i + V; ++j) {
-            typename Chain::template In<1> in;
-            typename Chain::template Out<1> out;
-            chain.template load<1>(j, in);
-            chain.template compute<1>(in, out);
-            chain.template store<1>(j, out);
-          }
-        }
-      }
-    }
-  }
-}
-
-// Persistent and software pipelined: the loads of a block's next tile are
-// issued before the current tile is computed and stored, so every block keeps
-// requests in flight from its first instruction to its last.
-template <int BLOCK, int V, int UNROLL, typename Chain>
-__device__ __forceinline__ void eltwise_pipelined(const Chain &chain, int64_t n) {
-  const int64_t tile = (int64_t)BLOCK * V * UNROLL;
-  const int64_t stride = (int64_t)gridDim.x * tile;
-  const int64_t full_end = n - n % tile; // full tiles only; the ragged tile is handled at the end
-  int64_t t0 = (int64_t)blockIdx.x * tile;
-  typename Chain::template In<V> cur[UNROLL], nxt[UNROLL];
-  if (t0 < full_end) {
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
-      chain.template load<V>(t0 + (int64_t)threadIdx.x * V + (int64_t)u * BLOCK * V, cur[u]);
-  }
-  for (; t0 < full_end; t0 += stride) {
-    const int64_t t1 = t0 + stride;
-    if (t1 < full_end) {
-#pragma unroll
-      for (int u = 0; u < UNROLL; ++u)
-        chain.template load<V>(t1 + (int64_t)threadIdx.x * V + (int64_t)u * BLOCK * V, nxt[u]);
-    }
-    typename Chain::template Out<V> out[UNROLL];
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
-      chain.template compute<V>(cur[u], out[u]);
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
-      chain.template store<V>(t0 + (int64_t)threadIdx.x * V + (int64_t)u * BLOCK * V, out[u]);
-#pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
-      cur[u] = nxt[u];
-  }
-  // the ragged last tile, by the block whose turn it would be
-  if (full_end < n && (full_end / tile) % gridDim.x == blockIdx.x) {
-    for (int u = 0; u < UNROLL; ++u) {
-      const int64_t i = full_end + (int64_t)threadIdx.x * V + (int64_t)u * BLOCK * V;
-      for (int64_t j = i; j < n && j < i + V; ++j) {
-        typename Chain::template In<1> in;
-        typename Chain::template Out<1> out;
-        chain.template load<1>(j, in);
-        chain.template compute<1>(in, out);
-        chain.template store<1>(j, out);
-      }
-    }
-  }
-}
-
 // Number of blocks eltwise_tile needs for n elements.
 __host__ __device__ inline int64_t eltwise_grid(int64_t n, int block, int v, int unroll) {
   const int64_t tile = (int64_t)block * v * unroll;
