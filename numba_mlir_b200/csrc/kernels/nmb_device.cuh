@@ -429,9 +429,7 @@ __device__ __forceinline__ float f_rsqrt(float x) {
 }
 #else
 __device__ __forceinline__ float f_sqrt(float x) { return __fsqrt_rn(x); }
-// 1/sqrt(x) rounded once (round to nearest even): half an ulp from the true
-// value, at most one from 1/sqrt(x) evaluated as two rounded operations.
-__device__ __forceinline__ float f_rsqrt(float x) { return __frsqrt_rn(x); }
+__device__ __forceinline__ float f_rsqrt(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
 #endif
 // erf in float32, branch free (both ranges are evaluated and one is selected, so
 // a warp whose lanes straddle the ranges pays nothing extra):

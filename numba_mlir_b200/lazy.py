@@ -179,7 +179,7 @@ _UFUNC_BY_OBJ[np.rad2deg] = "degrees"
 _UFUNC_BY_OBJ[np.deg2rad] = "radians"
 _UFUNC_BY_OBJ[np.bitwise_not] = "invert"
 
-# 1/sqrt(x) written as such (never produced by NumPy dispatch)
+# 1/sqrt(x) under fastmath (never produced by NumPy dispatch)
 UFUNCS["rsqrt"] = (None, _flt("nmb::f_rsqrt({0})", "(1.0 / sqrt({0}))"))
 
 REDUCTIONS = {np.sum: "sum", np.prod: "prod", np.min: "min", np.max: "max", np.amin: "min",
@@ -879,12 +879,9 @@ def apply_ufunc(trace, name, inputs):
     cast = [n if n.dtype == d else Node("cast", d, n.shape, (n,)) for n, d in zip(nodes, loop_in)]
     shape = broadcast_shapes(*[n.shape for n in nodes])
     node = Node("op", out_dt, shape, cast, op=name)
-    if name == "true_divide" and _is_one(cast[0]) and cast[1].kind == "op" \
+    if trace.fastmath and name == "true_divide" and _is_one(cast[0]) and cast[1].kind == "op" \
             and cast[1].op == "sqrt" and out_dt == np.float32 and cast[1].shape == shape:
-        # 1/sqrt(x) in one step: the correctly rounded reciprocal square root
-        # (within half an ulp of the true value; the two rounded steps it
-        # replaces are within one), rsqrt.approx under fastmath
-        node = Node("op", out_dt, shape, cast[1].inputs, op="rsqrt")
+        node = Node("op", out_dt, shape, cast[1].inputs, op="rsqrt")  # 1/sqrt(x): one instruction
     concrete = None
     if shape == () and all(isinstance(x, LazyArray) and x.concrete is not None or
                            not isinstance(x, (LazyArray, DeviceArray)) for x in inputs):

@@ -102,10 +102,7 @@ def _ulps(got, want64):
 def test_fastmath_division_and_sqrt_stay_within_two_ulp(queue):
     """fastmath=True (numba_mlir/mlir/tests/test_gpu.py:981-1010,1900-1934):
     division, sqrt and 1/sqrt take the approximate instructions, whose error
-    stays within 2 ulp of the exact float32 result; the default is bit-exact
-    for division and sqrt, and 1/sqrt(x) is the correctly rounded reciprocal
-    square root (half an ulp from the true value, so at most one ulp from the
-    two rounded steps NumPy takes)."""
+    stays within 2 ulp of the exact float32 result; the default is bit-exact."""
     import numba_mlir_b200 as nm
 
     def f(a, b):
@@ -119,13 +116,8 @@ def test_fastmath_division_and_sqrt_stay_within_two_ulp(queue):
     exact = nm.njit(f)(_dev(a), _dev(b))
     with np.errstate(over="ignore"):
         want = (a / b, np.sqrt(a), np.float32(1.0) / np.sqrt(a))
-    for got, w in zip(exact[:2], want[:2]):
+    for got, w in zip(exact, want):
         assert np.array_equal(got.copy_to_host(), w)
-    r = exact[2].copy_to_host()
-    with np.errstate(over="ignore"):
-        ok = np.isfinite(truth[2].astype(np.float32)) & (np.abs(truth[2]) > 1e-37)
-    assert _ulps(r[ok], truth[2][ok]).max() <= 0.5 + 1e-6
-    assert np.all(np.abs(r[ok].view(np.int32) - want[2][ok].view(np.int32)) <= 1)
     fast = nm.njit(f, fastmath=True)(_dev(a), _dev(b))
     for got, t in zip(fast, truth):
         g = got.copy_to_host()
