@@ -991,7 +991,7 @@ def run_gpu(args):
                 "timing": f"median of {blocks} timed blocks of {args.steps} steps (at least {MIN_TIMED_MS:.0f} ms "
                           "of device time in all), CUDA events on the launching stream, max over ranks",
                 "verified": "one step's output equals the CPU oracle's (checked outside the timed region)",
-                "host_numa_node_of_rank0": numa_node,
+                "host_cores_bound_to_rank0": numa_node,
             },
             "elements_per_s": w.units_per_step * world / (ms_per_step * 1e-3),
             "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,

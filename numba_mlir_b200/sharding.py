@@ -275,13 +275,14 @@ def _external_stream(queue):
 
 
 def bind_host_to_gpu(device_index):
-    """Runs this process on the CPU cores next to GPU `device_index` (the cores
-    of the NUMA node its PCIe slot hangs off), so that host buffers allocated
-    afterwards, page-locked ones included, land in that node's memory and the
-    copies of several ranks do not all cross one socket's memory and links.
-    Reads the topology from NVML and sysfs; changes only this process's CPU
-    affinity.  Returns the NUMA node, or None when the topology is not visible
-    (nothing is changed then)."""
+    """Runs this process on the CPU cores next to GPU `device_index`, so that
+    host buffers allocated afterwards, page-locked ones included, land in that
+    socket's memory and the copies of several ranks do not all cross one
+    socket's memory and links.  The cores come from NVML's CPU affinity of
+    the device (or, failing that, from the NUMA node sysfs names for its PCIe
+    slot); only this process's CPU affinity changes.  Returns the number of
+    cores the process is bound to, or None when the topology is not visible
+    or names every core anyway (nothing is changed then)."""
     try:
         import pynvml
 
@@ -292,25 +293,33 @@ def bind_host_to_gpu(device_index):
             ids = [v.strip() for v in visible.split(",") if v.strip()]
             if idx < len(ids) and ids[idx].isdigit():
                 idx = int(ids[idx])
-        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(idx)).busId
-        bus = bus.decode() if isinstance(bus, bytes) else bus
-        bus = bus.lower()
-        if len(bus.split(":")[0]) == 8:  # NVML prints an 8-digit PCI domain, sysfs a 4-digit one
-            bus = bus[4:]
-        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
-            node = int(f.read().strip())
-        if node < 0:
-            return None
-        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+        handle = pynvml.nvmlDeviceGetHandleByIndex(idx)
+        allowed = os.sched_getaffinity(0)
+        cpus = set()
+        try:
+            words = (max(allowed) + 64) // 64
+            for w, mask in enumerate(pynvml.nvmlDeviceGetCpuAffinity(handle, words)):
+                cpus.update(64 * w + b for b in range(64) if (int(mask) >> b) & 1)
+        except Exception:
             cpus = set()
-            for part in f.read().strip().split(","):
-                lo, _, hi = part.partition("-")
-                cpus.update(range(int(lo), int(hi or lo) + 1))
-        allowed = cpus & os.sched_getaffinity(0)
-        if not allowed:
+        if not cpus:
+            bus = pynvml.nvmlDeviceGetPciInfo(handle).busId
+            bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+            if len(bus.split(":")[0]) == 8:  # NVML prints an 8-digit PCI domain, sysfs a 4-digit one
+                bus = bus[4:]
+            with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+                node = int(f.read().strip())
+            if node < 0:
+                return None
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+                for part in f.read().strip().split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+        target = cpus & allowed
+        if not target or target == allowed:
             return None
-        os.sched_setaffinity(0, allowed)
-        return node
+        os.sched_setaffinity(0, target)
+        return len(target)
     except Exception:
         return None
 
