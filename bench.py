@@ -251,7 +251,8 @@ class BroadcastAdd(Workload):
 
 
 class AxisReduction(Workload):
-    """float32 (16384, 4096) ~ N(0,1): sum(axis=1), min(axis=0), argmin(axis=1).
+    """float32 (16384, 4096) ~ N(0,1): sum(axis=1), min(axis=0), argmin(axis=1),
+    and sqrt(sum(a*a, axis=1)) (a reduction fed by an elementwise chain).
     With `fraction` < 1 the GPU holds that part of the rows and the step
     rotates over several shards' worth of data to stay out of L2."""
 
@@ -263,7 +264,8 @@ class AxisReduction(Workload):
         self.rows = max(8, int(16384 * fraction))
         self.name = f"{which}_f32_{self.rows}x4096"
         self.units_per_step = self.rows * 4096
-        out_bytes = {"sum_axis1": 4 * self.rows, "min_axis0": 4 * 4096, "argmin_axis1": 8 * self.rows}[which]
+        out_bytes = {"sum_axis1": 4 * self.rows, "min_axis0": 4 * 4096, "argmin_axis1": 8 * self.rows,
+                     "row_norm": 4 * self.rows}[which]
         self.bytes_per_step = self.rows * 4096 * 4 + out_bytes
         self.graph_steps = rotation_sets(self.rows * 4096 * 4)
         if which == "min_axis0":
@@ -282,7 +284,7 @@ class AxisReduction(Workload):
         self.fn = getattr(workloads, self.which)
         self.dist = dist if self.which == "min_axis0" else None
         shape, dt = {"sum_axis1": (self.rows, f32), "min_axis0": (4096, f32),
-                     "argmin_axis1": (self.rows, np.int64)}[self.which]
+                     "argmin_axis1": (self.rows, np.int64), "row_norm": (self.rows, f32)}[self.which]
         self.out = nm.empty(shape, dt, queue)
         self.i = 0
         if self.which == "sum_axis1" and dist is None:
@@ -321,6 +323,10 @@ class AxisReduction(Workload):
                 assert np.array_equal(np.asarray(self.h_out).view(np.uint32), got.view(np.uint32))
         elif self.which == "argmin_axis1":
             assert np.array_equal(got, O.argmin_axis1(a)), "argmin(axis=1) differs from the oracle"
+        elif self.which == "row_norm":
+            truth = np.sqrt((a.astype(np.float64) ** 2).sum(axis=1))
+            np.testing.assert_allclose(got, truth, rtol=1e-5)
+            np.testing.assert_allclose(O.row_norm(a), truth, rtol=1e-5)
         else:
             # the unsharded result: the shards' oracle minima combined in rank
             # order with the same select(x < m) the oracle applies row by row
@@ -523,6 +529,7 @@ WORKLOADS = {
     "sum_axis1": lambda: AxisReduction("sum_axis1"),
     "min_axis0": lambda: AxisReduction("min_axis0"),
     "argmin_axis1": lambda: AxisReduction("argmin_axis1"),
+    "row_norm": lambda: AxisReduction("row_norm"),
     "int_sum": IntSum,
     "pairwise": Pairwise,
     "kmeans": KMeans,
@@ -638,11 +645,11 @@ def cpu_case(key, scale):
     if key == "bcast_add":
         a, b = O.make_inputs("bcast_add", scale)
         return lambda: O.bcast_add(a, b), 2 * a.nbytes + b.nbytes, a.size, BroadcastAdd.name
-    if key in ("sum_axis1", "min_axis0", "argmin_axis1"):
+    if key in ("sum_axis1", "min_axis0", "argmin_axis1", "row_norm"):
         (a,) = O.make_inputs("reduce_f32", scale)
         fn = getattr(O, key)
         out_bytes = {"sum_axis1": 4 * a.shape[0], "min_axis0": 4 * a.shape[1],
-                     "argmin_axis1": 8 * a.shape[0]}[key]
+                     "argmin_axis1": 8 * a.shape[0], "row_norm": 4 * a.shape[0]}[key]
         return lambda: fn(a), a.nbytes + out_bytes, a.size, f"{key}_f32_16384x4096"
     if key == "int_sum":
         (a,) = O.make_inputs("reduce_i32", scale)
@@ -940,7 +947,7 @@ def run_gpu(args):
         if world == 1:
             # the other configurations on one GPU
             for key in ("black_scholes_fastmath", "bcast_add", "sum_axis1", "min_axis0", "argmin_axis1",
-                        "int_sum", "pairwise", "kmeans", "kmeans_naive"):
+                        "row_norm", "int_sum", "pairwise", "kmeans", "kmeans_naive"):
                 ow = WORKLOADS[key]()
                 others[ow.name] = entry(ow)
                 del ow

@@ -16,6 +16,7 @@ from . import runtime as _rt
 from numba.core import types
 from numba.core.typing.templates import AbstractTemplate, ConcreteTemplate, infer_global, signature
 
+from .decorators import _wrap_arg, check_device_args
 from .device_array import DeviceArray
 
 
@@ -313,6 +314,7 @@ class Kernel:
         self.global_size = ()
         self.local_size = ()
         self._compiled = {}
+        self._launchers = {}  # (argument kinds, rank of the launch) -> (compiled kernel, index of an array argument)
 
     def copy(self):
         return copy.copy(self)
@@ -345,8 +347,40 @@ class Kernel:
     def __call__(self, *args, **kwargs):
         if kwargs:
             _raise_error("kwargs not supported")
-        from .decorators import _wrap_arg, check_device_args
+        # A call like one seen before (same argument kinds): straight to the
+        # native launch path, which reads pointers, shapes and scalars out of
+        # the argument objects and builds the GPUParamDesc array.
+        try:
+            key = tuple([a._call_sig if type(a) is DeviceArray else type(a) for a in args])
+        except AttributeError:
+            key = None
+        entry = self._launchers.get((key, len(self.global_size))) if key is not None else None
+        if entry is not None:
+            ck, first = entry
+            queue = args[first]._buf.queue
+            for a in args:
+                if type(a) is DeviceArray and a._buf.queue is not queue and a._buf.queue.device != queue.device:
+                    check_device_args(args)
+            kernel = ck._handles.get(queue) or ck.handle_on(queue)
+            gs = self.global_size
+            local = self.local_size or ck.block_size_on(queue, kernel, gs)
+            if 0 in gs:
+                return
+            grid = tuple([(g + l - 1) // l for g, l in zip(gs, local)])
+            tail = gs + (1,) * (3 - len(gs))
+            if ck.local_bytes:
+                tail += (-ck.local_bytes,)
+            try:
+                _rt.fastcall().launch_kernel(queue.handle, kernel, grid, local, ck.layout_code(), args, tail)
+            except RuntimeError:
+                _rt.check()
+                raise
+            return
+        self._call_slow(args)
 
+    def _call_slow(self, args):
+        """First call with these argument kinds: wraps foreign arrays, checks the
+        devices, compiles, and remembers the compiled kernel for the fast path."""
         args = tuple(_wrap_arg(a) for a in args)
         if not check_device_args(args):
             raise TypeError("kernel launch needs at least one device array argument")
@@ -362,7 +396,10 @@ class Kernel:
                                            fastmath=bool(self.options.get("fastmath", False)),
                                            index32=not self.options.get("gpu_use_64bit_index", True))
             self._compiled[key] = ck
-        queue = next(a.queue for a in args if isinstance(a, DeviceArray))
+        fast_key = tuple([a.call_sig if type(a) is DeviceArray else type(a) for a in args])
+        first = next(i for i, a in enumerate(args) if isinstance(a, DeviceArray))
+        self._launchers[(fast_key, ndim)] = (ck, first)
+        queue = args[first].queue
         kernel = ck.handle_on(queue)
         if self.local_size:
             local = tuple(self.local_size)

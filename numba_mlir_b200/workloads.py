@@ -67,6 +67,13 @@ def sum_axis1(a, out):
     out[:] = np.sum(a, axis=1)
 
 
+# A reduction fed by an elementwise chain (mlir/tests/test_gpu.py:2198-2224): the
+# squares are never written out, the rows are read once.
+@njit(parallel=True)
+def row_norm(a, out):
+    out[:] = np.sqrt(np.square(a).sum(axis=1))
+
+
 @njit(parallel=True)
 def min_axis0(a, out):
     out[:] = np.min(a, axis=0)

@@ -166,6 +166,19 @@ def sum_axis1(a):
     return out
 
 
+# sqrt(sum(a*a, axis=1)): the producer-into-reduction fusion the reference tests
+# (numba_mlir/mlir/tests/test_gpu.py:2198-2224); float32 accumulation per row.
+@njit(parallel=True)
+def row_norm(a):
+    out = np.empty(a.shape[0], np.float32)
+    for i in prange(a.shape[0]):
+        s = np.float32(0.0)
+        for j in range(a.shape[1]):
+            s += a[i, j] * a[i, j]
+        out[i] = np.sqrt(s)
+    return out
+
+
 # np.min(axis=0) is supported by the reference (numpy/funcs.py:298-303) but not
 # by upstream Numba; min is select(x < m, x, m) (builtin/funcs.py:140-146).
 @njit(parallel=True)
