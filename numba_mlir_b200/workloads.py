@@ -8,8 +8,8 @@ import math
 import numpy as np
 
 from .decorators import njit, vectorize
-from .kernel import (atomic, barrier, get_global_id, get_global_size, get_group_id, get_local_id,
-                     get_local_size, kernel, local, private)
+from .kernel import (atomic, barrier, get_global_id, get_group_id, get_local_id, get_local_size, kernel, local,
+                     private)
 
 
 @vectorize(nopython=True)
@@ -119,28 +119,25 @@ def kmeans_update(centroids, sums, counts):
 # batch of 256 x 2 points is labelled, 64 work-items (4 point phases x 16
 # dimensions) add the batch into float64 accumulator columns in local memory
 # that each of them owns, and only the 64 x 16 group totals meet the global
-# arrays through atomics, once per group.  (Eight phases, a 64 KB accumulator,
-# measured slower: 696 us against 585 us; four or eight points per work-item at
-# once, or one, measured slower than two: 664, 836 and 639 us against 569 us.)
-# The groups are persistent: the launch has as many groups as the device keeps
-# resident (four per multiprocessor) and group g takes the batches g,
-# g + groups, ...  With one group per 2048 points instead, 2048 groups ran as
-# 3.46 waves of 592, the last one 46 % full.
+# arrays through atomics, once per group.  (Measured slower: eight phases with
+# a 64 KB accumulator, 696 us against 585 us; one, four or eight points per
+# work-item through the centroid loop at once instead of two, 639, 664 and
+# 836 us against 569 us; persistent groups that take the 512-point batches
+# round robin, four groups per multiprocessor, 609 us against 573 us.)
 _KM_K = 64
 _KM_D = 16
+_KM_PTS = 8
 _KM_Q = 2  # points a work-item takes through the centroid loop at once
 _KM_PH = 4     # point phases of the accumulation
 _KM_COLS = _KM_PH * _KM_D  # accumulator columns per cluster: phases x dimensions
 KMEANS_LOCAL_SIZE = 256
-KMEANS_GROUPS_PER_SM = 4  # 56 registers x 256 work-items and 38.5 KB of local memory per group
 
 
 @kernel(gpu_use_64bit_index=False)  # 2^22 x 16 elements: every offset fits 32 bits
 def _kmeans_kernel(points, centroids, labels, sums, counts):
     lid = get_local_id(0)
     lsz = get_local_size(0)
-    groups = get_global_size(0) // lsz
-    batches = points.shape[0] // (lsz * _KM_Q)
+    base = get_group_id(0) * (lsz * _KM_PTS)
 
     cent = local.array((_KM_K, _KM_D), np.float32)
     lbl = local.array(KMEANS_LOCAL_SIZE * _KM_Q, np.int32)
@@ -169,9 +166,8 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
     d = private.array(_KM_Q, np.float32)
     best_d = private.array(_KM_Q, np.float32)
     best = private.array(_KM_Q, np.int32)
-    r = get_group_id(0)
-    while r < batches:
-        row0 = r * (lsz * _KM_Q)
+    for r in range(_KM_PTS // _KM_Q):
+        row0 = base + r * (lsz * _KM_Q)
         for q in range(_KM_Q):
             for jj in range(_KM_D):
                 p[q, jj] = points[row0 + q * lsz + lid, jj]
@@ -212,7 +208,6 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
                 acc[l2, lid] += x2
                 acc[l3, lid] += x3
         barrier()
-        r += groups
 
     e = lid
     while e < _KM_K * _KM_D:
@@ -256,13 +251,12 @@ def kmeans_step_naive(points, centroids, labels, sums, counts):
 
 def kmeans_step(points, centroids, labels, sums, counts):
     """Assignment + accumulation for every point.  N must be a multiple of
-    256 * 2 because every work-item of a group takes part in the barriers and a
-    batch is two points per work-item."""
+    256 * 8 because every work-item of a group takes part in the barriers and
+    handles 8 points."""
     n = points.shape[0]
     if centroids.shape != (_KM_K, _KM_D):
         raise ValueError("this kernel is written for K = 64 clusters of D = 16 dimensions")
-    batch = KMEANS_LOCAL_SIZE * _KM_Q
-    if n % batch:
-        raise ValueError(f"the number of points must be a multiple of {batch}")
-    groups = min(n // batch, points.queue.sm_count * KMEANS_GROUPS_PER_SM)
-    _kmeans_kernel[groups * KMEANS_LOCAL_SIZE, KMEANS_LOCAL_SIZE](points, centroids, labels, sums, counts)
+    chunk = KMEANS_LOCAL_SIZE * _KM_PTS
+    if n % chunk:
+        raise ValueError(f"the number of points must be a multiple of {chunk}")
+    _kmeans_kernel[n // _KM_PTS, KMEANS_LOCAL_SIZE](points, centroids, labels, sums, counts)
