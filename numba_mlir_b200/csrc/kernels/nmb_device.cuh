@@ -316,8 +316,9 @@ __device__ __forceinline__ void reduce_rows_fused(const Chain &chain, int64_t ro
 
 // out[0] = reduce_i value[i], i < n.  Blocks take tiles of BLOCK*V*UNROLL
 // elements round robin; n % V may be anything (the tail is read one by one).
+// Returns true in the one block that wrote the result (uniform over the block).
 template <int BLOCK, int V, int UNROLL, typename A, typename Op, typename Chain>
-__device__ __forceinline__ void reduce_all_fused(const Chain &chain, int64_t n, A *out, A *partials,
+__device__ __forceinline__ bool reduce_all_fused(const Chain &chain, int64_t n, A *out, A *partials,
                                                  uint32_t *counter, Op op, A identity, A *scratch) {
   constexpr int64_t tile = (int64_t)BLOCK * V * UNROLL;
   A acc = identity;
@@ -345,7 +346,7 @@ __device__ __forceinline__ void reduce_all_fused(const Chain &chain, int64_t n, 
   }
   __syncthreads();
   if (!last)
-    return;
+    return false;
   __threadfence();
   A m = identity;
   for (unsigned g = threadIdx.x; g < gridDim.x; g += BLOCK)
@@ -355,6 +356,7 @@ __device__ __forceinline__ void reduce_all_fused(const Chain &chain, int64_t n, 
     out[0] = m;
     *counter = 0;
   }
+  return true;
 }
 
 // out[c] = reduce_r value[r * cols + c].  A thread owns V adjacent columns;
@@ -394,13 +396,31 @@ __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t ro
     return;
   __threadfence();
   if (c < cols) {
+    // the row blocks' partials, eight rows of independent loads at a time,
+    // combined in row-block order
+    constexpr int kRows = 8;
+    A m[V];
 #pragma unroll
-    for (int l = 0; l < V; ++l) {
-      A m = identity;
-      for (int64_t yy = 0; yy < Y; ++yy)
-        m = op(m, load_partial(partials + yy * cols + c + l));
-      out[c + l] = m;
+    for (int l = 0; l < V; ++l)
+      m[l] = identity;
+    for (int64_t y0 = 0; y0 < Y; y0 += kRows) {
+      A part[kRows][V];
+#pragma unroll
+      for (int k = 0; k < kRows; ++k)
+#pragma unroll
+        for (int l = 0; l < V; ++l)
+          if (y0 + k < Y)
+            part[k][l] = load_partial(partials + (y0 + k) * cols + c + l);
+#pragma unroll
+      for (int k = 0; k < kRows; ++k)
+#pragma unroll
+        for (int l = 0; l < V; ++l)
+          if (y0 + k < Y)
+            m[l] = op(m[l], part[k][l]);
     }
+#pragma unroll
+    for (int l = 0; l < V; ++l)
+      out[c + l] = m[l];
   }
   if (threadIdx.x == 0)
     counters[blockIdx.x] = 0;

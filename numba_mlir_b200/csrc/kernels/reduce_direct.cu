@@ -1,0 +1,130 @@
+// Row and full reductions (sum, prod, min, max) that read the array with plain
+// 128-bit streaming loads, four per thread in flight, and reduce in registers:
+// the one-pass reducers that the array front end generates around an
+// elementwise chain (nmb::reduce_rows_fused / reduce_all_fused in
+// nmb_device.cuh), instantiated here ahead of time for the chain "the array
+// itself".  On B200 they measured faster than the shared-memory ring of TMA
+// bulk copies (reduce_ws.cuh) for these two shapes -- float32 (16384, 4096)
+// sum(axis=1) 41.4 us against 43.9 us, 2^28 int32 full sum 152.3 us against
+// 162.9 us -- so the host dispatch uses them; column reductions and
+// argmin/argmax stay on the ring.  Same semantics as there: sum/prod accumulate
+// in int64 for int32 input and in the array type otherwise, min/max are
+// select(x < m), NaNs never win, partials merged in index order.
+//
+// A full reduction over one GPU's shard finishes with the exchange between
+// the GPUs (peer_exchange.cuh) in the block that wrote the result.
+#include "../gpu_common.h"
+#include "nmb_device.cuh"
+#include "peer_exchange.cuh"
+
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kUnroll = 4;
+
+template <typename T> struct PlainChain {
+  const T *__restrict__ in0;
+  template <int V> struct In {
+    nmb::Vec<T, V> in0;
+  };
+  template <int V> struct Out {
+    nmb::Vec<T, V> out0;
+  };
+  template <int V> __device__ __forceinline__ void load(int64_t i, In<V> &r) const {
+    r.in0 = nmb::load_stream<T, V>(in0 + i);
+  }
+  template <int V> __device__ __forceinline__ void compute(const In<V> &r, Out<V> &o) const { o.out0 = r.in0; }
+};
+
+template <typename T> struct Wide { using type = T; };
+template <> struct Wide<int32_t> { using type = int64_t; };
+
+struct SumTag {
+  using Op = nmb::OpAdd;
+  template <typename T> using Acc = typename Wide<T>::type;
+  template <typename A> static __device__ __forceinline__ A identity() { return A(0); }
+};
+struct ProdTag {
+  using Op = nmb::OpMul;
+  template <typename T> using Acc = typename Wide<T>::type;
+  template <typename A> static __device__ __forceinline__ A identity() { return A(1); }
+};
+struct MinTag {
+  using Op = nmb::OpMin;
+  template <typename T> using Acc = T;
+  template <typename A> static __device__ __forceinline__ A identity() { return nmb::neutral_min<A>(); }
+};
+struct MaxTag {
+  using Op = nmb::OpMax;
+  template <typename T> using Acc = T;
+  template <typename A> static __device__ __forceinline__ A identity() { return nmb::neutral_max<A>(); }
+};
+
+// out[r] = reduce(a[r, :]); cols % (16 / sizeof(T)) == 0, a 16-byte aligned.
+template <typename Tag, typename T, bool BLOCK_ROW>
+__device__ __forceinline__ void rows_direct(const T *a, typename Tag::template Acc<T> *out, int64_t rows,
+                                            int64_t cols) {
+  using A = typename Tag::template Acc<T>;
+  constexpr int V = 16 / sizeof(T);
+  __shared__ A scratch[32];
+  PlainChain<T> chain{a};
+  nmb::reduce_rows_fused<kBlock, V, kUnroll, BLOCK_ROW>(chain, rows, cols, out, typename Tag::Op(),
+                                                        Tag::template identity<A>(), scratch);
+}
+
+// out[0] = reduce(a[0:n]); a 16-byte aligned.
+template <typename Tag, typename T>
+__device__ __forceinline__ void all_direct(const T *a, typename Tag::template Acc<T> *out, void *partials,
+                                           uint32_t *counter, int64_t n, uint32_t *status,
+                                           const nmb::peer::Args px) {
+  using A = typename Tag::template Acc<T>;
+  constexpr int V = 16 / sizeof(T);
+  __shared__ A scratch[32];
+  PlainChain<T> chain{a};
+  const bool wrote = nmb::reduce_all_fused<kBlock, V, kUnroll>(chain, n, out, static_cast<A *>(partials), counter,
+                                                               typename Tag::Op(), Tag::template identity<A>(),
+                                                               scratch);
+  if (wrote && px.world > 1) {
+    __syncthreads();
+    nmb::peer::allreduce_block<A>(out, 1, px.peers, px.rank, px.world, status, typename Tag::Op());
+  }
+}
+
+} // namespace
+
+// Launch (rows): grid.x blocks of 256 threads; a row belongs to one warp, or to
+// the whole block in the `_blockrow` variant (few long rows).
+// Launch (all): grid.x blocks of 256 threads taking tiles of 256 * (16 /
+// sizeof(T)) * 4 elements round robin; scratch holds grid.x accumulators and one
+// zeroed counter; peers/rank/world: the exchange that ends the kernel
+// (world <= 1: none).
+#define NMB_DIRECT(op, TAG, ty, T)                                                                         \
+  extern "C" __global__ void __launch_bounds__(kBlock)                                                     \
+      nmb_reduce_rows_direct_##op##_##ty(const T *a, TAG::Acc<T> *out, int64_t rows, int64_t cols) {       \
+    rows_direct<TAG, T, false>(a, out, rows, cols);                                                        \
+  }                                                                                                        \
+  NMB_REGISTER_KERNEL(nmb_reduce_rows_direct_##op##_##ty, 0);                                              \
+  extern "C" __global__ void __launch_bounds__(kBlock)                                                     \
+      nmb_reduce_rows_direct_blockrow_##op##_##ty(const T *a, TAG::Acc<T> *out, int64_t rows,              \
+                                                  int64_t cols) {                                          \
+    rows_direct<TAG, T, true>(a, out, rows, cols);                                                         \
+  }                                                                                                        \
+  NMB_REGISTER_KERNEL(nmb_reduce_rows_direct_blockrow_##op##_##ty, 0);                                     \
+  extern "C" __global__ void __launch_bounds__(kBlock)                                                     \
+      nmb_reduce_all_direct_##op##_##ty(const T *a, TAG::Acc<T> *out, void *partials, uint32_t *counter,   \
+                                        int64_t n, uint32_t *status, const unsigned long long *peers,      \
+                                        int32_t rank, int32_t world) {                                     \
+    all_direct<TAG, T>(a, out, partials, counter, n, status, nmb::peer::Args{peers, rank, world});         \
+  }                                                                                                        \
+  NMB_REGISTER_KERNEL(nmb_reduce_all_direct_##op##_##ty, 0);
+
+#define NMB_DIRECT_TYPES(op, TAG)                                                                          \
+  NMB_DIRECT(op, TAG, f32, float)                                                                          \
+  NMB_DIRECT(op, TAG, f64, double)                                                                         \
+  NMB_DIRECT(op, TAG, i32, int32_t)                                                                        \
+  NMB_DIRECT(op, TAG, i64, int64_t)
+
+NMB_DIRECT_TYPES(sum, SumTag)
+NMB_DIRECT_TYPES(prod, ProdTag)
+NMB_DIRECT_TYPES(min, MinTag)
+NMB_DIRECT_TYPES(max, MaxTag)

@@ -1,6 +1,9 @@
 """Host dispatch of the reduction kernels (sum/prod/min/max/argmin/argmax).
 
-Result dtypes follow the reference's _array_reduce
+Full and row reductions of sum/prod/min/max run on the direct-load kernels
+(csrc/kernels/reduce_direct.cu), column reductions and argmin/argmax on the
+TMA-staged ring (reduce_ws.cuh), anything unaligned or strided on the generic
+kernels.  Result dtypes follow the reference's _array_reduce
 (numba_mlir/numba_mlir/mlir/numpy/funcs.py:163-214): sum and prod of an integer
 array are int64, of a float array the array's dtype; min/max keep the dtype;
 argmin/argmax are int64 (NumPy's intp).  Everything runs on the device through
@@ -114,7 +117,19 @@ def reduce(a, op, axis=None, out=None):
     return out
 
 
+_DIRECT_OPS = ("sum", "prod", "min", "max")
+
+
 def _launch_rows(q, a, out, op, ty, rows, cols):
+    if op in _DIRECT_OPS:
+        # plain 128-bit loads, one warp per row (the whole block for few long
+        # rows): measured faster than the TMA ring for these reductions
+        block_row = cols >= 8192 and rows < q.sm_count * 8
+        k = q.builtin(f"nmb_reduce_rows_direct_{'blockrow_' if block_row else ''}{op}_{ty}")
+        units = rows if block_row else (rows + 7) // 8
+        q.launch(k, (max(1, min(units, q.sm_count * 8)),), (256,),
+                 [("ptr", a.ptr), ("ptr", out.ptr), _I64(rows), _I64(cols)])
+        return
     k = q.builtin(f"nmb_reduce_rows_{op}_{ty}")
     it = a.dtype.itemsize
     if cols * it > 2048:
@@ -159,6 +174,16 @@ def _launch_all(q, a, out, op, ty):
         _launch_generic(q, a.reshape(n), out, op, ty, 0, 1, n, 1)
         return
     peers, owed = _peer_params(q, op, out.nbytes)
+    if op in _DIRECT_OPS:
+        tile = 256 * (16 // a.dtype.itemsize) * 4  # elements a block takes per step
+        grid = max(1, min(q.sm_count * 8, (n + tile - 1) // tile))
+        counters, partials = q.scratch(grid * 8)
+        q.launch(q.builtin(f"nmb_reduce_all_direct_{op}_{ty}"), (grid,), (256,),
+                 [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters), _I64(n),
+                  ("ptr", q.status_ptr)] + peers)
+        if owed is not None:
+            owed.allreduce(out, op)
+        return
     k = q.builtin(f"nmb_reduce_all_{op}_{ty}")
     tile = _TILE_BYTES // a.dtype.itemsize
     grid = max(1, min(q.sm_count * _CTAS_PER_SM, (n + tile - 1) // tile))
