@@ -359,10 +359,38 @@ __device__ __forceinline__ bool reduce_all_fused(const Chain &chain, int64_t n, 
   return true;
 }
 
+// Merges `count` rows of partials (row stride `cols`) for this thread's V
+// columns at `c`, eight rows of independent loads at a time, in row order.
+template <int V, typename A, typename Op>
+__device__ __forceinline__ void merge_partial_rows(const A *rows, int64_t count, int64_t cols, int64_t c, A *m,
+                                                   Op op) {
+  constexpr int kRows = 8;
+  for (int64_t y0 = 0; y0 < count; y0 += kRows) {
+    A part[kRows][V];
+#pragma unroll
+    for (int k = 0; k < kRows; ++k)
+#pragma unroll
+      for (int l = 0; l < V; ++l)
+        if (y0 + k < count)
+          part[k][l] = load_partial(rows + (y0 + k) * cols + c + l);
+#pragma unroll
+    for (int k = 0; k < kRows; ++k)
+#pragma unroll
+      for (int l = 0; l < V; ++l)
+        if (y0 + k < count)
+          m[l] = op(m[l], part[k][l]);
+  }
+}
+
 // out[c] = reduce_r value[r * cols + c].  A thread owns V adjacent columns;
-// blockIdx.y splits the rows, and the row blocks of a column tile meet in
-// partials[gridDim.y][cols] behind one ticket counter per column tile.
-// cols % V == 0.
+// blockIdx.y splits the rows.  The row blocks of a column tile meet in two
+// steps so that no block merges more than a few rows: groups of kColFanIn row
+// blocks merge into one row each (the block that draws the group's last
+// ticket does it), and the block that completes the last group merges the
+// groups' rows into `out`.  Scratch: partials[gridDim.y + groups][cols];
+// counters: 1 + groups tickets per column tile, left at zero.  cols % V == 0.
+constexpr int kColFanIn = 16;
+
 template <int BLOCK, int V, int UNROLL, typename A, typename Op, typename Chain>
 __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t rows, int64_t cols, A *out,
                                                   A *partials, uint32_t *counters, Op op, A identity) {
@@ -386,44 +414,56 @@ __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t ro
   }
   if (Y == 1)
     return;
+  const int64_t groups = (Y + kColFanIn - 1) / kColFanIn;
+  const int64_t g = y / kColFanIn;
+  const int64_t gsize = Y - g * kColFanIn < kColFanIn ? Y - g * kColFanIn : kColFanIn;
+  uint32_t *tickets = counters + (int64_t)blockIdx.x * (groups + 1);
+  A *level2 = partials + Y * cols;
   __shared__ bool last;
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0)
-    last = atomicAdd(counters + blockIdx.x, 1u) == (unsigned)(Y - 1);
+  if (threadIdx.x == 0) {
+    last = atomicAdd(tickets + 1 + g, 1u) == (unsigned)(gsize - 1);
+    if (last)
+      tickets[1 + g] = 0;
+  }
+  __syncthreads();
+  if (!last)
+    return;
+  __threadfence();
+  A m[V];
+#pragma unroll
+  for (int l = 0; l < V; ++l)
+    m[l] = identity;
+  if (c < cols) {
+    merge_partial_rows<V>(partials + g * kColFanIn * cols, gsize, cols, c, m, op);
+    A *dst = groups == 1 ? out + c : level2 + g * cols + c;
+#pragma unroll
+    for (int l = 0; l < V; ++l)
+      dst[l] = m[l];
+  }
+  if (groups == 1)
+    return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    last = atomicAdd(tickets, 1u) == (unsigned)(groups - 1);
+    if (last)
+      tickets[0] = 0;
+  }
   __syncthreads();
   if (!last)
     return;
   __threadfence();
   if (c < cols) {
-    // the row blocks' partials, eight rows of independent loads at a time,
-    // combined in row-block order
-    constexpr int kRows = 8;
-    A m[V];
 #pragma unroll
     for (int l = 0; l < V; ++l)
       m[l] = identity;
-    for (int64_t y0 = 0; y0 < Y; y0 += kRows) {
-      A part[kRows][V];
-#pragma unroll
-      for (int k = 0; k < kRows; ++k)
-#pragma unroll
-        for (int l = 0; l < V; ++l)
-          if (y0 + k < Y)
-            part[k][l] = load_partial(partials + (y0 + k) * cols + c + l);
-#pragma unroll
-      for (int k = 0; k < kRows; ++k)
-#pragma unroll
-        for (int l = 0; l < V; ++l)
-          if (y0 + k < Y)
-            m[l] = op(m[l], part[k][l]);
-    }
+    merge_partial_rows<V>(level2, groups, cols, c, m, op);
 #pragma unroll
     for (int l = 0; l < V; ++l)
       out[c + l] = m[l];
   }
-  if (threadIdx.x == 0)
-    counters[blockIdx.x] = 0;
 }
 
 // ------------------------------------------------------------------- math ---

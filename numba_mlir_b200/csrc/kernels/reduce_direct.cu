@@ -99,18 +99,18 @@ __device__ __forceinline__ void all_direct(const T *a, typename Tag::template Ac
 // zeroed counter; peers/rank/world: the exchange that ends the kernel
 // (world <= 1: none).
 #define NMB_DIRECT(op, TAG, ty, T)                                                                         \
-  extern "C" __global__ void __launch_bounds__(kBlock)                                                     \
+  extern "C" __global__ void __launch_bounds__(kBlock, 6)                                                   \
       nmb_reduce_rows_direct_##op##_##ty(const T *a, TAG::Acc<T> *out, int64_t rows, int64_t cols) {       \
     rows_direct<TAG, T, false>(a, out, rows, cols);                                                        \
   }                                                                                                        \
   NMB_REGISTER_KERNEL(nmb_reduce_rows_direct_##op##_##ty, 0);                                              \
-  extern "C" __global__ void __launch_bounds__(kBlock)                                                     \
+  extern "C" __global__ void __launch_bounds__(kBlock, 6)                                                   \
       nmb_reduce_rows_direct_blockrow_##op##_##ty(const T *a, TAG::Acc<T> *out, int64_t rows,              \
                                                   int64_t cols) {                                          \
     rows_direct<TAG, T, true>(a, out, rows, cols);                                                         \
   }                                                                                                        \
   NMB_REGISTER_KERNEL(nmb_reduce_rows_direct_blockrow_##op##_##ty, 0);                                     \
-  extern "C" __global__ void __launch_bounds__(kBlock)                                                     \
+  extern "C" __global__ void __launch_bounds__(kBlock, 6)                                                   \
       nmb_reduce_all_direct_##op##_##ty(const T *a, TAG::Acc<T> *out, void *partials, uint32_t *counter,   \
                                         int64_t n, uint32_t *status, const unsigned long long *peers,      \
                                         int32_t rank, int32_t world) {                                     \

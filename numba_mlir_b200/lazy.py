@@ -1359,6 +1359,12 @@ class _ValueHolder:
 _FUSED_REDUCE_OPS = ("sum", "prod", "min", "max")
 
 
+def reduce_resident(em):
+    """Blocks per multiprocessor a generated reducer is compiled for: six (at
+    most 40 registers) for a short chain, four (64 registers) for a long one."""
+    return 6 if len(em.lines) <= 8 else 4
+
+
 def fused_reduce_mode(node):
     """How reduce(f(inputs)) can run in one pass over the inputs: 'rows' (the
     last axis), 'cols' (the first axis), 'all', or None (run the chain into a
@@ -1403,8 +1409,8 @@ def _emit_reduce_fused(trace, node, mode, dst):
     vec = 4 if vec_ok else 1
     n_streams = sum(1 for _s, k, _p, _d in em.leaves if k == "full")
     unroll = 4 if n_streams <= 2 else 2
-    sms = 148 if trace.dry else trace.queue.sm_count
-    block_row = mode == "rows" and cols >= 8192 and rows < sms * 8
+    sms = (148 if trace.dry else trace.queue.sm_count) * reduce_resident(em)  # residency slots
+    block_row = mode == "rows" and cols >= 8192 and rows < sms
     acc_dt = node.dtype
     shaped = any(k == "strided" for _s, k, _p, _d in em.leaves)
     sig = ("reduce", mode, node.op, acc_dt.name, block_row, tuple(shape) if shaped else len(shape),
@@ -1427,18 +1433,19 @@ def _emit_reduce_fused(trace, node, mode, dst):
     params.append(("slot", dst))
     if mode == "rows":
         units = rows if block_row else (rows + 7) // 8
-        grid = (max(1, min(units, sms * 8)),)
+        grid = (max(1, min(units, sms)),)
         params += [("i64", rows), ("i64", cols)]
     elif mode == "cols":
         gx = (cols + 256 * vec - 1) // (256 * vec)
-        gy = max(1, min((sms * 8 + gx - 1) // gx, (rows + 31) // 32, 65535))
-        if gx * 4 > 65536:
+        gy = max(1, min((sms + gx - 1) // gx, (rows + 31) // 32, 65535))
+        groups = (gy + 15) // 16  # the device merges row blocks in groups of 16 (kColFanIn)
+        if gx * (groups + 1) * 4 > 65536 - 4:
             return False  # more column tiles than ticket counters
         grid = (gx, gy)
-        params += [("scratch", gy * cols * acc_dt.itemsize), ("i64", rows), ("i64", cols)]
+        params += [("scratch", (gy + groups) * cols * acc_dt.itemsize), ("i64", rows), ("i64", cols)]
     else:
         tile = 256 * vec * unroll
-        grid = (max(1, min((n + tile - 1) // tile, sms * 8)),)
+        grid = (max(1, min((n + tile - 1) // tile, sms)),)
         params += [("scratch", grid[0] * acc_dt.itemsize), ("i64", n)]
     step = ("launch", blob, kname, grid, (256,), tuple(params))
     trace.steps.append(step)
@@ -1539,7 +1546,9 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
             tail = f"{act}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t n"
             call = (f"__shared__ {act} scratch[32];\n  nmb::reduce_all_fused<256, {vec}, {unroll}>(chain, n, "
                     f"out, partials, counters, {opc}(), {ident}, scratch);")
-        kernel = f"""extern "C" __global__ void __launch_bounds__(256) nmb_fused_reduce({', '.join(kparams + [tail])}) {{
+        # compiled for `resident` blocks per multiprocessor: the host launches one
+        # block per residency slot, rows and tiles go round robin
+        kernel = f"""extern "C" __global__ void __launch_bounds__(256, {reduce_resident(em)}) nmb_fused_reduce({', '.join(kparams + [tail])}) {{
   Chain chain{{{', '.join(ctor)}}};
   {call}
 }}"""

@@ -118,6 +118,10 @@ def reduce(a, op, axis=None, out=None):
 
 
 _DIRECT_OPS = ("sum", "prod", "min", "max")
+# the direct kernels are compiled for six resident blocks per multiprocessor and
+# hand out rows and tiles round robin: one block per residency slot keeps the
+# shares equal
+_DIRECT_BLOCKS_PER_SM = 6
 
 
 def _launch_rows(q, a, out, op, ty, rows, cols):
@@ -127,7 +131,7 @@ def _launch_rows(q, a, out, op, ty, rows, cols):
         block_row = cols >= 8192 and rows < q.sm_count * 8
         k = q.builtin(f"nmb_reduce_rows_direct_{'blockrow_' if block_row else ''}{op}_{ty}")
         units = rows if block_row else (rows + 7) // 8
-        q.launch(k, (max(1, min(units, q.sm_count * 8)),), (256,),
+        q.launch(k, (max(1, min(units, q.sm_count * _DIRECT_BLOCKS_PER_SM)),), (256,),
                  [("ptr", a.ptr), ("ptr", out.ptr), _I64(rows), _I64(cols)])
         return
     k = q.builtin(f"nmb_reduce_rows_{op}_{ty}")
@@ -176,7 +180,7 @@ def _launch_all(q, a, out, op, ty):
     peers, owed = _peer_params(q, op, out.nbytes)
     if op in _DIRECT_OPS:
         tile = 256 * (16 // a.dtype.itemsize) * 4  # elements a block takes per step
-        grid = max(1, min(q.sm_count * 8, (n + tile - 1) // tile))
+        grid = max(1, min(q.sm_count * _DIRECT_BLOCKS_PER_SM, (n + tile - 1) // tile))
         counters, partials = q.scratch(grid * 8)
         q.launch(q.builtin(f"nmb_reduce_all_direct_{op}_{ty}"), (grid,), (256,),
                  [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters), _I64(n),
