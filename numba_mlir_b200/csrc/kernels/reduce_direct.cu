@@ -6,8 +6,9 @@
 // itself".  On B200 they measured faster than the shared-memory ring of TMA
 // bulk copies (reduce_ws.cuh) for these two shapes -- float32 (16384, 4096)
 // sum(axis=1) 41.4 us against 43.9 us, 2^28 int32 full sum 152.3 us against
-// 162.9 us -- so the host dispatch uses them; column reductions and
-// argmin/argmax stay on the ring.  Same semantics as there: sum/prod accumulate
+// 162.9 us -- so the host dispatch uses them, and a warp-per-row argmin/argmax
+// built the same way; column reductions, and argmin/argmax over a few long
+// rows, stay on the ring.  Same semantics as there: sum/prod accumulate
 // in int64 for int32 input and in the array type otherwise, min/max are
 // select(x < m), NaNs never win, partials merged in index order.
 //
@@ -90,6 +91,63 @@ __device__ __forceinline__ void all_direct(const T *a, typename Tag::template Ac
   }
 }
 
+// out[r] = index of the first minimum (MIN) or maximum of a[r, :], one warp per
+// row.  A lane visits its elements in increasing index order, so a strict
+// comparison keeps the first occurrence; between lanes the lower index wins
+// ties.  NaNs never compare true and are passed over, as in the ring kernels;
+// a row in which nothing beats the identity gives index 0.
+template <typename T, bool MIN>
+__device__ __forceinline__ void rows_arg_direct(const T *__restrict__ a, int64_t *__restrict__ out,
+                                                int64_t rows, int64_t cols) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int64_t kNone = 0x7fffffffffffffffll;
+  const int lane = threadIdx.x & 31;
+  const int64_t first = (int64_t)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5);
+  const int64_t step = (int64_t)gridDim.x * (kBlock / 32);
+  constexpr int64_t span = 32 * V * kUnroll;
+  auto beats = [](T x, T v) { return MIN ? x < v : v < x; };
+  for (int64_t r = first; r < rows; r += step) {
+    const T *row = a + r * cols;
+    T bv = MIN ? nmb::neutral_min<T>() : nmb::neutral_max<T>();
+    int64_t bi = kNone;
+    int64_t k0 = 0;
+    for (; k0 + span <= cols; k0 += span) {
+      nmb::Vec<T, V> x[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        x[u] = nmb::load_stream<T, V>(row + k0 + (u * 32 + lane) * V);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+        for (int l = 0; l < V; ++l)
+          if (beats(x[u].v[l], bv)) {
+            bv = x[u].v[l];
+            bi = k0 + (u * 32 + lane) * V + l;
+          }
+    }
+    for (int64_t k = k0 + lane * V; k < cols; k += 32 * V) {
+      const nmb::Vec<T, V> x = nmb::load_stream<T, V>(row + k);
+#pragma unroll
+      for (int l = 0; l < V; ++l)
+        if (beats(x.v[l], bv)) {
+          bv = x.v[l];
+          bi = k + l;
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const T ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int64_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (beats(ov, bv) || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0)
+      out[r] = bi == kNone ? 0 : bi;
+  }
+}
+
 } // namespace
 
 // Launch (rows): grid.x blocks of 256 threads; a row belongs to one warp, or to
@@ -128,3 +186,19 @@ NMB_DIRECT_TYPES(sum, SumTag)
 NMB_DIRECT_TYPES(prod, ProdTag)
 NMB_DIRECT_TYPES(min, MinTag)
 NMB_DIRECT_TYPES(max, MaxTag)
+
+#define NMB_DIRECT_ARG(op, MIN, ty, T)                                                                     \
+  extern "C" __global__ void __launch_bounds__(kBlock, 6)                                                  \
+      nmb_reduce_rows_direct_##op##_##ty(const T *a, int64_t *out, int64_t rows, int64_t cols) {           \
+    rows_arg_direct<T, MIN>(a, out, rows, cols);                                                           \
+  }                                                                                                        \
+  NMB_REGISTER_KERNEL(nmb_reduce_rows_direct_##op##_##ty, 0);
+
+#define NMB_DIRECT_ARG_TYPES(op, MIN)                                                                      \
+  NMB_DIRECT_ARG(op, MIN, f32, float)                                                                      \
+  NMB_DIRECT_ARG(op, MIN, f64, double)                                                                     \
+  NMB_DIRECT_ARG(op, MIN, i32, int32_t)                                                                    \
+  NMB_DIRECT_ARG(op, MIN, i64, int64_t)
+
+NMB_DIRECT_ARG_TYPES(argmin, true)
+NMB_DIRECT_ARG_TYPES(argmax, false)

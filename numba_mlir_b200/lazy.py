@@ -1359,9 +1359,12 @@ class _ValueHolder:
 _FUSED_REDUCE_OPS = ("sum", "prod", "min", "max")
 
 
-def reduce_resident(em):
-    """Blocks per multiprocessor a generated reducer is compiled for: six (at
-    most 40 registers) for a short chain, four (64 registers) for a long one."""
+def reduce_resident(em, mode="all"):
+    """Blocks per multiprocessor a generated reducer is compiled for: eight (at
+    most 32 registers) for a row reduction of a short chain, six (40) for other
+    short chains, four (64) for a long one."""
+    if len(em.lines) <= 4 and mode == "rows":
+        return 8
     return 6 if len(em.lines) <= 8 else 4
 
 
@@ -1409,7 +1412,7 @@ def _emit_reduce_fused(trace, node, mode, dst):
     vec = 4 if vec_ok else 1
     n_streams = sum(1 for _s, k, _p, _d in em.leaves if k == "full")
     unroll = 4 if n_streams <= 2 else 2
-    sms = (148 if trace.dry else trace.queue.sm_count) * reduce_resident(em)  # residency slots
+    sms = (148 if trace.dry else trace.queue.sm_count) * reduce_resident(em, mode)  # residency slots
     block_row = mode == "rows" and cols >= 8192 and rows < sms
     acc_dt = node.dtype
     shaped = any(k == "strided" for _s, k, _p, _d in em.leaves)
@@ -1548,7 +1551,7 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
                     f"out, partials, counters, {opc}(), {ident}, scratch);")
         # compiled for `resident` blocks per multiprocessor: the host launches one
         # block per residency slot, rows and tiles go round robin
-        kernel = f"""extern "C" __global__ void __launch_bounds__(256, {reduce_resident(em)}) nmb_fused_reduce({', '.join(kparams + [tail])}) {{
+        kernel = f"""extern "C" __global__ void __launch_bounds__(256, {reduce_resident(em, mode)}) nmb_fused_reduce({', '.join(kparams + [tail])}) {{
   Chain chain{{{', '.join(ctor)}}};
   {call}
 }}"""

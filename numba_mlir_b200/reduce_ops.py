@@ -1,7 +1,8 @@
 """Host dispatch of the reduction kernels (sum/prod/min/max/argmin/argmax).
 
 Full and row reductions of sum/prod/min/max run on the direct-load kernels
-(csrc/kernels/reduce_direct.cu), column reductions and argmin/argmax on the
+(csrc/kernels/reduce_direct.cu), as do argmin/argmax along rows when there are
+enough rows; column reductions and argmin/argmax of a few long rows run on the
 TMA-staged ring (reduce_ws.cuh), anything unaligned or strided on the generic
 kernels.  Result dtypes follow the reference's _array_reduce
 (numba_mlir/numba_mlir/mlir/numpy/funcs.py:163-214): sum and prod of an integer
@@ -118,9 +119,11 @@ def reduce(a, op, axis=None, out=None):
 
 
 _DIRECT_OPS = ("sum", "prod", "min", "max")
-# the direct kernels are compiled for six resident blocks per multiprocessor and
-# hand out rows and tiles round robin: one block per residency slot keeps the
-# shares equal
+# the direct kernels hand out rows and tiles round robin and are compiled for a
+# fixed number of resident blocks per multiprocessor (rows: eight; full and
+# argmin/argmax: six):
+# one block per residency slot keeps the shares equal
+_DIRECT_ROWS_BLOCKS_PER_SM = 8
 _DIRECT_BLOCKS_PER_SM = 6
 
 
@@ -128,10 +131,17 @@ def _launch_rows(q, a, out, op, ty, rows, cols):
     if op in _DIRECT_OPS:
         # plain 128-bit loads, one warp per row (the whole block for few long
         # rows): measured faster than the TMA ring for these reductions
-        block_row = cols >= 8192 and rows < q.sm_count * 8
+        block_row = cols >= 8192 and rows < q.sm_count * _DIRECT_ROWS_BLOCKS_PER_SM
         k = q.builtin(f"nmb_reduce_rows_direct_{'blockrow_' if block_row else ''}{op}_{ty}")
         units = rows if block_row else (rows + 7) // 8
-        q.launch(k, (max(1, min(units, q.sm_count * _DIRECT_BLOCKS_PER_SM)),), (256,),
+        q.launch(k, (max(1, min(units, q.sm_count * _DIRECT_ROWS_BLOCKS_PER_SM)),), (256,),
+                 [("ptr", a.ptr), ("ptr", out.ptr), _I64(rows), _I64(cols)])
+        return
+    if rows >= q.sm_count * 2:
+        # argmin / argmax: one warp per row over plain loads (few long rows stay
+        # on the ring kernel below, which spreads a row over a whole block)
+        k = q.builtin(f"nmb_reduce_rows_direct_{op}_{ty}")
+        q.launch(k, (max(1, min((rows + 7) // 8, q.sm_count * _DIRECT_BLOCKS_PER_SM)),), (256,),
                  [("ptr", a.ptr), ("ptr", out.ptr), _I64(rows), _I64(cols)])
         return
     k = q.builtin(f"nmb_reduce_rows_{op}_{ty}")
