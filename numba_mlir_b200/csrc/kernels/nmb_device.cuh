@@ -359,6 +359,10 @@ __device__ __forceinline__ bool reduce_all_fused(const Chain &chain, int64_t n, 
   return true;
 }
 
+template <int N> struct IntTag {
+  static constexpr int value = N;
+};
+
 // Merges `count` rows of partials (row stride `cols`) for this thread's V
 // columns at `c`, eight rows of independent loads at a time, in row order.
 template <int V, typename A, typename Op>
@@ -382,38 +386,73 @@ __device__ __forceinline__ void merge_partial_rows(const A *rows, int64_t count,
   }
 }
 
-// out[c] = reduce_r value[r * cols + c].  A thread owns V adjacent columns;
-// blockIdx.y splits the rows.  The row blocks of a column tile meet in two
-// steps so that no block merges more than a few rows: groups of kColFanIn row
-// blocks merge into one row each (the block that draws the group's last
-// ticket does it), and the block that completes the last group merges the
-// groups' rows into `out`.  Scratch: partials[gridDim.y + groups][cols];
-// counters: 1 + groups tickets per column tile, left at zero.  cols % V == 0.
+// out[c] = reduce_r value[r * cols + c].  A block covers BLOCK * V * CV adjacent
+// columns: a thread owns CV groups of V adjacent columns, BLOCK * V apart, so
+// every row is read in whole 16-byte-per-lane segments and, when the block's
+// columns are all of them, as one contiguous stretch.  blockIdx.y splits the
+// rows.  The row blocks of a column tile meet in two steps so that no block
+// merges more than a few rows: groups of kColFanIn row blocks merge into one
+// row each (the block that draws the group's last ticket does it), and the
+// block that completes the last group merges the groups' rows into `out`.
+// Scratch: partials[gridDim.y + groups][cols]; counters: 1 + groups tickets per
+// column tile, left at zero.  cols % V == 0.
 constexpr int kColFanIn = 16;
 
-template <int BLOCK, int V, int UNROLL, typename A, typename Op, typename Chain>
+// `wrote` (optional, shared memory): set to 1 in the block that stored the
+// tile's final values into `out`.
+template <int BLOCK, int V, int CV, int UNROLL, typename A, typename Op, typename Chain>
 __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t rows, int64_t cols, A *out,
-                                                  A *partials, uint32_t *counters, Op op, A identity) {
-  const int64_t c = ((int64_t)blockIdx.x * BLOCK + threadIdx.x) * V;
+                                                  A *partials, uint32_t *counters, Op op, A identity,
+                                                  int *wrote = nullptr) {
+  const int64_t c0 = ((int64_t)blockIdx.x * BLOCK * CV + threadIdx.x) * V; // first group; group j at + j * BLOCK * V
   const int64_t Y = gridDim.y, y = blockIdx.y;
   const int64_t r0 = rows * y / Y, r1 = rows * (y + 1) / Y;
-  A acc[V];
+  A acc[CV][V];
 #pragma unroll
-  for (int l = 0; l < V; ++l)
-    acc[l] = identity;
-  if (c < cols) {
-    int64_t r = r0;
-    for (; r + UNROLL <= r1; r += UNROLL)
-      reduce_step<V, UNROLL, true>(chain, r * cols + c, cols, acc, op);
-    for (; r < r1; ++r)
-      reduce_step<V, 1, true>(chain, r * cols + c, 0, acc, op);
-    A *dst = Y == 1 ? out + c : partials + y * cols + c;
+  for (int j = 0; j < CV; ++j)
 #pragma unroll
     for (int l = 0; l < V; ++l)
-      dst[l] = acc[l];
+      acc[j][l] = identity;
+  auto rows_step = [&](int64_t r, auto unroll_tag) {
+    constexpr int U = decltype(unroll_tag)::value;
+    typename Chain::template In<V> in[U][CV];
+    typename Chain::template Out<V> val[U][CV];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < CV; ++j)
+        if (c0 + (int64_t)j * BLOCK * V < cols)
+          chain.template load<V>((r + u) * cols + c0 + (int64_t)j * BLOCK * V, in[u][j]);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < CV; ++j)
+        if (c0 + (int64_t)j * BLOCK * V < cols) {
+          chain.template compute<V>(in[u][j], val[u][j]);
+#pragma unroll
+          for (int l = 0; l < V; ++l)
+            acc[j][l] = op(acc[j][l], (A)val[u][j].out0.v[l]);
+        }
+  };
+  int64_t r = r0;
+  for (; r + UNROLL <= r1; r += UNROLL)
+    rows_step(r, IntTag<UNROLL>());
+  for (; r < r1; ++r)
+    rows_step(r, IntTag<1>());
+  {
+    A *dst = Y == 1 ? out : partials + y * cols;
+#pragma unroll
+    for (int j = 0; j < CV; ++j)
+      if (c0 + (int64_t)j * BLOCK * V < cols)
+#pragma unroll
+        for (int l = 0; l < V; ++l)
+          dst[c0 + (int64_t)j * BLOCK * V + l] = acc[j][l];
   }
-  if (Y == 1)
+  if (Y == 1) {
+    if (wrote && threadIdx.x == 0)
+      *wrote = 1;
     return;
+  }
   const int64_t groups = (Y + kColFanIn - 1) / kColFanIn;
   const int64_t g = y / kColFanIn;
   const int64_t gsize = Y - g * kColFanIn < kColFanIn ? Y - g * kColFanIn : kColFanIn;
@@ -431,19 +470,28 @@ __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t ro
   if (!last)
     return;
   __threadfence();
-  A m[V];
+  {
+    A *dst = groups == 1 ? out : level2 + g * cols;
 #pragma unroll
-  for (int l = 0; l < V; ++l)
-    m[l] = identity;
-  if (c < cols) {
-    merge_partial_rows<V>(partials + g * kColFanIn * cols, gsize, cols, c, m, op);
-    A *dst = groups == 1 ? out + c : level2 + g * cols + c;
+    for (int j = 0; j < CV; ++j) {
+      const int64_t c = c0 + (int64_t)j * BLOCK * V;
+      if (c < cols) {
+        A m[V];
 #pragma unroll
-    for (int l = 0; l < V; ++l)
-      dst[l] = m[l];
+        for (int l = 0; l < V; ++l)
+          m[l] = identity;
+        merge_partial_rows<V>(partials + g * kColFanIn * cols, gsize, cols, c, m, op);
+#pragma unroll
+        for (int l = 0; l < V; ++l)
+          dst[c + l] = m[l];
+      }
+    }
   }
-  if (groups == 1)
+  if (groups == 1) {
+    if (wrote && threadIdx.x == 0)
+      *wrote = 1;
     return;
+  }
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -455,15 +503,22 @@ __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t ro
   if (!last)
     return;
   __threadfence();
-  if (c < cols) {
 #pragma unroll
-    for (int l = 0; l < V; ++l)
-      m[l] = identity;
-    merge_partial_rows<V>(level2, groups, cols, c, m, op);
+  for (int j = 0; j < CV; ++j) {
+    const int64_t c = c0 + (int64_t)j * BLOCK * V;
+    if (c < cols) {
+      A m[V];
 #pragma unroll
-    for (int l = 0; l < V; ++l)
-      out[c + l] = m[l];
+      for (int l = 0; l < V; ++l)
+        m[l] = identity;
+      merge_partial_rows<V>(level2, groups, cols, c, m, op);
+#pragma unroll
+      for (int l = 0; l < V; ++l)
+        out[c + l] = m[l];
+    }
   }
+  if (wrote && threadIdx.x == 0)
+    *wrote = 1;
 }
 
 // ------------------------------------------------------------------- math ---

@@ -1362,7 +1362,9 @@ _FUSED_REDUCE_OPS = ("sum", "prod", "min", "max")
 def reduce_resident(em, mode="all"):
     """Blocks per multiprocessor a generated reducer is compiled for: eight (at
     most 32 registers) for a row reduction of a short chain, six (40) for other
-    short chains, four (64) for a long one."""
+    short chains, four (64) for a long one, two for column reductions."""
+    if mode == "cols":
+        return 2  # two row blocks per multiprocessor, many loads per thread in flight
     if len(em.lines) <= 4 and mode == "rows":
         return 8
     return 6 if len(em.lines) <= 8 else 4
@@ -1415,14 +1417,17 @@ def _emit_reduce_fused(trace, node, mode, dst):
     sms = (148 if trace.dry else trace.queue.sm_count) * reduce_resident(em, mode)  # residency slots
     block_row = mode == "rows" and cols >= 8192 and rows < sms
     acc_dt = node.dtype
+    # column reductions: a block spans up to four groups of 256 * vec columns, so
+    # that rows of up to 4096 elements are read as one contiguous stretch
+    col_vecs = max(1, min(4, (cols + 256 * vec - 1) // (256 * vec))) if mode == "cols" else 1
     shaped = any(k == "strided" for _s, k, _p, _d in em.leaves)
-    sig = ("reduce", mode, node.op, acc_dt.name, block_row, tuple(shape) if shaped else len(shape),
+    sig = ("reduce", mode, node.op, acc_dt.name, block_row, col_vecs, tuple(shape) if shaped else len(shape),
            tuple((k, p if k == "strided" else (), d.name) for _s, k, p, d in em.leaves),
            tuple(em.sig), (expr, src.dtype.name), vec, unroll, trace.fastmath)
     hit = _kernel_cache.get(sig)
     if hit is None:
         hit = _generate(em, results, shape, vec, unroll, [None], trace.fastmath,
-                        reduce=(mode, node.op, acc_dt, block_row))
+                        reduce=(mode, node.op, acc_dt, block_row, col_vecs))
         _kernel_cache[sig] = hit
     blob, kname = hit
 
@@ -1439,8 +1444,11 @@ def _emit_reduce_fused(trace, node, mode, dst):
         grid = (max(1, min(units, sms)),)
         params += [("i64", rows), ("i64", cols)]
     elif mode == "cols":
-        gx = (cols + 256 * vec - 1) // (256 * vec)
-        gy = max(1, min((sms + gx - 1) // gx, (rows + 31) // 32, 65535))
+        gx = (cols + 256 * vec * col_vecs - 1) // (256 * vec * col_vecs)
+        # two row blocks per multiprocessor in all: eight or more loads per thread
+        # keep the memory busy, and few partial rows keep the merge short
+        slots = (148 if trace.dry else trace.queue.sm_count) * 2
+        gy = max(1, min((slots + gx - 1) // gx, (rows + 31) // 32, 65535))
         groups = (gy + 15) // 16  # the device merges row blocks in groups of 16 (kColFanIn)
         if gx * (groups + 1) * 4 > 65536 - 4:
             return False  # more column tiles than ticket counters
@@ -1460,8 +1468,9 @@ def _emit_reduce_fused(trace, node, mode, dst):
 def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, shared_in=frozenset(),
               shared_out=frozenset(), reduce=None):
     """CUDA C for one fused chain; returns (tagged source blob, kernel name).
-    With `reduce` = (mode, op, accumulator dtype, block_row) the single result
-    is not stored but reduced on the way (nmb::reduce_*_fused)."""
+    With `reduce` = (mode, op, accumulator dtype, block_row, column groups per
+    thread) the single result is not stored but reduced on the way
+    (nmb::reduce_*_fused)."""
     members, ctor, kparams = [], [], []
     in_fields, loads = [], []
     nd = len(out_shape)
@@ -1530,7 +1539,7 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
 }}"""
         kname = "nmb_fused"
     else:
-        mode, op, acc_dt, block_row = reduce
+        mode, op, acc_dt, block_row, col_vecs = reduce
         act = ctype(acc_dt)
         opc, ident = {"sum": ("nmb::OpAdd", f"{act}(0)"), "prod": ("nmb::OpMul", f"{act}(1)"),
                       "min": ("nmb::OpMin", f"nmb::neutral_min<{act}>()"),
@@ -1543,8 +1552,8 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
         elif mode == "cols":
             tail = (f"{act}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t rows, "
                     "int64_t cols")
-            call = (f"nmb::reduce_cols_fused<256, {vec}, {unroll}>(chain, rows, cols, out, partials, "
-                    f"counters, {opc}(), {ident});")
+            call = (f"nmb::reduce_cols_fused<256, {vec}, {col_vecs}, {max(1, unroll // 2)}>(chain, rows, cols, "
+                    f"out, partials, counters, {opc}(), {ident});")
         else:
             tail = f"{act}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t n"
             call = (f"__shared__ {act} scratch[32];\n  nmb::reduce_all_fused<256, {vec}, {unroll}>(chain, n, "
