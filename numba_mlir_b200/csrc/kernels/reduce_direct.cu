@@ -7,8 +7,9 @@
 // bulk copies (reduce_ws.cuh) for these two shapes -- float32 (16384, 4096)
 // sum(axis=1) 41.4 us against 43.9 us, 2^28 int32 full sum 152.3 us against
 // 162.9 us -- so the host dispatch uses them, and a warp-per-row argmin/argmax
-// built the same way; column reductions, and argmin/argmax over a few long
-// rows, stay on the ring.  Same semantics as there: sum/prod accumulate
+// built the same way; column reductions (a direct-load column kernel took
+// 61-65 us against the ring's 47 us on the same matrix), and argmin/argmax over a
+// few long rows, stay on the ring.  Same semantics as there: sum/prod accumulate
 // in int64 for int32 input and in the array type otherwise, min/max are
 // select(x < m), NaNs never win, partials merged in index order.
 //
@@ -91,60 +92,6 @@ __device__ __forceinline__ void all_direct(const T *a, typename Tag::template Ac
   }
 }
 
-// out[c] = reduce(a[:, c]); cols % (16 / sizeof(T)) == 0, a 16-byte aligned.
-// A block spans 256 * (16 / sizeof(T)) * 4 columns (4096 float32: a whole row
-// of the benchmark's matrix, read as one contiguous stretch).  `done` counts
-// the column tiles that have their final values; with an exchange pending the
-// block that completes a tile all-reduces it across the GPUs, and the last of
-// them closes the call (as reduce_cols_ws does).
-template <typename Tag, typename T>
-__device__ __forceinline__ void cols_direct(const T *a, typename Tag::template Acc<T> *out, void *partials,
-                                            uint32_t *counters, int64_t rows, int64_t cols, uint32_t *status,
-                                            const nmb::peer::Args px) {
-  using A = typename Tag::template Acc<T>;
-  constexpr int V = 16 / sizeof(T);
-  constexpr int CV = 4;
-  PlainChain<T> chain{a};
-  // reduce_cols_fused returns in every block; the block that wrote `out` is
-  // the one for which the tile's last ticket came back, which it cannot tell
-  // us, so the exchange keys on a flag the writer sets in shared memory
-  __shared__ int wrote;
-  if (threadIdx.x == 0)
-    wrote = 0;
-  __syncthreads();
-  nmb::reduce_cols_fused<kBlock, V, CV, 2>(chain, rows, cols, out, static_cast<A *>(partials), counters,
-                                           typename Tag::Op(), Tag::template identity<A>(), &wrote);
-  if (px.world <= 1)
-    return;
-  __syncthreads();
-  if (!wrote)
-    return;
-  // this block holds the final values of its column tile
-  const int64_t c0 = (int64_t)blockIdx.x * kBlock * V * CV;
-  const int64_t ncols = cols - c0 < (int64_t)kBlock * V * CV ? cols - c0 : (int64_t)kBlock * V * CV;
-  __shared__ nmb::peer::Call call;
-  __shared__ bool last_tile;
-  __threadfence();
-  const unsigned long long off = (unsigned long long)c0 * sizeof(A);
-  if (!nmb::peer::args_ok(px.rank, px.world, off + (unsigned long long)ncols * sizeof(A))) {
-    if (threadIdx.x == 0)
-      atomicExch(status, (uint32_t)nmb::kStatusWaitTimeout);
-    return;
-  }
-  nmb::peer::begin(call, px.peers, px.rank, px.world);
-  nmb::peer::push(call, px.rank, px.world, out + c0, ncols, off);
-  nmb::peer::pull(call, px.rank, px.world, out + c0, ncols, off, typename Tag::Op(), status);
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint32_t *done = counters + 16383; // the last word of the 64 KB counter region
-    last_tile = atomicAdd(done, 1u) == gridDim.x - 1;
-    if (last_tile) {
-      *done = 0;
-      nmb::peer::end_call(call, px.rank);
-    }
-  }
-}
-
 // out[r] = index of the first minimum (MIN) or maximum of a[r, :], one warp per
 // row.  A lane visits its elements in increasing index order, so a strict
 // comparison keeps the first occurrence; between lanes the lower index wins
@@ -210,9 +157,6 @@ __device__ __forceinline__ void rows_arg_direct(const T *__restrict__ a, int64_t
 // sizeof(T)) * 4 elements round robin; scratch holds grid.x accumulators and one
 // zeroed counter; peers/rank/world: the exchange that ends the kernel
 // (world <= 1: none).
-// Launch (cols): grid = (column tiles of 256 * (16 / sizeof(T)) * 4 columns, row
-// blocks); scratch holds (row blocks + ceil(row blocks / 16)) partial rows and,
-// per column tile, 1 + ceil(row blocks / 16) zeroed counters.
 #define NMB_DIRECT(op, TAG, ty, T)                                                                         \
   extern "C" __global__ void __launch_bounds__(kBlock, 6)                                                   \
       nmb_reduce_rows_direct_##op##_##ty(const T *a, TAG::Acc<T> *out, int64_t rows, int64_t cols) {       \
@@ -233,25 +177,11 @@ __device__ __forceinline__ void rows_arg_direct(const T *__restrict__ a, int64_t
   }                                                                                                        \
   NMB_REGISTER_KERNEL(nmb_reduce_all_direct_##op##_##ty, 0);
 
-#define NMB_DIRECT_COLS(op, TAG, ty, T)                                                                    \
-  extern "C" __global__ void __launch_bounds__(kBlock, 2)                                                  \
-      nmb_reduce_cols_direct_##op##_##ty(const T *a, TAG::Acc<T> *out, void *partials, uint32_t *counters, \
-                                         int64_t rows, int64_t cols, uint32_t *status,                     \
-                                         const unsigned long long *peers, int32_t rank, int32_t world) {   \
-    cols_direct<TAG, T>(a, out, partials, counters, rows, cols, status,                                    \
-                        nmb::peer::Args{peers, rank, world});                                              \
-  }                                                                                                        \
-  NMB_REGISTER_KERNEL(nmb_reduce_cols_direct_##op##_##ty, 0);
-
 #define NMB_DIRECT_TYPES(op, TAG)                                                                          \
   NMB_DIRECT(op, TAG, f32, float)                                                                          \
   NMB_DIRECT(op, TAG, f64, double)                                                                         \
   NMB_DIRECT(op, TAG, i32, int32_t)                                                                        \
-  NMB_DIRECT(op, TAG, i64, int64_t)                                                                        \
-  NMB_DIRECT_COLS(op, TAG, f32, float)                                                                     \
-  NMB_DIRECT_COLS(op, TAG, f64, double)                                                                    \
-  NMB_DIRECT_COLS(op, TAG, i32, int32_t)                                                                   \
-  NMB_DIRECT_COLS(op, TAG, i64, int64_t)
+  NMB_DIRECT(op, TAG, i64, int64_t)
 
 NMB_DIRECT_TYPES(sum, SumTag)
 NMB_DIRECT_TYPES(prod, ProdTag)

@@ -1362,9 +1362,7 @@ _FUSED_REDUCE_OPS = ("sum", "prod", "min", "max")
 def reduce_resident(em, mode="all"):
     """Blocks per multiprocessor a generated reducer is compiled for: eight (at
     most 32 registers) for a row reduction of a short chain, six (40) for other
-    short chains, four (64) for a long one, two for column reductions."""
-    if mode == "cols":
-        return 2  # two row blocks per multiprocessor, many loads per thread in flight
+    short chains, four (64) for a long one."""
     if len(em.lines) <= 4 and mode == "rows":
         return 8
     return 6 if len(em.lines) <= 8 else 4
@@ -1417,9 +1415,9 @@ def _emit_reduce_fused(trace, node, mode, dst):
     sms = (148 if trace.dry else trace.queue.sm_count) * reduce_resident(em, mode)  # residency slots
     block_row = mode == "rows" and cols >= 8192 and rows < sms
     acc_dt = node.dtype
-    # column reductions: a block spans up to four groups of 256 * vec columns, so
-    # that rows of up to 4096 elements are read as one contiguous stretch
-    col_vecs = max(1, min(4, (cols + 256 * vec - 1) // (256 * vec))) if mode == "cols" else 1
+    # column reductions: one group of 256 * vec columns per block (four groups,
+    # whole 16 KB rows per block, measured slower: 66 us against 61 us)
+    col_vecs = 1
     shaped = any(k == "strided" for _s, k, _p, _d in em.leaves)
     sig = ("reduce", mode, node.op, acc_dt.name, block_row, col_vecs, tuple(shape) if shaped else len(shape),
            tuple((k, p if k == "strided" else (), d.name) for _s, k, p, d in em.leaves),
@@ -1445,10 +1443,7 @@ def _emit_reduce_fused(trace, node, mode, dst):
         params += [("i64", rows), ("i64", cols)]
     elif mode == "cols":
         gx = (cols + 256 * vec * col_vecs - 1) // (256 * vec * col_vecs)
-        # two row blocks per multiprocessor in all: eight or more loads per thread
-        # keep the memory busy, and few partial rows keep the merge short
-        slots = (148 if trace.dry else trace.queue.sm_count) * 2
-        gy = max(1, min((slots + gx - 1) // gx, (rows + 31) // 32, 65535))
+        gy = max(1, min((sms + gx - 1) // gx, (rows + 31) // 32, 65535))
         groups = (gy + 15) // 16  # the device merges row blocks in groups of 16 (kColFanIn)
         if gx * (groups + 1) * 4 > 65536 - 4:
             return False  # more column tiles than ticket counters
@@ -1552,7 +1547,7 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
         elif mode == "cols":
             tail = (f"{act}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t rows, "
                     "int64_t cols")
-            call = (f"nmb::reduce_cols_fused<256, {vec}, {col_vecs}, {max(1, unroll // 2)}>(chain, rows, cols, "
+            call = (f"nmb::reduce_cols_fused<256, {vec}, {col_vecs}, {unroll}>(chain, rows, cols, "
                     f"out, partials, counters, {opc}(), {ident});")
         else:
             tail = f"{act}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t n"

@@ -1,9 +1,11 @@
 """Host dispatch of the reduction kernels (sum/prod/min/max/argmin/argmax).
 
-Full, row and column reductions of sum/prod/min/max run on the direct-load
-kernels (csrc/kernels/reduce_direct.cu), as do argmin/argmax along rows when
-there are enough rows; argmin/argmax along columns or over a few long rows run
-on the TMA-staged ring (reduce_ws.cuh), anything unaligned or strided on the generic
+Full and row reductions of sum/prod/min/max run on the direct-load kernels
+(csrc/kernels/reduce_direct.cu), as do argmin/argmax along rows when there are
+enough rows; column reductions and argmin/argmax of a few long rows run on the
+TMA-staged ring (reduce_ws.cuh), which measured faster there (float32
+(16384, 4096) min(axis=0): 47 us against 61-65 us for direct-load column
+kernels), anything unaligned or strided on the generic
 kernels.  Result dtypes follow the reference's _array_reduce
 (numba_mlir/numba_mlir/mlir/numpy/funcs.py:163-214): sum and prod of an integer
 array are int64, of a float array the array's dtype; min/max keep the dtype;
@@ -157,22 +159,6 @@ def _launch_rows(q, a, out, op, ty, rows, cols):
 
 def _launch_cols(q, a, out, op, ty, rows, cols):
     peers, owed = _peer_params(q, op, out.nbytes)
-    if op in _DIRECT_OPS:
-        # plain loads, a block spans 256 x 4 column vectors (whole rows of up to
-        # 16 KB are read as one contiguous stretch), two row blocks per
-        # multiprocessor, partial rows merged in two steps of at most 16 rows
-        tile_cols = 256 * (16 // a.dtype.itemsize) * 4
-        gx = (cols + tile_cols - 1) // tile_cols
-        gy = max(1, min((2 * q.sm_count + gx - 1) // gx, (rows + 31) // 32, 65535))
-        groups = (gy + 15) // 16
-        if gx * (groups + 1) * 4 <= q.COUNTER_BYTES - 4:
-            counters, partials = q.scratch((gy + groups) * cols * _acc_bytes(op, a.dtype))
-            q.launch(q.builtin(f"nmb_reduce_cols_direct_{op}_{ty}"), (gx, gy), (256,),
-                     [("ptr", a.ptr), ("ptr", out.ptr), ("ptr", partials), ("ptr", counters), _I64(rows),
-                      _I64(cols), ("ptr", q.status_ptr)] + peers)
-            if owed is not None:
-                owed.allreduce(out, op)
-            return
     k = q.builtin(f"nmb_reduce_cols_{op}_{ty}")
     it = a.dtype.itemsize
     # column slabs of 4 KB: each thread owns one 16-byte column vector and the
