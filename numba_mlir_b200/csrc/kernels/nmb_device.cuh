@@ -286,8 +286,11 @@ __device__ __forceinline__ void reduce_step(const Chain &chain, int64_t i0, int6
 // out[r] = reduce_k value[r * cols + k].  A row belongs to one warp (or, with
 // BLOCK_ROW, to the whole block: few long rows); rows are taken round robin.
 // cols % V == 0.
-template <int BLOCK, int V, int UNROLL, bool BLOCK_ROW, typename A, typename Op, typename Chain>
-__device__ __forceinline__ void reduce_rows_fused(const Chain &chain, int64_t rows, int64_t cols, A *out, Op op,
+// Every result goes through chain.post(acc) on its way out: the elementwise
+// chain that follows the reduction (np.sqrt(np.sum(...)), a mean's division),
+// or the identity.
+template <int BLOCK, int V, int UNROLL, bool BLOCK_ROW, typename A, typename O, typename Op, typename Chain>
+__device__ __forceinline__ void reduce_rows_fused(const Chain &chain, int64_t rows, int64_t cols, O *out, Op op,
                                                   A identity, A *scratch) {
   constexpr int L = BLOCK_ROW ? BLOCK : 32;
   const int t = BLOCK_ROW ? threadIdx.x : (threadIdx.x & 31);
@@ -305,11 +308,11 @@ __device__ __forceinline__ void reduce_rows_fused(const Chain &chain, int64_t ro
     if (BLOCK_ROW) {
       acc = block_reduce(acc, op, identity, scratch);
       if (threadIdx.x == 0)
-        out[r] = acc;
+        out[r] = chain.post(acc);
     } else {
       acc = warp_reduce(acc, op);
       if (t == 0)
-        out[r] = acc;
+        out[r] = chain.post(acc);
     }
   }
 }
@@ -317,8 +320,8 @@ __device__ __forceinline__ void reduce_rows_fused(const Chain &chain, int64_t ro
 // out[0] = reduce_i value[i], i < n.  Blocks take tiles of BLOCK*V*UNROLL
 // elements round robin; n % V may be anything (the tail is read one by one).
 // Returns true in the one block that wrote the result (uniform over the block).
-template <int BLOCK, int V, int UNROLL, typename A, typename Op, typename Chain>
-__device__ __forceinline__ bool reduce_all_fused(const Chain &chain, int64_t n, A *out, A *partials,
+template <int BLOCK, int V, int UNROLL, typename A, typename O, typename Op, typename Chain>
+__device__ __forceinline__ bool reduce_all_fused(const Chain &chain, int64_t n, O *out, A *partials,
                                                  uint32_t *counter, Op op, A identity, A *scratch) {
   constexpr int64_t tile = (int64_t)BLOCK * V * UNROLL;
   A acc = identity;
@@ -353,7 +356,7 @@ __device__ __forceinline__ bool reduce_all_fused(const Chain &chain, int64_t n, 
     m = op(m, load_partial(partials + g));
   m = block_reduce(m, op, identity, scratch);
   if (threadIdx.x == 0) {
-    out[0] = m;
+    out[0] = chain.post(m);
     *counter = 0;
   }
   return true;
@@ -400,8 +403,8 @@ constexpr int kColFanIn = 16;
 
 // `wrote` (optional, shared memory): set to 1 in the block that stored the
 // tile's final values into `out`.
-template <int BLOCK, int V, int CV, int UNROLL, typename A, typename Op, typename Chain>
-__device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t rows, int64_t cols, A *out,
+template <int BLOCK, int V, int CV, int UNROLL, typename A, typename O, typename Op, typename Chain>
+__device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t rows, int64_t cols, O *out,
                                                   A *partials, uint32_t *counters, Op op, A identity,
                                                   int *wrote = nullptr) {
   const int64_t c0 = ((int64_t)blockIdx.x * BLOCK * CV + threadIdx.x) * V; // first group; group j at + j * BLOCK * V
@@ -439,15 +442,16 @@ __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t ro
     rows_step(r, IntTag<UNROLL>());
   for (; r < r1; ++r)
     rows_step(r, IntTag<1>());
-  {
-    A *dst = Y == 1 ? out : partials + y * cols;
 #pragma unroll
-    for (int j = 0; j < CV; ++j)
-      if (c0 + (int64_t)j * BLOCK * V < cols)
+  for (int j = 0; j < CV; ++j)
+    if (c0 + (int64_t)j * BLOCK * V < cols)
 #pragma unroll
-        for (int l = 0; l < V; ++l)
-          dst[c0 + (int64_t)j * BLOCK * V + l] = acc[j][l];
-  }
+      for (int l = 0; l < V; ++l) {
+        if (Y == 1)
+          out[c0 + (int64_t)j * BLOCK * V + l] = chain.post(acc[j][l]);
+        else
+          partials[y * cols + c0 + (int64_t)j * BLOCK * V + l] = acc[j][l];
+      }
   if (Y == 1) {
     if (wrote && threadIdx.x == 0)
       *wrote = 1;
@@ -470,20 +474,21 @@ __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t ro
   if (!last)
     return;
   __threadfence();
-  {
-    A *dst = groups == 1 ? out : level2 + g * cols;
 #pragma unroll
-    for (int j = 0; j < CV; ++j) {
-      const int64_t c = c0 + (int64_t)j * BLOCK * V;
-      if (c < cols) {
-        A m[V];
+  for (int j = 0; j < CV; ++j) {
+    const int64_t c = c0 + (int64_t)j * BLOCK * V;
+    if (c < cols) {
+      A m[V];
 #pragma unroll
-        for (int l = 0; l < V; ++l)
-          m[l] = identity;
-        merge_partial_rows<V>(partials + g * kColFanIn * cols, gsize, cols, c, m, op);
+      for (int l = 0; l < V; ++l)
+        m[l] = identity;
+      merge_partial_rows<V>(partials + g * kColFanIn * cols, gsize, cols, c, m, op);
 #pragma unroll
-        for (int l = 0; l < V; ++l)
-          dst[c + l] = m[l];
+      for (int l = 0; l < V; ++l) {
+        if (groups == 1)
+          out[c + l] = chain.post(m[l]);
+        else
+          level2[g * cols + c + l] = m[l];
       }
     }
   }
@@ -514,7 +519,7 @@ __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t ro
       merge_partial_rows<V>(level2, groups, cols, c, m, op);
 #pragma unroll
       for (int l = 0; l < V; ++l)
-        out[c + l] = m[l];
+        out[c + l] = chain.post(m[l]);
     }
   }
   if (wrote && threadIdx.x == 0)

@@ -36,6 +36,7 @@ template <typename T> struct PlainChain {
     r.in0 = nmb::load_stream<T, V>(in0 + i);
   }
   template <int V> __device__ __forceinline__ void compute(const In<V> &r, Out<V> &o) const { o.out0 = r.in0; }
+  template <typename A> __device__ __forceinline__ A post(A v) const { return v; }
 };
 
 template <typename T> struct Wide { using type = T; };

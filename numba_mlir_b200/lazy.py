@@ -529,6 +529,9 @@ class Trace:
         kind = node.kind
         spec = None
         if kind not in ("reduce", "dot"):
+            red = _match_post_reduce(node)
+            if red is not None:
+                return self._store_post_reduce(slot, node, red, emit)
             spec = _match_rowcol(self, node)
             if spec is None:
                 return False
@@ -549,6 +552,23 @@ class Trace:
             self._lower_dot(node, slot)
         else:
             self._lower_rowcol(node, spec, slot)
+        return True
+
+    def _store_post_reduce(self, slot, node, red, emit):
+        """`target = g(reduce(f(inputs)))` with g elementwise over the reduced
+        value alone: one generated reducer applies g on the way out."""
+        dst = self.arrays[slot]
+        if (dst.shape != node.shape or dst.dtype != node.dtype or dst.size == 0 or not dst.is_c_contiguous
+                or any(self.overlap(r, slot) for r in node_reads(node))):
+            return False
+        self.lower(red.inputs[0])
+        mode = fused_reduce_mode(red, leaf_ok=True)
+        if mode is None:
+            return False
+        emit()
+        if not _emit_reduce_fused(self, red, mode, slot, post=node):
+            return False
+        node.become_leaf(slot, borrowed=True)
         return True
 
     def materialize(self, lazy):
@@ -1147,6 +1167,30 @@ def _match_rowcol(trace, node):
     return alpha, product, row, col, func
 
 
+def _match_post_reduce(node):
+    """The reduction node when `node` is an elementwise chain over ONE
+    reduction's value and scalars only (np.sqrt(np.sum(...)), sum / count, ...)
+    with the reduction's shape; None otherwise."""
+    if node.kind not in ("op", "cast", "where", "call"):
+        return None
+    found = []
+
+    def walk(n):
+        if n.kind == "reduce":
+            if not found:
+                found.append(n)
+            return n is found[0]
+        if n.kind in ("const", "arg"):
+            return n.shape == ()
+        if n.kind in ("op", "cast", "where", "call"):
+            return all(walk(i) for i in n.inputs)
+        return False  # arrays, products, reshapes
+
+    if not walk(node) or not found or found[0].shape != node.shape:
+        return None
+    return found[0]
+
+
 def _is_row_norms(trace, term, operand_slot, transposed):
     """`term` is sum(x * x, axis=1) (possibly reshaped) of the matrix x whose
     rows the contraction's operand holds: x is the array of `operand_slot`, or
@@ -1368,12 +1412,15 @@ def reduce_resident(em, mode="all"):
     return 6 if len(em.lines) <= 8 else 4
 
 
-def fused_reduce_mode(node):
+def fused_reduce_mode(node, leaf_ok=False):
     """How reduce(f(inputs)) can run in one pass over the inputs: 'rows' (the
     last axis), 'cols' (the first axis), 'all', or None (run the chain into a
-    temporary first)."""
+    temporary first).  A plain array as operand goes to the library kernels
+    unless `leaf_ok` (a post-chain is to be fused into the generated kernel)."""
     src = node.inputs[0]
-    if node.op not in _FUSED_REDUCE_OPS or src.kind in ("leaf", "arg", "const") or not node_reads(src):
+    if node.op not in _FUSED_REDUCE_OPS or src.kind in ("arg", "const") or not node_reads(src):
+        return None
+    if src.kind == "leaf" and not leaf_ok:
         return None
     if src.dtype.name not in _REDUCE_KERNEL_DTYPES:
         return None
@@ -1387,14 +1434,23 @@ def fused_reduce_mode(node):
     return None
 
 
-def _emit_reduce_fused(trace, node, mode, dst):
-    """One kernel for reduce(chain): the chain's inputs are read once."""
+def _emit_reduce_fused(trace, node, mode, dst, post=None):
+    """One kernel for reduce(chain): the chain's inputs are read once.  `post`
+    is an elementwise chain over the reduced value alone (its root node): it is
+    applied to every result on its way out, so sqrt(sum(...)) or a mean's
+    division need no launch of their own."""
     src = node.inputs[0]
     shape = src.shape
     n = int(np.prod(shape, dtype=np.int64))
     em = _Emitter(trace, shape)
     expr = em.emit(src)
     results = [(None, expr, _ValueHolder(src.dtype))]
+    n_chain = len(em.lines)
+    post_expr, out_dt = "racc", node.dtype
+    if post is not None:
+        em.names[id(node)] = "racc"
+        em.sig.append(("racc", node.dtype.name))
+        post_expr, out_dt = em.emit(post), post.dtype
     if mode == "rows":
         rows, cols = n // shape[-1], shape[-1]
     elif mode == "cols":
@@ -1421,11 +1477,12 @@ def _emit_reduce_fused(trace, node, mode, dst):
     shaped = any(k == "strided" for _s, k, _p, _d in em.leaves)
     sig = ("reduce", mode, node.op, acc_dt.name, block_row, col_vecs, tuple(shape) if shaped else len(shape),
            tuple((k, p if k == "strided" else (), d.name) for _s, k, p, d in em.leaves),
-           tuple(em.sig), (expr, src.dtype.name), vec, unroll, trace.fastmath)
+           tuple(em.sig), (expr, src.dtype.name), (n_chain, post_expr, np.dtype(out_dt).name), vec, unroll,
+           trace.fastmath)
     hit = _kernel_cache.get(sig)
     if hit is None:
         hit = _generate(em, results, shape, vec, unroll, [None], trace.fastmath,
-                        reduce=(mode, node.op, acc_dt, block_row, col_vecs))
+                        reduce=(mode, node.op, acc_dt, block_row, col_vecs, n_chain, post_expr, out_dt))
         _kernel_cache[sig] = hit
     blob, kname = hit
 
@@ -1464,8 +1521,10 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
               shared_out=frozenset(), reduce=None):
     """CUDA C for one fused chain; returns (tagged source blob, kernel name).
     With `reduce` = (mode, op, accumulator dtype, block_row, column groups per
-    thread) the single result is not stored but reduced on the way
-    (nmb::reduce_*_fused)."""
+    thread, number of chain lines before the post-chain, post expression, output
+    dtype) the single result is not stored but reduced on the way
+    (nmb::reduce_*_fused); the lines after the chain's own and the post
+    expression turn the reduced value `racc` into what is stored."""
     members, ctor, kparams = [], [], []
     in_fields, loads = [], []
     nd = len(out_shape)
@@ -1526,6 +1585,12 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
             stores.append(" ".join(body))
     nl = "\n      "
     funcs = "\n".join(em.funcs.values())
+    chain_lines, post_method = em.lines, ""
+    if reduce is not None:
+        n_chain, post_expr, out_dt = reduce[5], reduce[6], reduce[7]
+        chain_lines = em.lines[:n_chain]
+        post_method = (f"  __device__ __forceinline__ {ctype(out_dt)} post({ctype(reduce[2])} racc) const {{\n    "
+                       + "\n    ".join(em.lines[n_chain:]) + f"\n    return {post_expr};\n  }}\n")
     if reduce is None:
         kparams.append("int64_t n")
         kernel = f"""extern "C" __global__ void __launch_bounds__(256) nmb_fused({', '.join(kparams)}) {{
@@ -1534,23 +1599,23 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
 }}"""
         kname = "nmb_fused"
     else:
-        mode, op, acc_dt, block_row, col_vecs = reduce
-        act = ctype(acc_dt)
+        mode, op, acc_dt, block_row, col_vecs = reduce[:5]
+        act, oct = ctype(acc_dt), ctype(reduce[7])
         opc, ident = {"sum": ("nmb::OpAdd", f"{act}(0)"), "prod": ("nmb::OpMul", f"{act}(1)"),
                       "min": ("nmb::OpMin", f"nmb::neutral_min<{act}>()"),
                       "max": ("nmb::OpMax", f"nmb::neutral_max<{act}>()")}[op]
         kname = "nmb_fused_reduce"
         if mode == "rows":
-            tail = f"{act}* __restrict__ out, int64_t rows, int64_t cols"
+            tail = f"{oct}* __restrict__ out, int64_t rows, int64_t cols"
             call = (f"__shared__ {act} scratch[32];\n  nmb::reduce_rows_fused<256, {vec}, {unroll}, "
                     f"{'true' if block_row else 'false'}>(chain, rows, cols, out, {opc}(), {ident}, scratch);")
         elif mode == "cols":
-            tail = (f"{act}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t rows, "
+            tail = (f"{oct}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t rows, "
                     "int64_t cols")
             call = (f"nmb::reduce_cols_fused<256, {vec}, {col_vecs}, {unroll}>(chain, rows, cols, "
                     f"out, partials, counters, {opc}(), {ident});")
         else:
-            tail = f"{act}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t n"
+            tail = f"{oct}* __restrict__ out, {act}* partials, uint32_t* counters, int64_t n"
             call = (f"__shared__ {act} scratch[32];\n  nmb::reduce_all_fused<256, {vec}, {unroll}>(chain, n, "
                     f"out, partials, counters, {opc}(), {ident}, scratch);")
         # compiled for `resident` blocks per multiprocessor: the host launches one
@@ -1576,10 +1641,11 @@ struct Chain {{
   template <int V> __device__ __forceinline__ void compute(const In<V>& r, Out<V>& o) const {{
 #pragma unroll
     for (int l = 0; l < V; ++l) {{
-      {nl.join(em.lines)}
+      {nl.join(chain_lines)}
       {nl.join(out_assign)}
     }}
   }}
+{post_method}
   template <int V> __device__ __forceinline__ void store(int64_t i, const Out<V>& o) const {{
     {(nl[:-2]).join(stores)}
   }}

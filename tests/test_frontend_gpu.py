@@ -527,7 +527,7 @@ def test_reduction_of_an_elementwise_chain_is_one_pass(queue):
     norm = nm.njit(lambda x: np.sqrt(np.square(x).sum(axis=1)))
     norm(da)  # traced; the second call replays the plan
     got, n = _launches(norm, da)
-    assert n == 2  # the reduction over the chain + the sqrt of the row sums
+    assert n == 1  # the reduction over the chain; the sqrt is applied to each row sum on its way out
     np.testing.assert_allclose(got.copy_to_host(), np.sqrt((a.astype(np.float64) ** 2).sum(1)), rtol=1e-5)
 
     rowsq = nm.njit(lambda x, out: out.__setitem__(slice(None), np.sum(x * x, axis=1)))
@@ -545,8 +545,13 @@ def test_reduction_of_an_elementwise_chain_is_one_pass(queue):
     mse = nm.njit(lambda x, y: np.mean((x - y) ** 2))
     mse(da, db)
     got, n = _launches(mse, da, db)
-    assert n == 2  # reduction, then the division by the element count
+    assert n == 1  # the division by the element count rides on the reduction
     np.testing.assert_allclose(float(got.copy_to_host()), np.mean((a.astype(np.float64) - b) ** 2), rtol=1e-5)
+
+    rms = nm.njit(lambda x, s: np.sqrt(np.sum(x, axis=1) * s + np.float32(1)))  # a plain array, a scalar argument
+    rms(da, np.float32(0.0))
+    got, n = _launches(rms, da, np.float32(0.0))
+    assert n == 1 and np.array_equal(got.copy_to_host(), np.ones(257, np.float32))
 
     colmin = nm.njit(lambda x, y: np.min(x * y, axis=0))
     colmin(da, db)
