@@ -158,13 +158,21 @@ __device__ __forceinline__ void rows_arg_direct(const T *__restrict__ a, int64_t
 // sizeof(T)) * 4 elements round robin; scratch holds grid.x accumulators and one
 // zeroed counter; peers/rank/world: the exchange that ends the kernel
 // (world <= 1: none).
+// Resident blocks per multiprocessor the row kernels are compiled for: eight
+// for float32 (32 registers hold everything), six for the types with 64-bit
+// values or accumulators.
+#define NMB_ROWS_RESIDENT_f32 8
+#define NMB_ROWS_RESIDENT_f64 6
+#define NMB_ROWS_RESIDENT_i32 6
+#define NMB_ROWS_RESIDENT_i64 6
+
 #define NMB_DIRECT(op, TAG, ty, T)                                                                         \
-  extern "C" __global__ void __launch_bounds__(kBlock, 6)                                                   \
+  extern "C" __global__ void __launch_bounds__(kBlock, NMB_ROWS_RESIDENT_##ty)                               \
       nmb_reduce_rows_direct_##op##_##ty(const T *a, TAG::Acc<T> *out, int64_t rows, int64_t cols) {       \
     rows_direct<TAG, T, false>(a, out, rows, cols);                                                        \
   }                                                                                                        \
   NMB_REGISTER_KERNEL(nmb_reduce_rows_direct_##op##_##ty, 0);                                              \
-  extern "C" __global__ void __launch_bounds__(kBlock, 6)                                                   \
+  extern "C" __global__ void __launch_bounds__(kBlock, NMB_ROWS_RESIDENT_##ty)                               \
       nmb_reduce_rows_direct_blockrow_##op##_##ty(const T *a, TAG::Acc<T> *out, int64_t rows,              \
                                                   int64_t cols) {                                          \
     rows_direct<TAG, T, true>(a, out, rows, cols);                                                         \

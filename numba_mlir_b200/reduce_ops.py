@@ -122,8 +122,8 @@ def reduce(a, op, axis=None, out=None):
 
 _DIRECT_OPS = ("sum", "prod", "min", "max")
 # the direct kernels hand out rows and tiles round robin and are compiled for a
-# fixed number of resident blocks per multiprocessor (rows: eight; full and
-# argmin/argmax: six):
+# fixed number of resident blocks per multiprocessor (float32 rows: eight;
+# other rows, full and argmin/argmax: six):
 # one block per residency slot keeps the shares equal
 _DIRECT_ROWS_BLOCKS_PER_SM = 8
 _DIRECT_BLOCKS_PER_SM = 6
@@ -133,10 +133,11 @@ def _launch_rows(q, a, out, op, ty, rows, cols):
     if op in _DIRECT_OPS:
         # plain 128-bit loads, one warp per row (the whole block for few long
         # rows): measured faster than the TMA ring for these reductions
-        block_row = cols >= 8192 and rows < q.sm_count * _DIRECT_ROWS_BLOCKS_PER_SM
+        resident = _DIRECT_ROWS_BLOCKS_PER_SM if ty == "f32" else _DIRECT_BLOCKS_PER_SM
+        block_row = cols >= 8192 and rows < q.sm_count * resident
         k = q.builtin(f"nmb_reduce_rows_direct_{'blockrow_' if block_row else ''}{op}_{ty}")
         units = rows if block_row else (rows + 7) // 8
-        q.launch(k, (max(1, min(units, q.sm_count * _DIRECT_ROWS_BLOCKS_PER_SM)),), (256,),
+        q.launch(k, (max(1, min(units, q.sm_count * resident)),), (256,),
                  [("ptr", a.ptr), ("ptr", out.ptr), _I64(rows), _I64(cols)])
         return
     if rows >= q.sm_count * 2:
