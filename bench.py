@@ -1050,8 +1050,11 @@ def dispatch_times(queue, calls):
     numba_mlir.py:17-75): a kernel of 1, 2, 6 or 12 array arguments on 8
     int32 elements, called through a configured kernel object
     ("dispatcher") and through `kernel[...]` each time ("full_dispatcher"),
-    plus an `njit` elementwise call replayed from its plan."""
+    the same launch repeated from native code (what is left when the
+    interpreter is taken out: GPUParamDesc unpacking in the runtime library and
+    the driver's launch), plus an `njit` elementwise call replayed from its plan."""
     import numba_mlir_b200 as nm
+    from numba_mlir_b200 import runtime
     from numba_mlir_b200.kernel import DEFAULT_LOCAL_SIZE, get_global_id, kernel
 
     def make(count):
@@ -1059,6 +1062,22 @@ def dispatch_times(queue, calls):
         scope = {"get_global_id": get_global_id}
         exec(f"def func({names}):\n    i = get_global_id(0)\n    arg1[i] = i\n", scope)
         return scope["func"]
+
+    # Host time only: the calls are issued in bursts short enough for the
+    # stream's launch queue never to fill (a full queue makes the host wait for
+    # the device, about 5.5 us per tiny kernel here), with an untimed
+    # synchronize between bursts.
+    burst = 200
+
+    def host_time(call):
+        spent = 0.0
+        for _ in range(max(1, calls // burst)):
+            t0 = time.perf_counter()
+            for _ in range(burst):
+                call()
+            spent += time.perf_counter() - t0
+            queue.synchronize()
+        return spent / (max(1, calls // burst) * burst) * 1e6
 
     out = {}
     for count in (1, 2, 6, 12):
@@ -1068,14 +1087,19 @@ def dispatch_times(queue, calls):
         a = (array,) * count
         fn(*a)
         queue.synchronize()
-        for name, call in (("dispatcher", lambda: fn(*a)),
-                           ("full_dispatcher", lambda: base[8, DEFAULT_LOCAL_SIZE](*a))):
-            t0 = time.perf_counter()
-            for _ in range(calls):
-                call()
-            host = time.perf_counter() - t0
+        out[f"dispatcher_{count}_args_us"] = host_time(lambda: fn(*a))
+        out[f"full_dispatcher_{count}_args_us"] = host_time(lambda: base[8, DEFAULT_LOCAL_SIZE](*a))
+        # the same launch issued from native code without returning to the
+        # interpreter: what the runtime library and the driver cost
+        ck, _first = next(iter(fn._launchers.values()))
+        handle = ck.handle_on(queue)
+        block = ck.block_size_on(queue, handle, (8,))
+        spent = 0.0
+        for _ in range(max(1, calls // burst)):
+            spent += runtime.fastcall().launch_kernel(queue.handle, handle, (1,), block, ck.layout_code(),
+                                                      a, (8, 1, 1), burst)
             queue.synchronize()
-            out[f"{name}_{count}_args_us"] = host / calls * 1e6
+        out[f"runtime_and_driver_{count}_args_us"] = spent / max(1, calls // burst) * 1e6
 
     @nm.njit
     def add(x, y, z):
@@ -1084,11 +1108,13 @@ def dispatch_times(queue, calls):
     x, y, z = (nm.empty(8, np.float32, queue) for _ in range(3))
     add(x, y, z)
     queue.synchronize()
+    out["njit_add_3_args_us"] = host_time(lambda: add(x, y, z))
+    # with the launch queue kept full, what a long run of back-to-back tiny launches costs per launch
     t0 = time.perf_counter()
     for _ in range(calls):
         add(x, y, z)
-    out["njit_add_3_args_us"] = (time.perf_counter() - t0) / calls * 1e6
     queue.synchronize()
+    out["njit_add_3_args_sustained_us"] = (time.perf_counter() - t0) / calls * 1e6
     return out
 
 

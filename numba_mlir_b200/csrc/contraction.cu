@@ -305,6 +305,7 @@ struct ContractParams {
   float alpha, beta;
   uint32_t *status;
   int tma_out;                  // 1: out_map is valid, results leave through TMA stores
+  int vec_out;                  // plain stores: base and row pitch allow 16-byte stores
 };
 
 constexpr int kAccBuffers = 4;                  // 4 x 128 fp32 columns: all of TMEM
@@ -614,12 +615,39 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
             tma_store_box(&out_map, stage, (int)col0, (int)row0);
             nmb::bulk_commit();
           }
-        } else if (row < p.M) {
-          float *orow = p.out + row * p.ldo;
+        } else {
+          // plain stores, through the same staging buffer so that they leave
+          // coalesced: eight lanes write the 128 bytes of one row, a warp
+          // instruction four rows
+          __syncwarp(); // the previous piece's reads of the buffer are done
 #pragma unroll
-          for (int k = 0; k < 32; ++k)
-            if (col0 + k < p.N)
-              orow[col0 + k] = w[k];
+          for (int k = 0; k < 8; ++k)
+            *reinterpret_cast<float4 *>(stage + lane * kStagePitch + ((k ^ (lane & 7)) << 4)) =
+                make_float4(w[k * 4], w[k * 4 + 1], w[k * 4 + 2], w[k * 4 + 3]);
+          __syncwarp();
+          const int c = lane & 7;
+          const int64_t col = col0 + c * 4;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int rr = k * 4 + (lane >> 3);
+            const float4 v = *reinterpret_cast<const float4 *>(stage + rr * kStagePitch + ((c ^ (rr & 7)) << 4));
+            const int64_t orow_i = row0 + rr;
+            if (orow_i < p.M) {
+              float *dst = p.out + orow_i * p.ldo + col;
+              if (p.vec_out && col + 3 < p.N) {
+                __stcs(reinterpret_cast<float4 *>(dst), v);
+              } else {
+                if (col < p.N)
+                  dst[0] = v.x;
+                if (col + 1 < p.N)
+                  dst[1] = v.y;
+                if (col + 2 < p.N)
+                  dst[2] = v.z;
+                if (col + 3 < p.N)
+                  dst[3] = v.w;
+              }
+            }
+          }
         }
       };
       finish_piece(w0, 0);
@@ -676,6 +704,14 @@ int smCount(int device) {
   if (device < 64)
     cached[device] = n;
   return n;
+}
+
+// NUMBA_MLIR_B200_CONTRACT_STORES=plain makes every result leave through the
+// coalesced plain stores (the path unaligned outputs take); read on every call
+// so that one process can time both.
+bool plainStoresForced() {
+  const char *v = getenv("NUMBA_MLIR_B200_CONTRACT_STORES");
+  return v && strcmp(v, "plain") == 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -795,6 +831,8 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
   memset(&out_map, 0, sizeof(out_map));
   bool tma_out = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ldo % 4 == 0 && ldo >= N &&
                  M < (1ll << 31) && N < (1ll << 31) && ldo < (1ll << 36);
+  if (tma_out && plainStoresForced())
+    tma_out = false;
   if (tma_out) {
     EncodeTiledFn enc = encodeTiled();
     const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
@@ -833,6 +871,7 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
     p.kpad = kpad;
     p.status = status;
     p.tma_out = tma_out ? 1 : 0;
+    p.vec_out = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ldo % 4 == 0 ? 1 : 0;
     p.func = rc.func;
     if (mode == 0 && single) {
       p.mode = 0;

@@ -21,6 +21,7 @@
 #define PY_SSIZE_T_CLEAN
 #include <Python.h>
 
+#include <chrono>
 #include <cstdint>
 #include <cstring>
 
@@ -193,12 +194,16 @@ PyObject *py_init(PyObject *, PyObject *args) {
 // three characters 'A', chr(ndim), 'C' or 'S' (strided: element strides follow
 // the shape), or one scalar code letter; tail: tuple of int64 values appended
 // (the global sizes), optionally followed by a negative number -(local bytes).
+// With `repeat` > 0 the launch is issued that many times in a row and the host
+// seconds per launch are returned.
 PyObject *py_launch_kernel(PyObject *, PyObject *pyargs) {
   unsigned long long queue, kernel;
   PyObject *grid, *block, *args, *tail;
   const char *layout;
   Py_ssize_t layout_len;
-  if (!PyArg_ParseTuple(pyargs, "KKOOy#OO", &queue, &kernel, &grid, &block, &layout, &layout_len, &args, &tail))
+  Py_ssize_t repeat = 0;
+  if (!PyArg_ParseTuple(pyargs, "KKOOy#OO|n", &queue, &kernel, &grid, &block, &layout, &layout_len, &args, &tail,
+                        &repeat))
     return nullptr;
   size_t g[3], b[3];
   if (!dims3(grid, g) || !dims3(block, b))
@@ -271,6 +276,16 @@ PyObject *py_launch_kernel(PyObject *, PyObject *pyargs) {
       return nullptr;
     if (v < 0 ? !p.local(-v) : !p.i64(v))
       return nullptr;
+  }
+  if (repeat > 0) {
+    // the same launch `repeat` times without returning to the interpreter:
+    // what the runtime and the driver cost per launch, in seconds
+    const auto t0 = std::chrono::steady_clock::now();
+    for (Py_ssize_t r = 0; r < repeat; ++r)
+      if (!do_launch(reinterpret_cast<void *>(queue), reinterpret_cast<void *>(kernel), g, b, p))
+        return nullptr;
+    const std::chrono::duration<double> dt = std::chrono::steady_clock::now() - t0;
+    return PyFloat_FromDouble(dt.count() / (double)repeat);
   }
   if (!do_launch(reinterpret_cast<void *>(queue), reinterpret_cast<void *>(kernel), g, b, p))
     return nullptr;
@@ -430,7 +445,7 @@ PyObject *py_signature(PyObject *, PyObject *pyargs) {
 PyMethodDef kMethods[] = {
     {"init", py_init, METH_VARARGS, "init(launch_address, destroy_event_address)"},
     {"launch_kernel", py_launch_kernel, METH_VARARGS,
-     "launch_kernel(queue, kernel, grid, block, layout, args, tail)"},
+     "launch_kernel(queue, kernel, grid, block, layout, args, tail[, repeat])"},
     {"replay", py_replay, METH_VARARGS, "replay(queue, launches, args)"},
     {"signature", py_signature, METH_VARARGS, "signature(args, array_type)"},
     {nullptr, nullptr, 0, nullptr}};
