@@ -101,6 +101,14 @@ void gpuxKernelDestroy(void *kernel);
 void *gpuxLaunchKernel(void *queue, void *kernel, size_t gridX, size_t gridY,
                        size_t gridZ, size_t blockX, size_t blockY,
                        size_t blockZ, void *events, void *params);
+/* Addition (no reference counterpart): gpuxLaunchKernel without the event, for
+ * callers that order their work by the queue alone and would destroy the
+ * event at once (saves the event record per launch).  Returns 1, or 0 with
+ * the error set. */
+int gpuxLaunchKernelNoEvent(void *queue, void *kernel, size_t gridX,
+                            size_t gridY, size_t gridZ, size_t blockX,
+                            size_t blockY, size_t blockZ, void *events,
+                            void *params);
 /* GpuRuntime.cpp:412.  Blocks until the event is reached.  With the
  * environment variable NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS set to a positive number
  * the wait is bounded on the host: past that many milliseconds the call

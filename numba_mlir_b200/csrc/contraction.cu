@@ -618,7 +618,8 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
         } else {
           // plain stores, through the same staging buffer so that they leave
           // coalesced: eight lanes write the 128 bytes of one row, a warp
-          // instruction four rows
+          // instruction four rows (for the 16384 x 16384 distance matrix this
+          // path took 268 us where the TMA stores take 234 us on the same GPU)
           __syncwarp(); // the previous piece's reads of the buffer are done
 #pragma unroll
           for (int k = 0; k < 8; ++k)
@@ -704,14 +705,6 @@ int smCount(int device) {
   if (device < 64)
     cached[device] = n;
   return n;
-}
-
-// NUMBA_MLIR_B200_CONTRACT_STORES=plain makes every result leave through the
-// coalesced plain stores (the path unaligned outputs take); read on every call
-// so that one process can time both.
-bool plainStoresForced() {
-  const char *v = getenv("NUMBA_MLIR_B200_CONTRACT_STORES");
-  return v && strcmp(v, "plain") == 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
@@ -831,8 +824,6 @@ bool runContraction(void *queue, const Operand &A, const Operand &B, float *out,
   memset(&out_map, 0, sizeof(out_map));
   bool tma_out = (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ldo % 4 == 0 && ldo >= N &&
                  M < (1ll << 31) && N < (1ll << 31) && ldo < (1ll << 36);
-  if (tma_out && plainStoresForced())
-    tma_out = false;
   if (tma_out) {
     EncodeTiledFn enc = encodeTiled();
     const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};

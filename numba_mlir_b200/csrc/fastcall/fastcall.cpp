@@ -37,7 +37,9 @@ enum { P_NULL = 0, P_BOOL, P_INT8, P_INT16, P_INT32, P_INT64, P_FLOAT32, P_FLOAT
 typedef void *(*LaunchFn)(void *, void *, size_t, size_t, size_t, size_t, size_t, size_t, void *, void *);
 typedef void (*DestroyEventFn)(void *, void *);
 
+typedef int (*LaunchNoEventFn)(void *, void *, size_t, size_t, size_t, size_t, size_t, size_t, void *, void *);
 LaunchFn gLaunch = nullptr;
+LaunchNoEventFn gLaunchNoEvent = nullptr; // preferred when set: nothing to destroy
 DestroyEventFn gDestroyEvent = nullptr;
 PyObject *sAddr = nullptr, *sShape = nullptr, *sStrides = nullptr, *sItemsize = nullptr, *sTraceSig = nullptr,
          *sExtent = nullptr, *sAlias = nullptr;
@@ -156,6 +158,14 @@ bool dims3(PyObject *t, size_t out[3]) {
 }
 
 bool do_launch(void *queue, void *kernel, const size_t g[3], const size_t b[3], Params &p) {
+  if (gLaunchNoEvent) {
+    p.finish();
+    if (!gLaunchNoEvent(queue, kernel, g[0], g[1], g[2], b[0], b[1], b[2], nullptr, p.desc)) {
+      PyErr_SetString(PyExc_RuntimeError, "gpuxLaunchKernelNoEvent failed");
+      return false;
+    }
+    return true;
+  }
   if (!gLaunch || !gDestroyEvent) {
     PyErr_SetString(PyExc_RuntimeError, "_fastcall.init was not called");
     return false;
@@ -181,11 +191,12 @@ bool array_addr(PyObject *a, uint64_t *out) {
 }
 
 PyObject *py_init(PyObject *, PyObject *args) {
-  unsigned long long launch = 0, destroy = 0;
-  if (!PyArg_ParseTuple(args, "KK", &launch, &destroy))
+  unsigned long long launch = 0, destroy = 0, launch_no_event = 0;
+  if (!PyArg_ParseTuple(args, "KK|K", &launch, &destroy, &launch_no_event))
     return nullptr;
   gLaunch = reinterpret_cast<LaunchFn>(launch);
   gDestroyEvent = reinterpret_cast<DestroyEventFn>(destroy);
+  gLaunchNoEvent = reinterpret_cast<LaunchNoEventFn>(launch_no_event);
   Py_RETURN_NONE;
 }
 
@@ -443,7 +454,7 @@ PyObject *py_signature(PyObject *, PyObject *pyargs) {
 }
 
 PyMethodDef kMethods[] = {
-    {"init", py_init, METH_VARARGS, "init(launch_address, destroy_event_address)"},
+    {"init", py_init, METH_VARARGS, "init(launch_address, destroy_event_address[, launch_no_event_address])"},
     {"launch_kernel", py_launch_kernel, METH_VARARGS,
      "launch_kernel(queue, kernel, grid, block, layout, args, tail[, repeat])"},
     {"replay", py_replay, METH_VARARGS, "replay(queue, launches, args)"},

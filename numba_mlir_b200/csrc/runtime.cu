@@ -856,19 +856,43 @@ GPUX_EXPORT void gpuxKernelDestroy(void *kernel) {
   delete static_cast<Kernel *>(kernel);
 }
 
+namespace {
+// The launch itself; false (sticky error set) on failure.
+bool launchKernel(void *queue, void *kernel, size_t gridX, size_t gridY, size_t gridZ, size_t blockX,
+                  size_t blockY, size_t blockZ, void *events, void *params);
+} // namespace
+
 GPUX_EXPORT void *gpuxLaunchKernel(void *queue, void *kernel, size_t gridX,
                                    size_t gridY, size_t gridZ, size_t blockX,
                                    size_t blockY, size_t blockZ, void *events,
                                    void *params) {
   LOG_FUNC();
+  if (!launchKernel(queue, kernel, gridX, gridY, gridZ, blockX, blockY, blockZ, events, params))
+    return nullptr;
+  return recordEvent(toQueue(queue));
+}
+
+// gpuxLaunchKernel for callers that order their work by the queue alone and
+// would destroy the returned event at once: no event is recorded.  Returns 1,
+// or 0 with the sticky error set.
+GPUX_EXPORT int gpuxLaunchKernelNoEvent(void *queue, void *kernel, size_t gridX, size_t gridY, size_t gridZ,
+                                        size_t blockX, size_t blockY, size_t blockZ, void *events,
+                                        void *params) {
+  LOG_FUNC();
+  return launchKernel(queue, kernel, gridX, gridY, gridZ, blockX, blockY, blockZ, events, params) ? 1 : 0;
+}
+
+namespace {
+bool launchKernel(void *queue, void *kernel, size_t gridX, size_t gridY, size_t gridZ, size_t blockX,
+                  size_t blockY, size_t blockZ, void *events, void *params) {
   if (!queue || !kernel) {
     nmb::setError("gpuxLaunchKernel: null queue or kernel");
-    return nullptr;
+    return false;
   }
   Queue *q = toQueue(queue);
   Kernel *k = static_cast<Kernel *>(kernel);
   if (!setDevice(q) || !waitDeps(q, events))
-    return nullptr;
+    return false;
 
   // Argument marshalling (Queue::setKernelArg, GpuRuntime.cpp:302-351).
   static const int kTypeSize[] = {0, 1, 1, 2, 4, 8, 4, 8, 8};
@@ -882,16 +906,16 @@ GPUX_EXPORT void *gpuxLaunchKernel(void *queue, void *kernel, size_t gridX,
          ++p) {
       if (nargs >= 256) {
         nmb::setError("gpuxLaunchKernel: more than 256 parameters");
-        return nullptr;
+        return false;
       }
       if (p->type <= GPUX_PARAM_NULL || p->type > GPUX_PARAM_PTR) {
         nmb::setError("Unhandled param type: %d", (int)p->type);
-        return nullptr;
+        return false;
       }
       if (p->type == GPUX_PARAM_PTR && p->data == nullptr) {
         if (nlocal >= 64) {
           nmb::setError("gpuxLaunchKernel: more than 64 local-memory params");
-          return nullptr;
+          return false;
         }
         dynSmem = (dynSmem + 15) & ~size_t(15);
         localOffsets[nlocal] = dynSmem;
@@ -902,7 +926,7 @@ GPUX_EXPORT void *gpuxLaunchKernel(void *queue, void *kernel, size_t gridX,
       if (p->size != kTypeSize[p->type]) {
         nmb::setError("param %zu: size %d does not match type %d", nargs,
                       (int)p->size, (int)p->type);
-        return nullptr;
+        return false;
       }
       args[nargs++] = const_cast<void *>(p->data);
     }
@@ -912,18 +936,19 @@ GPUX_EXPORT void *gpuxLaunchKernel(void *queue, void *kernel, size_t gridX,
     if (gridX > 0x7fffffffull || gridY > 65535 || gridZ > 65535) {
       nmb::setError("grid (%zu,%zu,%zu) exceeds CUDA limits (2^31-1,65535,65535)",
                     gridX, gridY, gridZ);
-      return nullptr;
+      return false;
     }
     CU_TRY(DRV(LaunchKernel, k->func, (unsigned)gridX, (unsigned)gridY,
                                  (unsigned)gridZ, (unsigned)blockX,
                                  (unsigned)blockY, (unsigned)blockZ,
                                  (unsigned)dynSmem, (CUstream)q->stream, args,
                                  nullptr),
-           return nullptr);
+           return false);
     ++gLaunchCount;
   }
-  return recordEvent(q);
+  return true;
 }
+} // namespace
 
 // Host-side bound on gpuxWait: NUMBA_MLIR_GPU_WAIT_TIMEOUT_MS (read at every
 // call, 0 or unset = wait for as long as it takes, like the reference's

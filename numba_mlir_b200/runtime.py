@@ -53,6 +53,7 @@ SIGNATURES = {
     "gpuxKernelGet": (_vp, [_vp, _cp]),
     "gpuxKernelDestroy": (None, [_vp]),
     "gpuxLaunchKernel": (_vp, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp]),
+    "gpuxLaunchKernelNoEvent": (ctypes.c_int, [_vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp]),
     "gpuxWait": (None, [_vp, _vp]),
     "gpuxDestroyEvent": (None, [_vp, _vp]),
     "gpuxAlloc": (None, [_vp, _sz, _sz, _i, _vp, ctypes.POINTER(GPUAllocResult)]),
@@ -172,7 +173,8 @@ _fast = None
 def fastcall():
     """The native launch path (`_fastcall` extension: argument unboxing,
     GPUParamDesc building and the launch in C++), bound to this library's
-    gpuxLaunchKernel / gpuxDestroyEvent.  Built by numba_mlir_b200.build."""
+    gpuxLaunchKernelNoEvent (the front end orders its work by the queue and
+    needs no event per launch).  Built by numba_mlir_b200.build."""
     global _fast
     if _fast is None:
         lib = load()
@@ -183,7 +185,8 @@ def fastcall():
                 f"the native launch path is missing ({e}): build it with `python -m numba_mlir_b200.build`"
             ) from None
         _fastcall.init(ctypes.cast(lib.gpuxLaunchKernel, ctypes.c_void_p).value,
-                       ctypes.cast(lib.gpuxDestroyEvent, ctypes.c_void_p).value)
+                       ctypes.cast(lib.gpuxDestroyEvent, ctypes.c_void_p).value,
+                       ctypes.cast(lib.gpuxLaunchKernelNoEvent, ctypes.c_void_p).value)
         _fast = _fastcall
     return _fast
 

@@ -123,7 +123,11 @@ def kmeans_update(centroids, sums, counts):
 # a 64 KB accumulator, 696 us against 585 us; one, four or eight points per
 # work-item through the centroid loop at once instead of two, 639, 664 and
 # 836 us against 569 us; persistent groups that take the 512-point batches
-# round robin, four groups per multiprocessor, 609 us against 573 us.)
+# round robin, four groups per multiprocessor, 609 us against 573 us; groups
+# of 320 in which 256 work-items only label and 64 only add the batch labelled
+# one pass earlier, so that nobody waits while 64 add, 563 us against 571 us:
+# the additions are 4 % of the instructions, the kernel is bound by the issue
+# rate of the 3 x 64 x 16 subtract, multiply and add instructions per point.)
 _KM_K = 64
 _KM_D = 16
 _KM_PTS = 8
@@ -222,117 +226,6 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
     if lid < _KM_K:
         if lcnt[lid] != 0:
             atomic.add(counts, lid, lcnt[lid])
-
-
-# The same program with the two jobs on different work-items of a group of
-# 320: work-items 64..319 only label points (two each per batch of 512), work-
-# items 0..63 only add the batch labelled in the previous pass into their
-# accumulator columns, so nobody waits at the barrier while 64 work-items add.
-KMEANS_WS_LOCAL_SIZE = 320
-_KM_WS_ASSIGNERS = 256
-_KM_WS_BATCH = _KM_WS_ASSIGNERS * _KM_Q          # points labelled per pass
-_KM_WS_BATCHES = 4                                # passes per group: 2048 points
-
-
-@kernel(gpu_use_64bit_index=False)
-def _kmeans_kernel_ws(points, centroids, labels, sums, counts):
-    lid = get_local_id(0)
-    lsz = get_local_size(0)
-    base = get_group_id(0) * (_KM_WS_BATCH * _KM_WS_BATCHES)
-
-    cent = local.array((_KM_K, _KM_D), np.float32)
-    lbl = local.array(2 * _KM_WS_BATCH, np.int32)   # two batches: one being written, one being added
-    lcnt = local.array(_KM_K, np.int32)
-    acc = local.array((_KM_K, _KM_COLS), np.float64)
-    j = lid
-    while j < _KM_K * _KM_D:
-        cent[j // _KM_D, j % _KM_D] = centroids[j // _KM_D, j % _KM_D]
-        j += lsz
-    j = lid
-    while j < _KM_K * _KM_COLS:
-        acc[j // _KM_COLS, j % _KM_COLS] = 0.0
-        j += lsz
-    if lid < _KM_K:
-        lcnt[lid] = 0
-    barrier()
-
-    jcol = lid & (_KM_D - 1)
-    phase = lid >> 4
-    a = lid - _KM_COLS
-    p = private.array((_KM_Q, _KM_D), np.float32)
-    d = private.array(_KM_Q, np.float32)
-    best_d = private.array(_KM_Q, np.float32)
-    best = private.array(_KM_Q, np.int32)
-    for r in range(_KM_WS_BATCHES + 1):
-        if lid >= _KM_COLS:
-            if r < _KM_WS_BATCHES:
-                row0 = base + r * _KM_WS_BATCH
-                half = (r & 1) * _KM_WS_BATCH
-                for q in range(_KM_Q):
-                    for jj in range(_KM_D):
-                        p[q, jj] = points[row0 + q * _KM_WS_ASSIGNERS + a, jj]
-                    best[q] = 0
-                    best_d[q] = np.float32(np.inf)
-                for k in range(_KM_K):
-                    for q in range(_KM_Q):
-                        d[q] = np.float32(0.0)
-                    for jj in range(_KM_D):
-                        c = cent[k, jj]
-                        for q in range(_KM_Q):
-                            t = p[q, jj] - c
-                            d[q] += t * t
-                    for q in range(_KM_Q):
-                        if d[q] < best_d[q]:
-                            best_d[q] = d[q]
-                            best[q] = k
-                for q in range(_KM_Q):
-                    labels[row0 + q * _KM_WS_ASSIGNERS + a] = best[q]
-                    atomic.add(lcnt, best[q], 1)
-                    lbl[half + q * _KM_WS_ASSIGNERS + a] = best[q]
-        else:
-            if r > 0:
-                prev0 = base + (r - 1) * _KM_WS_BATCH
-                phalf = ((r - 1) & 1) * _KM_WS_BATCH
-                # four rows per step: labels and values are fetched before the first
-                # read-modify-write, which would otherwise order every load behind it
-                for m in range(phase, _KM_WS_BATCH, 4 * _KM_PH):
-                    l0 = lbl[phalf + m]
-                    l1 = lbl[phalf + m + _KM_PH]
-                    l2 = lbl[phalf + m + 2 * _KM_PH]
-                    l3 = lbl[phalf + m + 3 * _KM_PH]
-                    x0 = points[prev0 + m, jcol]
-                    x1 = points[prev0 + m + _KM_PH, jcol]
-                    x2 = points[prev0 + m + 2 * _KM_PH, jcol]
-                    x3 = points[prev0 + m + 3 * _KM_PH, jcol]
-                    acc[l0, lid] += x0
-                    acc[l1, lid] += x1
-                    acc[l2, lid] += x2
-                    acc[l3, lid] += x3
-        barrier()
-
-    e = lid
-    while e < _KM_K * _KM_D:
-        k = e // _KM_D
-        jj = e % _KM_D
-        v = acc[k, jj]
-        for ph in range(1, _KM_PH):
-            v += acc[k, ph * _KM_D + jj]
-        if v != 0.0:
-            atomic.add(sums, (k, jj), v)
-        e += lsz
-    if lid < _KM_K:
-        if lcnt[lid] != 0:
-            atomic.add(counts, lid, lcnt[lid])
-
-
-def kmeans_step_ws(points, centroids, labels, sums, counts):
-    n = points.shape[0]
-    if centroids.shape != (_KM_K, _KM_D):
-        raise ValueError("this kernel is written for K = 64 clusters of D = 16 dimensions")
-    chunk = _KM_WS_BATCH * _KM_WS_BATCHES
-    if n % chunk:
-        raise ValueError(f"the number of points must be a multiple of {chunk}")
-    _kmeans_kernel_ws[n // chunk * KMEANS_WS_LOCAL_SIZE, KMEANS_WS_LOCAL_SIZE](points, centroids, labels, sums, counts)
 
 
 # The same iteration in the plain form: one point per work-item, every point
