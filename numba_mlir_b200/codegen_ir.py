@@ -361,7 +361,7 @@ class Translator:
         # counters, shapes, strides and whatever is computed from them alone
         # are 32-bit C variables, and element offsets are 32-bit products.
         self.index32 = bool(index32)
-        self.narrow = index_like_vars(tir) if self.index32 else frozenset()
+        self.narrow = set(index_like_vars(tir)) if self.index32 else set()
         self.typemap = tir.typemap
         self.calltypes = tir.calltypes
         self.cnames = {}
@@ -942,61 +942,379 @@ class Translator:
             return None
         return (1 if e.fn is op.iadd else -1), e.rhs
 
+    # packed inner loops ---------------------------------------------------------------
+    # sm_100 adds, subtracts and multiplies two float32 values in one instruction
+    # (nmb::add2 / sub2 / mul2).  A loop `for q in range(C)` with a small even
+    # constant C whose iterations are independent of one another is emitted as
+    # straight-line code, two iterations at a time, with the float32 +, -, * of
+    # the two iterations packed; everything else is emitted once per iteration.
+    # Iterations are known to be independent when the body is one block of
+    # assignments and element stores, every array it stores to is a private
+    # array indexed directly by the loop variable in one fixed position (so
+    # iteration q touches only elements with that index equal to q, in loads
+    # and stores alike), and no scalar computed in one iteration is read in
+    # the next.  The rounding of every operation is what the loop's was.
+    _PACK_FNS = {operator.add: "add2", operator.iadd: "add2", operator.sub: "sub2", operator.isub: "sub2",
+                 operator.mul: "mul2", operator.imul: "mul2"}
+    _PACK_MAX_TRIP = 16
+
+    def _array_origin(self, defs, name):
+        """('private' | 'local' | 'arg', defining variable) of an array variable, or None."""
+        from . import kernel_impl as K
+
+        ir = self.ir
+        for _ in range(64):
+            d = defs.get(name)
+            if d is None or len(d) != 1:
+                return None
+            d = d[0]
+            if isinstance(d, ir.Var):
+                name = d.name
+                continue
+            if isinstance(d, ir.Arg):
+                return ("arg", name)
+            if isinstance(d, ir.Expr) and d.op == "call":
+                fn = self.callee(d.func)
+                if fn is K.private_array:
+                    return ("private", name)
+                if fn is K.local_array:
+                    return ("local", name)
+            return None
+        return None
+
+    def _pure_call(self, expr):
+        types = self.types
+        try:
+            fn = self.callee(expr.func)
+        except Exception:
+            return False
+        if fn in (int, float, bool, abs, min, max) or isinstance(fn, np.ufunc):
+            return True
+        if isinstance(self.vtype(expr.func.name), types.NumberClass):
+            return True
+        if isinstance(fn, type) and issubclass(fn, np.generic):
+            return True
+        return getattr(fn, "__module__", None) == "math"
+
+    def packable_loops(self):
+        """{header label: (body label, exit label, trip count, induction variable
+        name)} of the loops that are emitted two iterations at a time."""
+        from numba.core.analysis import compute_cfg_from_blocks
+
+        ir, types = self.ir, self.types
+        blocks = self.tir.func_ir.blocks
+        defs = _single_defs(blocks, ir)
+        found = {}
+        try:
+            loops = compute_cfg_from_blocks(blocks).loops()
+        except Exception:
+            return found
+        for loop in loops.values():
+            if len(loop.body) != 2 or len(loop.entries) != 1 or len(loop.exits) != 1:
+                continue
+            head = loop.header
+            (body_label,) = [b for b in loop.body if b != head]
+            if head in self.block_prologue or head in self.block_epilogue or \
+                    body_label in self.block_prologue or body_label in self.block_epilogue:
+                continue
+            hb, bb = blocks[head].body, blocks[body_label].body
+            # header: iternext / pair_first / pair_second / phi copy / branch
+            if len(hb) != 5 or not isinstance(hb[4], ir.Branch) or hb[4].truebr != body_label:
+                continue
+            ops = [getattr(i.value, "op", None) if isinstance(i, ir.Assign) else None for i in hb[:3]]
+            if ops != ["iternext", "pair_first", "pair_second"] or not isinstance(hb[3], ir.Assign) \
+                    or not isinstance(hb[3].value, ir.Var) or hb[3].value.name != hb[1].target.name \
+                    or hb[4].cond.name != hb[2].target.name:
+                continue
+            phi = hb[3].target.name
+            if not isinstance(bb[-1], ir.Jump) or bb[-1].target != head:
+                continue
+            # trip count: range(C) or range(0, C) with a constant C
+            it = _resolve(defs, ir, hb[0].value.value.name)
+            if not (isinstance(it, ir.Expr) and it.op == "getiter"):
+                continue
+            rng = _resolve(defs, ir, it.value.name)
+            if not (isinstance(rng, ir.Expr) and rng.op == "call" and self.callee(rng.func) is range
+                    and 1 <= len(rng.args) <= 2 and not rng.kws):
+                continue
+            if it.value.name in self.par_ranges:
+                continue
+            try:
+                bounds = [self.static_value(a) for a in rng.args]
+            except UnsupportedError:
+                continue
+            if not all(isinstance(b, (int, np.integer)) for b in bounds) or (len(bounds) == 2 and bounds[0] != 0):
+                continue
+            trip = int(bounds[-1])
+            if trip < 2 or trip % 2 or trip > self._PACK_MAX_TRIP:
+                continue
+            if self._independent_iterations(bb[:-1], defs, phi, blocks, body_label, head):
+                found[head] = (body_label, hb[4].falsebr, trip, phi)
+        return found
+
+    def _independent_iterations(self, stmts, defs, phi, blocks, body_label, head):
+        ir, types = self.ir, self.types
+        f32 = types.float32
+        defined = set()
+        loop_var = {phi}            # names that hold the loop variable itself
+        index_pos = {}              # tuple variable -> positions holding the loop variable
+        stored, loaded = [], []     # (array variable, index variable)
+        packed = 0
+        for inst in stmts:
+            if isinstance(inst, ir.Del):
+                continue
+            if isinstance(inst, (ir.SetItem, ir.StaticSetItem)):
+                idx = inst.index_var if isinstance(inst, ir.StaticSetItem) else inst.index
+                if idx is None:
+                    return False
+                used = [inst.target, idx, inst.value]
+                stored.append((inst.target.name, idx.name))
+            elif isinstance(inst, ir.Assign):
+                v = inst.value
+                used = []
+                if isinstance(v, ir.Var):
+                    used = [v]
+                    if v.name in loop_var:
+                        loop_var.add(inst.target.name)
+                elif isinstance(v, (ir.Const, ir.Global, ir.FreeVar)):
+                    pass
+                elif isinstance(v, ir.Expr):
+                    used = v.list_vars()
+                    if v.op in ("binop", "inplace_binop"):
+                        sig = self.calltypes[v]
+                        if v.fn in self._PACK_FNS and all(types.unliteral(t) == f32 for t in sig.args) \
+                                and types.unliteral(sig.return_type) == f32:
+                            packed += 1
+                    elif v.op in ("getitem", "static_getitem"):
+                        idx = v.index_var if v.op == "static_getitem" else v.index
+                        vt = types.unliteral(self.vtype(v.value.name))
+                        if isinstance(vt, types.Array):
+                            if idx is None or not _is_scalar(types.unliteral(self.vtype(inst.target.name))):
+                                return False
+                            loaded.append((v.value.name, idx.name))
+                    elif v.op == "build_tuple":
+                        index_pos[inst.target.name] = [k for k, item in enumerate(v.items) if item.name in loop_var]
+                    elif v.op == "call":
+                        if not self._pure_call(v):
+                            return False
+                    elif v.op not in ("unary", "cast", "getattr"):
+                        return False
+                else:
+                    return False
+                # a value of this iteration only: defined before it is read, once
+                if inst.target.name in defined:
+                    return False
+            else:
+                return False
+            for u in used:
+                if u.name not in defined and u.name != phi:
+                    d = defs.get(u.name)
+                    if d is not None and any(isinstance(i, ir.Assign) and i.target.name == u.name for i in stmts):
+                        return False  # carried from the previous iteration
+            if isinstance(inst, ir.Assign):
+                defined.add(inst.target.name)
+        if not packed:
+            return False
+
+        def position(index_name):
+            """Position of the loop variable in an index, or None."""
+            if index_name in loop_var:
+                return 0
+            pos = index_pos.get(index_name)
+            return pos[0] if pos and len(pos) == 1 else None
+
+        roots = {}
+        for arr, idx in stored:
+            origin = self._array_origin(defs, arr)
+            if origin is None or origin[0] != "private":
+                return False
+            pos = position(idx)
+            if pos is None or roots.setdefault(origin[1], pos) != pos:
+                return False
+        for arr, idx in loaded:
+            origin = self._array_origin(defs, arr)
+            if origin is None:
+                return False
+            if origin[1] in roots and position(idx) != roots[origin[1]]:
+                return False
+        # values leaving the loop must be scalars (they are copied out of the last iteration)
+        for label, blk in blocks.items():
+            if label in (body_label, head):
+                continue
+            for inst in blk.body:
+                for u in inst.list_vars():
+                    if u.name in defined and not _is_scalar(types.unliteral(self.vtype(u.name))):
+                        if not any(isinstance(i, ir.Assign) and i.target.name == u.name for i in blk.body):
+                            return False
+        return True
+
+    def _renamed(self, inst, ren):
+        """Copy of a statement with the variables of `ren` renamed (types and call
+        signatures registered for the copies)."""
+        ir = self.ir
+
+        def v(var):
+            n = ren.get(var.name)
+            return ir.Var(var.scope, n, var.loc) if n is not None else var
+
+        def value(val):
+            if isinstance(val, ir.Var):
+                return v(val)
+            if isinstance(val, ir.Expr):
+                kws = {}
+                for k, x in val._kws.items():
+                    if isinstance(x, ir.Var):
+                        kws[k] = v(x)
+                    elif isinstance(x, (list, tuple)) and x and all(isinstance(e, ir.Var) for e in x):
+                        kws[k] = type(x)(v(e) for e in x)
+                    else:
+                        kws[k] = x
+                new = ir.Expr(val.op, val.loc, **kws)
+                if val in self.calltypes:
+                    self.calltypes[new] = self.calltypes[val]
+                return new
+            return val
+
+        if isinstance(inst, ir.Assign):
+            return ir.Assign(value(inst.value), v(inst.target), inst.loc)
+        if isinstance(inst, ir.StaticSetItem):
+            return ir.StaticSetItem(v(inst.target), inst.index,
+                                    v(inst.index_var) if inst.index_var is not None else None,
+                                    v(inst.value), inst.loc)
+        return ir.SetItem(v(inst.target), v(inst.index), v(inst.value), inst.loc)
+
+    def emit_packed_loop(self, head, info, out):
+        ir, types = self.ir, self.types
+        body_label, exit_label, trip, phi = info
+        blocks = self.tir.func_ir.blocks
+        stmts = [i for i in blocks[body_label].body[:-1] if not isinstance(i, ir.Del)]
+        local = [i.target.name for i in stmts if isinstance(i, ir.Assign)]
+        copies = []
+        for c in range(trip):
+            ren = {}
+            for name in local + [phi]:
+                new = f"{name}.u{head}.{c}"
+                ren[name] = new
+                self.typemap[new] = self.typemap[name]
+                if name in self.narrow:
+                    self.narrow.add(new)
+            self.consts[ren[phi]] = c
+            copies.append((ren, [self._renamed(i, ren) for i in stmts]))
+        f32 = types.float32
+        # A packed multiply must not feed an addition: the assembler merges
+        # mul.f32x2 with a dependent add/sub.f32x2 into a fused multiply-add even
+        # when both carry .rn.  A product is packed only when every reader is a
+        # multiply of this loop body; otherwise it stays a scalar multiply, whose
+        # .rn is honoured.
+        is_mul = lambda e: isinstance(e, ir.Expr) and e.op in ("binop", "inplace_binop") and \
+            self._PACK_FNS.get(e.fn) == "mul2"  # noqa: E731
+        keep_scalar = set()
+        for inst in stmts:
+            reader_is_mul = isinstance(inst, ir.Assign) and is_mul(inst.value)
+            if not reader_is_mul:
+                keep_scalar.update(u.name for u in inst.list_vars())
+        for label, blk in blocks.items():
+            if label != body_label:
+                for inst in blk.body:
+                    keep_scalar.update(u.name for u in inst.list_vars())
+        for c0 in range(0, trip, 2):
+            (ren0, s0), (ren1, s1) = copies[c0], copies[c0 + 1]
+            for k, (a, b) in enumerate(zip(s0, s1)):
+                v = a.value if isinstance(a, ir.Assign) else None
+                if isinstance(v, ir.Expr) and v.op in ("binop", "inplace_binop") and v.fn in self._PACK_FNS \
+                        and not (is_mul(v) and stmts[k].target.name in keep_scalar):
+                    sig = self.calltypes[v]
+                    if all(types.unliteral(t) == f32 for t in sig.args) and types.unliteral(sig.return_type) == f32:
+                        self.declare(a.target.name)
+                        self.declare(b.target.name)
+                        w = b.value
+                        out.append(f"nmb::{self._PACK_FNS[v.fn]}({self.scalar(v.lhs, f32)}, {self.scalar(w.lhs, f32)}, "
+                                   f"{self.scalar(v.rhs, f32)}, {self.scalar(w.rhs, f32)}, "
+                                   f"{self.cname(a.target.name)}, {self.cname(b.target.name)});")
+                        continue
+                for inst, ren in ((a, ren0), (b, ren1)):
+                    self.statement(inst, out, blocks)
+                    # the loop variable of this copy is a constant: later index
+                    # expressions use the literal
+                    if isinstance(inst, ir.Assign) and isinstance(inst.value, ir.Var) \
+                            and inst.value.name in self.consts \
+                            and _is_scalar(types.unliteral(self.vtype(inst.target.name))) \
+                            and inst.value.name == ren[phi]:
+                        self.consts[inst.target.name] = self.consts[inst.value.name]
+        # values of the last iteration under the loop's own names, for code after the loop
+        last = copies[-1][0]
+        for name in local:
+            if _is_scalar(types.unliteral(self.vtype(name))):
+                self.declare(name)
+                src = _NameRef(last[name])
+                out.append(f"{self.cname(name)} = {self.scalar(src, self.vtype(name))};")
+        out.append(f"goto L{exit_label};")
+
     # statements -------------------------------------------------------------------------
+    def statement(self, inst, out, blocks):
+        """C text of one IR statement, appended to `out`."""
+        ir, types = self.ir, self.types
+        if isinstance(inst, ir.Assign):
+            if isinstance(inst.value, ir.Const) and inst.value.value is ir.UNDEFINED:
+                return
+            self.assign(inst.target, inst.value, out)
+        elif isinstance(inst, (ir.SetItem, ir.StaticSetItem)):
+            arr = inst.target
+            self.declare(arr.name)
+            self.written_params.add(self.root_of(arr.name))
+            rep = self.arrays[arr.name]
+            if isinstance(inst, ir.StaticSetItem) and inst.index_var is None:
+                idx = inst.index if isinstance(inst.index, tuple) else (inst.index,)
+                idx_exprs = [f"{int(i)}ll" for i in idx]
+            else:
+                idx_exprs = self.index_list(inst.index_var if isinstance(inst, ir.StaticSetItem)
+                                            else inst.index)
+            ref = self.element_ref(arr, idx_exprs)
+            upd = self.parallel_update(inst, blocks) if self.mode == "parfor" else None
+            if upd is not None:
+                # `x[idx] += v` inside a parallel loop is an atomic update, as the
+                # reference makes it (mlir/tests/test_numpy.py:1039-1057)
+                sign, val = upd
+                v = self.scalar(val, rep.dtype)
+                out.append(f"nmb::atomic_add(&{ref}, ({rep.ctype})({'-' if sign < 0 else ''}({v})));")
+            else:
+                out.append(f"{ref} = {self.scalar(inst.value, rep.dtype)};")
+        elif isinstance(inst, ir.Del):
+            return
+        elif isinstance(inst, ir.Jump):
+            out.append(f"goto L{inst.target};")
+        elif isinstance(inst, ir.Branch):
+            out.append(f"if ({self.scalar(inst.cond, types.boolean)}) goto L{inst.truebr}; "
+                       f"else goto L{inst.falsebr};")
+        elif isinstance(inst, ir.Return):
+            if self.mode == "parfor" and self.return_store is not None:
+                out.append(f"{self.return_store} = {self.scalar(inst.value, self.tir.return_type)}; return;")
+            elif self.mode in ("kernel", "parfor"):
+                out.append("return;")
+            else:
+                out.append(f"return {self.scalar(inst.value, self.tir.return_type)};")
+        elif isinstance(inst, (ir.Raise, ir.StaticRaise)):
+            out.append("return;" if self.mode in ("kernel", "parfor") else "return 0;")
+        else:
+            raise UnsupportedError(f"statement {type(inst).__name__} in device code")
+
     def translate(self, param_names):
         ir, types = self.ir, self.types
         self.param_names = param_names
         blocks = self.tir.func_ir.blocks
         order = sorted(blocks)
         body = []
+        packed = self.packable_loops() if self.mode in ("kernel", "parfor") else {}
         for label in order:
             out = [f"L{label}: ;"] + list(self.block_prologue.get(label, ()))
+            if label in packed:
+                self.emit_packed_loop(label, packed[label], out)
+                body.append("\n    ".join(out))
+                continue
             for inst in blocks[label].body:
                 if isinstance(inst, (ir.Jump, ir.Branch, ir.Return)) and label in self.block_epilogue:
                     out.extend(self.block_epilogue[label])
-                if isinstance(inst, ir.Assign):
-                    if isinstance(inst.value, ir.Const) and inst.value.value is ir.UNDEFINED:
-                        continue
-                    self.assign(inst.target, inst.value, out)
-                elif isinstance(inst, (ir.SetItem, ir.StaticSetItem)):
-                    arr = inst.target
-                    self.declare(arr.name)
-                    self.written_params.add(self.root_of(arr.name))
-                    rep = self.arrays[arr.name]
-                    if isinstance(inst, ir.StaticSetItem) and inst.index_var is None:
-                        idx = inst.index if isinstance(inst.index, tuple) else (inst.index,)
-                        idx_exprs = [f"{int(i)}ll" for i in idx]
-                    else:
-                        idx_exprs = self.index_list(inst.index_var if isinstance(inst, ir.StaticSetItem)
-                                                    else inst.index)
-                    ref = self.element_ref(arr, idx_exprs)
-                    upd = self.parallel_update(inst, blocks) if self.mode == "parfor" else None
-                    if upd is not None:
-                        # `x[idx] += v` inside a parallel loop is an atomic update, as the
-                        # reference makes it (mlir/tests/test_numpy.py:1039-1057)
-                        sign, val = upd
-                        v = self.scalar(val, rep.dtype)
-                        out.append(f"nmb::atomic_add(&{ref}, ({rep.ctype})({'-' if sign < 0 else ''}({v})));")
-                    else:
-                        out.append(f"{ref} = {self.scalar(inst.value, rep.dtype)};")
-                elif isinstance(inst, ir.Del):
-                    continue
-                elif isinstance(inst, ir.Jump):
-                    out.append(f"goto L{inst.target};")
-                elif isinstance(inst, ir.Branch):
-                    out.append(f"if ({self.scalar(inst.cond, types.boolean)}) goto L{inst.truebr}; "
-                               f"else goto L{inst.falsebr};")
-                elif isinstance(inst, ir.Return):
-                    if self.mode == "parfor" and self.return_store is not None:
-                        out.append(f"{self.return_store} = {self.scalar(inst.value, self.tir.return_type)}; return;")
-                    elif self.mode in ("kernel", "parfor"):
-                        out.append("return;")
-                    else:
-                        out.append(f"return {self.scalar(inst.value, self.tir.return_type)};")
-                elif isinstance(inst, (ir.Raise, ir.StaticRaise)):
-                    out.append("return;" if self.mode in ("kernel", "parfor") else "return 0;")
-                else:
-                    raise UnsupportedError(f"statement {type(inst).__name__} in device code")
+                self.statement(inst, out, blocks)
             body.append("\n    ".join(out))
         return body
 

@@ -23,6 +23,7 @@ context in which the reference caches queue/module/kernel handles
 """
 
 import itertools
+import re
 import struct
 import threading
 import weakref
@@ -1260,6 +1261,46 @@ def _leaf_access(leaf_arr, out_shape):
     return "strided", tuple(strides)
 
 
+# float32 operations that exist as one instruction on two values (add/sub/mul.rn.f32x2)
+# (helper in nmb_device.cuh, number of operands it takes per element); `log` is
+# this library's own polynomial, evaluated for two elements with packed FMAs
+# Operations that may read a packed product: none of them adds to its operand
+# before rounding (multiplies; the IEEE division and square root, which use their
+# operands as multiplicands and as the addend of a residual; log, which starts
+# with integer operations; exp, which starts with a multiply; comparisons).
+_PRODUCT_READERS = frozenset(["multiply", "square", "true_divide", "sqrt", "log", "exp", "less", "less_equal",
+                              "greater", "greater_equal", "equal", "not_equal", "isnan"])
+_PACKED_OPS = {"add": ("add2", 2), "subtract": ("sub2", 2), "multiply": ("mul2", 2), "square": ("mul2", 2),
+               "log": ("log_pair", 1)}
+
+
+def _second_lane(text):
+    """The chain text of element l rewritten for element l + 1."""
+    return re.sub(r"\bt(\d+)\b", r"t\1_b", text).replace(".v[l]", ".v[l + 1]")
+
+
+def _paired_lines(em, lines, out_assign, fuse_ok=False):
+    """The chain for two adjacent elements at once: every line twice, except the
+    float32 additions, subtractions and multiplications, which become one
+    packed instruction for both elements (IEEE results, half the issue slots)."""
+    out = []
+    for i, line in enumerate(lines):
+        hit = em.packable.get(i)
+        if hit is not None and hit[0] == "mul2" and f"t{i}" in em.scalar_only and not fuse_ok:
+            hit = None
+        if hit is None:
+            out.append(line)
+            out.append(_second_lane(line))
+        else:
+            fn, operands = hit
+            both = ", ".join(f"{x}, {_second_lane(x)}" for x in operands)
+            out.append(f"float t{i}, t{i}_b; nmb::{fn}({both}, t{i}, t{i}_b);")
+    for line in out_assign:
+        out.append(line)
+        out.append(_second_lane(line))
+    return out
+
+
 class _Emitter:
     def __init__(self, trace, out_shape):
         self.trace = trace
@@ -1272,6 +1313,8 @@ class _Emitter:
         self.scalar_index = {}
         self.funcs = {}
         self.sig = []
+        self.packable = {}       # line index -> (packed helper, operand expressions)
+        self.scalar_only = set() # names of values read by something that may add to them
 
     def leaf(self, node):
         key = node.slot
@@ -1300,6 +1343,14 @@ class _Emitter:
             self.sig.append(("arg", self.scalar_index[node.value], node.dtype.name))
         else:
             ins = [self.emit(i) for i in node.inputs]
+            # A packed multiply must not feed an addition: the assembler merges
+            # mul.f32x2 with a dependent add/sub.f32x2 into one fused multiply-add
+            # even when both carry .rn, which would change the rounding.  So a
+            # product stays a scalar multiply (whose .rn is honoured) unless every
+            # reader is known not to add to it.
+            if not (node.kind == "op" and node.op in _PRODUCT_READERS):
+                for e in ins:
+                    self.scalar_only.add(e)
             if node.kind == "cast":
                 rhs = f"static_cast<{ctype(node.dtype)}>({ins[0]})"
                 if node.inputs[0].dtype.kind == "f" and node.dtype.kind == "b":
@@ -1312,6 +1363,11 @@ class _Emitter:
             else:
                 loop_dt = node.inputs[0].dtype
                 rhs = UFUNCS[node.op][1](loop_dt, *ins)
+                if (node.op in _PACKED_OPS and node.dtype == np.float32
+                        and all(i.dtype == np.float32 for i in node.inputs)):
+                    # two elements' worth of this operation fit f32x2 instructions
+                    fn, arity = _PACKED_OPS[node.op]
+                    self.packable[len(self.lines)] = (fn, (ins * 2)[:arity])
             expr = f"t{len(self.lines)}"
             self.lines.append(f"const {ctype(node.dtype)} {expr} = {rhs};")
             self.sig.append((node.kind, node.op if node.kind == "op" else
@@ -1624,6 +1680,25 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
   Chain chain{{{', '.join(ctor)}}};
   {call}
 }}"""
+    scalar_loop = f"""#pragma unroll
+    for (int l = 0; l < V; ++l) {{
+      {nl.join(list(chain_lines) + out_assign)}
+    }}"""
+    # under fastmath a*b+c may contract, so every product is packed too and the
+    # assembler's merging of packed multiply and add is welcome
+    n_packed = sum(1 for i, hit in em.packable.items()
+                   if i < len(chain_lines) and (fastmath or not (hit[0] == "mul2" and f"t{i}" in em.scalar_only)))
+    if n_packed:
+        compute_body = f"""    if constexpr (V % 2 == 0) {{
+#pragma unroll
+    for (int l = 0; l < V; l += 2) {{
+      {nl.join(_paired_lines(em, chain_lines, out_assign, fuse_ok=fastmath))}
+    }}
+    }} else {{
+{scalar_loop}
+    }}"""
+    else:
+        compute_body = scalar_loop
     # fastmath: a*b+c may contract and division/sqrt take the approximate
     # instructions (<= 2 ulp), as the reference's fast SPIR-V mode allows
     head = "//NMB200:OPTIONS\n#define NMB_FASTMATH 1" if fastmath else "//NMB200:OPTIONS --fmad=false"
@@ -1639,11 +1714,7 @@ struct Chain {{
     {(nl[:-2]).join(loads)}
   }}
   template <int V> __device__ __forceinline__ void compute(const In<V>& r, Out<V>& o) const {{
-#pragma unroll
-    for (int l = 0; l < V; ++l) {{
-      {nl.join(chain_lines)}
-      {nl.join(out_assign)}
-    }}
+{compute_body}
   }}
 {post_method}
   template <int V> __device__ __forceinline__ void store(int64_t i, const Out<V>& o) const {{

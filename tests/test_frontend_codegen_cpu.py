@@ -83,6 +83,41 @@ def test_fastmath_selects_the_approximate_division_and_sqrt(runtime_lib):
         assert len(runtime.compile_to_cubin(step[1])) > 0
 
 
+def test_float32_arithmetic_is_emitted_for_two_elements_at_once(runtime_lib):
+    """float32 +, - and * of a fused chain are emitted once per two adjacent
+    elements (add/sub/mul.rn.f32x2); everything else and other element types
+    keep the scalar form, and so does a multiply whose product something may
+    add to (the assembler would merge the packed pair into a fused
+    multiply-add) unless fastmath allows that contraction."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import lazy, runtime
+
+    def f(a, b):
+        return np.sqrt((a - b) * (a + b)) + b
+
+    def g(a, b):
+        return a * b - a  # a product that feeds a subtraction stays a scalar multiply
+
+    for dt, fast, packed in ((np.float32, False, True), (np.float64, False, False), (np.float32, True, True)):
+        args = [lazy.fake_array((4096,), dt), lazy.fake_array((4096,), dt)]
+        trace, _plan = nm.njit(f, fastmath=fast).trace_dry(*args)
+        (step,) = [s for s in trace.steps if s[0] == "launch"]
+        src = bytes(step[1]).decode()
+        assert ("nmb::mul2(" in src and "nmb::sub2(" in src and "nmb::add2(" in src) == packed
+        if packed:
+            assert src.count("nmb::f_sqrt(") == 3  # both elements of the pair, and the one-element form
+            assert "if constexpr (V % 2 == 0)" in src
+        assert len(runtime.compile_to_cubin(step[1])) > 0
+    args = [lazy.fake_array((4096,), np.float32), lazy.fake_array((4096,), np.float32)]
+    trace, _plan = nm.njit(g).trace_dry(*args)
+    (step,) = [s for s in trace.steps if s[0] == "launch"]
+    src = bytes(step[1]).decode()
+    assert "nmb::sub2(" in src and "nmb::mul2(" not in src
+    trace, _plan = nm.njit(g, fastmath=True).trace_dry(*args)
+    (step,) = [s for s in trace.steps if s[0] == "launch"]
+    assert "nmb::mul2(" in bytes(step[1]).decode()
+
+
 def test_large_local_arrays_move_to_the_local_memory_parameter(runtime_lib):
     """Local arrays stay static shared memory while the kernel's static total
     fits 48 KB; above that the kernel takes an offset parameter and the launch carries a local-memory
@@ -222,3 +257,61 @@ def test_32bit_index_mode_narrows_index_values_only(runtime_lib):
     assert "(int32_t)(" in narrow and "int32_t v1_table_s0" in narrow.replace("  ", " ")
     for src in (wide, narrow):
         assert len(runtime.compile_to_cubin(src)) > 0
+
+
+# ------------------------------------------------------- packed inner loops ---
+def test_independent_constant_loops_are_emitted_two_iterations_at_a_time(runtime_lib):
+    """A `for q in range(2)` loop over private arrays whose iterations do not
+    depend on one another is emitted as straight-line code with the float32
+    subtraction and addition of the two iterations packed (nmb::sub2 / add2);
+    the multiply that feeds the addition stays scalar, because the assembler
+    would merge a packed multiply into a dependent packed add.  Loops that
+    carry a value from one iteration to the next keep their loop form."""
+    from numba_mlir_b200 import codegen_ir, lazy, runtime
+    from numba_mlir_b200.kernel import get_global_id, private
+
+    def independent(x, c, out):
+        i = get_global_id(0)
+        p = private.array((2, 4), np.float32)
+        d = private.array(2, np.float32)
+        for q in range(2):
+            for j in range(4):
+                p[q, j] = x[2 * i + q, j]
+            d[q] = np.float32(0.0)
+        for j in range(4):
+            cj = c[j]
+            for q in range(2):
+                t = p[q, j] - cj
+                d[q] += t * t
+        out[2 * i] = d[0]
+        out[2 * i + 1] = d[1]
+
+    def carried(x, out):
+        i = get_global_id(0)
+        d = private.array(4, np.float32)
+        s = np.float32(0.0)
+        for q in range(4):
+            s = s + x[4 * i + q]      # a running value: iteration q reads iteration q - 1
+            d[q] = s * np.float32(2.0)
+        out[i] = d[3]
+
+    def shifted(x, out):
+        i = get_global_id(0)
+        d = private.array(5, np.float32)
+        d[0] = x[i]
+        for q in range(4):
+            d[q + 1] = d[q] + np.float32(1.0)   # not indexed by the loop variable itself
+        out[i] = d[4]
+
+    x2 = lazy.fake_array((64, 4), np.float32)
+    c = lazy.fake_array((4,), np.float32)
+    x1 = lazy.fake_array((64,), np.float32)
+    out = lazy.fake_array((64,), np.float32)
+    ck = codegen_ir.compile_kernel(independent, [x2, c, out], 1)
+    assert ck.source.count("nmb::sub2(") == 1 and ck.source.count("nmb::add2(") == 1
+    assert "nmb::mul2(" not in ck.source
+    assert len(runtime.compile_to_cubin(ck.source.encode())) > 0
+    for fn, args in ((carried, [x1, out]), (shifted, [x1, out])):
+        ck = codegen_ir.compile_kernel(fn, args, 1)
+        assert "nmb::add2(" not in ck.source and "nmb::mul2(" not in ck.source
+        assert len(runtime.compile_to_cubin(ck.source.encode())) > 0

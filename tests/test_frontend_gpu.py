@@ -304,6 +304,40 @@ def test_erf_float32_within_2ulp_of_the_true_value(queue):
     assert np.isnan(nan[0])
 
 
+@pytest.mark.parametrize("n", [1, 7, 1024, 4096 + 3, 1 << 20])
+def test_paired_float32_arithmetic_is_bit_identical_to_numpy(queue, n):
+    """The chain's float32 +, -, * run as f32x2 instructions over pairs of
+    elements (and element by element at a ragged end): every result is the
+    IEEE-rounded one NumPy computes, cancellation included."""
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(n)
+    a = rng.standard_normal(n).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32)
+    c = (a * np.float32(1.0001)).astype(np.float32)
+    d = (b * np.float32(0.9999)).astype(np.float32)
+    a[:1] = np.float32(1e-42)  # a subnormal operand and result
+    s = np.float32(3.0)
+
+    @nm.njit
+    def f(a, b, c, d, s):
+        return a * b - c * d, (a + b) * (c - d) + s * a, np.sqrt((a - c) * (a - c)) * (b + d)
+
+    r0, r1, r2 = f(_dev(a), _dev(b), _dev(c), _dev(d), s)
+    # products that feed a subtraction: every element differs if one is fused into it
+    np.testing.assert_array_equal(r0.copy_to_host(), a * b - c * d)
+    np.testing.assert_array_equal(r1.copy_to_host(), (a + b) * (c - d) + s * a)
+    np.testing.assert_array_equal(r2.copy_to_host(), np.sqrt((a - c) * (a - c)) * (b + d))
+    # a*b - float32(a*b) is exactly zero when the product rounds on its own
+    ab = a * b
+
+    @nm.njit
+    def residual(a, b, ab):
+        return a * b - ab
+
+    assert not residual(_dev(a), _dev(b), _dev(ab)).copy_to_host().any()
+
+
 def test_where_compare_cast_and_strided_operands(queue):
     import numba_mlir_b200 as nm
 

@@ -260,6 +260,59 @@ def test_private_array_and_kernel_func(queue):
     assert np.array_equal(out.copy_to_host(), want.astype(np.float32))
 
 
+def test_packed_inner_loops_round_like_the_scalar_loop(queue):
+    """Independent constant-trip loops over private arrays run two iterations
+    at a time with packed float32 add/sub (numba_mlir_b200/codegen_ir.py).
+    Every operation must still round on its own: x*y - float32(x*y) is
+    exactly zero unless a product were fused into the subtraction, and the
+    squared-distance accumulation equals NumPy's operation by operation."""
+    from numba_mlir_b200.kernel import get_global_id, kernel, private
+
+    def residual(x, y, z, out):
+        i = get_global_id(0)
+        v = private.array(4, np.float32)
+        for q in range(4):
+            t = x[4 * i + q] * y[4 * i + q]
+            v[q] = t - z[4 * i + q]
+        for q in range(4):
+            out[4 * i + q] = v[q]
+
+    def sqdist(x, c, out):
+        i = get_global_id(0)
+        p = private.array((2, 8), np.float32)
+        d = private.array(2, np.float32)
+        for q in range(2):
+            for j in range(8):
+                p[q, j] = x[2 * i + q, j]
+            d[q] = np.float32(0.0)
+        for j in range(8):
+            cj = c[j]
+            for q in range(2):
+                t = p[q, j] - cj
+                d[q] += t * t
+        for q in range(2):
+            out[2 * i + q] = d[q]
+
+    rng = np.random.default_rng(11)
+    n = 1 << 16
+    x = rng.standard_normal(n).astype(np.float32)
+    y = rng.standard_normal(n).astype(np.float32)
+    z = x * y
+    out = _dev(np.ones(n, np.float32))
+    kernel(residual)[n // 4](_dev(x), _dev(y), _dev(z), out)
+    assert not out.copy_to_host().any()
+
+    pts = rng.standard_normal((n, 8)).astype(np.float32)
+    c = rng.standard_normal(8).astype(np.float32)
+    out = _dev(np.zeros(n, np.float32))
+    kernel(sqdist)[n // 2](_dev(pts), _dev(c), out)
+    want = np.zeros(n, np.float32)
+    for j in range(8):
+        t = pts[:, j] - c[j]
+        want = want + t * t
+    assert np.array_equal(out.copy_to_host(), want)
+
+
 def test_kwargs_and_mixed_devices_are_rejected(queue):
     from numba_mlir_b200.kernel import get_global_id, kernel
 
