@@ -1360,7 +1360,36 @@ def compile_device_function(py_func, dtypes):
     sig = ", ".join(f"{c_scalar_type(t)} a{i}" for i, t in enumerate(argtypes))
     src = (f"__device__ __forceinline__ {rt} {name}({sig}) {{\n    " + "\n    ".join(tr.decls)
            + "\n    " + "\n    ".join(body) + "\n}\n")
-    return lazy.DeviceFunc(name, src, dtypes, as_dtype(tir.return_type))
+    return lazy.DeviceFunc(name, src, dtypes, as_dtype(tir.return_type), pair=_pair_routine(tr, tir))
+
+
+# float32 functions nmb_device.cuh also has for two values at once (f32x2 instructions)
+_PAIR_ROUTINES = {math.erf: "erf_pair", math.log: "log_pair"}
+
+
+def _pair_routine(tr, tir):
+    """Name of the two-values-at-once routine when the scalar function is
+    nothing but `return f(x)` in float32 for an f of _PAIR_ROUTINES."""
+    ir, types = tr.ir, tr.types
+    if len(tir.args) != 1 or types.unliteral(tir.args[0]) != types.float32 or \
+            types.unliteral(tir.return_type) != types.float32:
+        return None
+    blocks = tir.func_ir.blocks
+    if len(blocks) != 1:
+        return None
+    defs = _single_defs(blocks, ir)
+    calls = [i.value for blk in blocks.values() for i in blk.body
+             if isinstance(i, ir.Assign) and isinstance(i.value, ir.Expr) and i.value.op == "call"]
+    if len(calls) != 1 or len(calls[0].args) != 1 or calls[0].kws:
+        return None
+    routine = _PAIR_ROUTINES.get(tr.callee(calls[0].func))
+    if routine is None or not isinstance(_resolve(defs, ir, calls[0].args[0].name), ir.Arg):
+        return None
+    (ret,) = [i for blk in blocks.values() for i in blk.body if isinstance(i, ir.Return)]
+    value = _resolve(defs, ir, ret.value.name)
+    while isinstance(value, ir.Expr) and value.op == "cast":
+        value = _resolve(defs, ir, value.value.name)
+    return routine if value is calls[0] else None
 
 
 class CompiledKernel:

@@ -683,6 +683,37 @@ __device__ __forceinline__ float f_erf(float x) {
   const float large = copysignf(1.0f - e, x);
   return t < 1.0f ? small : large;
 }
+// f_erf for two values: the polynomials run as packed FMAs, the same operations
+// in the same order as the scalar form (bit-identical results).
+__device__ __forceinline__ void erf_pair(float x0, float x1, float &r0, float &r1) {
+  const float t0 = fabsf(x0), t1 = fabsf(x1);
+  const unsigned long long x = pack2(x0, x1);
+  unsigned long long s;
+  asm("mul.rn.f32x2 %0, %1, %1;" : "=l"(s) : "l"(x));
+  unsigned long long p = splat2(7.853846909711137e-05f);
+  p = fma2(p, s, splat2(-0.0008010189048945904f));
+  p = fma2(p, s, splat2(0.00518832728266716f));
+  p = fma2(p, s, splat2(-0.026853810995817184f));
+  p = fma2(p, s, splat2(0.1128358542919159f));
+  p = fma2(p, s, splat2(-0.3761262595653534f));
+  p = fma2(p, s, splat2(0.12837916612625122f));
+  float small0, small1;
+  unpack2(fma2(p, x, x), small0, small1);
+  const unsigned long long tc = pack2(t0 > 4.0f ? 4.0f : t0, t1 > 4.0f ? 4.0f : t1); // keeps NaN
+  unsigned long long u = splat2(-0.0002688896202016622f);
+  u = fma2(u, tc, splat2(0.004252584185451269f));
+  u = fma2(u, tc, splat2(-0.03150571510195732f));
+  u = fma2(u, tc, splat2(0.14875170588493347f));
+  u = fma2(u, tc, splat2(0.9206482768058777f));
+  u = fma2(u, tc, splat2(1.626046061515808f));
+  u = fma2(u, tc, splat2(0.0004926985129714012f));
+  float u0, u1, e0, e1;
+  unpack2(u, u0, u1);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(-u0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(-u1));
+  r0 = t0 < 1.0f ? small0 : copysignf(1.0f - e0, x0);
+  r1 = t1 < 1.0f ? small1 : copysignf(1.0f - e1, x1);
+}
 #ifdef NMB_FASTMATH
 __device__ __forceinline__ float f_div(float a, float b) {
   float r;

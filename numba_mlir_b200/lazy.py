@@ -253,11 +253,14 @@ class DeviceFunc:
     elementwise operation (what @vectorize of a scalar body gives the
     reference, numba_mlir/mlir/vectorize.py:45-70)."""
 
-    def __init__(self, name, source, arg_dtypes, ret_dtype):
+    def __init__(self, name, source, arg_dtypes, ret_dtype, pair=None):
         self.name = name
         self.source = source
         self.arg_dtypes = tuple(np.dtype(d) for d in arg_dtypes)
         self.ret_dtype = np.dtype(ret_dtype)
+        # name of the nmb_device.cuh routine that computes the function for two
+        # float32 values at once, when the body is nothing but that function
+        self.pair = pair
 
 
 # ---------------------------------------------------------------- tracing ---
@@ -1348,7 +1351,8 @@ class _Emitter:
             # even when both carry .rn, which would change the rounding.  So a
             # product stays a scalar multiply (whose .rn is honoured) unless every
             # reader is known not to add to it.
-            if not (node.kind == "op" and node.op in _PRODUCT_READERS):
+            pair_call = node.kind == "call" and node.op.pair and node.dtype == np.float32
+            if not (node.kind == "op" and node.op in _PRODUCT_READERS) and not pair_call:
                 for e in ins:
                     self.scalar_only.add(e)
             if node.kind == "cast":
@@ -1360,6 +1364,8 @@ class _Emitter:
             elif node.kind == "call":
                 self.funcs[node.op.name] = node.op.source
                 rhs = f"{node.op.name}({', '.join(ins)})"
+                if pair_call:
+                    self.packable[len(self.lines)] = (node.op.pair, ins)
             else:
                 loop_dt = node.inputs[0].dtype
                 rhs = UFUNCS[node.op][1](loop_dt, *ins)

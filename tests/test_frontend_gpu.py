@@ -338,6 +338,47 @@ def test_paired_float32_arithmetic_is_bit_identical_to_numpy(queue, n):
     assert not residual(_dev(a), _dev(b), _dev(ab)).copy_to_host().any()
 
 
+def test_log_float32_within_1ulp_and_pair_forms_equal_scalar_forms(queue):
+    """The library's own float32 log: every float32 of three binades around 1
+    at stride 5, a logarithmic sweep over the whole range, subnormals and the
+    special values, against float64 log rounded to float32 (1 ulp).  The
+    two-values-at-once forms of log and erf (used where a chain runs over
+    16-byte aligned data) give the very bits of the scalar forms (used for
+    unaligned data and ragged ends)."""
+    import numba_mlir_b200 as nm
+
+    @nm.vectorize
+    def gerf(x):
+        return math.erf(x)
+
+    lo, hi = np.float32(0.25).view(np.int32), np.float32(4.0).view(np.int32)
+    near = np.arange(lo, hi, 5, dtype=np.int32).view(np.float32)
+    sweep = np.logspace(-37.5, 38.4, 200001).astype(np.float32)
+    sub = np.logspace(-45, -38, 5000).astype(np.float32)
+    x = np.concatenate([near, sweep, sub, np.array([1.0, 0.99999994, 1.0000001, 0.70710677, 0.7071068, 1.4142135,
+                                                    1.4142137, 3.4028235e38, 1.1754944e-38], np.float32)])
+    if x.size % 2:
+        x = x[:-1]
+    flog = nm.njit(lambda a: np.log(a))
+    got = flog(_dev(x)).copy_to_host()
+    truth = np.log(x.astype(np.float64))
+    want = truth.astype(np.float32)
+    ulp = np.spacing(np.abs(want)).astype(np.float64)
+    ok = want != 0
+    err = np.abs(got.astype(np.float64) - truth)[ok] / ulp[ok]
+    assert err.max() <= 1.0, (err.max(), x[ok][err.argmax()])
+    special = np.array([0.0, -0.0, -1.0, np.inf, -np.inf, np.nan, 1.0], np.float32)
+    with np.errstate(all="ignore"):
+        np.testing.assert_array_equal(flog(_dev(special)).copy_to_host(), np.log(special))
+    # unaligned views take the one-element forms: same bits
+    pad = np.concatenate([np.zeros(1, np.float32), x])
+    np.testing.assert_array_equal(flog(_dev(pad)[1:]).copy_to_host(), got)
+    y = np.concatenate([np.linspace(-5, 5, 100001).astype(np.float32), np.float32([np.nan])])
+    ferf = nm.njit(lambda a: gerf(a))
+    pad = np.concatenate([np.zeros(1, np.float32), y])
+    np.testing.assert_array_equal(ferf(_dev(pad)[1:]).copy_to_host(), ferf(_dev(y)).copy_to_host())
+
+
 def test_where_compare_cast_and_strided_operands(queue):
     import numba_mlir_b200 as nm
 
