@@ -532,6 +532,12 @@ __device__ __forceinline__ void reduce_cols_fused(const Chain &chain, int64_t ro
 // rounded like the scalar instruction, so results are bit-identical; what is
 // saved is an issue slot per pair, which is what bounds long elementwise
 // chains.  The generated chains call these for two adjacent elements.
+// Callers keep a multiply whose product feeds an addition or subtraction
+// scalar: the assembler merges mul.f32x2 into a dependent add/sub.f32x2 (a
+// fused multiply-add, one rounding instead of two) although both carry .rn.
+// Writing the sum as fma.f32x2 with a multiplier of 1 does not prevent it
+// (measured: a*b + c still came out fused), so no packed form of "product
+// then sum" is offered outside fastmath.
 __device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
   unsigned long long r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
