@@ -347,8 +347,11 @@ class Translator:
     mode 'kernel': parameters are the kernel's own, `return` leaves the kernel.
     mode 'device': a `__device__` function returning a scalar."""
 
-    def __init__(self, tir, mode, func_name, index32=False):
+    def __init__(self, tir, mode, func_name, index32=False, fastmath=False):
         from numba.core import ir, types
+
+        # fastmath: a*b+c may contract, so packed products may feed packed sums
+        self.fastmath = bool(fastmath)
 
         self.ir = ir
         self.types = types
@@ -1209,12 +1212,12 @@ class Translator:
         is_mul = lambda e: isinstance(e, ir.Expr) and e.op in ("binop", "inplace_binop") and \
             self._PACK_FNS.get(e.fn) == "mul2"  # noqa: E731
         keep_scalar = set()
-        for inst in stmts:
+        for inst in ([] if self.fastmath else stmts):
             reader_is_mul = isinstance(inst, ir.Assign) and is_mul(inst.value)
             if not reader_is_mul:
                 keep_scalar.update(u.name for u in inst.list_vars())
         for label, blk in blocks.items():
-            if label != body_label:
+            if label != body_label and not self.fastmath:
                 for inst in blk.body:
                     keep_scalar.update(u.name for u in inst.list_vars())
         for c0 in range(0, trip, 2):
@@ -1469,7 +1472,7 @@ def compile_kernel(py_func, args, ndim, fastmath=False, index32=False, max_threa
     tir = typed_ir(py_func, argtypes)
     from numba.core import types
 
-    tr = Translator(tir, "kernel", "nmb_kernel", index32=index32)
+    tr = Translator(tir, "kernel", "nmb_kernel", index32=index32, fastmath=fastmath)
     pnames = [f"p{i}" for i in range(len(argtypes))]
     body = tr.translate(pnames)
     written = {int(r[6:-1]) for r in tr.written_params if r.startswith("<param")}
@@ -1696,7 +1699,7 @@ def compile_parfor(py_func, args, fastmath=False, index32=False):
         raise UnsupportedError(
             f"{py_func.__name__}: a function with prange loops returns None or a scalar (array "
             "results go to array arguments)")
-    tr = Translator(tir, "parfor", "nmb_parfor", index32=index32)
+    tr = Translator(tir, "parfor", "nmb_parfor", index32=index32, fastmath=fastmath)
     ir = tr.ir
     blocks = tir.func_ir.blocks
     cfg = compute_cfg_from_blocks(blocks)
