@@ -1063,6 +1063,7 @@ class Translator:
         index_pos = {}              # tuple variable -> positions holding the loop variable
         stored, loaded = [], []     # (array variable, index variable)
         packed = 0
+        body_targets = {i.target.name for i in stmts if isinstance(i, ir.Assign)}
         for inst in stmts:
             if isinstance(inst, ir.Del):
                 continue
@@ -1109,11 +1110,8 @@ class Translator:
                     return False
             else:
                 return False
-            for u in used:
-                if u.name not in defined and u.name != phi:
-                    d = defs.get(u.name)
-                    if d is not None and any(isinstance(i, ir.Assign) and i.target.name == u.name for i in stmts):
-                        return False  # carried from the previous iteration
+            if any(u.name in body_targets and u.name not in defined for u in used):
+                return False  # read before it is assigned: carried from the previous iteration
             if isinstance(inst, ir.Assign):
                 defined.add(inst.target.name)
         if not packed:

@@ -228,6 +228,14 @@ def _kmeans_kernel(points, centroids, labels, sums, counts):
             atomic.add(counts, lid, lcnt[lid])
 
 
+# The same program compiled with fastmath=True: the subtraction, the square and
+# the accumulation of two points then run as packed instructions that the
+# assembler merges into fused multiply-adds, so a distance is rounded once per
+# dimension instead of twice and a label may differ from the default build's
+# where two centroids are nearly equally near.
+_kmeans_kernel_fastmath = kernel(gpu_use_64bit_index=False, fastmath=True)(_kmeans_kernel.py_func)
+
+
 # The same iteration in the plain form: one point per work-item, every point
 # adds itself to its cluster's sum and count with global atomics.
 @kernel(gpu_use_64bit_index=False)
@@ -253,7 +261,7 @@ def kmeans_step_naive(points, centroids, labels, sums, counts):
     _kmeans_naive_kernel[points.shape[0], KMEANS_LOCAL_SIZE](points, centroids, labels, sums, counts)
 
 
-def kmeans_step(points, centroids, labels, sums, counts):
+def kmeans_step(points, centroids, labels, sums, counts, fastmath=False):
     """Assignment + accumulation for every point.  N must be a multiple of
     256 * 8 because every work-item of a group takes part in the barriers and
     handles 8 points."""
@@ -263,4 +271,5 @@ def kmeans_step(points, centroids, labels, sums, counts):
     chunk = KMEANS_LOCAL_SIZE * _KM_PTS
     if n % chunk:
         raise ValueError(f"the number of points must be a multiple of {chunk}")
-    _kmeans_kernel[n // _KM_PTS, KMEANS_LOCAL_SIZE](points, centroids, labels, sums, counts)
+    (_kmeans_kernel_fastmath if fastmath else _kmeans_kernel)[n // _KM_PTS, KMEANS_LOCAL_SIZE](
+        points, centroids, labels, sums, counts)

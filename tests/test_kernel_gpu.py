@@ -311,6 +311,11 @@ def test_packed_inner_loops_round_like_the_scalar_loop(queue):
         t = pts[:, j] - c[j]
         want = want + t * t
     assert np.array_equal(out.copy_to_host(), want)
+    # fastmath=True allows a*b+c to contract: the products are packed too (and
+    # merged with the sums), the result agrees to rounding
+    out = _dev(np.zeros(n, np.float32))
+    kernel(sqdist, fastmath=True)[n // 2](_dev(pts), _dev(c), out)
+    np.testing.assert_allclose(out.copy_to_host(), want, rtol=2e-6)
 
 
 def test_kwargs_and_mixed_devices_are_rejected(queue):
