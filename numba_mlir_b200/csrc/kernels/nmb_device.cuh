@@ -599,7 +599,7 @@ __device__ __forceinline__ float f_log(float x) {
   const int eb = (ix - 0x3f3504f3) & (int)0xff800000; // e * 2^23
   const float f = __fsub_rn(__int_as_float(ix - eb), 1.0f);
   const float s = __fmul_rn(f, f);
-  float p;
+  float p = 0.0f;
   bool first = true;
 #define NMB_STEP(c) p = first ? (c) : fmaf(p, f, (c)); first = false;
   NMB_LOG_COEFFS(NMB_STEP)
