@@ -1041,7 +1041,7 @@ def run_gpu(args):
             }
         if others:
             line["other_configs"] = others
-        if world == 1 and not args.no_extra and args.workload == "black_scholes":
+        if world == 1 and not args.no_extra and not args.no_dispatch and args.workload == "black_scholes":
             line["host_us_per_launch"] = dispatch_times(queue, 5000)
         if world == 1 and not args.no_cpu:
             times, threads, cpu_bytes, cpu_units = time_cpu(args.workload, budget_s=12.0, max_steps=100)
@@ -1152,6 +1152,8 @@ def main():
     ap.add_argument("--workload", default="black_scholes", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations")
+    ap.add_argument("--no-dispatch", action="store_true",
+                    help="skip the dispatcher microbenchmark (tens of thousands of tiny launches)")
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of a CUDA graph")
     ap.add_argument("--profile", action="store_true",
                     help="run only warmup + steps eager device steps of --workload (for ncu)")
