@@ -716,6 +716,14 @@ class LazyArray:
             return out
         if func is np.shape:
             return self.shape
+        if func in _STACKS:
+            return stack_lazy(self.trace, _STACKS[func], *args, **kwargs)
+        if func is np.flip:
+            return flip_lazy(self.trace, *args, **kwargs)
+        if func is np.outer and len(args) == 2 and not kwargs:
+            return outer_lazy(self.trace, *args)
+        if func in (np.tril, np.triu):
+            return triangle_lazy(self.trace, func is np.tril, *args, **kwargs)
         raise TypeError(f"numpy.{func.__name__} is not supported on device arrays")
 
     # operators -------------------------------------------------------------------
@@ -830,6 +838,7 @@ class LazyArray:
     def argmax(self, axis=None): return reduce_lazy(self.trace, "argmax", self, axis=axis)
     def dot(self, other): return dot(self.trace, self, other)
     def __matmul__(self, other): return dot(self.trace, self, other)
+    def __rmatmul__(self, other): return dot(self.trace, other, self)
 
     def astype(self, dtype):
         dtype = np.dtype(dtype)
@@ -1028,6 +1037,64 @@ def concatenate_lazy(trace, arrays, axis=0, out=None, dtype=None):
         res[idx] = p
         pos += p.shape[axis]
     return res
+
+
+def _lazy(trace, x):
+    return x if isinstance(x, LazyArray) else LazyArray(trace, _as_node(trace, x))
+
+
+# hstack / vstack / dstack (numba_mlir/mlir/numpy/funcs.py: numpy.hstack, vstack,
+# dstack): the operands get the rank NumPy gives them, then it is a concatenate
+_STACKS = {np.vstack: "v", np.hstack: "h", np.dstack: "d"}
+
+
+def stack_lazy(trace, kind, tup, dtype=None, casting=None):
+    parts = [_lazy(trace, x) for x in tup]
+    if not parts:
+        raise ValueError("need at least one array to concatenate")
+
+    def at_least(x, nd):
+        if x.ndim >= nd:
+            return x
+        if x.ndim == 0:
+            return x.reshape((1,) * nd)
+        if nd == 2:
+            return x.reshape(1, x.shape[0])                      # (N,) -> (1, N)
+        return x.reshape(1, x.shape[0], 1) if x.ndim == 1 else x.reshape(x.shape + (1,))
+
+    if kind == "v":
+        return concatenate_lazy(trace, [at_least(x, 2) for x in parts], axis=0, dtype=dtype)
+    if kind == "d":
+        return concatenate_lazy(trace, [at_least(x, 3) for x in parts], axis=2, dtype=dtype)
+    parts = [at_least(x, 1) for x in parts]
+    return concatenate_lazy(trace, parts, axis=0 if parts[0].ndim == 1 else 1, dtype=dtype)
+
+
+def flip_lazy(trace, m, axis=None):
+    """np.flip: a view with negative strides (numba_mlir/mlir/numpy/funcs.py: numpy.flip)."""
+    m = _lazy(trace, m)
+    axes = range(m.ndim) if axis is None else ([axis] if isinstance(axis, (int, np.integer)) else list(axis))
+    axes = {int(a) % m.ndim for a in axes}
+    return m[tuple(slice(None, None, -1) if d in axes else slice(None) for d in range(m.ndim))]
+
+
+def outer_lazy(trace, a, b):
+    a, b = _lazy(trace, a).ravel(), _lazy(trace, b).ravel()
+    return apply_ufunc(trace, "multiply", (a.reshape(a.shape[0], 1), b.reshape(1, b.shape[0])))
+
+
+def triangle_lazy(trace, lower, m, k=0):
+    """np.tril / np.triu over the last two axes: a select against row and column
+    numbers (two small index vectors travel to the device with the call)."""
+    m = _lazy(trace, m)
+    if m.ndim < 2:
+        raise ValueError("tril and triu need an array of at least two dimensions")
+    rows, cols = m.shape[-2], m.shape[-1]
+    i = np.arange(rows, dtype=np.int64).reshape(rows, 1)
+    j = np.arange(cols, dtype=np.int64).reshape(1, cols)
+    diff = apply_ufunc(trace, "subtract", (j, i))                 # column - row
+    keep = apply_ufunc(trace, "less_equal" if lower else "greater_equal", (diff, np.int64(k)))
+    return where(trace, keep, m, m.dtype.type(0))
 
 
 def clip_lazy(trace, a, a_min=None, a_max=None, out=None):

@@ -118,6 +118,22 @@ def test_float32_arithmetic_is_emitted_for_two_elements_at_once(runtime_lib):
     assert "nmb::mul2(" in bytes(step[1]).decode()
 
 
+def test_array_building_functions_trace_and_compile(runtime_lib):
+    """hstack / vstack / dstack, flip, outer, tril and triu of the reference's
+    NumPy table (numba_mlir/mlir/numpy/funcs.py) become stores into slices,
+    views with negative strides, a broadcast product and a select against row
+    and column numbers: every kernel they generate compiles."""
+    shapes = [((6, 8), np.float32), ((6, 8), np.float32), ((8,), np.float32), ((5,), np.float32)]
+    for fn in (lambda a, b, v, w: np.vstack((a, b + 1)),
+               lambda a, b, v, w: np.hstack((v, w)),
+               lambda a, b, v, w: np.dstack((a, b)),
+               lambda a, b, v, w: np.flip(a, axis=1) * 2,
+               lambda a, b, v, w: np.outer(v, w),
+               lambda a, b, v, w: np.triu(a, 1) + np.tril(b, -2)):
+        _trace, launches = _trace_and_compile(fn, shapes)
+        assert launches
+
+
 def test_large_local_arrays_move_to_the_local_memory_parameter(runtime_lib):
     """Local arrays stay static shared memory while the kernel's static total
     fits 48 KB; above that the kernel takes an offset parameter and the launch carries a local-memory

@@ -397,6 +397,41 @@ def test_where_compare_cast_and_strided_operands(queue):
     assert np.array_equal(got, (i * i).astype(np.float32) / np.float32(2))
 
 
+def test_stacking_flipping_outer_and_triangles(queue):
+    """The array-building functions of the reference's NumPy table
+    (numba_mlir/mlir/numpy/funcs.py: hstack, vstack, dstack, flip, outer,
+    tril, triu, eye) against NumPy, on arrays and on expressions."""
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(9)
+    a = rng.standard_normal((6, 8)).astype(np.float32)
+    b = rng.standard_normal((6, 8)).astype(np.float32)
+    v = rng.standard_normal(8).astype(np.float32)
+    w = rng.standard_normal(5).astype(np.float32)
+    cases = [
+        (lambda a, b, v, w: np.vstack((a, b + 1)), None),
+        (lambda a, b, v, w: np.hstack((a, b * 2)), None),
+        (lambda a, b, v, w: np.dstack((a, b)), None),
+        (lambda a, b, v, w: np.hstack((v, w)), None),
+        (lambda a, b, v, w: np.vstack((v, v * 3)), None),
+        (lambda a, b, v, w: np.dstack((v, v)), None),
+        (lambda a, b, v, w: np.flip(a) + b, None),
+        (lambda a, b, v, w: np.flip(a, axis=1) * 2, None),
+        (lambda a, b, v, w: np.flip(a + b, axis=0), None),
+        (lambda a, b, v, w: np.outer(v, w), None),
+        (lambda a, b, v, w: np.outer(a, w + 1), None),
+        (lambda a, b, v, w: np.tril(a), None),
+        (lambda a, b, v, w: np.triu(a, 1) + np.tril(b, -2), None),
+        (lambda a, b, v, w: np.tril(a + b, k=2), None),
+        (lambda a, b, v, w: a * np.eye(6, 8, dtype=np.float32), None),
+    ]
+    for fn, _ in cases:
+        got = nm.njit(fn)(_dev(a), _dev(b), _dev(v), _dev(w)).copy_to_host()
+        want = fn(a, b, v, w)
+        assert got.shape == want.shape and got.dtype == want.dtype
+        np.testing.assert_array_equal(got, want)
+
+
 def test_dot_and_norm_expansion_distance(queue):
     """np.dot on device arrays reaches the tensor-core gemm (numpy/funcs.py:752-812);
     the distance matrix written with it matches the direct loop to 1e-5."""
