@@ -583,10 +583,10 @@ __device__ __forceinline__ unsigned long long splat2(float v) { return pack2(v, 
 // arguments take the library's logf.  The pair form computes two values with
 // f32x2 instructions: the same operations in the same order, bit-identical
 // to the scalar form.
-#define NMB_LOG_COEFFS(X)                                                                         \
-  X(-0.07634449750185013f) X(0.12761560082435608f) X(-0.13160191476345062f) X(0.14201760292053223f) \
-  X(-0.16623356938362122f) X(0.20001226663589478f) X(-0.2500081956386566f)
-constexpr float kLogC0 = 0.3333333134651184f;
+// Coefficients of P, highest power first; the constant term follows.
+constexpr float kLogC7 = -0.07634449750185013f, kLogC6 = 0.12761560082435608f, kLogC5 = -0.13160191476345062f,
+                kLogC4 = 0.14201760292053223f, kLogC3 = -0.16623356938362122f, kLogC2 = 0.20001226663589478f,
+                kLogC1 = -0.2500081956386566f, kLogC0 = 0.3333333134651184f;
 constexpr float kLn2Over2p23 = 0.693147182464599609375f * 1.1920928955078125e-07f; // ln2 (float32) * 2^-23, exact
 __device__ __forceinline__ bool log_fast_range(float x) {
   // positive, normal, finite
@@ -599,11 +599,13 @@ __device__ __forceinline__ float f_log(float x) {
   const int eb = (ix - 0x3f3504f3) & (int)0xff800000; // e * 2^23
   const float f = __fsub_rn(__int_as_float(ix - eb), 1.0f);
   const float s = __fmul_rn(f, f);
-  float p = 0.0f;
-  bool first = true;
-#define NMB_STEP(c) p = first ? (c) : fmaf(p, f, (c)); first = false;
-  NMB_LOG_COEFFS(NMB_STEP)
-#undef NMB_STEP
+  float p = kLogC7;
+  p = fmaf(p, f, kLogC6);
+  p = fmaf(p, f, kLogC5);
+  p = fmaf(p, f, kLogC4);
+  p = fmaf(p, f, kLogC3);
+  p = fmaf(p, f, kLogC2);
+  p = fmaf(p, f, kLogC1);
   p = fmaf(p, f, kLogC0);
   const float t = fmaf(p, f, -0.5f);
   const float r = fmaf(t, s, f);
@@ -617,17 +619,18 @@ __device__ __forceinline__ void log_pair(float x0, float x1, float &r0, float &r
   }
   const int i0 = __float_as_int(x0), i1 = __float_as_int(x1);
   const int e0 = (i0 - 0x3f3504f3) & (int)0xff800000, e1 = (i1 - 0x3f3504f3) & (int)0xff800000;
-  unsigned long long f, fdummy;
+  unsigned long long f, s;
   asm("sub.rn.f32x2 %0, %1, %2;"
       : "=l"(f)
       : "l"(pack2(__int_as_float(i0 - e0), __int_as_float(i1 - e1))), "l"(splat2(1.0f)));
-  asm("mul.rn.f32x2 %0, %1, %1;" : "=l"(fdummy) : "l"(f));
-  const unsigned long long s = fdummy;
-  unsigned long long p = 0;
-  bool first = true;
-#define NMB_STEP(c) p = first ? splat2(c) : fma2(p, f, splat2(c)); first = false;
-  NMB_LOG_COEFFS(NMB_STEP)
-#undef NMB_STEP
+  asm("mul.rn.f32x2 %0, %1, %1;" : "=l"(s) : "l"(f));
+  unsigned long long p = splat2(kLogC7);
+  p = fma2(p, f, splat2(kLogC6));
+  p = fma2(p, f, splat2(kLogC5));
+  p = fma2(p, f, splat2(kLogC4));
+  p = fma2(p, f, splat2(kLogC3));
+  p = fma2(p, f, splat2(kLogC2));
+  p = fma2(p, f, splat2(kLogC1));
   p = fma2(p, f, splat2(kLogC0));
   const unsigned long long t = fma2(p, f, splat2(-0.5f));
   const unsigned long long r = fma2(t, s, f);
