@@ -197,8 +197,16 @@ class Dispatcher:
             except parfor_split.SplitError as e:
                 raise TypeError(str(e)) from None
         queue = next(a.queue for a in args if isinstance(a, DeviceArray))
-        result, _plan = lazy.trace_call(self._split_func, args, queue,
-                                        fastmath=bool(self.options.get("fastmath", False)))
+        key = lazy.signature_of(args)
+        plan = self._plans.get(key) if key is not None else None
+        if plan is not None:
+            return plan.replay(args, queue)
+        result, plan = lazy.trace_call(self._split_func, args, queue,
+                                       fastmath=bool(self.options.get("fastmath", False)))
+        if plan is not None and key is not None:
+            # loops that hand no scalar back to the host code are steps of the
+            # plan like the kernels of the array expressions around them
+            self._plans[key] = plan
         return result
 
     def _call_parfor_in_trace(self, trace, args):
@@ -207,26 +215,39 @@ class Dispatcher:
         its scalar result (if any) comes back as a host value."""
         if trace.dry:
             raise TypeError("prange loops cannot be traced without a device")
-        real = []
+        real, specs, replayable = [], [], True
         for a in args:
             if isinstance(a, lazy.LazyArray):
                 if a.shape == () and a.concrete is not None and a.node.kind != "leaf":
                     real.append(a.concrete)
+                    if a.node.kind == "arg":
+                        specs.append(("arg", a.node.value))   # a scalar argument of the call
+                    elif a.node.kind == "const":
+                        specs.append(("const", a.concrete))
+                    else:
+                        replayable = False                     # computed from argument values
                     continue
                 slot = trace.materialize(a)
                 arr = trace.arrays[slot]
                 if a.shape == ():
                     real.append(arr.copy_to_host()[()])  # a device scalar: the loop takes its value
+                    replayable = False
                 else:
                     trace.before_direct_write(slot)  # the loop may write it
                     real.append(arr)
+                    specs.append(("slot", slot))
             else:
                 real.append(a)
-        trace.value_dependent = True  # the launch is not part of a replayable plan
+                specs.append(("const", a))  # a shape or a literal: fixed for this signature
         trace.flush()
         if not any(isinstance(a, DeviceArray) for a in real):
             raise TypeError(f"{self.py_func.__name__}: a prange loop needs at least one device array")
-        return self._call_parfor(tuple(real))
+        result = self._call_parfor(tuple(real))
+        if result is not None or not replayable:
+            trace.value_dependent = True  # a scalar goes back to the host code: no replayable plan
+        else:
+            trace.steps.append(("parfor", self, tuple(specs)))
+        return result
 
     def trace_dry(self, *args):
         """Records the plan and generates the kernels without a device (used

@@ -1937,6 +1937,10 @@ class Plan:
                 contraction.gemm(get(step[1]), get(step[2]), get(step[3]), blocking=False)
             elif tag == "contract":
                 run_contract(step, get)
+            elif tag == "parfor":
+                # a `prange` loop cut out of the function: its own compiled kernel
+                real = [get(s[1]) if s[0] == "slot" else args[s[1]] if s[0] == "arg" else s[1] for s in step[2]]
+                step[1]._call_parfor(tuple(real))
         for i in _result_slots(self.result_spec):
             get(i)
         return _build_result(self.result_spec, arrays)

@@ -357,6 +357,40 @@ def test_loops_mixed_with_array_expressions_and_host_scalars(queue):
         np.testing.assert_allclose(out.copy_to_host(), want, rtol=1e-6)
 
 
+def test_loops_without_host_scalars_are_replayed_from_the_plan(queue):
+    """A function cut at its loops whose loops hand nothing back to the host
+    code is recorded once per signature (loops and array expressions alike are
+    steps of the plan) and replayed on later calls; new data, a scalar
+    argument and a different length all give NumPy's results."""
+    import numba
+
+    import numba_mlir_b200 as nm
+
+    def py_func(a, b, alpha, out):
+        tmp = a * alpha + b                  # array expression
+        for i in numba.prange(a.shape[0]):   # loop over the expression's value
+            out[i] = tmp[i] * tmp[i]
+        out[:] = out - b                     # array expression between the loops
+        for i in numba.prange(a.shape[0] - 1):
+            out[i] = out[i] + a[i + 1]
+
+    def want(a, b, alpha):
+        tmp = a * alpha + b
+        o = tmp * tmp - b
+        o[:-1] = o[:-1] + a[1:]
+        return o
+
+    f = nm.njit(py_func)
+    rng = np.random.default_rng(8)
+    for n, alpha in ((4000, 2.0), (4000, 3.0), (4000, -1.5), (1000, 0.5), (1000, 4.0)):
+        a = rng.integers(-4, 5, n).astype(np.float32)
+        b = rng.integers(-4, 5, n).astype(np.float32)
+        out = nm.zeros(n, np.float32)
+        f(_dev(a), _dev(b), np.float32(alpha), out)
+        assert np.array_equal(out.copy_to_host(), want(a, b, np.float32(alpha)))
+    assert len(f._plans) == 2  # one plan per length, reused by the later calls
+
+
 def test_njit_replace_parfors_offloads_only_the_loops(queue):
     """mlir_njit_replace_parfors (decorators.py:84-104): the loops go to the
     device, the code around them stays on the host, also when there is only
