@@ -317,6 +317,77 @@ __device__ __forceinline__ void reduce_rows_fused(const Chain &chain, int64_t ro
   }
 }
 
+template <typename T, int N> __device__ T vec_element(const Vec<T, N> &);
+template <typename T> __device__ __forceinline__ T neutral_min(); // defined with the @kernel API below
+template <typename T> __device__ __forceinline__ T neutral_max();
+
+// out[r] = position of the smallest (MIN) or largest value[r * cols + k] of row
+// r, one warp per row, rows taken round robin; cols % V == 0.  A lane visits
+// its elements in increasing column order, so a strict comparison keeps the
+// first occurrence; between lanes the lower column wins ties.  NaNs never
+// compare true and are passed over, as in the library's argmin kernels; a row
+// in which nothing beats the identity gives 0.
+template <int BLOCK, int V, int UNROLL, bool MIN, typename Chain>
+__device__ __forceinline__ void reduce_rows_arg_fused(const Chain &chain, int64_t rows, int64_t cols,
+                                                      int64_t *out) {
+  using In = typename Chain::template In<V>;
+  using Out = typename Chain::template Out<V>;
+  using T = decltype(vec_element(Out().out0));
+  constexpr int64_t kNone = 0x7fffffffffffffffll;
+  const int lane = threadIdx.x & 31;
+  const int64_t first = (int64_t)blockIdx.x * (BLOCK / 32) + (threadIdx.x >> 5);
+  const int64_t step = (int64_t)gridDim.x * (BLOCK / 32);
+  constexpr int64_t span = (int64_t)32 * V * UNROLL;
+  auto beats = [](T x, T v) { return MIN ? x < v : v < x; };
+  for (int64_t r = first; r < rows; r += step) {
+    const int64_t base = r * cols;
+    T bv = MIN ? neutral_min<T>() : neutral_max<T>();
+    int64_t bi = kNone;
+    int64_t k0 = 0;
+    for (; k0 + span <= cols; k0 += span) {
+      In in[UNROLL];
+      Out val[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        chain.template load<V>(base + k0 + (int64_t)(u * 32 + lane) * V, in[u]);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        chain.template compute<V>(in[u], val[u]);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+        for (int l = 0; l < V; ++l)
+          if (beats(val[u].out0.v[l], bv)) {
+            bv = val[u].out0.v[l];
+            bi = k0 + (int64_t)(u * 32 + lane) * V + l;
+          }
+    }
+    for (int64_t k = k0 + (int64_t)lane * V; k < cols; k += 32 * V) {
+      In in;
+      Out val;
+      chain.template load<V>(base + k, in);
+      chain.template compute<V>(in, val);
+#pragma unroll
+      for (int l = 0; l < V; ++l)
+        if (beats(val.out0.v[l], bv)) {
+          bv = val.out0.v[l];
+          bi = k + l;
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const T ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int64_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (beats(ov, bv) || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0)
+      out[r] = bi == kNone ? 0 : bi;
+  }
+}
+
 // out[0] = reduce_i value[i], i < n.  Blocks take tiles of BLOCK*V*UNROLL
 // elements round robin; n % V may be anything (the tail is read one by one).
 // Returns true in the one block that wrote the result (uniform over the block).

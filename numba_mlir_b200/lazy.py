@@ -1530,6 +1530,7 @@ class _ValueHolder:
 
 
 _FUSED_REDUCE_OPS = ("sum", "prod", "min", "max")
+_FUSED_ARG_OPS = ("argmin", "argmax")  # along the last axis only
 
 
 def reduce_resident(em, mode="all"):
@@ -1547,13 +1548,16 @@ def fused_reduce_mode(node, leaf_ok=False):
     temporary first).  A plain array as operand goes to the library kernels
     unless `leaf_ok` (a post-chain is to be fused into the generated kernel)."""
     src = node.inputs[0]
-    if node.op not in _FUSED_REDUCE_OPS or src.kind in ("arg", "const") or not node_reads(src):
+    if node.op not in _FUSED_REDUCE_OPS + _FUSED_ARG_OPS or src.kind in ("arg", "const") or not node_reads(src):
         return None
     if src.kind == "leaf" and not leaf_ok:
         return None
     if src.dtype.name not in _REDUCE_KERNEL_DTYPES:
         return None
     nd, axis = len(src.shape), node.value
+    if node.op in _FUSED_ARG_OPS:
+        # the position of the extreme value of every row, one warp per row
+        return "rows" if nd >= 2 and axis == nd - 1 and src.shape[-1] % 4 == 0 else None
     if axis is None or nd == 1:
         return "all"
     if axis == nd - 1:
@@ -1598,7 +1602,7 @@ def _emit_reduce_fused(trace, node, mode, dst, post=None):
     n_streams = sum(1 for _s, k, _p, _d in em.leaves if k == "full")
     unroll = 4 if n_streams <= 2 else 2
     sms = (148 if trace.dry else trace.queue.sm_count) * reduce_resident(em, mode)  # residency slots
-    block_row = mode == "rows" and cols >= 8192 and rows < sms
+    block_row = mode == "rows" and cols >= 8192 and rows < sms and node.op not in _FUSED_ARG_OPS
     acc_dt = node.dtype
     # column reductions: one group of 256 * vec columns per block (four groups,
     # whole 16 KB rows per block, measured slower: 66 us against 61 us)
@@ -1732,9 +1736,14 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
         act, oct = ctype(acc_dt), ctype(reduce[7])
         opc, ident = {"sum": ("nmb::OpAdd", f"{act}(0)"), "prod": ("nmb::OpMul", f"{act}(1)"),
                       "min": ("nmb::OpMin", f"nmb::neutral_min<{act}>()"),
-                      "max": ("nmb::OpMax", f"nmb::neutral_max<{act}>()")}[op]
+                      "max": ("nmb::OpMax", f"nmb::neutral_max<{act}>()"),
+                      "argmin": (None, None), "argmax": (None, None)}[op]
         kname = "nmb_fused_reduce"
-        if mode == "rows":
+        if op in _FUSED_ARG_OPS:
+            tail = "int64_t* __restrict__ out, int64_t rows, int64_t cols"
+            call = (f"nmb::reduce_rows_arg_fused<256, {vec}, {unroll}, {'true' if op == 'argmin' else 'false'}>"
+                    "(chain, rows, cols, out);")
+        elif mode == "rows":
             tail = f"{oct}* __restrict__ out, int64_t rows, int64_t cols"
             call = (f"__shared__ {act} scratch[32];\n  nmb::reduce_rows_fused<256, {vec}, {unroll}, "
                     f"{'true' if block_row else 'false'}>(chain, rows, cols, out, {opc}(), {ident}, scratch);")

@@ -134,6 +134,18 @@ def test_array_building_functions_trace_and_compile(runtime_lib):
         assert launches
 
 
+def test_argmin_of_a_chain_along_the_last_axis_is_one_kernel(runtime_lib):
+    """np.argmin / np.argmax of an elementwise chain along the last axis is
+    one generated kernel (a warp per row keeps value and position); along
+    another axis the chain goes to a temporary and the library kernel."""
+    _trace, launches = _trace_and_compile(lambda a, b: np.argmin(a * a - b, axis=1),
+                                          [((512, 256), np.float32), ((512, 256), np.float32)])
+    assert [s[2] for s in launches] == ["nmb_fused_reduce"] and len(_trace.steps) == 2  # alloc + launch
+    assert "reduce_rows_arg_fused<256, 4, 4, true>" in bytes(launches[0][1]).decode()
+    trace, launches = _trace_and_compile(lambda a: np.argmax(a * 2, axis=0), [((512, 256), np.float32)])
+    assert [s[0] for s in trace.steps].count("reduce") == 1 and [s[2] for s in launches] == ["nmb_fused"]
+
+
 def test_large_local_arrays_move_to_the_local_memory_parameter(runtime_lib):
     """Local arrays stay static shared memory while the kernel's static total
     fits 48 KB; above that the kernel takes an offset parameter and the launch carries a local-memory

@@ -669,6 +669,29 @@ def test_reduction_of_an_elementwise_chain_is_one_pass(queue):
     assert n == 1
     assert np.array_equal(got.copy_to_host(), (a * b).min(axis=0))
 
+    # argmin / argmax of a chain along the last axis: one warp per row, first
+    # occurrence on ties (quantised values make ties frequent)
+    qa = np.round(a * 2).astype(np.float32)
+    qb = np.round(b * 2).astype(np.float32)
+    dqa, dqb = _dev(qa), _dev(qb)
+    amin = nm.njit(lambda x, y: np.argmin(x * x - y, axis=1))
+    amin(dqa, dqb)
+    got, n = _launches(amin, dqa, dqb)
+    assert n == 1 and got.dtype == np.int64
+    assert np.array_equal(got.copy_to_host(), np.argmin(qa * qa - qb, axis=1))
+    amax = nm.njit(lambda x, y: (np.abs(x) + y).argmax(axis=-1))
+    amax(dqa, dqb)
+    got, n = _launches(amax, dqa, dqb)
+    assert n == 1 and np.array_equal(got.copy_to_host(), np.argmax(np.abs(qa) + qb, axis=1))
+    ia = rng.integers(-50, 50, (300, 64)).astype(np.int32)
+    imax = nm.njit(lambda x: np.argmax(x * x - 7, axis=1))
+    got = imax(_dev(ia))
+    assert np.array_equal(got.copy_to_host(), np.argmax(ia * ia - 7, axis=1))
+    # three dimensions: rows are the leading axes flattened
+    t3 = np.round(rng.standard_normal((5, 7, 32)) * 3).astype(np.float32)
+    got = nm.njit(lambda x: np.argmin(x + 1, axis=2))(_dev(t3))
+    assert got.shape == (5, 7) and np.array_equal(got.copy_to_host(), np.argmin(t3 + 1, axis=2))
+
 
 @pytest.mark.parametrize("shape", [(1, 1), (3, 5), (64, 63), (1000, 8), (5, 40000), (2, 3, 17), (1031,)])
 @pytest.mark.parametrize("op", ["sum", "prod", "min", "max"])
