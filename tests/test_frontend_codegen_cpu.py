@@ -59,6 +59,11 @@ def test_black_scholes_chain_is_one_kernel(runtime_lib):
     launches = [s for s in trace.steps if s[0] == "launch"]
     assert len(launches) == 1 and plan is not None
     assert len(runtime.compile_to_cubin(launches[0][1])) > 0
+    # the chain runs for two options at once: its own +, -, *, the library's log
+    # and the @vectorize function that is nothing but erf use packed instructions
+    src = bytes(launches[0][1]).decode()
+    assert "nmb::log_pair(" in src and src.count("nmb::erf_pair(") == 2
+    assert "nmb::sub2(" in src and "nmb::add2(" in src and "nmb::mul2(" in src
 
 
 def test_fastmath_selects_the_approximate_division_and_sqrt(runtime_lib):
