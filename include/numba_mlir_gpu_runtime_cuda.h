@@ -73,6 +73,13 @@ typedef struct GPUXMemref2f {
   size_t dims[2];
   size_t strides[2];
 } GPUXMemref2f;
+typedef struct GPUXMemref2d {
+  void *userData;
+  double *data;
+  size_t offset;
+  size_t dims[2];
+  size_t strides[2];
+} GPUXMemref2d;
 
 /* ---- the 13 reference exports -------------------------------------------- */
 
@@ -143,6 +150,14 @@ void _mlir_ciface_mkl_gemm_float32_device(void *queue, const GPUXMemref2f *a,
 void mkl_gemm_float32_device(void *queue, const GPUXMemref2f *a,
                              const GPUXMemref2f *b, float alpha, float beta,
                              GPUXMemref2f *c);
+/* The float64 variant the reference registers beside it
+ * (mlir/math_runtime.py:36-40): any strides, blocking. */
+void _mlir_ciface_mkl_gemm_float64_device(void *queue, const GPUXMemref2d *a,
+                                          const GPUXMemref2d *b, double alpha,
+                                          double beta, GPUXMemref2d *c);
+void mkl_gemm_float64_device(void *queue, const GPUXMemref2d *a,
+                             const GPUXMemref2d *b, double alpha, double beta,
+                             GPUXMemref2d *c);
 
 /* ---- extensions (no counterpart in the reference, where dpctl moved the
  * data: mlir/tests/test_gpu.py:52-87) ------------------------------------- */
@@ -252,6 +267,9 @@ void *_mlir_ciface_nmb_pairwise_distance_float32_device(void *queue,
 void *_mlir_ciface_nmb_gemm_float32_device_async(void *queue, const GPUXMemref2f *a,
                                                  const GPUXMemref2f *b, float alpha,
                                                  float beta, GPUXMemref2f *c);
+void *_mlir_ciface_nmb_gemm_float64_device_async(void *queue, const GPUXMemref2d *a,
+                                                 const GPUXMemref2d *b, double alpha,
+                                                 double beta, GPUXMemref2d *c);
 
 /* The contraction with the elementwise chain around the product fused as its
  * epilogue, what the reference gets by fusing the linalg.generic ops around a

@@ -14,9 +14,9 @@ from . import runtime as _rt
 from .device_array import empty
 
 
-def _memref(a):
-    if a.dtype != np.float32 or a.ndim != 2:
-        raise TypeError("the tensor-core contraction takes 2-D float32 device arrays")
+def _memref(a, dtype=np.float32):
+    if a.dtype != dtype or a.ndim != 2:
+        raise TypeError(f"this routine takes 2-D {np.dtype(dtype).name} device arrays")
     it = a.dtype.itemsize
     m = _rt.Memref2f()
     m.userData = None
@@ -34,16 +34,21 @@ def gemm(a, b, c, alpha=1.0, beta=0.0, blocking=True):
     """c = alpha * a @ b + beta * c.  Blocking like the reference's call by
     default; `blocking=False` only enqueues it on the queue's stream."""
     lib = _rt.load()
-    ma, mb, mc = _memref(a), _memref(b), _memref(c)
+    if a.dtype == np.float64:
+        # the float64 entry (CUDA cores; B200 has no fast float64 tensor path)
+        ma, mb, mc = (_memref(x, np.float64) for x in (a, b, c))
+        sync, enqueue, scalar = (lib._mlir_ciface_mkl_gemm_float64_device,
+                                 lib._mlir_ciface_nmb_gemm_float64_device_async, ctypes.c_double)
+    else:
+        ma, mb, mc = _memref(a), _memref(b), _memref(c)
+        sync, enqueue, scalar = (lib._mlir_ciface_mkl_gemm_float32_device,
+                                 lib._mlir_ciface_nmb_gemm_float32_device_async, ctypes.c_float)
     if blocking:
-        lib._mlir_ciface_mkl_gemm_float32_device(c.queue.handle, ctypes.byref(ma), ctypes.byref(mb),
-                                                 ctypes.c_float(alpha), ctypes.c_float(beta),
-                                                 ctypes.byref(mc))
+        sync(c.queue.handle, ctypes.byref(ma), ctypes.byref(mb), scalar(alpha), scalar(beta), ctypes.byref(mc))
         _rt.check()
         return c
-    ev = lib._mlir_ciface_nmb_gemm_float32_device_async(c.queue.handle, ctypes.byref(ma), ctypes.byref(mb),
-                                                        ctypes.c_float(alpha), ctypes.c_float(beta),
-                                                        ctypes.byref(mc))
+    ev = enqueue(c.queue.handle, ctypes.byref(ma), ctypes.byref(mb), scalar(alpha), scalar(beta),
+                 ctypes.byref(mc))
     if not ev:
         _rt.check()
         raise _rt.GpuRuntimeError("gemm launch failed")

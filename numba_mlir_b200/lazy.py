@@ -487,9 +487,9 @@ class Trace:
         from . import contraction
 
         sa, sb = self.force(node.inputs[0]), self.force(node.inputs[1])
-        for s in (sa, sb):
-            if self.arrays[s].dtype != np.float32:
-                raise TypeError("np.dot on device arrays is implemented for float32 operands")
+        dts = {self.arrays[s].dtype for s in (sa, sb)}
+        if len(dts) != 1 or dts.pop() not in (np.float32, np.float64):
+            raise TypeError("np.dot on device arrays takes two float32 or two float64 operands")
         borrowed = dst is not None
         if dst is None:
             dst = self.add_tmp_slot(node.shape, node.dtype)
@@ -724,6 +724,8 @@ class LazyArray:
             return outer_lazy(self.trace, *args)
         if func in (np.tril, np.triu):
             return triangle_lazy(self.trace, func is np.tril, *args, **kwargs)
+        if func is np.cov:
+            return cov_lazy(self.trace, *args, **kwargs)
         raise TypeError(f"numpy.{func.__name__} is not supported on device arrays")
 
     # operators -------------------------------------------------------------------
@@ -1095,6 +1097,30 @@ def triangle_lazy(trace, lower, m, k=0):
     diff = apply_ufunc(trace, "subtract", (j, i))                 # column - row
     keep = apply_ufunc(trace, "less_equal" if lower else "greater_equal", (diff, np.int64(k)))
     return where(trace, keep, m, m.dtype.type(0))
+
+
+def cov_lazy(trace, m, y=None, rowvar=True, bias=False, ddof=None, fweights=None, aweights=None, dtype=None):
+    """np.cov of one set of observations (numba_mlir/mlir/numpy/funcs.py:
+    numpy.cov), with NumPy's steps: the data in float64 (or `dtype`), minus
+    the mean of every variable, times its own transpose (the float64 product),
+    times 1 / (N - ddof)."""
+    if y is not None or fweights is not None or aweights is not None:
+        raise TypeError("np.cov on device arrays takes one array and no weights")
+    m = _lazy(trace, m)
+    if m.ndim > 2:
+        raise ValueError("m has more than 2 dimensions")
+    dt = np.dtype(dtype) if dtype is not None else np.result_type(m.dtype, np.float64)
+    x = m if m.dtype == dt else m.astype(dt)
+    if x.ndim < 2:
+        x = x.reshape(1, x.size)
+    elif not rowvar and x.shape[0] != 1:
+        x = x.T
+    if ddof is None:
+        ddof = 0 if bias else 1
+    fact = max(x.shape[1] - ddof, 0)
+    centred = x - mean_lazy(trace, x, axis=1, keepdims=True)
+    c = dot(trace, centred, centred.T) * np.true_divide(1, fact).astype(dt)
+    return reduce_lazy(trace, "sum", c) if c.shape == (1, 1) else c
 
 
 def clip_lazy(trace, a, a_min=None, a_max=None, out=None):

@@ -78,6 +78,22 @@ SIGNATURES = {
         [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.c_float, ctypes.c_float,
          ctypes.POINTER(Memref2f)],
     ),
+    # Memref<2,double> has the same layout (the data pointer is passed as void*)
+    "_mlir_ciface_mkl_gemm_float64_device": (
+        None,
+        [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.c_double, ctypes.c_double,
+         ctypes.POINTER(Memref2f)],
+    ),
+    "mkl_gemm_float64_device": (
+        None,
+        [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.c_double, ctypes.c_double,
+         ctypes.POINTER(Memref2f)],
+    ),
+    "_mlir_ciface_nmb_gemm_float64_device_async": (
+        _vp,
+        [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.c_double, ctypes.c_double,
+         ctypes.POINTER(Memref2f)],
+    ),
     "_mlir_ciface_nmb_contract_rowcol_float32_device": (
         _vp,
         [_vp, ctypes.POINTER(Memref2f), ctypes.POINTER(Memref2f), ctypes.c_float, _i, _vp, _i, _vp, _i,

@@ -119,3 +119,49 @@ def test_gemm_column_major_output_and_errors(queue):
     assert np.array_equal(ct.copy_to_host().T, a @ b)
     with pytest.raises(runtime.GpuRuntimeError, match="shape mismatch"):
         contraction.gemm(_dev(a), _dev(a), zeros((40, 40), np.float32))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (65, 33, 17), (200, 300, 129), (64, 64, 16), (7, 513, 1000)])
+def test_gemm_float64_matches_numpy(queue, m, n, k):
+    """The float64 entry the reference registers beside the float32 one
+    (mlir/math_runtime.py:36-40): sums in index order with fused multiply-adds,
+    compared with NumPy's float64 product; operands with any strides; alpha,
+    beta; np.dot and @ on float64 device arrays reach it."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import contraction
+
+    rng = np.random.default_rng(m * 1000 + n + k)
+    a = rng.standard_normal((m, k))
+    b = rng.standard_normal((k, n))
+    c0 = rng.standard_normal((m, n))
+    scale = np.abs(a) @ np.abs(b) + 1.0
+
+    c = _dev(c0.copy())
+    contraction.gemm(_dev(a), _dev(b), c)
+    assert np.all(np.abs(c.copy_to_host() - a @ b) <= 1e-14 * k * scale)
+
+    # transposed views (no copies) and alpha / beta
+    at, bt = _dev(np.ascontiguousarray(a.T)).T, _dev(np.ascontiguousarray(b.T)).T
+    c = _dev(c0.copy())
+    contraction.gemm(at, bt, c, alpha=-0.5, beta=2.0)
+    assert np.all(np.abs(c.copy_to_host() - (-0.5 * (a @ b) + 2.0 * c0)) <= 1e-14 * k * (scale + np.abs(c0)))
+
+    got = nm.njit(lambda x, y: np.dot(x, y) + 1.0)(_dev(a), _dev(b))
+    assert got.dtype == np.float64
+    assert np.all(np.abs(got.copy_to_host() - (a @ b + 1.0)) <= 1e-14 * k * scale)
+    got = nm.njit(lambda x, y: x @ y)(_dev(a), _dev(b))
+    assert np.all(np.abs(got.copy_to_host() - a @ b) <= 1e-14 * k * scale)
+
+
+def test_gemm_float64_rejects_mixed_types_and_bad_shapes(queue):
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import contraction, runtime
+
+    a = _dev(np.ones((4, 3)))
+    b32 = _dev(np.ones((3, 5), np.float32))
+    with pytest.raises(TypeError):
+        contraction.gemm(a, b32, _dev(np.zeros((4, 5))))
+    with pytest.raises(TypeError):
+        nm.njit(lambda x, y: np.dot(x, y))(a, b32)
+    with pytest.raises(runtime.GpuRuntimeError, match="shape mismatch"):
+        contraction.gemm(a, _dev(np.ones((4, 5))), _dev(np.zeros((4, 5))))

@@ -432,6 +432,30 @@ def test_stacking_flipping_outer_and_triangles(queue):
         np.testing.assert_array_equal(got, want)
 
 
+def test_cov_uses_the_float64_product(queue):
+    """np.cov (numba_mlir/mlir/numpy/funcs.py: numpy.cov): float64 whatever the
+    input type, variables in rows or columns, bias and ddof, a single variable."""
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(21)
+    m32 = rng.standard_normal((5, 200)).astype(np.float32)
+    m64 = rng.standard_normal((3, 50))
+    v = rng.standard_normal(300).astype(np.float32)
+    cases = [
+        (lambda m: np.cov(m), m32),
+        (lambda m: np.cov(m), m64),
+        (lambda m: np.cov(m, rowvar=False), m64.T.copy()),
+        (lambda m: np.cov(m, bias=True), m32),
+        (lambda m: np.cov(m, ddof=2) * 2.0, m64),
+        (lambda m: np.cov(m), v),
+    ]
+    for fn, data in cases:
+        got = nm.njit(fn)(_dev(data)).copy_to_host()
+        want = fn(data)
+        assert got.dtype == np.float64 and got.shape == np.shape(want)
+        np.testing.assert_allclose(got, want, rtol=1e-10, atol=1e-12)
+
+
 def test_dot_and_norm_expansion_distance(queue):
     """np.dot on device arrays reaches the tensor-core gemm (numpy/funcs.py:752-812);
     the distance matrix written with it matches the direct loop to 1e-5."""
