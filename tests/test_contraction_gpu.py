@@ -121,7 +121,8 @@ def test_gemm_column_major_output_and_errors(queue):
         contraction.gemm(_dev(a), _dev(a), zeros((40, 40), np.float32))
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (65, 33, 17), (200, 300, 129), (64, 64, 16), (7, 513, 1000)])
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (65, 33, 17), (200, 300, 129), (64, 64, 16), (7, 513, 1000),
+                                   (2500, 2300, 70)])  # the last one takes the 128 x 128 tiles
 def test_gemm_float64_matches_numpy(queue, m, n, k):
     """The float64 entry the reference registers beside the float32 one
     (mlir/math_runtime.py:36-40): sums in index order with fused multiply-adds,
