@@ -103,7 +103,7 @@ class Dispatcher:
 
             if codegen_ir.uses_prange(self.py_func):
                 return self._call_parfor_in_trace(lazy.current_trace(), args)
-            return self.py_func(*args)
+            return lazy.with_device_creators(self.py_func)(*args)
         args = tuple(_wrap_arg(a) for a in args)
         devs = check_device_args(args)
         if not devs:

@@ -2050,9 +2050,107 @@ def fake_array(shape, dtype, ptr=None):
     return DeviceArray(_Foreign(None, ptr, n * dtype.itemsize, None), shape, dtype)
 
 
+# ---- arrays created inside a traced function ------------------------------
+# np.empty / zeros / ones / full called with a shape have no array argument, so
+# NumPy's protocols never show them to the trace; the function therefore runs
+# with its module-level `numpy` name (and any of those functions imported by
+# name) bound to stand-ins that hand out device temporaries while a trace is
+# active (the reference types numpy.empty, zeros, ones in
+# numba_mlir/mlir/numpy/funcs.py and allocates them on the device) and are
+# NumPy itself otherwise.
+def _shape_of(shape):
+    if isinstance(shape, (int, np.integer, LazyArray)):
+        shape = (shape,)
+    return tuple(int(d) for d in shape)
+
+
+def _device_empty(shape, dtype=float, order="C", **kwargs):
+    trace = current_trace()
+    if trace is None or kwargs or order != "C" or np.dtype(dtype).name not in _CTYPE:
+        return np.empty(shape, dtype, order, **kwargs)
+    return trace.leaf(trace.add_tmp_slot(_shape_of(shape), np.dtype(dtype)))
+
+
+def _device_filled(np_func, value):
+    def create(shape, *args, **kwargs):
+        trace = current_trace()
+        if value is None:  # np.full(shape, fill_value, dtype=None)
+            fill = args[0] if args else kwargs.pop("fill_value")
+            rest = args[1:]
+            dtype = rest[0] if rest else kwargs.pop("dtype", None)
+            if dtype is None:
+                dtype = scalar_dtype(fill) if isinstance(fill, (bool, int, float, np.generic)) else None
+        else:
+            fill = value
+            dtype = args[0] if args else kwargs.pop("dtype", float)
+            rest = args[1:]
+        if trace is None or kwargs or rest[1:] or dtype is None or np.dtype(dtype).name not in _CTYPE \
+                or not isinstance(fill, (bool, int, float, np.generic, LazyArray)):
+            return np_func(shape, *args, **kwargs)
+        out = trace.leaf(trace.add_tmp_slot(_shape_of(shape), np.dtype(dtype)))
+        out[...] = fill if isinstance(fill, LazyArray) else np.dtype(dtype).type(fill)
+        return out
+
+    create.__name__ = np_func.__name__
+    return create
+
+
+_CREATORS = {np.empty: _device_empty, np.zeros: _device_filled(np.zeros, 0), np.ones: _device_filled(np.ones, 1),
+             np.full: _device_filled(np.full, None)}
+
+
+class _NumpyStandIn:
+    """`numpy` as the traced function sees it: everything is NumPy's except the
+    array creators above."""
+
+    def __getattr__(self, name):
+        value = getattr(np, name)
+        try:
+            return _CREATORS.get(value, value)
+        except TypeError:  # unhashable attribute
+            return value
+
+
+_numpy_stand_in = _NumpyStandIn()
+_rebound = weakref.WeakKeyDictionary()
+
+
+def with_device_creators(func):
+    """`func` with the module-level names that are NumPy (or one of its array
+    creators) rebound to the stand-ins; the function itself when it has none."""
+    import types
+
+    if not isinstance(func, types.FunctionType):
+        return func
+    hit = _rebound.get(func)
+    if hit is not None:
+        return hit
+    changes = {}
+    for name in func.__code__.co_names:
+        value = func.__globals__.get(name)
+        if value is np:
+            changes[name] = _numpy_stand_in
+        else:
+            try:
+                if value in _CREATORS:
+                    changes[name] = _CREATORS[value]
+            except TypeError:
+                pass
+    if not changes:
+        new = func
+    else:
+        scope = dict(func.__globals__)
+        scope.update(changes)
+        new = types.FunctionType(func.__code__, scope, func.__name__, func.__defaults__, func.__closure__)
+        new.__kwdefaults__ = func.__kwdefaults__
+    _rebound[func] = new
+    return new
+
+
 def trace_call(func, args, queue, dry=False, fastmath=False):
     """Runs `func` on symbolic arguments, executing the device work as it is
     recorded (unless `dry`).  Returns (result, plan or None)."""
+    func = with_device_creators(func)
     trace = Trace(queue, args, dry=dry, fastmath=fastmath)
     with _TraceScope(trace):
         sym = []

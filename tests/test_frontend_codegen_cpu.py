@@ -151,6 +151,27 @@ def test_argmin_of_a_chain_along_the_last_axis_is_one_kernel(runtime_lib):
     assert [s[0] for s in trace.steps].count("reduce") == 1 and [s[2] for s in launches] == ["nmb_fused"]
 
 
+def test_arrays_created_inside_a_function_are_device_temporaries(runtime_lib):
+    """np.empty / zeros / ones / full called with a shape inside a traced
+    function (numba_mlir/mlir/numpy/funcs.py types numpy.empty, zeros, ones)
+    give device temporaries, so `out = np.empty(n); out[:] = ...; return out`
+    works and the call is recorded as a replayable plan; outside a trace the
+    same names are NumPy's."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import lazy
+
+    def f(a):
+        out = np.empty(a.shape, a.dtype)
+        out[:] = a + np.float32(1)
+        acc = np.zeros(a.shape[0], np.float32)
+        acc += out
+        return acc * np.ones(a.shape, dtype=np.float32) + np.full(a.shape, 2.5, np.float32)
+
+    trace, plan = nm.njit(f).trace_dry(lazy.fake_array((256,), np.float32))
+    assert plan is not None and [s[0] for s in trace.steps].count("alloc") >= 4
+    assert isinstance(lazy.with_device_creators(f)(np.ones(3, np.float32)), np.ndarray)  # no trace: plain NumPy
+
+
 def test_large_local_arrays_move_to_the_local_memory_parameter(runtime_lib):
     """Local arrays stay static shared memory while the kernel's static total
     fits 48 KB; above that the kernel takes an offset parameter and the launch carries a local-memory

@@ -456,6 +456,31 @@ def test_cov_uses_the_float64_product(queue):
         np.testing.assert_allclose(got, want, rtol=1e-10, atol=1e-12)
 
 
+def test_arrays_created_inside_a_function(queue):
+    """np.empty / zeros / ones / full with a shape inside an njit function are
+    device arrays (numba_mlir/mlir/numpy/funcs.py: numpy.empty, zeros, ones);
+    the function can fill them, return them, and is replayed from its plan."""
+    import numba_mlir_b200 as nm
+
+    def f(a, s):
+        out = np.empty(a.shape, a.dtype)
+        out[:] = a * s
+        acc = np.zeros((a.shape[0], 1), np.float32)
+        acc += out.sum(axis=1).reshape(-1, 1)
+        return out + np.ones(a.shape, dtype=np.float32), acc, np.full(a.shape[1], 3, np.int32)
+
+    g = nm.njit(f)
+    rng = np.random.default_rng(17)
+    for _ in range(3):
+        a = rng.integers(-3, 4, (33, 20)).astype(np.float32)
+        s = np.float32(rng.integers(1, 5))
+        got = g(_dev(a), s)
+        want = f(a, s)
+        for x, y in zip(got, want):
+            assert x.dtype == y.dtype and np.array_equal(x.copy_to_host(), y)
+    assert len(g._plans) == 1
+
+
 def test_dot_and_norm_expansion_distance(queue):
     """np.dot on device arrays reaches the tensor-core gemm (numpy/funcs.py:752-812);
     the distance matrix written with it matches the direct loop to 1e-5."""
