@@ -1086,15 +1086,13 @@ def outer_lazy(trace, a, b):
 
 
 def triangle_lazy(trace, lower, m, k=0):
-    """np.tril / np.triu over the last two axes: a select against row and column
-    numbers (two small index vectors travel to the device with the call)."""
+    """np.tril / np.triu over the last two axes: a select against the element's
+    own row and column numbers."""
     m = _lazy(trace, m)
     if m.ndim < 2:
         raise ValueError("tril and triu need an array of at least two dimensions")
     rows, cols = m.shape[-2], m.shape[-1]
-    i = np.arange(rows, dtype=np.int64).reshape(rows, 1)
-    j = np.arange(cols, dtype=np.int64).reshape(1, cols)
-    diff = apply_ufunc(trace, "subtract", (j, i))                 # column - row
+    diff = _index_array(trace, (1, cols), 1) - _index_array(trace, (rows, 1), 0)   # column - row
     keep = apply_ufunc(trace, "less_equal" if lower else "greater_equal", (diff, np.int64(k)))
     return where(trace, keep, m, m.dtype.type(0))
 
@@ -1372,7 +1370,7 @@ _PACKED_OPS = {"add": ("add2", 2), "subtract": ("sub2", 2), "multiply": ("mul2",
 
 def _second_lane(text):
     """The chain text of element l rewritten for element l + 1."""
-    return re.sub(r"\bt(\d+)\b", r"t\1_b", text).replace(".v[l]", ".v[l + 1]")
+    return re.sub(r"\bt(\d+)\b", r"t\1_b", text).replace(".v[l]", ".v[l + 1]").replace("(r.base + l)", "(r.base + l + 1)")
 
 
 def _paired_lines(em, lines, out_assign, fuse_ok=False):
@@ -1411,6 +1409,7 @@ class _Emitter:
         self.sig = []
         self.packable = {}       # line index -> (packed helper, operand expressions)
         self.scalar_only = set() # names of values read by something that may add to them
+        self.uses_index = False  # some value is the element's own coordinate (needs the flat position)
 
     def leaf(self, node):
         key = node.slot
@@ -1437,6 +1436,18 @@ class _Emitter:
                 self.scalar_args.append((node.value, node.dtype))
             expr = f"s{self.scalar_index[node.value]}"
             self.sig.append(("arg", self.scalar_index[node.value], node.dtype.name))
+        elif node.kind == "index":
+            # the element's own coordinate along one axis, from its flat position
+            axis = node.value + len(self.out_shape) - len(node.shape)
+            extent = self.out_shape[axis]
+            stride = int(np.prod(self.out_shape[axis + 1:], dtype=np.int64))
+            expr = "(r.base + l)"
+            if stride != 1:
+                expr = f"({expr} / {stride}ll)"
+            if axis != 0:
+                expr = f"({expr} % {extent}ll)"
+            self.uses_index = True
+            self.sig.append(("index", axis, stride, extent))
         else:
             ins = [self.emit(i) for i in node.inputs]
             # A packed multiply must not feed an addition: the assembler merges
@@ -1719,6 +1730,9 @@ def _generate(em, results, out_shape, vec, unroll, ostrides, fastmath=False, sha
                     body.append(f"rem /= {out_shape[d]}ll;")
             body.append(f"r.in{i}.v[l] = {ldg}(in{i} + off); }}")
             loads.append(" ".join(body))
+    if em.uses_index:
+        in_fields.append("int64_t base;")  # flat position of the step's first element
+        loads.append("r.base = i;")
     for j, (index, dt) in enumerate(em.scalar_args):
         members.append(f"{ctype(dt)} s{j};")
         kparams.append(f"{ctype(dt)} s{j}")
@@ -2095,7 +2109,49 @@ def _device_filled(np_func, value):
     return create
 
 
-_CREATORS = {np.empty: _device_empty, np.zeros: _device_filled(np.zeros, 0), np.ones: _device_filled(np.ones, 1),
+def _index_array(trace, shape, axis):
+    """int64 array whose elements are their own coordinate along `axis`."""
+    return LazyArray(trace, Node("index", np.int64, shape, value=axis))
+
+
+def _device_arange(*args, dtype=None, **kwargs):
+    """np.arange with host scalars: start + step * (the element's position)."""
+    trace = current_trace()
+    vals = [a.concrete if isinstance(a, LazyArray) and a.concrete is not None else a for a in args]
+    if trace is None or kwargs or not vals or not all(isinstance(v, (int, float, np.integer, np.floating))
+                                                      for v in vals):
+        return np.arange(*args, dtype=dtype, **kwargs)
+    start, stop, step = (0, vals[0], 1) if len(vals) == 1 else (vals[0], vals[1], vals[2] if len(vals) > 2 else 1)
+    out_dt = np.dtype(dtype) if dtype is not None else np.arange(0, 1, 1).dtype if all(
+        isinstance(v, (int, np.integer)) for v in (start, stop, step)) else np.dtype(np.float64)
+    if out_dt.name not in _CTYPE or step == 0:
+        return np.arange(*args, dtype=dtype)
+    n = max(0, int(np.ceil((stop - start) / step)))
+    if any(isinstance(a, LazyArray) for a in args):
+        trace.value_dependent = True  # the length came from an argument's value
+    work = np.dtype(np.int64) if out_dt.kind in "iub" else np.dtype(np.float64)
+    res = _index_array(trace, (n,), 0)
+    if work.kind == "f":
+        res = res.astype(work)
+    if step != 1:
+        res = res * work.type(step)
+    if start != 0:
+        res = res + work.type(start)
+    return res if res.dtype == out_dt else res.astype(out_dt)
+
+
+def _device_eye(N, M=None, k=0, dtype=float, order="C", **kwargs):
+    trace = current_trace()
+    if trace is None or kwargs or order != "C" or np.dtype(dtype).name not in _CTYPE \
+            or not all(isinstance(v, (int, np.integer)) for v in (N, k) + (() if M is None else (M,))):
+        return np.eye(N, M, k, dtype, order, **kwargs)
+    M = N if M is None else M
+    diff = _index_array(trace, (1, int(M)), 1) - _index_array(trace, (int(N), 1), 0)  # column - row
+    dt = np.dtype(dtype)
+    return where(trace, diff == np.int64(k), dt.type(1), dt.type(0))
+
+
+_CREATORS = {np.arange: _device_arange, np.eye: _device_eye, np.empty: _device_empty, np.zeros: _device_filled(np.zeros, 0), np.ones: _device_filled(np.ones, 1),
              np.full: _device_filled(np.full, None)}
 
 

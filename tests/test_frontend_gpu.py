@@ -424,6 +424,12 @@ def test_stacking_flipping_outer_and_triangles(queue):
         (lambda a, b, v, w: np.triu(a, 1) + np.tril(b, -2), None),
         (lambda a, b, v, w: np.tril(a + b, k=2), None),
         (lambda a, b, v, w: a * np.eye(6, 8, dtype=np.float32), None),
+        (lambda a, b, v, w: np.eye(6, 8, 1) + a, None),
+        (lambda a, b, v, w: v + np.arange(8, dtype=np.float32), None),
+        (lambda a, b, v, w: np.arange(3, 19, 2) * v.astype(np.int64), None),
+        (lambda a, b, v, w: np.arange(0.0, 0.8, 0.1) + v, None),
+        (lambda a, b, v, w: a + np.arange(8).astype(np.float32), None),  # (float32 + int64 is float32 under Numba's typing)
+        (lambda a, b, v, w: (np.arange(6).reshape(6, 1) * 10 + np.arange(8)) * (a > 0), None),
     ]
     for fn, _ in cases:
         got = nm.njit(fn)(_dev(a), _dev(b), _dev(v), _dev(w)).copy_to_host()
