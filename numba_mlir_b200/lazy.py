@@ -2151,7 +2151,36 @@ def _device_eye(N, M=None, k=0, dtype=float, order="C", **kwargs):
     return where(trace, diff == np.int64(k), dt.type(1), dt.type(0))
 
 
-_CREATORS = {np.arange: _device_arange, np.eye: _device_eye, np.empty: _device_empty, np.zeros: _device_filled(np.zeros, 0), np.ones: _device_filled(np.ones, 1),
+def _device_layout(np_func, fortran):
+    """np.asarray / ascontiguousarray / asfortranarray of a traced array: NumPy
+    converts the argument before any protocol could see it, so they are
+    routed here.  Column-major order is a transposed view of a C-ordered copy
+    of the transpose."""
+    def convert(a, dtype=None, **kwargs):
+        trace = current_trace()
+        if trace is None or not isinstance(a, LazyArray) or kwargs:
+            return np_func(a, dtype, **kwargs)
+        if dtype is not None and np.dtype(dtype) != a.dtype:
+            a = a.astype(dtype)
+        if np_func is np.asarray:
+            return a
+        if not fortran or a.ndim < 2:
+            if a.node.kind != "leaf":
+                return a
+            arr = trace.arrays[a.node.slot]
+            return a if arr.is_c_contiguous else a.copy()
+        t = trace.leaf(trace.add_tmp_slot(a.shape[::-1], a.dtype))
+        t[...] = (a if a.node.kind == "leaf" else trace.leaf(trace.materialize(a))).T
+        return t.T
+
+    convert.__name__ = np_func.__name__
+    return convert
+
+
+_CREATORS = {np.asarray: _device_layout(np.asarray, False),
+             np.ascontiguousarray: _device_layout(np.ascontiguousarray, False),
+             np.asfortranarray: _device_layout(np.asfortranarray, True),
+             np.arange: _device_arange, np.eye: _device_eye, np.empty: _device_empty, np.zeros: _device_filled(np.zeros, 0), np.ones: _device_filled(np.ones, 1),
              np.full: _device_filled(np.full, None)}
 
 

@@ -487,6 +487,24 @@ def test_arrays_created_inside_a_function(queue):
     assert len(g._plans) == 1
 
 
+def test_layout_conversions_inside_a_function(queue):
+    """np.asfortranarray (numba_mlir/mlir/numpy/funcs.py: numpy.asfortranarray),
+    np.ascontiguousarray and np.asarray of traced arrays: same values, the
+    requested order."""
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(23)
+    a = rng.standard_normal((6, 8)).astype(np.float32)
+    f = nm.njit(lambda x: np.asfortranarray(x))(_dev(a))
+    assert f.shape == (6, 8) and f.strides == (4, 24)
+    np.testing.assert_array_equal(f.copy_to_host(), a)
+    g = nm.njit(lambda x: np.ascontiguousarray(x.T) + np.float32(1))(_dev(a))
+    assert g.shape == (8, 6) and g.is_c_contiguous
+    np.testing.assert_array_equal(g.copy_to_host(), a.T + np.float32(1))
+    h = nm.njit(lambda x: np.asarray(x) * np.asfortranarray(x + np.float32(2)))(_dev(a))
+    np.testing.assert_array_equal(h.copy_to_host(), a * (a + np.float32(2)))
+
+
 def test_dot_and_norm_expansion_distance(queue):
     """np.dot on device arrays reaches the tensor-core gemm (numpy/funcs.py:752-812);
     the distance matrix written with it matches the direct loop to 1e-5."""
