@@ -2202,7 +2202,9 @@ _rebound = weakref.WeakKeyDictionary()
 
 def with_device_creators(func):
     """`func` with the module-level names that are NumPy (or one of its array
-    creators) rebound to the stand-ins; the function itself when it has none."""
+    creators) rebound to the stand-ins; the function itself when it has none.
+    The copy sees the module's other names as they are when it is first made
+    (Numba likewise freezes globals when it compiles)."""
     import types
 
     if not isinstance(func, types.FunctionType):
