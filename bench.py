@@ -70,7 +70,7 @@ NCU_TRAFFIC_BYTES = {
     "black_scholes": 201362432 + 90091008,   # output partly still dirty in L2 at kernel end
     "bcast_add": 16797184 + 0,               # two-launch capture: the result stays in L2
     "sum_axis1": 268446208 + 3861760,        # the few MB of writes are evictions of the previous launch's lines
-    "min_axis0": 268518144 + 4005632,
+    "min_axis0": 268525568 + 3505408,
     "argmin_axis1": 268448000 + 4131840,
     "row_norm": 268450048 + 5443072,
     "int_sum": 1073772000 + 4045312,
