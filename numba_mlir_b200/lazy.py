@@ -663,6 +663,27 @@ class LazyArray:
     def size(self):
         return int(np.prod(self.node.shape, dtype=np.int64))
 
+    @property
+    def itemsize(self):
+        return self.node.dtype.itemsize
+
+    @property
+    def nbytes(self):
+        return self.size * self.node.dtype.itemsize
+
+    @property
+    def strides(self):
+        """Byte strides (array.strides, numba_mlir/mlir/numpy/funcs.py): those
+        of the device array for an argument or a view, C order for a value that
+        is still an expression, which is how it is written out."""
+        if self.node.kind == "leaf":
+            return tuple(self.trace.arrays[self.node.slot].strides)
+        out, step = [], self.node.dtype.itemsize
+        for d in reversed(self.node.shape):
+            out.append(step)
+            step *= max(d, 1)
+        return tuple(reversed(out))
+
     def __len__(self):
         return self.node.shape[0]
 

@@ -505,6 +505,23 @@ def test_layout_conversions_inside_a_function(queue):
     np.testing.assert_array_equal(h.copy_to_host(), a * (a + np.float32(2)))
 
 
+def test_array_attributes_inside_a_function(queue):
+    """array.size / itemsize / strides / shape / T / dtype and len() of traced
+    arrays (the attributes numba_mlir/mlir/numpy/funcs.py registers) are the
+    ones NumPy reports, for arguments, views and unevaluated expressions."""
+    import numba_mlir_b200 as nm
+
+    def f(a):
+        v = a[1:, ::2]
+        e = a + a
+        return (a * np.float32(a.size + a.itemsize + a.strides[0] + len(a))
+                + np.float32(v.strides[0] + v.strides[1] + v.size + e.strides[0] + e.T.shape[0] + e.nbytes))
+
+    a = np.arange(48, dtype=np.float32).reshape(6, 8)
+    got = nm.njit(f)(_dev(a))
+    np.testing.assert_array_equal(got.copy_to_host(), f(a))
+
+
 def test_dot_and_norm_expansion_distance(queue):
     """np.dot on device arrays reaches the tensor-core gemm (numpy/funcs.py:752-812);
     the distance matrix written with it matches the direct loop to 1e-5."""
