@@ -338,6 +338,38 @@ def test_paired_float32_arithmetic_is_bit_identical_to_numpy(queue, n):
     assert not residual(_dev(a), _dev(b), _dev(ab)).copy_to_host().any()
 
 
+def test_chains_with_division_and_square_root_match_numpy_bit_for_bit(queue):
+    """Quotients, square roots and 1/sqrt of ordinary, tiny, huge, zero,
+    subnormal, infinite, negative and NaN operands are the IEEE-rounded values
+    NumPy computes, in the aligned (paired) and the unaligned (one element at a
+    time) forms of the chain."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import from_host
+
+    rng = np.random.default_rng(5)
+    n = 1 << 16
+    a = (rng.standard_normal(n) * 10.0 ** rng.integers(-30, 30, n)).astype(np.float32)
+    b = (rng.standard_normal(n) * 10.0 ** rng.integers(-30, 30, n)).astype(np.float32)
+    special = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e-42, -1e-42, 3.4028235e38, 1.1754944e-38,
+                        1.0, -1.0, 3.0, 2.0 ** -60, 2.0 ** 60, 2.0 ** -61, 2.0 ** 61, 2.0 ** 100, 2.0 ** -100,
+                        2.0 ** 101, 2.0 ** -101], np.float32)
+    k = special.size
+    a[: k * k] = np.repeat(special, k)
+    b[: k * k] = np.tile(special, k)
+    # an in-range value next to each special one, and the other way round
+    a[k * k: 2 * k * k: 2] = np.float32(1.5)
+    f = nm.njit(lambda x, y: (x / y, np.sqrt(np.abs(x)), np.float32(1) / np.sqrt(np.abs(y)), np.float32(1) / x))
+    with np.errstate(all="ignore"):
+        want = (a / b, np.sqrt(np.abs(a)), np.float32(1) / np.sqrt(np.abs(b)), np.float32(1) / a)
+        got = f(from_host(a), from_host(b))
+        for g, w in zip(got, want):
+            np.testing.assert_array_equal(g.copy_to_host(), w)
+        pa = from_host(np.concatenate([np.zeros(1, np.float32), a]))[1:]
+        pb = from_host(np.concatenate([np.zeros(1, np.float32), b]))[1:]
+        for g, w in zip(f(pa, pb), want):
+            np.testing.assert_array_equal(g.copy_to_host(), w)
+
+
 def test_log_float32_within_1ulp_and_pair_forms_equal_scalar_forms(queue):
     """The library's own float32 log: every float32 of three binades around 1
     at stride 5, a logarithmic sweep over the whole range, subnormals and the
