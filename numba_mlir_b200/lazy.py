@@ -689,12 +689,22 @@ class LazyArray:
 
     # numpy protocols -------------------------------------------------------------
     def __array_ufunc__(self, ufunc, method, *inputs, **kwargs):
-        if method != "__call__" or kwargs.get("out") is not None:
+        out = kwargs.pop("out", None)
+        if method != "__call__" or kwargs:
             return NotImplemented
         name = _UFUNC_BY_OBJ.get(ufunc)
         if name is None:
             raise TypeError(f"numpy.{ufunc.__name__} is not supported on device arrays")
-        return apply_ufunc(self.trace, name, inputs)
+        res = apply_ufunc(self.trace, name, inputs)
+        if out is None:
+            return res
+        # np.add(a, b, c) / out=c: the value is stored into c, converted to its
+        # type (numba_mlir/mlir/tests/test_numpy.py: test_binary_inplace)
+        (target,) = out if isinstance(out, tuple) else (out,)
+        if not isinstance(target, LazyArray):
+            raise TypeError("out= must be a device array")
+        target[...] = res
+        return target
 
     def __array_function__(self, func, types, args, kwargs):
         if func in REDUCTIONS:
@@ -737,6 +747,11 @@ class LazyArray:
             return out
         if func is np.shape:
             return self.shape
+        if func is np.atleast_2d and len(args) == 1 and not kwargs:
+            a = args[0]
+            if a.ndim >= 2:
+                return a
+            return a.reshape((1, a.shape[0]) if a.ndim else (1, 1))
         if func in _STACKS:
             return stack_lazy(self.trace, _STACKS[func], *args, **kwargs)
         if func is np.flip:
@@ -1143,9 +1158,8 @@ def cov_lazy(trace, m, y=None, rowvar=True, bias=False, ddof=None, fweights=None
 
 
 def clip_lazy(trace, a, a_min=None, a_max=None, out=None):
-    """np.clip: bounds are converted to the array's type, as Numba types it."""
-    if out is not None:
-        raise TypeError("out= is not supported on device arrays")
+    """np.clip: bounds are converted to the array's type, as Numba types it;
+    with `out` the result is stored there (test_numpy.py: test_ternary_inplace)."""
     if not isinstance(a, LazyArray):
         a = LazyArray(trace, _as_node(trace, a))
 
@@ -1157,6 +1171,11 @@ def clip_lazy(trace, a, a_min=None, a_max=None, out=None):
         res = apply_ufunc(trace, "maximum", (res, bound(a_min)))
     if a_max is not None:
         res = apply_ufunc(trace, "minimum", (res, bound(a_max)))
+    if out is not None:
+        if not isinstance(out, LazyArray):
+            raise TypeError("out= must be a device array")
+        out[...] = res
+        return out
     return res
 
 

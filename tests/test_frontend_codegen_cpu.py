@@ -139,6 +139,18 @@ def test_array_building_functions_trace_and_compile(runtime_lib):
         assert launches
 
 
+def test_out_arguments_store_into_the_given_array(runtime_lib):
+    """np.add(a, b, c) and np.clip(a, lo, hi, out=c) are one kernel each that
+    writes c; no temporary is allocated."""
+    shapes = [((6, 8), np.float32)] * 3
+    for fn in (lambda a, b, c: np.add(a, b, c),
+               lambda a, b, c: np.multiply(a, b, out=c),
+               lambda a, b, c: np.clip(a, np.float32(0), np.float32(1), c),
+               lambda a, b, c: np.clip(a, b, b + 1, out=c)):
+        trace, launches = _trace_and_compile(fn, shapes)
+        assert len(launches) == 1 and not [s for s in trace.steps if s[0] == "alloc"]
+
+
 def test_argmin_of_a_chain_along_the_last_axis_is_one_kernel(runtime_lib):
     """np.argmin / np.argmax of an elementwise chain along the last axis is
     one generated kernel (a warp per row keeps value and position); along

@@ -554,6 +554,36 @@ def test_array_attributes_inside_a_function(queue):
     np.testing.assert_array_equal(got.copy_to_host(), f(a))
 
 
+def test_out_arguments_and_atleast_2d(queue):
+    """np.add(a, b, c), np.true_divide(a, b, out=c), np.clip(a, lo, hi, out)
+    store into the given array, converted to its type, and return it
+    (numba_mlir/mlir/tests/test_numpy.py: test_binary_inplace,
+    test_ternary_inplace); np.atleast_2d gives the (1, n) view."""
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(31)
+    a = rng.standard_normal((5, 8)).astype(np.float32)
+    b = rng.standard_normal(8).astype(np.float32) + np.float32(3)
+
+    def f(a, b, c, d, e):
+        r = np.add(a, b, c)
+        np.true_divide(a, b, out=d)
+        np.clip(a, np.float32(-0.5), np.float32(0.5), e)
+        np.maximum(r, d, out=r)
+        return np.atleast_2d(b) * np.float32(2), np.atleast_2d(a)
+
+    outs = [np.zeros((5, 8), np.float64), np.zeros((5, 8), np.float32), np.zeros((5, 8), np.float32)]
+    want_outs = [o.copy() for o in outs]
+    want = f(a, b, *want_outs)
+    dev = [_dev(o) for o in outs]
+    got = nm.njit(f)(_dev(a), _dev(b), *dev)
+    for g, w in zip(dev, want_outs):
+        np.testing.assert_array_equal(g.copy_to_host(), w)
+    for g, w in zip(got, want):
+        assert g.shape == w.shape
+        np.testing.assert_array_equal(g.copy_to_host(), w)
+
+
 def test_dot_and_norm_expansion_distance(queue):
     """np.dot on device arrays reaches the tensor-core gemm (numpy/funcs.py:752-812);
     the distance matrix written with it matches the direct loop to 1e-5."""
