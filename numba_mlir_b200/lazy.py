@@ -922,6 +922,8 @@ class LazyArray:
             dims = iter(self.shape)
             shape = [1 if i is None else next(dims) for i in idx] + list(dims)
             return self.reshape(shape)
+        if isinstance(idx, LazyArray):
+            return gather_lazy(self.trace, self, idx)
         return self._view(("getitem", idx), lambda a: a[idx])
 
     def __setitem__(self, idx, value):
@@ -1106,6 +1108,62 @@ def stack_lazy(trace, kind, tup, dtype=None, casting=None):
         return concatenate_lazy(trace, [at_least(x, 3) for x in parts], axis=2, dtype=dtype)
     parts = [at_least(x, 1) for x in parts]
     return concatenate_lazy(trace, parts, axis=0 if parts[0].ndim == 1 else 1, dtype=dtype)
+
+
+_GATHER_SOURCE = """//NMB200:CUDA-SOURCE
+#include "nmb_device.cuh"
+extern "C" __global__ void __launch_bounds__(256) nmb_gather(
+    const {T}* __restrict__ src, const {I}* __restrict__ idx, {T}* __restrict__ out,
+    int64_t n, int64_t extent, int64_t row_stride, int64_t inner) {{
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += step) {{
+    const int64_t i = e / inner, j = e - i * inner;
+    int64_t k = (int64_t)idx[i];
+    k = k < 0 ? k + extent : k;
+    k = k < 0 ? 0 : (k >= extent ? extent - 1 : k);  // stays inside the array whatever the index holds
+    out[e] = src[k * row_stride + j];
+  }}
+}}
+"""
+
+
+def gather_lazy(trace, a, idx):
+    """a[idx] with an integer index array (numba_mlir/mlir/tests/test_numpy.py:
+    test_getitem_offset): element i of the result is a[idx[i]] (a row of `a`
+    when it has more dimensions); negative indices count from the end.  An
+    index outside the array, for which NumPy raises, reads the nearest valid
+    element: a kernel cannot raise, and it must not read outside the array."""
+    if idx.dtype.kind not in "iu":
+        raise TypeError("indexing with a mask is not supported on device arrays: the size of the result "
+                        "depends on device data")
+    if a.ndim == 0:
+        raise IndexError("too many indices for a 0-dimensional array")
+    if a.shape[0] == 0:
+        raise IndexError("index array into an empty array")
+    a_slot = trace.materialize(a)
+    if a.ndim > 1 and not trace.arrays[a_slot].is_c_contiguous:
+        a_slot = trace.materialize(a.copy())
+    i_slot = trace.materialize(idx)
+    if not trace.arrays[i_slot].is_c_contiguous:
+        i_slot = trace.materialize(idx.copy())
+    src, ind = trace.arrays[a_slot], trace.arrays[i_slot]
+    inner = int(np.prod(src.shape[1:], dtype=np.int64))
+    row_stride = src.strides[0] // src.dtype.itemsize if src.ndim == 1 else inner
+    out_slot = trace.add_tmp_slot(tuple(ind.shape) + tuple(src.shape[1:]), src.dtype)
+    n = int(np.prod(ind.shape, dtype=np.int64)) * inner
+    if n:
+        key = ("gather", src.dtype.name, ind.dtype.name)
+        blob = _kernel_cache.get(key)
+        if blob is None:
+            blob = _kernel_cache[key] = _GATHER_SOURCE.format(T=ctype(src.dtype), I=ctype(ind.dtype)).encode()
+        grid = min((n + 255) // 256, 148 * 8)
+        step = ("launch", blob, "nmb_gather", (grid,), (256,),
+                (("slot", a_slot), ("slot", i_slot), ("slot", out_slot), ("i64", n), ("i64", src.shape[0]),
+                 ("i64", row_stride), ("i64", inner)))
+        trace.steps.append(step)
+        if not trace.dry:
+            run_launch(trace.queue, step, trace.arrays, trace.args)
+    return trace.leaf(out_slot)
 
 
 def flip_lazy(trace, m, axis=None):

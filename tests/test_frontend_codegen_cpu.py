@@ -151,6 +151,18 @@ def test_out_arguments_store_into_the_given_array(runtime_lib):
         assert len(launches) == 1 and not [s for s in trace.steps if s[0] == "alloc"]
 
 
+def test_index_arrays_become_a_gather_launch(runtime_lib):
+    """a[m] with an integer array is one gather launch into a temporary of
+    m's shape (plus a's trailing dimensions); views that the kernel cannot
+    address directly are copied first."""
+    trace, launches = _trace_and_compile(lambda a, m: a[m], [((16,), np.float32), ((3,), np.int32)])
+    assert [s[2] for s in launches] == ["nmb_gather"]
+    trace, launches = _trace_and_compile(lambda a, m: a[m] * 2, [((16, 4), np.float64), ((2, 3), np.int64)])
+    assert [s[2] for s in launches] == ["nmb_gather", "nmb_fused"]
+    trace, launches = _trace_and_compile(lambda a, m: a.T[m[::-1]], [((16, 4), np.float32), ((3,), np.int32)])
+    assert [s[2] for s in launches].count("nmb_gather") == 1 and len(launches) == 3
+
+
 def test_argmin_of_a_chain_along_the_last_axis_is_one_kernel(runtime_lib):
     """np.argmin / np.argmax of an elementwise chain along the last axis is
     one generated kernel (a warp per row keeps value and position); along

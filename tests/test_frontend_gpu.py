@@ -584,6 +584,35 @@ def test_out_arguments_and_atleast_2d(queue):
         np.testing.assert_array_equal(g.copy_to_host(), w)
 
 
+@pytest.mark.parametrize("offset", [[], [0], [1, 2, 3], [3, 2, 1], [-1, 0, -4, 2]])
+def test_indexing_with_an_index_array(queue, offset):
+    """a[m] with an integer array m (numba_mlir/mlir/tests/test_numpy.py:
+    test_getitem_offset), on arrays, views and expressions, for one- and
+    two-dimensional sources; negative indices count from the end."""
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(len(offset))
+    a = rng.standard_normal(9).astype(np.float32)
+    b = rng.integers(-9, 9, (4, 6)).astype(np.int64)
+    for dt in (np.int32, np.int64):
+        m = np.array(offset, dt)
+        for fn, args in ((lambda a, m: a[m], (a, m)),
+                         (lambda a, m: a[::2][m] + (a * 2)[m], (a, m)),
+                         (lambda a, m: a[::-1][m], (a, m)),
+                         (lambda b, m: b[m], (b, m)),
+                         (lambda b, m: b.T[m] + 1, (b, m))):
+            got = nm.njit(fn)(*[_dev(x) for x in args])
+            want = fn(*args)
+            assert got.shape == want.shape and got.dtype == want.dtype
+            np.testing.assert_array_equal(got.copy_to_host(), want)
+    if offset:
+        m2 = np.array([offset, offset[::-1]], np.int32)
+        got = nm.njit(lambda a, m: a[m])(_dev(a), _dev(m2))
+        np.testing.assert_array_equal(got.copy_to_host(), a[m2])
+    with pytest.raises(TypeError, match="mask"):
+        nm.njit(lambda a, m: a[m])(_dev(a), _dev(a > 0))
+
+
 def test_dot_and_norm_expansion_distance(queue):
     """np.dot on device arrays reaches the tensor-core gemm (numpy/funcs.py:752-812);
     the distance matrix written with it matches the direct loop to 1e-5."""
