@@ -1133,9 +1133,10 @@ def gather_lazy(trace, a, idx):
     when it has more dimensions); negative indices count from the end.  An
     index outside the array, for which NumPy raises, reads the nearest valid
     element: a kernel cannot raise, and it must not read outside the array."""
+    if idx.dtype.kind == "b":
+        return select_lazy(trace, a, idx)
     if idx.dtype.kind not in "iu":
-        raise TypeError("indexing with a mask is not supported on device arrays: the size of the result "
-                        "depends on device data")
+        raise TypeError("an index array must hold integers or booleans")
     if a.ndim == 0:
         raise IndexError("too many indices for a 0-dimensional array")
     if a.shape[0] == 0:
@@ -1163,6 +1164,117 @@ def gather_lazy(trace, a, idx):
         trace.steps.append(step)
         if not trace.dry:
             run_launch(trace.queue, step, trace.arrays, trace.args)
+    return trace.leaf(out_slot)
+
+
+_SELECT_SOURCE = """//NMB200:CUDA-SOURCE
+#include "nmb_device.cuh"
+// Order-preserving selection out[k] = src[i] for the k-th set mask[i]: counts
+// per block of 2048 elements, one block turns the counts into offsets (and the
+// total), then every block writes its elements from its offset on.
+__device__ __forceinline__ int tile_count(const unsigned char* __restrict__ mask, int64_t n, int64_t base) {{
+  int c = 0;
+#pragma unroll
+  for (int l = 0; l < 8; ++l) c += (base + l < n) && mask[base + l] != 0;
+  return c;
+}}
+// exclusive prefix of `v` over the 256 threads of the block; `total` = the block's sum
+__device__ __forceinline__ int block_prefix(int v, int& total) {{
+  __shared__ int warp_sums[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {{
+    const int t = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += t;
+  }}
+  if (lane == 31) warp_sums[warp] = inc;
+  __syncthreads();
+  int before = 0, all = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {{
+    before += w < warp ? warp_sums[w] : 0;
+    all += warp_sums[w];
+  }}
+  __syncthreads();
+  total = all;
+  return before + inc - v;
+}}
+extern "C" __global__ void __launch_bounds__(256) nmb_select_count(
+    const unsigned char* __restrict__ mask, int64_t n, int64_t* __restrict__ offsets) {{
+  int total;
+  block_prefix(tile_count(mask, n, ((int64_t)blockIdx.x * 256 + threadIdx.x) * 8), total);
+  if (threadIdx.x == 0) offsets[blockIdx.x] = total;
+}}
+// offsets[b] <- sum of offsets[0..b); offsets[blocks] <- the total
+extern "C" __global__ void __launch_bounds__(256) nmb_select_offsets(int64_t* __restrict__ offsets, int64_t blocks) {{
+  __shared__ int64_t carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int64_t start = 0; start < blocks; start += 256) {{
+    const int64_t b = start + threadIdx.x;
+    const int v = b < blocks ? (int)offsets[b] : 0;  // a block holds at most 2048
+    int total;
+    const int before = block_prefix(v, total);
+    if (b < blocks) offsets[b] = carry + before;
+    __syncthreads();
+    if (threadIdx.x == 0) carry += total;
+    __syncthreads();
+  }}
+  if (threadIdx.x == 0) offsets[blocks] = carry;
+}}
+extern "C" __global__ void __launch_bounds__(256) nmb_select_write(
+    const {T}* __restrict__ src, const unsigned char* __restrict__ mask, {T}* __restrict__ out, int64_t n,
+    const int64_t* __restrict__ offsets) {{
+  const int64_t base = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 8;
+  int total;
+  int64_t k = offsets[blockIdx.x] + block_prefix(tile_count(mask, n, base), total);
+#pragma unroll
+  for (int l = 0; l < 8; ++l)
+    if (base + l < n && mask[base + l] != 0) out[k++] = src[base + l];
+}}
+"""
+
+
+def select_lazy(trace, a, mask):
+    """a[mask] with a boolean array of a's shape (numba_mlir/mlir/tests/
+    test_numpy.py: test_getitem_mask): the selected elements in C order.  The
+    size of the result is read back from the device, so the call is traced
+    afresh every time instead of being replayed from a recorded plan."""
+    if tuple(mask.shape) != tuple(a.shape):
+        raise IndexError(f"boolean index of shape {tuple(mask.shape)} does not match the array's {tuple(a.shape)}")
+    if trace.dry:
+        raise TypeError("the size of a[mask] is not available while tracing without a device")
+    slots = []
+    for x in (a, mask):
+        slot = trace.materialize(x)
+        if not trace.arrays[slot].is_c_contiguous:
+            slot = trace.materialize(x.copy())
+        slots.append(slot)
+    a_slot, m_slot = slots
+    n = a.size
+    trace.value_dependent = True
+    if n == 0:
+        return trace.leaf(trace.add_tmp_slot((0,), a.dtype))
+    key = ("select", a.dtype.name)
+    blob = _kernel_cache.get(key)
+    if blob is None:
+        blob = _kernel_cache[key] = _SELECT_SOURCE.format(T=ctype(a.dtype)).encode()
+    blocks = (n + 2047) // 2048
+    off_slot = trace.add_tmp_slot((blocks + 1,), np.int64)
+
+    def launch(name, grid, params):
+        step = ("launch", blob, name, (grid,), (256,), params)
+        trace.steps.append(step)
+        run_launch(trace.queue, step, trace.arrays, trace.args)
+
+    launch("nmb_select_count", blocks, (("slot", m_slot), ("i64", n), ("slot", off_slot)))
+    launch("nmb_select_offsets", 1, (("slot", off_slot), ("i64", blocks)))
+    count = int(trace.arrays[off_slot][blocks:].copy_to_host()[0])
+    out_slot = trace.add_tmp_slot((count,), a.dtype)
+    if count:
+        launch("nmb_select_write", blocks, (("slot", a_slot), ("slot", m_slot), ("slot", out_slot), ("i64", n),
+                                            ("slot", off_slot)))
     return trace.leaf(out_slot)
 
 

@@ -609,8 +609,32 @@ def test_indexing_with_an_index_array(queue, offset):
         m2 = np.array([offset, offset[::-1]], np.int32)
         got = nm.njit(lambda a, m: a[m])(_dev(a), _dev(m2))
         np.testing.assert_array_equal(got.copy_to_host(), a[m2])
-    with pytest.raises(TypeError, match="mask"):
-        nm.njit(lambda a, m: a[m])(_dev(a), _dev(a > 0))
+
+
+@pytest.mark.parametrize("pattern", [[True], [False], [True, False], [False, True]])
+def test_indexing_with_a_mask(queue, pattern):
+    """a[m] with a boolean array of a's shape (numba_mlir/mlir/tests/
+    test_numpy.py: test_getitem_mask): the selected elements in order, for
+    sizes of one block, many blocks and more blocks than one scan step holds;
+    masks computed inside the function; two-dimensional arrays."""
+    import numba_mlir_b200 as nm
+
+    f = nm.njit(lambda a, m: a[m])
+    rng = np.random.default_rng(3)
+    for n in (1, 7, 2048, 100003, 1300003):
+        a = rng.standard_normal(n).astype(np.float32)
+        m = np.resize(pattern, n)
+        got = f(_dev(a), _dev(m))
+        assert got.shape == a[m].shape
+        np.testing.assert_array_equal(got.copy_to_host(), a[m])
+    a = rng.standard_normal(300001)
+    got = nm.njit(lambda a: a[a > 0.5] * 2)(_dev(a))
+    np.testing.assert_array_equal(got.copy_to_host(), a[a > 0.5] * 2)
+    b = rng.integers(-5, 5, (37, 53)).astype(np.int32)
+    got = nm.njit(lambda b: b.T[b.T > 0])(_dev(b))
+    np.testing.assert_array_equal(got.copy_to_host(), b.T[b.T > 0])
+    empty = f(_dev(np.zeros(0, np.float32)), _dev(np.zeros(0, np.bool_)))
+    assert empty.shape == (0,)
 
 
 def test_dot_and_norm_expansion_distance(queue):
