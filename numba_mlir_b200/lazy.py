@@ -922,12 +922,15 @@ class LazyArray:
             dims = iter(self.shape)
             shape = [1 if i is None else next(dims) for i in idx] + list(dims)
             return self.reshape(shape)
-        if isinstance(idx, LazyArray):
-            return gather_lazy(self.trace, self, idx)
+        if isinstance(idx, LazyArray) and (idx.ndim > 0 or idx.concrete is None):
+            return gather_lazy(self.trace, self, idx)  # an index array, or a position computed on the device
         return self._view(("getitem", idx), lambda a: a[idx])
 
     def __setitem__(self, idx, value):
-        target = self if (idx is Ellipsis or idx == slice(None)) else self[idx]
+        whole = idx is Ellipsis or (isinstance(idx, slice) and idx == slice(None))
+        if isinstance(idx, LazyArray) and (idx.ndim > 0 or idx.concrete is None):
+            raise TypeError("assignment through an index array or a mask is not supported on device arrays")
+        target = self if whole else self[idx]
         if target.node.kind != "leaf":
             raise TypeError("cannot assign into an expression")
         vnode = _as_node(self.trace, value)

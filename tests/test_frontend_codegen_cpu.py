@@ -163,6 +163,33 @@ def test_index_arrays_become_a_gather_launch(runtime_lib):
     assert [s[2] for s in launches].count("nmb_gather") == 1 and len(launches) == 3
 
 
+def test_scalar_arguments_as_indices(runtime_lib):
+    """a[b] = 42; return a[b] with b a scalar argument (numba_mlir/mlir/tests/
+    test_numpy.py: test_setitem1, test_setitem2): views at the argument's
+    value, one store; assignment through an index array is refused."""
+    import numba_mlir_b200 as nm
+    from numba_mlir_b200 import lazy
+
+    def f(a, b):
+        a[b] = 42
+        return a[b]
+
+    def g(a, b, c):
+        a[b, c] = 42
+        return a[b, c]
+
+    for fn, args in ((f, [lazy.fake_array((3,), np.int64), -2]),
+                     (g, [lazy.fake_array((2, 3), np.int64), 1, 2])):
+        trace, _plan = nm.njit(fn).trace_dry(*args)
+        assert [s[0] for s in trace.steps] == ["launch"]
+
+    def scatter(a, m):
+        a[m] = 1
+
+    with pytest.raises(TypeError, match="index array"):
+        nm.njit(scatter).trace_dry(lazy.fake_array((8,), np.float32), lazy.fake_array((3,), np.int32))
+
+
 def test_argmin_of_a_chain_along_the_last_axis_is_one_kernel(runtime_lib):
     """np.argmin / np.argmax of an elementwise chain along the last axis is
     one generated kernel (a warp per row keeps value and position); along

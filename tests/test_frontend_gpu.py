@@ -16,6 +16,11 @@ def _dev(a):
     return from_host(a)
 
 
+def _host(x):
+    """Host value of a result that may be a device array or already a scalar."""
+    return x.copy_to_host() if hasattr(x, "copy_to_host") else x
+
+
 def test_config1_broadcast_add_through_njit(queue):
     import numba_mlir_b200 as nm
     from oracle import configs as O
@@ -609,6 +614,37 @@ def test_indexing_with_an_index_array(queue, offset):
         m2 = np.array([offset, offset[::-1]], np.int32)
         got = nm.njit(lambda a, m: a[m])(_dev(a), _dev(m2))
         np.testing.assert_array_equal(got.copy_to_host(), a[m2])
+
+
+@pytest.mark.parametrize("i", list(range(-2, 3)))
+def test_scalar_arguments_and_computed_positions_as_indices(queue, i):
+    """a[b] = 42; return a[b] with a scalar argument b (numba_mlir/mlir/tests/
+    test_numpy.py: test_setitem1, test_setitem2), and a position computed on
+    the device (a[np.argmax(a)]) as an index."""
+    import numba_mlir_b200 as nm
+
+    def f(a, b):
+        a[b] = 42
+        return a[b]
+
+    def g(a, b, c):
+        a[b, c] = 42
+        return a[b, c]
+
+    arr = np.asarray([1, 2, 3])
+    d = _dev(arr.copy())
+    host = arr.copy()
+    assert int(np.asarray(_host(nm.njit(f)(d, i)))) == f(host, i)
+    np.testing.assert_array_equal(d.copy_to_host(), host)
+    arr2 = np.asarray([[1, 2, 3], [4, 5, 6]])
+    d2 = _dev(arr2.copy())
+    host2 = arr2.copy()
+    assert int(np.asarray(_host(nm.njit(g)(d2, 1, i)))) == g(host2, 1, i)
+    np.testing.assert_array_equal(d2.copy_to_host(), host2)
+    rng = np.random.default_rng(i + 2)
+    x = rng.standard_normal(1000).astype(np.float32)
+    got = nm.njit(lambda a: a[np.argmax(a)] - a[np.argmin(a)])(_dev(x))
+    assert np.float32(np.asarray(_host(got))) == x[np.argmax(x)] - x[np.argmin(x)]
 
 
 @pytest.mark.parametrize("pattern", [[True], [False], [True, False], [False, True]])
