@@ -612,8 +612,13 @@ def test_indexing_with_an_index_array(queue, offset):
             np.testing.assert_array_equal(got.copy_to_host(), want)
     if offset:
         m2 = np.array([offset, offset[::-1]], np.int32)
-        got = nm.njit(lambda a, m: a[m])(_dev(a), _dev(m2))
+        take = nm.njit(lambda a, m: a[m])
+        got = take(_dev(a), _dev(m2))
         np.testing.assert_array_equal(got.copy_to_host(), a[m2])
+        # the second call replays the recorded plan on new data
+        a2, m3 = a[::-1].copy(), (m2 * 0 + 1).astype(np.int32)
+        np.testing.assert_array_equal(take(_dev(a2), _dev(m3)).copy_to_host(), a2[m3])
+        assert len(take._plans) == 1
 
 
 @pytest.mark.parametrize("i", list(range(-2, 3)))
