@@ -190,6 +190,73 @@ def test_scalar_arguments_as_indices(runtime_lib):
         nm.njit(scatter).trace_dry(lazy.fake_array((8,), np.float32), lazy.fake_array((3,), np.int32))
 
 
+def _batchnorm(x, eps=1e-5):
+    mean = np.empty(x.shape, dtype=x.dtype)
+    mean[:] = np.sum(x, axis=0) / x.shape[0]
+    std = np.empty(x.shape, dtype=x.dtype)
+    std[:] = np.sqrt(np.sum((x - mean) ** 2, axis=0) / x.shape[0])
+    return (x - mean) / np.sqrt(std + eps)
+
+
+def _write_through_a_view(a, b):
+    e = b[1:]
+    c = a + b
+    e[:] = c[1:]
+    d = a - b
+    return c, d
+
+
+def _self_alias(n):
+    a = np.arange(n)
+    a[:] += 3 * np.flip(a)
+    return a
+
+
+def _atleast_2d_then_transpose(m, rowvar):
+    m_arr = np.atleast_2d(m)
+    if not rowvar:
+        m_arr = m_arr.T
+    return m_arr
+
+
+_F32, _I32 = np.float32, np.int32
+_BODIES = [
+    # bodies of the reference's array tests (numba_mlir/mlir/tests/test_numpy.py), on shape-only arrays
+    (_batchnorm, [((8, 14, 14, 32), _F32)], ()),
+    (_write_through_a_view, [((12,), np.int64), ((12,), np.int64)], ()),
+    (_self_alias, [], (1000,)),
+    (_atleast_2d_then_transpose, [((4, 5), _F32)], (False,)),
+    (lambda a, b, c: np.dot(a, b, out=c), [((8, 16), _F32), ((16, 8), _F32), ((8, 8), _F32)], ()),
+    (lambda a: a * np.pi + np.e, [((16,), _F32)], ()),
+    (lambda a, b: a.size / b, [((2, 3, 1), _F32)], (3,)),
+    (lambda a: np.sum(a, dtype=np.int16, axis=0), [((4, 5), _I32)], ()),
+    (lambda a: np.prod(a, dtype=np.int16), [((4, 5), _I32)], ()),
+    (lambda a: np.mean(a, axis=0, keepdims=True) + np.var(a, axis=0), [((4, 8), _F32)], ()),
+    (lambda a: np.std(a) + a.sum(axis=0), [((4, 8), _F32)], ()),
+    (lambda a: a ** 2 + a ** 0.5, [((16,), _F32)], ()),
+    (lambda a: a.astype(np.int32), [((16,), _F32)], ()),
+    (lambda a: a[::-1] + a[1:3, None].sum(), [((16,), _F32)], ()),
+    (lambda a: a[1:3, :, ::2] * 2 + a[..., 0][1:3, :, None], [((4, 5, 6), _F32)], ()),
+    (lambda a, b: a // b + a % b, [((16,), _F32), ((16,), _F32)], ()),
+    (lambda a, b: (a << 1) + (b >> 1) + (a & b) + (a | b) + (a ^ b) + ~a, [((16,), _I32), ((16,), _I32)], ()),
+    (lambda a, b: np.logical_and(a > 0, b > 0) | np.logical_not(a > b), [((16,), _F32), ((16,), _F32)], ()),
+    (lambda a: np.any(a > 0) & np.all(a > 0), [((16,), _F32)], ()),
+    (lambda a: np.count_nonzero(a) + np.argmax(a), [((4, 16), _F32)], ()),
+    (lambda a: np.tanh(a) + np.arctan2(a, a) + np.hypot(a, a) + np.floor(a) + np.ceil(a) + np.trunc(a)
+     + np.sign(a), [((16,), _F32)], ()),
+    (lambda a: np.isfinite(a) | np.isinf(a) | np.isnan(a), [((16,), _F32)], ()),
+    (lambda a: a.flatten() + np.ravel(a) + a.reshape(-1), [((4, 4), _F32)], ()),
+    (lambda a: (a + a.size + a.itemsize + a.strides[0] + len(a), a.shape, a.T), [((8, 16), _F32)], ()),
+    (lambda a, m: a[m] + a[m[::-1]], [((16,), _F32), ((3,), _I32)], ()),
+]
+
+
+@pytest.mark.parametrize("case", range(len(_BODIES)))
+def test_bodies_of_the_reference_array_tests_trace_and_compile(runtime_lib, case):
+    py_func, arrays, scalars = _BODIES[case]
+    _trace_and_compile(py_func, arrays, scalars)
+
+
 def test_argmin_of_a_chain_along_the_last_axis_is_one_kernel(runtime_lib):
     """np.argmin / np.argmax of an elementwise chain along the last axis is
     one generated kernel (a warp per row keeps value and position); along
