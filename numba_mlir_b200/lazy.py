@@ -747,6 +747,41 @@ class LazyArray:
             return out
         if func is np.shape:
             return self.shape
+        if func is np.transpose and len(args) == 2 and not kwargs and args[1] is not None:
+            a = args[0]
+            axes = tuple(int(x) % a.ndim for x in args[1])
+            if sorted(axes) != list(range(a.ndim)):
+                raise ValueError("axes don't match array")
+            return a._view(("transpose", axes), lambda x: _permuted(x, axes))
+        if func is np.swapaxes and len(args) == 3 and not kwargs:
+            a = args[0]
+            axes = list(range(a.ndim))
+            i, j = int(args[1]) % a.ndim, int(args[2]) % a.ndim
+            axes[i], axes[j] = axes[j], axes[i]
+            return a._view(("transpose", tuple(axes)), lambda x: _permuted(x, axes))
+        if func is np.expand_dims and len(args) == 2 and not kwargs:
+            a = args[0]
+            new = args[1] if isinstance(args[1], (tuple, list)) else (args[1],)
+            nd = a.ndim + len(new)
+            new = {int(x) % nd for x in new}
+            return a[tuple(None if d in new else slice(None) for d in range(nd))]
+        if func is np.squeeze and len(args) == 1 and set(kwargs) <= {"axis"}:
+            a = args[0]
+            axis = kwargs.get("axis")
+            drop = {d for d in range(a.ndim) if a.shape[d] == 1} if axis is None else \
+                {int(x) % a.ndim for x in (axis if isinstance(axis, (tuple, list)) else (axis,))}
+            if any(a.shape[d] != 1 for d in drop):
+                raise ValueError("cannot select an axis to squeeze out which has size not equal to one")
+            if not drop:
+                return a
+            return a._view(("getitem", tuple(0 if d in drop else slice(None) for d in range(a.ndim))),
+                           lambda x: x[tuple(0 if d in drop else slice(None) for d in range(a.ndim))])
+        if func is np.broadcast_to and len(args) == 2 and not kwargs:
+            a = args[0]
+            shape = tuple(int(d) for d in (args[1] if isinstance(args[1], (tuple, list)) else (args[1],)))
+            if tuple(broadcast_shapes(a.shape, shape)) != shape:
+                raise ValueError(f"cannot broadcast {a.shape} to {shape}")
+            return a._view(("broadcast", shape), lambda x: _broadcast(x, shape))
         if func is np.atleast_2d and len(args) == 1 and not kwargs:
             a = args[0]
             if a.ndim >= 2:
@@ -2176,7 +2211,7 @@ class Plan:
                     arr = args[s[1]]
                 elif s[0] == "view":
                     base, op = get(s[1]), s[2]
-                    arr = base.T if op[0] == "T" else base.reshape(op[1]) if op[0] == "reshape" else base[op[1]]
+                    arr = _apply_view(base, op)
                 else:
                     raise RuntimeError("plan slot used before its allocation")
                 arrays[i] = arr
@@ -2263,6 +2298,32 @@ def signature_of(args):
 
 
 _fake_addresses = itertools.count(0x7F0000000000, 1 << 36)
+
+
+def _permuted(arr, axes):
+    return DeviceArray(arr._buf, [arr.shape[i] for i in axes], arr.dtype, [arr.strides[i] for i in axes],
+                       arr._offset)
+
+
+def _broadcast(arr, shape):
+    """View of `arr` with the extent `shape`: new and stretched axes get stride 0."""
+    lead = len(shape) - arr.ndim
+    strides = [0] * lead + [0 if d == 1 and shape[lead + i] != 1 else st
+                            for i, (d, st) in enumerate(zip(arr.shape, arr.strides))]
+    return DeviceArray(arr._buf, shape, arr.dtype, strides, arr._offset)
+
+
+def _apply_view(base, op):
+    """The view `op` (recorded by LazyArray._view) of a new base array."""
+    if op[0] == "T":
+        return base.T
+    if op[0] == "reshape":
+        return base.reshape(op[1])
+    if op[0] == "transpose":
+        return _permuted(base, op[1])
+    if op[0] == "broadcast":
+        return _broadcast(base, op[1])
+    return base[op[1]]
 
 
 def fake_array(shape, dtype, ptr=None):

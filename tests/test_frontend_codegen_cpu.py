@@ -248,6 +248,11 @@ _BODIES = [
     (lambda a: a.flatten() + np.ravel(a) + a.reshape(-1), [((4, 4), _F32)], ()),
     (lambda a: (a + a.size + a.itemsize + a.strides[0] + len(a), a.shape, a.T), [((8, 16), _F32)], ()),
     (lambda a, m: a[m] + a[m[::-1]], [((16,), _F32), ((3,), _I32)], ()),
+    # axis views: new, dropped, permuted and stretched axes
+    (lambda a: np.expand_dims(a, 0) + np.expand_dims(a, -1), [((16,), _F32)], ()),
+    (lambda a: np.squeeze(a * 2, axis=0) + np.squeeze(a, axis=(0, 2))[:, None], [((1, 16, 1), _F32)], ()),
+    (lambda a: np.broadcast_to(a, (3, 4, 5)) * 2, [((4, 1), _F32)], ()),
+    (lambda a: np.swapaxes(a, 0, 2) + np.transpose(a, (2, 1, 0)), [((3, 4, 5), _F32)], ()),
 ]
 
 

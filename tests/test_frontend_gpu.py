@@ -621,6 +621,36 @@ def test_indexing_with_an_index_array(queue, offset):
         assert len(take._plans) == 1
 
 
+def test_axis_views(queue):
+    """np.expand_dims, squeeze, swapaxes, transpose with axes and broadcast_to
+    are views (new axes, dropped axes, permuted or zero strides) that the
+    chains read in place; the second call replays the recorded plan."""
+    import numba_mlir_b200 as nm
+
+    rng = np.random.default_rng(12)
+    v = rng.standard_normal(16).astype(np.float32)
+    m = rng.standard_normal((4, 1)).astype(np.float32)
+    t = rng.standard_normal((3, 4, 5)).astype(np.float32)
+    one = rng.standard_normal((1, 16, 1)).astype(np.float32)
+    cases = [
+        (lambda a: np.expand_dims(a, 0) + np.expand_dims(a, -1), v),
+        (lambda a: np.expand_dims(a + 1, (0, 2)) * 2, t[0]),
+        (lambda a: np.squeeze(a) + 1, one),
+        (lambda a: np.squeeze(a * 2, axis=0) + np.squeeze(a, axis=(0, 2))[:, None], one),
+        (lambda a: np.broadcast_to(a, (4, 16)) + 1, v),
+        (lambda a: np.broadcast_to(a, (3, 4, 5)) * 2, m),
+        (lambda a: np.swapaxes(a, 0, 2) + 1, t),
+        (lambda a: np.transpose(a, (1, 2, 0)) - np.transpose(a + 1, (1, 2, 0)), t),
+        (lambda a: np.swapaxes(a, -1, 1).sum(axis=0), t),
+    ]
+    for fn, x in cases:
+        f = nm.njit(fn)
+        for data in (x, (x * 3).astype(x.dtype)):
+            got, want = f(_dev(data)), fn(data)
+            assert got.shape == want.shape and got.dtype == want.dtype
+            np.testing.assert_allclose(got.copy_to_host(), want, rtol=1e-6)
+
+
 @pytest.mark.parametrize("i", list(range(-2, 3)))
 def test_scalar_arguments_and_computed_positions_as_indices(queue, i):
     """a[b] = 42; return a[b] with a scalar argument b (numba_mlir/mlir/tests/
