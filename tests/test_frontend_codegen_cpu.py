@@ -262,6 +262,22 @@ def test_bodies_of_the_reference_array_tests_trace_and_compile(runtime_lib, case
     _trace_and_compile(py_func, arrays, scalars)
 
 
+def test_view_operations_give_numpy_shapes_and_strides():
+    """The views a recorded plan re-applies to new arguments (transpose,
+    permutation, broadcast, indexing, reshape) have NumPy's shape and strides."""
+    from numba_mlir_b200 import lazy
+
+    host = np.zeros((3, 1, 5), np.float32)
+    dev = lazy.fake_array(host.shape, host.dtype)
+    for op, want in ((("T",), host.T),
+                     (("transpose", (2, 0, 1)), host.transpose(2, 0, 1)),
+                     (("broadcast", (4, 3, 6, 5)), np.broadcast_to(host, (4, 3, 6, 5))),
+                     (("getitem", (slice(1, None), 0, slice(None, None, -2))), host[1:, 0, ::-2]),
+                     (("reshape", (5, 3)), host.reshape(5, 3))):
+        got = lazy._apply_view(dev, op)
+        assert got.shape == want.shape and tuple(got.strides) == want.strides, op
+
+
 def test_argmin_of_a_chain_along_the_last_axis_is_one_kernel(runtime_lib):
     """np.argmin / np.argmax of an elementwise chain along the last axis is
     one generated kernel (a warp per row keeps value and position); along
